@@ -1,0 +1,106 @@
+"""ctypes loader for the native kernel library (``ops/lib/libob_kernels.so``).
+
+The library is built in-tree by :mod:`optimus_dl_b200.ops.build`. On a machine with a
+CUDA device the kernels are mandatory: if the library is missing it is built on the
+spot when ``nvcc`` exists, and otherwise loading fails loudly instead of falling back
+to eager PyTorch. On CPU-only machines ``available()`` is False and callers use their
+PyTorch reference implementations.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import threading
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from . import build as _build
+
+_lock = threading.Lock()
+_lib: ctypes.CDLL | None = None
+_status_bufs: dict[int, torch.Tensor] = {}
+
+
+class KernelError(RuntimeError):
+    """A launcher returned a non-zero code or a kernel reported a bounded-wait timeout."""
+
+
+def available() -> bool:
+    return torch.cuda.is_available()
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            path = _build.LIB_PATH
+            if not path.exists():
+                path = _build.build()
+            _lib = ctypes.CDLL(str(path))
+            _declare(_lib)
+    return _lib
+
+
+def ptr(t: torch.Tensor | None) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def status_word(device: torch.device | None = None) -> torch.Tensor:
+    """Per-device int32 word kernels write their error status into (0 = ok)."""
+    idx = torch.cuda.current_device() if device is None or device.index is None else device.index
+    buf = _status_bufs.get(idx)
+    if buf is None:
+        buf = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status_bufs[idx] = buf
+    return buf
+
+
+def check_status(device: torch.device | None = None) -> None:
+    """Synchronously read the status word; raise if a kernel reported a timeout."""
+    buf = status_word(device)
+    code = int(buf.item())
+    if code != 0:
+        buf.zero_()
+        names = {1: "mbarrier wait timed out", 2: "flag wait timed out", 3: "bad arguments"}
+        raise KernelError(f"kernel status {code}: {names.get(code, 'unknown')}")
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise KernelError(f"{what} failed with code {rc}")
+
+
+def _declare(l: ctypes.CDLL) -> None:
+    P, I, L, F = c_void_p, c_int, c_longlong, c_float
+
+    def sig(name, args):
+        fn = getattr(l, name, None)
+        if fn is not None:
+            fn.argtypes = args
+            fn.restype = c_int
+
+    sig("ob_gemm_bf16", [P, L, I, P, L, I, P, L, I, I, I, I, I, P, I, F, P, I, I, P, I, I, I, I, I, P, P])
+    sig("ob_gemm_swiglu_bf16", [P, L, P, P, L, P, P, P, L, I, I, I, P, P])
+    sig("ob_rmsnorm_fwd", [P, P, P, P, P, I, I, F, P])
+    sig("ob_rmsnorm_bwd", [P, P, P, P, P, P, P, I, I, P])
+    sig("ob_layernorm_fwd", [P, P, P, P, P, P, I, I, F, P])
+    sig("ob_layernorm_bwd", [P, P, P, P, P, P, P, P, P, I, I, P])
+    sig("ob_qknorm_rope", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P])
+    sig("ob_swiglu_fwd", [P, P, P, L, P])
+    sig("ob_swiglu_bwd", [P, P, P, P, P, P, L, P])
+    sig("ob_adamw", [P, P, P, P, P, L, F, F, F, F, F, F, F, P, I, P])
+    sig("ob_sumsq", [P, L, I, P, P])
+    sig("ob_ce_partial", [P, L, P, P, P, P, I, I, I, I, F, I, P])
+    sig("ob_ce_finalize", [P, P, P, P, P, P, P, I, I, F, P])
+    sig("ob_ce_grad", [P, L, P, P, P, P, I, I, I, I, F, F, I, F, P])
+    sig("ob_embedding_fwd", [P, P, P, L, I, P])
+    sig("ob_embedding_bwd", [P, P, P, L, I, I, P])
+    sig("ob_attn_fwd", [P, P, P, P, P, P, P, I, I, I, I, I, F, I, I, P, P])
+    sig("ob_attn_bwd", [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, I, I, P, P])

@@ -1,0 +1,385 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a.
+//
+//   C[M,N] = epilogue( A[M,K] * B[N,K]^T )
+//
+// Operands arrive through TMA into 128-byte-swizzled shared-memory tiles, the
+// product is accumulated by tcgen05.mma into TMEM (two 128x256 fp32 accumulators,
+// so that the epilogue of tile i overlaps the main loop of tile i+1), and the
+// epilogue reads TMEM with tcgen05.ld.
+//
+// Either operand may be "K-major" (reduction dimension contiguous in global
+// memory: A stored [M,K], B stored [N,K]) or "MN-major" (A stored [K,M], B stored
+// [K,N]).  With both forms available the forward (x W^T), input-gradient (dy W)
+// and weight-gradient (dy^T x) products of a linear layer run without a transpose.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM
+// owner, warps 2..5 = epilogue (each owns the TMEM lane quarter warp_id % 4).
+#pragma once
+#include "common.cuh"
+
+namespace ob {
+namespace gemm {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;      // one 128-byte swizzle atom of bf16 along K
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int ACC_STAGES = 2;
+constexpr int NUM_THREADS = 192;
+constexpr int A_TILE_BYTES = BM * BK * 2;   // 16 KB
+constexpr int B_TILE_BYTES = BN * BK * 2;   // 32 KB
+constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int GROUP_M = 16;
+
+enum Act : int { kActNone = 0, kActGelu = 1, kActRelu2 = 2, kActSilu = 3 };
+
+struct Params {
+  int M, N, K;
+  void* C;               // output, row-major [M, ldc]
+  long long ldc;
+  int out_fp32;          // 0: bf16 output, 1: fp32 output
+  int accumulate;        // 1: C += result (same dtype as output)
+  const void* bias;      // optional [N] (bf16), added before the activation
+  int act;               // Act
+  float alpha;           // scale applied to the accumulator
+  // SwiGLU mode (template flag): B tile = 128 rows of B (gate) followed by 128 rows
+  // of B2 (up); outputs h = silu(g)*u to C (width N) and, when set, g and u.
+  void* G;
+  void* U;
+  // Optional readiness flags, one per group of `flag_rows` rows of the B operand
+  // (K-major B only).  The producer waits until flags[row / flag_rows] >= flag_value
+  // before it loads a B tile.  Used by kernels that land B in local memory from
+  // peers while the product runs.
+  const int* b_flags;
+  int flag_rows;
+  int flag_value;
+  // Same for the A operand (rows of A), K-major A only.
+  const int* a_flags;
+  int a_flag_rows;
+  int a_flag_value;
+  int* status;           // error word (see StatusCode)
+  int tile_order;        // 0: grouped-M raster, 1: flag-friendly order starting at first_n_tile
+  int first_tile_shift;  // rotates the n-tile (or m-tile) order so locally owned chunks go first
+};
+
+struct TileCoord {
+  int m, n;
+};
+
+__device__ __forceinline__ TileCoord tile_coord(int tile, int tiles_m, int tiles_n, const Params& p) {
+  TileCoord c;
+  if (p.tile_order == 1) {
+    // n-major order (all m-tiles of one n-tile before the next), rotated: tiles that
+    // read rows already resident run first while the rest is still arriving.
+    int n = tile / tiles_m;
+    c.m = tile - n * tiles_m;
+    c.n = (n + p.first_tile_shift) % tiles_n;
+    return c;
+  }
+  if (p.tile_order == 2) {
+    // m-major rotated order, for a gathered A operand.
+    int m = tile / tiles_n;
+    c.n = tile - m * tiles_n;
+    c.m = (m + p.first_tile_shift) % tiles_m;
+    return c;
+  }
+  const int per_group = GROUP_M * tiles_n;
+  const int g = tile / per_group;
+  const int first_m = g * GROUP_M;
+  const int gm = min(GROUP_M, tiles_m - first_m);
+  const int r = tile - g * per_group;
+  c.m = first_m + (r % gm);
+  c.n = r / gm;
+  return c;
+}
+
+__device__ __forceinline__ bool wait_flag(const int* flag, int value, volatile int* abort_flag, int* status) {
+  for (uint32_t it = 0; it < (1u << 26); ++it) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v >= value) return true;
+    if ((it & 0x3f) == 0x3f) {
+      if (*abort_flag) return false;
+      __nanosleep(64);
+    }
+  }
+  *abort_flag = 1;
+  if (status) atomicCAS(status, kStatusOk, kStatusFlagTimeout);
+  return false;
+}
+
+__device__ __forceinline__ float apply_act(float x, int act) {
+  switch (act) {
+    case kActGelu: return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
+    case kActRelu2: { float r = fmaxf(x, 0.0f); return r * r; }
+    case kActSilu: return x / (1.0f + __expf(-x));
+    default: return x;
+  }
+}
+
+// One CTA's share of the persistent GEMM. `first_tile`/`tile_stride` give the static
+// tile schedule (callers with extra non-GEMM CTAs pass the GEMM CTA index and count).
+template <int A_MN, int B_MN, int SWIGLU>
+__device__ __forceinline__ void gemm_cta(const CUtensorMap* tmA, const CUtensorMap* tmB, const CUtensorMap* tmB2,
+                                         const Params& p, int first_tile, int tile_stride, uint8_t* smem_raw) {
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full_bar = bars;                          // [STAGES]
+  uint64_t* empty_bar = bars + STAGES;                // [STAGES]
+  uint64_t* acc_full = bars + 2 * STAGES;             // [ACC_STAGES]
+  uint64_t* acc_empty = bars + 2 * STAGES + ACC_STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * ACC_STAGES);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_n = (p.N + (SWIGLU ? BN / 2 : BN) - 1) / (SWIGLU ? BN / 2 : BN);
+  const int num_tiles = tiles_m * tiles_n;
+  const int k_tiles = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int a = 0; a < ACC_STAGES; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(tmA);
+      tma_prefetch_desc(tmB);
+      if (SWIGLU) tma_prefetch_desc(tmB2);
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride) {
+        TileCoord tc = tile_coord(tile, tiles_m, tiles_n, p);
+        const int m0 = tc.m * BM;
+        const int n0 = tc.n * (SWIGLU ? BN / 2 : BN);
+        if (p.b_flags) {
+          const int f0 = n0 / p.flag_rows;
+          const int f1 = (min(n0 + (SWIGLU ? BN / 2 : BN), p.N) - 1) / p.flag_rows;
+          for (int f = f0; f <= f1 && ok; ++f) ok = wait_flag(p.b_flags + f, p.flag_value, abort_flag, p.status);
+        }
+        if (p.a_flags) {
+          const int f0 = m0 / p.a_flag_rows;
+          const int f1 = (min(m0 + BM, p.M) - 1) / p.a_flag_rows;
+          for (int f = f0; f <= f1 && ok; ++f) ok = wait_flag(p.a_flags + f, p.a_flag_value, abort_flag, p.status);
+        }
+        for (int kt = 0; kt < k_tiles && ok; ++kt) {
+          ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status);
+          if (!ok) break;
+          uint8_t* sA = smem + stage * STAGE_BYTES;
+          uint8_t* sB = sA + A_TILE_BYTES;
+          mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
+          const int k0 = kt * BK;
+          if (A_MN) {
+            // global A is [K, M]: boxes of 64 (m) x 64 (k), one per 64 columns of the tile
+            tma_load_2d(sA, tmA, &full_bar[stage], m0, k0);
+            tma_load_2d(sA + 8192, tmA, &full_bar[stage], m0 + 64, k0);
+          } else {
+            tma_load_2d(sA, tmA, &full_bar[stage], k0, m0);
+          }
+          if (SWIGLU) {
+            tma_load_2d(sB, tmB, &full_bar[stage], k0, n0);
+            tma_load_2d(sB + B_TILE_BYTES / 2, tmB2, &full_bar[stage], k0, n0);
+          } else if (B_MN) {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) tma_load_2d(sB + c * 8192, tmB, &full_bar[stage], n0 + c * 64, k0);
+          } else {
+            tma_load_2d(sB, tmB, &full_bar[stage], k0, n0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      // Drain: wait (bounded) until every stage this thread filled has been consumed, so
+      // that no copy is still in flight towards this CTA's shared memory at exit.
+      for (int s = 0; s < STAGES; ++s) {
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status)) break;
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      int stage = 0; uint32_t phase = 0;
+      int acc = 0; uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride) {
+        ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kt = 0; kt < k_tiles; ++kt) {
+          ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sA = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sB = sA + A_TILE_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            // K-major: step 32 bytes inside the swizzle atom; MN-major: step 16 k-rows of 128 bytes.
+            const uint64_t da = A_MN ? make_smem_desc_sw128(sA + kk * 2048, 8192, 1024)
+                                     : make_smem_desc_sw128(sA + kk * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc_sw128(sB + kk * 2048, 8192, 1024)
+                                     : make_smem_desc_sw128(sB + kk * 32, 16, 1024);
+            umma_f16_ss(d_tmem, da, db, idesc, (kt | kk) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);   // frees this smem stage once the MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        umma_commit(&acc_full[acc]);        // accumulator complete
+        if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;            // TMEM lanes [32*quarter, 32*quarter+32)
+    int acc = 0; uint32_t acc_phase = 0;
+    bool ok = true;
+    const bool vec_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+    for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride) {
+      TileCoord tc = tile_coord(tile, tiles_m, tiles_n, p);
+      const int m0 = tc.m * BM;
+      const int n0 = tc.n * (SWIGLU ? BN / 2 : BN);
+      ok = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
+      if (SWIGLU) {
+        // columns [0,128) hold the gate product, [128,256) the up product
+#pragma unroll 1
+        for (int c = 0; c < 128; c += 32) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32(t_row + c, g);
+          tmem_ld_32x32(t_row + 128 + c, u);
+          tmem_ld_wait();
+          if (row < p.M) {
+            const int col = n0 + c;
+            __nv_bfloat16* hrow = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col;
+            __nv_bfloat16* grow = p.G ? reinterpret_cast<__nv_bfloat16*>(p.G) + (long long)row * p.ldc + col : nullptr;
+            __nv_bfloat16* urow = p.U ? reinterpret_cast<__nv_bfloat16*>(p.U) + (long long)row * p.ldc + col : nullptr;
+            if (vec_ok && col + 32 <= p.N) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint32_t hp[4], gp[4], up[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  // round the gate and up products to bf16 first, as the unfused path does
+                  float g0 = __bfloat162float(__float2bfloat16(__uint_as_float(g[v * 8 + 2 * j])));
+                  float g1 = __bfloat162float(__float2bfloat16(__uint_as_float(g[v * 8 + 2 * j + 1])));
+                  float u0 = __bfloat162float(__float2bfloat16(__uint_as_float(u[v * 8 + 2 * j])));
+                  float u1 = __bfloat162float(__float2bfloat16(__uint_as_float(u[v * 8 + 2 * j + 1])));
+                  gp[j] = pack_bf16x2(g0, g1);
+                  up[j] = pack_bf16x2(u0, u1);
+                  hp[j] = pack_bf16x2(g0 / (1.0f + __expf(-g0)) * u0, g1 / (1.0f + __expf(-g1)) * u1);
+                }
+                *reinterpret_cast<uint4*>(hrow + v * 8) = make_uint4(hp[0], hp[1], hp[2], hp[3]);
+                if (grow) *reinterpret_cast<uint4*>(grow + v * 8) = make_uint4(gp[0], gp[1], gp[2], gp[3]);
+                if (urow) *reinterpret_cast<uint4*>(urow + v * 8) = make_uint4(up[0], up[1], up[2], up[3]);
+              }
+            } else {
+              for (int j = 0; j < 32; ++j) {
+                if (col + j < p.N) {
+                  float g0 = __bfloat162float(__float2bfloat16(__uint_as_float(g[j])));
+                  float u0 = __bfloat162float(__float2bfloat16(__uint_as_float(u[j])));
+                  hrow[j] = __float2bfloat16(g0 / (1.0f + __expf(-g0)) * u0);
+                  if (grow) grow[j] = __float2bfloat16(g0);
+                  if (urow) urow[j] = __float2bfloat16(u0);
+                }
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          const int col = n0 + c;
+          if (col >= p.N) break;   // warp-uniform
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c, r);
+          tmem_ld_wait();
+          if (row < p.M) {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+            if (p.bias) {
+              const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(p.bias) + col;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) if (col + j < p.N) v[j] += __bfloat162float(b[j]);
+            }
+            if (p.act != kActNone) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.act);
+            }
+            if (p.out_fp32) {
+              float* crow = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col;
+              if ((p.ldc % 4 == 0) && col + 32 <= p.N && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0)) {
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                  float4 o = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                  if (p.accumulate) {
+                    float4 old = *reinterpret_cast<float4*>(crow + 4 * q);
+                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                  }
+                  *reinterpret_cast<float4*>(crow + 4 * q) = o;
+                }
+              } else {
+                for (int j = 0; j < 32; ++j)
+                  if (col + j < p.N) crow[j] = p.accumulate ? crow[j] + v[j] : v[j];
+              }
+            } else {
+              __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col;
+              if (vec_ok && col + 32 <= p.N) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  if (p.accumulate) {
+                    uint4 old = *reinterpret_cast<uint4*>(crow + 8 * q);
+                    float2 a0 = unpack_bf16x2(old.x), a1 = unpack_bf16x2(old.y), a2 = unpack_bf16x2(old.z),
+                           a3 = unpack_bf16x2(old.w);
+                    v[8 * q] += a0.x; v[8 * q + 1] += a0.y; v[8 * q + 2] += a1.x; v[8 * q + 3] += a1.y;
+                    v[8 * q + 4] += a2.x; v[8 * q + 5] += a2.y; v[8 * q + 6] += a3.x; v[8 * q + 7] += a3.y;
+                  }
+                  uint4 o = make_uint4(pack_bf16x2(v[8 * q], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
+                                       pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+                  *reinterpret_cast<uint4*>(crow + 8 * q) = o;
+                }
+              } else {
+                for (int j = 0; j < 32; ++j)
+                  if (col + j < p.N)
+                    crow[j] = __float2bfloat16(p.accumulate ? __bfloat162float(crow[j]) + v[j] : v[j]);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace gemm
+}  // namespace ob

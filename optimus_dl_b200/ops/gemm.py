@@ -1,0 +1,171 @@
+"""bf16 GEMM on the tcgen05 tensor cores, and the autograd ``linear`` built on it.
+
+``matmul_nt`` & friends call the persistent TMA + TMEM kernel in
+``csrc/gemm_core.cuh``. A linear layer needs three products; all run on the same
+kernel by choosing which operand is stored reduction-major:
+
+* forward   ``y  = x  @ W^T``  : A = x  [M,K] K-major,  B = W  [N,K] K-major
+* dgrad     ``dx = dy @ W``    : A = dy [M,N] K-major,  B = W  [N,K] read as MN-major
+* wgrad     ``dW = dy^T @ x``  : A = dy [M,N] read as MN-major, B = x [M,K] read as MN-major
+
+On CPU (tests, the fp32 oracle) the same functions fall back to ``torch.matmul``.
+Replaces the cuBLAS calls behind ``nn.Linear`` in the reference
+(optimus_dl/modules/model/blocks/attention.py:317-319,528; blocks/mlp.py:73-78).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+ACT = {"none": 0, "gelu": 1, "relu2": 2, "silu": 3}
+
+
+def _use_kernel(*ts: torch.Tensor) -> bool:
+    return all(t.is_cuda and t.dtype == torch.bfloat16 for t in ts)
+
+
+def _row_major_2d(t: torch.Tensor) -> torch.Tensor:
+    if t.dim() != 2:
+        t = t.reshape(-1, t.shape[-1])
+    if t.stride(1) != 1 or (t.stride(0) * t.element_size()) % 16 != 0 or t.data_ptr() % 16 != 0:
+        t = t.contiguous()
+    return t
+
+
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    *,
+    a_mn: bool = False,
+    b_mn: bool = False,
+    out: torch.Tensor | None = None,
+    out_dtype: torch.dtype = torch.bfloat16,
+    accumulate: bool = False,
+    bias: torch.Tensor | None = None,
+    act: str = "none",
+    alpha: float = 1.0,
+    b_flags: torch.Tensor | None = None,
+    flag_rows: int = 0,
+    flag_value: int = 0,
+    a_flags: torch.Tensor | None = None,
+    a_flag_rows: int = 0,
+    a_flag_value: int = 0,
+    tile_order: int = 0,
+    first_tile_shift: int = 0,
+    max_ctas: int = 0,
+) -> torch.Tensor:
+    """``C[M,N] = act(alpha * A B^T + bias)`` with bf16 inputs and fp32 accumulation.
+
+    ``a`` is ``[M,K]`` (or ``[K,M]`` when ``a_mn``); ``b`` is ``[N,K]`` (or ``[K,N]`` when
+    ``b_mn``). ``out`` may be bf16 or fp32; with ``accumulate`` the product is added to it.
+    """
+    a = _row_major_2d(a)
+    b = _row_major_2d(b)
+    M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+    N, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
+    if K != Kb:
+        raise ValueError(f"inner dimensions differ: {K} vs {Kb}")
+    if out is None:
+        if accumulate:
+            raise ValueError("accumulate needs an output tensor")
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    if out.shape != (M, N) or out.stride(1) != 1:
+        raise ValueError("bad output shape")
+    if not _use_kernel(a, b) or out.dtype not in (torch.bfloat16, torch.float32):
+        A = a.t() if a_mn else a
+        Bt = b if b_mn else b.t()
+        r = (A.float() @ Bt.float()) * alpha
+        if bias is not None:
+            r = r + bias.float()
+        if act == "gelu":
+            r = torch.nn.functional.gelu(r)
+        elif act == "relu2":
+            r = torch.relu(r) ** 2
+        elif act == "silu":
+            r = torch.nn.functional.silu(r)
+        if accumulate:
+            out.add_(r.to(out.dtype))
+        else:
+            out.copy_(r.to(out.dtype))
+        return out
+    l = _lib.lib()
+    rc = l.ob_gemm_bf16(
+        _lib.ptr(a), a.stride(0), int(a_mn), _lib.ptr(b), b.stride(0), int(b_mn),
+        _lib.ptr(out), out.stride(0), M, N, K, int(out.dtype == torch.float32), int(accumulate),
+        _lib.ptr(bias), ACT[act], float(alpha),
+        _lib.ptr(b_flags), int(flag_rows), int(flag_value),
+        _lib.ptr(a_flags), int(a_flag_rows), int(a_flag_value),
+        int(tile_order), int(first_tile_shift), int(max_ctas),
+        _lib.ptr(_lib.status_word(a.device)), _lib.stream(),
+    )
+    _lib.check(rc, "ob_gemm_bf16")
+    return out
+
+
+def matmul_nt(x: torch.Tensor, w: torch.Tensor, **kw) -> torch.Tensor:
+    """``x[M,K] @ w[N,K]^T``."""
+    return gemm(x, w, **kw)
+
+
+def matmul_nn(x: torch.Tensor, w: torch.Tensor, **kw) -> torch.Tensor:
+    """``x[M,K] @ w[K,N]``."""
+    return gemm(x, w, b_mn=True, **kw)
+
+
+def matmul_tn(x: torch.Tensor, y: torch.Tensor, **kw) -> torch.Tensor:
+    """``x[K,M]^T @ y[K,N]`` (the weight-gradient product)."""
+    return gemm(x, y, a_mn=True, b_mn=True, **kw)
+
+
+def swiglu_gemm(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, save_gu: bool = True):
+    """``h = silu(x w1^T) * (x w2^T)`` in one kernel; returns ``(h, g, u)`` (g, u None unless saved)."""
+    x2 = _row_major_2d(x)
+    M, K = x2.shape
+    N = w1.shape[0]
+    if not _use_kernel(x2, w1, w2) or w1.stride(0) != w2.stride(0):
+        g = (x2.float() @ w1.float().t()).to(x.dtype)
+        u = (x2.float() @ w2.float().t()).to(x.dtype)
+        h = (torch.nn.functional.silu(g.float()) * u.float()).to(x.dtype)
+        return h, (g if save_gu else None), (u if save_gu else None)
+    h = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    g = torch.empty_like(h) if save_gu else None
+    u = torch.empty_like(h) if save_gu else None
+    rc = _lib.lib().ob_gemm_swiglu_bf16(
+        _lib.ptr(x2), x2.stride(0), _lib.ptr(w1), _lib.ptr(w2), w1.stride(0), _lib.ptr(h), _lib.ptr(g), _lib.ptr(u),
+        h.stride(0), M, N, K, _lib.ptr(_lib.status_word(x.device)), _lib.stream(),
+    )
+    _lib.check(rc, "ob_gemm_swiglu_bf16")
+    return h, g, u
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        ctx.save_for_backward(x, w)
+        ctx.has_bias = bias is not None
+        shp = x.shape
+        y = gemm(x.reshape(-1, shp[-1]), w, bias=bias)
+        return y.view(*shp[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        x2 = x.reshape(-1, x.shape[-1])
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, b_mn=True).view_as(x)
+        if ctx.needs_input_grad[1]:
+            dw = gemm(dy2, x2, a_mn=True, b_mn=True)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(dy.dtype)
+        return dx, dw, db
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """Autograd-aware ``x @ w^T + bias``; tcgen05 kernel for CUDA bf16, ``F.linear`` otherwise."""
+    if _use_kernel(x, w) and (bias is None or bias.dtype == torch.bfloat16):
+        return _Linear.apply(x, w, bias)
+    return torch.nn.functional.linear(x, w, bias)
