@@ -1,0 +1,88 @@
+"""Self-attention blocks (optimus_dl/modules/model/blocks/attention.py:68-612).
+
+Same parameters (``wq, wk, wv, wo`` and optional ``q_norm, k_norm``) and the same forward
+signature; the computation is one fused QKV projection, QK-norm + RoPE and masked attention in
+``ops.attention.qkv_attention``, then the output projection. Full-width QK-norm (OLMo-3 style,
+``qk_norm_per_head=False``) normalises the q and k slices before the per-head path.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from ...ops import attention as attn_ops
+from ...ops import linear as lin_ops
+from .layer_norms import RMSNorm
+
+
+class BaseSelfAttention(nn.Module):
+    use_rope = False
+
+    def __init__(self, n_embd: int, n_head: int, n_kv_head: int | None = None, head_dim: int | None = None,
+                 dropout: float = 0.0, bias: bool = False, use_qk_norm: bool = False, qk_norm_per_head: bool = True,
+                 rmsnorm_eps: float = 1e-5, sliding_window: int | None = None):
+        super().__init__()
+        assert n_embd % n_head == 0, "n_embd must be divisible by n_head"
+        self.n_head = n_head
+        self.n_kv_head = n_kv_head if n_kv_head is not None else n_head
+        assert self.n_head % self.n_kv_head == 0, "n_head must be divisible by n_kv_head"
+        self.n_rep = self.n_head // self.n_kv_head
+        self.head_dim = head_dim or n_embd // n_head
+        self.n_embd = n_embd
+        self.dropout = dropout
+        self.use_qk_norm = use_qk_norm
+        self.qk_norm_per_head = qk_norm_per_head
+        self.sliding_window = sliding_window
+        self.rmsnorm_eps = rmsnorm_eps
+        self.wq = nn.Linear(n_embd, n_head * self.head_dim, bias=bias)
+        self.wk = nn.Linear(n_embd, self.n_kv_head * self.head_dim, bias=bias)
+        self.wv = nn.Linear(n_embd, self.n_kv_head * self.head_dim, bias=bias)
+        self.wo = nn.Linear(n_head * self.head_dim, n_embd, bias=bias)
+        if use_qk_norm:
+            qd = self.head_dim if qk_norm_per_head else n_head * self.head_dim
+            kd = self.head_dim if qk_norm_per_head else self.n_kv_head * self.head_dim
+            self.q_norm = RMSNorm(qd, eps=rmsnorm_eps)
+            self.k_norm = RMSNorm(kd, eps=rmsnorm_eps)
+        self.resid_dropout = nn.Dropout(dropout) if dropout > 0 else None
+        # tensor-parallel state, set by parallel.tp: local head counts and the group
+        self.tp_group = None
+
+    def forward(self, x: torch.Tensor, freqs_cis: torch.Tensor | None = None, seq_lens: torch.Tensor | None = None,
+                document_ids: torch.Tensor | None = None, position_ids: torch.Tensor | None = None,
+                cu_seqlens: torch.Tensor | None = None, max_seqlen: int | None = None,
+                doc_start: torch.Tensor | None = None) -> torch.Tensor:
+        B, T, _ = x.shape
+        if cu_seqlens is not None:
+            assert B == 1, f"cu_seqlens is only supported for flat batches (B=1), but got B={B}"
+            assert cu_seqlens.ndim == 1, f"cu_seqlens must be a 1D tensor, got ndim={cu_seqlens.ndim}"
+        if doc_start is None:
+            doc_start = attn_ops.build_doc_start(B, T, x.device, document_ids, cu_seqlens)
+        biases = [self.wq.bias, self.wk.bias, self.wv.bias]
+        qkv = lin_ops.multi_linear(x, [self.wq.weight, self.wk.weight, self.wv.weight], biases)
+        Hq, Hk, hd = self.n_head, self.n_kv_head, self.head_dim
+        qw = kw = None
+        if self.use_qk_norm:
+            if self.qk_norm_per_head:
+                qw, kw = self.q_norm.weight, self.k_norm.weight
+            else:
+                q, k, v = qkv.split([Hq * hd, Hk * hd, Hk * hd], dim=-1)
+                qkv = torch.cat([self.q_norm(q.contiguous()), self.k_norm(k.contiguous()), v], dim=-1)
+        y = attn_ops.qkv_attention(qkv, n_head=Hq, n_kv_head=Hk, head_dim=hd, doc_start=doc_start,
+                                   freqs_cis=freqs_cis if self.use_rope else None,
+                                   position_ids=position_ids if self.use_rope else None, q_norm_weight=qw,
+                                   k_norm_weight=kw, norm_eps=self.rmsnorm_eps, window=self.sliding_window)
+        y = lin_ops.linear(y, self.wo.weight, self.wo.bias)
+        return self.resid_dropout(y) if self.resid_dropout is not None else y
+
+
+class CausalSelfAttention(BaseSelfAttention):
+    """GPT-2 attention: built from a config with ``n_embd, n_head, dropout, bias`` and no RoPE."""
+
+    def __init__(self, config):
+        super().__init__(n_embd=config.n_embd, n_head=config.n_head, n_kv_head=None,
+                         head_dim=getattr(config, "head_dim", None), dropout=config.dropout, bias=config.bias)
+
+
+class RotarySelfAttention(BaseSelfAttention):
+    use_rope = True

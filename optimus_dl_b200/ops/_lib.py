@@ -88,19 +88,20 @@ def _declare(l: ctypes.CDLL) -> None:
 
     sig("ob_gemm_bf16", [P, L, I, P, L, I, P, L, I, I, I, I, I, P, I, F, P, I, I, P, I, I, I, I, I, P, P])
     sig("ob_gemm_swiglu_bf16", [P, L, P, P, L, P, P, P, L, I, I, I, P, P])
-    sig("ob_rmsnorm_fwd", [P, P, P, P, P, I, I, F, P])
-    sig("ob_rmsnorm_bwd", [P, P, P, P, P, P, P, I, I, P])
+    sig("ob_rmsnorm_fwd", [P, P, P, P, P, P, I, I, F, P])
+    sig("ob_rmsnorm_bwd", [P, P, P, P, P, P, P, P, P, I, I, I, P])
+    sig("ob_norm_bwd_grid", [I])
     sig("ob_layernorm_fwd", [P, P, P, P, P, P, I, I, F, P])
     sig("ob_layernorm_bwd", [P, P, P, P, P, P, P, P, P, I, I, P])
-    sig("ob_qknorm_rope", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P])
+    sig("ob_rope_grid", [L])
+    sig("ob_qknorm_rope_fwd", [P, P, L, L, P, P, P, P, P, I, I, I, I, I, F, P])
+    sig("ob_qknorm_rope_bwd", [P, P, L, L, P, L, P, P, P, P, P, P, I, I, I, I, I, P])
     sig("ob_swiglu_fwd", [P, P, P, L, P])
     sig("ob_swiglu_bwd", [P, P, P, P, P, P, L, P])
-    sig("ob_adamw", [P, P, P, P, P, L, F, F, F, F, F, F, F, P, I, P])
-    sig("ob_sumsq", [P, L, I, P, P])
-    sig("ob_ce_partial", [P, L, P, P, P, P, I, I, I, I, F, I, P])
-    sig("ob_ce_finalize", [P, P, P, P, P, P, P, I, I, F, P])
-    sig("ob_ce_grad", [P, L, P, P, P, P, I, I, I, I, F, F, I, F, P])
-    sig("ob_embedding_fwd", [P, P, P, L, I, P])
-    sig("ob_embedding_bwd", [P, P, P, L, I, I, P])
-    sig("ob_attn_fwd", [P, P, P, P, P, P, P, I, I, I, I, I, F, I, I, P, P])
-    sig("ob_attn_bwd", [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, I, I, P, P])
+    sig("ob_adamw", [P, P, P, P, I, P, L, F, F, F, F, F, F, F, F, P, F, P])
+    sig("ob_sumsq", [P, L, I, P, P, I, P])
+    sig("ob_embedding_fwd", [P, P, P, L, I, I, P])
+    sig("ob_embedding_bwd", [P, P, P, P, L, I, I, I, I, P])
+    sig("ob_add_f32_to_bf16", [P, P, L, I, P])
+    sig("ob_ce_stats", [P, L, P, P, P, P, P, P, P, I, I, I, I, F, P])
+    sig("ob_ce_grad", [P, L, P, P, I, I, I, I, L, F, P, F, I, F, P])

@@ -1,0 +1,164 @@
+"""Chunked fused linear + cross-entropy.
+
+``linear_cross_entropy(x, W, targets)`` computes ``mean CE(x W^T, targets)`` without ever
+holding the ``[tokens, vocab]`` logits: rows are processed in chunks; each chunk's logits come
+from the tcgen05 GEMM, two kernels (``csrc/ce.cu``) turn them into per-row statistics and then,
+in place, into ``d loss / d logits``; two more GEMMs give ``dX`` and accumulate ``dW``. The
+backward pass therefore only rescales the stored gradients.
+
+With a tensor-parallel group the weight is a vocabulary shard ``[V/tp, d]``; ranks exchange
+``(max, sum-exp, target logit, sum of logits, arg max)`` per row (5 floats) instead of logits.
+
+Loss definition (ignore index, label smoothing, tanh / sigmoid soft-capping, mean over valid
+targets) follows optimus_dl/modules/criterion/cross_entropy.py:191-267 of the reference.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib, gemm
+
+SOFTCAP = {None: 0, "none": 0, "tanh": 1, "sigmoid": 2}
+
+
+def apply_softcap(logits: torch.Tensor, softcap: float | None, softcap_type: str = "tanh") -> torch.Tensor:
+    if softcap is None and softcap_type != "sigmoid":
+        return logits
+    if softcap_type == "sigmoid":
+        return 23.0 * torch.sigmoid((logits + 5.0) / 7.5)
+    return softcap * torch.tanh(logits / softcap)
+
+
+@dataclass
+class CEResult:
+    loss: torch.Tensor          # mean over valid targets (scalar, fp32, differentiable)
+    n_valid: torch.Tensor       # number of non-ignored targets (scalar, int64)
+    n_correct: torch.Tensor     # arg-max hits among valid targets (scalar, int64)
+    loss_sum: torch.Tensor      # sum of per-token losses (scalar, fp32, detached)
+
+
+def cross_entropy_ref(logits: torch.Tensor, targets: torch.Tensor, ignore_index: int = -100,
+                      label_smoothing: float = 0.0, softcap: float | None = None, softcap_type: str = "tanh") -> CEResult:
+    """fp32 PyTorch reference on materialised logits ``[rows, V]``."""
+    z = logits.float()
+    if softcap is not None or softcap_type == "sigmoid":
+        z = apply_softcap(z, softcap, softcap_type)
+    valid = targets != ignore_index
+    loss_sum = F.cross_entropy(z, targets, ignore_index=ignore_index, label_smoothing=label_smoothing, reduction="sum")
+    n_valid = valid.sum()
+    n_correct = ((z.argmax(-1) == targets) & valid).sum()
+    return CEResult(loss_sum / n_valid.clamp(min=1), n_valid, n_correct, loss_sum.detach())
+
+
+class _LinearCE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, targets, ignore_index, smoothing, softcap, softcap_type, chunk_rows, tp_group,
+                vocab_offset, total_vocab):
+        l = _lib.lib()
+        dev = x.device
+        d = x.shape[-1]
+        x2 = x.reshape(-1, d)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        tg = targets.reshape(-1).to(torch.int64).contiguous()
+        T = x2.shape[0]
+        V = weight.shape[0]
+        total_vocab = total_vocab or V
+        mode = SOFTCAP["sigmoid" if softcap_type == "sigmoid" else ("tanh" if softcap is not None else None)]
+        cap_c = float(softcap) if softcap is not None else 1.0
+        valid = tg != ignore_index
+        n_valid = valid.sum()
+        inv_n = (1.0 / n_valid.clamp(min=1).float()).reshape(1)
+        need_dx = ctx.needs_input_grad[0]
+        need_dw = ctx.needs_input_grad[1]
+        dx = torch.empty_like(x2) if need_dx else None
+        dw = torch.empty_like(weight) if need_dw else None
+        ld = (V + 7) // 8 * 8
+        chunk_rows = min(chunk_rows, T)
+        logits_buf = torch.empty((chunk_rows, ld), dtype=torch.bfloat16, device=dev)
+        stats = torch.empty((5, T), dtype=torch.float32, device=dev)
+        best_idx = torch.empty(T, dtype=torch.int32, device=dev)
+        lse_all = torch.empty(T, dtype=torch.float32, device=dev)
+        first = True
+        for r0 in range(0, T, chunk_rows):
+            r1 = min(T, r0 + chunk_rows)
+            rows = r1 - r0
+            lg = logits_buf[:rows, :V] if ld == V else logits_buf[:rows]
+            out_view = logits_buf[:rows].as_strided((rows, V), (ld, 1))
+            gemm.gemm(x2[r0:r1], weight, out=out_view)
+            st = stats[:, r0:r1]
+            rc = l.ob_ce_stats(_lib.ptr(out_view), ld, _lib.ptr(tg[r0:r1]), _lib.ptr(st[0]), _lib.ptr(st[1]),
+                               _lib.ptr(st[2]), _lib.ptr(st[3]), _lib.ptr(st[4]), _lib.ptr(best_idx[r0:r1]), rows, V,
+                               int(vocab_offset), mode, cap_c, _lib.stream())
+            _lib.check(rc, "ob_ce_stats")
+            mx, se, sz, zt, bv = st[0], st[1], st[2], st[3], st[4]
+            if tp_group is not None:
+                import torch.distributed as dist
+
+                ws = dist.get_world_size(tp_group)
+                pack = torch.stack([mx, se, sz, zt, bv, best_idx[r0:r1].float()], 0).contiguous()
+                allp = torch.empty((ws, *pack.shape), dtype=pack.dtype, device=dev)
+                dist.all_gather_into_tensor(allp, pack, group=tp_group)
+                gmx = allp[:, 0].max(0).values
+                gse = (allp[:, 1] * torch.exp(allp[:, 0] - gmx)).sum(0)
+                sz = allp[:, 2].sum(0)
+                zt = allp[:, 3].sum(0)
+                bi = allp[:, 4].argmax(0, keepdim=True)
+                best_idx[r0:r1] = allp[:, 5].gather(0, bi).squeeze(0).to(torch.int32)
+                mx, se = gmx, gse
+                stats[2, r0:r1] = sz
+                stats[3, r0:r1] = zt
+            lse = mx + torch.log(se)
+            lse_all[r0:r1] = lse
+            if need_dx or need_dw:
+                rc = l.ob_ce_grad(_lib.ptr(out_view), ld, _lib.ptr(tg[r0:r1]), _lib.ptr(lse), rows, V, int(vocab_offset),
+                                  int(total_vocab), int(ignore_index), float(smoothing), _lib.ptr(inv_n), 1.0, mode,
+                                  cap_c, _lib.stream())
+                _lib.check(rc, "ob_ce_grad")
+                if need_dx:
+                    gemm.gemm(out_view, weight, b_mn=True, out=dx[r0:r1])
+                if need_dw:
+                    gemm.gemm(out_view, x2[r0:r1], a_mn=True, b_mn=True, out=dw, accumulate=not first)
+            first = False
+        zt_all, sz_all = stats[3], stats[2]
+        per_tok = lse_all - (1.0 - smoothing) * zt_all - smoothing * sz_all / total_vocab
+        per_tok = torch.where(valid, per_tok, torch.zeros_like(per_tok))
+        loss_sum = per_tok.sum()
+        loss = loss_sum * inv_n[0]
+        n_correct = ((best_idx.to(torch.int64) == tg) & valid).sum()
+        if need_dx and tp_group is not None:
+            import torch.distributed as dist
+
+            dist.all_reduce(dx, group=tp_group)
+        ctx.save_for_backward(dx if need_dx else torch.empty(0), dw if need_dw else torch.empty(0))
+        ctx.x_shape = x.shape
+        ctx.flags = (need_dx, need_dw)
+        ctx.mark_non_differentiable(n_valid, n_correct, loss_sum)
+        return loss, n_valid, n_correct, loss_sum
+
+    @staticmethod
+    def backward(ctx, dloss, *_):
+        dx, dw = ctx.saved_tensors
+        need_dx, need_dw = ctx.flags
+        gx = (dx * dloss.to(dx.dtype)).view(ctx.x_shape) if need_dx else None
+        gw = dw * dloss.to(dw.dtype) if need_dw else None
+        return gx, gw, None, None, None, None, None, None, None, None, None
+
+
+def linear_cross_entropy(x: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor, *, ignore_index: int = -100,
+                         label_smoothing: float = 0.0, softcap: float | None = None, softcap_type: str = "tanh",
+                         chunk_rows: int = 4096, tp_group=None, vocab_offset: int = 0,
+                         total_vocab: int | None = None) -> CEResult:
+    """Mean cross-entropy of ``x @ weight^T`` against ``targets`` (see module docstring)."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0:
+        loss, n_valid, n_correct, loss_sum = _LinearCE.apply(x, weight, targets, ignore_index, label_smoothing, softcap,
+                                                             softcap_type, chunk_rows, tp_group, vocab_offset, total_vocab)
+        return CEResult(loss, n_valid, n_correct, loss_sum)
+    if tp_group is not None:
+        raise NotImplementedError("vocabulary-parallel loss needs the CUDA bf16 path")
+    logits = F.linear(x.reshape(-1, x.shape[-1]), weight)
+    return cross_entropy_ref(logits, targets.reshape(-1), ignore_index, label_smoothing, softcap, softcap_type)
