@@ -1,0 +1,225 @@
+"""Flagship benchmark: Llama-3-8B bf16 training throughput (tokens/s) under this framework's
+fully-sharded engine, on N GPUs of one node.
+
+    python bench.py --gpus 1 --steps 8 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29501 bench.py --gpus 8 --steps 8 --warmup 3
+
+Prints ONE JSON line (rank 0). ``value`` is device-timed (CUDA events bracketed by a barrier and a
+synchronize, max over ranks) over exactly ``--steps`` optimizer steps, each a full forward,
+backward, gradient reduce-scatter and sharded AdamW update of the named model on synthetic
+uniform-random token ids with random-init weights. ``e2e`` repeats the measurement through the
+same public calls a training script makes, adding the per-step host->device copy of the batch from
+pinned memory and the device->host read of the loss. ``--impl reference`` reports why the
+unmodified reference cannot run on this image.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+REF_UNAVAILABLE = ("reference not installable offline: pip --no-deps yields only optimus_dl/__init__.py "
+                   "(its pyproject lists packages=['optimus_dl'] without sub-packages) and omegaconf, hydra-core, "
+                   "colorlog are absent from the wheelhouse, so `import optimus_dl` fails")
+
+MODELS = {
+    "llama3-8b": dict(_name="llama2", n_layer=32, n_head=32, n_kv_head=8, n_embd=4096, intermediate_size=14336,
+                      vocab_size=128256, rope_theta=500000.0, sequence_length=8192, tie_word_embeddings=False,
+                      rmsnorm_eps=1e-5),
+    "llama-1b": dict(_name="llama2", n_layer=16, n_head=32, n_kv_head=8, n_embd=2048, intermediate_size=8192,
+                     vocab_size=128256, rope_theta=500000.0, sequence_length=8192, tie_word_embeddings=False),
+    "tiny": dict(_name="llama2", n_layer=2, n_head=8, n_kv_head=2, n_embd=512, intermediate_size=1536,
+                 vocab_size=32000, rope_theta=500000.0, sequence_length=2048, tie_word_embeddings=False),
+}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc = None
+        self.gpu = gpu_index
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=6)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--model", default="llama3-8b", choices=sorted(MODELS))
+    ap.add_argument("--seq-len", type=int, default=None)
+    ap.add_argument("--micro-batch", type=int, default=1)
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"impl": "reference", "unavailable": REF_UNAVAILABLE}))
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from optimus_dl_b200.criterion import build_criterion
+    from optimus_dl_b200.model_transforms import build_model_transform
+    from optimus_dl_b200.models import build_model
+    from optimus_dl_b200.optim import build_optimizer
+    from optimus_dl_b200.ops import _lib
+    from optimus_dl_b200.parallel import build_best_collective
+
+    warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if rank == 0:
+            print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}; using WORLD_SIZE", file=sys.stderr)
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    from optimus_dl_b200.parallel.collective import DistributedConfig
+
+    collective = build_best_collective(DistributedConfig(tp_size=1, sharding_world_size=world), device)
+
+    mcfg = dict(MODELS[args.model])
+    seq = args.seq_len or mcfg["sequence_length"]
+    mcfg["sequence_length"] = max(seq, mcfg["sequence_length"])
+    torch.manual_seed(0)
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    with torch.device(device):
+        model = build_model(mcfg)
+    torch.set_default_dtype(prev)
+    model = build_model_transform({"_name": "fully_shard", "reshard_after_forward": False}).apply(
+        model, collective=collective, device=device)
+    criterion = build_criterion({"_name": "cross_entropy"}, collective=collective)
+    optimizer = build_optimizer({"_name": "adamw", "lr": 3e-4, "betas": [0.9, 0.95], "weight_decay": 0.1},
+                                params=model.make_parameter_groups())
+    model.train()
+    vocab = mcfg["vocab_size"]
+    mb = args.micro_batch
+    total_steps = warmup + args.steps
+    gen = torch.Generator().manual_seed(1234 + rank)
+    host_batches = torch.randint(0, vocab, (total_steps, mb, seq + 1), generator=gen, dtype=torch.int64).pin_memory()
+    dev_batches = host_batches.to(device)
+
+    def train_step(ids: torch.Tensor) -> torch.Tensor:
+        optimizer.zero_grad()
+        loss, _ = criterion(model, {"input_ids": ids})
+        loss.backward()
+        optimizer.step()
+        return loss
+
+    def sync_all() -> None:
+        if world > 1:
+            dist.barrier(device_ids=[local_rank])
+        torch.cuda.synchronize(device)
+
+    def timed(run_step) -> tuple[float, int]:
+        for i in range(warmup):
+            run_step(i)
+        sync_all()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        calls0 = _lib.launch_count()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for i in range(warmup, total_steps):
+            run_step(i)
+        e.record()
+        sync_all()
+        ms = s.elapsed_time(e)
+        launches = _lib.launch_count() - calls0
+        clocks = sampler.stop() if rank == 0 else {}
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        _lib.check_status(device)
+        return float(t.item()), launches, clocks
+
+    last_loss = {}
+
+    def step_device(i: int) -> None:
+        last_loss["v"] = train_step(dev_batches[i])
+
+    def step_e2e(i: int) -> None:
+        ids = host_batches[i].to(device, non_blocking=True)
+        last_loss["f"] = float(train_step(ids).item())
+
+    ms, launches, clocks = timed(step_device)
+    tokens_per_step = world * mb * seq
+    value = tokens_per_step * args.steps / (ms / 1e3)
+    e2e = None
+    if not args.no_e2e:
+        ms2, _, _ = timed(step_e2e)
+        e2e = {"value": tokens_per_step * args.steps / (ms2 / 1e3), "unit": "tokens/s",
+               "h2d_bytes_per_step": int(host_batches[0].numel() * host_batches.element_size()),
+               "d2h_bytes_per_step": 4, "ms_per_step": ms2 / args.steps, "final_loss": last_loss.get("f")}
+    if rank == 0:
+        out = {
+            "metric": "Llama-3-8B FSDP2 bf16 train tokens/s (device-timed, max/rank)" if args.model == "llama3-8b"
+            else f"{args.model} bf16 train tokens/s (device-timed, max/rank)",
+            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights",
+            "impl": "ours",
+            "config": {"model": args.model, "global_batch": world * mb, "seq_len": seq,
+                       "parallelism": f"fsdp{world}" if world > 1 else "fsdp1 (single GPU, same sharded engine)",
+                       "optimizer": "AdamW fp32 master/moments, fused into the gradient reduce kernel",
+                       "l2": "working set (16 GB bf16 weights + activations) far exceeds the 126 MB L2"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+            "final_loss": float(last_loss["v"].item()) if "v" in last_loss else None,
+            "peak_mem_gb": torch.cuda.max_memory_allocated(device) / 2**30,
+        }
+        print(json.dumps(out))
+    if world > 1:
+        collective.close()
+
+
+if __name__ == "__main__":
+    main()

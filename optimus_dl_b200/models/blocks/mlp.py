@@ -31,6 +31,9 @@ class SwiGLUMLP(nn.Module):
         self.dropout = nn.Dropout(dropout) if dropout > 0 else None
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.w1.bias is None and self.c_proj.bias is None:
+            y = act_ops.swiglu_mlp(x, self.w1.weight, self.w2.weight, self.c_proj.weight)
+            return self.dropout(y) if self.dropout is not None else y
         if self.w1.bias is None:
             h = act_ops.swiglu_mlp_up(x, self.w1.weight, self.w2.weight)
         else:

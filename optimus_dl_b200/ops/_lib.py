@@ -30,7 +30,41 @@ def available() -> bool:
     return torch.cuda.is_available()
 
 
-def lib() -> ctypes.CDLL:
+class _CountingLib:
+    """Proxy over the CDLL that counts launcher calls (every launcher starts at least one kernel)."""
+
+    def __init__(self, cdll: ctypes.CDLL):
+        object.__setattr__(self, "_cdll", cdll)
+        object.__setattr__(self, "_wrapped", {})
+        object.__setattr__(self, "calls", 0)
+
+    def __getattr__(self, name: str):
+        w = self._wrapped.get(name)
+        if w is not None:
+            return w
+        fn = getattr(self._cdll, name)  # AttributeError if the symbol does not exist
+        if name in _NO_LAUNCH:
+            self._wrapped[name] = fn
+            return fn
+
+        def counted(*args, _fn=fn, _self=self):
+            if not getattr(_tls, "bound", False):
+                # first call into the library from this host thread: bind the CUDA device
+                _tls.bound = True
+                if torch.cuda.is_available():
+                    _self._cdll.ob_bind_thread(torch.cuda.current_device())
+            object.__setattr__(_self, "calls", _self.calls + 1)
+            return _fn(*args)
+
+        self._wrapped[name] = counted
+        return counted
+
+
+_NO_LAUNCH = {"ob_norm_bwd_grid", "ob_rope_grid", "ob_bind_thread"}
+_tls = threading.local()
+
+
+def lib() -> "_CountingLib":
     global _lib
     if _lib is not None:
         return _lib
@@ -39,9 +73,15 @@ def lib() -> ctypes.CDLL:
             path = _build.LIB_PATH
             if not path.exists():
                 path = _build.build()
-            _lib = ctypes.CDLL(str(path))
-            _declare(_lib)
+            cdll = ctypes.CDLL(str(path))
+            _declare(cdll)
+            _lib = _CountingLib(cdll)
     return _lib
+
+
+def launch_count() -> int:
+    """Number of kernel-launching calls made into the native library so far."""
+    return 0 if _lib is None else _lib.calls
 
 
 def ptr(t: torch.Tensor | None) -> c_void_p:
@@ -105,3 +145,11 @@ def _declare(l: ctypes.CDLL) -> None:
     sig("ob_add_f32_to_bf16", [P, P, L, I, P])
     sig("ob_ce_stats", [P, L, P, P, P, P, P, P, P, I, I, I, I, F, P])
     sig("ob_ce_grad", [P, L, P, P, I, I, I, I, L, F, P, F, I, F, P])
+    sig("ob_attn_fwd", [P, P, P, P, P, P, I, I, I, I, L, L, L, F, I, P, P])
+    sig("ob_attn_bwd", [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, L, L, L, F, I, P, P])  # 23 args
+    sig("ob_bind_thread", [I])
+    PP = ctypes.POINTER(c_void_p)
+    sig("ob_barrier", [PP, I, I, I, P, P])
+    sig("ob_pull", [P, I, PP, I, P, P, I, I, P])
+    sig("ob_rs_adamw", [I, P, I, PP, I, P, P, P, P, P, F, F, F, F, F, F, F, F, P, P, P, I, P])
+    sig("ob_gemm_ag_bf16", [P, L, P, L, P, L, I, I, I, P, P, I, PP, I, P, P, I, I, I, I, I, P, P])

@@ -89,3 +89,61 @@ def swiglu_mlp_up(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor) -> torch.
     if _ok(x, w1, w2) and w1.shape == w2.shape and w1.stride() == w2.stride():
         return _SwiGLUMLPUp.apply(x, w1, w2)
     return F.silu(F.linear(x, w1)) * F.linear(x, w2)
+
+
+class _SwiGLUMLP(torch.autograd.Function):
+    """Whole SwiGLU feed-forward ``(silu(x W1^T) * (x W2^T)) Wc^T``.
+
+    Saves only ``x``, ``g`` and ``u``: the product ``h`` that feeds the down projection is rebuilt
+    by the backward activation kernel (it is needed there for the down projection's weight
+    gradient), which removes one ``[tokens, hidden]`` tensor per layer from the saved set.
+    """
+
+    @staticmethod
+    def forward(ctx, x, w1, w2, wc):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1])
+        h, g, u = gemm.swiglu_gemm(x2, w1, w2, save_gu=True)
+        y = gemm.gemm(h, wc)
+        ctx.save_for_backward(x2, w1, w2, wc, g, u)
+        ctx.params = (w1, w2, wc)
+        return y.view(*shp[:-1], wc.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        from .linear import main_grad_of, main_grad_write
+
+        x2, w1, w2, wc, g, u = ctx.saved_tensors
+        p1, p2, pc = ctx.params
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dh = gemm.gemm(dy2, wc, b_mn=True)
+        h = torch.empty_like(g)
+        # in place: g <- dg, u <- du (the saved tensors are dead after this call)
+        _lib.check(_lib.lib().ob_swiglu_bwd(_lib.ptr(dh), _lib.ptr(g), _lib.ptr(u), _lib.ptr(g), _lib.ptr(u), _lib.ptr(h),
+                                            g.numel(), _lib.stream()), "swiglu_bwd")
+        dg, du = g, u
+        del dh
+        grads = [None, None, None]
+        for i, (p, a, b) in enumerate(((pc, dy2, h), (p1, dg, x2), (p2, du, x2))):
+            if not ctx.needs_input_grad[(3, 1, 2)[i]]:
+                continue
+            mg = main_grad_of(p)
+            if mg is not None:
+                gemm.gemm(a, b, a_mn=True, b_mn=True, out=mg, accumulate=main_grad_write(p))
+            else:
+                grads[i] = gemm.gemm(a, b, a_mn=True, b_mn=True)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm.gemm(dg, w1, b_mn=True)
+            gemm.gemm(du, w2, b_mn=True, out=dx, accumulate=True)
+            dx = dx.view(*dy.shape[:-1], x2.shape[-1])
+        return dx, grads[1], grads[2], grads[0]
+
+
+def swiglu_mlp(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, wc: torch.Tensor) -> torch.Tensor:
+    """Bias-free SwiGLU feed-forward block; kernels on CUDA bf16, eager otherwise."""
+    if _ok(x, w1, w2, wc) and w1.shape == w2.shape and w1.stride() == w2.stride() and wc.shape[1] % 8 == 0:
+        return _SwiGLUMLP.apply(x, w1, w2, wc)
+    return F.linear(F.silu(F.linear(x, w1)) * F.linear(x, w2), wc)

@@ -130,11 +130,12 @@ class _QKVAttention(torch.autograd.Function):
         dout = dout.contiguous()
         dqkv = torch.empty_like(work)
         delta = torch.empty((Hq, N), dtype=torch.float32, device=dev)
+        kv_last = torch.empty(((N + 127) // 128,), dtype=torch.int32, device=dev)
         rc = l.ob_attn_bwd(_lib.ptr(work), _lib.ptr(work[:, Hq * hd:]), _lib.ptr(work[:, (Hq + Hk) * hd:]),
                            _lib.ptr(out), _lib.ptr(dout), _lib.ptr(lse), _lib.ptr(delta), _lib.ptr(dqkv),
-                           _lib.ptr(dqkv[:, Hq * hd:]), _lib.ptr(dqkv[:, (Hq + Hk) * hd:]), _lib.ptr(doc_start), N, Hq,
-                           Hk, hd, work.stride(0), out.stride(0), float(scale), int(window or 0),
-                           _lib.ptr(_lib.status_word(dev)), _lib.stream())
+                           _lib.ptr(dqkv[:, Hq * hd:]), _lib.ptr(dqkv[:, (Hq + Hk) * hd:]), _lib.ptr(doc_start),
+                           _lib.ptr(kv_last), N, Hq, Hk, hd, work.stride(0), out.stride(0), dqkv.stride(0),
+                           float(scale), int(window or 0), _lib.ptr(_lib.status_word(dev)), _lib.stream())
         _lib.check(rc, "ob_attn_bwd")
         dqw = dkw = None
         if freqs is not None or has_norm:

@@ -57,7 +57,7 @@ def cross_entropy_ref(logits: torch.Tensor, targets: torch.Tensor, ignore_index:
 class _LinearCE(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, targets, ignore_index, smoothing, softcap, softcap_type, chunk_rows, tp_group,
-                vocab_offset, total_vocab):
+                vocab_offset, total_vocab, grad_scale):
         l = _lib.lib()
         dev = x.device
         d = x.shape[-1]
@@ -76,7 +76,16 @@ class _LinearCE(torch.autograd.Function):
         need_dx = ctx.needs_input_grad[0]
         need_dw = ctx.needs_input_grad[1]
         dx = torch.empty_like(x2) if need_dx else None
-        dw = torch.empty_like(weight) if need_dw else None
+        mg = getattr(weight, "main_grad", None) if need_dw else None
+        if mg is not None:
+            # accumulate straight into the sharding engine's flat gradient buffer (unit upstream
+            # gradient is assumed: the criterion passes the loss scale through ``grad_scale``)
+            dw = mg
+            first_acc = bool(getattr(weight, "_main_grad_filled", False))
+            weight._main_grad_filled = True
+        else:
+            dw = torch.empty_like(weight) if need_dw else None
+            first_acc = False
         ld = (V + 7) // 8 * 8
         chunk_rows = min(chunk_rows, T)
         logits_buf = torch.empty((chunk_rows, ld), dtype=torch.bfloat16, device=dev)
@@ -116,13 +125,13 @@ class _LinearCE(torch.autograd.Function):
             lse_all[r0:r1] = lse
             if need_dx or need_dw:
                 rc = l.ob_ce_grad(_lib.ptr(out_view), ld, _lib.ptr(tg[r0:r1]), _lib.ptr(lse), rows, V, int(vocab_offset),
-                                  int(total_vocab), int(ignore_index), float(smoothing), _lib.ptr(inv_n), 1.0, mode,
+                                  int(total_vocab), int(ignore_index), float(smoothing), _lib.ptr(inv_n), float(grad_scale), mode,
                                   cap_c, _lib.stream())
                 _lib.check(rc, "ob_ce_grad")
                 if need_dx:
                     gemm.gemm(out_view, weight, b_mn=True, out=dx[r0:r1])
                 if need_dw:
-                    gemm.gemm(out_view, x2[r0:r1], a_mn=True, b_mn=True, out=dw, accumulate=not first)
+                    gemm.gemm(out_view, x2[r0:r1], a_mn=True, b_mn=True, out=dw, accumulate=(not first) or first_acc)
             first = False
         zt_all, sz_all = stats[3], stats[2]
         per_tok = lse_all - (1.0 - smoothing) * zt_all - smoothing * sz_all / total_vocab
@@ -134,9 +143,10 @@ class _LinearCE(torch.autograd.Function):
             import torch.distributed as dist
 
             dist.all_reduce(dx, group=tp_group)
-        ctx.save_for_backward(dx if need_dx else torch.empty(0), dw if need_dw else torch.empty(0))
+        ctx.save_for_backward(dx if need_dx else torch.empty(0), dw if (need_dw and mg is None) else torch.empty(0))
         ctx.x_shape = x.shape
-        ctx.flags = (need_dx, need_dw)
+        ctx.grad_scale = float(grad_scale)
+        ctx.flags = (need_dx, need_dw and mg is None)
         ctx.mark_non_differentiable(n_valid, n_correct, loss_sum)
         return loss, n_valid, n_correct, loss_sum
 
@@ -144,19 +154,24 @@ class _LinearCE(torch.autograd.Function):
     def backward(ctx, dloss, *_):
         dx, dw = ctx.saved_tensors
         need_dx, need_dw = ctx.flags
-        gx = (dx * dloss.to(dx.dtype)).view(ctx.x_shape) if need_dx else None
-        gw = dw * dloss.to(dw.dtype) if need_dw else None
-        return gx, gw, None, None, None, None, None, None, None, None, None
+        # gradients were computed with ``grad_scale`` folded in; a unit upstream gradient is the
+        # common case (loss.backward()), anything else rescales here
+        # (``grad_scale`` is the upstream gradient the caller promised, e.g. 1 / accumulation steps)
+        factor = dloss / ctx.grad_scale
+        gx = (dx * factor.to(dx.dtype)).view(ctx.x_shape) if need_dx else None
+        gw = dw * factor.to(dw.dtype) if need_dw else None
+        return gx, gw, None, None, None, None, None, None, None, None, None, None
 
 
 def linear_cross_entropy(x: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor, *, ignore_index: int = -100,
                          label_smoothing: float = 0.0, softcap: float | None = None, softcap_type: str = "tanh",
                          chunk_rows: int = 4096, tp_group=None, vocab_offset: int = 0,
-                         total_vocab: int | None = None) -> CEResult:
+                         total_vocab: int | None = None, grad_scale: float = 1.0) -> CEResult:
     """Mean cross-entropy of ``x @ weight^T`` against ``targets`` (see module docstring)."""
     if x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0:
         loss, n_valid, n_correct, loss_sum = _LinearCE.apply(x, weight, targets, ignore_index, label_smoothing, softcap,
-                                                             softcap_type, chunk_rows, tp_group, vocab_offset, total_vocab)
+                                                             softcap_type, chunk_rows, tp_group, vocab_offset, total_vocab,
+                                                             grad_scale)
         return CEResult(loss, n_valid, n_correct, loss_sum)
     if tp_group is not None:
         raise NotImplementedError("vocabulary-parallel loss needs the CUDA bf16 path")

@@ -1,0 +1,528 @@
+// Flash-attention backward for sm_100a (same masking rule as attention_fwd.cu).
+//
+// Three launches:
+//   delta kernel : delta[h, i] = sum_c dO[i,h,c] * O[i,h,c]
+//   dQ kernel    : one CTA per (128-query tile, head); loops over key tiles:
+//                    S = Q K^T, dP = dO V^T (tcgen05, operands in smem) -> TMEM
+//                    dS = exp2(S*scale - lse) * (dP - delta) * scale   (thread per query row)
+//                    dQ += dS K   (dS from TMEM, K tile re-read as an MN-major operand)
+//   dKV kernel   : one CTA per (128-key tile, kv head); loops over the query heads of the group
+//                  and the query tiles that can see these keys, transposed problem:
+//                    S^T = K Q^T, dP^T = V dO^T -> TMEM (thread per key row)
+//                    dV += P^T dO, dK += dS^T Q  (P^T / dS^T from TMEM, dO / Q tiles MN-major)
+// Recomputing S and dP in both kernels costs two extra products but needs no atomics: every
+// output element is written by exactly one CTA in a fixed order (bitwise reproducible).
+#include "common.cuh"
+#include "tensormap.cuh"
+
+namespace ob {
+namespace attnb {
+
+constexpr int BM = 128;
+constexpr int BN = 128;
+constexpr int STAGES = 2;
+constexpr int THREADS = 192;
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct BwdParams {
+  int N, Hq, Hk, window;
+  float scale, scale_log2;
+  const int* doc_start;
+  const float* lse;        // [Hq, N]
+  const float* delta;      // [Hq, N]
+  __nv_bfloat16* dq; __nv_bfloat16* dk; __nv_bfloat16* dv;
+  long long dqkv_stride;   // token stride of dq / dk / dv (elements)
+  const int* kv_last_q;    // [key tiles] last query index that can attend a key of the tile
+  int* status;
+};
+
+__global__ void delta_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
+                             long long out_stride, long long dout_stride, float* __restrict__ delta, int N, int Hq,
+                             int hd) {
+  const int lane = threadIdx.x & 31;
+  const long long total = (long long)N * Hq;
+  for (long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); item < total;
+       item += (long long)gridDim.x * (blockDim.x >> 5)) {
+    const int i = (int)(item / Hq), h = (int)(item % Hq);
+    const __nv_bfloat16* o = out + i * out_stride + (long long)h * hd;
+    const __nv_bfloat16* d = dout + i * dout_stride + (long long)h * hd;
+    float s = 0.f;
+    for (int c = lane * 2; c < hd; c += 64) {
+      float2 a = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(o + c));
+      float2 b = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(d + c));
+      s += a.x * b.x + a.y * b.y;
+    }
+    s = warp_sum(s);
+    if (lane == 0) delta[(long long)h * N + i] = s;
+  }
+}
+
+// last query that may attend any key of tile t: largest i with max(doc_start[i], i-window+1) <= k_hi
+__global__ void kv_last_q_kernel(const int* __restrict__ doc_start, int N, int window, int* __restrict__ out,
+                                 int n_tiles) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n_tiles) return;
+  const int k_hi = min(t * BN + BN - 1, N - 1);
+  int lo = k_hi, hi = N - 1;   // the key itself is always attendable by query k_hi
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    int l = doc_start[mid];
+    if (window > 0) l = max(l, mid - window + 1);
+    if (l <= k_hi) lo = mid; else hi = mid - 1;
+  }
+  out[t] = lo;
+}
+
+template <int HD>
+struct SmemQ {   // dQ kernel
+  static constexpr int TILE = BM * HD * 2;
+  static constexpr int Q_OFF = 0, DO_OFF = TILE, K_OFF = 2 * TILE, V_OFF = K_OFF + STAGES * TILE;
+  static constexpr int BAR_OFF = V_OFF + STAGES * TILE;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                   const BwdParams p) {
+  using L = SmemQ<HD>;
+  constexpr int SLABS = HD / 64;
+  constexpr int SLAB_BYTES = BM * 128;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* qdo_full = bars;
+  uint64_t* k_full = bars + 1; uint64_t* k_empty = bars + 3;
+  uint64_t* v_full = bars + 5; uint64_t* v_empty = bars + 7;
+  uint64_t* sdp_full = bars + 9; uint64_t* ds_ready = bars + 10; uint64_t* dq_final = bars + 11;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_qtiles = (p.N + BM - 1) / BM;
+  const int h = blockIdx.x % p.Hq;
+  const int qt = n_qtiles - 1 - blockIdx.x / p.Hq;
+  const int kvh = h / (p.Hq / p.Hk);
+  const int q_lo = qt * BM, q_hi = min(q_lo + BM - 1, p.N - 1);
+  int lo_first = p.doc_start[q_lo], lo_last = p.doc_start[q_hi];
+  if (p.window > 0) { lo_first = max(lo_first, q_lo - p.window + 1); lo_last = max(lo_last, q_hi - p.window + 1); }
+  const int j_lo = lo_first / BN, j_hi = q_hi / BN;
+
+  if (threadIdx.x == 0) {
+    mbar_init(qdo_full, 1);
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+    mbar_init(sdp_full, 1); mbar_init(ds_ready, 4); mbar_init(dq_final, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 5) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(qdo_full, 2 * L::TILE);
+#pragma unroll
+      for (int s = 0; s < SLABS; ++s) {
+        tma_load_2d(smem + L::Q_OFF + s * SLAB_BYTES, &tmQ, qdo_full, h * HD + s * 64, q_lo);
+        tma_load_2d(smem + L::DO_OFF + s * SLAB_BYTES, &tmDO, qdo_full, h * HD + s * 64, q_lo);
+      }
+      bool ok = true;
+      for (int j = j_lo; j <= j_hi && ok; ++j) {
+        const int t = j - j_lo, st = t % STAGES;
+        const uint32_t ph = (t / STAGES) & 1;
+        ok = mbar_wait(&k_empty[st], ph ^ 1, abort_flag, p.status);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&k_full[st], L::TILE);
+#pragma unroll
+        for (int s = 0; s < SLABS; ++s)
+          tma_load_2d(smem + L::K_OFF + st * L::TILE + s * SLAB_BYTES, &tmK, &k_full[st], kvh * HD + s * 64, j * BN);
+        ok = mbar_wait(&v_empty[st], ph ^ 1, abort_flag, p.status);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&v_full[st], L::TILE);
+#pragma unroll
+        for (int s = 0; s < SLABS; ++s)
+          tma_load_2d(smem + L::V_OFF + st * L::TILE + s * SLAB_BYTES, &tmV, &v_full[st], kvh * HD + s * 64, j * BN);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(BM, BN, 0, 0);
+      constexpr uint32_t idesc_dq = make_idesc_bf16(BM, HD, 0, 1);
+      const uint32_t sQ = smem_u32(smem + L::Q_OFF), sDO = smem_u32(smem + L::DO_OFF);
+      const uint32_t sK = smem_u32(smem + L::K_OFF), sV = smem_u32(smem + L::V_OFF);
+      bool ok = mbar_wait(qdo_full, 0, abort_flag, p.status);
+      uint32_t ds_phase = 0;
+      for (int j = j_lo; j <= j_hi && ok; ++j) {
+        const int t = j - j_lo, st = t % STAGES;
+        const uint32_t ph = (t / STAGES) & 1;
+        ok = mbar_wait(&k_full[st], ph, abort_flag, p.status) && mbar_wait(&v_full[st], ph, abort_flag, p.status);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk / 4) * SLAB_BYTES + (kk % 4) * 32;
+          umma_f16_ss(tmem_base, make_smem_desc_sw128(sQ + off, 16, 1024),
+                      make_smem_desc_sw128(sK + st * L::TILE + off, 16, 1024), idesc_s, kk ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk / 4) * SLAB_BYTES + (kk % 4) * 32;
+          umma_f16_ss(tmem_base + BN, make_smem_desc_sw128(sDO + off, 16, 1024),
+                      make_smem_desc_sw128(sV + st * L::TILE + off, 16, 1024), idesc_s, kk ? 1u : 0u);
+        }
+        umma_commit(sdp_full);
+        umma_commit(&v_empty[st]);
+        ok = mbar_wait(ds_ready, ds_phase, abort_flag, p.status);
+        if (!ok) break;
+        ds_phase ^= 1;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk)
+          umma_f16_ts(tmem_base + 2 * BN, tmem_base + kk * 8,
+                      make_smem_desc_sw128(sK + st * L::TILE + kk * 2048, SLAB_BYTES, 1024), idesc_dq,
+                      (j > j_lo || kk) ? 1u : 0u);
+        umma_commit(&k_empty[st]);
+      }
+      umma_commit(dq_final);
+    }
+  } else {
+    const int row = warp * 32 + lane;
+    const int qi = q_lo + row;
+    const bool row_valid = qi < p.N;
+    int lo_row = 0;
+    float lse2 = 0.f, dl = 0.f;
+    if (row_valid) {
+      lo_row = p.doc_start[qi];
+      if (p.window > 0) lo_row = max(lo_row, qi - p.window + 1);
+      lse2 = p.lse[(long long)h * p.N + qi] * LOG2E;
+      dl = p.delta[(long long)h * p.N + qi];
+    }
+    const uint32_t t_s = tmem_base + (uint32_t(warp * 32) << 16);
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int j = j_lo; j <= j_hi && ok; ++j) {
+      ok = mbar_wait(sdp_full, phase, abort_flag, p.status);
+      if (!ok) break;
+      phase ^= 1;
+      tc_fence_after();
+      const int k0 = j * BN;
+      const bool need_mask = (k0 + BN - 1 > q_lo) || (k0 < lo_last) || (q_lo + BM > p.N);
+#pragma unroll
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t s[32], dp[32], pk[16];
+        tmem_ld_32x32(t_s + c, s);
+        tmem_ld_32x32(t_s + BN + c, dp);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float v[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int kj = k0 + c + e + u;
+            const bool valid = !need_mask || (row_valid && kj <= qi && kj >= lo_row);
+            const float pr = valid ? exp2f(__uint_as_float(s[e + u]) * p.scale_log2 - lse2) : 0.f;
+            v[u] = pr * (__uint_as_float(dp[e + u]) - dl) * p.scale;
+          }
+          pk[e / 2] = pack_bf16x2(v[0], v[1]);
+        }
+        tmem_st_32x16(t_s + c / 2, pk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_ready);
+    }
+    if (ok) ok = mbar_wait(dq_final, 0, abort_flag, p.status);
+    if (ok) {
+      tc_fence_after();
+      __nv_bfloat16* drow = p.dq + (long long)qi * p.dqkv_stride + h * HD;
+#pragma unroll
+      for (int c = 0; c < HD; c += 32) {
+        uint32_t o[32];
+        tmem_ld_32x32(t_s + 2 * BN + c, o);
+        tmem_ld_wait();
+        if (row_valid) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v)
+            *reinterpret_cast<uint4*>(drow + c + 8 * v) =
+                make_uint4(pack_bf16x2(__uint_as_float(o[8 * v]), __uint_as_float(o[8 * v + 1])),
+                           pack_bf16x2(__uint_as_float(o[8 * v + 2]), __uint_as_float(o[8 * v + 3])),
+                           pack_bf16x2(__uint_as_float(o[8 * v + 4]), __uint_as_float(o[8 * v + 5])),
+                           pack_bf16x2(__uint_as_float(o[8 * v + 6]), __uint_as_float(o[8 * v + 7])));
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+template <int HD>
+struct SmemKV {   // dK/dV kernel
+  static constexpr int TILE = BM * HD * 2;
+  static constexpr int K_OFF = 0, V_OFF = TILE, Q_OFF = 2 * TILE, DO_OFF = Q_OFF + STAGES * TILE;
+  static constexpr int VEC_OFF = DO_OFF + STAGES * TILE;            // [4 warps][3][BM] 4-byte values
+  static constexpr int BAR_OFF = VEC_OFF + 4 * 3 * BM * 4;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS, 1)
+attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                    const BwdParams p) {
+  using L = SmemKV<HD>;
+  constexpr int SLABS = HD / 64;
+  constexpr int SLAB_BYTES = BM * 128;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* kv_full = bars;
+  uint64_t* q_full = bars + 1; uint64_t* q_empty = bars + 3;
+  uint64_t* sdp_full = bars + 5; uint64_t* pds_ready = bars + 6; uint64_t* final_bar = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* vec = reinterpret_cast<float*>(smem + L::VEC_OFF);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_ktiles = (p.N + BN - 1) / BN;
+  const int kvh = blockIdx.x % p.Hk;
+  const int kt = blockIdx.x / p.Hk;               // early key tiles see the most queries: they go first
+  const int G = p.Hq / p.Hk;
+  const int k0 = kt * BN;
+  const int i_lo = k0 / BM;
+  const int i_hi = p.kv_last_q[kt] / BM;
+  const int n_i = i_hi - i_lo + 1;
+  const int n_iter = G * n_i;
+  (void)n_ktiles;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
+    mbar_init(sdp_full, 1); mbar_init(pds_ready, 4); mbar_init(final_bar, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 5) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(kv_full, 2 * L::TILE);
+#pragma unroll
+      for (int s = 0; s < SLABS; ++s) {
+        tma_load_2d(smem + L::K_OFF + s * SLAB_BYTES, &tmK, kv_full, kvh * HD + s * 64, k0);
+        tma_load_2d(smem + L::V_OFF + s * SLAB_BYTES, &tmV, kv_full, kvh * HD + s * 64, k0);
+      }
+      bool ok = true;
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int g = it / n_i, i = i_lo + it % n_i, h = kvh * G + g;
+        const int st = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        ok = mbar_wait(&q_empty[st], ph ^ 1, abort_flag, p.status);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&q_full[st], 2 * L::TILE);
+#pragma unroll
+        for (int s = 0; s < SLABS; ++s) {
+          tma_load_2d(smem + L::Q_OFF + st * L::TILE + s * SLAB_BYTES, &tmQ, &q_full[st], h * HD + s * 64, i * BM);
+          tma_load_2d(smem + L::DO_OFF + st * L::TILE + s * SLAB_BYTES, &tmDO, &q_full[st], h * HD + s * 64, i * BM);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(BN, BM, 0, 0);
+      constexpr uint32_t idesc_o = make_idesc_bf16(BN, HD, 0, 1);
+      const uint32_t sK = smem_u32(smem + L::K_OFF), sV = smem_u32(smem + L::V_OFF);
+      const uint32_t sQ = smem_u32(smem + L::Q_OFF), sDO = smem_u32(smem + L::DO_OFF);
+      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status);
+      uint32_t pds_phase = 0;
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int st = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        ok = mbar_wait(&q_full[st], ph, abort_flag, p.status);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk / 4) * SLAB_BYTES + (kk % 4) * 32;
+          umma_f16_ss(tmem_base, make_smem_desc_sw128(sK + off, 16, 1024),
+                      make_smem_desc_sw128(sQ + st * L::TILE + off, 16, 1024), idesc_s, kk ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk / 4) * SLAB_BYTES + (kk % 4) * 32;
+          umma_f16_ss(tmem_base + BM, make_smem_desc_sw128(sV + off, 16, 1024),
+                      make_smem_desc_sw128(sDO + st * L::TILE + off, 16, 1024), idesc_s, kk ? 1u : 0u);
+        }
+        umma_commit(sdp_full);
+        ok = mbar_wait(pds_ready, pds_phase, abort_flag, p.status);
+        if (!ok) break;
+        pds_phase ^= 1;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < BM / 16; ++kk)   // dV += P^T dO
+          umma_f16_ts(tmem_base + 2 * BM, tmem_base + kk * 8,
+                      make_smem_desc_sw128(sDO + st * L::TILE + kk * 2048, SLAB_BYTES, 1024), idesc_o,
+                      (it > 0 || kk) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < BM / 16; ++kk)   // dK += dS^T Q
+          umma_f16_ts(tmem_base + 3 * BM, tmem_base + BM + kk * 8,
+                      make_smem_desc_sw128(sQ + st * L::TILE + kk * 2048, SLAB_BYTES, 1024), idesc_o,
+                      (it > 0 || kk) ? 1u : 0u);
+        umma_commit(&q_empty[st]);
+      }
+      umma_commit(final_bar);
+    }
+  } else {
+    const int row = warp * 32 + lane;        // key row == TMEM lane
+    const int kj = k0 + row;
+    const bool key_valid = kj < p.N;
+    const uint32_t t_s = tmem_base + (uint32_t(warp * 32) << 16);
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int g = it / n_i, i = i_lo + it % n_i, h = kvh * G + g;
+      // every warp keeps its own copy of the per-query vectors (no CTA-wide barrier needed)
+      float* vb = vec + warp * 3 * BM;
+      int* lo_s = reinterpret_cast<int*>(vb + 2 * BM);
+      __syncwarp();
+#pragma unroll
+      for (int cc = lane; cc < BM; cc += 32) {
+        const int qi = i * BM + cc;
+        float l2 = 0.f, dl = 0.f;
+        int lo = 0x7fffffff;
+        if (qi < p.N) {
+          l2 = p.lse[(long long)h * p.N + qi] * LOG2E;
+          dl = p.delta[(long long)h * p.N + qi];
+          lo = p.doc_start[qi];
+          if (p.window > 0) lo = max(lo, qi - p.window + 1);
+        }
+        vb[cc] = l2; vb[BM + cc] = dl; lo_s[cc] = lo;
+      }
+      __syncwarp();
+      ok = mbar_wait(sdp_full, phase, abort_flag, p.status);
+      if (!ok) break;
+      phase ^= 1;
+      tc_fence_after();
+      const int q_first = i * BM;
+      const bool need_mask = (q_first < k0 + BN - 1) || (lo_s[BM - 1] > k0) || (k0 + BN > p.N);
+#pragma unroll
+      for (int c = 0; c < BM; c += 32) {
+        uint32_t s[32], dp[32], pk[16], dk_[16];
+        tmem_ld_32x32(t_s + c, s);
+        tmem_ld_32x32(t_s + BM + c, dp);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float pv[2], dv_[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int col = c + e + u;
+            const int qi = q_first + col;
+            const bool valid = !need_mask || (key_valid && kj <= qi && kj >= lo_s[col]);
+            const float pr = valid ? exp2f(__uint_as_float(s[e + u]) * p.scale_log2 - vb[col]) : 0.f;
+            pv[u] = pr;
+            dv_[u] = pr * (__uint_as_float(dp[e + u]) - vb[BM + col]) * p.scale;
+          }
+          pk[e / 2] = pack_bf16x2(pv[0], pv[1]);
+          dk_[e / 2] = pack_bf16x2(dv_[0], dv_[1]);
+        }
+        tmem_st_32x16(t_s + c / 2, pk);
+        tmem_st_32x16(t_s + BM + c / 2, dk_);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_ready);
+    }
+    if (ok) ok = mbar_wait(final_bar, 0, abort_flag, p.status);
+    if (ok) {
+      tc_fence_after();
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        __nv_bfloat16* drow = (which == 0 ? p.dv : p.dk) + (long long)kj * p.dqkv_stride + kvh * HD;
+        const uint32_t t_acc = t_s + (2 + which) * BM;
+#pragma unroll
+        for (int c = 0; c < HD; c += 32) {
+          uint32_t o[32];
+          tmem_ld_32x32(t_acc + c, o);
+          tmem_ld_wait();
+          if (key_valid) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v)
+              *reinterpret_cast<uint4*>(drow + c + 8 * v) =
+                  make_uint4(pack_bf16x2(__uint_as_float(o[8 * v]), __uint_as_float(o[8 * v + 1])),
+                             pack_bf16x2(__uint_as_float(o[8 * v + 2]), __uint_as_float(o[8 * v + 3])),
+                             pack_bf16x2(__uint_as_float(o[8 * v + 4]), __uint_as_float(o[8 * v + 5])),
+                             pack_bf16x2(__uint_as_float(o[8 * v + 6]), __uint_as_float(o[8 * v + 7])));
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+}  // namespace attnb
+}  // namespace ob
+
+using namespace ob;
+using namespace ob::attnb;
+
+template <int HD>
+static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+                      const BwdParams& p, cudaStream_t stream) {
+  auto kq = attn_bwd_dq_kernel<HD>;
+  auto kkv = attn_bwd_dkv_kernel<HD>;
+  static bool configured = false;
+  if (!configured) {
+    OB_CUDA_CHECK(cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemQ<HD>::TOTAL));
+    OB_CUDA_CHECK(cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemKV<HD>::TOTAL));
+    configured = true;
+  }
+  const int n_qtiles = (p.N + BM - 1) / BM, n_ktiles = (p.N + BN - 1) / BN;
+  kkv<<<n_ktiles * p.Hk, THREADS, SmemKV<HD>::TOTAL, stream>>>(tq, tk, tv, tdo, p);
+  kq<<<n_qtiles * p.Hq, THREADS, SmemQ<HD>::TOTAL, stream>>>(tq, tk, tv, tdo, p);
+  return (int)cudaGetLastError();
+}
+
+// q, k, v: post-RoPE projections (views of one buffer, token stride qkv_stride); out / dout: [N, Hq*hd]
+// (token stride out_stride); lse: fp32 [Hq, N] from the forward; delta: fp32 scratch [Hq, N];
+// dq, dk, dv: views of one gradient buffer with token stride dqkv_stride; kv_last: int32 scratch
+// of ceil(N / 128) entries.
+extern "C" int ob_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                           const void* lse, void* delta, void* dq, void* dk, void* dv, const void* doc_start,
+                           void* kv_last, int N, int Hq, int Hk, int hd, long long qkv_stride, long long out_stride,
+                           long long dqkv_stride, float scale, int window, int* status, cudaStream_t stream) {
+  if (N <= 0) return 0;
+  if (hd != 64 && hd != 128) return -1;
+  CUtensorMap tq, tk, tv, tdo;
+  int rc = make_tmap_2d(&tq, q, N, (uint64_t)Hq * hd, qkv_stride, BM, 64, 2);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tk, k, N, (uint64_t)Hk * hd, qkv_stride, BN, 64, 2);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tv, v, N, (uint64_t)Hk * hd, qkv_stride, BN, 64, 2);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tdo, dout, N, (uint64_t)Hq * hd, out_stride, BM, 64, 2);
+  if (rc) return rc;
+  const int n_ktiles = (N + BN - 1) / BN;
+  long long items = (long long)N * Hq;
+  int grid = (int)((items + 7) / 8 < 148 * 16 ? (items + 7) / 8 : 148 * 16);
+  delta_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)dout, out_stride, out_stride,
+                                         (float*)delta, N, Hq, hd);
+  kv_last_q_kernel<<<(n_ktiles + 127) / 128, 128, 0, stream>>>((const int*)doc_start, N, window, (int*)kv_last, n_ktiles);
+  BwdParams p{N, Hq, Hk, window, scale, scale * LOG2E, (const int*)doc_start, (const float*)lse, (const float*)delta,
+              (__nv_bfloat16*)dq, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, dqkv_stride, (const int*)kv_last, status};
+  return hd == 128 ? launch_bwd<128>(tq, tk, tv, tdo, p, stream) : launch_bwd<64>(tq, tk, tv, tdo, p, stream);
+}

@@ -1,0 +1,221 @@
+// Collective kernels that run over NVLink peer memory (see comm.cuh):
+//   ob_barrier       : bounded cross-GPU barrier on a symmetric flag array
+//   ob_pull          : all-gather as P2P pulls of copy tasks (no staging, lands in place)
+//   ob_rs_adamw      : gradient reduce-scatter fused with bf16->fp32 cast, scaling, optional
+//                      squared-norm partial and the sharded AdamW update (three modes)
+// The GEMM that overlaps an all-gather with its own tiles lives in gemm_ag.cu.
+#include "comm.cuh"
+
+namespace ob {
+namespace comm {
+
+// flags: this rank's symmetric int array [MAX_RANKS]; peers.p[r] = rank r's array.
+// Rank `me` writes `epoch` into slot `me` of every rank, then waits for all slots of its own array.
+__global__ void barrier_kernel(PeerPtrs peers, int me, int world, int epoch, int* status) {
+  const int r = threadIdx.x;
+  if (r >= world) return;
+  __threadfence_system();
+  int* remote = reinterpret_cast<int*>(peers.p[r]) + me;
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+  const int* mine = reinterpret_cast<const int*>(peers.p[me]) + r;
+  bool ok = false;
+  for (uint32_t it = 0; it < (1u << 24); ++it) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if (v >= epoch) { ok = true; break; }
+    __nanosleep(100);
+  }
+  if (!ok && status) atomicCAS(status, kStatusOk, kStatusFlagTimeout);
+  __threadfence_system();
+}
+
+__global__ void __launch_bounds__(1024)
+pull_kernel(const CopyTask* __restrict__ tasks, int n_tasks, PeerPtrs src, __nv_bfloat16* dst, int* flags, int epoch) {
+  run_copy_tasks(tasks, n_tasks, blockIdx.x, gridDim.x, src, dst, flags, epoch);
+}
+
+// One owned slice of a parameter: `numel` elements that sit at `flat_off` in the (symmetric) flat
+// gradient / parameter buffers and at `shard_off` in this rank's fp32 shard state.
+struct Segment {
+  long long flat_off;
+  long long shard_off;
+  int numel;
+  float weight_decay;
+  float lr_scale;
+  int pad;
+};
+
+struct AdamArgs {
+  float lr, beta1, beta2, eps, bc1, bc2;
+  float grad_scale;        // e.g. 1 / (world * accumulation steps)
+  float max_norm;          // > 0: clip with *sumsq_in
+  const float* sumsq_in;   // squared global gradient norm (before grad_scale), device scalar
+};
+
+enum Mode : int { kFused = 0, kReduceOnly = 1, kUpdateOnly = 2 };
+
+// MODE kFused     : g = sum_r peer_grad[r][flat]  -> AdamW -> master/m/v, bf16 param out
+// MODE kReduceOnly: g -> grad_shard (fp32), per-block partial of sum g^2 (for the global norm)
+// MODE kUpdateOnly: g = grad_shard -> AdamW (with clip) -> master/m/v, bf16 param out
+template <int MODE>
+__global__ void __launch_bounds__(256)
+rs_adamw_kernel(const Segment* __restrict__ segs, int n_segs, PeerPtrs grads, int world,
+                float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
+                float* __restrict__ grad_shard, __nv_bfloat16* __restrict__ param_out, AdamArgs a,
+                float* __restrict__ sq_partials) {
+  float scale = a.grad_scale;
+  if (MODE != kReduceOnly && a.sumsq_in && a.max_norm > 0.f) {
+    const float norm = sqrtf(*a.sumsq_in) * a.grad_scale;
+    scale *= fminf(1.0f, a.max_norm / (norm + 1e-6f));
+  }
+  const float inv_sqrt_bc2 = rsqrtf(a.bc2);
+  float sq = 0.f;
+  for (int s = 0; s < n_segs; ++s) {
+    const Segment seg = segs[s];
+    const bool aligned = (seg.flat_off % 8 == 0) && (seg.shard_off % 4 == 0);
+    const int nvec = aligned ? seg.numel / 8 : 0;
+    const float lr = a.lr * seg.lr_scale;
+    const float step = lr / a.bc1;
+    const float decay = 1.0f - lr * seg.weight_decay;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += gridDim.x * blockDim.x) {
+      float g[8];
+      if (MODE == kUpdateOnly) {
+        const float4 g0 = reinterpret_cast<const float4*>(grad_shard + seg.shard_off)[2 * i];
+        const float4 g1 = reinterpret_cast<const float4*>(grad_shard + seg.shard_off)[2 * i + 1];
+        g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w; g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) g[j] = 0.f;
+        // fixed rank order: every owner adds in the same order, so results are reproducible
+        for (int r = 0; r < world; ++r) {
+          const uint4 u = ld_peer_16(reinterpret_cast<const uint4*>(
+                                         reinterpret_cast<const __nv_bfloat16*>(grads.p[r]) + seg.flat_off) + i);
+          const float2 a0 = unpack_bf16x2(u.x), a1 = unpack_bf16x2(u.y), a2 = unpack_bf16x2(u.z), a3 = unpack_bf16x2(u.w);
+          g[0] += a0.x; g[1] += a0.y; g[2] += a1.x; g[3] += a1.y; g[4] += a2.x; g[5] += a2.y; g[6] += a3.x; g[7] += a3.y;
+        }
+      }
+      if (MODE == kReduceOnly) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sq += g[j] * g[j];
+        reinterpret_cast<float4*>(grad_shard + seg.shard_off)[2 * i] = make_float4(g[0], g[1], g[2], g[3]);
+        reinterpret_cast<float4*>(grad_shard + seg.shard_off)[2 * i + 1] = make_float4(g[4], g[5], g[6], g[7]);
+        continue;
+      }
+      float4* mp = reinterpret_cast<float4*>(master + seg.shard_off) + 2 * i;
+      float4* mm = reinterpret_cast<float4*>(m + seg.shard_off) + 2 * i;
+      float4* vv = reinterpret_cast<float4*>(v + seg.shard_off) + 2 * i;
+      float4 p0 = mp[0], p1 = mp[1], m0 = mm[0], m1 = mm[1], v0 = vv[0], v1 = vv[1];
+      float p[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+      float mo[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+      float vo[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float gj = g[j] * scale;
+        mo[j] = a.beta1 * mo[j] + (1.0f - a.beta1) * gj;
+        vo[j] = a.beta2 * vo[j] + (1.0f - a.beta2) * gj * gj;
+        p[j] = p[j] * decay - step * mo[j] / (sqrtf(vo[j]) * inv_sqrt_bc2 + a.eps);
+      }
+      mp[0] = make_float4(p[0], p[1], p[2], p[3]); mp[1] = make_float4(p[4], p[5], p[6], p[7]);
+      mm[0] = make_float4(mo[0], mo[1], mo[2], mo[3]); mm[1] = make_float4(mo[4], mo[5], mo[6], mo[7]);
+      vv[0] = make_float4(vo[0], vo[1], vo[2], vo[3]); vv[1] = make_float4(vo[4], vo[5], vo[6], vo[7]);
+      reinterpret_cast<uint4*>(param_out + seg.flat_off)[i] =
+          make_uint4(pack_bf16x2(p[0], p[1]), pack_bf16x2(p[2], p[3]), pack_bf16x2(p[4], p[5]), pack_bf16x2(p[6], p[7]));
+    }
+    // scalar tail (segments whose length is not a multiple of 8)
+    for (int i = nvec * 8 + blockIdx.x * blockDim.x + threadIdx.x; i < seg.numel; i += gridDim.x * blockDim.x) {
+      float g = 0.f;
+      if (MODE == kUpdateOnly) {
+        g = grad_shard[seg.shard_off + i];
+      } else {
+        for (int r = 0; r < world; ++r)
+          g += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(grads.p[r])[seg.flat_off + i]);
+      }
+      if (MODE == kReduceOnly) { sq += g * g; grad_shard[seg.shard_off + i] = g; continue; }
+      const float gj = g * scale;
+      const long long k = seg.shard_off + i;
+      const float mo = a.beta1 * m[k] + (1.0f - a.beta1) * gj;
+      const float vo = a.beta2 * v[k] + (1.0f - a.beta2) * gj * gj;
+      const float p = master[k] * decay - step * mo / (sqrtf(vo) * inv_sqrt_bc2 + a.eps);
+      master[k] = p; m[k] = mo; v[k] = vo;
+      param_out[seg.flat_off + i] = __float2bfloat16(p);
+    }
+  }
+  if (MODE == kReduceOnly && sq_partials) {
+    __shared__ float red[8];
+    sq = warp_sum(sq);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+      for (int w = 0; w < 8; ++w) t += red[w];
+      sq_partials[blockIdx.x] = t;
+    }
+  }
+}
+
+// out (+)= sum of partials in index order (single thread: a few hundred values)
+__global__ void sum_partials_kernel(const float* __restrict__ partials, int n, float* __restrict__ out, int accumulate) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < n; ++i) t += partials[i];
+    *out = accumulate ? *out + t : t;
+  }
+}
+
+}  // namespace comm
+}  // namespace ob
+
+using namespace ob;
+using namespace ob::comm;
+
+static PeerPtrs make_peers(const void* const* ptrs, int world) {
+  PeerPtrs p{};
+  for (int i = 0; i < world && i < MAX_RANKS; ++i) p.p[i] = const_cast<void*>(ptrs[i]);
+  return p;
+}
+
+extern "C" int ob_barrier(const void* const* flag_ptrs, int me, int world, int epoch, int* status,
+                          cudaStream_t stream) {
+  if (world > MAX_RANKS) return -1;
+  barrier_kernel<<<1, 32, 0, stream>>>(make_peers(flag_ptrs, world), me, world, epoch, status);
+  return (int)cudaGetLastError();
+}
+
+// tasks: device array of CopyTask (24 bytes each).  dst is this rank's buffer, src_ptrs the peers'.
+extern "C" int ob_pull(const void* tasks, int n_tasks, const void* const* src_ptrs, int world, void* dst, int* flags,
+                       int epoch, int n_ctas, cudaStream_t stream) {
+  if (world > MAX_RANKS) return -1;
+  if (n_tasks == 0) return 0;
+  if (n_ctas <= 0) n_ctas = 32;
+  if (n_ctas > n_tasks) n_ctas = n_tasks;
+  pull_kernel<<<n_ctas, 1024, 0, stream>>>((const CopyTask*)tasks, n_tasks, make_peers(src_ptrs, world),
+                                           (__nv_bfloat16*)dst, flags, epoch);
+  return (int)cudaGetLastError();
+}
+
+// mode: 0 fused reduce+AdamW, 1 reduce only (writes grad_shard, adds sum of squares to *sumsq_out),
+//       2 AdamW from grad_shard.  sq_scratch: >= n_ctas floats (mode 1).
+extern "C" int ob_rs_adamw(int mode, const void* segs, int n_segs, const void* const* grad_ptrs, int world,
+                           void* master, void* m, void* v, void* grad_shard, void* param_out, float lr, float beta1,
+                           float beta2, float eps, float bc1, float bc2, float grad_scale, float max_norm,
+                           const void* sumsq_in, void* sq_scratch, void* sumsq_out, int n_ctas, cudaStream_t stream) {
+  if (world > MAX_RANKS) return -1;
+  if (n_segs == 0) return 0;
+  if (n_ctas <= 0) n_ctas = 148 * 2;
+  AdamArgs a{lr, beta1, beta2, eps, bc1, bc2, grad_scale, max_norm, (const float*)sumsq_in};
+  PeerPtrs g = make_peers(grad_ptrs, world);
+  if (mode == kFused)
+    rs_adamw_kernel<kFused><<<n_ctas, 256, 0, stream>>>((const Segment*)segs, n_segs, g, world, (float*)master,
+                                                        (float*)m, (float*)v, nullptr, (__nv_bfloat16*)param_out, a,
+                                                        nullptr);
+  else if (mode == kReduceOnly) {
+    rs_adamw_kernel<kReduceOnly><<<n_ctas, 256, 0, stream>>>((const Segment*)segs, n_segs, g, world, nullptr, nullptr,
+                                                             nullptr, (float*)grad_shard, nullptr, a,
+                                                             (float*)sq_scratch);
+    if (sumsq_out) sum_partials_kernel<<<1, 32, 0, stream>>>((const float*)sq_scratch, n_ctas, (float*)sumsq_out, 1);
+  } else
+    rs_adamw_kernel<kUpdateOnly><<<n_ctas, 256, 0, stream>>>((const Segment*)segs, n_segs, g, world, (float*)master,
+                                                             (float*)m, (float*)v, (float*)grad_shard,
+                                                             (__nv_bfloat16*)param_out, a, nullptr);
+  return (int)cudaGetLastError();
+}

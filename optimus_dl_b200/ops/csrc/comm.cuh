@@ -1,0 +1,70 @@
+// Device-side pieces of the NVLink data plane: peer copy tasks, flags and bounded barriers.
+//
+// Every rank maps every peer's symmetric buffers, so a kernel addresses peer memory with
+// ordinary loads and stores (system scope where ordering matters).  No bulk-tensor copy with a
+// cluster-wide broadcast is used anywhere in this data plane.
+#pragma once
+#include "common.cuh"
+
+namespace ob {
+namespace comm {
+
+constexpr int MAX_RANKS = 16;
+
+struct PeerPtrs {
+  void* p[MAX_RANKS];
+};
+
+// One unit of copy work: `numel` bf16 elements at element offset `offset` (same offset on both
+// sides: buffers are symmetric) pulled from rank `peer`.  `flag` >= 0 names a readiness flag that
+// is set to the launch's epoch when the chunk has landed.
+struct CopyTask {
+  long long offset;
+  int numel;
+  short peer;
+  short pad;
+  int flag;
+};
+
+__device__ __forceinline__ uint4 ld_peer_16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+// Executed by a whole CTA: copy tasks [first, n) with stride `stride`.
+__device__ __forceinline__ void run_copy_tasks(const CopyTask* tasks, int n_tasks, int first, int stride,
+                                               const PeerPtrs& src, __nv_bfloat16* dst, int* flags, int epoch) {
+  for (int t = first; t < n_tasks; t += stride) {
+    const CopyTask task = tasks[t];
+    const __nv_bfloat16* s = reinterpret_cast<const __nv_bfloat16*>(src.p[task.peer]) + task.offset;
+    __nv_bfloat16* d = dst + task.offset;
+    const int nvec = (task.offset % 8 == 0) ? task.numel / 8 : 0;
+    constexpr int UNROLL = 4;
+    int i = threadIdx.x;
+    for (; i + (UNROLL - 1) * (int)blockDim.x < nvec; i += UNROLL * blockDim.x) {
+      uint4 v[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) v[u] = ld_peer_16(reinterpret_cast<const uint4*>(s) + i + u * blockDim.x);
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) reinterpret_cast<uint4*>(d)[i + u * blockDim.x] = v[u];
+    }
+    for (; i < nvec; i += blockDim.x) reinterpret_cast<uint4*>(d)[i] = ld_peer_16(reinterpret_cast<const uint4*>(s) + i);
+    for (int j = nvec * 8 + threadIdx.x; j < task.numel; j += blockDim.x) d[j] = s[j];
+    if (task.flag >= 0) {
+      // the consumer reads these bytes through TMA (async proxy): order our generic-proxy stores
+      asm volatile("fence.proxy.async.global;" ::: "memory");
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        __threadfence();
+        asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(flags + task.flag), "r"(epoch) : "memory");
+      }
+    }
+  }
+}
+
+}  // namespace comm
+}  // namespace ob

@@ -1,0 +1,82 @@
+// All-gather fused with the GEMM that consumes the gathered operand.
+//
+// One launch holds two kinds of CTAs:
+//   * copy CTAs (blockIdx < n_copy): pull remote shards of the operand over NVLink with plain
+//     peer loads, write them into this GPU's own buffer and publish a per-row-group flag;
+//     after the flagged tasks they keep pulling "trailing" tasks (the rest of a parameter
+//     group, which later kernels of the layer need) without flags;
+//   * GEMM CTAs: the persistent tcgen05 GEMM of gemm_core.cuh; its TMA producer waits for the
+//     flag of the rows a tile needs, and tiles are ordered so that rows this rank already owns
+//     come first and remote rows follow in the order the copy CTAs fetch them.
+// The operand therefore crosses NVLink once, lands where every later kernel reads it, and the
+// transfer overlaps the tensor-core work tile by tile.  Both weight-gathered (FSDP: B operand)
+// and activation-gathered (sequence parallel: A operand) forms are provided.
+#include "comm.cuh"
+#include "gemm_core.cuh"
+#include "tensormap.cuh"
+
+namespace ob {
+namespace gemm {
+
+constexpr int AG_THREADS = 1024;  // copy CTAs use all of them; GEMM CTAs only the first 192
+
+__global__ void __launch_bounds__(AG_THREADS, 1)
+ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p,
+               const comm::CopyTask* __restrict__ tasks, int n_tasks, comm::PeerPtrs src, __nv_bfloat16* dst,
+               int* flags, int epoch, int n_copy) {
+  extern __shared__ uint8_t smem_raw[];
+  if ((int)blockIdx.x < n_copy) {
+    comm::run_copy_tasks(tasks, n_tasks, blockIdx.x, n_copy, src, dst, flags, epoch);
+    return;
+  }
+  if (threadIdx.x >= NUM_THREADS) return;  // spare warps of a GEMM CTA
+  gemm_cta<0, 0, 0>(&tmA, &tmB, &tmB, p, blockIdx.x - n_copy, gridDim.x - n_copy, smem_raw);
+}
+
+}  // namespace gemm
+}  // namespace ob
+
+using namespace ob;
+using namespace ob::gemm;
+
+// C[M,N] = A[M,K] B[N,K]^T where B (gather_a = 0) or A (gather_a = 1) is being gathered by this
+// same launch.  `dst` is the local buffer that holds the gathered operand (and possibly more:
+// task offsets are relative to it), `src_ptrs` the peers' copies of it.  flags[i] >= epoch means
+// rows [i*flag_rows, (i+1)*flag_rows) of the gathered operand are in place; the caller pre-sets
+// the flags of locally owned rows.
+extern "C" int ob_gemm_ag_bf16(const void* A, long long lda, const void* B, long long ldb, void* C, long long ldc,
+                               int M, int N, int K, const void* bias, const void* tasks, int n_tasks,
+                               const void* const* src_ptrs, int world, void* dst, int* flags, int flag_rows,
+                               int epoch, int gather_a, int first_tile_shift, int n_copy, int* status,
+                               cudaStream_t stream) {
+  if (world > comm::MAX_RANKS) return -1;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d(&ta, A, M, K, lda, BM, BK, 2);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tb, B, N, K, ldb, BN, BK, 2);
+  if (rc) return rc;
+  Params p{};
+  p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.alpha = 1.0f; p.bias = bias; p.status = status;
+  p.flag_rows = 1; p.a_flag_rows = 1;
+  if (gather_a) { p.a_flags = flags; p.a_flag_rows = flag_rows; p.a_flag_value = epoch; p.tile_order = 2; }
+  else { p.b_flags = flags; p.flag_rows = flag_rows; p.flag_value = epoch; p.tile_order = 1; }
+  p.first_tile_shift = first_tile_shift;
+  static bool configured = false;
+  if (!configured) {
+    OB_CUDA_CHECK(cudaFuncSetAttribute(ag_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    configured = true;
+  }
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (n_tasks == 0) n_copy = 0;
+  if (n_copy > sms / 2) n_copy = sms / 2;
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  int gemm_ctas = sms - n_copy;
+  if (gemm_ctas > tiles) gemm_ctas = tiles;
+  comm::PeerPtrs src{};
+  for (int i = 0; i < world; ++i) src.p[i] = const_cast<void*>(src_ptrs[i]);
+  ag_gemm_kernel<<<n_copy + gemm_ctas, AG_THREADS, SMEM_BYTES, stream>>>(
+      ta, tb, p, (const comm::CopyTask*)tasks, n_tasks, src, (__nv_bfloat16*)dst, flags, epoch, n_copy);
+  return (int)cudaGetLastError();
+}

@@ -177,6 +177,7 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap* tmA, const CUtensorM
           const int f1 = (min(m0 + BM, p.M) - 1) / p.a_flag_rows;
           for (int f = f0; f <= f1 && ok; ++f) ok = wait_flag(p.a_flags + f, p.a_flag_value, abort_flag, p.status);
         }
+        if (p.b_flags || p.a_flags) asm volatile("fence.proxy.async.global;" ::: "memory");
         for (int kt = 0; kt < k_tiles && ok; ++kt) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status);
           if (!ok) break;

@@ -25,6 +25,7 @@ class _Embedding(torch.autograd.Function):
         ctx.save_for_backward(ids64)
         ctx.table_shape = (V, D)
         ctx.pad_id = -1 if pad_id is None else int(pad_id)
+        ctx.table = table  # for main_grad lookup
         return out.view(*ids.shape, D)
 
     @staticmethod
@@ -33,10 +34,19 @@ class _Embedding(torch.autograd.Function):
         V, D = ctx.table_shape
         sorted_ids, perm = torch.sort(ids64, stable=True)
         d2 = dout.reshape(-1, D).contiguous()
-        dtable = torch.zeros((V, D), dtype=dout.dtype, device=dout.device)
+        mg = getattr(ctx.table, "main_grad", None)
+        if mg is not None:
+            # scatter straight into the sharding engine's flat gradient buffer
+            if not getattr(ctx.table, "_main_grad_filled", False):
+                mg.zero_()
+                ctx.table._main_grad_filled = True
+            dtable, acc, ret = mg, 1, None
+        else:
+            dtable = torch.zeros((V, D), dtype=dout.dtype, device=dout.device)
+            acc, ret = 0, dtable
         _lib.check(_lib.lib().ob_embedding_bwd(_lib.ptr(sorted_ids), _lib.ptr(perm), _lib.ptr(d2), _lib.ptr(dtable),
-                                               ids64.numel(), D, V, ctx.pad_id, 0, _lib.stream()), "ob_embedding_bwd")
-        return None, dtable, None
+                                               ids64.numel(), D, V, ctx.pad_id, acc, _lib.stream()), "ob_embedding_bwd")
+        return None, ret, None
 
 
 def embedding(ids: torch.Tensor, table: torch.Tensor, padding_idx: int | None = None) -> torch.Tensor:

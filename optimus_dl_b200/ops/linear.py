@@ -67,7 +67,12 @@ class _MultiLinear(torch.autograd.Function):
         shp = x.shape
         x2 = x.reshape(-1, shp[-1])
         sizes = [w.shape[0] for w in ws]
-        if _adjacent(ws):
+        job = getattr(ws[0], "_ag_pending", None)
+        if job is not None and not job.done and _adjacent(ws):
+            # the weight is still being gathered from its owners: the same launch pulls it over
+            # NVLink and multiplies, tile by tile (parallel/fsdp.AGJob -> csrc/gemm_ag.cu)
+            y = job.run(x2 if x2.is_contiguous() else x2.contiguous(), _fused_bias(bs) if has_bias else None)
+        elif _adjacent(ws):
             wf = _fused_view(ws)
             bias = None
             if has_bias:

@@ -1,0 +1,211 @@
+"""Numerics of the sm_100a kernels against plain PyTorch fp32 references."""
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+def _close(a, b, rtol, atol, what=""):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    ref = b.abs().max().item()
+    assert err <= atol + rtol * ref, f"{what}: max err {err} vs ref max {ref}"
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (1000, 776, 328), (384, 1024, 2048)])
+def test_gemm_layouts(a_mn, b_mn, M, N, K):
+    from optimus_dl_b200.ops import _lib, gemm
+
+    torch.manual_seed(0)
+    A = torch.randn((K, M) if a_mn else (M, K), device=_dev(), dtype=torch.bfloat16)
+    B = torch.randn((K, N) if b_mn else (N, K), device=_dev(), dtype=torch.bfloat16)
+    out = gemm.gemm(A, B, a_mn=a_mn, b_mn=b_mn)
+    ref = (A.float().t() if a_mn else A.float()) @ (B.float() if b_mn else B.float().t())
+    _lib.check_status()
+    _close(out, ref, 1e-2, 1e-2, "gemm")
+
+
+def test_gemm_epilogues():
+    from optimus_dl_b200.ops import _lib, gemm
+
+    torch.manual_seed(0)
+    A = torch.randn(512, 256, device=_dev(), dtype=torch.bfloat16)
+    B = torch.randn(384, 256, device=_dev(), dtype=torch.bfloat16)
+    bias = torch.randn(384, device=_dev(), dtype=torch.bfloat16)
+    ref = A.float() @ B.float().t()
+    out32 = gemm.gemm(A, B, out_dtype=torch.float32)
+    _close(out32, ref, 1e-5, 1e-3, "fp32 out")
+    acc = torch.ones(512, 384, device=_dev(), dtype=torch.float32)
+    gemm.gemm(A, B, out=acc, accumulate=True)
+    _close(acc, ref + 1.0, 1e-5, 1e-3, "accumulate")
+    g = gemm.gemm(A, B, bias=bias, act="gelu", alpha=0.05)
+    _close(g, torch.nn.functional.gelu(ref * 0.05 + bias.float()), 1e-2, 1e-2, "bias+gelu")
+    _lib.check_status()
+
+
+def test_swiglu_dual_gemm_and_mlp_grad():
+    from optimus_dl_b200.ops import _lib, activation, gemm
+
+    torch.manual_seed(0)
+    d, f, T = 256, 768, 384
+    x = (torch.randn(T, d, device=_dev()) * 0.5).to(torch.bfloat16).requires_grad_()
+    w1 = (torch.randn(f, d, device=_dev()) * 0.05).to(torch.bfloat16).requires_grad_()
+    w2 = (torch.randn(f, d, device=_dev()) * 0.05).to(torch.bfloat16).requires_grad_()
+    wc = (torch.randn(d, f, device=_dev()) * 0.05).to(torch.bfloat16).requires_grad_()
+    h, g, u = gemm.swiglu_gemm(x.detach(), w1.detach(), w2.detach())
+    gr, ur = x.float() @ w1.float().t(), x.float() @ w2.float().t()
+    _close(g, gr, 1e-2, 1e-2, "gate")
+    _close(h, torch.nn.functional.silu(gr) * ur, 2e-2, 2e-2, "h")
+    y = activation.swiglu_mlp(x, w1, w2, wc)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xf, w1f, w2f, wcf = [t.detach().float().requires_grad_() for t in (x, w1, w2, wc)]
+    yr = (torch.nn.functional.silu(xf @ w1f.t()) * (xf @ w2f.t())) @ wcf.t()
+    yr.backward(dy.float())
+    _close(y, yr, 2e-2, 2e-2, "mlp y")
+    for a, b, n in ((x.grad, xf.grad, "dx"), (w1.grad, w1f.grad, "dw1"), (w2.grad, w2f.grad, "dw2"), (wc.grad, wcf.grad, "dwc")):
+        _close(a, b, 3e-2, 3e-2, n)
+    _lib.check_status()
+
+
+@pytest.mark.parametrize("D", [512, 4096])
+def test_rmsnorm_fwd_bwd(D):
+    from optimus_dl_b200.ops import norm
+
+    torch.manual_seed(0)
+    x = torch.randn(300, D, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    res = torch.randn(300, D, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(D, device=_dev())).to(torch.bfloat16).requires_grad_()
+    y, h = norm.rms_norm(x, w, 1e-5, residual=res)
+    dy, dh = torch.randn_like(y), torch.randn_like(h)
+    (y * dy).sum().backward(retain_graph=True)
+    gx1 = x.grad.clone()
+    x.grad = None; res.grad = None; w.grad = None
+    torch.autograd.backward([y, h], [dy, dh])
+    xf, rf, wf = [t.detach().float().requires_grad_() for t in (x, res, w)]
+    hf = (xf + rf).to(torch.bfloat16).float()  # the stream is stored in bf16
+    hf2 = xf + rf
+    yr = hf2 * torch.rsqrt(hf2.pow(2).mean(-1, keepdim=True) + 1e-5) * wf
+    torch.autograd.backward([yr, hf2], [dy.float(), dh.float()])
+    _close(y, yr, 2e-2, 2e-2, "y")
+    _close(h, hf, 1e-2, 1e-2, "h")
+    _close(x.grad, xf.grad, 3e-2, 3e-2, "dx")
+    _close(res.grad, rf.grad, 3e-2, 3e-2, "dres")
+    _close(w.grad, wf.grad, 3e-2, 5e-2, "dw")
+    assert gx1.isfinite().all()
+
+
+def test_layernorm_fwd_bwd():
+    from optimus_dl_b200.ops import norm
+
+    torch.manual_seed(0)
+    D = 768
+    x = torch.randn(257, D, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(D, device=_dev())).to(torch.bfloat16).requires_grad_()
+    b = (0.1 * torch.randn(D, device=_dev())).to(torch.bfloat16).requires_grad_()
+    y = norm.layer_norm(x, w, b)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xf, wf, bf = [t.detach().float().requires_grad_() for t in (x, w, b)]
+    yr = torch.nn.functional.layer_norm(xf, (D,), wf, bf, 1e-5)
+    yr.backward(dy.float())
+    _close(y, yr, 2e-2, 2e-2, "y")
+    _close(x.grad, xf.grad, 3e-2, 3e-2, "dx")
+    _close(w.grad, wf.grad, 3e-2, 5e-2, "dw")
+    _close(b.grad, bf.grad, 3e-2, 5e-2, "db")
+
+
+def test_adamw_matches_torch():
+    from optimus_dl_b200.ops import optim
+
+    torch.manual_seed(0)
+    n = 100003
+    p0 = torch.randn(n, device=_dev())
+    ref = torch.nn.Parameter(p0.clone())
+    o = torch.optim.AdamW([ref], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    master, m, v = p0.clone(), torch.zeros(n, device=_dev()), torch.zeros(n, device=_dev())
+    lp = torch.empty(n, device=_dev(), dtype=torch.bfloat16)
+    for step in range(1, 4):
+        g = torch.randn(n, device=_dev()).to(torch.bfloat16)
+        ref.grad = g.float()
+        o.step()
+        optim.adamw_step_(master, m, v, g, lp, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step)
+    _close(master, ref.detach(), 1e-5, 1e-5, "adamw")
+    _close(lp, ref.detach(), 1e-2, 1e-2, "bf16 copy")
+    out = torch.zeros(1, device=_dev())
+    optim.sumsq_(g, out)
+    _close(out, g.float().pow(2).sum().reshape(1), 1e-4, 1e-3, "sumsq")
+
+
+@pytest.mark.parametrize("softcap,stype,smooth", [(None, "tanh", 0.0), (30.0, "tanh", 0.1), (None, "sigmoid", 0.0)])
+def test_linear_cross_entropy(softcap, stype, smooth):
+    from optimus_dl_b200.ops import _lib, cross_entropy as ce
+
+    torch.manual_seed(0)
+    T, d, V = 700, 256, 5003
+    x = torch.randn(T, d, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(V, d, device=_dev()) * 0.05).to(torch.bfloat16).requires_grad_()
+    tg = torch.randint(0, V, (T,), device=_dev())
+    tg[::7] = -100
+    res = ce.linear_cross_entropy(x, w, tg, label_smoothing=smooth, softcap=softcap, softcap_type=stype, chunk_rows=256)
+    res.loss.backward()
+    xf, wf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    logits = (xf @ wf.t())
+    r = ce.cross_entropy_ref(logits.detach().to(torch.bfloat16).float() + (logits - logits.detach()), tg, -100, smooth, softcap, stype)
+    r.loss.backward()
+    assert abs(res.loss.item() - r.loss.item()) < 2e-2 * max(1.0, abs(r.loss.item()))
+    assert int(res.n_valid) == int(r.n_valid)
+    assert abs(int(res.n_correct) - int(r.n_correct)) <= 2
+    _close(x.grad, xf.grad, 5e-2, 1e-4, "dx")
+    _close(w.grad, wf.grad, 5e-2, 1e-4, "dw")
+    _lib.check_status()
+
+
+def test_embedding_fwd_bwd():
+    from optimus_dl_b200.ops import embedding
+
+    torch.manual_seed(0)
+    V, D = 1000, 256
+    table = torch.randn(V, D, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    ids = torch.randint(0, 50, (4, 64), device=_dev())  # many repeats
+    out = embedding.embedding(ids, table)
+    dout = torch.randn_like(out)
+    out.backward(dout)
+    tf = table.detach().float().requires_grad_()
+    torch.nn.functional.embedding(ids, tf).backward(dout.float())
+    assert torch.equal(out, table.detach()[ids])
+    _close(table.grad, tf.grad, 2e-2, 2e-2, "dtable")
+
+
+@pytest.mark.parametrize("hd,norm", [(64, False), (128, False), (128, True)])
+def test_rope_kernel_matches_reference(hd, norm):
+    from optimus_dl_b200.ops import rope
+
+    torch.manual_seed(0)
+    T, Hq, Hk = 100, 4, 2
+    W = (Hq + 2 * Hk) * hd
+    qkv = torch.randn(T, W, device=_dev(), dtype=torch.bfloat16)
+    freqs = rope.precompute_freqs_cis(hd, 256, 10000.0).to(_dev())
+    pos = torch.randint(0, 256, (T,), device=_dev(), dtype=torch.int32)
+    qw = (1 + 0.1 * torch.randn(hd, device=_dev())).to(torch.bfloat16) if norm else None
+    kw = (1 + 0.1 * torch.randn(hd, device=_dev())).to(torch.bfloat16) if norm else None
+    out = torch.empty_like(qkv)
+    rstd = torch.empty(T, Hq + Hk, device=_dev()) if norm else None
+    rope.rope_kernel_fwd(qkv, out, W, W, freqs, pos, qw, kw, rstd, T, Hq, Hk, hd, 256, 1e-6)
+    q = qkv[:, : Hq * hd].view(1, T, Hq, hd)
+    k = qkv[:, Hq * hd: (Hq + Hk) * hd].view(1, T, Hk, hd)
+    if norm:
+        from optimus_dl_b200.ops.norm import rms_norm_ref
+
+        q, k = rms_norm_ref(q, qw, 1e-6), rms_norm_ref(k, kw, 1e-6)
+    qr, kr = rope.apply_rotary_emb(q, k, freqs, pos.long().view(1, T))
+    _close(out[:, : Hq * hd].view(1, T, Hq, hd), qr, 2e-2, 2e-2, "q")
+    _close(out[:, Hq * hd: (Hq + Hk) * hd].view(1, T, Hk, hd), kr, 2e-2, 2e-2, "k")
