@@ -94,6 +94,8 @@ def main() -> None:
     ap.add_argument("--seq-len", type=int, default=None)
     ap.add_argument("--micro-batch", type=int, default=1)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--n-layer", type=int, default=None, help="override the layer count (profiling only; the "
+                    "reported metric then says so)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -128,6 +130,8 @@ def main() -> None:
     mcfg = dict(MODELS[args.model])
     seq = args.seq_len or mcfg["sequence_length"]
     mcfg["sequence_length"] = max(seq, mcfg["sequence_length"])
+    if args.n_layer is not None:
+        mcfg["n_layer"] = args.n_layer
     torch.manual_seed(0)
     prev = torch.get_default_dtype()
     torch.set_default_dtype(torch.bfloat16)
@@ -202,7 +206,7 @@ def main() -> None:
                "d2h_bytes_per_step": 4, "ms_per_step": ms2 / args.steps, "final_loss": last_loss.get("f")}
     if rank == 0:
         out = {
-            "metric": "Llama-3-8B FSDP2 bf16 train tokens/s (device-timed, max/rank)" if args.model == "llama3-8b"
+            "metric": "Llama-3-8B FSDP2 bf16 train tokens/s (device-timed, max/rank)" if (args.model == "llama3-8b" and args.n_layer is None)
             else f"{args.model} bf16 train tokens/s (device-timed, max/rank)",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,

@@ -1,0 +1,77 @@
+"""``tokenized_flat``: memory-maps raw token files as one stream, gives every rank an equal token
+span and yields ready ``(batch_size, seq_len + 1)`` blocks
+(optimus_dl/modules/data/datasets/tokenized_flat_dataset.py:17-173)."""
+
+from __future__ import annotations
+
+import glob
+import os
+from dataclasses import dataclass
+from typing import Any
+
+import numpy as np
+
+from ...core.registry import RegistryConfigStrict
+from . import register_dataset
+from .base import BaseDataset
+
+
+@dataclass
+class TokenizedFlatDatasetConfig(RegistryConfigStrict):
+    files: Any = "???"              # path, glob or list of paths
+    dtype: str = "uint16"
+    batch_size: int = 1
+    seq_len: int = 1024
+    header_bytes: int = 0
+    add_one_for_shift: bool = True
+
+
+@register_dataset("tokenized_flat", TokenizedFlatDatasetConfig)
+class TokenizedFlatDataset(BaseDataset):
+    def __init__(self, cfg, rank: int = 0, world_size: int = 1, seed: int = 0, **kwargs: Any):
+        super().__init__(cfg, rank, world_size, seed)
+        files = cfg.files
+        if isinstance(files, str):
+            files = sorted(glob.glob(os.path.expanduser(files))) or [os.path.expanduser(files)]
+        self.files = list(files)
+        self.maps = []
+        for f in self.files:
+            if f.endswith(".npy"):
+                self.maps.append(np.load(f, mmap_mode="r"))
+            else:
+                self.maps.append(np.memmap(f, dtype=np.dtype(cfg.dtype), mode="r", offset=int(cfg.header_bytes)))
+        self.cum = np.concatenate([[0], np.cumsum([len(m) for m in self.maps])]).astype(np.int64)
+        total = int(self.cum[-1])
+        per = total // world_size
+        self.start, self.end = rank * per, (rank + 1) * per
+        self.block = int(cfg.batch_size) * int(cfg.seq_len)
+        self.pos = self.start
+
+    def _read(self, a: int, b: int) -> np.ndarray:
+        out = np.empty(b - a, dtype=np.int64)
+        o = 0
+        f = int(np.searchsorted(self.cum, a, side="right") - 1)
+        while a < b:
+            fe = int(self.cum[f + 1])
+            take = min(b, fe)
+            out[o:o + take - a] = self.maps[f][a - int(self.cum[f]): take - int(self.cum[f])]
+            o += take - a
+            a = take
+            f += 1
+        return out
+
+    def reset(self, initial_state: dict | None = None):
+        super().reset(initial_state)
+        self.pos = int(initial_state["pos"]) if initial_state else self.start
+
+    def get_state(self) -> dict[str, Any]:
+        return {"pos": self.pos}
+
+    def next(self) -> dict[str, Any]:
+        extra = 1 if self.cfg.add_one_for_shift else 0
+        B, T = int(self.cfg.batch_size), int(self.cfg.seq_len)
+        if self.pos + self.block + extra > self.end:
+            raise StopIteration
+        rows = [self._read(self.pos + i * T, self.pos + (i + 1) * T + extra) for i in range(B)]
+        self.pos += self.block
+        return {"input_ids": np.stack(rows)}

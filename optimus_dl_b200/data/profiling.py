@@ -1,0 +1,145 @@
+"""Data-pipeline profiler (optimus_dl/modules/data/profiling.py:16-389).
+
+Every node built by a transform is wrapped in a ``ProfilingProxyNode`` when profiling is on. The
+profiler keeps, per node, total time inside ``next()`` and *self* time (total minus time spent in
+upstream nodes called on the same thread). A node whose upstream runs on another thread
+(prefetchers, parallel mappers) is an async boundary: time it spends waiting is reported as
+"blocked" rather than "compute". Every ``report_freq`` root batches a table is logged, slowest first.
+"""
+
+from __future__ import annotations
+
+import contextvars
+import logging
+import threading
+import time
+from contextlib import contextmanager
+from typing import Any
+
+from torchdata.nodes import BaseNode
+
+logger = logging.getLogger(__name__)
+
+_current_profiler: contextvars.ContextVar = contextvars.ContextVar("optimus_data_profiler", default=None)
+_call_stack = threading.local()
+
+
+@contextmanager
+def scope_profiler(profiler: "PipelineProfiler | None"):
+    tok = _current_profiler.set(profiler)
+    try:
+        yield profiler
+    finally:
+        _current_profiler.reset(tok)
+
+
+def current_profiler() -> "PipelineProfiler | None":
+    return _current_profiler.get()
+
+
+class NodeStats:
+    __slots__ = ("name", "calls", "total", "self_time", "threads", "parent_threads")
+
+    def __init__(self, name: str):
+        self.name, self.calls, self.total, self.self_time = name, 0, 0.0, 0.0
+        self.threads: set[int] = set()
+        self.parent_threads: set[int] = set()
+
+
+class PipelineProfiler:
+    def __init__(self, name: str, report_freq: int = 500):
+        self.name, self.report_freq = name, max(1, int(report_freq))
+        self.stats: dict[int, NodeStats] = {}
+        self.root_nodes: list[Any] = []
+        self._lock = threading.Lock()
+        self._root_batches = 0
+
+    def register(self, node_id: int, name: str) -> NodeStats:
+        with self._lock:
+            return self.stats.setdefault(node_id, NodeStats(name))
+
+    def record(self, node_id: int, total: float, child: float, is_root: bool, parent_thread: int | None) -> None:
+        st = self.stats[node_id]
+        with self._lock:
+            st.calls += 1
+            st.total += total
+            st.self_time += max(0.0, total - child)
+            st.threads.add(threading.get_ident())
+            if parent_thread is not None:
+                st.parent_threads.add(parent_thread)
+            if is_root:
+                self._root_batches += 1
+                due = self._root_batches % self.report_freq == 0
+            else:
+                due = False
+        if due:
+            logger.info("%s", self.report())
+
+    def is_async_boundary(self, st: NodeStats) -> bool:
+        return bool(st.threads and st.parent_threads and not (st.threads & st.parent_threads))
+
+    def report(self) -> str:
+        rows = sorted(self.stats.values(), key=lambda s: s.self_time, reverse=True)
+        lines = [f"data pipeline '{self.name}' after {self._root_batches} batches:",
+                 f"  {'node':<48}{'calls':>10}{'total s':>10}{'self s':>10}{'ms/call':>10}  kind"]
+        for s in rows:
+            kind = "blocked" if self.is_async_boundary(s) else "compute"
+            per = 1e3 * s.self_time / s.calls if s.calls else 0.0
+            lines.append(f"  {s.name[:47]:<48}{s.calls:>10}{s.total:>10.2f}{s.self_time:>10.2f}{per:>10.3f}  {kind}")
+        if rows:
+            lines.append(f"  bottleneck: {rows[0].name}")
+        return "\n".join(lines)
+
+
+class PipelineTracer:
+    """Prints the tree of nodes of a pipeline (debug aid)."""
+
+    @staticmethod
+    def describe(node: Any, depth: int = 0) -> str:
+        out = "  " * depth + repr(type(node).__name__)
+        for attr in ("node", "source", "inner"):
+            child = getattr(node, attr, None)
+            if child is not None:
+                out += "\n" + PipelineTracer.describe(child, depth + 1)
+                break
+        return out
+
+
+class ProfilingProxyNode(BaseNode):
+    def __init__(self, node: BaseNode, name: str, profiler: PipelineProfiler):
+        super().__init__()
+        self.node, self.name, self.profiler = node, name, profiler
+        self._is_root = False
+        self._creator_thread: int | None = None
+        profiler.register(id(self), name)
+
+    def reset(self, initial_state: dict | None = None):
+        super().reset(initial_state)
+        self.node.reset(initial_state)
+
+    def get_state(self) -> dict[str, Any]:
+        return self.node.state_dict()
+
+    def next(self):
+        stack = getattr(_call_stack, "frames", None)
+        if stack is None:
+            stack = _call_stack.frames = []
+        parent_thread = stack[-1][1] if stack else self._creator_thread
+        frame = [0.0, threading.get_ident()]
+        stack.append(frame)
+        t0 = time.perf_counter()
+        try:
+            return next(self.node)
+        finally:
+            dt = time.perf_counter() - t0
+            stack.pop()
+            if stack:
+                stack[-1][0] += dt
+            self.profiler.record(id(self), dt, frame[0], self._is_root, parent_thread)
+
+
+def maybe_profile(node: BaseNode, name: str) -> BaseNode:
+    prof = current_profiler()
+    if prof is None or isinstance(node, ProfilingProxyNode):
+        return node
+    return ProfilingProxyNode(node, name, prof)

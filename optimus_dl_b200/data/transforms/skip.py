@@ -1,0 +1,95 @@
+"""``skip_interleaved`` / ``skip_random``: drop items deterministically, e.g. to carve disjoint
+subsets out of one stream (optimus_dl/modules/data/transforms/skip.py)."""
+
+from __future__ import annotations
+
+import random
+from dataclasses import dataclass
+from typing import Any
+
+from torchdata.nodes import BaseNode
+
+from ...core.registry import RegistryConfigStrict
+from . import register_transform
+from .base import BaseTransform
+
+
+@dataclass
+class SkipInterleavedConfig(RegistryConfigStrict):
+    keep_every: int = 2      # keep one item out of this many
+    offset: int = 0          # index (mod keep_every) of the kept item
+
+
+class SkipInterleavedNode(BaseNode):
+    def __init__(self, node: BaseNode, keep_every: int, offset: int):
+        super().__init__()
+        self.node, self.keep_every, self.offset = node, max(1, int(keep_every)), int(offset)
+        self.count = 0
+
+    def reset(self, initial_state: dict | None = None):
+        super().reset(initial_state)
+        if initial_state:
+            self.count = initial_state["count"]
+            self.node.reset(initial_state["source_state"])
+        else:
+            self.count = 0
+            self.node.reset()
+
+    def get_state(self) -> dict[str, Any]:
+        return {"count": self.count, "source_state": self.node.state_dict()}
+
+    def next(self) -> Any:
+        while True:
+            item = next(self.node)
+            keep = self.count % self.keep_every == self.offset % self.keep_every
+            self.count += 1
+            if keep:
+                return item
+
+
+@register_transform("skip_interleaved", SkipInterleavedConfig)
+class SkipInterleaved(BaseTransform):
+    def build(self, source: BaseNode) -> BaseNode:
+        return SkipInterleavedNode(source, self.cfg.keep_every, self.cfg.offset)
+
+
+@dataclass
+class SkipRandomConfig(RegistryConfigStrict):
+    keep_probability: float = 0.5
+    seed: int = 0
+    invert: bool = False     # keep exactly the items the non-inverted transform drops
+
+
+class SkipRandomNode(BaseNode):
+    def __init__(self, node: BaseNode, p: float, seed: int, invert: bool):
+        super().__init__()
+        self.node, self.p, self.seed, self.invert = node, float(p), int(seed), bool(invert)
+        self.rng = random.Random(self.seed)
+
+    def reset(self, initial_state: dict | None = None):
+        super().reset(initial_state)
+        if initial_state:
+            self.rng.setstate(initial_state["rng"])
+            self.node.reset(initial_state["source_state"])
+        else:
+            self.rng = random.Random(self.seed)
+            self.node.reset()
+
+    def get_state(self) -> dict[str, Any]:
+        return {"rng": self.rng.getstate(), "source_state": self.node.state_dict()}
+
+    def next(self) -> Any:
+        while True:
+            item = next(self.node)
+            keep = self.rng.random() < self.p
+            if keep != self.invert:
+                return item
+
+
+@register_transform("skip_random", SkipRandomConfig)
+class SkipRandom(BaseTransform):
+    def __init__(self, cfg, seed: int = 0, **kwargs: Any):
+        super().__init__(cfg)
+
+    def build(self, source: BaseNode) -> BaseNode:
+        return SkipRandomNode(source, self.cfg.keep_probability, self.cfg.seed, self.cfg.invert)

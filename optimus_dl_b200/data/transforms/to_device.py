@@ -1,0 +1,63 @@
+"""``to_device``: numpy -> tensors, pin, asynchronous host-to-device copy, small prefetch so the copy
+of batch i+1 overlaps the compute of batch i (optimus_dl/modules/data/transforms/to_device.py:21-119)."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any
+
+import numpy as np
+import torch
+from torchdata.nodes import BaseNode, Mapper, PinMemory, Prefetcher
+
+from ...core.registry import RegistryConfigStrict
+from . import register_transform
+from .base import BaseTransform
+
+
+@dataclass
+class ToDeviceTransformConfig(RegistryConfigStrict):
+    device: str | None = None
+    pin_memory: bool = True
+    prefetch_factor: int = 2
+    non_blocking: bool = True
+
+
+def _to_tensor(batch: Any) -> Any:
+    if isinstance(batch, dict):
+        return {k: _to_tensor(v) for k, v in batch.items()}
+    if isinstance(batch, np.ndarray):
+        return torch.from_numpy(np.ascontiguousarray(batch))
+    return batch
+
+
+class _Mover:
+    def __init__(self, device: torch.device, non_blocking: bool):
+        self.device, self.non_blocking = device, non_blocking
+
+    def __call__(self, batch: Any) -> Any:
+        if isinstance(batch, dict):
+            return {k: self(v) for k, v in batch.items()}
+        if isinstance(batch, torch.Tensor):
+            return batch.to(self.device, non_blocking=self.non_blocking)
+        return batch
+
+
+@register_transform("to_device", ToDeviceTransformConfig)
+class ToDeviceTransform(BaseTransform):
+    def __init__(self, cfg, device: Any = None, **kwargs: Any):
+        super().__init__(cfg)
+        dev = cfg.device if cfg.device is not None else device
+        self.device = torch.device(dev) if dev is not None else torch.device("cuda" if torch.cuda.is_available() else "cpu")
+
+    def build(self, source: BaseNode) -> BaseNode:
+        node: BaseNode = Mapper(source, _to_tensor)
+        if self.device.type == "cuda":
+            if self.cfg.pin_memory:
+                node = PinMemory(node, pin_memory_device="cuda")
+            node = Mapper(node, _Mover(self.device, bool(self.cfg.non_blocking)))
+            if self.cfg.prefetch_factor and self.cfg.prefetch_factor > 0:
+                node = Prefetcher(node, prefetch_factor=int(self.cfg.prefetch_factor))
+        elif self.device.type != "cpu":
+            node = Mapper(node, _Mover(self.device, False))
+        return node

@@ -1,0 +1,60 @@
+"""``tokenize``: text -> token ids with a registry tokenizer through a parallel mapper
+(optimus_dl/modules/data/transforms/tokenize.py:27-103)."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any
+
+from torchdata.nodes import BaseNode, Mapper, ParallelMapper
+
+from ...core.registry import RegistryConfig
+from . import register_transform
+from .base import BaseTransform, MapperConfig
+
+
+@dataclass
+class TokenizeTransformConfig(RegistryConfig):
+    tokenizer_config: Any = None
+    worker_cfg: MapperConfig = field(default_factory=MapperConfig)
+    input_field: str = "text"
+    output_field: str = "input_ids"
+    keep_text: bool = False
+
+
+class _Tokenize:
+    """Picklable callable; the tokenizer is built lazily inside each worker."""
+
+    def __init__(self, tok_cfg: Any, in_f: str, out_f: str, keep: bool):
+        self.tok_cfg, self.in_f, self.out_f, self.keep = tok_cfg, in_f, out_f, keep
+        self._tok = None
+
+    def __call__(self, item: dict) -> dict:
+        if self._tok is None:
+            from ...tokenizer import build_tokenizer
+
+            self._tok = build_tokenizer(self.tok_cfg)
+        out = dict(item) if self.keep else {k: v for k, v in item.items() if k != self.in_f}
+        out[self.out_f] = self._tok.encode(item[self.in_f])
+        return out
+
+    def __getstate__(self):
+        return {"tok_cfg": self.tok_cfg, "in_f": self.in_f, "out_f": self.out_f, "keep": self.keep, "_tok": None}
+
+
+@register_transform("tokenize", TokenizeTransformConfig)
+class TokenizeTransform(BaseTransform):
+    def __init__(self, cfg, **kwargs: Any):
+        super().__init__(cfg)
+
+    def build(self, source: BaseNode) -> BaseNode:
+        from ...core import conf
+
+        tok_cfg = conf.to_container(self.cfg.tokenizer_config, resolve=True) if conf.is_config(self.cfg.tokenizer_config) \
+            else self.cfg.tokenizer_config
+        fn = _Tokenize(tok_cfg, self.cfg.input_field, self.cfg.output_field, bool(self.cfg.keep_text))
+        w = self.cfg.worker_cfg
+        if not w.num_workers:
+            return Mapper(source, fn)
+        return ParallelMapper(source, fn, num_workers=int(w.num_workers), in_order=bool(w.in_order), method=w.method,
+                              snapshot_frequency=int(w.snapshot_frequency), prebatch=w.prebatch)

@@ -54,6 +54,16 @@ class _CountingLib:
                 if torch.cuda.is_available():
                     _self._cdll.ob_bind_thread(torch.cuda.current_device())
             object.__setattr__(_self, "calls", _self.calls + 1)
+            if _timeline is not None:
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record()
+                rc = _fn(*args)
+                e.record()
+                key = name
+                if name == "ob_gemm_bf16":
+                    key = f"gemm a_mn={args[2]} b_mn={args[5]} {args[8]}x{args[9]}x{args[10]}"
+                _timeline.append((key, s, e))
+                return rc
             return _fn(*args)
 
         self._wrapped[name] = counted
@@ -77,6 +87,27 @@ def lib() -> "_CountingLib":
             _declare(cdll)
             _lib = _CountingLib(cdll)
     return _lib
+
+
+_timeline: list | None = None
+
+
+def timeline_start() -> None:
+    """Start bracketing every launcher call with CUDA events (diagnostics; adds launch overhead)."""
+    global _timeline
+    _timeline = []
+
+
+def timeline_report() -> dict[str, tuple[int, float]]:
+    """Stop the timeline; returns ``{launcher: (calls, total_ms)}`` measured on the launching stream."""
+    global _timeline
+    tl, _timeline = _timeline or [], None
+    torch.cuda.synchronize()
+    out: dict[str, tuple[int, float]] = {}
+    for name, s, e in tl:
+        n, ms = out.get(name, (0, 0.0))
+        out[name] = (n + 1, ms + s.elapsed_time(e))
+    return out
 
 
 def launch_count() -> int:

@@ -4,7 +4,7 @@
 //   delta kernel : delta[h, i] = sum_c dO[i,h,c] * O[i,h,c]
 //   dQ kernel    : one CTA per (128-query tile, head); loops over key tiles:
 //                    S = Q K^T, dP = dO V^T (tcgen05, operands in smem) -> TMEM
-//                    dS = exp2(S*scale - lse) * (dP - delta) * scale   (thread per query row)
+//                    dS = exp2(S*scale - lse) * (dP - delta)           (thread per query row)
 //                    dQ += dS K   (dS from TMEM, K tile re-read as an MN-major operand)
 //   dKV kernel   : one CTA per (128-key tile, kv head); loops over the query heads of the group
 //                  and the query tiles that can see these keys, transposed problem:
@@ -12,6 +12,12 @@
 //                    dV += P^T dO, dK += dS^T Q  (P^T / dS^T from TMEM, dO / Q tiles MN-major)
 // Recomputing S and dP in both kernels costs two extra products but needs no atomics: every
 // output element is written by exactly one CTA in a fixed order (bitwise reproducible).
+//
+// Pipelining: every 128-wide tile is processed as two 64-wide halves with their own TMEM
+// regions and barriers.  Two compute warpgroups (one per half) turn S/dP into P/dS while the
+// MMA warp already issues the products of the other half and of the next tile, so the tensor
+// pipe and the softmax arithmetic overlap.  The softmax scale is applied once in the epilogue
+// (dQ and dK), not per score.
 #include "common.cuh"
 #include "tensormap.cuh"
 
@@ -20,8 +26,9 @@ namespace attnb {
 
 constexpr int BM = 128;
 constexpr int BN = 128;
+constexpr int HALF = 64;
 constexpr int STAGES = 2;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;      // 8 compute warps + TMA warp + MMA warp
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct BwdParams {
@@ -73,14 +80,26 @@ __global__ void kv_last_q_kernel(const int* __restrict__ doc_start, int N, int w
   out[t] = lo;
 }
 
+__device__ __forceinline__ void store_row_bf16(__nv_bfloat16* drow, const uint32_t* o, float mul) {
+#pragma unroll
+  for (int v = 0; v < 4; ++v)
+    *reinterpret_cast<uint4*>(drow + 8 * v) =
+        make_uint4(pack_bf16x2(__uint_as_float(o[8 * v]) * mul, __uint_as_float(o[8 * v + 1]) * mul),
+                   pack_bf16x2(__uint_as_float(o[8 * v + 2]) * mul, __uint_as_float(o[8 * v + 3]) * mul),
+                   pack_bf16x2(__uint_as_float(o[8 * v + 4]) * mul, __uint_as_float(o[8 * v + 5]) * mul),
+                   pack_bf16x2(__uint_as_float(o[8 * v + 6]) * mul, __uint_as_float(o[8 * v + 7]) * mul));
+}
+
+// ============================================================================ dQ kernel
 template <int HD>
-struct SmemQ {   // dQ kernel
+struct SmemQ {
   static constexpr int TILE = BM * HD * 2;
   static constexpr int Q_OFF = 0, DO_OFF = TILE, K_OFF = 2 * TILE, V_OFF = K_OFF + STAGES * TILE;
   static constexpr int BAR_OFF = V_OFF + STAGES * TILE;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
+// TMEM columns: S_a [0,64) S_b [64,128) dP_a [128,192) dP_b [192,256) dQ [256,256+HD)
 template <int HD>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -89,14 +108,17 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   using L = SmemQ<HD>;
   constexpr int SLABS = HD / 64;
   constexpr int SLAB_BYTES = BM * 128;
+  constexpr int HALF_BYTES = HALF * 128;     // 64 rows of one slab
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   uint64_t* qdo_full = bars;
   uint64_t* k_full = bars + 1; uint64_t* k_empty = bars + 3;
   uint64_t* v_full = bars + 5; uint64_t* v_empty = bars + 7;
-  uint64_t* sdp_full = bars + 9; uint64_t* ds_ready = bars + 10; uint64_t* dq_final = bars + 11;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* sdp_full = bars + 9;      // [2] per half
+  uint64_t* ds_ready = bars + 11;     // [2] per half
+  uint64_t* dq_final = bars + 13;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -108,21 +130,25 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   int lo_first = p.doc_start[q_lo], lo_last = p.doc_start[q_hi];
   if (p.window > 0) { lo_first = max(lo_first, q_lo - p.window + 1); lo_last = max(lo_last, q_hi - p.window + 1); }
   const int j_lo = lo_first / BN, j_hi = q_hi / BN;
+  const int n_tiles = j_hi - j_lo + 1;
+  const int n_steps = 2 * n_tiles;
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
     for (int s = 0; s < STAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
-    mbar_init(sdp_full, 1); mbar_init(ds_ready, 4); mbar_init(dq_final, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&sdp_full[s], 1); mbar_init(&ds_ready[s], 4); }
+    mbar_init(dq_final, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 5) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  if (warp == 9) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 4) {
+  if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       mbar_arrive_expect_tx(qdo_full, 2 * L::TILE);
 #pragma unroll
@@ -131,8 +157,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tma_load_2d(smem + L::DO_OFF + s * SLAB_BYTES, &tmDO, qdo_full, h * HD + s * 64, q_lo);
       }
       bool ok = true;
-      for (int j = j_lo; j <= j_hi && ok; ++j) {
-        const int t = j - j_lo, st = t % STAGES;
+      for (int t = 0; t < n_tiles && ok; ++t) {
+        const int st = t % STAGES, j = j_lo + t;
         const uint32_t ph = (t / STAGES) & 1;
         ok = mbar_wait(&k_empty[st], ph ^ 1, abort_flag, p.status);
         if (!ok) break;
@@ -148,49 +174,62 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           tma_load_2d(smem + L::V_OFF + st * L::TILE + s * SLAB_BYTES, &tmV, &v_full[st], kvh * HD + s * 64, j * BN);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(BM, BN, 0, 0);
+      constexpr uint32_t idesc_s = make_idesc_bf16(BM, HALF, 0, 0);
       constexpr uint32_t idesc_dq = make_idesc_bf16(BM, HD, 0, 1);
       const uint32_t sQ = smem_u32(smem + L::Q_OFF), sDO = smem_u32(smem + L::DO_OFF);
       const uint32_t sK = smem_u32(smem + L::K_OFF), sV = smem_u32(smem + L::V_OFF);
       bool ok = mbar_wait(qdo_full, 0, abort_flag, p.status);
-      uint32_t ds_phase = 0;
-      for (int j = j_lo; j <= j_hi && ok; ++j) {
-        const int t = j - j_lo, st = t % STAGES;
-        const uint32_t ph = (t / STAGES) & 1;
-        ok = mbar_wait(&k_full[st], ph, abort_flag, p.status) && mbar_wait(&v_full[st], ph, abort_flag, p.status);
-        if (!ok) break;
+
+      auto issue_sdp = [&](int s) -> bool {
+        const int hf = s & 1, t = s >> 1, st = t % STAGES;
+        if (hf == 0) {
+          const uint32_t ph = (t / STAGES) & 1;
+          if (!mbar_wait(&k_full[st], ph, abort_flag, p.status)) return false;
+          if (!mbar_wait(&v_full[st], ph, abort_flag, p.status)) return false;
+        }
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk / 4) * SLAB_BYTES + (kk % 4) * 32;
-          umma_f16_ss(tmem_base, make_smem_desc_sw128(sQ + off, 16, 1024),
-                      make_smem_desc_sw128(sK + st * L::TILE + off, 16, 1024), idesc_s, kk ? 1u : 0u);
+          umma_f16_ss(tmem_base + hf * HALF, make_smem_desc_sw128(sQ + off, 16, 1024),
+                      make_smem_desc_sw128(sK + st * L::TILE + hf * HALF_BYTES + off, 16, 1024), idesc_s, kk ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk / 4) * SLAB_BYTES + (kk % 4) * 32;
-          umma_f16_ss(tmem_base + BN, make_smem_desc_sw128(sDO + off, 16, 1024),
-                      make_smem_desc_sw128(sV + st * L::TILE + off, 16, 1024), idesc_s, kk ? 1u : 0u);
+          umma_f16_ss(tmem_base + BN + hf * HALF, make_smem_desc_sw128(sDO + off, 16, 1024),
+                      make_smem_desc_sw128(sV + st * L::TILE + hf * HALF_BYTES + off, 16, 1024), idesc_s, kk ? 1u : 0u);
         }
-        umma_commit(sdp_full);
-        umma_commit(&v_empty[st]);
-        ok = mbar_wait(ds_ready, ds_phase, abort_flag, p.status);
+        umma_commit(&sdp_full[hf]);
+        if (hf == 1) umma_commit(&v_empty[st]);
+        return true;
+      };
+
+      if (ok) ok = issue_sdp(0);
+      if (ok) ok = issue_sdp(1);
+      for (int s = 0; s < n_steps && ok; ++s) {
+        const int hf = s & 1, t = s >> 1, st = t % STAGES;
+        ok = mbar_wait(&ds_ready[hf], t & 1, abort_flag, p.status);
         if (!ok) break;
-        ds_phase ^= 1;
         tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk)
-          umma_f16_ts(tmem_base + 2 * BN, tmem_base + kk * 8,
-                      make_smem_desc_sw128(sK + st * L::TILE + kk * 2048, SLAB_BYTES, 1024), idesc_dq,
-                      (j > j_lo || kk) ? 1u : 0u);
-        umma_commit(&k_empty[st]);
+        for (int kk = 0; kk < HALF / 16; ++kk)
+          umma_f16_ts(tmem_base + 2 * BN, tmem_base + hf * HALF + kk * 8,
+                      make_smem_desc_sw128(sK + st * L::TILE + hf * HALF_BYTES + kk * 2048, SLAB_BYTES, 1024), idesc_dq,
+                      (s > 0 || kk) ? 1u : 0u);
+        if (hf == 1) umma_commit(&k_empty[st]);
+        if (s + 2 < n_steps) ok = issue_sdp(s + 2);
       }
       umma_commit(dq_final);
     }
   } else {
-    const int row = warp * 32 + lane;
+    // ------------------------------------------------------------------ compute warpgroups
+    const int hf = warp >> 2;                 // which half of every key tile this warpgroup owns
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
     const int qi = q_lo + row;
     const bool row_valid = qi < p.N;
     int lo_row = 0;
@@ -201,76 +240,76 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       lse2 = p.lse[(long long)h * p.N + qi] * LOG2E;
       dl = p.delta[(long long)h * p.N + qi];
     }
-    const uint32_t t_s = tmem_base + (uint32_t(warp * 32) << 16);
-    uint32_t phase = 0;
+    const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16);
+    const uint32_t t_s = t_row + hf * HALF, t_dp = t_row + BN + hf * HALF;
     bool ok = true;
-    for (int j = j_lo; j <= j_hi && ok; ++j) {
-      ok = mbar_wait(sdp_full, phase, abort_flag, p.status);
+    for (int t = 0; t < n_tiles && ok; ++t) {
+      ok = mbar_wait(&sdp_full[hf], t & 1, abort_flag, p.status);
       if (!ok) break;
-      phase ^= 1;
       tc_fence_after();
-      const int k0 = j * BN;
-      const bool need_mask = (k0 + BN - 1 > q_lo) || (k0 < lo_last) || (q_lo + BM > p.N);
+      uint32_t s[HALF], dp[HALF], pk[HALF / 2];
+      tmem_ld_32x32(t_s, s);
+      tmem_ld_32x32(t_s + 32, s + 32);
+      tmem_ld_32x32(t_dp, dp);
+      tmem_ld_32x32(t_dp + 32, dp + 32);
+      tmem_ld_wait();
+      const int k0 = (j_lo + t) * BN + hf * HALF;
+      const bool need_mask = (k0 + HALF - 1 > q_lo) || (k0 < lo_last);
+      if (need_mask) {
 #pragma unroll
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t s[32], dp[32], pk[16];
-        tmem_ld_32x32(t_s + c, s);
-        tmem_ld_32x32(t_s + BN + c, dp);
-        tmem_ld_wait();
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float v[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int kj = k0 + c + e + u;
-            const bool valid = !need_mask || (row_valid && kj <= qi && kj >= lo_row);
-            const float pr = valid ? exp2f(__uint_as_float(s[e + u]) * p.scale_log2 - lse2) : 0.f;
-            v[u] = pr * (__uint_as_float(dp[e + u]) - dl) * p.scale;
-          }
-          pk[e / 2] = pack_bf16x2(v[0], v[1]);
+        for (int e = 0; e < HALF; e += 2) {
+          const int kj = k0 + e;
+          const bool v0 = row_valid && kj <= qi && kj >= lo_row;
+          const bool v1 = row_valid && kj + 1 <= qi && kj + 1 >= lo_row;
+          const float p0 = v0 ? exp2f(fmaf(__uint_as_float(s[e]), p.scale_log2, -lse2)) : 0.f;
+          const float p1 = v1 ? exp2f(fmaf(__uint_as_float(s[e + 1]), p.scale_log2, -lse2)) : 0.f;
+          pk[e / 2] = pack_bf16x2(p0 * (__uint_as_float(dp[e]) - dl), p1 * (__uint_as_float(dp[e + 1]) - dl));
         }
-        tmem_st_32x16(t_s + c / 2, pk);
+      } else {
+#pragma unroll
+        for (int e = 0; e < HALF; e += 2) {
+          const float p0 = exp2f(fmaf(__uint_as_float(s[e]), p.scale_log2, -lse2));
+          const float p1 = exp2f(fmaf(__uint_as_float(s[e + 1]), p.scale_log2, -lse2));
+          pk[e / 2] = pack_bf16x2(p0 * (__uint_as_float(dp[e]) - dl), p1 * (__uint_as_float(dp[e + 1]) - dl));
+        }
       }
+      tmem_st_32x16(t_s, pk);
+      tmem_st_32x16(t_s + 16, pk + 16);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(ds_ready);
+      if (lane == 0) mbar_arrive(&ds_ready[hf]);
     }
     if (ok) ok = mbar_wait(dq_final, 0, abort_flag, p.status);
     if (ok) {
       tc_fence_after();
+      // the two warpgroups split the head dimension of the output
       __nv_bfloat16* drow = p.dq + (long long)qi * p.dqkv_stride + h * HD;
 #pragma unroll
-      for (int c = 0; c < HD; c += 32) {
+      for (int c = hf * (HD / 2); c < (hf + 1) * (HD / 2); c += 32) {
         uint32_t o[32];
-        tmem_ld_32x32(t_s + 2 * BN + c, o);
+        tmem_ld_32x32(t_row + 2 * BN + c, o);
         tmem_ld_wait();
-        if (row_valid) {
-#pragma unroll
-          for (int v = 0; v < 4; ++v)
-            *reinterpret_cast<uint4*>(drow + c + 8 * v) =
-                make_uint4(pack_bf16x2(__uint_as_float(o[8 * v]), __uint_as_float(o[8 * v + 1])),
-                           pack_bf16x2(__uint_as_float(o[8 * v + 2]), __uint_as_float(o[8 * v + 3])),
-                           pack_bf16x2(__uint_as_float(o[8 * v + 4]), __uint_as_float(o[8 * v + 5])),
-                           pack_bf16x2(__uint_as_float(o[8 * v + 6]), __uint_as_float(o[8 * v + 7])));
-        }
+        if (row_valid) store_row_bf16(drow + c, o, p.scale);
       }
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+  if (warp == 9) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
+// ============================================================================ dK/dV kernel
 template <int HD>
-struct SmemKV {   // dK/dV kernel
+struct SmemKV {
   static constexpr int TILE = BM * HD * 2;
   static constexpr int K_OFF = 0, V_OFF = TILE, Q_OFF = 2 * TILE, DO_OFF = Q_OFF + STAGES * TILE;
-  static constexpr int VEC_OFF = DO_OFF + STAGES * TILE;            // [4 warps][3][BM] 4-byte values
-  static constexpr int BAR_OFF = VEC_OFF + 4 * 3 * BM * 4;
+  static constexpr int VEC_OFF = DO_OFF + STAGES * TILE;            // [8 warps][3][HALF] 4-byte values
+  static constexpr int BAR_OFF = VEC_OFF + 8 * 3 * HALF * 4;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
+// TMEM columns: S^T_a [0,64) S^T_b [64,128) dP^T_a [128,192) dP^T_b [192,256) dV [256,384) dK [384,512)
 template <int HD>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -279,18 +318,20 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   using L = SmemKV<HD>;
   constexpr int SLABS = HD / 64;
   constexpr int SLAB_BYTES = BM * 128;
+  constexpr int HALF_BYTES = HALF * 128;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   uint64_t* kv_full = bars;
   uint64_t* q_full = bars + 1; uint64_t* q_empty = bars + 3;
-  uint64_t* sdp_full = bars + 5; uint64_t* pds_ready = bars + 6; uint64_t* final_bar = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* sdp_full = bars + 5;      // [2]
+  uint64_t* pds_ready = bars + 7;     // [2]
+  uint64_t* final_bar = bars + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* vec = reinterpret_cast<float*>(smem + L::VEC_OFF);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_ktiles = (p.N + BN - 1) / BN;
   const int kvh = blockIdx.x % p.Hk;
   const int kt = blockIdx.x / p.Hk;               // early key tiles see the most queries: they go first
   const int G = p.Hq / p.Hk;
@@ -299,22 +340,23 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int i_hi = p.kv_last_q[kt] / BM;
   const int n_i = i_hi - i_lo + 1;
   const int n_iter = G * n_i;
-  (void)n_ktiles;
+  const int n_steps = 2 * n_iter;
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int s = 0; s < STAGES; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
-    mbar_init(sdp_full, 1); mbar_init(pds_ready, 4); mbar_init(final_bar, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&sdp_full[s], 1); mbar_init(&pds_ready[s], 4); }
+    mbar_init(final_bar, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 5) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  if (warp == 9) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 4) {
+  if (warp == 8) {
     if (lane == 0) {
       mbar_arrive_expect_tx(kv_full, 2 * L::TILE);
 #pragma unroll
@@ -337,67 +379,74 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(BN, BM, 0, 0);
+      constexpr uint32_t idesc_s = make_idesc_bf16(BN, HALF, 0, 0);
       constexpr uint32_t idesc_o = make_idesc_bf16(BN, HD, 0, 1);
       const uint32_t sK = smem_u32(smem + L::K_OFF), sV = smem_u32(smem + L::V_OFF);
       const uint32_t sQ = smem_u32(smem + L::Q_OFF), sDO = smem_u32(smem + L::DO_OFF);
       bool ok = mbar_wait(kv_full, 0, abort_flag, p.status);
-      uint32_t pds_phase = 0;
-      for (int it = 0; it < n_iter && ok; ++it) {
-        const int st = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1;
-        ok = mbar_wait(&q_full[st], ph, abort_flag, p.status);
-        if (!ok) break;
+
+      auto issue_sdp = [&](int s) -> bool {
+        const int hf = s & 1, it = s >> 1, st = it % STAGES;
+        if (hf == 0 && !mbar_wait(&q_full[st], (it / STAGES) & 1, abort_flag, p.status)) return false;
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk / 4) * SLAB_BYTES + (kk % 4) * 32;
-          umma_f16_ss(tmem_base, make_smem_desc_sw128(sK + off, 16, 1024),
-                      make_smem_desc_sw128(sQ + st * L::TILE + off, 16, 1024), idesc_s, kk ? 1u : 0u);
+          umma_f16_ss(tmem_base + hf * HALF, make_smem_desc_sw128(sK + off, 16, 1024),
+                      make_smem_desc_sw128(sQ + st * L::TILE + hf * HALF_BYTES + off, 16, 1024), idesc_s, kk ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk / 4) * SLAB_BYTES + (kk % 4) * 32;
-          umma_f16_ss(tmem_base + BM, make_smem_desc_sw128(sV + off, 16, 1024),
-                      make_smem_desc_sw128(sDO + st * L::TILE + off, 16, 1024), idesc_s, kk ? 1u : 0u);
+          umma_f16_ss(tmem_base + BM + hf * HALF, make_smem_desc_sw128(sV + off, 16, 1024),
+                      make_smem_desc_sw128(sDO + st * L::TILE + hf * HALF_BYTES + off, 16, 1024), idesc_s, kk ? 1u : 0u);
         }
-        umma_commit(sdp_full);
-        ok = mbar_wait(pds_ready, pds_phase, abort_flag, p.status);
+        umma_commit(&sdp_full[hf]);
+        return true;
+      };
+
+      if (ok) ok = issue_sdp(0);
+      if (ok && n_steps > 1) ok = issue_sdp(1);
+      for (int s = 0; s < n_steps && ok; ++s) {
+        const int hf = s & 1, it = s >> 1, st = it % STAGES;
+        ok = mbar_wait(&pds_ready[hf], it & 1, abort_flag, p.status);
         if (!ok) break;
-        pds_phase ^= 1;
         tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < BM / 16; ++kk)   // dV += P^T dO
-          umma_f16_ts(tmem_base + 2 * BM, tmem_base + kk * 8,
-                      make_smem_desc_sw128(sDO + st * L::TILE + kk * 2048, SLAB_BYTES, 1024), idesc_o,
-                      (it > 0 || kk) ? 1u : 0u);
+        for (int kk = 0; kk < HALF / 16; ++kk)   // dV += P^T dO
+          umma_f16_ts(tmem_base + 2 * BM, tmem_base + hf * HALF + kk * 8,
+                      make_smem_desc_sw128(sDO + st * L::TILE + hf * HALF_BYTES + kk * 2048, SLAB_BYTES, 1024), idesc_o,
+                      (s > 0 || kk) ? 1u : 0u);
 #pragma unroll
-        for (int kk = 0; kk < BM / 16; ++kk)   // dK += dS^T Q
-          umma_f16_ts(tmem_base + 3 * BM, tmem_base + BM + kk * 8,
-                      make_smem_desc_sw128(sQ + st * L::TILE + kk * 2048, SLAB_BYTES, 1024), idesc_o,
-                      (it > 0 || kk) ? 1u : 0u);
-        umma_commit(&q_empty[st]);
+        for (int kk = 0; kk < HALF / 16; ++kk)   // dK += dS^T Q
+          umma_f16_ts(tmem_base + 3 * BM, tmem_base + BM + hf * HALF + kk * 8,
+                      make_smem_desc_sw128(sQ + st * L::TILE + hf * HALF_BYTES + kk * 2048, SLAB_BYTES, 1024), idesc_o,
+                      (s > 0 || kk) ? 1u : 0u);
+        if (hf == 1) umma_commit(&q_empty[st]);
+        if (s + 2 < n_steps) ok = issue_sdp(s + 2);
       }
       umma_commit(final_bar);
     }
   } else {
-    const int row = warp * 32 + lane;        // key row == TMEM lane
+    const int hf = warp >> 2;
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;        // key row == TMEM lane
     const int kj = k0 + row;
     const bool key_valid = kj < p.N;
-    const uint32_t t_s = tmem_base + (uint32_t(warp * 32) << 16);
-    uint32_t phase = 0;
+    const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16);
+    const uint32_t t_s = t_row + hf * HALF, t_dp = t_row + BM + hf * HALF;
+    float* vb = vec + warp * 3 * HALF;          // this warp's copy: lse*log2e, delta, lowest key
+    int* lo_s = reinterpret_cast<int*>(vb + 2 * HALF);
     bool ok = true;
     for (int it = 0; it < n_iter && ok; ++it) {
       const int g = it / n_i, i = i_lo + it % n_i, h = kvh * G + g;
-      // every warp keeps its own copy of the per-query vectors (no CTA-wide barrier needed)
-      float* vb = vec + warp * 3 * BM;
-      int* lo_s = reinterpret_cast<int*>(vb + 2 * BM);
+      const int q_first = i * BM + hf * HALF;
       __syncwarp();
 #pragma unroll
-      for (int cc = lane; cc < BM; cc += 32) {
-        const int qi = i * BM + cc;
+      for (int cc = lane; cc < HALF; cc += 32) {
+        const int qi = q_first + cc;
         float l2 = 0.f, dl = 0.f;
         int lo = 0x7fffffff;
         if (qi < p.N) {
@@ -406,72 +455,82 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           lo = p.doc_start[qi];
           if (p.window > 0) lo = max(lo, qi - p.window + 1);
         }
-        vb[cc] = l2; vb[BM + cc] = dl; lo_s[cc] = lo;
+        vb[cc] = l2; vb[HALF + cc] = dl; lo_s[cc] = lo;
       }
       __syncwarp();
-      ok = mbar_wait(sdp_full, phase, abort_flag, p.status);
+      ok = mbar_wait(&sdp_full[hf], it & 1, abort_flag, p.status);
       if (!ok) break;
-      phase ^= 1;
       tc_fence_after();
-      const int q_first = i * BM;
-      const bool need_mask = (q_first < k0 + BN - 1) || (lo_s[BM - 1] > k0) || (k0 + BN > p.N);
+      uint32_t s[HALF], dp[HALF], pk[HALF / 2], dk_[HALF / 2];
+      tmem_ld_32x32(t_s, s);
+      tmem_ld_32x32(t_s + 32, s + 32);
+      tmem_ld_32x32(t_dp, dp);
+      tmem_ld_32x32(t_dp + 32, dp + 32);
+      tmem_ld_wait();
+      const bool need_mask = (q_first < k0 + BN - 1) || (lo_s[HALF - 1] > k0) || (k0 + BN > p.N);
+      if (need_mask) {
 #pragma unroll
-      for (int c = 0; c < BM; c += 32) {
-        uint32_t s[32], dp[32], pk[16], dk_[16];
-        tmem_ld_32x32(t_s + c, s);
-        tmem_ld_32x32(t_s + BM + c, dp);
-        tmem_ld_wait();
+        for (int e = 0; e < HALF; e += 4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(vb + e);
+          const float4 d4 = *reinterpret_cast<const float4*>(vb + HALF + e);
+          const int4 lo4 = *reinterpret_cast<const int4*>(lo_s + e);
+          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv4[4] = {d4.x, d4.y, d4.z, d4.w};
+          const int lov[4] = {lo4.x, lo4.y, lo4.z, lo4.w};
+          float pr[4], ds[4];
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float pv[2], dv_[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = c + e + u;
-            const int qi = q_first + col;
-            const bool valid = !need_mask || (key_valid && kj <= qi && kj >= lo_s[col]);
-            const float pr = valid ? exp2f(__uint_as_float(s[e + u]) * p.scale_log2 - vb[col]) : 0.f;
-            pv[u] = pr;
-            dv_[u] = pr * (__uint_as_float(dp[e + u]) - vb[BM + col]) * p.scale;
+          for (int u = 0; u < 4; ++u) {
+            const int qi = q_first + e + u;
+            const bool valid = key_valid && kj <= qi && kj >= lov[u];
+            pr[u] = valid ? exp2f(fmaf(__uint_as_float(s[e + u]), p.scale_log2, -lv[u])) : 0.f;
+            ds[u] = pr[u] * (__uint_as_float(dp[e + u]) - dv4[u]);
           }
-          pk[e / 2] = pack_bf16x2(pv[0], pv[1]);
-          dk_[e / 2] = pack_bf16x2(dv_[0], dv_[1]);
+          pk[e / 2] = pack_bf16x2(pr[0], pr[1]); pk[e / 2 + 1] = pack_bf16x2(pr[2], pr[3]);
+          dk_[e / 2] = pack_bf16x2(ds[0], ds[1]); dk_[e / 2 + 1] = pack_bf16x2(ds[2], ds[3]);
         }
-        tmem_st_32x16(t_s + c / 2, pk);
-        tmem_st_32x16(t_s + BM + c / 2, dk_);
+      } else {
+#pragma unroll
+        for (int e = 0; e < HALF; e += 4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(vb + e);
+          const float4 d4 = *reinterpret_cast<const float4*>(vb + HALF + e);
+          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv4[4] = {d4.x, d4.y, d4.z, d4.w};
+          float pr[4], ds[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            pr[u] = exp2f(fmaf(__uint_as_float(s[e + u]), p.scale_log2, -lv[u]));
+            ds[u] = pr[u] * (__uint_as_float(dp[e + u]) - dv4[u]);
+          }
+          pk[e / 2] = pack_bf16x2(pr[0], pr[1]); pk[e / 2 + 1] = pack_bf16x2(pr[2], pr[3]);
+          dk_[e / 2] = pack_bf16x2(ds[0], ds[1]); dk_[e / 2 + 1] = pack_bf16x2(ds[2], ds[3]);
+        }
       }
+      tmem_st_32x16(t_s, pk);
+      tmem_st_32x16(t_s + 16, pk + 16);
+      tmem_st_32x16(t_dp, dk_);
+      tmem_st_32x16(t_dp + 16, dk_ + 16);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(pds_ready);
+      if (lane == 0) mbar_arrive(&pds_ready[hf]);
     }
     if (ok) ok = mbar_wait(final_bar, 0, abort_flag, p.status);
     if (ok) {
       tc_fence_after();
+      // warpgroup 0 writes dV, warpgroup 1 writes dK (scaled)
+      __nv_bfloat16* drow = (hf == 0 ? p.dv : p.dk) + (long long)kj * p.dqkv_stride + kvh * HD;
+      const uint32_t t_acc = t_row + (2 + hf) * BM;
+      const float mul = hf == 0 ? 1.0f : p.scale;
 #pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        __nv_bfloat16* drow = (which == 0 ? p.dv : p.dk) + (long long)kj * p.dqkv_stride + kvh * HD;
-        const uint32_t t_acc = t_s + (2 + which) * BM;
-#pragma unroll
-        for (int c = 0; c < HD; c += 32) {
-          uint32_t o[32];
-          tmem_ld_32x32(t_acc + c, o);
-          tmem_ld_wait();
-          if (key_valid) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v)
-              *reinterpret_cast<uint4*>(drow + c + 8 * v) =
-                  make_uint4(pack_bf16x2(__uint_as_float(o[8 * v]), __uint_as_float(o[8 * v + 1])),
-                             pack_bf16x2(__uint_as_float(o[8 * v + 2]), __uint_as_float(o[8 * v + 3])),
-                             pack_bf16x2(__uint_as_float(o[8 * v + 4]), __uint_as_float(o[8 * v + 5])),
-                             pack_bf16x2(__uint_as_float(o[8 * v + 6]), __uint_as_float(o[8 * v + 7])));
-          }
-        }
+      for (int c = 0; c < HD; c += 32) {
+        uint32_t o[32];
+        tmem_ld_32x32(t_acc + c, o);
+        tmem_ld_wait();
+        if (key_valid) store_row_bf16(drow + c, o, mul);
       }
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+  if (warp == 9) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
 }  // namespace attnb
