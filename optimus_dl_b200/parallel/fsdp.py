@@ -283,7 +283,7 @@ class ShardGroup:
         b1, b2 = hp["betas"]
         bc1 = 1.0 - b1 ** step
         bc2 = 1.0 - b2 ** step
-        n_ctas = n_ctas or 296
+        n_ctas = n_ctas or 888
         rc = _lib.lib().ob_rs_adamw(mode, _lib.ptr(segs), self._n_segments, self.grad_buf.peers.c, self.world,
                                     _lib.ptr(self.master), _lib.ptr(self.exp_avg), _lib.ptr(self.exp_avg_sq),
                                     _lib.ptr(self.grad_shard), _lib.ptr(self.flat_param), float(hp["lr"]), float(b1),
@@ -480,7 +480,7 @@ class ShardingEngine:
                 g.gathered = self.world == 1
             else:
                 hp = opt.hyper() if opt is not None else dict(lr=0.0, betas=(0.9, 0.999), eps=1e-8)
-                g.rs_adamw(1, hp, 1, 1.0, sumsq=self.sumsq, scratch=self.sq_scratch, n_ctas=296)
+                g.rs_adamw(1, hp, 1, 1.0, sumsq=self.sumsq, scratch=self.sq_scratch, n_ctas=888)
 
     # ---------------------------------------------------------------- accumulation / step protocol
     def set_requires_gradient_sync(self, flag: bool) -> None:

@@ -1,0 +1,28 @@
+"""Multi-GPU checks (run as child processes over NCCL + peer memory, NVLS off)."""
+
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(script: str, nproc: int, port: int, *args: str, timeout: int = 600) -> str:
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, script), *args]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+    out = res.stdout + res.stderr
+    assert res.returncode == 0, out[-4000:]
+    return out
+
+
+@pytest.mark.parametrize("clip", ["0", "0.5"])
+def test_fsdp_matches_single_process(unique_port, clip):
+    n = min(torch.cuda.device_count(), 4)
+    out = _run("_mp_fsdp_check.py", n, unique_port, clip)
+    assert "MP_FSDP_OK" in out, out[-4000:]
