@@ -276,3 +276,65 @@ extern "C" int ob_layernorm_bwd(const void* dy, const void* x, const void* w, co
   reduce_partials_kernel<<<(D + 255) / 256, 256, 0, stream>>>(dbp, grid, D, (__nv_bfloat16*)db_bf16, nullptr, 0);
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------------------------
+// RMSNorm backward for callers that must not allocate (declared in rmsnorm_bwd_noalloc.h).
+//
+// Same math and kernels as ob_rmsnorm_bwd, but the per-CTA weight-gradient partials live in a
+// fixed array inside this library instead of a buffer the caller allocates.
+#include "rmsnorm_bwd_noalloc.h"
+
+#include <cstdio>
+#include <mutex>
+
+// 128 CTAs x 8192 columns x 4 bytes = 4 MiB per GPU that loads the library, held until exit.
+static __device__ __align__(256) float g_rmsnorm_bwd_partials[OB_RMSNORM_NOALLOC_MAX_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_partials_ptr[kMaxDevices] = {};
+std::mutex g_partials_mutex;
+
+// Device address of the array on the current device; looked up once per device (the array's
+// name is only a host-side handle and must never be handed to a kernel directly).
+int partials_for_current_device(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return OB_RMSNORM_NOALLOC_ERR_DEVICE;
+  std::lock_guard<std::mutex> lock(g_partials_mutex);
+  if (g_partials_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_rmsnorm_bwd_partials);
+    if (e != cudaSuccess) return (int)e;
+    g_partials_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_partials_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" int ob_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const void* rstd, void* dx,
+                                      void* dw_bf16, int rows, int D, cudaStream_t stream) {
+  if (rows < 0 || D <= 0 || !norm_args_ok(D)) {
+    std::fprintf(stderr, "ob_rmsnorm_bwd_noalloc: unsupported width D=%d (need D %% 8 == 0 and D <= %d)\n", D,
+                 THREADS * 8 * MAX_VEC);
+    return OB_RMSNORM_NOALLOC_ERR_SHAPE;
+  }
+  if (rows == 0) return 0;
+  const int grid = rows < OB_RMSNORM_NOALLOC_MAX_CTAS ? rows : OB_RMSNORM_NOALLOC_MAX_CTAS;
+  if ((long long)grid * D > (long long)OB_RMSNORM_NOALLOC_MAX_FLOATS) {
+    std::fprintf(stderr, "ob_rmsnorm_bwd_noalloc: %d CTAs x D=%d needs %lld floats of scratch, the built-in array holds %d\n",
+                 grid, D, (long long)grid * D, OB_RMSNORM_NOALLOC_MAX_FLOATS);
+    return OB_RMSNORM_NOALLOC_ERR_TOO_LARGE;
+  }
+  float* partial = nullptr;
+  const int rc = partials_for_current_device(&partial);
+  if (rc != 0) return rc;
+  // every CTA overwrites its whole row of partials, so nothing has to be cleared between calls
+  norm_bwd_kernel<false><<<grid, THREADS, 0, stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+                                                       (const __nv_bfloat16*)w, (const float*)rstd, nullptr, nullptr,
+                                                       (__nv_bfloat16*)dx, partial, nullptr, rows, D);
+  reduce_partials_kernel<<<(D + 255) / 256, 256, 0, stream>>>(partial, grid, D, (__nv_bfloat16*)dw_bf16, nullptr, 0);
+  return (int)cudaGetLastError();
+}
