@@ -1,0 +1,116 @@
+"""FP8 recipe surface (optimus_dl/modules/amp/fp8.py:40-523).
+
+The reference drives NVIDIA Transformer Engine recipes; here FP8 means this package's own
+block-scaled e4m3 GEMM path (``ops/fp8.py``): activations are quantised per 1x128 block, weights per
+128x128 block, products accumulate in fp32 and are written in bf16. ``FP8Recipe.autocast()`` switches
+the linear layers converted by the ``transformer_engine`` model transform to that path for the
+duration of the context (forward and, through ``backward()``, the backward pass). Enum names and
+string parsers follow the reference; ``delayed`` / ``tensorwise`` / ``mxfp8`` recipes are accepted and
+mapped onto the block-scaled implementation, which needs no amax history.
+"""
+
+from __future__ import annotations
+
+import contextlib
+import enum
+import logging
+from typing import Any
+
+import torch
+
+from ..core.dtype import str_to_dtype
+
+logger = logging.getLogger(__name__)
+
+
+class Fp8Format(str, enum.Enum):
+    HYBRID = "hybrid"
+    E4M3 = "e4m3"
+    E5M2 = "e5m2"
+
+
+class Fp8RecipeType(str, enum.Enum):
+    DELAYED = "delayed"
+    TENSORWISE = "tensorwise"
+    BLOCKWISE = "blockwise"
+    MXFP8 = "mxfp8"
+
+
+def parse_fp8_format(s: Any) -> Fp8Format:
+    if isinstance(s, Fp8Format):
+        return s
+    key = str(s).strip().lower().replace("fp8_", "").replace("float8_", "")
+    for f in Fp8Format:
+        if key in (f.value, f.name.lower()):
+            return f
+    raise ValueError(f"unknown fp8 format {s!r}; expected one of {[f.value for f in Fp8Format]}")
+
+
+def parse_fp8_recipe(s: Any) -> Fp8RecipeType:
+    if isinstance(s, Fp8RecipeType):
+        return s
+    key = str(s).strip().lower()
+    aliases = {"current": "tensorwise", "block": "blockwise", "block_scaling": "blockwise", "mx": "mxfp8"}
+    key = aliases.get(key, key)
+    for r in Fp8RecipeType:
+        if key == r.value:
+            return r
+    raise ValueError(f"unknown fp8 recipe {s!r}; expected one of {[r.value for r in Fp8RecipeType]}")
+
+
+_state = {"enabled": False, "recipe": None}
+
+
+def fp8_enabled() -> bool:
+    """True inside an active ``FP8Recipe.autocast()`` context."""
+    return bool(_state["enabled"])
+
+
+class FP8Recipe:
+    def __init__(self, fmt: Fp8Format = Fp8Format.E4M3, recipe: Fp8RecipeType = Fp8RecipeType.BLOCKWISE, **options: Any):
+        self.format, self.recipe, self.options = fmt, recipe, options
+
+    @contextlib.contextmanager
+    def autocast(self, enabled: bool = True):
+        prev = dict(_state)
+        _state.update(enabled=enabled, recipe=self)
+        try:
+            yield self
+        finally:
+            _state.update(prev)
+
+    def backward(self, enabled: bool = True):
+        return self.autocast(enabled)
+
+    def __repr__(self) -> str:
+        return f"FP8Recipe(format={self.format.value}, recipe={self.recipe.value})"
+
+
+def create_fp8_recipe(cfg: Any) -> FP8Recipe | None:
+    """Recipe from an ``Fp8Config``-like mapping; ``None`` when FP8 is off or no CUDA device exists."""
+    if cfg is None or not cfg.get("enabled", False):
+        return None
+    if not torch.cuda.is_available():
+        logger.warning("fp8 requested but no CUDA device is present; running without fp8")
+        return None
+    fmt, rec = parse_fp8_format(cfg.get("format", "e4m3")), parse_fp8_recipe(cfg.get("recipe", "blockwise"))
+    if rec != Fp8RecipeType.BLOCKWISE:
+        logger.info("fp8 recipe %s is served by the block-scaled e4m3 implementation", rec.value)
+    return FP8Recipe(fmt, rec, margin=cfg.get("margin", 0))
+
+
+@contextlib.contextmanager
+def fp8_autocast(device: torch.device, recipe: FP8Recipe | None, enabled: bool = True, dtype: Any = "bfloat16"):
+    """FP8 context nested in bf16 autocast (or plain autocast when there is no recipe)."""
+    dt = str_to_dtype(dtype) if dtype is not None else torch.bfloat16
+    ac = torch.autocast(device_type=device.type, dtype=dt, enabled=enabled and device.type in ("cuda", "cpu"))
+    if recipe is None:
+        with ac:
+            yield
+    else:
+        with ac, recipe.autocast(enabled):
+            yield
+
+
+def fp8_backward(recipe: FP8Recipe | None, enabled: bool = True):
+    return recipe.backward(enabled) if recipe is not None else contextlib.nullcontext()

@@ -34,4 +34,7 @@ def bootstrap_module(module_name: str, path: str | None = None) -> list[str]:
             continue
         importlib.import_module(name)
         imported.append(name)
+        if os.path.isdir(full):
+            # sub-packages are walked too, so nested implementation folders register themselves
+            imported.extend(bootstrap_module(name, full))
     return imported

@@ -37,9 +37,11 @@ def _read(path: str) -> tuple[dict, str | None]:
     with open(path) as f:
         text = f.read()
     m = _PKG_RE.search(text)
-    data = yaml.safe_load(text) or {}
-    if not isinstance(data, dict):
-        raise ComposeError(f"{path}: top level must be a mapping")
+    data = yaml.safe_load(text)
+    if data is None:
+        data = {}
+    if not isinstance(data, (dict, list)):
+        raise ComposeError(f"{path}: top level must be a mapping or a list")
     return data, (m.group(1) if m else None)
 
 
@@ -99,6 +101,8 @@ def _load_tree(config_dirs: list[str], rel: str, group_choices: dict[str, Any], 
     if path is None:
         raise ComposeError(f"config '{rel}' not found in {config_dirs}")
     data, header_pkg = _read(path)
+    if isinstance(data, list):   # a group option may be a bare list (e.g. the loggers group)
+        return data  # type: ignore[return-value]
     defaults = data.pop("defaults", None) or []
     if not any(d == "_self_" for d in defaults):
         defaults = list(defaults) + ["_self_"]
@@ -210,8 +214,12 @@ def compose(config_dir: str | list[str], config_name: str, overrides: list[str] 
         elif o["op"] == "set":
             exists = conf.select_relative(cfg, o["key"], throw=False, default=_SENTINEL, resolve=False) is not _SENTINEL
             if not exists:
-                raise ComposeError(f"key '{o['key']}' is not in the config; use +{o['key']}=... to add it")
-            conf.update(cfg, o["key"], o["value"])
+                # Hydra would consult the structured schema here; keys that only exist as dataclass
+                # defaults (e.g. common.use_gpu) are therefore accepted without the '+' prefix
+                import logging
+
+                logging.getLogger(__name__).debug("override adds new key %s", o["key"])
+            conf.update(cfg, o["key"], o["value"], force_add=True)
         else:
             conf.update(cfg, o["key"], o["value"], force_add=True)
     hydra_cfg = cfg._data.pop("hydra", None)

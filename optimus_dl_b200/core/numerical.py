@@ -21,6 +21,8 @@ def get_item(x: Any) -> Any:
 
 def safe_round(x: Any, ndigits: int | None = None) -> Any:
     x = get_item(x)
+    if ndigits is None:
+        return x
     try:
         return round(x, ndigits)
     except TypeError:

@@ -24,3 +24,6 @@ from .common import (  # noqa: F401
     log_min,
     log_summed,
 )
+from . import engine, metrics, source  # noqa: E402,F401
+from .sources import causal_lm as _s1, generation as _s2, model_info as _s3  # noqa: E402,F401
+from .engine import MetricEngine  # noqa: E402,F401

@@ -1,0 +1,105 @@
+"""Sharded state dicts of the FSDP engine, in the layout ``torch.distributed.checkpoint`` expects.
+
+Model entries are the fp32 master shards and optimizer entries the fp32 moment shards, each
+wrapped as a ``DTensor`` sharded on dim 0 over the shard group's mesh (plain tensors when the
+world is one). Row ranges follow ``torch.chunk`` (the first ranks hold ``ceil(rows / world)`` rows),
+which is also how FSDP2 shards, so checkpoints written here load under ``fully_shard`` in plain
+PyTorch and the other way round. Tensors are views: loading in place updates the engine.
+"""
+
+from __future__ import annotations
+
+from typing import Any
+
+import torch
+import torch.nn as nn
+
+
+def _wrap(local: torch.Tensor, full_shape: tuple, mesh: Any) -> Any:
+    if mesh is None:
+        return local
+    from torch.distributed.tensor import DTensor, Shard
+
+    stride = torch.empty(full_shape, device="meta").stride()
+    return DTensor.from_local(local, mesh, [Shard(0)], run_check=False, shape=torch.Size(full_shape), stride=stride)
+
+
+def engine_of(model: nn.Module) -> Any:
+    return getattr(model, "_sharding_engine", None)
+
+
+def model_state_dict(model: nn.Module, mesh: Any = None) -> dict[str, Any]:
+    """``{fqn: tensor}``; engine-managed parameters appear as (sharded) fp32 master weights."""
+    eng = engine_of(model)
+    if eng is None:
+        return dict(model.state_dict())
+    out: dict[str, Any] = {}
+    use_mesh = mesh if eng.world > 1 else None
+    for name, g, inf in eng.named_sharded_state():
+        out[name] = _wrap(g.local_shard(inf, g.master), inf.shape, use_mesh) if len(inf.shape) > 0 else g.local_shard(inf, g.master)
+    # tied parameters appear once in named_parameters; mirror the aliases the module's own
+    # state_dict would list (e.g. lm_head.weight == transformer.wte.weight)
+    by_id = {id(p): n for n, p in model.named_parameters()}
+    for n, p in model.named_parameters(remove_duplicate=False):
+        if n not in out and id(p) in by_id and by_id[id(p)] in out:
+            out[n] = out[by_id[id(p)]]
+    for n, b in model.named_buffers():
+        out[n] = b
+    return out
+
+
+def after_model_load(model: nn.Module) -> None:
+    """Call after the master shards were overwritten: refresh bf16 rows and force a re-gather."""
+    eng = engine_of(model)
+    if eng is None:
+        return
+    for g in eng.groups:
+        g.refresh_lp_from_master()
+        g.gathered = eng.world == 1
+    if eng.world > 1:
+        torch.cuda.synchronize(eng.device)
+        import torch.distributed as dist
+
+        dist.barrier(group=eng.pg)
+        eng.gather_all()
+        torch.cuda.synchronize(eng.device)
+        dist.barrier(group=eng.pg)
+
+
+def optimizer_state_dict(model: nn.Module, optimizer: Any, mesh: Any = None) -> dict[str, Any]:
+    """``{"state": {fqn: {step, exp_avg, exp_avg_sq}}, "param_groups": [...]}`` with sharded moments."""
+    eng = engine_of(model)
+    from .fsdp import ShardedAdamW
+
+    if eng is None or not isinstance(optimizer, ShardedAdamW):
+        return optimizer.state_dict()
+    use_mesh = mesh if eng.world > 1 else None
+    state: dict[str, Any] = {}
+    for name, g, inf in eng.named_sharded_state():
+        g.ensure_state()
+        state[name] = {
+            "step": torch.tensor(float(optimizer.step_count)),
+            "exp_avg": _wrap(g.local_shard(inf, g.exp_avg), inf.shape, use_mesh),
+            "exp_avg_sq": _wrap(g.local_shard(inf, g.exp_avg_sq), inf.shape, use_mesh),
+        }
+    names = {id(p): n for n, p in model.named_parameters()}
+    groups = []
+    for pg in optimizer.param_groups:
+        d = {k: v for k, v in pg.items() if k != "params"}
+        d["params"] = [names[id(p)] for p in pg["params"]]
+        groups.append(d)
+    return {"state": state, "param_groups": groups}
+
+
+def load_optimizer_state_dict(model: nn.Module, optimizer: Any, sd: dict[str, Any]) -> None:
+    eng = engine_of(model)
+    from .fsdp import ShardedAdamW
+
+    if eng is None or not isinstance(optimizer, ShardedAdamW):
+        optimizer.load_state_dict(sd)
+        return
+    steps = [float(v["step"]) for v in sd.get("state", {}).values() if "step" in v]
+    if steps:
+        optimizer.step_count = int(max(steps))
+    for pg, saved in zip(optimizer.param_groups, sd.get("param_groups", [])):
+        pg.update({k: v for k, v in saved.items() if k != "params"})

@@ -1,0 +1,129 @@
+"""Periodic evaluation (optimus_dl/recipe/train/mixins/managers/evaluation_manager.py:49-548).
+
+For every evaluation dataset (sorted by name, each with its own ``eval_freq`` / ``eval_iterations``):
+iterate its resettable loader under ``torch.no_grad`` and the AMP / FP8 forward context, log into
+the meter group ``eval/{name}``, agree across ranks on exhaustion with an ``all_reduce(MAX)`` of a
+flag (skipped when ``eval_guaranteed_same_batches``), optionally save per-rank mid-evaluation state
+every ``eval_checkpointing`` batches and resume from it, then aggregate meters over ranks.
+Returns ``{f"{prefix}/{name}": metrics}``."""
+
+from __future__ import annotations
+
+import contextlib
+import logging
+import time
+from dataclasses import dataclass
+from typing import Any
+
+import torch
+
+from .....core.profile import measured_next
+from .....core.registry import RegistryConfig, make_registry
+from .....metrics import MetricEngine
+from .....metrics.base import compute_meters, meters_group, step_meters
+from .....metrics.common import log_averaged, log_event_end, log_event_start
+
+logger = logging.getLogger(__name__)
+
+
+@dataclass
+class EvaluatorConfig(RegistryConfig):
+    amp: Any = None
+
+
+class Evaluator:
+    def __init__(self, cfg: Any = None, eval_freq: int = 0, eval_iterations: int | None = None,
+                 eval_guaranteed_same_batches: bool = False, eval_checkpointing: int | None = None,
+                 metrics_config: Any = None, eval_checkpoint_manager: Any = None, **kwargs: Any):
+        self.cfg = cfg
+        self.eval_freq, self.eval_iterations = eval_freq, eval_iterations
+        self.same_batches, self.eval_checkpointing = eval_guaranteed_same_batches, eval_checkpointing
+        self.metrics_config = metrics_config or {}
+        self.eval_ckpt = eval_checkpoint_manager
+
+    def should_evaluate(self, iteration: int, pipeline: Any = None) -> bool:
+        freq = (pipeline.eval_freq if pipeline is not None and pipeline.eval_freq is not None else self.eval_freq)
+        return bool(freq) and freq > 0 and iteration % freq == 0
+
+    def any_due(self, iteration: int, eval_data: dict[str, Any]) -> bool:
+        return any(self.should_evaluate(iteration, p) for p in eval_data.values())
+
+    def forward_context(self, training_context: dict[str, Any] | None):
+        if training_context is None:
+            return contextlib.nullcontext()
+        return training_context["amp_ctx"]()
+
+    @torch.no_grad()
+    def run_evaluation(self, model: torch.nn.Module, criterion: Any, eval_data: dict[str, Any], iteration: int,
+                       collective: Any = None, training_context: dict[str, Any] | None = None, prefix: str = "eval",
+                       force: bool = False) -> dict[str, dict[str, Any]]:
+        was_training = model.training
+        model.eval()
+        results: dict[str, dict[str, Any]] = {}
+        device = training_context["device"] if training_context else next(model.parameters()).device
+        try:
+            for name in sorted(eval_data):
+                pipe = eval_data[name]
+                if not force and not self.should_evaluate(iteration, pipe):
+                    continue
+                results[f"{prefix}/{name}"] = self._evaluate_one(model, criterion, name, pipe, iteration, collective,
+                                                                 training_context, device, prefix)
+        finally:
+            model.train(was_training)
+        return results
+
+    def _evaluate_one(self, model, criterion, name, pipe, iteration, collective, ctx, device, prefix) -> dict[str, Any]:
+        group = f"{prefix}/{name}"
+        cfgs = self.metrics_config.get(name) if hasattr(self.metrics_config, "get") else None
+        engine = MetricEngine(group, cfgs) if cfgs else None
+        max_iters = pipe.eval_iterations if pipe.eval_iterations is not None else self.eval_iterations
+        same = pipe.eval_guaranteed_same_batches if pipe.eval_guaranteed_same_batches is not None else self.same_batches
+        ckpt_every = pipe.eval_checkpointing if pipe.eval_checkpointing is not None else self.eval_checkpointing
+        world = collective.world_size if collective is not None else 1
+        with meters_group(group, log_freq=1, force_recreate=True):
+            t_start = time.perf_counter()
+            log_event_start("perf/total_run")
+            data_iter = iter(pipe.dataloader)
+            processed = 0
+            if self.eval_ckpt is not None and ckpt_every:
+                st = self.eval_ckpt.load_iteration_state(iteration, name, group)
+                if st is not None:
+                    processed = int(st.get("eval_iterations_processed", 0))
+                    if st.get("dataloader") is not None and hasattr(pipe.dataloader, "load_state_dict"):
+                        pipe.dataloader.load_state_dict(st["dataloader"])
+                        data_iter = iter(pipe.dataloader)
+                    logger.info("resuming evaluation %s at batch %d", name, processed)
+            requested = engine.required_external_protocols if engine is not None else None
+            while max_iters is None or processed < max_iters:
+                exhausted, batch = 0, None
+                try:
+                    _, batch = measured_next(data_iter)
+                except StopIteration:
+                    exhausted = 1
+                if world > 1 and not same:
+                    flag = torch.tensor([exhausted], dtype=torch.int32, device=device)
+                    collective.all_reduce(flag, op=torch.distributed.ReduceOp.MAX)
+                    exhausted = int(flag.item())
+                if exhausted:
+                    break
+                log_event_start("perf/full_iteration")
+                with self.forward_context(ctx):
+                    loss, exposed = criterion(model, batch, requested_protocols=requested)
+                if engine is not None:
+                    engine.update(dict(model=model, batch=batch), exposed)
+                log_event_end("perf/full_iteration")
+                step_meters(group)
+                processed += 1
+                if self.eval_ckpt is not None and ckpt_every and processed % int(ckpt_every) == 0:
+                    dl_state = pipe.dataloader.state_dict() if hasattr(pipe.dataloader, "state_dict") else None
+                    self.eval_ckpt.save_iteration_state(iteration, name, group, dl_state, processed)
+            log_event_end("perf/total_run")
+            total_ms = (time.perf_counter() - t_start) * 1e3
+            log_averaged("perf/total_run_ms", total_ms, round=1)
+            log_averaged("perf/ms_per_batch", total_ms / max(processed, 1), round=2)
+        raw = compute_meters(group, aggregate=True, collective=collective)
+        return engine.compute(raw) if engine is not None else raw
+
+
+_R, register_evaluator, build_evaluator = make_registry("evaluator")
+register_evaluator("base", EvaluatorConfig)(Evaluator)
