@@ -224,10 +224,9 @@ def compose(config_dir: str | list[str], config_name: str, overrides: list[str] 
             conf.update(cfg, o["key"], o["value"], force_add=True)
     hydra_cfg = cfg._data.pop("hydra", None)
     if apply_env and isinstance(hydra_cfg, conf.DictNode):
-        env = conf.select(hydra_cfg, "job.env_set", default=None)
-        if env:
-            for k, v in conf.to_container(env, resolve=True).items():
-                os.environ.setdefault(str(k), str(v))
+        env = (conf.to_container(hydra_cfg, resolve=False).get("job") or {}).get("env_set") or {}
+        for k, v in env.items():
+            os.environ.setdefault(str(k), str(v))
     return cfg
 
 

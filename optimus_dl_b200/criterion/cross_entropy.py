@@ -57,7 +57,9 @@ class CrossEntropyCriterion(BaseCriterion):
     # ------------------------------------------------------------------ batch preparation
     @staticmethod
     def prepare_batch(batch: dict[str, Any]) -> tuple[dict[str, Any], torch.Tensor]:
-        batch = dict(batch)
+        # batches straight from a batcher (no ``to_device`` transform) carry numpy arrays
+        batch = {k: (torch.from_numpy(v) if type(v).__module__ == "numpy" and hasattr(v, "dtype") and v.ndim > 0 else v)
+                 for k, v in batch.items()}
         if "labels" in batch:
             targets = batch.pop("labels")
             return batch, targets

@@ -72,7 +72,11 @@ def optimizer_state_dict(model: nn.Module, optimizer: Any, mesh: Any = None) -> 
     from .fsdp import ShardedAdamW
 
     if eng is None or not isinstance(optimizer, ShardedAdamW):
-        return optimizer.state_dict()
+        # FQN-keyed and with the (possibly still empty) per-parameter state materialised, so that a
+        # fresh optimizer can be filled in place by a checkpoint load
+        from torch.distributed.checkpoint.state_dict import get_optimizer_state_dict
+
+        return get_optimizer_state_dict(model, optimizer)
     use_mesh = mesh if eng.world > 1 else None
     state: dict[str, Any] = {}
     for name, g, inf in eng.named_sharded_state():
@@ -96,7 +100,9 @@ def load_optimizer_state_dict(model: nn.Module, optimizer: Any, sd: dict[str, An
     from .fsdp import ShardedAdamW
 
     if eng is None or not isinstance(optimizer, ShardedAdamW):
-        optimizer.load_state_dict(sd)
+        from torch.distributed.checkpoint.state_dict import set_optimizer_state_dict
+
+        set_optimizer_state_dict(model, optimizer, sd)
         return
     steps = [float(v["step"]) for v in sd.get("state", {}).values() if "step" in v]
     if steps:

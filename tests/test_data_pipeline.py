@@ -1,0 +1,189 @@
+"""Datasets, sampling strategies, batchers and exact resume of pipeline state."""
+
+import json
+
+import numpy as np
+import pytest
+import torch
+import torchdata.nodes as tn
+
+from optimus_dl_b200.data import build_data_pipeline
+from optimus_dl_b200.data.datasets import build_dataset
+from optimus_dl_b200.data.transforms import build_transform
+
+
+class _ListNode(tn.BaseNode):
+    def __init__(self, items):
+        super().__init__()
+        self.items, self.i = items, 0
+
+    def reset(self, initial_state=None):
+        super().reset(initial_state)
+        self.i = initial_state["i"] if initial_state else 0
+
+    def get_state(self):
+        return {"i": self.i}
+
+    def next(self):
+        if self.i >= len(self.items):
+            raise StopIteration
+        self.i += 1
+        return self.items[self.i - 1]
+
+
+def _docs(lens, kind=list):
+    out, c = [], 0
+    for n in lens:
+        seq = list(range(c, c + n))
+        c += n
+        out.append({"input_ids": seq if kind is list else (np.array(seq) if kind is np.ndarray else torch.tensor(seq))})
+    return out
+
+
+def test_flat_batcher_packs_shifts_and_tracks_documents():
+    node = build_transform({"_name": "flat_batcher", "batch_size": 2, "seq_len": 4, "mask_documents": True}).build(_ListNode(_docs([6, 1, 7])))
+    node.reset()
+    b = next(node)
+    assert b["input_ids"].tolist() == [[0, 1, 2, 3], [4, 7, 8, 9]] and b["labels"].tolist() == [[1, 2, 3, 4], [5, 8, 9, 10]]
+    assert b["position_ids"].tolist() == [[0, 1, 2, 3], [4, 0, 1, 2]] and b["document_ids"].tolist() == [[0, 0, 0, 0], [0, 1, 1, 1]]
+    flat = build_transform({"_name": "flat_batcher", "max_tokens": 8, "mask_documents": True, "flatten": True}).build(_ListNode(_docs([4, 6, 5])))
+    flat.reset()
+    f = next(flat)
+    assert f["input_ids"].shape == (1, 8) and f["cu_seqlens"].tolist() == [0, 3, 8] and f["max_seqlen"] == 5
+    with pytest.raises(ValueError):
+        build_transform({"_name": "flat_batcher", "max_tokens": 8, "flatten": True}).build(_ListNode([]))
+
+
+@pytest.mark.parametrize("kind", [list, np.ndarray, torch.Tensor])
+def test_basic_batcher_padding_token_budget_and_flatten(kind):
+    items = _docs([3, 5, 2, 9, 1], kind)
+    node = build_transform({"_name": "basic_batcher", "max_tokens": 8, "pad_token_id": -1}).build(_ListNode(items))
+    node.reset()
+    b1, b2, b3 = next(node), next(node), next(node)
+    assert np.asarray(b1["seq_lens"]).tolist() == [3, 5] and np.asarray(b1["input_ids"]).shape == (2, 5)
+    assert np.asarray(b1["input_ids"])[0].tolist() == [0, 1, 2, -1, -1] and np.asarray(b1["position_ids"])[0].tolist() == [0, 1, 2, 0, 0]
+    assert np.asarray(b2["seq_lens"]).tolist() == [2] and np.asarray(b3["seq_lens"]).tolist() == [9]      # oversized item alone
+    fl = build_transform({"_name": "basic_batcher", "batch_size": 2, "pad_token_id": 0, "flatten": True}).build(_ListNode(items))
+    fl.reset()
+    f = next(fl)
+    assert np.asarray(f["input_ids"]).tolist() == [[0, 1, 3, 4, 5, 6]] and np.asarray(f["labels"]).tolist() == [[1, 2, 4, 5, 6, 7]]
+    assert np.asarray(f["cu_seqlens"]).tolist() == [0, 2, 6] and f["max_seqlen"] == 4
+
+
+def test_chunk_shuffle_skip_and_resume_exactness():
+    cfg = {"source": {"_name": "synthetic_tokens", "vocab_size": 97, "mean_length": 40.0, "min_length": 2, "seed": 3},
+           "transform": {"_name": "compose", "transforms": [
+               {"_name": "chunk_tokens", "max_seq_len": 16}, {"_name": "shuffle", "buffer_size": 8},
+               {"_name": "skip_interleaved", "keep_every": 2}, {"_name": "flat_batcher", "batch_size": 2, "seq_len": 8}]}}
+    p = build_data_pipeline(cfg, rank=0, world_size=1, seed=11)
+    loader = tn.Loader(p.dataloader)
+    it = iter(loader)
+    first = [next(it)["input_ids"].copy() for _ in range(5)]
+    state = loader.state_dict()
+    after = [next(it)["input_ids"].copy() for _ in range(5)]
+    p2 = build_data_pipeline(cfg, rank=0, world_size=1, seed=11)
+    loader2 = tn.Loader(p2.dataloader)
+    loader2.load_state_dict(state)
+    again = [b["input_ids"].copy() for _, b in zip(range(5), iter(loader2))]
+    assert all(np.array_equal(a, b) for a, b in zip(after, again))
+    assert not all(np.array_equal(a, b) for a, b in zip(first, after))
+
+
+def _write_shards(tmp_path, lens_per_shard):
+    files, c = [], 0
+    for i, lens in enumerate(lens_per_shard):
+        toks = np.arange(c, c + sum(lens), dtype=np.uint16)
+        c += sum(lens)
+        np.save(tmp_path / f"s_{i:010d}.npy", toks)
+        np.save(tmp_path / f"s_{i:010d}_lens.npy", np.array(lens, dtype=np.int64))
+        files.append({"file": f"s_{i:010d}.npy", "lens_file": f"s_{i:010d}_lens.npy"})
+    (tmp_path / "index.json").write_text(json.dumps({"files": files}))
+    return c
+
+
+@pytest.mark.parametrize("strategy", [{"_name": "document"}, {"_name": "document", "shuffle": True},
+                                      {"_name": "concat_random", "chunk_size": 7, "random_offset": False}])
+def test_tokenized_dataset_totality_across_ranks(tmp_path, strategy):
+    total = _write_shards(tmp_path, [[5, 9, 3], [11, 2], [8]])
+    seen = []
+    for rank in range(3):
+        ds = build_dataset({"_name": "tokenized_dataset", "data_dir": str(tmp_path), "strategy": strategy}, rank=rank, world_size=3, seed=1)
+        ds.reset()
+        while True:
+            try:
+                seen.extend(next(ds)["input_ids"].tolist())
+            except StopIteration:
+                break
+    if strategy["_name"] == "document":
+        assert sorted(seen) == list(range(total))          # every token exactly once
+    else:
+        assert len(seen) == len(set(seen)) == (total // 7) * 7
+
+
+def test_tokenized_dataset_checkpoint_and_rank_guard(tmp_path):
+    _write_shards(tmp_path, [[4, 4, 4, 4, 4]])
+    cfg = {"_name": "tokenized_dataset", "data_dir": str(tmp_path)}
+    ds = build_dataset(cfg, rank=0, world_size=1, seed=0)
+    ds.reset()
+    next(ds), next(ds)
+    st = ds.state_dict()
+    nxt = next(ds)["input_ids"].tolist()
+    ds2 = build_dataset(cfg, rank=0, world_size=1, seed=0)
+    ds2.reset(st)
+    assert next(ds2)["input_ids"].tolist() == nxt
+    ds3 = build_dataset(cfg, rank=1, world_size=2, seed=0)
+    with pytest.raises(AssertionError):
+        ds3.reset(st)
+
+
+def test_composite_weights_stop_criteria_and_strict_load():
+    def cfg(stop, cycle=True):
+        return {"_name": "composite", "stop_criteria": stop, "datasets": {
+            "a": {"dataset": {"_name": "synthetic_tokens", "length": 4, "num_documents": 5}, "weight": 1.0, "cycle": cycle},
+            "b": {"dataset": {"_name": "synthetic_tokens", "length": 8, "num_documents": 400}, "weight": 3.0, "cycle": cycle}}}
+    ds = build_dataset(cfg("CYCLE_FOREVER"), rank=0, world_size=1, seed=4)
+    ds.reset()
+    lens = [len(next(ds)["input_ids"]) for _ in range(400)]
+    assert 0.15 < lens.count(4) / 400 < 0.35
+    ds = build_dataset(cfg("FIRST_DATASET_EXHAUSTED"), rank=0, world_size=1, seed=4)
+    ds.reset()
+    n = 0
+    with pytest.raises(StopIteration):
+        while True:
+            next(ds)
+            n += 1
+    assert n < 100
+    ds = build_dataset(cfg("ALL_DATASETS_EXHAUSTED", cycle=False), rank=0, world_size=1, seed=4)
+    ds.reset()
+    n = sum(1 for _ in iter(lambda: _next_or_none(ds), None))
+    assert n == 405
+    st = ds.state_dict()
+    st["datasets"].pop("a")
+    with pytest.raises(ValueError):
+        build_dataset(cfg("CYCLE_FOREVER"), rank=0, world_size=1, seed=4).reset(st)
+
+
+def _next_or_none(ds):
+    try:
+        return next(ds)
+    except StopIteration:
+        return None
+
+
+def test_txt_lines_and_tokenizers(tmp_path):
+    f = tmp_path / "t.txt"
+    f.write_text("alpha\n\nbeta\ngamma\ndelta\n")
+    got = []
+    for r in range(2):
+        ds = build_dataset({"_name": "txt_lines", "file_link": str(f)}, rank=r, world_size=2)
+        ds.reset()
+        got.append([x["text"] for x in iter(lambda: _next_or_none(ds), None)])
+    assert got == [["alpha", "beta"], ["gamma", "delta"]]
+    from optimus_dl_b200.tokenizer import build_tokenizer
+
+    ch = build_tokenizer({"_name": "char_tokenize"})
+    assert ch.decode(ch.encode("héy")) == "héy" and ch.encode("a")[0] == 256 and ch.vocab_size == 258
+    il = build_tokenizer({"_name": "inline_tokens_tokenizer", "tokens": ["A", "AB", "C"], "unk_strategy": "ignore", "add_eos": False})
+    assert il.encode("ABxC") == [il.bos_token_id, 1, 2]
+    with pytest.raises(ValueError):
+        build_tokenizer({"_name": "inline_tokens_tokenizer", "tokens": ["A"]}).encode("B")
