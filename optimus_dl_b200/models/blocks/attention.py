@@ -45,13 +45,21 @@ class BaseSelfAttention(nn.Module):
             self.q_norm = RMSNorm(qd, eps=rmsnorm_eps)
             self.k_norm = RMSNorm(kd, eps=rmsnorm_eps)
         self.resid_dropout = nn.Dropout(dropout) if dropout > 0 else None
-        # tensor-parallel state, set by parallel.tp: local head counts and the group
-        self.tp_group = None
+        # tensor-parallel state (parallel.tp.TPState), set by apply_tensor_parallel together with local head counts
+        self.tp = None
 
     def forward(self, x: torch.Tensor, freqs_cis: torch.Tensor | None = None, seq_lens: torch.Tensor | None = None,
                 document_ids: torch.Tensor | None = None, position_ids: torch.Tensor | None = None,
                 cu_seqlens: torch.Tensor | None = None, max_seqlen: int | None = None,
                 doc_start: torch.Tensor | None = None) -> torch.Tensor:
+        if self.tp is not None:
+            from ...parallel import tp as tp_ops
+
+            B, T = self.tp.full_shape
+            if doc_start is None:
+                doc_start = attn_ops.build_doc_start(B, T, x.device, document_ids, cu_seqlens)
+            return tp_ops.attention_forward(self, x, freqs_cis=freqs_cis, position_ids=position_ids,
+                                            doc_start=doc_start)
         B, T, _ = x.shape
         if cu_seqlens is not None:
             assert B == 1, f"cu_seqlens is only supported for flat batches (B=1), but got B={B}"

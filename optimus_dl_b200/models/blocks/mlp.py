@@ -29,8 +29,16 @@ class SwiGLUMLP(nn.Module):
         self.w2 = nn.Linear(n_embd, hidden, bias=bias)
         self.c_proj = nn.Linear(hidden, n_embd, bias=bias)
         self.dropout = nn.Dropout(dropout) if dropout > 0 else None
+        self.tp = None  # parallel.tp.TPState once the block is tensor-parallel
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """``mlp(x)``, or ``residual + mlp(x)`` when a residual is given."""
+        if self.tp is not None:
+            from ...parallel import tp as tp_ops
+
+            return tp_ops.swiglu_mlp_forward(self, x, residual)
+        if residual is not None:
+            return residual + self.forward(x)
         if self.w1.bias is None and self.c_proj.bias is None:
             y = act_ops.swiglu_mlp(x, self.w1.weight, self.w2.weight, self.c_proj.weight)
             return self.dropout(y) if self.dropout is not None else y
@@ -52,8 +60,15 @@ class ReLU2MLP(nn.Module):
         self.c_fc = nn.Linear(n_embd, hidden, bias=bias)
         self.c_proj = nn.Linear(hidden, n_embd, bias=bias)
         self.dropout = nn.Dropout(dropout) if dropout > 0 else None
+        self.tp = None
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        if self.tp is not None:
+            from ...parallel import tp as tp_ops
+
+            return tp_ops.dense_mlp_forward(self, x, lambda t: torch.relu(t).square(), residual)
+        if residual is not None:
+            return residual + self.forward(x)
         h = torch.relu(lin_ops.linear(x, self.c_fc.weight, self.c_fc.bias)).square()
         y = lin_ops.linear(h, self.c_proj.weight, self.c_proj.bias)
         return self.dropout(y) if self.dropout is not None else y
@@ -68,8 +83,15 @@ class GELUMLP(nn.Module):
         self.c_fc = nn.Linear(n_embd, hidden, bias=bias)
         self.c_proj = nn.Linear(hidden, n_embd, bias=bias)
         self.dropout = nn.Dropout(dropout) if dropout > 0 else None
+        self.tp = None
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        if self.tp is not None:
+            from ...parallel import tp as tp_ops
+
+            return tp_ops.dense_mlp_forward(self, x, torch.nn.functional.gelu, residual)
+        if residual is not None:
+            return residual + self.forward(x)
         h = torch.nn.functional.gelu(lin_ops.linear(x, self.c_fc.weight, self.c_fc.bias))
         y = lin_ops.linear(h, self.c_proj.weight, self.c_proj.bias)
         return self.dropout(y) if self.dropout is not None else y

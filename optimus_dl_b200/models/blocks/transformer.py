@@ -32,4 +32,4 @@ class RotaryTransformerBlock(nn.Module):
                       position_ids=position_ids, cu_seqlens=cu_seqlens, max_seqlen=max_seqlen, doc_start=doc_start)
         # second norm fuses the residual add: h = x + a, y = norm(h)
         y, h = self.ln_2(a, residual=x)
-        return h + self.mlp(y)
+        return self.mlp(y, residual=h)

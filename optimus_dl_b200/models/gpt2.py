@@ -92,9 +92,17 @@ class GPT(BaseModel):
 
     # ------------------------------------------------------------------ forward
     def embed(self, input_ids: torch.Tensor) -> torch.Tensor:
+        if getattr(self, "_tp", None) is not None:
+            from ..parallel import tp as tp_ops
+
+            return tp_ops.embed_forward(self, input_ids)
         return emb_ops.embedding(input_ids, self.transformer.wte.weight, self.config.padding_token_id)
 
     def head(self, x: torch.Tensor) -> torch.Tensor:
+        if getattr(self, "_tp", None) is not None:
+            from ..parallel import tp as tp_ops
+
+            return tp_ops.head_forward(self, x)
         return lin_ops.linear(x, self.lm_head.weight)
 
     def forward(self, input_ids: torch.Tensor, seq_lens=None, document_ids=None, position_ids=None, cu_seqlens=None,

@@ -91,6 +91,9 @@ class Llama(GPT):
                 max_seqlen=None, skip_lm_head: bool = False, **kwargs):
         B, T = input_ids.shape
         assert T <= self.config.sequence_length, f"sequence of length {T} exceeds {self.config.sequence_length}"
+        tp = getattr(self, "_tp", None)
+        if tp is not None:
+            tp.full_shape = (B, T)
         x = self.transformer.drop(self.embed(input_ids))
         doc_start = attn_ops.build_doc_start(B, T, x.device, document_ids, cu_seqlens)
         common = dict(freqs_cis=self.freqs_on(x.device), seq_lens=seq_lens, document_ids=document_ids,
@@ -99,13 +102,18 @@ class Llama(GPT):
             x = block(x, **self.block_kwargs(i, block, common))
         x = self.transformer.ln_f(x)
         if skip_lm_head:
+            if tp is not None:
+                from ..parallel import tp as tp_ops
+
+                x = tp_ops.hidden_forward(self, x)
             return {"hidden": x}
         return {"logits": self.head(x)}
 
-    def apply_tp(self, mesh, **kwargs):
+    def apply_tp(self, mesh, loss_parallel: bool = False, sequence_parallel: bool = False, **kwargs):
+        """Shard the model over the tensor-parallel mesh (same options as the reference's ``apply_tp``)."""
         from ..parallel.tp import apply_tensor_parallel
 
-        apply_tensor_parallel(self, mesh, **kwargs)
+        apply_tensor_parallel(self, mesh, loss_parallel=loss_parallel, sequence_parallel=sequence_parallel, **kwargs)
 
 
 @Llama.register_arch("7b")

@@ -184,3 +184,7 @@ def _declare(l: ctypes.CDLL) -> None:
     sig("ob_pull", [P, I, PP, I, P, P, I, I, P])
     sig("ob_rs_adamw", [I, P, I, PP, I, P, P, P, P, P, F, F, F, F, F, F, F, F, P, P, P, I, P])
     sig("ob_gemm_ag_bf16", [P, L, P, L, P, L, I, I, I, P, P, I, PP, I, P, P, I, I, I, I, I, P, P])
+    sig("ob_gemm_ag_act_bf16", [P, L, P, P, L, I, P, P, P, L, I, I, I, P, P, I, PP, I, P, P, I, I, I, I, P, P])
+    sig("ob_gemm_rs_bf16", [P, L, I, P, L, I, P, PP, I, I, I, L, I, I, I, I, P, P])
+    sig("ob_embedding_push", [P, I, P, I, I, I, PP, I, I, P])
+    sig("ob_rs_sum", [PP, I, I, I, P, I, I, L, P, L, P, L, I, P, P])

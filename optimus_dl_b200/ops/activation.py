@@ -37,6 +37,21 @@ class _SwiGLU(torch.autograd.Function):
         return dg, du
 
 
+def swiglu_backward(dh: torch.Tensor, g: torch.Tensor, u: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """``(dg, du)`` of ``h = silu(g) * u`` (no autograd; kernel on CUDA bf16)."""
+    if _ok(dh, g, u):
+        dg = torch.empty_like(g)
+        du = torch.empty_like(u)
+        _lib.check(_lib.lib().ob_swiglu_bwd(_lib.ptr(dh), _lib.ptr(g), _lib.ptr(u), _lib.ptr(dg), _lib.ptr(du), None,
+                                            g.numel(), _lib.stream()), "swiglu_bwd")
+        return dg, du
+    gf, uf, df = g.float(), u.float(), dh.float()
+    sig = torch.sigmoid(gf)
+    dg = df * uf * sig * (1.0 + gf * (1.0 - sig))
+    du = df * gf * sig
+    return dg.to(g.dtype), du.to(u.dtype)
+
+
 def swiglu(g: torch.Tensor, u: torch.Tensor) -> torch.Tensor:
     """``silu(g) * u`` with autograd."""
     if _ok(g, u):

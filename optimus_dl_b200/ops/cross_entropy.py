@@ -163,6 +163,43 @@ class _LinearCE(torch.autograd.Function):
         return gx, gw, None, None, None, None, None, None, None, None, None, None
 
 
+class _SumGradOverGroup(torch.autograd.Function):
+    """Identity forward; the gradient is summed over the group (replicated input of a sharded op)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x
+
+    @staticmethod
+    def backward(ctx, dy):
+        import torch.distributed as dist
+
+        dy = dy.contiguous().clone()
+        dist.all_reduce(dy, group=ctx.group)
+        return dy, None
+
+
+class _GatherVocab(torch.autograd.Function):
+    """All-gather of vocabulary shards along the last dimension; the gradient is sliced."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        import torch.distributed as dist
+
+        ctx.group, ctx.cols = group, x.shape[-1]
+        parts = [torch.empty_like(x) for _ in range(dist.get_world_size(group))]
+        dist.all_gather(parts, x.contiguous(), group=group)
+        return torch.cat(parts, dim=-1)
+
+    @staticmethod
+    def backward(ctx, dy):
+        import torch.distributed as dist
+
+        r = dist.get_rank(ctx.group)
+        return dy[..., r * ctx.cols:(r + 1) * ctx.cols].contiguous(), None
+
+
 def linear_cross_entropy(x: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor, *, ignore_index: int = -100,
                          label_smoothing: float = 0.0, softcap: float | None = None, softcap_type: str = "tanh",
                          chunk_rows: int = 4096, tp_group=None, vocab_offset: int = 0,
@@ -174,6 +211,9 @@ def linear_cross_entropy(x: torch.Tensor, weight: torch.Tensor, targets: torch.T
                                                              grad_scale)
         return CEResult(loss, n_valid, n_correct, loss_sum)
     if tp_group is not None:
-        raise NotImplementedError("vocabulary-parallel loss needs the CUDA bf16 path")
+        # eager fallback (CPU / fp32): local logits, gathered over the vocabulary with autograd-aware collectives
+        logits = _GatherVocab.apply(F.linear(_SumGradOverGroup.apply(x.reshape(-1, x.shape[-1]), tp_group), weight),
+                                    tp_group)
+        return cross_entropy_ref(logits, targets.reshape(-1), ignore_index, label_smoothing, softcap, softcap_type)
     logits = F.linear(x.reshape(-1, x.shape[-1]), weight)
     return cross_entropy_ref(logits, targets.reshape(-1), ignore_index, label_smoothing, softcap, softcap_type)

@@ -168,6 +168,88 @@ __global__ void sum_partials_kernel(const float* __restrict__ partials, int n, f
 using namespace ob;
 using namespace ob::comm;
 
+// Receive half of a reduce-scatter whose send half ran in a GEMM epilogue (ob_gemm_rs_bf16):
+// cross-GPU barrier, then out[r][c] = residual[r][c] + sum_s staging[s][r][c] (fp32, fixed slot
+// order, one rounding to bf16).  The barrier is part of the kernel: block 0 publishes this rank's
+// arrival, every block waits (bounded) until all ranks have arrived before it touches `staging`.
+__global__ void __launch_bounds__(256)
+rs_sum_kernel(PeerPtrs flag_peers, int me, int world, int epoch, const __nv_bfloat16* __restrict__ staging, int rows,
+              int D, long long ld, const __nv_bfloat16* __restrict__ residual, long long res_ld,
+              __nv_bfloat16* __restrict__ out, long long out_ld, int* status) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (flag_peers.p[me] != nullptr && world > 1) {
+    if (blockIdx.x == 0 && (int)threadIdx.x < world) {
+      __threadfence_system();
+      int* remote = reinterpret_cast<int*>(flag_peers.p[threadIdx.x]) + me;
+      asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+    }
+    if ((int)threadIdx.x < world) {
+      const int* mine = reinterpret_cast<const int*>(flag_peers.p[me]) + threadIdx.x;
+      bool ok = false;
+      for (uint32_t it = 0; it < (1u << 24); ++it) {
+        int v;
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+        if (v >= epoch) { ok = true; break; }
+        __nanosleep(100);
+      }
+      if (!ok) {
+        s_ok = 0;
+        if (status) atomicCAS(status, kStatusOk, kStatusFlagTimeout);
+      }
+    }
+    __syncthreads();
+    if (!s_ok) return;
+  }
+  const int vec_per_row = D / 8;
+  const long long total = (long long)rows * vec_per_row;
+  const long long slot = (long long)rows * ld;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / vec_per_row);
+    const int c = (int)(i - (long long)r * vec_per_row) * 8;
+    float acc[8];
+    if (residual) {
+      const uint4 u = *reinterpret_cast<const uint4*>(residual + (long long)r * res_ld + c);
+      const float2 a0 = unpack_bf16x2(u.x), a1 = unpack_bf16x2(u.y), a2 = unpack_bf16x2(u.z), a3 = unpack_bf16x2(u.w);
+      acc[0] = a0.x; acc[1] = a0.y; acc[2] = a1.x; acc[3] = a1.y; acc[4] = a2.x; acc[5] = a2.y; acc[6] = a3.x; acc[7] = a3.y;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    }
+    for (int s = 0; s < world; ++s) {
+      const uint4 u = ld_peer_16(staging + s * slot + (long long)r * ld + c);
+      const float2 a0 = unpack_bf16x2(u.x), a1 = unpack_bf16x2(u.y), a2 = unpack_bf16x2(u.z), a3 = unpack_bf16x2(u.w);
+      acc[0] += a0.x; acc[1] += a0.y; acc[2] += a1.x; acc[3] += a1.y; acc[4] += a2.x; acc[5] += a2.y; acc[6] += a3.x; acc[7] += a3.y;
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + (long long)r * out_ld + c) = o;
+  }
+}
+
+// Vocabulary-parallel embedding without partial sums: this rank owns table rows
+// [voff, voff + v_local); for every token whose id falls in that range it stores the row into
+// the activation buffer of the rank that holds the token (token t lives on rank t / rows_per_rank).
+// One warp per token; ids outside the range are another rank's job.
+__global__ void __launch_bounds__(256)
+embedding_push_kernel(const long long* __restrict__ ids, int T, const __nv_bfloat16* __restrict__ table, int v_local,
+                      int voff, int D, PeerPtrs dst, int rows_per_rank) {
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < T; t += warps) {
+    const long long id = ids[t] - voff;
+    if (id < 0 || id >= v_local) continue;
+    const int owner = t / rows_per_rank;
+    const uint4* src = reinterpret_cast<const uint4*>(table + id * D);
+    uint4* out = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dst.p[owner]) +
+                                          (long long)(t - owner * rows_per_rank) * D);
+    for (int i = lane; i < D / 8; i += 32) out[i] = src[i];
+  }
+}
+
 static PeerPtrs make_peers(const void* const* ptrs, int world) {
   PeerPtrs p{};
   for (int i = 0; i < world && i < MAX_RANKS; ++i) p.p[i] = const_cast<void*>(ptrs[i]);
@@ -217,5 +299,33 @@ extern "C" int ob_rs_adamw(int mode, const void* segs, int n_segs, const void* c
     rs_adamw_kernel<kUpdateOnly><<<n_ctas, 256, 0, stream>>>((const Segment*)segs, n_segs, g, world, (float*)master,
                                                              (float*)m, (float*)v, (float*)grad_shard,
                                                              (__nv_bfloat16*)param_out, a, nullptr);
+  return (int)cudaGetLastError();
+}
+
+// staging: this rank's buffer [world][rows][ld] (bf16) that the peers' GEMM epilogues filled.
+// flag_ptrs may be null (or world == 1) to skip the built-in barrier.
+extern "C" int ob_rs_sum(const void* const* flag_ptrs, int me, int world, int epoch, const void* staging, int rows,
+                         int D, long long ld, const void* residual, long long res_ld, void* out, long long out_ld,
+                         int n_ctas, int* status, cudaStream_t stream) {
+  if (world > MAX_RANKS || D % 8 != 0 || ld % 8 != 0 || out_ld % 8 != 0 || (residual && res_ld % 8 != 0)) return -1;
+  if (rows <= 0) return 0;
+  PeerPtrs fp{};
+  if (flag_ptrs) fp = make_peers(flag_ptrs, world);
+  if (n_ctas <= 0) n_ctas = 296;
+  rs_sum_kernel<<<n_ctas, 256, 0, stream>>>(fp, me, world, epoch, (const __nv_bfloat16*)staging, rows, D, ld,
+                                            (const __nv_bfloat16*)residual, res_ld, (__nv_bfloat16*)out, out_ld,
+                                            status);
+  return (int)cudaGetLastError();
+}
+
+// ids: int64 [T] (the same on every rank); table: this rank's [v_local, D] bf16 rows.
+extern "C" int ob_embedding_push(const void* ids, int T, const void* table, int v_local, int voff, int D,
+                                 const void* const* dst_ptrs, int world, int rows_per_rank, cudaStream_t stream) {
+  if (world > MAX_RANKS || D % 8 != 0 || rows_per_rank <= 0) return -1;
+  if (T <= 0) return 0;
+  int blocks = (T + 7) / 8;
+  if (blocks > 1184) blocks = 1184;
+  embedding_push_kernel<<<blocks, 256, 0, stream>>>((const long long*)ids, T, (const __nv_bfloat16*)table, v_local, voff,
+                                                    D, make_peers(dst_ptrs, world), rows_per_rank);
   return (int)cudaGetLastError();
 }

@@ -43,7 +43,7 @@ __device__ __forceinline__ void run_copy_tasks(const CopyTask* tasks, int n_task
     const __nv_bfloat16* s = reinterpret_cast<const __nv_bfloat16*>(src.p[task.peer]) + task.offset;
     __nv_bfloat16* d = dst + task.offset;
     const int nvec = (task.offset % 8 == 0) ? task.numel / 8 : 0;
-    constexpr int UNROLL = 4;
+    constexpr int UNROLL = 8;
     int i = threadIdx.x;
     for (; i + (UNROLL - 1) * (int)blockDim.x < nvec; i += UNROLL * blockDim.x) {
       uint4 v[UNROLL];

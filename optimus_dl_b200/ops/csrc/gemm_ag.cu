@@ -18,10 +18,12 @@
 namespace ob {
 namespace gemm {
 
-constexpr int AG_THREADS = 1024;  // copy CTAs use all of them; GEMM CTAs only the first 192
+constexpr int AG_THREADS = 512;  // copy CTAs use all of them; GEMM CTAs only the first 192 (512 keeps 128 registers per thread for the epilogue)
 
+template <int B_MN, int SWIGLU>
 __global__ void __launch_bounds__(AG_THREADS, 1)
-ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p,
+ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmB2, const Params p,
                const comm::CopyTask* __restrict__ tasks, int n_tasks, comm::PeerPtrs src, __nv_bfloat16* dst,
                int* flags, int epoch, int n_copy) {
   extern __shared__ uint8_t smem_raw[];
@@ -30,7 +32,33 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     return;
   }
   if (threadIdx.x >= NUM_THREADS) return;  // spare warps of a GEMM CTA
-  gemm_cta<0, 0, 0>(&tmA, &tmB, &tmB, p, blockIdx.x - n_copy, gridDim.x - n_copy, smem_raw);
+  gemm_cta<0, B_MN, SWIGLU>(&tmA, &tmB, &tmB2, p, blockIdx.x - n_copy, gridDim.x - n_copy, smem_raw);
+}
+
+template <int B_MN, int SWIGLU>
+static int launch_ag(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const Params& p,
+                     const void* tasks, int n_tasks, const void* const* src_ptrs, int world, void* dst, int* flags,
+                     int epoch, int n_copy, cudaStream_t stream) {
+  auto kern = ag_gemm_kernel<B_MN, SWIGLU>;
+  static bool configured = false;
+  if (!configured) {
+    OB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    configured = true;
+  }
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (n_tasks == 0) n_copy = 0;
+  if (n_copy > sms / 2) n_copy = sms / 2;
+  const int bn = SWIGLU ? BN / 2 : BN;
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + bn - 1) / bn);
+  int gemm_ctas = sms - n_copy;
+  if (gemm_ctas > tiles) gemm_ctas = tiles;
+  comm::PeerPtrs src{};
+  for (int i = 0; i < world; ++i) src.p[i] = const_cast<void*>(src_ptrs[i]);
+  kern<<<n_copy + gemm_ctas, AG_THREADS, SMEM_BYTES, stream>>>(ta, tb, tb2, p, (const comm::CopyTask*)tasks, n_tasks,
+                                                               src, (__nv_bfloat16*)dst, flags, epoch, n_copy);
+  return (int)cudaGetLastError();
 }
 
 }  // namespace gemm
@@ -61,22 +89,44 @@ extern "C" int ob_gemm_ag_bf16(const void* A, long long lda, const void* B, long
   if (gather_a) { p.a_flags = flags; p.a_flag_rows = flag_rows; p.a_flag_value = epoch; p.tile_order = 2; }
   else { p.b_flags = flags; p.flag_rows = flag_rows; p.flag_value = epoch; p.tile_order = 1; }
   p.first_tile_shift = first_tile_shift;
-  static bool configured = false;
-  if (!configured) {
-    OB_CUDA_CHECK(cudaFuncSetAttribute(ag_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    configured = true;
+  return launch_ag<0, 0>(ta, tb, tb, p, tasks, n_tasks, src_ptrs, world, dst, flags, epoch, n_copy, stream);
+}
+
+// Sequence-parallel forms: the activation A[M,K] is the gathered operand (flags per `flag_rows`
+// rows of A, m-major tile order rotated by first_tile_shift m-tiles).
+//   b_mn = 0: B is [N,K] row-major (column-parallel forward);  b_mn = 1: B is [K,N] row-major
+//   (row-parallel backward, dx = dy_full W).
+//   B2 != nullptr: dual-B SwiGLU, H = silu(A B^T) * (A B2^T) with optional G / U outputs (b_mn = 0 only).
+extern "C" int ob_gemm_ag_act_bf16(const void* A, long long lda, const void* B, const void* B2, long long ldb, int b_mn,
+                                   void* C, void* G, void* U, long long ldc, int M, int N, int K, const void* bias,
+                                   const void* tasks, int n_tasks, const void* const* src_ptrs, int world, void* dst,
+                                   int* flags, int flag_rows, int epoch, int first_tile_shift, int n_copy,
+                                   int* status, cudaStream_t stream) {
+  if (world > comm::MAX_RANKS) return -1;
+  if (B2 != nullptr && b_mn) return -2;
+  CUtensorMap ta, tb, tb2;
+  int rc = make_tmap_2d(&ta, A, M, K, lda, BM, BK, 2);
+  if (rc) return rc;
+  if (B2 != nullptr) {
+    rc = make_tmap_2d(&tb, B, N, K, ldb, BN / 2, BK, 2);
+    if (rc) return rc;
+    rc = make_tmap_2d(&tb2, B2, N, K, ldb, BN / 2, BK, 2);
+  } else if (b_mn) {
+    rc = make_tmap_2d(&tb, B, K, N, ldb, BK, 64, 2);
+    tb2 = tb;
+  } else {
+    rc = make_tmap_2d(&tb, B, N, K, ldb, BN, BK, 2);
+    tb2 = tb;
   }
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (n_tasks == 0) n_copy = 0;
-  if (n_copy > sms / 2) n_copy = sms / 2;
-  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  int gemm_ctas = sms - n_copy;
-  if (gemm_ctas > tiles) gemm_ctas = tiles;
-  comm::PeerPtrs src{};
-  for (int i = 0; i < world; ++i) src.p[i] = const_cast<void*>(src_ptrs[i]);
-  ag_gemm_kernel<<<n_copy + gemm_ctas, AG_THREADS, SMEM_BYTES, stream>>>(
-      ta, tb, p, (const comm::CopyTask*)tasks, n_tasks, src, (__nv_bfloat16*)dst, flags, epoch, n_copy);
-  return (int)cudaGetLastError();
+  if (rc) return rc;
+  Params p{};
+  p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.alpha = 1.0f; p.bias = bias; p.status = status;
+  p.G = G; p.U = U;
+  p.flag_rows = 1;
+  p.a_flags = flags; p.a_flag_rows = flag_rows > 0 ? flag_rows : 1; p.a_flag_value = epoch; p.tile_order = 2;
+  p.first_tile_shift = first_tile_shift;
+  if (B2 != nullptr)
+    return launch_ag<0, 1>(ta, tb, tb2, p, tasks, n_tasks, src_ptrs, world, dst, flags, epoch, n_copy, stream);
+  if (b_mn) return launch_ag<1, 0>(ta, tb, tb2, p, tasks, n_tasks, src_ptrs, world, dst, flags, epoch, n_copy, stream);
+  return launch_ag<0, 0>(ta, tb, tb2, p, tasks, n_tasks, src_ptrs, world, dst, flags, epoch, n_copy, stream);
 }

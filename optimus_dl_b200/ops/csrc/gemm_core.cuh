@@ -62,6 +62,14 @@ struct Params {
   int* status;           // error word (see StatusCode)
   int tile_order;        // 0: grouped-M raster, 1: flag-friendly order starting at first_n_tile
   int first_tile_shift;  // rotates the n-tile (or m-tile) order so locally owned chunks go first
+  // Reduce-scatter push (bf16 output only): when rs_rows > 0 the output row `r` belongs to rank
+  // r / rs_rows and is stored, straight from the epilogue, into that rank's staging buffer
+  // rs_dst[owner] at slot `rs_me` (layout [world][rs_rows][ldc]) over NVLink peer stores.  The
+  // owner adds the `world` slots afterwards (ob_rs_sum).  With `accumulate`, the local C[M,ldc]
+  // is added to the product before it is sent.
+  void* rs_dst[16];
+  int rs_rows;
+  int rs_me;
 };
 
 struct TileCoord {
@@ -344,11 +352,18 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap* tmA, const CUtensorM
               }
             } else {
               __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col;
+              // with `accumulate` the addend is always read from the local C, also in reduce-scatter mode
+              const __nv_bfloat16* srow = crow;
+              if (p.rs_rows > 0) {
+                const int owner = row / p.rs_rows;
+                crow = reinterpret_cast<__nv_bfloat16*>(p.rs_dst[owner]) +
+                       ((long long)p.rs_me * p.rs_rows + (row - owner * p.rs_rows)) * p.ldc + col;
+              }
               if (vec_ok && col + 32 <= p.N) {
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                   if (p.accumulate) {
-                    uint4 old = *reinterpret_cast<uint4*>(crow + 8 * q);
+                    uint4 old = *reinterpret_cast<const uint4*>(srow + 8 * q);
                     float2 a0 = unpack_bf16x2(old.x), a1 = unpack_bf16x2(old.y), a2 = unpack_bf16x2(old.z),
                            a3 = unpack_bf16x2(old.w);
                     v[8 * q] += a0.x; v[8 * q + 1] += a0.y; v[8 * q + 2] += a1.x; v[8 * q + 3] += a1.y;
@@ -361,7 +376,7 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap* tmA, const CUtensorM
               } else {
                 for (int j = 0; j < 32; ++j)
                   if (col + j < p.N)
-                    crow[j] = __float2bfloat16(p.accumulate ? __bfloat162float(crow[j]) + v[j] : v[j]);
+                    crow[j] = __float2bfloat16(p.accumulate ? __bfloat162float(srow[j]) + v[j] : v[j]);
               }
             }
           }

@@ -97,3 +97,37 @@ extern "C" int ob_gemm_swiglu_bf16(const void* X, long long ldx, const void* W1,
   p.flag_rows = 1; p.a_flag_rows = 1;
   return launch<0, 0, 1>(ta, tb1, tb2, p, sm_count(), stream);
 }
+
+// GEMM whose epilogue is the send half of a reduce-scatter.  Each rank computes its partial
+// product P = A * B^T for all M rows; row r belongs to rank r / rows_per_rank and is stored from
+// the accumulator straight into that rank's staging buffer dst_ptrs[owner] at
+// [me][r % rows_per_rank][0..N) (staging layout [world][rows_per_rank][ldc], bf16).  Tiles run
+// m-major starting at `first_tile_shift` m-tiles so that ranks send to different owners at the
+// same time and their own rows come last.  After a barrier the owner sums its `world` slots
+// (ob_rs_sum).  `addend` (optional, local bf16 [M, ldc]) is added to the product before sending.
+extern "C" int ob_gemm_rs_bf16(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn,
+                               const void* addend, const void* const* dst_ptrs, int world, int me, int rows_per_rank,
+                               long long ldc, int M, int N, int K, int first_tile_shift, int* status,
+                               cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (world > 16 || rows_per_rank <= 0 || (long long)rows_per_rank * world < M) return -1;
+  CUtensorMap ta, tb;
+  int rc;
+  if (a_mn) rc = make_tmap_2d(&ta, A, K, M, lda, BK, 64, 2);
+  else      rc = make_tmap_2d(&ta, A, M, K, lda, BM, BK, 2);
+  if (rc) return rc;
+  if (b_mn) rc = make_tmap_2d(&tb, B, K, N, ldb, BK, 64, 2);
+  else      rc = make_tmap_2d(&tb, B, N, K, ldb, BN, BK, 2);
+  if (rc) return rc;
+  Params p{};
+  p.M = M; p.N = N; p.K = K; p.C = const_cast<void*>(addend); p.accumulate = addend != nullptr; p.ldc = ldc;
+  p.alpha = 1.0f; p.status = status;
+  p.flag_rows = 1; p.a_flag_rows = 1; p.tile_order = 2; p.first_tile_shift = first_tile_shift;
+  for (int i = 0; i < world; ++i) p.rs_dst[i] = const_cast<void*>(dst_ptrs[i]);
+  p.rs_rows = rows_per_rank; p.rs_me = me;
+  const int sms = sm_count();
+  if (!a_mn && !b_mn) return launch<0, 0, 0>(ta, tb, tb, p, sms, stream);
+  if (!a_mn && b_mn) return launch<0, 1, 0>(ta, tb, tb, p, sms, stream);
+  if (a_mn && !b_mn) return launch<1, 0, 0>(ta, tb, tb, p, sms, stream);
+  return launch<1, 1, 0>(ta, tb, tb, p, sms, stream);
+}

@@ -41,7 +41,7 @@ def gemm(
     a_mn: bool = False,
     b_mn: bool = False,
     out: torch.Tensor | None = None,
-    out_dtype: torch.dtype = torch.bfloat16,
+    out_dtype: torch.dtype | None = None,
     accumulate: bool = False,
     bias: torch.Tensor | None = None,
     act: str = "none",
@@ -70,6 +70,8 @@ def gemm(
     if out is None:
         if accumulate:
             raise ValueError("accumulate needs an output tensor")
+        if out_dtype is None:  # bf16 on the kernel path; the operand dtype for the eager fallback
+            out_dtype = torch.bfloat16 if _use_kernel(a, b) else a.dtype
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
     if out.shape != (M, N) or out.stride(1) != 1:
         raise ValueError("bad output shape")

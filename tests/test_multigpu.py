@@ -26,3 +26,11 @@ def test_fsdp_matches_single_process(unique_port, clip):
     n = min(torch.cuda.device_count(), 4)
     out = _run("_mp_fsdp_check.py", n, unique_port, clip)
     assert "MP_FSDP_OK" in out, out[-4000:]
+
+
+@pytest.mark.parametrize("kind,sp", [("llama", "1"), ("llama", "0"), ("qwen3", "1"), ("olmo3", "1")])
+def test_tensor_parallel_matches_unsharded(unique_port, kind, sp):
+    """Fused all-gather GEMM / GEMM reduce-scatter / embedding push against the unsharded model."""
+    n = 2
+    out = _run("_mp_tp_check.py", n, unique_port, "nccl", kind, sp, str(unique_port))
+    assert "TP_OK" in out, out[-4000:]
