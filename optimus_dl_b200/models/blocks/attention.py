@@ -47,11 +47,15 @@ class BaseSelfAttention(nn.Module):
         self.resid_dropout = nn.Dropout(dropout) if dropout > 0 else None
         # tensor-parallel state (parallel.tp.TPState), set by apply_tensor_parallel together with local head counts
         self.tp = None
+        # decoding state (recipe.generation.LayerKV) while a generation session is active
+        self.kv = None
 
     def forward(self, x: torch.Tensor, freqs_cis: torch.Tensor | None = None, seq_lens: torch.Tensor | None = None,
                 document_ids: torch.Tensor | None = None, position_ids: torch.Tensor | None = None,
                 cu_seqlens: torch.Tensor | None = None, max_seqlen: int | None = None,
                 doc_start: torch.Tensor | None = None) -> torch.Tensor:
+        if self.kv is not None:
+            return self._forward_cached(x, freqs_cis, position_ids)
         if self.tp is not None:
             from ...parallel import tp as tp_ops
 
@@ -82,6 +86,50 @@ class BaseSelfAttention(nn.Module):
                                    k_norm_weight=kw, norm_eps=self.rmsnorm_eps, window=self.sliding_window)
         y = lin_ops.linear(y, self.wo.weight, self.wo.bias)
         return self.resid_dropout(y) if self.resid_dropout is not None else y
+
+
+    @torch.no_grad()
+    def _forward_cached(self, x: torch.Tensor, freqs_cis: torch.Tensor | None, position_ids: torch.Tensor | None):
+        """Inference with a key/value cache: a multi-token call is a prefill that fills the cache, a
+        one-token call attends over the cache with the decode kernel (which also appends)."""
+        from ...ops import decode as dec_ops
+
+        kv = self.kv
+        B, T, _ = x.shape
+        Hq, Hk, hd = self.n_head, self.n_kv_head, self.head_dim
+        qkv = lin_ops.multi_linear(x, [self.wq.weight, self.wk.weight, self.wv.weight],
+                                   [self.wq.bias, self.wk.bias, self.wv.bias])
+        qw = kw = None
+        if self.use_qk_norm:
+            if self.qk_norm_per_head:
+                qw, kw = self.q_norm.weight, self.k_norm.weight
+            else:
+                q, k, v = qkv.split([Hq * hd, Hk * hd, Hk * hd], dim=-1)
+                qkv = torch.cat([self.q_norm(q.contiguous()), self.k_norm(k.contiguous()), v], dim=-1)
+        if position_ids is None:
+            position_ids = (kv.seq_lens.to(torch.long)[:, None] - T
+                            + torch.arange(T, device=x.device)[None, :]) if kv.filled else None
+        work = attn_ops.rotate_qkv(qkv.contiguous(), n_head=Hq, n_kv_head=Hk, head_dim=hd,
+                                   freqs_cis=freqs_cis if self.use_rope else None,
+                                   position_ids=position_ids if self.use_rope else None, q_norm_weight=qw,
+                                   k_norm_weight=kw, norm_eps=self.rmsnorm_eps)
+        k_new = work[..., Hq * hd:(Hq + Hk) * hd].reshape(B, T, Hk, hd)
+        v_new = work[..., (Hq + Hk) * hd:].reshape(B, T, Hk, hd)
+        if T > 1 or not kv.filled:
+            assert not kv.filled, "multi-token calls are only supported as the prefill of an empty cache"
+            kv.k[:, :T].copy_(k_new)
+            kv.v[:, :T].copy_(v_new)
+            doc_start = attn_ops.build_doc_start(B, T, x.device, None, None)
+            y = attn_ops.attention_rotated(work, n_head=Hq, n_kv_head=Hk, head_dim=hd, doc_start=doc_start,
+                                           window=self.sliding_window)
+        else:
+            w2 = work.view(B, -1)
+            q = w2[:, : Hq * hd].unflatten(1, (Hq, hd))
+            kn = w2[:, Hq * hd:(Hq + Hk) * hd].unflatten(1, (Hk, hd))
+            vn = w2[:, (Hq + Hk) * hd:].unflatten(1, (Hk, hd))
+            y = dec_ops.decode_attention(q, kn, vn, kv.k, kv.v, kv.seq_lens, window=self.sliding_window,
+                                         n_splits=kv.n_splits, workspace=kv.workspace).view(B, 1, Hq * hd)
+        return lin_ops.linear(y, self.wo.weight, self.wo.bias)
 
 
 class CausalSelfAttention(BaseSelfAttention):

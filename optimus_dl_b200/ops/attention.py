@@ -214,3 +214,65 @@ def attention_sdpa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, doc_start:
         vh = vh.repeat_interleave(Hq // Hk, dim=1)
     o = F.scaled_dot_product_attention(qh, kh, vh, attn_mask=mask, scale=scale)
     return o.squeeze(0).transpose(0, 1)
+
+
+# ---------------------------------------------------------------------- inference helpers (no autograd)
+@torch.no_grad()
+def rotate_qkv(qkv: torch.Tensor, *, n_head: int, n_kv_head: int, head_dim: int,
+               freqs_cis: torch.Tensor | None = None, position_ids: torch.Tensor | None = None,
+               q_norm_weight: torch.Tensor | None = None, k_norm_weight: torch.Tensor | None = None,
+               norm_eps: float = 1e-6, seq_len: int | None = None) -> torch.Tensor:
+    """Per-head QK-norm and RoPE on a fused projection ``[B, T, (Hq + 2 Hk) * hd]``; returns the same layout."""
+    B, T, W = qkv.shape
+    Hq, Hk, hd = n_head, n_kv_head, head_dim
+    has_norm = q_norm_weight is not None
+    if freqs_cis is None and not has_norm:
+        return qkv
+    if _kernel_ok(qkv, hd):
+        flat = qkv.reshape(B * T, W)
+        pos = position_ids.reshape(-1).to(torch.int32).contiguous() if position_ids is not None else None
+        fr = (freqs_cis.to(device=qkv.device, dtype=torch.float32).contiguous() if freqs_cis is not None
+              else _identity_freqs(seq_len or T, hd, qkv.device))
+        work = flat
+        if has_norm:
+            work = torch.empty_like(flat)
+            work[:, (Hq + Hk) * hd:].copy_(flat[:, (Hq + Hk) * hd:])
+        qw = q_norm_weight.to(torch.bfloat16).contiguous() if has_norm else None
+        kw = k_norm_weight.to(torch.bfloat16).contiguous() if has_norm else None
+        rstd = torch.empty((B * T, Hq + Hk), dtype=torch.float32, device=qkv.device) if has_norm else None
+        rope_ops.rope_kernel_fwd(flat, work, flat.stride(0), work.stride(0), fr, pos, qw, kw, rstd, B * T, Hq, Hk, hd,
+                                 seq_len or T, norm_eps)
+        return work.view(B, T, W)
+    q, k, v = qkv.split([Hq * hd, Hk * hd, Hk * hd], dim=-1)
+    q = q.reshape(B, T, Hq, hd)
+    k = k.reshape(B, T, Hk, hd)
+    if has_norm:
+        q = rms_norm_ref(q, q_norm_weight, norm_eps)
+        k = rms_norm_ref(k, k_norm_weight, norm_eps)
+    if freqs_cis is not None:
+        q, k = rope_ops.apply_rotary_emb(q, k, freqs_cis, position_ids)
+    return torch.cat([q.reshape(B, T, -1).to(qkv.dtype), k.reshape(B, T, -1).to(qkv.dtype), v], dim=-1)
+
+
+@torch.no_grad()
+def attention_rotated(work: torch.Tensor, *, n_head: int, n_kv_head: int, head_dim: int, doc_start: torch.Tensor,
+                      window: int | None = None, scale: float | None = None) -> torch.Tensor:
+    """Masked attention on an already normalised / rotated fused projection (prefill path)."""
+    B, T, W = work.shape
+    Hq, Hk, hd = n_head, n_kv_head, head_dim
+    scale = scale if scale is not None else 1.0 / math.sqrt(hd)
+    if _kernel_ok(work, hd):
+        flat = work.reshape(B * T, W)
+        N = B * T
+        out = torch.empty((N, Hq * hd), dtype=torch.bfloat16, device=work.device)
+        lse = torch.empty((Hq, N), dtype=torch.float32, device=work.device)
+        rc = _lib.lib().ob_attn_fwd(_lib.ptr(flat), _lib.ptr(flat[:, Hq * hd:]), _lib.ptr(flat[:, (Hq + Hk) * hd:]),
+                                    _lib.ptr(out), _lib.ptr(lse), _lib.ptr(doc_start), N, Hq, Hk, hd, flat.stride(0),
+                                    flat.stride(0), out.stride(0), float(scale), int(window or 0),
+                                    _lib.ptr(_lib.status_word(work.device)), _lib.stream())
+        _lib.check(rc, "ob_attn_fwd")
+        return out.view(B, T, Hq * hd)
+    q, k, v = work.split([Hq * hd, Hk * hd, Hk * hd], dim=-1)
+    out = attention_sdpa(q.reshape(B * T, Hq, hd), k.reshape(B * T, Hk, hd), v.reshape(B * T, Hk, hd), doc_start, window,
+                         scale)
+    return out.reshape(B, T, Hq * hd)
