@@ -175,7 +175,7 @@ def _declare(l: ctypes.CDLL) -> None:
     sig("ob_embedding_bwd", [P, P, P, P, L, I, I, I, I, P])
     sig("ob_add_f32_to_bf16", [P, P, L, I, P])
     sig("ob_ce_stats", [P, L, P, P, P, P, P, P, P, I, I, I, I, F, P])
-    sig("ob_ce_grad", [P, L, P, P, I, I, I, I, L, F, P, F, I, F, P])
+    sig("ob_ce_grad", [P, L, P, P, I, I, I, I, L, F, P, F, I, F, P, P])
     sig("ob_attn_fwd", [P, P, P, P, P, P, I, I, I, I, L, L, L, F, I, P, P])
     sig("ob_attn_bwd", [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, L, L, L, F, I, P, P])  # 23 args
     sig("ob_bind_thread", [I])

@@ -126,7 +126,7 @@ class _LinearCE(torch.autograd.Function):
             if need_dx or need_dw:
                 rc = l.ob_ce_grad(_lib.ptr(out_view), ld, _lib.ptr(tg[r0:r1]), _lib.ptr(lse), rows, V, int(vocab_offset),
                                   int(total_vocab), int(ignore_index), float(smoothing), _lib.ptr(inv_n), float(grad_scale), mode,
-                                  cap_c, _lib.stream())
+                                  cap_c, None, _lib.stream())
                 _lib.check(rc, "ob_ce_grad")
                 if need_dx:
                     gemm.gemm(out_view, weight, b_mn=True, out=dx[r0:r1])
@@ -161,6 +161,97 @@ class _LinearCE(torch.autograd.Function):
         gx = (dx * factor.to(dx.dtype)).view(ctx.x_shape) if need_dx else None
         gw = dw * factor.to(dw.dtype) if need_dw else None
         return gx, gw, None, None, None, None, None, None, None, None, None, None
+
+
+class _LinearTokenLoss(torch.autograd.Function):
+    """Sum of an arbitrary per-token loss of ``log p(target)`` under the head ``x W^T``.
+
+    ``loss_fn(nll_chunk, r0, r1) -> (loss_chunk, dloss_dnll_chunk)`` is evaluated per row chunk
+    between the statistics kernel and the gradient kernel, so losses whose per-token weight depends
+    on the log-probability itself (clipped policy ratios, KL penalties) need one pass over the
+    ``[tokens, vocab]`` logits, which are never held beyond a chunk.
+    """
+
+    @staticmethod
+    def forward(ctx, x, weight, targets, loss_fn, chunk_rows):
+        l = _lib.lib()
+        dev = x.device
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        tg = targets.reshape(-1).to(torch.int64).contiguous()
+        T, V = x2.shape[0], weight.shape[0]
+        need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        dx = torch.empty_like(x2) if need_dx else None
+        mg = getattr(weight, "main_grad", None) if need_dw else None
+        if mg is not None:
+            dw, first_acc = mg, bool(getattr(weight, "_main_grad_filled", False))
+            weight._main_grad_filled = True
+        else:
+            dw, first_acc = (torch.empty_like(weight) if need_dw else None), False
+        ld = (V + 7) // 8 * 8
+        chunk_rows = min(chunk_rows, T)
+        logits_buf = torch.empty((chunk_rows, ld), dtype=torch.bfloat16, device=dev)
+        st = torch.empty((5, chunk_rows), dtype=torch.float32, device=dev)
+        best = torch.empty(chunk_rows, dtype=torch.int32, device=dev)
+        nll_all = torch.empty(T, dtype=torch.float32, device=dev)
+        total = torch.zeros((), dtype=torch.float32, device=dev)
+        first = True
+        for r0 in range(0, T, chunk_rows):
+            r1 = min(T, r0 + chunk_rows)
+            rows = r1 - r0
+            out_view = logits_buf[:rows].as_strided((rows, V), (ld, 1))
+            gemm.gemm(x2[r0:r1], weight, out=out_view)
+            rc = l.ob_ce_stats(_lib.ptr(out_view), ld, _lib.ptr(tg[r0:r1]), _lib.ptr(st[0]), _lib.ptr(st[1]),
+                               _lib.ptr(st[2]), _lib.ptr(st[3]), _lib.ptr(st[4]), _lib.ptr(best), rows, V, 0, 0, 1.0,
+                               _lib.stream())
+            _lib.check(rc, "ob_ce_stats")
+            lse = st[0, :rows] + torch.log(st[1, :rows])
+            nll = lse - st[3, :rows]
+            nll_all[r0:r1] = nll
+            loss_chunk, dl_dnll = loss_fn(nll, r0, r1)
+            total += loss_chunk.sum()
+            if need_dx or need_dw:
+                w_rows = dl_dnll.to(torch.float32).contiguous()
+                rc = l.ob_ce_grad(_lib.ptr(out_view), ld, _lib.ptr(tg[r0:r1]), _lib.ptr(lse.contiguous()), rows, V, 0, V,
+                                  -(1 << 62), 0.0, None, 1.0, 0, 1.0, _lib.ptr(w_rows), _lib.stream())
+                _lib.check(rc, "ob_ce_grad")
+                if need_dx:
+                    gemm.gemm(out_view, weight, b_mn=True, out=dx[r0:r1])
+                if need_dw:
+                    gemm.gemm(out_view, x2[r0:r1], a_mn=True, b_mn=True, out=dw, accumulate=(not first) or first_acc)
+            first = False
+        ctx.save_for_backward(dx if need_dx else torch.empty(0), dw if (need_dw and mg is None) else torch.empty(0))
+        ctx.x_shape = x.shape
+        ctx.flags = (need_dx, need_dw and mg is None)
+        ctx.mark_non_differentiable(nll_all)
+        return total, nll_all
+
+    @staticmethod
+    def backward(ctx, dloss, _dnll):
+        dx, dw = ctx.saved_tensors
+        need_dx, need_dw = ctx.flags
+        gx = (dx * dloss.to(dx.dtype)).view(ctx.x_shape) if need_dx else None
+        gw = dw * dloss.to(dw.dtype) if need_dw else None
+        return gx, gw, None, None, None
+
+
+def linear_token_loss(x: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor, loss_fn, chunk_rows: int = 4096):
+    """``(sum_i loss_i, nll)`` where ``nll_i = -log softmax(x_i W^T)[target_i]`` and
+    ``loss_fn(nll_chunk, r0, r1) -> (loss_chunk, dloss/dnll chunk)`` defines the per-token loss.
+
+    The returned sum is differentiable with respect to ``x`` and ``weight`` (the gradient uses the
+    derivative ``loss_fn`` reports, treated as exact); ``nll`` is detached. Every target must be a
+    valid class: mask tokens through ``loss_fn`` (zero loss and zero derivative), not the target.
+    """
+    if x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0:
+        return _LinearTokenLoss.apply(x, weight, targets, loss_fn, chunk_rows)
+    logits = F.linear(x.reshape(-1, x.shape[-1]), weight).float()
+    nll = F.cross_entropy(logits, targets.reshape(-1), reduction="none")
+    loss_vals, dl = loss_fn(nll.detach(), 0, nll.numel())
+    # same contract as the kernel path: the value comes from loss_fn, the gradient from its reported derivative
+    total = loss_vals.sum().detach() + ((nll - nll.detach()) * dl.detach()).sum()
+    return total, nll.detach()
 
 
 class _SumGradOverGroup(torch.autograd.Function):

@@ -100,9 +100,10 @@ __global__ void __launch_bounds__(THREADS)
 ce_grad_kernel(__nv_bfloat16* __restrict__ logits, long long ld, const long long* __restrict__ targets,
                const float* __restrict__ row_lse, int rows, int V, int vocab_offset, int total_vocab,
                long long ignore_index, float smoothing, const float* __restrict__ scale_ptr, float scale_mul,
-               int softcap, float cap_c) {
-  const float scale = (scale_ptr ? *scale_ptr : 1.0f) * scale_mul;
+               int softcap, float cap_c, const float* __restrict__ row_weight) {
+  const float scale0 = (scale_ptr ? *scale_ptr : 1.0f) * scale_mul;
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float scale = row_weight ? scale0 * row_weight[row] : scale0;
     __nv_bfloat16* z = logits + (long long)row * ld;
     const long long tgt = targets[row];
     const bool ignored = (tgt == ignore_index);
@@ -159,10 +160,12 @@ extern "C" int ob_ce_stats(const void* logits, long long ld, const void* targets
 
 extern "C" int ob_ce_grad(void* logits, long long ld, const void* targets, const void* row_lse, int rows, int V,
                           int vocab_offset, int total_vocab, long long ignore_index, float smoothing,
-                          const void* scale_ptr, float scale_mul, int softcap, float cap_c, cudaStream_t stream) {
+                          const void* scale_ptr, float scale_mul, int softcap, float cap_c, const void* row_weight,
+                          cudaStream_t stream) {
   if (rows == 0) return 0;
   ce_grad_kernel<<<rows, THREADS, 0, stream>>>((__nv_bfloat16*)logits, ld, (const long long*)targets,
                                                (const float*)row_lse, rows, V, vocab_offset, total_vocab, ignore_index,
-                                               smoothing, (const float*)scale_ptr, scale_mul, softcap, cap_c);
+                                               smoothing, (const float*)scale_ptr, scale_mul, softcap, cap_c,
+                                               (const float*)row_weight);
   return (int)cudaGetLastError();
 }
