@@ -1,0 +1,130 @@
+"""Composite, Muon and SOAP optimizers (CPU)."""
+
+import copy
+
+import pytest
+import torch
+import torch.nn as nn
+
+from optimus_dl_b200.core import conf
+from optimus_dl_b200.optim import build_optimizer
+from optimus_dl_b200.optim.composite import CompositeOptimizer, get_subgroup
+from optimus_dl_b200.optim.muon import Muon, newton_schulz
+from optimus_dl_b200.optim.soap import SOAP, merged_shape
+
+
+def _net():
+    torch.manual_seed(0)
+    return nn.Sequential(nn.Linear(16, 32), nn.Tanh(), nn.Linear(32, 8))
+
+
+def _named(m):
+    return [(n, p) for n, p in m.named_parameters()]
+
+
+def test_newton_schulz_orthogonalises():
+    torch.manual_seed(0)
+    for shape in [(32, 64), (64, 32), (48, 48)]:
+        g = torch.randn(*shape)
+        o = newton_schulz(g, steps=10).float()
+        s = torch.linalg.svdvals(o)
+        assert s.max() < 1.3 and s.min() > 0.5, (shape, s.min(), s.max())
+        u, _, vh = torch.linalg.svd(g, full_matrices=False)
+        assert torch.nn.functional.cosine_similarity((u @ vh).flatten(), o.flatten(), dim=0) > 0.9
+
+
+def test_muon_matches_torch_muon():
+    if not hasattr(torch.optim, "Muon"):
+        pytest.skip("torch.optim.Muon not available")
+    torch.manual_seed(0)
+    w1 = nn.Parameter(torch.randn(24, 40))
+    w2 = nn.Parameter(w1.detach().clone())
+    ours, ref = Muon([w1], lr=0.02), torch.optim.Muon([w2], lr=0.02)
+    for i in range(3):
+        g = torch.randn(24, 40, generator=torch.Generator().manual_seed(i))
+        w1.grad, w2.grad = g.clone(), g.clone()
+        ours.step()
+        ref.step()
+    assert torch.allclose(w1, w2, atol=2e-2), (w1 - w2).abs().max()
+
+
+def test_muon_factory_builds_composite_and_trains():
+    net = _net()
+    cfg = conf.create({"_name": "muon", "lr": 0.02, "weight_decay": 0.0})
+    opt = build_optimizer(cfg, params=_named(net))
+    assert isinstance(opt, CompositeOptimizer) and set(opt.optimizers) == {"muon", "support"}
+    names = {g["composite_optimizer_name"] for g in opt.param_groups}
+    assert names == {"muon", "support"}
+    x, y = torch.randn(64, 16), torch.randn(64, 8)
+    first = None
+    for _ in range(40):
+        opt.zero_grad()
+        loss = (net(x) - y).pow(2).mean()
+        loss.backward()
+        opt.step()
+        first = first if first is not None else loss.item()
+    assert loss.item() < 0.7 * first
+
+
+def test_composite_routing_state_roundtrip_and_lr_alias():
+    net = _net()
+    cfg = conf.create({"_name": "composite", "optimizers": {
+        "a": {"params_regexp": r"0\..*", "optimizer_config": {"_name": "adamw", "lr": 1e-2, "fused": False}},
+        "rest": {"params_regexp": None, "optimizer_config": {"_name": "soap", "lr": 1e-2}}}})
+    opt = build_optimizer(cfg, params=_named(net))
+    assert [g["composite_optimizer_path"] for g in opt.param_groups] == [["a"], ["rest"]]
+    x, y = torch.randn(32, 16), torch.randn(32, 8)
+    for _ in range(3):
+        opt.zero_grad()
+        (net(x) - y).pow(2).mean().backward()
+        opt.step()
+    # a scheduler writing into the composite's groups must reach the children
+    opt.param_groups[0]["lr"] = 5e-3
+    assert opt.optimizers["a"].param_groups[0]["lr"] == 5e-3
+    sd = copy.deepcopy(opt.state_dict())
+    net2 = _net()
+    opt2 = build_optimizer(cfg, params=_named(net2))
+    opt2.load_state_dict(sd)
+    net2.load_state_dict(net.state_dict())
+    assert opt2.optimizers["a"].param_groups[0] is opt2.param_groups[0]
+    assert opt2.optimizers["a"].state is opt2.state
+    for o, n in ((opt, net), (opt2, net2)):
+        o.zero_grad()
+        (n(x) - y).pow(2).mean().backward()
+        o.step()
+    for p, q in zip(net.parameters(), net2.parameters()):
+        assert torch.allclose(p, q, atol=1e-6)
+
+
+def test_composite_errors():
+    net = _net()
+    with pytest.raises(ValueError, match="did not match"):
+        build_optimizer(conf.create({"_name": "composite", "optimizers": {
+            "a": {"params_regexp": "nothing", "optimizer_config": {"_name": "adamw"}}}}), params=_named(net))
+    with pytest.raises(ValueError, match="not matched by any"):
+        build_optimizer(conf.create({"_name": "composite", "optimizers": {
+            "a": {"params_regexp": r"0\..*", "optimizer_config": {"_name": "adamw", "fused": False}}}}), params=_named(net))
+    with pytest.raises(ValueError):
+        get_subgroup(list(net.parameters()), lambda n, p: True)
+
+
+def test_soap_descends_and_merges_dims():
+    assert merged_shape((4, 8, 3, 3), 100) == [96, 3]
+    assert merged_shape((50000, 64), 10000) == [50000, 64]
+    torch.manual_seed(0)
+    w = nn.Parameter(torch.randn(20, 12))
+    b = nn.Parameter(torch.zeros(20))
+    x = torch.randn(256, 12)
+    target = x @ torch.randn(12, 20)
+    opt = SOAP([w, b], lr=0.05, weight_decay=0.0, precondition_frequency=5)
+    losses = []
+    for _ in range(80):
+        opt.zero_grad()
+        loss = ((x @ w.t() + b) - target).pow(2).mean()
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    assert losses[-1] < 0.05 * losses[0]
+    q = opt.state[w]["Q"]
+    assert torch.allclose(q[0].t() @ q[0], torch.eye(20), atol=1e-4)
+    assert opt.state[b]["GG"] == [None]
