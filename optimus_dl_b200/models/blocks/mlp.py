@@ -39,6 +39,12 @@ class SwiGLUMLP(nn.Module):
             return tp_ops.swiglu_mlp_forward(self, x, residual)
         if residual is not None:
             return residual + self.forward(x)
+        if lin_ops.fp8_route([self.w1.weight, self.w2.weight, self.c_proj.weight]):
+            # FP8 context: gate/up as one block-scaled GEMM, SwiGLU, then the down projection
+            gu = lin_ops.multi_linear(x, [self.w1.weight, self.w2.weight], [self.w1.bias, self.w2.bias])
+            g, u = gu.split(self.w1.weight.shape[0], dim=-1)
+            y = lin_ops.linear(act_ops.swiglu(g.contiguous(), u.contiguous()), self.c_proj.weight, self.c_proj.bias)
+            return self.dropout(y) if self.dropout is not None else y
         if self.w1.bias is None and self.c_proj.bias is None:
             y = act_ops.swiglu_mlp(x, self.w1.weight, self.w2.weight, self.c_proj.weight)
             return self.dropout(y) if self.dropout is not None else y

@@ -1,0 +1,202 @@
+"""Block-scaled e4m3 matrix products (``csrc/gemm_fp8.cu``).
+
+Scaling follows the fine-grained scheme used for FP8 training of large models: activations (and
+output gradients) carry one scale per ``1 x 128`` block along the reduction dimension, weights one
+scale per ``128 x 128`` block; products accumulate in fp32 per 128-wide k-block, are scaled and
+summed in registers, and leave the kernel in bf16. This is the path the reference reaches through
+Transformer Engine's ``Float8BlockScaling`` recipe (optimus_dl/modules/amp/fp8.py:180-315); here it is
+a hand-written tcgen05 kernel.
+
+``fp8_linear`` is the autograd function behind FP8 linear layers: forward ``y = q(x) q(W)^T`` and
+input gradient ``dx = q(dy) q(W^T)^T`` in FP8, weight gradient ``dW = dy^T x`` in bf16 (it feeds the
+fp32 master-weight update and is the product most sensitive to quantisation noise). The quantised
+weight and its transpose are cached per parameter version, i.e. re-made once per optimizer step.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _lib, gemm
+from . import linear as lin_ops
+
+E4M3_MAX = 448.0
+BLOCK = 128
+
+
+def kernel_ok(*ts: torch.Tensor) -> bool:
+    return all(t.is_cuda and t.dtype == torch.bfloat16 for t in ts) and _lib.available()
+
+
+# ---------------------------------------------------------------------- reference (PyTorch) quantisers
+def quantize_rowwise_ref(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """``x [rows, cols]`` -> (e4m3 values ``[rows, cols]``, scales ``[cols / 128, rows]`` fp32)."""
+    rows, cols = x.shape
+    xb = x.float().view(rows, cols // BLOCK, BLOCK)
+    amax = xb.abs().amax(-1)
+    scale = torch.where(amax > 0, amax / E4M3_MAX, torch.ones_like(amax))
+    q = (xb / scale[..., None]).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn).view(rows, cols)
+    return q, scale.t().contiguous()
+
+
+def quantize_block_ref(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """``w [rows, cols]`` -> (e4m3 ``[rows, cols]``, scales ``[ceil(rows/128), ceil(cols/128)]``)."""
+    rows, cols = w.shape
+    pr, pc = (-rows) % BLOCK, (-cols) % BLOCK
+    wp = torch.nn.functional.pad(w.float(), (0, pc, 0, pr))
+    R, C = wp.shape[0] // BLOCK, wp.shape[1] // BLOCK
+    wb = wp.view(R, BLOCK, C, BLOCK)
+    amax = wb.abs().amax(dim=(1, 3))
+    scale = torch.where(amax > 0, amax / E4M3_MAX, torch.ones_like(amax))
+    q = (wb / scale[:, None, :, None]).clamp(-E4M3_MAX, E4M3_MAX).view(wp.shape)[:rows, :cols]
+    return q.to(torch.float8_e4m3fn).contiguous(), scale
+
+
+def gemm_fp8_ref(a8: torch.Tensor, sa: torch.Tensor, b8: torch.Tensor, sb: torch.Tensor) -> torch.Tensor:
+    """fp32 statement of the block-scaled product (dequantise, then multiply)."""
+    M, K = a8.shape
+    N = b8.shape[0]
+    a = a8.float().view(M, K // BLOCK, BLOCK) * sa.t()[:, :, None]
+    nb = torch.arange(N, device=b8.device) // BLOCK
+    b = b8.float().view(N, K // BLOCK, BLOCK) * sb[nb][:, :, None]
+    return a.reshape(M, K) @ b.reshape(N, K).t()
+
+
+# ---------------------------------------------------------------------- kernels
+def quantize_rowwise(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    x = x.reshape(-1, x.shape[-1])
+    rows, cols = x.shape
+    if not kernel_ok(x) or cols % BLOCK != 0:
+        return quantize_rowwise_ref(x)
+    if x.stride(1) != 1 or x.stride(0) % 4 != 0:
+        x = x.contiguous()
+    q = torch.empty((rows, cols), dtype=torch.float8_e4m3fn, device=x.device)
+    scales = torch.empty((cols // BLOCK, rows), dtype=torch.float32, device=x.device)
+    rc = _lib.lib().ob_quant_fp8_rowwise(_lib.ptr(x), x.stride(0), _lib.ptr(q), cols, _lib.ptr(scales), rows, rows, cols,
+                                         _lib.stream())
+    _lib.check(rc, "ob_quant_fp8_rowwise")
+    return q, scales
+
+
+def quantize_block(w: torch.Tensor, with_transpose: bool = False):
+    """Returns ``(q, scales)`` or, with ``with_transpose``, ``(q, scales, q_t, scales_t)``."""
+    rows, cols = w.shape
+    if not kernel_ok(w) or rows % 16 != 0 or cols % 16 != 0 or not w.is_contiguous():
+        q, s = quantize_block_ref(w)
+        if with_transpose:
+            return q, s, q.t().contiguous(), s.t().contiguous()
+        return q, s
+    R, C = (rows + BLOCK - 1) // BLOCK, (cols + BLOCK - 1) // BLOCK
+    q = torch.empty((rows, cols), dtype=torch.float8_e4m3fn, device=w.device)
+    s = torch.empty((R, C), dtype=torch.float32, device=w.device)
+    qt = st = None
+    if with_transpose:
+        qt = torch.empty((cols, rows), dtype=torch.float8_e4m3fn, device=w.device)
+        st = torch.empty((C, R), dtype=torch.float32, device=w.device)
+    rc = _lib.lib().ob_quant_fp8_block(_lib.ptr(w), w.stride(0), _lib.ptr(q), cols, _lib.ptr(qt), rows, _lib.ptr(s),
+                                       _lib.ptr(st), rows, cols, _lib.stream())
+    _lib.check(rc, "ob_quant_fp8_block")
+    return (q, s, qt, st) if with_transpose else (q, s)
+
+
+def gemm_fp8(a8: torch.Tensor, sa: torch.Tensor, b8: torch.Tensor, sb: torch.Tensor,
+             out: torch.Tensor | None = None) -> torch.Tensor:
+    """``C[M,N] = sum_kb sa[kb, m] sb[n // 128, kb] (A8[m, kb] . B8[n, kb])`` in bf16."""
+    M, K = a8.shape
+    N = b8.shape[0]
+    if not (a8.is_cuda and _lib.available()) or K % BLOCK != 0 or K % 16 != 0:
+        r = gemm_fp8_ref(a8, sa, b8, sb).to(torch.bfloat16)
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a8.device)
+    rc = _lib.lib().ob_gemm_fp8_block(_lib.ptr(a8), a8.stride(0), _lib.ptr(sa), sa.stride(0), _lib.ptr(b8), b8.stride(0),
+                                      _lib.ptr(sb), _lib.ptr(out), out.stride(0), M, N, K,
+                                      _lib.ptr(_lib.status_word(a8.device)), _lib.stream())
+    _lib.check(rc, "ob_gemm_fp8_block")
+    return out
+
+
+# ---------------------------------------------------------------------- autograd
+def _cached_weight(w: torch.Tensor, holder: torch.Tensor | None = None):
+    """Quantised weight and transpose, re-made when the parameter's version counter moves. ``holder`` is
+    the long-lived tensor the cache is attached to when ``w`` is a temporary view of several parameters."""
+    holder = holder if holder is not None else w
+    key = (w.data_ptr(), holder._version, tuple(w.shape))
+    hit = getattr(holder, "_fp8_cache", None)
+    if hit is None or hit[0] != key:
+        q, s, qt, st = quantize_block(w.detach(), with_transpose=True)
+        hit = (key, q, s, qt, st)
+        holder._fp8_cache = hit
+    return hit[1:]
+
+
+class _Fp8Linear(torch.autograd.Function):
+    """``y = x cat(W_i)^T + b``; the ``W_i`` are adjacent in memory (or a single matrix), so their
+    concatenation is a view. Weight gradients go to each ``W_i`` (through ``main_grad`` when it has one)."""
+
+    @staticmethod
+    def forward(ctx, x, bias, *owners):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        w = owners[0] if len(owners) == 1 else lin_ops._fused_view(list(owners))
+        wq, ws, _, _ = _cached_weight(w, owners[0])
+        xq, xs = quantize_rowwise(x2)
+        y = gemm_fp8(xq, xs, wq, ws)
+        if bias is not None:
+            y = y + bias
+        ctx.save_for_backward(x2, *owners)
+        ctx.owners = owners
+        ctx.has_bias = bias is not None
+        ctx.x_shape = shp
+        return y.view(*shp[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2 = ctx.saved_tensors[0]
+        owners = ctx.owners
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = db = None
+        if ctx.needs_input_grad[0]:
+            w = owners[0] if len(owners) == 1 else lin_ops._fused_view(list(owners))
+            _, _, wqt, wst = _cached_weight(w, owners[0])
+            dq, ds = quantize_rowwise(dy2)
+            dx = gemm_fp8(dq, ds, wqt, wst).view(ctx.x_shape)
+        dws: list = [None] * len(owners)
+        o = 0
+        for i, p in enumerate(owners):
+            rows = p.shape[0]
+            if ctx.needs_input_grad[2 + i]:
+                mg = lin_ops.main_grad_of(p)
+                if mg is not None:
+                    gemm.gemm(dy2[:, o:o + rows], x2, a_mn=True, b_mn=True, out=mg, accumulate=lin_ops.main_grad_write(p))
+                else:
+                    dws[i] = gemm.gemm(dy2[:, o:o + rows], x2, a_mn=True, b_mn=True)
+            o += rows
+        if ctx.has_bias:
+            db = dy2.float().sum(0).to(dy.dtype)
+        return (dx, db, *dws)
+
+
+def fp8_shapes_ok(weights: list[torch.Tensor]) -> bool:
+    k = weights[0].shape[1]
+    return k % BLOCK == 0 and sum(w.shape[0] for w in weights) % 16 == 0 and all(w.is_contiguous() for w in weights)
+
+
+def fp8_linear(x: torch.Tensor, weights: torch.Tensor | list[torch.Tensor], bias: torch.Tensor | None = None) -> torch.Tensor:
+    """``x @ cat(weights)^T + bias`` through the block-scaled e4m3 GEMM. ``weights`` is one matrix or a
+    list of matrices that sit back to back in memory. Falls back to the bf16 GEMM when shapes do not fit."""
+    ws = [weights] if isinstance(weights, torch.Tensor) else list(weights)
+    if kernel_ok(x, *ws) and fp8_shapes_ok(ws) and (len(ws) == 1 or lin_ops._adjacent(ws)):
+        return _Fp8Linear.apply(x, bias, *ws)
+    if len(ws) == 1:
+        return lin_ops._MultiLinear.apply(x, 1, ws[0], bias) if lin_ops._kernel_ok(x, ws, [bias]) else \
+            torch.nn.functional.linear(x, ws[0], bias)
+    y = lin_ops._MultiLinear.apply(x, len(ws), *ws, *([None] * len(ws)))
+    return y if bias is None else y + bias

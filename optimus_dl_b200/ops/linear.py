@@ -166,6 +166,35 @@ def _kernel_ok(x: torch.Tensor, ws: list[torch.Tensor], bs: list) -> bool:
     return sum(w.shape[0] for w in ws) % 8 == 0
 
 
+def ensure_gathered(weights: list[torch.Tensor]) -> None:
+    """Finish a pending fused all-gather of these weights when the consumer is not the fused AG GEMM."""
+    job = getattr(weights[0], "_ag_pending", None)
+    if job is not None and not job.done:
+        job.gather_only()
+
+
+def fp8_route(weights: list[torch.Tensor]) -> bool:
+    """True when an FP8 autocast context is active and every weight was marked for FP8 execution
+    (``_fp8`` attribute, set by the ``transformer_engine`` model transform)."""
+    if not all(getattr(w, "_fp8", False) for w in weights):
+        return False
+    from ..amp.fp8 import fp8_enabled
+
+    return fp8_enabled()
+
+
+def _fp8_multi_linear(x: torch.Tensor, weights: list[torch.Tensor], biases: list) -> torch.Tensor:
+    from . import fp8 as fp8_ops
+
+    ensure_gathered(weights)
+    if len(weights) == 1:
+        return fp8_ops.fp8_linear(x, weights[0], biases[0])
+    if _adjacent(weights):
+        bias = None if biases[0] is None else _fused_bias(biases)
+        return fp8_ops.fp8_linear(x, weights, bias)
+    return torch.cat([fp8_ops.fp8_linear(x, w, b) for w, b in zip(weights, biases)], dim=-1)
+
+
 def multi_linear(x: torch.Tensor, weights: list[torch.Tensor], biases: list | None = None) -> torch.Tensor:
     """``cat([x @ W_i^T + b_i], -1)`` with one GEMM when the weights are adjacent in memory."""
     n = len(weights)
@@ -174,6 +203,8 @@ def multi_linear(x: torch.Tensor, weights: list[torch.Tensor], biases: list | No
         biases = [None] * n
     elif any(b is None for b in biases):
         raise ValueError("either every projection has a bias or none")
+    if fp8_route(weights) and _kernel_ok(x, weights, biases):
+        return _fp8_multi_linear(x, weights, biases)
     if _kernel_ok(x, weights, biases):
         return _MultiLinear.apply(x, n, *weights, *biases)
     return torch.cat([F.linear(x, w, b) for w, b in zip(weights, biases)], dim=-1)
@@ -181,6 +212,8 @@ def multi_linear(x: torch.Tensor, weights: list[torch.Tensor], biases: list | No
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
     """``x @ weight^T + bias`` (tcgen05 GEMM for CUDA bf16, ``F.linear`` otherwise)."""
+    if fp8_route([weight]) and _kernel_ok(x, [weight], [bias]):
+        return _fp8_multi_linear(x, [weight], [bias])
     if _kernel_ok(x, [weight], [bias]):
         return _MultiLinear.apply(x, 1, weight, bias)
     return F.linear(x, weight, bias)

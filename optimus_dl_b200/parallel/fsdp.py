@@ -544,6 +544,14 @@ class AGJob:
             inf.param._ag_pending = None
         return out
 
+    def gather_only(self, pull_ctas: int = 24) -> None:
+        """Complete the gather without the fused GEMM (for consumers that run another kernel on the weight)."""
+        if not self.done:
+            self.group.pull("first", pull_ctas)
+            self.done = True
+            for inf in self.group.first_gemm_infos:
+                inf.param._ag_pending = None
+
 
 class _nullctx:
     def __enter__(self):

@@ -1,0 +1,120 @@
+"""Block-scaled e4m3 GEMM, quantisers and the FP8 linear path against fp32 PyTorch statements."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _dq_row(q, s):
+    rows, cols = q.shape
+    return (q.float().view(rows, cols // 128, 128) * s.t()[:, :, None]).view(rows, cols)
+
+
+def test_rowwise_quantiser():
+    from optimus_dl_b200.ops import fp8
+
+    torch.manual_seed(0)
+    x = (torch.randn(300, 512, device="cuda") * torch.rand(300, 1, device="cuda") * 4).bfloat16()
+    x[5] = 0
+    q, s = fp8.quantize_rowwise(x)
+    qr, sr = fp8.quantize_rowwise_ref(x)
+    assert q.dtype == torch.float8_e4m3fn and s.shape == (4, 300)
+    assert torch.allclose(s, sr, rtol=1e-6)
+    assert (q.float() == qr.float()).float().mean() > 0.999
+    rel = (_dq_row(q, s) - x.float()).abs().max() / x.float().abs().max()
+    assert rel < 0.07
+    assert torch.all(_dq_row(q, s)[5] == 0)
+
+
+def test_block_quantiser_and_transpose():
+    from optimus_dl_b200.ops import fp8
+
+    torch.manual_seed(0)
+    w = (torch.randn(400, 384, device="cuda") * 0.05).bfloat16()
+    q, s, qt, st = fp8.quantize_block(w, with_transpose=True)
+    qr, sr = fp8.quantize_block_ref(w)
+    assert s.shape == (4, 3) and st.shape == (3, 4)
+    assert torch.allclose(s, sr, rtol=1e-6) and torch.equal(st, s.t())
+    assert (q.float() == qr.float()).float().mean() > 0.999
+    assert torch.equal(qt.float(), q.float().t())
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (512, 1024, 1024), (300, 400, 384), (4096, 4096, 4096), (77, 130, 256)])
+def test_fp8_gemm_matches_dequantised_product(M, N, K):
+    from optimus_dl_b200.ops import _lib, fp8
+
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
+    a8, sa = fp8.quantize_rowwise_ref(a)
+    b8, sb = fp8.quantize_block_ref(b)
+    out = fp8.gemm_fp8(a8, sa, b8, sb)
+    torch.cuda.synchronize()
+    _lib.check_status(torch.device("cuda"))
+    ref = fp8.gemm_fp8_ref(a8, sa, b8, sb)
+    err = (out.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-9)
+    assert err < 1e-2, err
+    # and the whole chain is a usable approximation of the bf16 product
+    exact = a.float() @ b.float().t()
+    rel = (out.float() - exact).norm() / exact.norm()
+    assert rel < 0.06, rel
+
+
+def test_fp8_linear_forward_backward():
+    from optimus_dl_b200.ops import fp8
+
+    torch.manual_seed(0)
+    x = torch.randn(2, 192, 512, device="cuda").bfloat16().requires_grad_(True)
+    w = (torch.randn(768, 512, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    b = torch.randn(768, device="cuda").bfloat16().requires_grad_(True)
+    y = fp8.fp8_linear(x, w, b)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xf, wf, bf = (t.detach().float().requires_grad_(True) for t in (x, w, b))
+    yr = torch.nn.functional.linear(xf, wf, bf)
+    yr.backward(dy.float())
+    rel = lambda a, r: ((a.float() - r).norm() / r.norm()).item()  # noqa: E731
+    assert rel(y, yr) < 0.05
+    assert rel(x.grad, xf.grad) < 0.06
+    assert rel(w.grad, wf.grad) < 0.02     # weight gradient stays in bf16
+    assert rel(b.grad, bf.grad) < 0.02
+    # the cache follows the parameter version
+    first = w._fp8_cache[0]
+    with torch.no_grad():
+        w.add_(0.01)
+    fp8.fp8_linear(x, w, b)
+    assert w._fp8_cache[0] != first
+
+
+def test_fp8_training_tracks_bf16():
+    from optimus_dl_b200.amp.fp8 import FP8Recipe
+    from optimus_dl_b200.criterion.cross_entropy import CrossEntropyCriterion, CrossEntropyCriterionConfig
+    from optimus_dl_b200.model_transforms.transformer_engine import mark_fp8_linears
+    from optimus_dl_b200.models.llama2 import Llama, LlamaConfig
+
+    def run(fp8_on: bool):
+        torch.manual_seed(0)
+        cfg = LlamaConfig(n_layer=2, n_head=4, n_kv_head=2, n_embd=256, vocab_size=512, sequence_length=128,
+                          intermediate_size=512, tie_word_embeddings=False)
+        model = Llama(cfg).to(device="cuda", dtype=torch.bfloat16)
+        if fp8_on:
+            assert mark_fp8_linears(model) == 14
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+        crit = CrossEntropyCriterion(CrossEntropyCriterionConfig())
+        recipe = FP8Recipe()
+        ids = torch.randint(0, 512, (4, 129), device="cuda", generator=torch.Generator(device="cuda").manual_seed(1))
+        losses = []
+        for _ in range(12):
+            opt.zero_grad()
+            with recipe.autocast(fp8_on):
+                loss, _ = crit(model, {"input_ids": ids})
+                loss.backward()
+            opt.step()
+            losses.append(loss.item())
+        return losses
+
+    ref, got = run(False), run(True)
+    assert got[-1] < got[0] - 0.5, got
+    assert abs(got[-1] - ref[-1]) < 0.25, (ref[-1], got[-1])
+    assert abs(got[0] - ref[0]) < 0.05
