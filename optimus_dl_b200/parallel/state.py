@@ -28,15 +28,85 @@ def engine_of(model: nn.Module) -> Any:
     return getattr(model, "_sharding_engine", None)
 
 
+def _tp_mesh_of(param: torch.Tensor) -> Any:
+    tp = getattr(param, "_tp_state", None)
+    if tp is None or tp.size == 1:
+        return None
+    if tp.mesh is None:
+        from torch.distributed.device_mesh import DeviceMesh
+
+        tp.mesh = DeviceMesh.from_group(tp.group, tp.device.type)
+    return tp.mesh
+
+
+def _wrap_tp(local: torch.Tensor, param: torch.Tensor) -> Any:
+    """Tensor-parallel shard -> ``DTensor`` sharded on the parameter's tensor-parallel dimension, the layout
+    ``parallelize_module`` gives the reference's parameters (row-sharded ``wq``, column-sharded ``wo``, ...)."""
+    dim = getattr(param, "_tp_shard_dim", None)
+    mesh = _tp_mesh_of(param)
+    if dim is None or mesh is None:
+        return local
+    from torch.distributed.tensor import DTensor, Shard
+
+    full = list(local.shape)
+    full[dim] *= mesh.size(0)
+    stride = torch.empty(full, device="meta").stride()
+    return DTensor.from_local(local, mesh, [Shard(dim)], run_check=False, shape=torch.Size(full), stride=stride)
+
+
+def _wrap_2d(local: torch.Tensor, inf_shape: tuple, param: torch.Tensor, dp_mesh: Any) -> Any:
+    """Shard of a parameter that is split over tensor-parallel ranks first and over the data-parallel shard
+    group second: a 2-D ``DTensor`` on ``(dp_shard, tp)``. When both splits hit dim 0 the data-parallel
+    placement is the strided shard PyTorch uses for FSDP2 on top of tensor parallelism, so the global
+    tensor keeps its natural row order."""
+    from torch.distributed.device_mesh import DeviceMesh
+    from torch.distributed.tensor import DTensor, Shard
+    from torch.distributed.tensor.placement_types import _StridedShard
+
+    tp_mesh = _tp_mesh_of(param)
+    dim = int(param._tp_shard_dim)
+    tp_size = tp_mesh.size(0)
+    if dim == 0 and inf_shape[0] % dp_mesh.size(0) != 0:
+        raise NotImplementedError("checkpointing uneven data-parallel shards of a row-split tensor-parallel parameter")
+    root = getattr(tp_mesh, "_get_root_mesh", lambda: None)()
+    mesh2d = root["dp_shard", "tp"] if root is not None and root is not tp_mesh and "dp_shard" in (root.mesh_dim_names or ()) \
+        else None
+    if mesh2d is None:
+        raise NotImplementedError("tensor-parallel x sharded checkpoints need the (dp_shard, tp) device mesh")
+    full = list(inf_shape)
+    full[dim] *= tp_size
+    dp_place = _StridedShard(0, split_factor=tp_size) if dim == 0 else Shard(0)
+    stride = torch.empty(full, device="meta").stride()
+    return DTensor.from_local(local, mesh2d, [dp_place, Shard(dim)], run_check=False, shape=torch.Size(full), stride=stride)
+
+
+def _wrap_shard(local: torch.Tensor, inf: Any, use_mesh: Any) -> Any:
+    """Checkpoint view of one engine shard: plain, 1-D (data-parallel or tensor-parallel) or 2-D ``DTensor``."""
+    if len(inf.shape) == 0:
+        return local
+    tp_sharded = getattr(inf.param, "_tp_shard_dim", None) is not None and _tp_mesh_of(inf.param) is not None
+    if tp_sharded and use_mesh is not None:
+        return _wrap_2d(local, inf.shape, inf.param, use_mesh)
+    if tp_sharded:
+        return _wrap_tp(local.view(inf.shape), inf.param)
+    return _wrap(local, inf.shape, use_mesh)
+
+
 def model_state_dict(model: nn.Module, mesh: Any = None) -> dict[str, Any]:
     """``{fqn: tensor}``; engine-managed parameters appear as (sharded) fp32 master weights."""
     eng = engine_of(model)
     if eng is None:
-        return dict(model.state_dict())
+        sd = dict(model.state_dict())
+        if getattr(model, "_tp", None) is not None:
+            params = dict(model.named_parameters(remove_duplicate=False))
+            for name, p in params.items():
+                if name in sd and getattr(p, "_tp_shard_dim", None) is not None:
+                    sd[name] = _wrap_tp(sd[name], p)
+        return sd
     out: dict[str, Any] = {}
     use_mesh = mesh if eng.world > 1 else None
     for name, g, inf in eng.named_sharded_state():
-        out[name] = _wrap(g.local_shard(inf, g.master), inf.shape, use_mesh) if len(inf.shape) > 0 else g.local_shard(inf, g.master)
+        out[name] = _wrap_shard(g.local_shard(inf, g.master), inf, use_mesh)
     # tied parameters appear once in named_parameters; mirror the aliases the module's own
     # state_dict would list (e.g. lm_head.weight == transformer.wte.weight)
     by_id = {id(p): n for n, p in model.named_parameters()}
@@ -83,8 +153,8 @@ def optimizer_state_dict(model: nn.Module, optimizer: Any, mesh: Any = None) -> 
         g.ensure_state()
         state[name] = {
             "step": torch.tensor(float(optimizer.step_count)),
-            "exp_avg": _wrap(g.local_shard(inf, g.exp_avg), inf.shape, use_mesh),
-            "exp_avg_sq": _wrap(g.local_shard(inf, g.exp_avg_sq), inf.shape, use_mesh),
+            "exp_avg": _wrap_shard(g.local_shard(inf, g.exp_avg), inf, use_mesh),
+            "exp_avg_sq": _wrap_shard(g.local_shard(inf, g.exp_avg_sq), inf, use_mesh),
         }
     names = {id(p): n for n, p in model.named_parameters()}
     groups = []

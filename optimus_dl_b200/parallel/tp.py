@@ -290,6 +290,7 @@ class _ColumnParallel(torch.autograd.Function):
     @staticmethod
     def forward(ctx, tp: TPState, sp: bool, x, n, *wb):
         ws, bs = list(wb[:n]), list(wb[n:])
+        lin_ops.ensure_gathered(ws)   # a sharding engine may still be gathering these weights
         bias = None if bs[0] is None else lin_ops._fused_bias(bs)
         wf = _cat_weights(ws)
         if sp:
