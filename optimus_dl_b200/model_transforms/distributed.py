@@ -105,15 +105,24 @@ class FullyShardTransform(BaseModelTransform):
         if device.type != "cuda":
             logger.warning("fully_shard: no CUDA device; model left unsharded (fp32, single process semantics)")
             return model.to(device)
-        group = None
+        group = rep_group = None
+        rep_world = 1
         if collective is not None and collective.world_size > 1:
             mesh = getattr(collective, "parallel_mesh", None)
             group = mesh.get_group("dp_shard") if mesh is not None else collective.process_group
+            if mesh is not None and mesh["dp_replicate"].size() > 1:
+                if bool(self.cfg.use_hybrid_sharding):
+                    # shard inside dp_shard (NVLink domain), sum gradients over dp_replicate
+                    rep_group, rep_world = mesh.get_group("dp_replicate"), mesh["dp_replicate"].size()
+                else:
+                    # one flat shard group over every data-parallel rank
+                    group = mesh["dp_replicate", "dp_shard"]._flatten("dp").get_group()
         cfg = FSDPConfig(reshard_after_forward=bool(self.cfg.reshard_after_forward),
                          fuse_optimizer_in_backward=bool(self.cfg.fuse_optimizer_in_backward),
                          copy_ctas=int(self.cfg.copy_ctas), pull_ctas=int(self.cfg.pull_ctas),
                          sync_grad_accum=bool(self.cfg.sync_grad_accum))
-        fully_shard_model(model, group, device, cfg)
+        engine = fully_shard_model(model, group, device, cfg)
+        engine.replicate_group, engine.replicate_world = rep_group, rep_world
         return model
 
 

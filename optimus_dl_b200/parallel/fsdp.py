@@ -348,6 +348,10 @@ class ShardingEngine:
         self.barrier = symm.DeviceBarrier(self.heap)
         self.comm_stream = torch.cuda.Stream(device=device) if device.type == "cuda" else None
         self.require_grad_sync = True
+        # hybrid sharding: gradients are additionally summed over this group of replicas (one rank per
+        # replica holding the same shard) before the update; set by the fully_shard transform
+        self.replicate_group: Any | None = None
+        self.replicate_world = 1
         self.optimizer: "ShardedAdamW | None" = None
         self._callback_queued = False
         self._step_open = False
@@ -466,7 +470,8 @@ class ShardingEngine:
         g.fold_autograd_grads()
         g.grads_reduced = True
         opt = self.optimizer
-        fused = (opt is not None and self.cfg.fuse_optimizer_in_backward and opt.max_norm <= 0.0)
+        fused = (opt is not None and self.cfg.fuse_optimizer_in_backward and opt.max_norm <= 0.0
+                 and self.replicate_group is None)
         run_on_side = self.comm_stream is not None
         stream = self.comm_stream if run_on_side else torch.cuda.current_stream()
         if run_on_side:
@@ -608,7 +613,7 @@ class ShardedAdamW(torch.optim.Optimizer):
         return dict(lr=pg["lr"], betas=pg["betas"], eps=pg["eps"])
 
     def grad_scale(self, world: int) -> float:
-        return 1.0 / world
+        return 1.0 / (world * max(int(self.engine.replicate_world), 1))
 
     def set_max_norm(self, max_norm: float | None) -> None:
         self.max_norm = float(max_norm or 0.0)
@@ -623,6 +628,12 @@ class ShardedAdamW(torch.optim.Optimizer):
             torch.cuda.current_stream().wait_stream(eng.comm_stream)
         pending = [g for g in eng.groups if not g.updated_in_backward]
         if pending:
+            if eng.replicate_group is not None:
+                # sum the reduced fp32 shards over the replicas, then rebuild the squared norm from the sums
+                eng.sumsq.zero_()
+                for g in pending:
+                    dist.all_reduce(g.grad_shard, group=eng.replicate_group)
+                    eng.sumsq += g.grad_shard.pow(2).sum()
             if eng.world > 1:
                 dist.all_reduce(eng.sumsq, group=eng.pg)
             for g in pending:

@@ -23,10 +23,11 @@ CFG = dict(_name="llama2", n_layer=2, n_head=8, n_kv_head=2, n_embd=256, interme
 
 def main() -> None:
     clip = float(sys.argv[1]) if len(sys.argv) > 1 else 0.0
+    shard = int(sys.argv[2]) if len(sys.argv) > 2 else 0   # sharding world size; 0 = all ranks (no replicas)
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    coll = build_best_collective(DistributedConfig(tp_size=1, sharding_world_size=world), dev)
+    coll = build_best_collective(DistributedConfig(tp_size=1, sharding_world_size=shard or world), dev)
     torch.manual_seed(0)
     ref = build_model(CFG)
     gpu = copy.deepcopy(ref).to(dev, torch.bfloat16)

@@ -28,6 +28,12 @@ def test_fsdp_matches_single_process(unique_port, clip):
     assert "MP_FSDP_OK" in out, out[-4000:]
 
 
+def test_hybrid_sharding_replicas_stay_in_sync(unique_port):
+    """Two replicas of a one-rank shard group: gradients are summed over the replicate group before the update."""
+    out = _run("_mp_fsdp_check.py", 2, unique_port, "0.5", "1")
+    assert "MP_FSDP_OK" in out, out[-4000:]
+
+
 @pytest.mark.parametrize("kind,sp", [("llama", "1"), ("llama", "0"), ("qwen3", "1"), ("olmo3", "1")])
 def test_tensor_parallel_matches_unsharded(unique_port, kind, sp):
     """Fused all-gather GEMM / GEMM reduce-scatter / embedding push against the unsharded model."""
