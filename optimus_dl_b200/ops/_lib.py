@@ -189,7 +189,7 @@ def _declare(l: ctypes.CDLL) -> None:
     sig("ob_gemm_fp8_block", [P, L, P, L, P, L, P, P, L, I, I, I, P, P])
     sig("ob_quant_fp8_rowwise", [P, L, P, L, P, L, I, I, P])
     sig("ob_quant_fp8_block", [P, L, P, L, P, L, P, P, I, I, P])
-    sig("ob_attn_decode", [P, L, P, P, L, P, P, L, L, P, P, L, P, P, I, I, I, I, I, I, F, I, P])
+    sig("ob_attn_decode", [P, L, P, P, L, P, P, L, L, L, P, P, L, P, P, I, I, I, I, I, I, F, I, P])
     sig("ob_sample", [P, I, L, I, I, F, I, F, I, ctypes.c_uint64, ctypes.c_uint64, P, P])
     sig("ob_embedding_push", [P, I, P, I, I, I, PP, I, I, P])
     sig("ob_rs_sum", [PP, I, I, I, P, I, I, L, P, L, P, L, I, P, P])

@@ -1,0 +1,242 @@
+"""Kernel micro-benchmarks: ``python -m optimus_dl_b200.ops.benchmark --op <name> [--size ...]``.
+
+Every case is timed with CUDA events on the launching stream after warm-up, with a synchronise on
+both sides; between timed iterations a buffer larger than the L2 cache is overwritten, so no case
+reads its operands from a warm L2. One JSON line per case: the achieved rate, the algorithmic work
+it is computed from, and (when ``MEASURED_PEAKS.json`` is found next to the repository root) the
+fraction of the measured copy bandwidth / cuBLAS bf16 throughput. Multi-GPU cases
+(``--op tp_ag_gemm`` / ``tp_gemm_rs``) are launched with ``torchrun`` and report the maximum over ranks.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+from typing import Callable
+
+import torch
+
+
+def _peaks() -> dict:
+    here = os.path.dirname(os.path.abspath(__file__))
+    for up in (3, 2):
+        p = os.path.join(here, *[".."] * (up - 1), "MEASURED_PEAKS.json")
+        if os.path.exists(p):
+            try:
+                return json.load(open(p))
+            except Exception:  # noqa: BLE001
+                return {}
+    return {}
+
+
+class Timer:
+    def __init__(self, iters: int = 20, warmup: int = 3, flush_mb: int = 512):
+        self.iters, self.warmup = iters, warmup
+        self.flush = torch.empty(flush_mb * 1024 * 1024 // 4, dtype=torch.float32, device="cuda") if flush_mb else None
+
+    def __call__(self, fn: Callable[[], None]) -> float:
+        """Median milliseconds per call."""
+        for _ in range(self.warmup):
+            fn()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(self.iters):
+            if self.flush is not None:
+                self.flush.add_(1.0)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+        times.sort()
+        return times[len(times) // 2]
+
+
+def _emit(op: str, case: dict, ms: float, flops: float = 0.0, bytes_: float = 0.0, **extra) -> None:
+    pk = _peaks()
+    rec = {"op": op, **case, "ms": round(ms, 4)}
+    if flops:
+        tf = flops / ms / 1e9
+        rec["tflops"] = round(tf, 1)
+        if pk.get("bf16_tflops"):
+            rec["of_measured_bf16_peak"] = round(tf / pk["bf16_tflops"], 3)
+    if bytes_:
+        gbs = bytes_ / ms / 1e6
+        rec["gbs"] = round(gbs, 1)
+        if pk.get("hbm_gbs"):
+            rec["of_measured_hbm"] = round(gbs / pk["hbm_gbs"], 3)
+    rec.update(extra)
+    print(json.dumps(rec), flush=True)
+
+
+def bench_gemm_bf16(t: Timer, sizes) -> None:
+    from . import gemm
+
+    for M, N, K in sizes:
+        a = torch.randn(M, K, device="cuda").bfloat16()
+        b = torch.randn(N, K, device="cuda").bfloat16()
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        ms = t(lambda: gemm.gemm(a, b, out=out))
+        ms_ref = t(lambda: torch.matmul(a, b.t(), out=out))
+        _emit("gemm_bf16", dict(M=M, N=N, K=K), ms, flops=2.0 * M * N * K, cublas_ms=round(ms_ref, 4))
+
+
+def bench_gemm_fp8(t: Timer, sizes) -> None:
+    from . import fp8
+
+    for M, N, K in sizes:
+        a = torch.randn(M, K, device="cuda").bfloat16()
+        b = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
+        a8, sa = fp8.quantize_rowwise(a)
+        b8, sb = fp8.quantize_block(b)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        ms = t(lambda: fp8.gemm_fp8(a8, sa, b8, sb, out=out))
+        msq = t(lambda: fp8.quantize_rowwise(a))
+        _emit("gemm_fp8_block", dict(M=M, N=N, K=K), ms, flops=2.0 * M * N * K, quant_rowwise_ms=round(msq, 4),
+              quant_gbs=round(M * K * 3 / msq / 1e6, 1))
+
+
+def bench_attention(t: Timer, cases) -> None:
+    from . import attention as A
+
+    for T, Hq, Hk, hd in cases:
+        qkv = torch.randn(1, T, (Hq + 2 * Hk) * hd, device="cuda").bfloat16().requires_grad_(True)
+        ds = A.build_doc_start(1, T, qkv.device, None, None)
+        flops_f = 4.0 * T * T * Hq * hd / 2   # causal: half of the score matrix
+        out = A.qkv_attention(qkv, n_head=Hq, n_kv_head=Hk, head_dim=hd, doc_start=ds)
+        dout = torch.randn_like(out)
+        ms_f = t(lambda: A.qkv_attention(qkv.detach(), n_head=Hq, n_kv_head=Hk, head_dim=hd, doc_start=ds))
+        _emit("attention_fwd", dict(T=T, Hq=Hq, Hk=Hk, hd=hd), ms_f, flops=flops_f)
+
+        def fb():
+            qkv.grad = None
+            o = A.qkv_attention(qkv, n_head=Hq, n_kv_head=Hk, head_dim=hd, doc_start=ds)
+            o.backward(dout)
+
+        ms_fb = t(fb)
+        _emit("attention_fwd_bwd", dict(T=T, Hq=Hq, Hk=Hk, hd=hd), ms_fb, flops=flops_f * 3.5)
+
+
+def bench_decode(t: Timer, cases) -> None:
+    from . import decode as D
+
+    for B, T, Hq, Hk, hd in cases:
+        kc = torch.randn(B, Hk, T, hd, device="cuda").bfloat16().permute(0, 2, 1, 3)   # head-major storage
+        vc = torch.randn(B, Hk, T, hd, device="cuda").bfloat16().permute(0, 2, 1, 3)
+        qkv = torch.randn(B, (Hq + 2 * Hk) * hd, device="cuda").bfloat16()
+        q = qkv[:, : Hq * hd].unflatten(1, (Hq, hd))
+        kn = qkv[:, Hq * hd:(Hq + Hk) * hd].unflatten(1, (Hk, hd))
+        vn = qkv[:, (Hq + Hk) * hd:].unflatten(1, (Hk, hd))
+        lens = torch.full((B,), T, dtype=torch.int32, device="cuda")
+        ctas = B * Hk
+        splits = max(1, min(32, (12 * 148 + ctas - 1) // ctas, (T + 127) // 128))
+        ws: dict = {}
+        ms = t(lambda: D.decode_attention(q, kn, vn, kc, vc, lens, n_splits=splits, workspace=ws))
+        _emit("decode_attention", dict(B=B, T=T, Hq=Hq, Hk=Hk, hd=hd, splits=splits), ms, bytes_=2.0 * B * T * Hk * hd * 2)
+
+
+def bench_sampler(t: Timer, cases) -> None:
+    from . import decode as D
+
+    for B, V in cases:
+        logits = torch.randn(B, V, device="cuda")
+        for kw in (dict(), dict(top_k=50), dict(top_p=0.9)):
+            ms = t(lambda: D.sample(logits, temperature=1.0, seed=1, offset=0, **kw))
+            ms_ref = t(lambda: D.sample_ref(logits, 1.0, kw.get("top_k"), kw.get("top_p")))
+            _emit("sampler", dict(B=B, V=V, **kw), ms, bytes_=4.0 * B * V, torch_ms=round(ms_ref, 4))
+
+
+def bench_tp(op: str, t: Timer, cases) -> None:
+    """All-gather + GEMM and GEMM + reduce-scatter against NCCL collective followed by / following the plain GEMM."""
+    import torch.distributed as dist
+
+    from ..parallel import tp as T
+    from . import gemm
+
+    rank = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl")
+    world = dist.get_world_size()
+    state = T.TPState(dist.group.WORLD, torch.device("cuda", rank), sequence_parallel=True)
+    for M, N, K in cases:
+        rows = M // world
+        if op == "tp_ag_gemm":
+            x = torch.randn(rows, K, device="cuda").bfloat16()
+            w = torch.randn(N, K, device="cuda").bfloat16()
+            fused = lambda: T.ag_gemm(state, x, w)  # noqa: E731
+
+            def base():
+                xf = T.all_gather_rows(state, x)
+                return gemm.gemm(xf, w)
+        else:
+            x = torch.randn(M, K, device="cuda").bfloat16()
+            w = torch.randn(N, K, device="cuda").bfloat16()
+            fused = lambda: T.gemm_rs(state, x, w)  # noqa: E731
+
+            def base():
+                return T.reduce_scatter_rows(state, gemm.gemm(x, w))
+
+        x_plain = x if op != "tp_ag_gemm" else torch.randn(M, K, device="cuda").bfloat16()
+
+        def stream_time(fn, reps: int = 10) -> float:
+            """Per-call milliseconds of ``reps`` calls issued back to back: ranks stay in lockstep through the
+            collectives themselves, so host-side launch skew between the processes is not part of the number.
+            Operands and outputs of consecutive calls (> 126 MB together) do not fit in L2."""
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            dist.barrier()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(reps):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / reps
+
+        ms_plain = stream_time(lambda: gemm.gemm(x_plain, w))
+        vals = torch.tensor([stream_time(fused), stream_time(base), ms_plain], device="cuda")
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+        if dist.get_rank() == 0:
+            link_bytes = (world - 1) / world * M * (K if op == "tp_ag_gemm" else N) * 2
+            roof_ms = max(2.0 * M * N * K / (_peaks().get("bf16_tflops", 1590.0) * 1e9), link_bytes / 770e6)
+            _emit(op, dict(M=M, N=N, K=K, world=world), float(vals[0]), flops=2.0 * M * N * K,
+                  nccl_then_gemm_ms=round(float(vals[1]), 4), gemm_only_ms=round(float(vals[2]), 4),
+                  roofline_ms=round(roof_ms, 4), of_roofline=round(roof_ms / float(vals[0]), 3))
+    torch.cuda.synchronize()
+    _ = state
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", required=True, choices=["gemm_bf16", "gemm_fp8", "attention", "decode", "sampler",
+                                                    "tp_ag_gemm", "tp_gemm_rs"])
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--small", action="store_true", help="one small case (for profiler captures)")
+    args = ap.parse_args()
+    t = Timer(args.iters)
+    if args.op == "gemm_bf16":
+        bench_gemm_bf16(t, [(4096, 4096, 4096)] if args.small else [(8192, 8192, 8192), (8192, 6144, 4096), (8192, 4096, 14336),
+                                                                    (8192, 28672, 4096)])
+    elif args.op == "gemm_fp8":
+        bench_gemm_fp8(t, [(4096, 4096, 4096)] if args.small else [(8192, 8192, 8192), (8192, 6144, 4096), (8192, 4096, 14336),
+                                                                   (8192, 28672, 4096)])
+    elif args.op == "attention":
+        bench_attention(t, [(4096, 8, 2, 128)] if args.small else [(8192, 32, 8, 128), (16384, 40, 8, 128)])
+    elif args.op == "decode":
+        bench_decode(t, [(64, 768, 16, 8, 128)] if args.small else [(64, 768, 16, 8, 128), (512, 768, 16, 8, 128),
+                                                                     (1, 8192, 32, 8, 128), (8, 4096, 32, 8, 128)])
+    elif args.op == "sampler":
+        bench_sampler(t, [(64, 151936)] if args.small else [(64, 151936), (512, 151936)])
+    else:
+        bench_tp(args.op, t, [(8192, 6144, 4096), (16384, 5120, 17408 // 2), (16384, 17408 // 2, 5120)])
+
+
+if __name__ == "__main__":
+    main()

@@ -2,7 +2,8 @@
 //
 //   q        [B, Hq, HD]     bf16, row stride q_stride (it usually lives inside the fused qkv row)
 //   k_new    [B, Hk, HD]     bf16, the current token's key (already normalised / rotated); v_new alike
-//   k_cache  [B, Tmax, Hk, HD] bf16 (v_cache alike); sequence b holds seq_lens[b] tokens *including*
+//   k_cache  logical [B, Tmax, Hk, HD] bf16 with arbitrary batch / token / head strides (v_cache alike;
+//            a head-major allocation gives every CTA one contiguous stream); sequence b holds seq_lens[b] tokens *including*
 //            the current one, whose row (seq_lens[b] - 1) this kernel writes before it attends
 //   out      [B, Hq, HD]     bf16
 //
@@ -54,10 +55,10 @@ __device__ __forceinline__ void load_tile(Smem<HD>& sm, int buf, const __nv_bflo
 }
 
 template <int HD>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 3)
 decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, const __nv_bfloat16* __restrict__ k_new,
               const __nv_bfloat16* __restrict__ v_new, long long new_stride, __nv_bfloat16* __restrict__ k_cache,
-              __nv_bfloat16* __restrict__ v_cache, long long batch_stride, long long tok_stride,
+              __nv_bfloat16* __restrict__ v_cache, long long batch_stride, long long tok_stride, long long head_stride,
               const int* __restrict__ seq_lens, __nv_bfloat16* __restrict__ out, long long out_stride,
               float* __restrict__ part_o, float* __restrict__ part_ml, int Hq, int Hk, int n_splits, int t_max,
               float scale_log2, int window) {
@@ -69,8 +70,8 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, const __n
   int len = seq_lens[b];
   if (len > t_max) len = t_max;
   if (len < 0) len = 0;  // an empty sequence still writes zeros / empty partials
-  __nv_bfloat16* kc = k_cache + (long long)b * batch_stride + (long long)hk * HD;
-  __nv_bfloat16* vc = v_cache + (long long)b * batch_stride + (long long)hk * HD;
+  __nv_bfloat16* kc = k_cache + (long long)b * batch_stride + (long long)hk * head_stride;
+  __nv_bfloat16* vc = v_cache + (long long)b * batch_stride + (long long)hk * head_stride;
   const int start = (window > 0 && len > window) ? len - window : 0;
   const int span = len - start;
   const int per = ((span + n_splits - 1) / n_splits + TILE - 1) / TILE * TILE;
@@ -116,7 +117,8 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, const __n
       const int r = item / TILE, t = item - r * TILE;
       float dot = -INFINITY;
       if (t < valid) {
-        dot = 0.f;
+        // four independent partial sums: one serial chain of 128 dependent FMAs would cost more than the loads
+        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
         const uint4* krow = reinterpret_cast<const uint4*>(&sm.k[buf][t][0]);
         const float4* qrow = reinterpret_cast<const float4*>(&sm.q[r][0]);
 #pragma unroll
@@ -124,8 +126,10 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, const __n
           const uint4 kk = krow[c];
           const float4 qa = qrow[2 * c], qb = qrow[2 * c + 1];
           const float2 k0 = unpack_bf16x2(kk.x), k1 = unpack_bf16x2(kk.y), k2 = unpack_bf16x2(kk.z), k3 = unpack_bf16x2(kk.w);
-          dot += qa.x * k0.x + qa.y * k0.y + qa.z * k1.x + qa.w * k1.y + qb.x * k2.x + qb.y * k2.y + qb.z * k3.x + qb.w * k3.y;
+          d0 = fmaf(qa.x, k0.x, d0); d1 = fmaf(qa.y, k0.y, d1); d2 = fmaf(qa.z, k1.x, d2); d3 = fmaf(qa.w, k1.y, d3);
+          d0 = fmaf(qb.x, k2.x, d0); d1 = fmaf(qb.y, k2.y, d1); d2 = fmaf(qb.z, k3.x, d2); d3 = fmaf(qb.w, k3.y, d3);
         }
+        dot = (d0 + d1) + (d2 + d3);
       }
       sm.s[r][t] = dot;
     }
@@ -154,11 +158,26 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, const __n
 #pragma unroll
     for (int r = 0; r < MAX_REP; ++r)
       if (r < n_rep) acc[r] *= sm.alpha[r];
-    for (int t = sub; t < valid; t += SUB) {
-      const float vv = __bfloat162float(sm.v[buf][t][d]);
+    {
+      // positions in groups of four: the probabilities come as one float4 (broadcast) per query head,
+      // and the four products per head are summed as a tree before they join the accumulator
+      const int t_end4 = (SUB == 1) ? (valid & ~3) : 0;
+      for (int t = 0; t < t_end4; t += 4) {
+        const float v0 = __bfloat162float(sm.v[buf][t][d]), v1 = __bfloat162float(sm.v[buf][t + 1][d]);
+        const float v2 = __bfloat162float(sm.v[buf][t + 2][d]), v3 = __bfloat162float(sm.v[buf][t + 3][d]);
 #pragma unroll
-      for (int r = 0; r < MAX_REP; ++r)
-        if (r < n_rep) acc[r] += sm.s[r][t] * vv;
+        for (int r = 0; r < MAX_REP; ++r)
+          if (r < n_rep) {
+            const float4 p4 = *reinterpret_cast<const float4*>(&sm.s[r][t]);
+            acc[r] += (p4.x * v0 + p4.y * v1) + (p4.z * v2 + p4.w * v3);
+          }
+      }
+      for (int t = t_end4 + sub; t < valid; t += SUB) {
+        const float vv = __bfloat162float(sm.v[buf][t][d]);
+#pragma unroll
+        for (int r = 0; r < MAX_REP; ++r)
+          if (r < n_rep) acc[r] += sm.s[r][t] * vv;
+      }
     }
     __syncthreads();
   }
@@ -213,8 +232,8 @@ combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_
 
 template <int HD>
 static int launch(const void* q, long long q_stride, const void* k_new, const void* v_new, long long new_stride,
-                  void* k_cache, void* v_cache, long long batch_stride, long long tok_stride, const int* seq_lens,
-                  void* out, long long out_stride, float* part_o, float* part_ml, int B, int Hq, int Hk, int n_splits,
+                  void* k_cache, void* v_cache, long long batch_stride, long long tok_stride, long long head_stride,
+                  const int* seq_lens, void* out, long long out_stride, float* part_o, float* part_ml, int B, int Hq, int Hk, int n_splits,
                   int t_max, float scale, int window, cudaStream_t stream) {
   auto kern = decode_kernel<HD>;
   static bool configured = false;
@@ -226,7 +245,7 @@ static int launch(const void* q, long long q_stride, const void* k_new, const vo
   dim3 grid(Hk, B, n_splits);
   kern<<<grid, THREADS, smem, stream>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_new,
                                         (const __nv_bfloat16*)v_new, new_stride, (__nv_bfloat16*)k_cache,
-                                        (__nv_bfloat16*)v_cache, batch_stride, tok_stride, seq_lens,
+                                        (__nv_bfloat16*)v_cache, batch_stride, tok_stride, head_stride, seq_lens,
                                         (__nv_bfloat16*)out, out_stride, part_o, part_ml, Hq, Hk, n_splits, t_max,
                                         scale * 1.4426950408889634f, window);
   int rc = (int)cudaGetLastError();
@@ -242,19 +261,19 @@ static int launch(const void* q, long long q_stride, const void* k_new, const vo
 // k_new / v_new may be null when the cache already holds the current token.
 extern "C" int ob_attn_decode(const void* q, long long q_stride, const void* k_new, const void* v_new,
                               long long new_stride, void* k_cache, void* v_cache, long long batch_stride,
-                              long long tok_stride, const void* seq_lens, void* out, long long out_stride,
+                              long long tok_stride, long long head_stride, const void* seq_lens, void* out, long long out_stride,
                               void* part_o, void* part_ml, int B, int Hq, int Hk, int hd, int n_splits, int t_max,
                               float scale, int window, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (Hk <= 0 || Hq % Hk != 0 || Hq / Hk > ob::decode::MAX_REP || n_splits < 1) return -1;
   if (n_splits > 1 && (part_o == nullptr || part_ml == nullptr)) return -2;
-  if ((q_stride | new_stride | batch_stride | tok_stride | out_stride) % 8 != 0) return -3;
+  if ((q_stride | new_stride | batch_stride | tok_stride | head_stride | out_stride) % 8 != 0) return -3;
   if (hd == 128)
-    return ob::decode::launch<128>(q, q_stride, k_new, v_new, new_stride, k_cache, v_cache, batch_stride, tok_stride,
+    return ob::decode::launch<128>(q, q_stride, k_new, v_new, new_stride, k_cache, v_cache, batch_stride, tok_stride, head_stride,
                                    (const int*)seq_lens, out, out_stride, (float*)part_o, (float*)part_ml, B, Hq, Hk,
                                    n_splits, t_max, scale, window, stream);
   if (hd == 64)
-    return ob::decode::launch<64>(q, q_stride, k_new, v_new, new_stride, k_cache, v_cache, batch_stride, tok_stride,
+    return ob::decode::launch<64>(q, q_stride, k_new, v_new, new_stride, k_cache, v_cache, batch_stride, tok_stride, head_stride,
                                   (const int*)seq_lens, out, out_stride, (float*)part_o, (float*)part_ml, B, Hq, Hk,
                                   n_splits, t_max, scale, window, stream);
   return -4;

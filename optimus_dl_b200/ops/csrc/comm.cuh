@@ -35,7 +35,9 @@ __device__ __forceinline__ uint4 ld_peer_16(const void* p) {
   return v;
 }
 
-// Executed by a whole CTA: copy tasks [first, n) with stride `stride`.
+// Executed by a whole CTA: copy tasks [first, n) with stride `stride`.  UNROLL 16-byte loads per thread are
+// issued before the first store, i.e. blockDim.x * UNROLL * 16 bytes are in flight per CTA.
+template <int UNROLL = 8>
 __device__ __forceinline__ void run_copy_tasks(const CopyTask* tasks, int n_tasks, int first, int stride,
                                                const PeerPtrs& src, __nv_bfloat16* dst, int* flags, int epoch) {
   for (int t = first; t < n_tasks; t += stride) {
@@ -43,7 +45,6 @@ __device__ __forceinline__ void run_copy_tasks(const CopyTask* tasks, int n_task
     const __nv_bfloat16* s = reinterpret_cast<const __nv_bfloat16*>(src.p[task.peer]) + task.offset;
     __nv_bfloat16* d = dst + task.offset;
     const int nvec = (task.offset % 8 == 0) ? task.numel / 8 : 0;
-    constexpr int UNROLL = 8;
     int i = threadIdx.x;
     for (; i + (UNROLL - 1) * (int)blockDim.x < nvec; i += UNROLL * blockDim.x) {
       uint4 v[UNROLL];

@@ -28,7 +28,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                int* flags, int epoch, int n_copy) {
   extern __shared__ uint8_t smem_raw[];
   if ((int)blockIdx.x < n_copy) {
-    comm::run_copy_tasks(tasks, n_tasks, blockIdx.x, n_copy, src, dst, flags, epoch);
+    comm::run_copy_tasks<16>(tasks, n_tasks, blockIdx.x, n_copy, src, dst, flags, epoch);
     return;
   }
   if (threadIdx.x >= NUM_THREADS) return;  // spare warps of a GEMM CTA

@@ -30,7 +30,11 @@ constexpr int NUM_THREADS = 192;
 constexpr int A_TILE_BYTES = BM * BK * 2;   // 16 KB
 constexpr int B_TILE_BYTES = BN * BK * 2;   // 32 KB
 constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+// Reduce-scatter epilogue: each epilogue warp stages 32 rows x 64 bf16 columns (rows padded to 144 bytes,
+// conflict-free for 16-byte accesses) so that peer stores leave as 128-byte row segments.
+constexpr int RS_ROW_ELEMS = 72;
+constexpr int RS_STAGE_BYTES = 4 * 32 * RS_ROW_ELEMS * 2;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + RS_STAGE_BYTES;
 constexpr int GROUP_M = 16;
 
 enum Act : int { kActNone = 0, kActGelu = 1, kActRelu2 = 2, kActSilu = 3 };
@@ -140,6 +144,7 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap* tmA, const CUtensorM
   uint64_t* acc_empty = bars + 2 * STAGES + ACC_STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * ACC_STAGES);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  __nv_bfloat16* rs_stage_base = reinterpret_cast<__nv_bfloat16*>(smem + STAGES * STAGE_BYTES + 256);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -355,10 +360,20 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap* tmA, const CUtensorM
               // with `accumulate` the addend is always read from the local C, also in reduce-scatter mode
               const __nv_bfloat16* srow = crow;
               if (p.rs_rows > 0) {
-                const int owner = row / p.rs_rows;
-                crow = reinterpret_cast<__nv_bfloat16*>(p.rs_dst[owner]) +
-                       ((long long)p.rs_me * p.rs_rows + (row - owner * p.rs_rows)) * p.ldc + col;
-              }
+                // reduce-scatter mode: park the 32 columns in this warp's staging rows; the flush below
+                // (outside the row guard, all lanes take part) sends them as 128-byte segments
+                if (p.accumulate) {
+#pragma unroll
+                  for (int j = 0; j < 32; ++j)
+                    if (col + j < p.N) v[j] += __bfloat162float(srow[j]);
+                }
+                __nv_bfloat16* st = rs_stage_base + ((warp & 3) * 32 + lane) * RS_ROW_ELEMS + ((c >> 5) & 1) * 32;
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                  *reinterpret_cast<uint4*>(st + 8 * q) =
+                      make_uint4(pack_bf16x2(v[8 * q], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
+                                 pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+              } else
               if (vec_ok && col + 32 <= p.N) {
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
@@ -379,6 +394,24 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap* tmA, const CUtensorM
                     crow[j] = __float2bfloat16(p.accumulate ? __bfloat162float(srow[j]) + v[j] : v[j]);
               }
             }
+          }
+          if (p.rs_rows > 0 && (((c >> 5) & 1) == 1 || c + 32 >= BN || n0 + c + 32 >= p.N)) {
+            __syncwarp();
+            const __nv_bfloat16* stw = rs_stage_base + (warp & 3) * 32 * RS_ROW_ELEMS;
+            const int seg = lane & 7;
+            const int colg = n0 + (c & ~63) + seg * 8;
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              const int rr = it * 4 + (lane >> 3);
+              const int rowg = m0 + quarter * 32 + rr;
+              if (rowg < p.M && colg < p.N && (colg < n0 + c + 32)) {
+                const int owner = rowg / p.rs_rows;
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.rs_dst[owner]) +
+                                     ((long long)p.rs_me * p.rs_rows + (rowg - owner * p.rs_rows)) * p.ldc + colg;
+                *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(stw + rr * RS_ROW_ELEMS + seg * 8);
+              }
+            }
+            __syncwarp();
           }
         }
       }

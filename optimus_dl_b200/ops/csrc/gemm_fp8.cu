@@ -10,11 +10,12 @@
 // Each k-block is one 128-byte swizzle atom of e4m3, i.e. four tcgen05.mma.kind::f8f6f4
 // instructions of K = 32.  Because every k-block has its own scale, the tensor core never
 // accumulates across k-blocks: the MMA warp writes each k-block's 128 x 256 partial product into one
-// of two TMEM slots, and eight epilogue warps (two per TMEM lane quarter, 128 columns each) pull
+// of two TMEM slots, and sixteen epilogue warps (four per TMEM lane quarter, 64 columns each) pull
 // the partial out with tcgen05.ld, scale it and add it to fp32 accumulators held in registers while
-// the tensor core already works on the next k-block in the other slot.
+// the tensor core already works on the next k-block in the other slot.  The drain is a chain of
+// TMEM-load latencies per warp, so it is spread over many warps to keep it shorter than the MMAs.
 //
-// Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer / TMEM owner, warps 2..9 epilogue.
+// Warp roles (576 threads): warp 0 TMA producer, warp 1 MMA issuer / TMEM owner, warps 2..17 epilogue.
 #include <cuda_fp8.h>
 
 #include "common.cuh"
@@ -29,8 +30,9 @@ constexpr int BK = 128;       // one scale block = one swizzle atom of 8-bit ele
 constexpr int UMMA_K = 32;
 constexpr int STAGES = 4;
 constexpr int SLOTS = 2;
-constexpr int NUM_THREADS = 320;
-constexpr int EPI_WARPS = 8;
+constexpr int EPI_WARPS = 16;     // four per TMEM lane quarter, 64 columns each
+constexpr int NUM_THREADS = 64 + EPI_WARPS * 32;
+constexpr int EPI_COLS = BN / (EPI_WARPS / 4);
 constexpr int A_TILE_BYTES = BM * BK;
 constexpr int B_TILE_BYTES = BN * BK;
 constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
@@ -145,9 +147,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
     }
   } else {
-    const int e = warp - 2;                 // 0..7
+    const int e = warp - 2;                 // 0..EPI_WARPS-1
     const int quarter = warp & 3;           // TMEM lane quarter this warp may read
-    const int half = e >> 2;                // which 128 columns of the 256-wide tile
+    const int chunk = e >> 2;               // which EPI_COLS columns of the 256-wide tile
     int slot = 0; uint32_t slot_phase = 0;
     bool ok = true;
     const int sb_ld = k_blocks;
@@ -155,22 +157,28 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       int tm, tn;
       tile_of(tile, tiles_m, tiles_n, tm, tn);
       const int row = tm * BM + quarter * 32 + lane;
-      const int col0 = tn * BN + half * 128;
+      const int col0 = tn * BN + chunk * EPI_COLS;
       const bool row_ok = row < p.M;
       const bool cols_ok = col0 < p.N;
       const float* sa_row = p.sa + (row_ok ? row : 0);
       const float* sb_row = p.sb + (long long)(cols_ok ? col0 / 128 : 0) * sb_ld;
-      float acc[128];
+      float acc[EPI_COLS];
 #pragma unroll
-      for (int j = 0; j < 128; ++j) acc[j] = 0.f;
+      for (int j = 0; j < EPI_COLS; ++j) acc[j] = 0.f;
+      // scales are fetched two k-blocks ahead: their global-load latency must not sit between the barrier
+      // and the first use
+      float sa0 = sa_row[0], sb0 = sb_row[0];
+      float sa1 = k_blocks > 1 ? sa_row[p.sa_ld] : 0.f, sb1 = k_blocks > 1 ? sb_row[1] : 0.f;
       for (int kb = 0; kb < k_blocks; ++kb) {
-        const float s = sa_row[(long long)kb * p.sa_ld] * sb_row[kb];
+        const float s = sa0 * sb0;
+        sa0 = sa1; sb0 = sb1;
+        if (kb + 2 < k_blocks) { sa1 = sa_row[(long long)(kb + 2) * p.sa_ld]; sb1 = sb_row[kb + 2]; }
         ok = mbar_wait(&part_full[slot], slot_phase, abort_flag, p.status);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + slot * BN + half * 128;
+        const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + slot * BN + chunk * EPI_COLS;
 #pragma unroll
-        for (int c = 0; c < 128; c += 16) {
+        for (int c = 0; c < EPI_COLS; c += 16) {
           uint32_t r[16];
           tmem_ld_32x16(t_row + c, r);
           tmem_ld_wait();
@@ -185,17 +193,17 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       if (!ok) break;
       if (row_ok && cols_ok) {
         __nv_bfloat16* crow = p.C + (long long)row * p.ldc + col0;
-        const bool vec = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && col0 + 128 <= p.N;
+        const bool vec = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && col0 + EPI_COLS <= p.N;
         if (vec) {
 #pragma unroll
-          for (int q = 0; q < 16; ++q) {
+          for (int q = 0; q < EPI_COLS / 8; ++q) {
             uint4 o = make_uint4(pack_bf16x2(acc[8 * q], acc[8 * q + 1]), pack_bf16x2(acc[8 * q + 2], acc[8 * q + 3]),
                                  pack_bf16x2(acc[8 * q + 4], acc[8 * q + 5]), pack_bf16x2(acc[8 * q + 6], acc[8 * q + 7]));
             *reinterpret_cast<uint4*>(crow + 8 * q) = o;
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < 128; ++j)
+          for (int j = 0; j < EPI_COLS; ++j)
             if (col0 + j < p.N) crow[j] = __float2bfloat16(acc[j]);
         }
       }

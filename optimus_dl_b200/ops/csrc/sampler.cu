@@ -3,9 +3,10 @@
 // One CTA per row of logits [B, V].  Nothing is sorted and no probability vector is written:
 //   * top-k: radix select (4 passes of 8 bits over order-preserving keys) finds the k-th largest
 //     scaled logit; everything >= it is kept (ties are kept, like a `logits < kth` mask);
-//   * top-p: the same radix descent over probability *mass* finds the value at which the
-//     cumulative mass of larger elements first exceeds top_p (an element is kept iff the mass of
-//     strictly larger elements is <= top_p, the usual shifted nucleus rule);
+//   * top-p: an element is in the nucleus iff the mass of strictly larger elements is <= top_p (the
+//     usual shifted rule).  The kernel draws from the candidates, tests that condition for the draw
+//     with one summation pass, and on failure discards everything at or below the draw and repeats
+//     (rejection sampling; the accepted draw is an exact sample of the renormalised nucleus);
 //   * the draw is arg max (z_i + Gumbel_i) over the kept set, which is an exact sample from
 //     softmax(z) restricted to that set; the noise is a counter-based hash of (seed, offset, row, i).
 // With neither top-k nor top-p the whole thing is a single pass over the row.
@@ -73,15 +74,34 @@ __device__ ArgMax block_argmax(ArgMax x, ArgMax* scratch) {
   return scratch[0];
 }
 
+__device__ float block_sum(float v, float* scratch) {
+  v = warp_sum(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int w = 0; w < THREADS / 32; ++w) t += scratch[w];   // same order in every thread
+  return t;
+}
+
+__device__ float block_max(float v, float* scratch) {
+  v = warp_max(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = scratch[0];
+  for (int w = 1; w < THREADS / 32; ++w) t = fmaxf(t, scratch[w]);
+  return t;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(const T* __restrict__ logits, long long row_stride, int V, float inv_temp, int top_k, float top_p,
               int greedy, unsigned long long seed, unsigned long long offset, long long* __restrict__ out) {
   __shared__ ArgMax scratch[THREADS / 32];
   __shared__ uint32_t hist_n[256];
-  __shared__ float hist_m[256];
   __shared__ uint32_t s_prefix, s_k;
-  __shared__ float s_above, s_fscratch[THREADS / 32];
+  __shared__ float s_fscratch[THREADS / 32];
   const int row = blockIdx.x, tid = threadIdx.x;
   const T* z_row = logits + (long long)row * row_stride;
 
@@ -124,54 +144,51 @@ sample_kernel(const T* __restrict__ logits, long long row_stride, int V, float i
     thr_key = prefix;
   }
   if (use_p) {
-    // row maximum and normaliser over the (top-k restricted) candidates
+    // Nucleus sampling by rejection: draw from the current candidates; the draw is inside the nucleus iff
+    // the probability mass of strictly larger candidates is at most top_p.  Otherwise everything at or
+    // below the draw lies outside the nucleus (the nucleus is closed upwards), is removed, and we draw
+    // again.  Every round is two plain passes over the row; no sorting, no histogram.
     float mx = -INFINITY;
     for (int i = tid; i < V; i += THREADS) mx = fmaxf(mx, ldz(z_row, i) * inv_temp);
-    mx = warp_max(mx);
-    if ((tid & 31) == 0) s_fscratch[tid >> 5] = mx;
-    __syncthreads();
-    mx = s_fscratch[0];
-    for (int w = 1; w < THREADS / 32; ++w) mx = fmaxf(mx, s_fscratch[w]);
-    __syncthreads();
+    mx = block_max(mx, s_fscratch);
     float zsum = 0.f;
     for (int i = tid; i < V; i += THREADS) {
       const float z = ldz(z_row, i) * inv_temp;
       if (f2key(z) >= thr_key) zsum += __expf(z - mx);
     }
-    zsum = warp_sum(zsum);
-    if ((tid & 31) == 0) s_fscratch[tid >> 5] = zsum;
-    __syncthreads();
-    zsum = 0.f;
-    for (int w = 0; w < THREADS / 32; ++w) zsum += s_fscratch[w];
-    __syncthreads();
+    zsum = block_sum(zsum, s_fscratch);
     const float target = top_p * zsum;
-    uint32_t prefix = 0, mask = 0;
-    float above = 0.f;  // mass of candidates strictly above the current prefix range
-    for (int shift = 24; shift >= 0; shift -= 8) {
-      for (int i = tid; i < 256; i += THREADS) hist_m[i] = 0.f;
-      __syncthreads();
+    float low = -INFINITY;   // candidates must have z > low
+    int chosen = -1;
+    for (int round = 0; round < 32 && chosen < 0; ++round) {
+      ArgMax cand{-INFINITY, -1};
       for (int i = tid; i < V; i += THREADS) {
         const float z = ldz(z_row, i) * inv_temp;
-        const uint32_t key = f2key(z);
-        if (key >= thr_key && (key & mask) == prefix) atomicAdd(&hist_m[(key >> shift) & 0xFF], __expf(z - mx));
+        if (f2key(z) >= thr_key && z > low)
+          cand = better(cand, ArgMax{z + gumbel(seed + 0x632BE59BD9B4E019ULL * (round + 1), offset, row, i), i});
       }
-      __syncthreads();
-      if (tid == 0) {
-        float cum = above;
-        int bin = 255;
-        for (; bin > 0; --bin) {
-          if (cum + hist_m[bin] > target) break;
-          cum += hist_m[bin];
-        }
-        s_prefix = prefix | ((uint32_t)bin << shift);
-        s_above = cum;
+      cand = block_argmax(cand, scratch);
+      if (cand.i < 0) break;
+      const float zj = ldz(z_row, cand.i) * inv_temp;
+      float above = 0.f;
+      for (int i = tid; i < V; i += THREADS) {
+        const float z = ldz(z_row, i) * inv_temp;
+        if (f2key(z) >= thr_key && z > zj) above += __expf(z - mx);
       }
-      __syncthreads();
-      prefix = s_prefix;
-      above = s_above;
-      mask |= 0xFFu << shift;
+      above = block_sum(above, s_fscratch);
+      if (above <= target) chosen = cand.i;
+      else low = zj;
     }
-    if (prefix > thr_key) thr_key = prefix;
+    if (chosen < 0) {   // numerically empty candidate set: fall back to the most likely candidate
+      ArgMax top{-INFINITY, -1};
+      for (int i = tid; i < V; i += THREADS) {
+        const float z = ldz(z_row, i) * inv_temp;
+        if (f2key(z) >= thr_key) top = better(top, ArgMax{z, i});
+      }
+      chosen = block_argmax(top, scratch).i;
+    }
+    if (tid == 0) out[row] = chosen;
+    return;
   }
   ArgMax best{-INFINITY, -1};
   for (int i = tid; i < V; i += THREADS) {

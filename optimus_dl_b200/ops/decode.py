@@ -28,7 +28,8 @@ def decode_attention(q: torch.Tensor, k_new: torch.Tensor | None, v_new: torch.T
 
     ``q``: ``[B, Hq, hd]`` (may be a strided view into a fused qkv row); ``k_new``/``v_new``:
     ``[B, Hk, hd]`` of the current token, stored at row ``seq_lens[b] - 1`` of the caches
-    ``[B, Tmax, Hk, hd]`` before attending (pass ``None`` if already stored); ``seq_lens``: int32
+    ``[B, Tmax, Hk, hd]`` (any batch / token / head strides; a head-major allocation viewed this way reads
+    fastest) before attending (pass ``None`` if already stored); ``seq_lens``: int32
     ``[B]``, counts *including* the current token. Returns ``[B, Hq, hd]``.
     """
     B, Hq, hd = q.shape
@@ -36,7 +37,7 @@ def decode_attention(q: torch.Tensor, k_new: torch.Tensor | None, v_new: torch.T
     scale = scale if scale is not None else 1.0 / math.sqrt(hd)
     if (_kernel_ok(q, k_cache, v_cache) and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
             and hd in (64, 128) and Hq // Hk <= 8 and q.stride(2) == 1 and q.stride(1) == hd
-            and k_cache.is_contiguous() and v_cache.is_contiguous()):
+            and k_cache.stride(3) == 1 and v_cache.stride() == k_cache.stride()):
         out = torch.empty((B, Hq, hd), dtype=torch.bfloat16, device=q.device)
         part_o = part_ml = None
         if n_splits > 1:
@@ -53,7 +54,7 @@ def decode_attention(q: torch.Tensor, k_new: torch.Tensor | None, v_new: torch.T
             new_stride = k_new.stride(0)
         rc = _lib.lib().ob_attn_decode(
             _lib.ptr(q), q.stride(0), _lib.ptr(k_new), _lib.ptr(v_new), new_stride, _lib.ptr(k_cache), _lib.ptr(v_cache),
-            k_cache.stride(0), k_cache.stride(1), _lib.ptr(seq_lens), _lib.ptr(out), out.stride(0), _lib.ptr(part_o),
+            k_cache.stride(0), k_cache.stride(1), k_cache.stride(2), _lib.ptr(seq_lens), _lib.ptr(out), out.stride(0), _lib.ptr(part_o),
             _lib.ptr(part_ml), B, Hq, Hk, hd, int(n_splits), Tmax, float(scale), int(window or 0), _lib.stream())
         _lib.check(rc, "ob_attn_decode")
         return out

@@ -113,8 +113,8 @@ class TPState:
         return self._epoch
 
     def gather_tasks(self, rows: int, width: int, flag_rows: int):
-        """Copy tasks that pull every rank's ``rows x width`` slice (own slice first, then the
-        peers in ring order), one task and one flag per ``flag_rows`` rows."""
+        """Copy tasks that pull every other rank's ``rows x width`` slice (peers in ring order starting
+        after this rank), one task and one flag per ``flag_rows`` rows."""
         key = (rows, width, flag_rows)
         hit = self._tasks.get(key)
         if hit is None:
@@ -122,7 +122,7 @@ class TPState:
 
             tasks = []
             per = rows // flag_rows
-            for step in range(self.size):
+            for step in range(1, self.size):   # the own slice is copied locally by the caller
                 peer = (self.rank + step) % self.size
                 for j in range(per):
                     row0 = peer * rows + j * flag_rows
@@ -195,6 +195,9 @@ def ag_gemm(tp: TPState, x_local: torch.Tensor, w: torch.Tensor, w2: torch.Tenso
     flags = tp.flags(M // fr + 1)
     epoch = tp.next_epoch()
     x_full = torch.empty((M, K), dtype=torch.bfloat16, device=x_local.device)
+    # this rank's rows are in place (and flagged) before the kernel starts: its first tiles never wait
+    x_full[tp.rank * rows:(tp.rank + 1) * rows].copy_(x_local)
+    flags[(tp.rank * rows) // fr:((tp.rank + 1) * rows + fr - 1) // fr].fill_(epoch)
     y = torch.empty((M, N), dtype=torch.bfloat16, device=x_local.device)
     g = u = None
     if w2 is not None and save_gu:

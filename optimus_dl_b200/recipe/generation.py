@@ -91,12 +91,14 @@ class DecodeSession:
         sms = 148
         a0 = self.attn[0]
         ctas = max(1, batch * a0.n_kv_head)
-        self.n_splits = 1 if ctas >= sms else max(1, min(32, (2 * sms) // ctas, (max_len + 255) // 256))
+        # enough CTAs for about four full waves (three resident per SM), but at least two 64-token tiles per split
+        self.n_splits = max(1, min(32, (12 * sms + ctas - 1) // ctas, (max_len + 127) // 128))
         self.layers = []
         for a in self.attn:
-            shape = (batch, max_len, a.n_kv_head, a.head_dim)
-            self.layers.append(LayerKV(self, torch.zeros(shape, dtype=self.dtype, device=self.device),
-                                       torch.zeros(shape, dtype=self.dtype, device=self.device)))
+            # stored head-major ([B, Hk, T, hd]: one contiguous stream per (sequence, head)), used as [B, T, Hk, hd]
+            shape = (batch, a.n_kv_head, max_len, a.head_dim)
+            self.layers.append(LayerKV(self, torch.zeros(shape, dtype=self.dtype, device=self.device).permute(0, 2, 1, 3),
+                                       torch.zeros(shape, dtype=self.dtype, device=self.device).permute(0, 2, 1, 3)))
         self._graph = None
         self._static_ids = None
         self._static_pos = None
