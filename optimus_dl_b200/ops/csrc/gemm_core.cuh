@@ -107,13 +107,26 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int tiles_m, int tiles
   return c;
 }
 
+#ifndef OB_FLAG_WAIT_NS
+#define OB_FLAG_WAIT_NS 2000000000ULL   // a flag that is not set within two seconds is reported, not waited for
+#endif
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait for `*flag >= value`.  On expiry (or when another role of the CTA already gave up) returns false
+// after raising the CTA's abort flag and recording kStatusFlagTimeout; the caller unwinds normally.
 __device__ __forceinline__ bool wait_flag(const int* flag, int value, volatile int* abort_flag, int* status) {
-  for (uint32_t it = 0; it < (1u << 26); ++it) {
+  const unsigned long long t0 = global_ns();
+  for (uint32_t it = 0;; ++it) {
     int v;
     asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
     if (v >= value) return true;
     if ((it & 0x3f) == 0x3f) {
       if (*abort_flag) return false;
+      if (global_ns() - t0 > OB_FLAG_WAIT_NS) break;
       __nanosleep(64);
     }
   }

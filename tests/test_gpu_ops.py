@@ -209,3 +209,32 @@ def test_rope_kernel_matches_reference(hd, norm):
     qr, kr = rope.apply_rotary_emb(q, k, freqs, pos.long().view(1, T))
     _close(out[:, : Hq * hd].view(1, T, Hq, hd), qr, 2e-2, 2e-2, "q")
     _close(out[:, Hq * hd: (Hq + Hk) * hd].view(1, T, Hk, hd), kr, 2e-2, 2e-2, "k")
+
+
+def test_flag_wait_times_out():
+    """A GEMM whose operand flags nobody sets must give up after its bounded wait, report it through the status
+    word and leave the context usable (no trap, no hang)."""
+    import time
+
+    from optimus_dl_b200.ops import _lib, gemm
+
+    dev = torch.device("cuda")
+    a = torch.randn(128, 128, device=dev).bfloat16()
+    b = torch.randn(256, 128, device=dev).bfloat16()
+    flags = torch.zeros(4, dtype=torch.int32, device=dev)
+    torch.cuda.synchronize()
+    t0 = time.time()
+    gemm.gemm(a, b, b_flags=flags, flag_rows=128, flag_value=1, tile_order=1)
+    torch.cuda.synchronize()
+    waited = time.time() - t0
+    assert 1.0 < waited < 20.0, waited
+    with pytest.raises(_lib.KernelError, match="flag wait timed out"):
+        _lib.check_status(dev)
+    _lib.check_status(dev)   # the status word was cleared by the report
+    # the same operation with the flags set completes and is correct
+    flags.fill_(1)
+    out = gemm.gemm(a, b, b_flags=flags, flag_rows=128, flag_value=1, tile_order=1)
+    torch.cuda.synchronize()
+    _lib.check_status(dev)
+    ref = a.float() @ b.float().t()
+    assert (out.float() - ref).abs().max().item() < 0.05 * ref.abs().max().item()
