@@ -94,6 +94,8 @@ def main() -> None:
     ap.add_argument("--seq-len", type=int, default=None)
     ap.add_argument("--micro-batch", type=int, default=1)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--timeline", default=None, help="write a per-launcher device-time breakdown of one extra step "
+                                                       "(JSON lines) to this file")
     ap.add_argument("--n-layer", type=int, default=None, help="override the layer count (profiling only; the "
                     "reported metric then says so)")
     args = ap.parse_args()
@@ -204,6 +206,19 @@ def main() -> None:
         e2e = {"value": tokens_per_step * args.steps / (ms2 / 1e3), "unit": "tokens/s",
                "h2d_bytes_per_step": int(host_batches[0].numel() * host_batches.element_size()),
                "d2h_bytes_per_step": 4, "ms_per_step": ms2 / args.steps, "final_loss": last_loss.get("f")}
+    if args.timeline and rank == 0:
+        # one more step with every launcher call bracketed by CUDA events: per-kernel device time of a step
+        # (diagnostics only; the numbers above were measured without it)
+        _lib.timeline_start()
+        step_device(total_steps - 1)
+        report = _lib.timeline_report()
+        total = sum(ms_ for _, ms_ in report.values()) or 1.0
+        rows = sorted(report.items(), key=lambda kv: -kv[1][1])
+        with open(args.timeline, "w") as f:
+            for name, (n, ms_) in rows:
+                f.write(json.dumps({"launcher": name, "calls": n, "ms": round(ms_, 3), "share": round(ms_ / total, 4)}) + "\n")
+    elif args.timeline:
+        step_device(total_steps - 1)   # keep the ranks in lockstep for the collectives of that extra step
     if rank == 0:
         out = {
             "metric": "Llama-3-8B FSDP2 bf16 train tokens/s (device-timed, max/rank)" if (args.model == "llama3-8b" and args.n_layer is None)

@@ -149,6 +149,32 @@ def bench_sampler(t: Timer, cases) -> None:
             _emit("sampler", dict(B=B, V=V, **kw), ms, bytes_=4.0 * B * V, torch_ms=round(ms_ref, 4))
 
 
+def bench_elementwise(t: Timer) -> None:
+    from . import activation as act
+    from . import norm
+
+    M, F, D = 8192, 14336, 4096
+    g = torch.randn(M, F, device="cuda").bfloat16()
+    u = torch.randn(M, F, device="cuda").bfloat16()
+    dh = torch.randn(M, F, device="cuda").bfloat16()
+    ms = t(lambda: act.swiglu_backward(dh, g, u))
+    _emit("swiglu_bwd", dict(rows=M, cols=F), ms, bytes_=5.0 * M * F * 2)
+    x = torch.randn(M, D, device="cuda").bfloat16().requires_grad_(True)
+    w = torch.ones(D, device="cuda").bfloat16().requires_grad_(True)
+    ms = t(lambda: norm.rms_norm(x.detach(), w.detach(), 1e-5))
+    _emit("rmsnorm_fwd", dict(rows=M, D=D), ms, bytes_=2.0 * M * D * 2)
+    y = norm.rms_norm(x, w, 1e-5)
+    dy = torch.randn_like(y)
+
+    def bwd():
+        x.grad = None
+        w.grad = None
+        y.backward(dy, retain_graph=True)
+
+    ms = t(bwd)
+    _emit("rmsnorm_bwd", dict(rows=M, D=D), ms, bytes_=3.0 * M * D * 2)
+
+
 def bench_tp(op: str, t: Timer, cases) -> None:
     """All-gather + GEMM and GEMM + reduce-scatter against NCCL collective followed by / following the plain GEMM."""
     import torch.distributed as dist
@@ -215,7 +241,7 @@ def bench_tp(op: str, t: Timer, cases) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", required=True, choices=["gemm_bf16", "gemm_fp8", "attention", "decode", "sampler",
+    ap.add_argument("--op", required=True, choices=["gemm_bf16", "gemm_fp8", "attention", "decode", "sampler", "elementwise",
                                                     "tp_ag_gemm", "tp_gemm_rs"])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--small", action="store_true", help="one small case (for profiler captures)")
@@ -232,6 +258,8 @@ def main() -> None:
     elif args.op == "decode":
         bench_decode(t, [(64, 768, 16, 8, 128)] if args.small else [(64, 768, 16, 8, 128), (512, 768, 16, 8, 128),
                                                                      (1, 8192, 32, 8, 128), (8, 4096, 32, 8, 128)])
+    elif args.op == "elementwise":
+        bench_elementwise(t)
     elif args.op == "sampler":
         bench_sampler(t, [(64, 151936)] if args.small else [(64, 151936), (512, 151936)])
     else:

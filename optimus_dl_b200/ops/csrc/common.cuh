@@ -69,15 +69,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait. `abort_flag` lives in shared memory and is sticky for the CTA;
 // `status` is a global word the host reads. Returns false if the wait gave up.
-#ifndef OB_MBAR_SPIN_LIMIT
-#define OB_MBAR_SPIN_LIMIT (1u << 24)
-#endif
+#ifndef OB_MBAR_WAIT_NS
+#define OB_MBAR_WAIT_NS 4000000000ULL   // longer than any flag wait (2 s), so that the role that waits on another
+#endif                                  // GPU reports first and the roles behind it merely follow its abort flag
+__device__ __forceinline__ unsigned long long mbar_now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* status) {
   if (mbar_try_wait(bar, parity)) return true;
-  for (uint32_t it = 0; it < OB_MBAR_SPIN_LIMIT; ++it) {
+  const unsigned long long t0 = mbar_now_ns();
+  for (uint32_t it = 0;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 0xff) == 0xff && *abort_flag) return false;
+    if ((it & 0xff) == 0xff) {
+      if (*abort_flag) return false;
+      if (mbar_now_ns() - t0 > OB_MBAR_WAIT_NS) break;
+    }
   }
   *abort_flag = 1;
   if (status) atomicCAS(status, kStatusOk, kStatusMbarTimeout);

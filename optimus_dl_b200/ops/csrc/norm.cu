@@ -108,8 +108,10 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
   }
 }
 
-template <bool LAYERNORM>
-__global__ void __launch_bounds__(THREADS)
+// NVEC = uint4 slots per thread (1, 2 or 4): register arrays are sized for the row width actually used,
+// which decides how many rows an SM keeps in flight.
+template <bool LAYERNORM, int NVEC>
+__global__ void __launch_bounds__(THREADS, NVEC <= 2 ? 3 : 1)
 norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                 const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
                 const float* __restrict__ mean_in, const __nv_bfloat16* __restrict__ dres,
@@ -117,9 +119,9 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
                 int rows, int D) {
   __shared__ float red[THREADS / 32];
   const int nvec = D / 8;
-  float dw_acc[MAX_VEC][8], db_acc[MAX_VEC][8], ww[MAX_VEC][8];
+  float dw_acc[NVEC][8], db_acc[NVEC][8], ww[NVEC][8];
 #pragma unroll
-  for (int i = 0; i < MAX_VEC; ++i) {
+  for (int i = 0; i < NVEC; ++i) {
     const int idx = threadIdx.x + i * THREADS;
 #pragma unroll
     for (int j = 0; j < 8; ++j) { dw_acc[i][j] = 0.f; db_acc[i][j] = 0.f; ww[i][j] = 0.f; }
@@ -134,10 +136,10 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
     const float mean = LAYERNORM ? mean_in[row] : 0.f;
     const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * D);
     const uint4* gr = reinterpret_cast<const uint4*>(dy + (size_t)row * D);
-    float xh[MAX_VEC][8], g[MAX_VEC][8];
+    float xh[NVEC][8], g[NVEC][8];
     float c1 = 0.f, c2 = 0.f;
 #pragma unroll
-    for (int i = 0; i < MAX_VEC; ++i) {
+    for (int i = 0; i < NVEC; ++i) {
       const int idx = threadIdx.x + i * THREADS;
       if (idx < nvec) {
         uint4 xu = xr[idx], gu = gr[idx];
@@ -161,7 +163,7 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
     uint4* dxr = reinterpret_cast<uint4*>(dx + (size_t)row * D);
     const uint4* drr = dres ? reinterpret_cast<const uint4*>(dres + (size_t)row * D) : nullptr;
 #pragma unroll
-    for (int i = 0; i < MAX_VEC; ++i) {
+    for (int i = 0; i < NVEC; ++i) {
       const int idx = threadIdx.x + i * THREADS;
       if (idx < nvec) {
         float o[8];
@@ -180,7 +182,7 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
   float* dwp = dw_partial + (size_t)blockIdx.x * D;
   float* dbp = (LAYERNORM && db_partial) ? db_partial + (size_t)blockIdx.x * D : nullptr;
 #pragma unroll
-  for (int i = 0; i < MAX_VEC; ++i) {
+  for (int i = 0; i < NVEC; ++i) {
     const int idx = threadIdx.x + i * THREADS;
     if (idx < nvec) {
       reinterpret_cast<float4*>(dwp)[idx * 2] = make_float4(dw_acc[i][0], dw_acc[i][1], dw_acc[i][2], dw_acc[i][3]);
@@ -193,16 +195,26 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
   }
 }
 
-// out[c] (+)= sum_p partial[p, c], fixed summation order.
-__global__ void reduce_partials_kernel(const float* __restrict__ partial, int nparts, int D,
-                                       __nv_bfloat16* __restrict__ out_bf16, float* __restrict__ out_f32,
-                                       int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= D) return;
+// out[c] (+)= sum_p partial[p, c], fixed summation order.  A CTA owns 32 columns; its 8 warps each add every
+// eighth partial row (coalesced 128-byte reads), then the 8 sub-sums are added in warp order.
+__global__ void __launch_bounds__(256)
+reduce_partials_kernel(const float* __restrict__ partial, int nparts, int D, __nv_bfloat16* __restrict__ out_bf16,
+                       float* __restrict__ out_f32, int accumulate) {
+  __shared__ float sub[8][32];
+  const int cg = threadIdx.x & 31, rg = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cg;
   float s = 0.f;
-  for (int p = 0; p < nparts; ++p) s += partial[(size_t)p * D + c];
-  if (out_f32) out_f32[c] = accumulate ? out_f32[c] + s : s;
-  if (out_bf16) out_bf16[c] = __float2bfloat16(accumulate ? __bfloat162float(out_bf16[c]) + s : s);
+  if (c < D)
+    for (int p = rg; p < nparts; p += 8) s += partial[(size_t)p * D + c];
+  sub[rg][cg] = s;
+  __syncthreads();
+  if (rg == 0 && c < D) {
+    float t = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) t += sub[r][cg];
+    if (out_f32) out_f32[c] = accumulate ? out_f32[c] + t : t;
+    if (out_bf16) out_bf16[c] = __float2bfloat16(accumulate ? __bfloat162float(out_bf16[c]) + t : t);
+  }
 }
 
 }  // namespace norm
@@ -219,6 +231,13 @@ static int norm_grid(int rows) {
 }
 
 extern "C" int ob_norm_bwd_grid(int rows) { return norm_grid(rows); }
+
+#define OB_NORM_BWD_LAUNCH(LN, D, ...)                                                     \
+  do {                                                                                     \
+    if ((D) <= THREADS * 8) norm_bwd_kernel<LN, 1><<<grid, THREADS, 0, stream>>>(__VA_ARGS__);            \
+    else if ((D) <= THREADS * 16) norm_bwd_kernel<LN, 2><<<grid, THREADS, 0, stream>>>(__VA_ARGS__);      \
+    else norm_bwd_kernel<LN, 4><<<grid, THREADS, 0, stream>>>(__VA_ARGS__);                               \
+  } while (0)
 
 static bool norm_args_ok(int D) { return D % 8 == 0 && D <= THREADS * 8 * MAX_VEC; }
 
@@ -241,11 +260,11 @@ extern "C" int ob_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
   if (!norm_args_ok(D)) return -1;
   if (rows == 0) return 0;
   const int grid = norm_grid(rows);
-  norm_bwd_kernel<false><<<grid, THREADS, 0, stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+  OB_NORM_BWD_LAUNCH(false, D, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
                                                        (const __nv_bfloat16*)w, (const float*)rstd, nullptr,
                                                        (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx,
                                                        (float*)partial, nullptr, rows, D);
-  reduce_partials_kernel<<<(D + 255) / 256, 256, 0, stream>>>((const float*)partial, grid, D, (__nv_bfloat16*)dw_bf16,
+  reduce_partials_kernel<<<(D + 31) / 32, 256, 0, stream>>>((const float*)partial, grid, D, (__nv_bfloat16*)dw_bf16,
                                                               (float*)dw_f32, accumulate);
   return (int)cudaGetLastError();
 }
@@ -269,11 +288,11 @@ extern "C" int ob_layernorm_bwd(const void* dy, const void* x, const void* w, co
   const int grid = norm_grid(rows);
   float* dwp = (float*)partial;
   float* dbp = dwp + (size_t)grid * D;
-  norm_bwd_kernel<true><<<grid, THREADS, 0, stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+  OB_NORM_BWD_LAUNCH(true, D, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
                                                       (const __nv_bfloat16*)w, (const float*)rstd, (const float*)mean,
                                                       nullptr, (__nv_bfloat16*)dx, dwp, dbp, rows, D);
-  reduce_partials_kernel<<<(D + 255) / 256, 256, 0, stream>>>(dwp, grid, D, (__nv_bfloat16*)dw_bf16, nullptr, 0);
-  reduce_partials_kernel<<<(D + 255) / 256, 256, 0, stream>>>(dbp, grid, D, (__nv_bfloat16*)db_bf16, nullptr, 0);
+  reduce_partials_kernel<<<(D + 31) / 32, 256, 0, stream>>>(dwp, grid, D, (__nv_bfloat16*)dw_bf16, nullptr, 0);
+  reduce_partials_kernel<<<(D + 31) / 32, 256, 0, stream>>>(dbp, grid, D, (__nv_bfloat16*)db_bf16, nullptr, 0);
   return (int)cudaGetLastError();
 }
 
@@ -332,9 +351,9 @@ extern "C" int ob_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void*
   const int rc = partials_for_current_device(&partial);
   if (rc != 0) return rc;
   // every CTA overwrites its whole row of partials, so nothing has to be cleared between calls
-  norm_bwd_kernel<false><<<grid, THREADS, 0, stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+  OB_NORM_BWD_LAUNCH(false, D, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
                                                        (const __nv_bfloat16*)w, (const float*)rstd, nullptr, nullptr,
                                                        (__nv_bfloat16*)dx, partial, nullptr, rows, D);
-  reduce_partials_kernel<<<(D + 255) / 256, 256, 0, stream>>>(partial, grid, D, (__nv_bfloat16*)dw_bf16, nullptr, 0);
+  reduce_partials_kernel<<<(D + 31) / 32, 256, 0, stream>>>(partial, grid, D, (__nv_bfloat16*)dw_bf16, nullptr, 0);
   return (int)cudaGetLastError();
 }
