@@ -40,3 +40,14 @@ def test_tensor_parallel_matches_unsharded(unique_port, kind, sp):
     n = 2
     out = _run("_mp_tp_check.py", n, unique_port, "nccl", kind, sp, str(unique_port))
     assert "TP_OK" in out, out[-4000:]
+
+
+@pytest.mark.parametrize("tp", [2, 4])
+def test_tensor_parallel_times_sharded_data_parallel(unique_port, tp):
+    """TP (with SP and the sharded loss) composed with the FSDP engine on a (dp_shard, tp) mesh."""
+    n = torch.cuda.device_count()
+    if n < 2 * tp and not (tp == 2 and n >= 2):
+        pytest.skip(f"needs {2 * tp} GPUs")
+    nproc = 2 * tp if n >= 2 * tp else tp   # falls back to tp x 1 (engine with a one-rank shard group)
+    out = _run("_mp_tp_fsdp_check.py", nproc, unique_port, str(tp))
+    assert "MP_TP_FSDP_OK" in out, out[-4000:]
