@@ -42,7 +42,10 @@ def _read(path: str) -> tuple[dict, str | None]:
         data = {}
     if not isinstance(data, (dict, list)):
         raise ComposeError(f"{path}: top level must be a mapping or a list")
-    return data, (m.group(1) if m else None)
+    pkg = m.group(1) if m else None
+    if pkg is not None:
+        pkg = pkg.lstrip("@")   # '# @package @_global_' is written in some configs; the package is _global_
+    return data, pkg
 
 
 def _find(config_dirs: list[str], rel: str) -> str | None:
@@ -123,6 +126,8 @@ def _load_tree(config_dirs: list[str], rel: str, group_choices: dict[str, Any], 
         group = d["group"]
         if group.startswith("hydra/") or group == "hydra":
             continue
+        if d["override"]:
+            continue   # only changes the option of a group chosen elsewhere (collected by _collect_overrides)
         full_group = group if not base_dir or group.startswith("/") else group
         option = group_choices.get(full_group, d["option"])
         if option is None or option == "null":
@@ -147,6 +152,27 @@ def _load_tree(config_dirs: list[str], rel: str, group_choices: dict[str, Any], 
             merged = conf.merge(merged, _place(sub_plain, None if sub_header else pkg))
     out = conf.to_container(merged, resolve=False)
     return _place(out, header_pkg) if header_pkg and header_pkg != "_global_" else out
+
+
+def _collect_overrides(config_dirs: list[str], rel: str, out: dict[str, Any]) -> None:
+    """``- override group: option`` entries of a config (and of the config files it includes) re-select the
+    option of a group that some other defaults list chooses. The outermost file wins."""
+    path = _find(config_dirs, rel)
+    if path is None:
+        return
+    data, _ = _read(path)
+    if not isinstance(data, dict):
+        return
+    base_dir = os.path.dirname(rel)
+    for entry in data.get("defaults") or []:
+        d = _parse_default(entry)
+        if d["kind"] == "group" and d["override"] and not d["group"].startswith("hydra"):
+            out.setdefault(d["group"], d["option"])
+        elif d["kind"] == "file":
+            sub_rel = os.path.join(base_dir, d["option"]) if base_dir else d["option"]
+            if _find(config_dirs, sub_rel) is None:
+                sub_rel = d["option"]
+            _collect_overrides(config_dirs, sub_rel, out)
 
 
 _OVR = re.compile(r"^(?P<prefix>\+\+|\+|~)?(?P<key>[^=]+?)(=(?P<value>.*))?$", re.S)
@@ -191,6 +217,10 @@ def compose(config_dir: str | list[str], config_name: str, overrides: list[str] 
             group_choices[gkey] = None
         else:
             value_ops.append(o)
+    file_overrides: dict[str, Any] = {}
+    _collect_overrides(config_dirs, config_name, file_overrides)
+    for g, opt in file_overrides.items():
+        group_choices.setdefault(g, opt)   # the command line has priority
     plain = _load_tree(config_dirs, config_name, group_choices)
     # groups chosen on the command line that the defaults list did not mention are appended
     cfg = conf.create(plain)

@@ -42,6 +42,7 @@ class LlamaConfig(GPTConfig):
 class LlamaBlock(RotaryTransformerBlock):
     def __init__(self, config):
         super().__init__(n_embd=config.n_embd, n_head=config.n_head, n_kv_head=config.n_kv_head,
+                         head_dim=getattr(config, "head_dim", None),
                          dropout=config.dropout, rmsnorm_eps=config.rmsnorm_eps, bias=config.bias,
                          attention_bias=config.attention_bias, intermediate_size=config.intermediate_size,
                          multiple_of=config.multiple_of, use_qk_norm=config.use_qk_norm, mlp_type=config.mlp_type)

@@ -1,0 +1,55 @@
+"""Every shipped root config composes, resolves and validates against its recipe's config schema."""
+
+import os
+
+import pytest
+
+from optimus_dl_b200.core import compose, conf
+from optimus_dl_b200.core.config_utils import non_resolving_instantiate
+
+ROOT = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "configs")
+
+
+@pytest.mark.parametrize("name", ["train_llama", "train_llama_efficient", "train_llama_fp8", "train_llama_pretokenized",
+                                  "train_llama_shakespeare", "train_gpt2_speedrun", "train_synthetic"])
+def test_train_configs_compose(name):
+    cfg = compose.compose([os.path.join(ROOT, "train")], name, [])
+    cfg = non_resolving_instantiate(cfg)
+    # fields that only exist as defaults of the recipe's structured config (filled in when the recipe is built)
+    for key, default in (("exp_tags", []), ("exp_description", None)):
+        if key not in cfg.common:
+            cfg.common[key] = default
+    plain = conf.to_container(cfg, resolve=True)
+    assert plain["_name"] == "base"
+    assert plain["optimization"]["iterations"] > 0
+    assert isinstance(plain["model_transforms"], list)
+    if name == "train_llama_efficient":
+        assert plain["model"]["_name"] == "llama2-7b" and plain["optimization"]["acc_steps"] == 32
+        assert plain["data"]["scratch"]["base_transforms"]["transforms"][1]["max_seq_len"] == 4096
+    if name == "train_gpt2_speedrun":
+        assert plain["optimization"]["optimizer"]["_name"] == "muon"
+        assert plain["criterion"]["softcap_type"] == "sigmoid"
+    if name == "train_llama_fp8":
+        assert plain["optimization"]["amp"]["fp8"]["enabled"] is True
+        assert plain["model_transforms"][0]["_name"] == "transformer_engine"
+
+
+@pytest.mark.parametrize("group,name,overrides", [
+    ("eval", "quick", ["common.checkpoint_path=null"]), ("metrics", "default", []), ("serve", "char_shakespeare", []),
+    ("serve", "tinyllama", []), ("prepare_data", "default", []), ("grpo", "default", [])])
+def test_other_configs_compose(group, name, overrides):
+    cfg = compose.compose([os.path.join(ROOT, group)], name, overrides)
+    assert conf.is_config(cfg)
+    if group == "prepare_data":
+        assert cfg.tokenizer._name == "tiktoken" and cfg.processing.dtype == "uint16"
+    if group == "grpo":
+        assert conf.to_container(cfg, resolve=True)["grpo"]["group_size"] == 8
+
+
+def test_transformer_engine_variants_parse():
+    cfg = conf.load(os.path.join(ROOT, "model", "transforms", "transformer_engine.yaml"))
+    assert set(cfg.keys()) >= {"_default", "full", "linear_only", "norm_only", "disabled"}
+    from optimus_dl_b200.model_transforms import build_model_transform
+
+    for key in cfg.keys():
+        assert build_model_transform(cfg[key]) is not None
