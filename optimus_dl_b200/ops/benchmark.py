@@ -241,7 +241,7 @@ def bench_tp(op: str, t: Timer, cases) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", required=True, choices=["gemm_bf16", "gemm_fp8", "attention", "decode", "sampler", "elementwise",
+    ap.add_argument("--op", required=True, choices=["gemm_bf16", "gemm_skinny", "gemm_fp8", "attention", "decode", "sampler", "elementwise",
                                                     "tp_ag_gemm", "tp_gemm_rs"])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--small", action="store_true", help="one small case (for profiler captures)")
@@ -250,6 +250,8 @@ def main() -> None:
     if args.op == "gemm_bf16":
         bench_gemm_bf16(t, [(4096, 4096, 4096)] if args.small else [(8192, 8192, 8192), (8192, 6144, 4096), (8192, 4096, 14336),
                                                                     (8192, 28672, 4096)])
+    elif args.op == "gemm_skinny":   # decode-step shapes of a 1.7B model at batch 64: weight-streaming bound
+        bench_gemm_bf16(t, [(64, 4096, 2048), (64, 12288, 2048), (64, 2048, 6144), (64, 151936, 2048), (8, 4096, 4096)])
     elif args.op == "gemm_fp8":
         bench_gemm_fp8(t, [(4096, 4096, 4096)] if args.small else [(8192, 8192, 8192), (8192, 6144, 4096), (8192, 4096, 14336),
                                                                    (8192, 28672, 4096)])

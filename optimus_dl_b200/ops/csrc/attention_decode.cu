@@ -7,11 +7,11 @@
 //            the current one, whose row (seq_lens[b] - 1) this kernel writes before it attends
 //   out      [B, Hq, HD]     bf16
 //
-// The kernel is bound by the cache read, so it is organised around keeping loads in flight rather
-// than around tensor cores: one CTA per (kv head, sequence, split of the sequence) streams 64-token
-// K and V tiles through shared memory with cp.async double buffering; all query heads that share
-// the kv head (GQA group, up to 8) are served from the same tile.  With more than one split the
-// partial (max, sum, accumulator) triples are merged by a second small kernel.
+// The kernel is bound by the cache read: one CTA per (kv head, sequence, split of the sequence) streams 64-token
+// K and V tiles through shared memory with cp.async double buffering; all query heads that share the kv head (GQA
+// group, up to 8) are served from the same tile as the rows of small tensor-core products, so the instruction count
+// per cached byte stays low.  With more than one split the partial (max, sum, accumulator) triples are merged by a
+// second small kernel.
 #include "common.cuh"
 
 namespace ob {
@@ -29,15 +29,14 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// Shared memory: K and V tiles with rows padded by 16 bytes (conflict-free ldmatrix), the query group as a
+// 16-row bf16 matrix (rows beyond the group are zero), and after the main loop the per-warp partial results.
 template <int HD>
 struct Smem {
-  static constexpr int KPAD = HD + 8;  // 16-byte skew per row: conflict-free 16-byte row reads
-  __nv_bfloat16 k[2][TILE][KPAD];
-  __nv_bfloat16 v[2][TILE][HD];
-  float q[MAX_REP][HD];
-  float s[MAX_REP][TILE];
-  float m[MAX_REP], l[MAX_REP], alpha[MAX_REP];
-  float red[THREADS / HD > 1 ? MAX_REP * THREADS : 1];
+  static constexpr int PAD = HD + 8;
+  __nv_bfloat16 k[2][TILE][PAD];
+  __nv_bfloat16 v[2][TILE][PAD];
+  __nv_bfloat16 q[16][PAD];
 };
 
 template <int HD>
@@ -50,10 +49,37 @@ __device__ __forceinline__ void load_tile(Smem<HD>& sm, int buf, const __nv_bflo
     if (t < t_end) {
       cp_async_16(&sm.k[buf][r][c * 8], kbase + (long long)t * tok_stride + c * 8);
       cp_async_16(&sm.v[buf][r][c * 8], vbase + (long long)t * tok_stride + c * 8);
+    } else {
+      // rows past the end must be finite: their probabilities are zero, but 0 * NaN would poison the sums
+      *reinterpret_cast<uint4*>(&sm.k[buf][r][c * 8]) = make_uint4(0, 0, 0, 0);
+      *reinterpret_cast<uint4*>(&sm.v[buf][r][c * 8]) = make_uint4(0, 0, 0, 0);
     }
   }
 }
 
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(smem_row));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(smem_row));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+// D (16x8, fp32) += A (16x16, bf16, row) * B (16x8, bf16, col)
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// The GQA group (up to 8 query heads that share this kv head) is the M dimension of small tensor-core products
+// (legacy mma.sync: the tiles are far too small for tcgen05 and the kernel is bound by the cache stream, not by
+// math).  Each of the four warps owns 16 of the 64 positions of a tile and keeps its own running maximum, sum and
+// 16 x HD output accumulator, so no cross-warp step happens per tile; the four partial results are merged once at
+// the end, like split partials.
 template <int HD>
 __global__ void __launch_bounds__(THREADS, 3)
 decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, const __nv_bfloat16* __restrict__ k_new,
@@ -66,7 +92,7 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, const __n
   Smem<HD>& sm = *reinterpret_cast<Smem<HD>*>(smem_raw);
   const int hk = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
   const int n_rep = Hq / Hk;
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   int len = seq_lens[b];
   if (len > t_max) len = t_max;
   if (len < 0) len = 0;  // an empty sequence still writes zeros / empty partials
@@ -89,18 +115,25 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, const __n
       *reinterpret_cast<uint4*>(vc + (long long)(len - 1) * tok_stride + c * 8) = vv;
     }
   }
-  for (int i = tid; i < n_rep * HD; i += THREADS) {
-    const int r = i / HD, d = i - r * HD;
-    sm.q[r][d] = __bfloat162float(q[(long long)b * q_stride + (long long)(hk * n_rep + r) * HD + d]) * scale_log2;
+  // query group -> 16 x HD bf16 matrix in shared memory (zero rows beyond the group)
+  for (int i = tid; i < 16 * (HD / 8); i += THREADS) {
+    const int r = i / (HD / 8), c = i - r * (HD / 8);
+    uint4 val = make_uint4(0, 0, 0, 0);
+    if (r < n_rep) val = *reinterpret_cast<const uint4*>(q + (long long)b * q_stride + (long long)(hk * n_rep + r) * HD + c * 8);
+    *reinterpret_cast<uint4*>(&sm.q[r][c * 8]) = val;
   }
-  if (tid < MAX_REP) { sm.m[tid] = -INFINITY; sm.l[tid] = 0.f; sm.alpha[tid] = 1.f; }
   __syncthreads();  // also orders the appended row before the cp.async reads below
 
-  constexpr int SUB = THREADS / HD;       // position subsets in the PV phase (1 for HD 128, 2 for HD 64)
-  const int d = tid % HD, sub = tid / HD;
-  float acc[MAX_REP];
+  // A fragments of Q for every 16-wide k-step, kept in registers for the whole kernel
+  uint32_t qf[HD / 16][4];
 #pragma unroll
-  for (int r = 0; r < MAX_REP; ++r) acc[r] = 0.f;
+  for (int s = 0; s < HD / 16; ++s)
+    ldmatrix_x4(qf[s], &sm.q[(lane & 7) + ((lane >> 3) & 1) * 8][s * 16 + (lane >> 4) * 8]);
+
+  float o[HD / 8][4];
+#pragma unroll
+  for (int j = 0; j < HD / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // rows lane/4 and lane/4 + 8
 
   const int n_tiles = t0 < t1 ? (t1 - t0 + TILE - 1) / TILE : 0;
   if (n_tiles > 0) load_tile<HD>(sm, 0, kc, vc, tok_stride, t0, t1);
@@ -111,102 +144,104 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, const __n
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
-    const int valid = min(TILE, t1 - (t0 + tile * TILE));
-    // scores: one (query head, position) pair per work item
-    for (int item = tid; item < n_rep * TILE; item += THREADS) {
-      const int r = item / TILE, t = item - r * TILE;
-      float dot = -INFINITY;
-      if (t < valid) {
-        // four independent partial sums: one serial chain of 128 dependent FMAs would cost more than the loads
-        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
-        const uint4* krow = reinterpret_cast<const uint4*>(&sm.k[buf][t][0]);
-        const float4* qrow = reinterpret_cast<const float4*>(&sm.q[r][0]);
+    const int p0 = warp * 16;                                   // this warp's positions inside the tile
+    const int valid = t1 - (t0 + tile * TILE);                  // positions of the tile that exist
+    if (p0 < valid) {
+      // S = Q K^T for 16 positions: two 16x8 accumulators
+      float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int c = 0; c < HD / 8; ++c) {
-          const uint4 kk = krow[c];
-          const float4 qa = qrow[2 * c], qb = qrow[2 * c + 1];
-          const float2 k0 = unpack_bf16x2(kk.x), k1 = unpack_bf16x2(kk.y), k2 = unpack_bf16x2(kk.z), k3 = unpack_bf16x2(kk.w);
-          d0 = fmaf(qa.x, k0.x, d0); d1 = fmaf(qa.y, k0.y, d1); d2 = fmaf(qa.z, k1.x, d2); d3 = fmaf(qa.w, k1.y, d3);
-          d0 = fmaf(qb.x, k2.x, d0); d1 = fmaf(qb.y, k2.y, d1); d2 = fmaf(qb.z, k3.x, d2); d3 = fmaf(qb.w, k3.y, d3);
-        }
-        dot = (d0 + d1) + (d2 + d3);
+      for (int s = 0; s < HD / 16; ++s) {
+        uint32_t kf[4];
+        ldmatrix_x4(kf, &sm.k[buf][p0 + (lane & 7) + (lane >> 4) * 8][s * 16 + ((lane >> 3) & 1) * 8]);
+        mma_16816(s0, qf[s], kf[0], kf[1]);
+        mma_16816(s1, qf[s], kf[2], kf[3]);
       }
-      sm.s[r][t] = dot;
-    }
-    __syncthreads();
-    // online softmax bookkeeping: warp w owns query heads w, w + 4
-    {
-      const int warp = tid >> 5, lane = tid & 31;
-      for (int r = warp; r < n_rep; r += THREADS / 32) {
-        const float s0 = sm.s[r][lane], s1 = sm.s[r][lane + 32];
-        const float m_old = sm.m[r];
-        const float m_new = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
-        const float p0 = exp2f(s0 - m_new), p1 = exp2f(s1 - m_new);
-        sm.s[r][lane] = p0;
-        sm.s[r][lane + 32] = p1;
-        const float sum = warp_sum(p0 + p1);
-        if (lane == 0) {
-          const float a = exp2f(m_old - m_new);
-          sm.alpha[r] = a;
-          sm.l[r] = sm.l[r] * a + sum;
-          sm.m[r] = m_new;
-        }
+      // scale, mask the tail, online softmax per row (rows r = lane/4 and r + 8; 4 columns each per thread)
+      const int c0 = p0 + 2 * (lane & 3);
+      float e[8] = {s0[0], s0[1], s1[0], s1[1], s0[2], s0[3], s1[2], s1[3]};   // row r: e[0..3], row r+8: e[4..7]
+      const int cols[4] = {c0, c0 + 1, c0 + 8, c0 + 9};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const bool okc = cols[i] < valid;
+        e[i] = okc ? e[i] * scale_log2 : -INFINITY;
+        e[4 + i] = okc ? e[4 + i] * scale_log2 : -INFINITY;
       }
-    }
-    __syncthreads();
-    // P V: thread owns output dimension d (and every SUB-th position)
+      float mx0 = fmaxf(fmaxf(e[0], e[1]), fmaxf(e[2], e[3])), mx1 = fmaxf(fmaxf(e[4], e[5]), fmaxf(e[6], e[7]));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);     // finite: position p0 of this warp exists
+      const float a0 = exp2f(m0 - n0), a1 = exp2f(m1 - n1);
+      m0 = n0; m1 = n1;
+      float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
-    for (int r = 0; r < MAX_REP; ++r)
-      if (r < n_rep) acc[r] *= sm.alpha[r];
-    {
-      // positions in groups of four: the probabilities come as one float4 (broadcast) per query head,
-      // and the four products per head are summed as a tree before they join the accumulator
-      const int t_end4 = (SUB == 1) ? (valid & ~3) : 0;
-      for (int t = 0; t < t_end4; t += 4) {
-        const float v0 = __bfloat162float(sm.v[buf][t][d]), v1 = __bfloat162float(sm.v[buf][t + 1][d]);
-        const float v2 = __bfloat162float(sm.v[buf][t + 2][d]), v3 = __bfloat162float(sm.v[buf][t + 3][d]);
-#pragma unroll
-        for (int r = 0; r < MAX_REP; ++r)
-          if (r < n_rep) {
-            const float4 p4 = *reinterpret_cast<const float4*>(&sm.s[r][t]);
-            acc[r] += (p4.x * v0 + p4.y * v1) + (p4.z * v2 + p4.w * v3);
-          }
+      for (int i = 0; i < 4; ++i) {
+        e[i] = exp2f(e[i] - n0); sum0 += e[i];
+        e[4 + i] = exp2f(e[4 + i] - n1); sum1 += e[4 + i];
       }
-      for (int t = t_end4 + sub; t < valid; t += SUB) {
-        const float vv = __bfloat162float(sm.v[buf][t][d]);
+      sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1); sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+      sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1); sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+      l0 = l0 * a0 + sum0;
+      l1 = l1 * a1 + sum1;
+      // P as the A fragment of the second product (accumulator layout of two n-tiles = A layout of one k-step)
+      uint32_t pf[4];
+      pf[0] = pack_bf16x2(e[0], e[1]);   // row r,     k 0..7 part
+      pf[1] = pack_bf16x2(e[4], e[5]);   // row r + 8, k 0..7 part
+      pf[2] = pack_bf16x2(e[2], e[3]);   // row r,     k 8..15 part
+      pf[3] = pack_bf16x2(e[6], e[7]);   // row r + 8, k 8..15 part
 #pragma unroll
-        for (int r = 0; r < MAX_REP; ++r)
-          if (r < n_rep) acc[r] += sm.s[r][t] * vv;
+      for (int j = 0; j < HD / 16; ++j) {
+        o[2 * j][0] *= a0; o[2 * j][1] *= a0; o[2 * j][2] *= a1; o[2 * j][3] *= a1;
+        o[2 * j + 1][0] *= a0; o[2 * j + 1][1] *= a0; o[2 * j + 1][2] *= a1; o[2 * j + 1][3] *= a1;
+        uint32_t vf[4];
+        ldmatrix_x4_trans(vf, &sm.v[buf][p0 + (lane & 7) + ((lane >> 3) & 1) * 8][j * 16 + (lane >> 4) * 8]);
+        mma_16816(o[2 * j], pf, vf[0], vf[1]);
+        mma_16816(o[2 * j + 1], pf, vf[2], vf[3]);
       }
     }
     __syncthreads();
   }
   cp_async_wait<0>();
+  __syncthreads();
 
-  if (SUB > 1) {
+  // merge the four warps (fixed order).  The K/V tile memory is free now and holds the partials:
+  //   po[warp][row][HD] fp32, pm[warp][row], pl[warp][row]
+  float* po = reinterpret_cast<float*>(smem_raw);
+  float* pm = po + 4 * 16 * HD;
+  float* pl = pm + 4 * 16;
+  const int r0 = lane >> 2, cq = 2 * (lane & 3);
 #pragma unroll
-    for (int r = 0; r < MAX_REP; ++r)
-      if (r < n_rep) sm.red[r * THREADS + tid] = acc[r];
-    __syncthreads();
-    if (sub == 0) {
-#pragma unroll
-      for (int r = 0; r < MAX_REP; ++r)
-        if (r < n_rep)
-          for (int s2 = 1; s2 < SUB; ++s2) acc[r] += sm.red[r * THREADS + s2 * HD + d];
-    }
+  for (int j = 0; j < HD / 8; ++j) {
+    float* base0 = po + (warp * 16 + r0) * HD + j * 8 + cq;
+    float* base1 = po + (warp * 16 + r0 + 8) * HD + j * 8 + cq;
+    base0[0] = o[j][0]; base0[1] = o[j][1];
+    base1[0] = o[j][2]; base1[1] = o[j][3];
   }
-  if (sub != 0) return;
+  if ((lane & 3) == 0) {
+    pm[warp * 16 + r0] = m0; pl[warp * 16 + r0] = l0;
+    pm[warp * 16 + r0 + 8] = m1; pl[warp * 16 + r0 + 8] = l1;
+  }
+  __syncthreads();
+  for (int i = tid; i < n_rep * HD; i += THREADS) {
+    const int r = i / HD, d = i - r * HD;
+    float mm = -INFINITY;
 #pragma unroll
-  for (int r = 0; r < MAX_REP; ++r) {
-    if (r >= n_rep) break;
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, pm[w * 16 + r]);
+    float num = 0.f, den = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = pm[w * 16 + r];
+      if (mw == -INFINITY) continue;
+      const float f = exp2f(mw - mm);
+      num += f * po[(w * 16 + r) * HD + d];
+      den += f * pl[w * 16 + r];
+    }
     const int hq = hk * n_rep + r;
     if (n_splits == 1) {
-      const float l = sm.l[r];
-      out[(long long)b * out_stride + (long long)hq * HD + d] = __float2bfloat16(l > 0.f ? acc[r] / l : 0.f);
+      out[(long long)b * out_stride + (long long)hq * HD + d] = __float2bfloat16(den > 0.f ? num / den : 0.f);
     } else {
       const long long slot = ((long long)b * Hq + hq) * n_splits + split;
-      part_o[slot * HD + d] = acc[r];
-      if (d == 0) { part_ml[slot * 2] = sm.m[r]; part_ml[slot * 2 + 1] = sm.l[r]; }
+      part_o[slot * HD + d] = num;
+      if (d == 0) { part_ml[slot * 2] = mm; part_ml[slot * 2 + 1] = den; }
     }
   }
 }

@@ -26,6 +26,18 @@ struct CopyTask {
   int flag;
 };
 
+// Bulk data loads from a peer.  The data was published before a barrier that this launch is ordered after, so
+// a weak load is enough; it must not allocate in L1 (the line could survive into a later launch) and, unlike a
+// system-scope relaxed load, it may be issued back to back with its neighbours.
+__device__ __forceinline__ uint4 ld_peer_bulk_16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
 __device__ __forceinline__ uint4 ld_peer_16(const void* p) {
   uint4 v;
   asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];"
@@ -49,11 +61,11 @@ __device__ __forceinline__ void run_copy_tasks(const CopyTask* tasks, int n_task
     for (; i + (UNROLL - 1) * (int)blockDim.x < nvec; i += UNROLL * blockDim.x) {
       uint4 v[UNROLL];
 #pragma unroll
-      for (int u = 0; u < UNROLL; ++u) v[u] = ld_peer_16(reinterpret_cast<const uint4*>(s) + i + u * blockDim.x);
+      for (int u = 0; u < UNROLL; ++u) v[u] = ld_peer_bulk_16(reinterpret_cast<const uint4*>(s) + i + u * blockDim.x);
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) reinterpret_cast<uint4*>(d)[i + u * blockDim.x] = v[u];
     }
-    for (; i < nvec; i += blockDim.x) reinterpret_cast<uint4*>(d)[i] = ld_peer_16(reinterpret_cast<const uint4*>(s) + i);
+    for (; i < nvec; i += blockDim.x) reinterpret_cast<uint4*>(d)[i] = ld_peer_bulk_16(reinterpret_cast<const uint4*>(s) + i);
     for (int j = nvec * 8 + threadIdx.x; j < task.numel; j += blockDim.x) d[j] = s[j];
     if (task.flag >= 0) {
       // the consumer reads these bytes through TMA (async proxy): order our generic-proxy stores

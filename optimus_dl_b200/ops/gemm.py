@@ -20,6 +20,7 @@ import torch
 from . import _lib
 
 ACT = {"none": 0, "gelu": 1, "relu2": 2, "silu": 3}
+SKINNY_M = 64   # inference-only products with at most this many rows use the library GEMM (see gemm())
 
 
 def _use_kernel(*ts: torch.Tensor) -> bool:
@@ -91,6 +92,15 @@ def gemm(
             out.add_(r.to(out.dtype))
         else:
             out.copy_(r.to(out.dtype))
+        return out
+    if (M <= SKINNY_M and not a_mn and not accumulate and act == "none" and alpha == 1.0 and out.dtype == torch.bfloat16
+            and b_flags is None and a_flags is None and out.is_contiguous() and not torch.is_grad_enabled()):
+        # single-token decode steps: a handful of rows against a whole weight matrix is a weight-streaming
+        # problem that wants split-K / narrow tiles over all SMs, not 128 x 256 output tiles; this plain
+        # product (no fused epilogue, no collective) goes to the library
+        torch.matmul(a, b if b_mn else b.t(), out=out)
+        if bias is not None:
+            out.add_(bias)
         return out
     l = _lib.lib()
     rc = l.ob_gemm_bf16(
