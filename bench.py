@@ -34,6 +34,10 @@ MODELS = {
                       rmsnorm_eps=1e-5),
     "llama-1b": dict(_name="llama2", n_layer=16, n_head=32, n_kv_head=8, n_embd=2048, intermediate_size=8192,
                      vocab_size=128256, rope_theta=500000.0, sequence_length=8192, tie_word_embeddings=False),
+    # BASELINE config 3: Qwen-style 14B (per-head QK-norm), meant for --tp 8 --seq-len 16384 --packed-docs
+    "qwen3-14b": dict(_name="qwen3", n_layer=40, n_head=40, n_kv_head=8, n_embd=5120, head_dim=128, intermediate_size=17408,
+                      vocab_size=151936, rope_theta=1000000.0, sequence_length=16384, tie_word_embeddings=False,
+                      attention_bias=False),
     "tiny": dict(_name="llama2", n_layer=2, n_head=8, n_kv_head=2, n_embd=512, intermediate_size=1536,
                  vocab_size=32000, rope_theta=500000.0, sequence_length=2048, tie_word_embeddings=False),
 }
@@ -94,6 +98,11 @@ def main() -> None:
     ap.add_argument("--seq-len", type=int, default=None)
     ap.add_argument("--micro-batch", type=int, default=1)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (with sequence parallelism and the sharded "
+                                                      "loss); the remaining ranks form the sharded data-parallel group")
+    ap.add_argument("--acc-steps", type=int, default=1, help="micro-batches accumulated per optimizer step")
+    ap.add_argument("--packed-docs", action="store_true", help="each sequence is packed from documents with exponential "
+                    "lengths (mean 2048, min 32) and attends block-diagonally")
     ap.add_argument("--timeline", default=None, help="write a per-launcher device-time breakdown of one extra step "
                                                        "(JSON lines) to this file")
     ap.add_argument("--n-layer", type=int, default=None, help="override the layer count (profiling only; the "
@@ -127,7 +136,10 @@ def main() -> None:
     device = torch.device("cuda", local_rank)
     from optimus_dl_b200.parallel.collective import DistributedConfig
 
-    collective = build_best_collective(DistributedConfig(tp_size=1, sharding_world_size=world), device)
+    tp = max(int(args.tp), 1)
+    assert world % tp == 0, "--tp must divide the number of ranks"
+    dp = world // tp
+    collective = build_best_collective(DistributedConfig(tp_size=tp, sharding_world_size=dp), device)
 
     mcfg = dict(MODELS[args.model])
     seq = args.seq_len or mcfg["sequence_length"]
@@ -140,8 +152,12 @@ def main() -> None:
     with torch.device(device):
         model = build_model(mcfg)
     torch.set_default_dtype(prev)
-    model = build_model_transform({"_name": "fully_shard", "reshard_after_forward": False}).apply(
-        model, collective=collective, device=device)
+    if tp > 1:
+        model = build_model_transform({"_name": "tensor_parallel", "custom_model_kwargs": {
+            "sequence_parallel": True, "loss_parallel": True}}).apply(model, collective=collective, device=device)
+    if tp == 1 or dp > 1:
+        model = build_model_transform({"_name": "fully_shard", "reshard_after_forward": False}).apply(
+            model, collective=collective, device=device)
     criterion = build_criterion({"_name": "cross_entropy"}, collective=collective)
     optimizer = build_optimizer({"_name": "adamw", "lr": 3e-4, "betas": [0.9, 0.95], "weight_decay": 0.1},
                                 params=model.make_parameter_groups())
@@ -149,14 +165,37 @@ def main() -> None:
     vocab = mcfg["vocab_size"]
     mb = args.micro_batch
     total_steps = warmup + args.steps
-    gen = torch.Generator().manual_seed(1234 + rank)
-    host_batches = torch.randint(0, vocab, (total_steps, mb, seq + 1), generator=gen, dtype=torch.int64).pin_memory()
+    gen = torch.Generator().manual_seed(1234 + collective.dp_rank)   # tensor-parallel peers see the same batch
+    acc = max(int(args.acc_steps), 1)
+    host_batches = torch.randint(0, vocab, (total_steps, mb * acc, seq + 1), generator=gen, dtype=torch.int64).pin_memory()
     dev_batches = host_batches.to(device)
+    doc_ids = None
+    if args.packed_docs:
+        g2 = torch.Generator().manual_seed(0)
+        rows = []
+        for _ in range(mb):
+            lens, total = [], 0
+            while total < seq + 1:
+                n = max(32, int(torch.empty(1).exponential_(1.0 / 2048.0, generator=g2).item()))
+                lens.append(min(n, seq + 1 - total))
+                total += lens[-1]
+            rows.append(torch.repeat_interleave(torch.arange(len(lens)), torch.tensor(lens)))
+        doc_ids = torch.stack(rows).to(device)
+
+    from optimus_dl_b200.model_transforms.distributed import accumulation_context
+
+    criterion.grad_scale = 1.0 / acc
 
     def train_step(ids: torch.Tensor) -> torch.Tensor:
         optimizer.zero_grad()
-        loss, _ = criterion(model, {"input_ids": ids})
-        loss.backward()
+        loss = None
+        for a in range(acc):
+            batch = {"input_ids": ids[a * mb:(a + 1) * mb]}
+            if doc_ids is not None:
+                batch["document_ids"] = doc_ids
+            with accumulation_context(model, a == acc - 1):
+                loss, _ = criterion(model, batch)
+                (loss / acc).backward()
         optimizer.step()
         return loss
 
@@ -198,7 +237,7 @@ def main() -> None:
         last_loss["f"] = float(train_step(ids).item())
 
     ms, launches, clocks = timed(step_device)
-    tokens_per_step = world * mb * seq
+    tokens_per_step = dp * mb * acc * seq
     value = tokens_per_step * args.steps / (ms / 1e3)
     e2e = None
     if not args.no_e2e:
@@ -227,8 +266,10 @@ def main() -> None:
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights",
             "impl": "ours",
-            "config": {"model": args.model, "global_batch": world * mb, "seq_len": seq,
-                       "parallelism": f"fsdp{world}" if world > 1 else "fsdp1 (single GPU, same sharded engine)",
+            "config": {"model": args.model, "global_batch": dp * mb * acc, "seq_len": seq,
+                       "parallelism": (f"tp{tp}+sp x fsdp{dp}" if tp > 1 else
+                                       (f"fsdp{world}" if world > 1 else "fsdp1 (single GPU, same sharded engine)")),
+                       "packed_docs": bool(args.packed_docs),
                        "optimizer": "AdamW fp32 master/moments, fused into the gradient reduce kernel",
                        "l2": "working set (16 GB bf16 weights + activations) far exceeds the 126 MB L2"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,

@@ -159,6 +159,13 @@ class _SwiGLUMLP(torch.autograd.Function):
 
 def swiglu_mlp(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, wc: torch.Tensor) -> torch.Tensor:
     """Bias-free SwiGLU feed-forward block; kernels on CUDA bf16, eager otherwise."""
+    if _ok(x, w1, w2, wc) and not torch.is_grad_enabled() and x.numel() // x.shape[-1] <= gemm.SKINNY_M:
+        # decode steps: weight-streaming products (see gemm.gemm) and the elementwise activation
+        from . import linear as lin_ops
+
+        gu = lin_ops.multi_linear(x, [w1, w2])
+        g, u = gu.split(w1.shape[0], dim=-1)
+        return lin_ops.linear(swiglu(g.contiguous(), u.contiguous()), wc)
     if _ok(x, w1, w2, wc) and w1.shape == w2.shape and w1.stride() == w2.stride() and wc.shape[1] % 8 == 0:
         return _SwiGLUMLP.apply(x, w1, w2, wc)
     return F.linear(F.silu(F.linear(x, w1)) * F.linear(x, w2), wc)
