@@ -100,6 +100,7 @@ def main() -> None:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (with sequence parallelism and the sharded "
                                                       "loss); the remaining ranks form the sharded data-parallel group")
+    ap.add_argument("--fp8", action="store_true", help="block-scaled e4m3 GEMMs for the transformer blocks' linear layers")
     ap.add_argument("--acc-steps", type=int, default=1, help="micro-batches accumulated per optimizer step")
     ap.add_argument("--packed-docs", action="store_true", help="each sequence is packed from documents with exponential "
                     "lengths (mean 2048, min 32) and attends block-diagonally")
@@ -152,6 +153,8 @@ def main() -> None:
     with torch.device(device):
         model = build_model(mcfg)
     torch.set_default_dtype(prev)
+    if args.fp8:
+        model = build_model_transform({"_name": "transformer_engine", "replace_norm": False}).apply(model)
     if tp > 1:
         model = build_model_transform({"_name": "tensor_parallel", "custom_model_kwargs": {
             "sequence_parallel": True, "loss_parallel": True}}).apply(model, collective=collective, device=device)
@@ -186,7 +189,17 @@ def main() -> None:
 
     criterion.grad_scale = 1.0 / acc
 
+    import contextlib
+
+    from optimus_dl_b200.amp.fp8 import FP8Recipe
+
+    fp8_recipe = FP8Recipe() if args.fp8 else None
+
     def train_step(ids: torch.Tensor) -> torch.Tensor:
+        with (fp8_recipe.autocast(True) if fp8_recipe is not None else contextlib.nullcontext()):
+            return _train_step(ids)
+
+    def _train_step(ids: torch.Tensor) -> torch.Tensor:
         optimizer.zero_grad()
         loss = None
         for a in range(acc):
@@ -264,7 +277,8 @@ def main() -> None:
             else f"{args.model} bf16 train tokens/s (device-timed, max/rank)",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights",
+            "dtype": "fp8 e4m3 block-scaled GEMMs, bf16 elsewhere" if args.fp8 else "bf16",
+            "data": "synthetic uniform-random token ids, random-init weights",
             "impl": "ours",
             "config": {"model": args.model, "global_batch": dp * mb * acc, "seq_len": seq,
                        "parallelism": (f"tp{tp}+sp x fsdp{dp}" if tp > 1 else

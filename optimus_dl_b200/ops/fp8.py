@@ -133,6 +133,28 @@ def _cached_weight(w: torch.Tensor, holder: torch.Tensor | None = None):
     return hit[1:]
 
 
+def forward_product(x2: torch.Tensor, owners: list[torch.Tensor]) -> torch.Tensor:
+    """``x2 @ cat(owners)^T`` with both operands quantised (no autograd); ``owners`` adjacent or single."""
+    w = owners[0] if len(owners) == 1 else lin_ops._fused_view(list(owners))
+    wq, ws, _, _ = _cached_weight(w, owners[0])
+    xq, xs = quantize_rowwise(x2)
+    return gemm_fp8(xq, xs, wq, ws)
+
+
+def dgrad_product(dy2: torch.Tensor, owners: list[torch.Tensor]) -> torch.Tensor:
+    """``dy2 @ cat(owners)`` (input gradient of :func:`forward_product`) with both operands quantised."""
+    w = owners[0] if len(owners) == 1 else lin_ops._fused_view(list(owners))
+    _, _, wqt, wst = _cached_weight(w, owners[0])
+    dq, ds = quantize_rowwise(dy2)
+    return gemm_fp8(dq, ds, wqt, wst)
+
+
+def usable(x2: torch.Tensor, owners: list[torch.Tensor]) -> bool:
+    """FP8 execution applies: autocast active, weights marked, CUDA bf16, shapes fit the 128-wide scale blocks."""
+    return (lin_ops.fp8_route(list(owners)) and kernel_ok(x2, *owners) and fp8_shapes_ok(list(owners))
+            and sum(w.shape[0] for w in owners) % BLOCK == 0 and (len(owners) == 1 or lin_ops._adjacent(list(owners))))
+
+
 class _Fp8Linear(torch.autograd.Function):
     """``y = x cat(W_i)^T + b``; the ``W_i`` are adjacent in memory (or a single matrix), so their
     concatenation is a view. Weight gradients go to each ``W_i`` (through ``main_grad`` when it has one)."""

@@ -35,6 +35,7 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from ..ops import _lib, gemm
+from ..ops import fp8 as fp8_ops
 from ..ops import linear as lin_ops
 
 logger = logging.getLogger(__name__)
@@ -296,11 +297,19 @@ class _ColumnParallel(torch.autograd.Function):
         lin_ops.ensure_gathered(ws)   # a sharding engine may still be gathering these weights
         bias = None if bs[0] is None else lin_ops._fused_bias(bs)
         wf = _cat_weights(ws)
-        if sp:
+        use_fp8 = fp8_ops.usable(x, ws)
+        if use_fp8:
+            # FP8 context: block-scaled e4m3 products; the collectives run as separate library calls here
+            x_full = all_gather_rows(tp, x) if sp else x
+            y = fp8_ops.forward_product(x_full, ws)
+            if bias is not None:
+                y = y + bias
+        elif sp:
             x_full, y = ag_gemm(tp, x, wf, bias=bias)
         else:
             x_full, y = x, gemm.gemm(x, wf, bias=bias)
         ctx.save_for_backward(x_full, *ws)
+        ctx.use_fp8 = use_fp8
         ctx.tp, ctx.sp, ctx.n, ctx.params, ctx.has_bias = tp, sp, n, ws, bias is not None
         ctx.sizes = [w.shape[0] for w in ws]
         return y
@@ -313,7 +322,13 @@ class _ColumnParallel(torch.autograd.Function):
         wf = _cat_weights(ws)
         dx = None
         if ctx.needs_input_grad[2]:
-            if ctx.sp:
+            if ctx.use_fp8:
+                dx = fp8_ops.dgrad_product(dy2, ctx.params)
+                if ctx.sp:
+                    dx = reduce_scatter_rows(tp, dx)
+                else:
+                    dist.all_reduce(dx, group=tp.group)
+            elif ctx.sp:
                 dx = gemm_rs(tp, dy2, wf, b_mn=True)
             else:
                 dx = gemm.gemm(dy2, wf, b_mn=True)
@@ -372,7 +387,19 @@ class _RowParallel(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, tp: TPState, sp: bool, x, w, bias, residual):
-        if sp:
+        use_fp8 = fp8_ops.usable(x, [w])
+        ctx.use_fp8 = use_fp8
+        if use_fp8:
+            y = fp8_ops.forward_product(x if x.is_contiguous() else x.contiguous(), [w])
+            if sp:
+                y = reduce_scatter_rows(tp, y)
+            else:
+                dist.all_reduce(y, group=tp.group)
+            if bias is not None:
+                y = y + bias
+            if residual is not None:
+                y = y + residual
+        elif sp:
             y = gemm_rs(tp, x, w, residual=residual)
             if bias is not None:
                 y = y + bias
@@ -392,7 +419,10 @@ class _RowParallel(torch.autograd.Function):
         x, w = ctx.saved_tensors
         tp = ctx.tp
         dy2 = dy if dy.is_contiguous() else dy.contiguous()
-        if ctx.sp:
+        if ctx.use_fp8:
+            dy_full = all_gather_rows(tp, dy2) if ctx.sp else dy2
+            dx = fp8_ops.dgrad_product(dy_full, [ctx.param])
+        elif ctx.sp:
             dy_full, dx = ag_gemm(tp, dy2, w, b_mn=True)
         else:
             dy_full, dx = dy2, gemm.gemm(dy2, w, b_mn=True)
@@ -614,11 +644,11 @@ def swiglu_mlp_forward(mod: nn.Module, x: torch.Tensor, residual: torch.Tensor |
     tp: TPState = mod.tp
     shp = x.shape
     x2 = x.reshape(-1, shp[-1])
-    if mod.w1.bias is None:
+    if mod.w1.bias is None and not lin_ops.fp8_route([mod.w1.weight, mod.w2.weight]):
         h = column_parallel_swiglu(tp, x2, mod.w1.weight, mod.w2.weight)
     else:
         gu = column_parallel_linear(tp, x2, [mod.w1.weight, mod.w2.weight], [mod.w1.bias, mod.w2.bias])
-        g, u = gu.split(mod.w1.weight.shape[0], dim=-1)
+        g, u = gu.split(mod.w1.weight.shape[0], dim=-1)   # also the FP8 form: gate/up as one block-scaled GEMM
         h = act_ops.swiglu(g.contiguous(), u.contiguous())
     res2 = residual.reshape(-1, shp[-1]) if residual is not None else None
     y = row_parallel_linear(tp, h, mod.c_proj.weight, mod.c_proj.bias, residual=res2).view(shp)
@@ -713,7 +743,10 @@ def _shard_linears_adjacent(mods: list[nn.Linear], dim: int, tp: TPState) -> Non
         view = flat[o:o + shp[0] * shp[1]].view(shp)
         _shard_param(m.weight, dim, r, P, dev, out=view)
         req = m.weight.requires_grad
+        marked_fp8 = bool(getattr(m.weight, "_fp8", False))
         m.weight = _mark(nn.Parameter(view, requires_grad=req), tp, dim)
+        if marked_fp8:
+            m.weight._fp8 = True   # the FP8 mark of the transformer_engine transform survives the re-sharding
         o += shp[0] * shp[1]
         if dim == 0:
             m.out_features = shp[0]

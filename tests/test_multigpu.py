@@ -51,3 +51,9 @@ def test_tensor_parallel_times_sharded_data_parallel(unique_port, tp):
     nproc = 2 * tp if n >= 2 * tp else tp   # falls back to tp x 1 (engine with a one-rank shard group)
     out = _run("_mp_tp_fsdp_check.py", nproc, unique_port, str(tp))
     assert "MP_TP_FSDP_OK" in out, out[-4000:]
+
+
+def test_tensor_parallel_fp8(unique_port):
+    """Block-scaled FP8 projections under tensor + sequence parallelism stay close to the unsharded bf16 model."""
+    out = _run("_mp_tp_check.py", 2, unique_port, "nccl", "llama", "1", str(unique_port), "fp8")
+    assert "TP_OK" in out, out[-4000:]
