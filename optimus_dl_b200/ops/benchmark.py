@@ -192,7 +192,7 @@ def bench_tp(op: str, t: Timer, cases) -> None:
         if op == "tp_ag_gemm":
             x = torch.randn(rows, K, device="cuda").bfloat16()
             w = torch.randn(N, K, device="cuda").bfloat16()
-            fused = lambda: T.ag_gemm(state, x, w)  # noqa: E731
+            fused = lambda: T.ag_gemm(state, x, w, site=("bench", M, N, K))  # noqa: E731
 
             def base():
                 xf = T.all_gather_rows(state, x)

@@ -79,5 +79,37 @@ __device__ __forceinline__ void run_copy_tasks(const CopyTask* tasks, int n_task
   }
 }
 
+// Push variant: the chunks of this rank's own slice (`src`, local) are stored into the peers' operand buffers
+// and the peers' row flags are raised.  task.offset is the element offset inside the peer's buffer, the source
+// element offset is task.offset - slice_base.  Stores over NVLink are posted, so a few CTAs saturate the link
+// where loads would wait a round trip each.
+template <int UNROLL = 8>
+__device__ __forceinline__ void run_push_tasks(const CopyTask* tasks, int n_tasks, int first, int stride,
+                                               const __nv_bfloat16* src, long long slice_base, const PeerPtrs& dst,
+                                               const PeerPtrs& flag_ptrs, int epoch) {
+  for (int t = first; t < n_tasks; t += stride) {
+    const CopyTask task = tasks[t];
+    const uint4* s = reinterpret_cast<const uint4*>(src + (task.offset - slice_base));
+    uint4* d = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dst.p[task.peer]) + task.offset);
+    const int nvec = task.numel / 8;   // chunks are whole rows of a width that is a multiple of 8
+    int i = threadIdx.x;
+    for (; i + (UNROLL - 1) * (int)blockDim.x < nvec; i += UNROLL * blockDim.x) {
+      uint4 v[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) v[u] = s[i + u * blockDim.x];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) d[i + u * blockDim.x] = v[u];
+    }
+    for (; i < nvec; i += blockDim.x) d[i] = s[i];
+    // make this CTA's stores visible at system scope, then publish the chunk on the peer
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0 && task.flag >= 0) {
+      int* f = reinterpret_cast<int*>(flag_ptrs.p[task.peer]) + task.flag;
+      asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(f), "r"(epoch) : "memory");
+    }
+  }
+}
+
 }  // namespace comm
 }  // namespace ob

@@ -35,6 +35,53 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   gemm_cta<0, B_MN, SWIGLU>(&tmA, &tmB, &tmB2, p, blockIdx.x - n_copy, gridDim.x - n_copy, smem_raw);
 }
 
+// Push form of the same launch: copy CTAs store this rank's slice into every peer's operand buffer.
+template <int B_MN, int SWIGLU>
+__global__ void __launch_bounds__(AG_THREADS, 1)
+ag_push_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmB2, const Params p,
+                    const comm::CopyTask* __restrict__ tasks, int n_tasks, const __nv_bfloat16* __restrict__ src,
+                    long long slice_base, comm::PeerPtrs dst, comm::PeerPtrs flag_ptrs, int epoch, int n_copy) {
+  extern __shared__ uint8_t smem_raw[];
+  if ((int)blockIdx.x < n_copy) {
+    comm::run_push_tasks<8>(tasks, n_tasks, blockIdx.x, n_copy, src, slice_base, dst, flag_ptrs, epoch);
+    return;
+  }
+  if (threadIdx.x >= NUM_THREADS) return;
+  gemm_cta<0, B_MN, SWIGLU>(&tmA, &tmB, &tmB2, p, blockIdx.x - n_copy, gridDim.x - n_copy, smem_raw);
+}
+
+template <int B_MN, int SWIGLU>
+static int launch_ag_push(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const Params& p,
+                          const void* tasks, int n_tasks, const void* src, long long slice_base,
+                          const void* const* dst_ptrs, const void* const* flag_ptrs, int world, int epoch, int n_copy,
+                          cudaStream_t stream) {
+  auto kern = ag_push_gemm_kernel<B_MN, SWIGLU>;
+  static bool configured = false;
+  if (!configured) {
+    OB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    configured = true;
+  }
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (n_tasks == 0) n_copy = 0;
+  if (n_copy > sms / 2) n_copy = sms / 2;
+  const int bn = SWIGLU ? BN / 2 : BN;
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + bn - 1) / bn);
+  int gemm_ctas = sms - n_copy;
+  if (gemm_ctas > tiles) gemm_ctas = tiles;
+  comm::PeerPtrs dst{}, fl{};
+  for (int i = 0; i < world; ++i) {
+    dst.p[i] = const_cast<void*>(dst_ptrs[i]);
+    fl.p[i] = const_cast<void*>(flag_ptrs[i]);
+  }
+  kern<<<n_copy + gemm_ctas, AG_THREADS, SMEM_BYTES, stream>>>(ta, tb, tb2, p, (const comm::CopyTask*)tasks, n_tasks,
+                                                               (const __nv_bfloat16*)src, slice_base, dst, fl, epoch,
+                                                               n_copy);
+  return (int)cudaGetLastError();
+}
+
 template <int B_MN, int SWIGLU>
 static int launch_ag(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const Params& p,
                      const void* tasks, int n_tasks, const void* const* src_ptrs, int world, void* dst, int* flags,
@@ -129,4 +176,47 @@ extern "C" int ob_gemm_ag_act_bf16(const void* A, long long lda, const void* B, 
     return launch_ag<0, 1>(ta, tb, tb2, p, tasks, n_tasks, src_ptrs, world, dst, flags, epoch, n_copy, stream);
   if (b_mn) return launch_ag<1, 0>(ta, tb, tb2, p, tasks, n_tasks, src_ptrs, world, dst, flags, epoch, n_copy, stream);
   return launch_ag<0, 0>(ta, tb, tb2, p, tasks, n_tasks, src_ptrs, world, dst, flags, epoch, n_copy, stream);
+}
+
+// Push form of ob_gemm_ag_act_bf16.  A is this rank's gathered-operand buffer [M,K] in symmetric memory (its own
+// rows already copied and flagged by the caller); `x_local` is this rank's slice, whose chunks the copy CTAs
+// store into dst_ptrs[peer] + task.offset and publish through flag_ptrs[peer][task.flag] = epoch.  The GEMM CTAs
+// wait on this rank's own flag array `flags` (the one the peers write).
+extern "C" int ob_gemm_ag_push_bf16(const void* A, long long lda, const void* x_local, long long slice_base,
+                                    const void* B, const void* B2, long long ldb, int b_mn, void* C, void* G, void* U,
+                                    long long ldc, int M, int N, int K, const void* bias, const void* tasks,
+                                    int n_tasks, const void* const* dst_ptrs, const void* const* flag_ptrs, int world,
+                                    int* flags, int flag_rows, int epoch, int first_tile_shift, int n_copy,
+                                    int* status, cudaStream_t stream) {
+  if (world > comm::MAX_RANKS) return -1;
+  if (B2 != nullptr && b_mn) return -2;
+  CUtensorMap ta, tb, tb2;
+  int rc = make_tmap_2d(&ta, A, M, K, lda, BM, BK, 2);
+  if (rc) return rc;
+  if (B2 != nullptr) {
+    rc = make_tmap_2d(&tb, B, N, K, ldb, BN / 2, BK, 2);
+    if (rc) return rc;
+    rc = make_tmap_2d(&tb2, B2, N, K, ldb, BN / 2, BK, 2);
+  } else if (b_mn) {
+    rc = make_tmap_2d(&tb, B, K, N, ldb, BK, 64, 2);
+    tb2 = tb;
+  } else {
+    rc = make_tmap_2d(&tb, B, N, K, ldb, BN, BK, 2);
+    tb2 = tb;
+  }
+  if (rc) return rc;
+  Params p{};
+  p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.alpha = 1.0f; p.bias = bias; p.status = status;
+  p.G = G; p.U = U;
+  p.flag_rows = 1;
+  p.a_flags = flags; p.a_flag_rows = flag_rows > 0 ? flag_rows : 1; p.a_flag_value = epoch; p.tile_order = 2;
+  p.first_tile_shift = first_tile_shift;
+  if (B2 != nullptr)
+    return launch_ag_push<0, 1>(ta, tb, tb2, p, tasks, n_tasks, x_local, slice_base, dst_ptrs, flag_ptrs, world, epoch,
+                                n_copy, stream);
+  if (b_mn)
+    return launch_ag_push<1, 0>(ta, tb, tb2, p, tasks, n_tasks, x_local, slice_base, dst_ptrs, flag_ptrs, world, epoch,
+                                n_copy, stream);
+  return launch_ag_push<0, 0>(ta, tb, tb2, p, tasks, n_tasks, x_local, slice_base, dst_ptrs, flag_ptrs, world, epoch,
+                              n_copy, stream);
 }

@@ -122,7 +122,8 @@ __device__ __forceinline__ bool wait_flag(const int* flag, int value, volatile i
   const unsigned long long t0 = global_ns();
   for (uint32_t it = 0;; ++it) {
     int v;
-    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    // system scope: the flag (and the data it covers) may have been written by another GPU
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
     if (v >= value) return true;
     if ((it & 0x3f) == 0x3f) {
       if (*abort_flag) return false;

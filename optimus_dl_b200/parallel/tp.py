@@ -28,6 +28,7 @@ which every peer reaches only after finishing its reads of use ``k``.
 from __future__ import annotations
 
 import logging
+import os
 from typing import Any
 
 import torch
@@ -65,6 +66,12 @@ class TPState:
         self._epoch = 0
         self._tasks: dict = {}
         self.n_copy = 16
+        self.n_push = 8              # copy CTAs of the push all-gather (posted stores need few)
+        # from this group size on the fused all-gather pushes instead of pulling (with two ranks the pull
+        # form is as fast and needs no persistent buffers); OB_TP_PUSH_MIN_WORLD overrides it for tests
+        self.push_min_world = int(os.environ.get("OB_TP_PUSH_MIN_WORLD", "3"))
+        self._sites: dict = {}       # persistent gathered-operand buffers, one per call site
+        self._push_tasks: dict = {}
 
     # ------------------------------------------------------------------ symmetric buffers
     def heap(self):
@@ -133,6 +140,48 @@ class TPState:
         return hit
 
 
+class _Site:
+    """Gathered operand ``[P * rows, width]`` of one call site in symmetric memory plus its row flags. Peers
+    store their slices into it (``ob_gemm_ag_push_bf16``); it stays valid until the same site runs again,
+    so the backward pass can read the gathered operand without keeping another copy."""
+
+    def __init__(self, tp: "TPState", numel: int, n_flags: int):
+        heap = tp.heap()
+        self.buf = heap.empty(numel, torch.bfloat16)
+        self.flags = heap.empty(max(n_flags, 16), torch.int32, zero=True)
+        self.numel, self.n_flags, self.epoch = numel, n_flags, 0
+        torch.cuda.synchronize(tp.device)
+        dist.barrier(group=tp.group)   # zeroed flags are in place everywhere before anybody publishes into them
+
+
+def _site_of(tp: "TPState", key: Any, numel: int, n_flags: int) -> "_Site":
+    site = tp._sites.get(key)
+    if site is None or site.numel < numel or site.n_flags < n_flags:
+        site = _Site(tp, numel, n_flags)
+        tp._sites[key] = site
+    return site
+
+
+def _push_tasks_of(tp: "TPState", rows: int, width: int, flag_rows: int):
+    """Chunks of this rank's slice for every peer, nearest lower rank first: a receiver then sees the slices of
+    ranks me+1, me+2, ... arrive in the order its tiles consume them."""
+    key = (rows, width, flag_rows)
+    hit = tp._push_tasks.get(key)
+    if hit is None:
+        from .symm import tasks_to_device
+
+        tasks = []
+        per = rows // flag_rows
+        for step in range(1, tp.size):
+            peer = (tp.rank - step) % tp.size
+            for j in range(per):
+                row0 = tp.rank * rows + j * flag_rows
+                tasks.append((row0 * width, flag_rows * width, peer, row0 // flag_rows))
+        hit = (tasks_to_device(tasks, tp.device), len(tasks))
+        tp._push_tasks[key] = hit
+    return hit
+
+
 def _flag_rows(rows_per_rank: int) -> int:
     return 128 if rows_per_rank % 128 == 0 else rows_per_rank
 
@@ -173,11 +222,13 @@ def _publish_rows(tp: TPState, x_local: torch.Tensor):
 
 
 def ag_gemm(tp: TPState, x_local: torch.Tensor, w: torch.Tensor, w2: torch.Tensor | None = None, *,
-            b_mn: bool = False, bias: torch.Tensor | None = None, save_gu: bool = False):
+            b_mn: bool = False, bias: torch.Tensor | None = None, save_gu: bool = False, site: Any = None):
     """Gather ``x`` over the group and multiply in one launch.
 
     Returns ``(x_full, y)`` or, with ``w2`` (SwiGLU), ``(x_full, h, g, u)``. ``w`` is ``[N, K]``
-    (``[K, N]`` with ``b_mn``).
+    (``[K, N]`` with ``b_mn``). With a ``site`` key (any hashable that names the call site) and more than two
+    ranks the gather is a push into a persistent symmetric buffer of that site, and ``x_full`` is a view of it
+    that stays valid until the site runs again; otherwise slices are pulled into a fresh tensor.
     """
     rows, K = x_local.shape
     M = rows * tp.size
@@ -190,6 +241,8 @@ def ag_gemm(tp: TPState, x_local: torch.Tensor, w: torch.Tensor, w2: torch.Tenso
             return x_full, gemm.gemm(x_full, w, b_mn=b_mn, bias=bias)
         h, g, u = gemm.swiglu_gemm(x_full, w, w2, save_gu=save_gu)
         return x_full, h, g, u
+    if site is not None and tp.size >= tp.push_min_world and rows % 128 == 0:
+        return _ag_gemm_push(tp, x_local.contiguous(), w, w2, b_mn, bias, save_gu, site)
     buf, _, _ = _publish_rows(tp, x_local.contiguous())
     fr = _flag_rows(rows)
     tasks, n_tasks = tp.gather_tasks(rows, K, fr)
@@ -209,6 +262,38 @@ def ag_gemm(tp: TPState, x_local: torch.Tensor, w: torch.Tensor, w2: torch.Tenso
         N, M, N, K, _lib.ptr(bias), _lib.ptr(tasks), n_tasks, buf.peers.c, tp.size, _lib.ptr(x_full), _lib.ptr(flags),
         fr, epoch, (tp.rank * rows) // 128, tp.n_copy, _lib.ptr(_lib.status_word(x_local.device)), _lib.stream())
     _lib.check(rc, "ob_gemm_ag_act_bf16")
+    if w2 is None:
+        return x_full, y
+    return x_full, y, g, u
+
+
+def _ag_gemm_push(tp: TPState, x_local: torch.Tensor, w, w2, b_mn: bool, bias, save_gu: bool, site_key: Any):
+    rows, K = x_local.shape
+    M = rows * tp.size
+    N = w.shape[1] if b_mn else w.shape[0]
+    fr = 128
+    site = _site_of(tp, (site_key, M, K), M * K, M // fr)
+    site.epoch += 1
+    x_full = site.buf.tensor[: M * K].view(M, K)
+    lo = tp.rank * rows
+    x_full[lo:lo + rows].copy_(x_local)
+    site.flags.tensor[lo // fr:(lo + rows) // fr].fill_(site.epoch)
+    # every rank has finished reading this site's previous contents (its last reader ran before this point in
+    # stream order on each rank) once all ranks have arrived here
+    tp.barrier()
+    tasks, n_tasks = _push_tasks_of(tp, rows, K, fr)
+    dev = x_local.device
+    y = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    g = u = None
+    if w2 is not None and save_gu:
+        g = torch.empty_like(y)
+        u = torch.empty_like(y)
+    rc = _lib.lib().ob_gemm_ag_push_bf16(
+        _lib.ptr(x_full), K, _lib.ptr(x_local), lo * K, _lib.ptr(w), _lib.ptr(w2), w.stride(0), int(b_mn), _lib.ptr(y),
+        _lib.ptr(g), _lib.ptr(u), N, M, N, K, _lib.ptr(bias), _lib.ptr(tasks), n_tasks, site.buf.peers.c,
+        site.flags.peers.c, tp.size, _lib.ptr(site.flags.tensor), fr, site.epoch, lo // 128, tp.n_push,
+        _lib.ptr(_lib.status_word(dev)), _lib.stream())
+    _lib.check(rc, "ob_gemm_ag_push_bf16")
     if w2 is None:
         return x_full, y
     return x_full, y, g, u
@@ -305,7 +390,7 @@ class _ColumnParallel(torch.autograd.Function):
             if bias is not None:
                 y = y + bias
         elif sp:
-            x_full, y = ag_gemm(tp, x, wf, bias=bias)
+            x_full, y = ag_gemm(tp, x, wf, bias=bias, site=("col", id(ws[0])))
         else:
             x_full, y = x, gemm.gemm(x, wf, bias=bias)
         ctx.save_for_backward(x_full, *ws)
@@ -350,7 +435,7 @@ class _ColumnParallelSwiGLU(torch.autograd.Function):
     @staticmethod
     def forward(ctx, tp: TPState, sp: bool, x, w1, w2):
         if sp:
-            x_full, h, g, u = ag_gemm(tp, x, w1, w2, save_gu=True)
+            x_full, h, g, u = ag_gemm(tp, x, w1, w2, save_gu=True, site=("glu", id(w1)))
         else:
             x_full = x
             h, g, u = gemm.swiglu_gemm(x, w1, w2, save_gu=True)
@@ -423,7 +508,7 @@ class _RowParallel(torch.autograd.Function):
             dy_full = all_gather_rows(tp, dy2) if ctx.sp else dy2
             dx = fp8_ops.dgrad_product(dy_full, [ctx.param])
         elif ctx.sp:
-            dy_full, dx = ag_gemm(tp, dy2, w, b_mn=True)
+            dy_full, dx = ag_gemm(tp, dy2, w, b_mn=True, site=("row_bwd", id(ctx.param)))
         else:
             dy_full, dx = dy2, gemm.gemm(dy2, w, b_mn=True)
         dw = _weight_grads([ctx.param], dy_full, x, [w.shape[0]], [ctx.needs_input_grad[3]])[0]

@@ -11,8 +11,8 @@ pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _run(script: str, nproc: int, port: int, *args: str, timeout: int = 600) -> str:
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+def _run(script: str, nproc: int, port: int, *args: str, timeout: int = 600, extra_env: dict | None = None) -> str:
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", **(extra_env or {}))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, script), *args]
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
@@ -56,4 +56,12 @@ def test_tensor_parallel_times_sharded_data_parallel(unique_port, tp):
 def test_tensor_parallel_fp8(unique_port):
     """Block-scaled FP8 projections under tensor + sequence parallelism stay close to the unsharded bf16 model."""
     out = _run("_mp_tp_check.py", 2, unique_port, "nccl", "llama", "1", str(unique_port), "fp8")
+    assert "TP_OK" in out, out[-4000:]
+
+
+@pytest.mark.parametrize("kind", ["llama", "qwen3"])
+def test_tensor_parallel_push_all_gather(unique_port, kind):
+    """The push form of the fused all-gather (default from 3 ranks on) forced on at 2 ranks."""
+    out = _run("_mp_tp_check.py", 2, unique_port, "nccl", kind, "1", str(unique_port),
+               extra_env={"OB_TP_PUSH_MIN_WORLD": "2"})
     assert "TP_OK" in out, out[-4000:]
