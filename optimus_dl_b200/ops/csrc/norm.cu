@@ -29,8 +29,8 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return t;
 }
 
-template <bool LAYERNORM>
-__global__ void __launch_bounds__(THREADS)
+template <bool LAYERNORM, int NVEC>
+__global__ void __launch_bounds__(THREADS, NVEC <= 2 ? 6 : 2)
 norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
                 const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ b,
                 __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ h_out, float* __restrict__ rstd_out,
@@ -40,10 +40,10 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * D);
     const uint4* rr = residual ? reinterpret_cast<const uint4*>(residual + (size_t)row * D) : nullptr;
-    float v[MAX_VEC][8];
+    float v[NVEC][8];
     float s = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int i = 0; i < MAX_VEC; ++i) {
+    for (int i = 0; i < NVEC; ++i) {
       const int idx = threadIdx.x + i * THREADS;
       if (idx < nvec) {
         uint4 u = xr[idx];
@@ -69,7 +69,7 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
       mean = block_sum(s, red) / D;
       float var = 0.f;
 #pragma unroll
-      for (int i = 0; i < MAX_VEC; ++i) {
+      for (int i = 0; i < NVEC; ++i) {
         const int idx = threadIdx.x + i * THREADS;
         if (idx < nvec) {
 #pragma unroll
@@ -86,7 +86,7 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
     }
     uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * D);
 #pragma unroll
-    for (int i = 0; i < MAX_VEC; ++i) {
+    for (int i = 0; i < NVEC; ++i) {
       const int idx = threadIdx.x + i * THREADS;
       if (idx < nvec) {
         uint4 wu = reinterpret_cast<const uint4*>(w)[idx];
@@ -222,15 +222,31 @@ reduce_partials_kernel(const float* __restrict__ partial, int nparts, int D, __n
 
 using namespace ob::norm;
 
-static int norm_grid(int rows) {
+static int sm_count_() {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  int g = sms * 4;
+  return sms;
+}
+// Resident CTAs per SM follow the launch bounds of the kernels (backward: 3, forward: 6 for rows up to 4096 wide),
+// so every CTA of the grid is running and each keeps one row in flight.
+static int norm_grid(int rows) {
+  const int g = sm_count_() * 3;
+  return rows < g ? rows : g;
+}
+static int norm_fwd_grid(int rows) {
+  const int g = sm_count_() * 6;
   return rows < g ? rows : g;
 }
 
 extern "C" int ob_norm_bwd_grid(int rows) { return norm_grid(rows); }
+
+#define OB_NORM_FWD_LAUNCH(LN, D, grid, ...)                                              \
+  do {                                                                                     \
+    if ((D) <= THREADS * 8) norm_fwd_kernel<LN, 1><<<grid, THREADS, 0, stream>>>(__VA_ARGS__);            \
+    else if ((D) <= THREADS * 16) norm_fwd_kernel<LN, 2><<<grid, THREADS, 0, stream>>>(__VA_ARGS__);      \
+    else norm_fwd_kernel<LN, 4><<<grid, THREADS, 0, stream>>>(__VA_ARGS__);                               \
+  } while (0)
 
 #define OB_NORM_BWD_LAUNCH(LN, D, ...)                                                     \
   do {                                                                                     \
@@ -246,8 +262,7 @@ extern "C" int ob_rmsnorm_fwd(const void* x, const void* residual, const void* w
                               int rows, int D, float eps, cudaStream_t stream) {
   if (!norm_args_ok(D)) return -1;
   if (rows == 0) return 0;
-  norm_fwd_kernel<false><<<norm_grid(rows), THREADS, 0, stream>>>(
-      (const __nv_bfloat16*)x, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)w, nullptr, (__nv_bfloat16*)y,
+  OB_NORM_FWD_LAUNCH(false, D, norm_fwd_grid(rows), (const __nv_bfloat16*)x, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)w, nullptr, (__nv_bfloat16*)y,
       (__nv_bfloat16*)h_out, (float*)rstd, nullptr, rows, D, eps);
   return (int)cudaGetLastError();
 }
@@ -273,8 +288,7 @@ extern "C" int ob_layernorm_fwd(const void* x, const void* w, const void* b, voi
                                 int D, float eps, cudaStream_t stream) {
   if (!norm_args_ok(D)) return -1;
   if (rows == 0) return 0;
-  norm_fwd_kernel<true><<<norm_grid(rows), THREADS, 0, stream>>>(
-      (const __nv_bfloat16*)x, nullptr, (const __nv_bfloat16*)w, (const __nv_bfloat16*)b, (__nv_bfloat16*)y, nullptr,
+  OB_NORM_FWD_LAUNCH(true, D, norm_fwd_grid(rows), (const __nv_bfloat16*)x, nullptr, (const __nv_bfloat16*)w, (const __nv_bfloat16*)b, (__nv_bfloat16*)y, nullptr,
       (float*)rstd, (float*)mean, rows, D, eps);
   return (int)cudaGetLastError();
 }
