@@ -67,9 +67,9 @@ class TPState:
         self._tasks: dict = {}
         self.n_copy = 16
         self.n_push = 8              # copy CTAs of the push all-gather (posted stores need few)
-        # from this group size on the fused all-gather pushes instead of pulling (with two ranks the pull
-        # form is as fast and needs no persistent buffers); OB_TP_PUSH_MIN_WORLD overrides it for tests
-        self.push_min_world = int(os.environ.get("OB_TP_PUSH_MIN_WORLD", "3"))
+        # from this group size on the fused all-gather pushes instead of pulling (the pull
+        # form needs no persistent buffers and remains for call sites without a site key); OB_TP_PUSH_MIN_WORLD overrides it
+        self.push_min_world = int(os.environ.get("OB_TP_PUSH_MIN_WORLD", "2"))
         self._sites: dict = {}       # persistent gathered-operand buffers, one per call site
         self._push_tasks: dict = {}
 

@@ -60,8 +60,8 @@ def test_tensor_parallel_fp8(unique_port):
 
 
 @pytest.mark.parametrize("kind", ["llama", "qwen3"])
-def test_tensor_parallel_push_all_gather(unique_port, kind):
-    """The push form of the fused all-gather (default from 3 ranks on) forced on at 2 ranks."""
+def test_tensor_parallel_pull_all_gather(unique_port, kind):
+    """The pull form of the fused all-gather (the push form is the default) forced on."""
     out = _run("_mp_tp_check.py", 2, unique_port, "nccl", kind, "1", str(unique_port),
-               extra_env={"OB_TP_PUSH_MIN_WORLD": "2"})
+               extra_env={"OB_TP_PUSH_MIN_WORLD": "99"})
     assert "TP_OK" in out, out[-4000:]
