@@ -227,28 +227,40 @@ __device__ __forceinline__ uint8_t to_e4m3(float x) {
   return (uint8_t)__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
 }
 
-// 1 x 128 blocks along the contiguous dimension of x [rows, cols]: one warp per (row, block).
+// 1 x 128 blocks along the contiguous dimension of x [rows, cols]: 16 threads per block, 8 elements (one
+// 16-byte load) per thread, block maximum by four shuffles inside the half-warp.
 // q [rows, cols] e4m3; scales stored [cols/128][scale_ld].
 __global__ void __launch_bounds__(256)
 quant_rowwise_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ q, long long ldq,
                      float* __restrict__ scales, long long scale_ld, int rows, int cols) {
-  const int blocks_per_row = cols / 128;
-  const long long total = (long long)rows * blocks_per_row;
+  const int vec_per_row = cols / 8;
+  const long long total = (long long)rows * vec_per_row;   // a multiple of 16 (cols % 128 == 0)
+  const long long stride = (long long)gridDim.x * blockDim.x;
   const int lane = threadIdx.x & 31;
-  for (long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; w < total;
-       w += ((long long)gridDim.x * blockDim.x) >> 5) {
-    const int row = (int)(w / blocks_per_row);
-    const int kb = (int)(w - (long long)row * blocks_per_row);
-    const uint2 raw = *reinterpret_cast<const uint2*>(x + (long long)row * ldx + kb * 128 + lane * 4);
-    const float2 a = unpack_bf16x2(raw.x), b = unpack_bf16x2(raw.y);
-    float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y)));
-    amax = warp_max(amax);
+  // the loop bound is uniform per warp (all 32 lanes take part in the shuffles); a half-warp past the end idles
+  for (long long base = (long long)blockIdx.x * blockDim.x + (threadIdx.x - lane); base < total; base += stride) {
+    const long long i = base + lane;
+    const bool live = i < total;
+    const int row = live ? (int)(i / vec_per_row) : 0;
+    const int v = live ? (int)(i - (long long)row * vec_per_row) : 0;
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (live) raw = *reinterpret_cast<const uint4*>(x + (long long)row * ldx + v * 8);
+    const float2 a = unpack_bf16x2(raw.x), b = unpack_bf16x2(raw.y), c = unpack_bf16x2(raw.z), d = unpack_bf16x2(raw.w);
+    float amax = fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y))),
+                       fmaxf(fmaxf(fabsf(c.x), fabsf(c.y)), fmaxf(fabsf(d.x), fabsf(d.y))));
+#pragma unroll
+    for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     const float scale = amax > 0.f ? amax / E4M3_MAX : 1.0f;
     const float inv = 1.0f / scale;
-    const uint32_t packed = (uint32_t)to_e4m3(a.x * inv) | ((uint32_t)to_e4m3(a.y * inv) << 8) |
-                            ((uint32_t)to_e4m3(b.x * inv) << 16) | ((uint32_t)to_e4m3(b.y * inv) << 24);
-    *reinterpret_cast<uint32_t*>(q + (long long)row * ldq + kb * 128 + lane * 4) = packed;
-    if (lane == 0) scales[(long long)kb * scale_ld + row] = scale;
+    uint2 packed;
+    packed.x = (uint32_t)to_e4m3(a.x * inv) | ((uint32_t)to_e4m3(a.y * inv) << 8) |
+               ((uint32_t)to_e4m3(b.x * inv) << 16) | ((uint32_t)to_e4m3(b.y * inv) << 24);
+    packed.y = (uint32_t)to_e4m3(c.x * inv) | ((uint32_t)to_e4m3(c.y * inv) << 8) |
+               ((uint32_t)to_e4m3(d.x * inv) << 16) | ((uint32_t)to_e4m3(d.y * inv) << 24);
+    if (live) {
+      *reinterpret_cast<uint2*>(q + (long long)row * ldq + v * 8) = packed;
+      if ((v & 15) == 0) scales[(long long)(v >> 4) * scale_ld + row] = scale;
+    }
   }
 }
 
@@ -356,9 +368,9 @@ extern "C" int ob_gemm_fp8_block(const void* A8, long long lda, const void* sa, 
 extern "C" int ob_quant_fp8_rowwise(const void* x, long long ldx, void* q, long long ldq, void* scales,
                                     long long scale_ld, int rows, int cols, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return 0;
-  if (cols % 128 != 0 || ldx % 4 != 0 || ldq % 4 != 0) return -1;
-  const long long warps = (long long)rows * (cols / 128);
-  long long blocks = (warps + 7) / 8;
+  if (cols % 128 != 0 || ldx % 8 != 0 || ldq % 8 != 0) return -1;
+  const long long vecs = (long long)rows * (cols / 8);
+  long long blocks = (vecs + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   quant_rowwise_kernel<<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq, (float*)scales,
                                                         scale_ld, rows, cols);

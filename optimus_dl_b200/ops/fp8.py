@@ -68,7 +68,7 @@ def quantize_rowwise(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     rows, cols = x.shape
     if not kernel_ok(x) or cols % BLOCK != 0:
         return quantize_rowwise_ref(x)
-    if x.stride(1) != 1 or x.stride(0) % 4 != 0:
+    if x.stride(1) != 1 or x.stride(0) % 8 != 0 or x.data_ptr() % 16 != 0:
         x = x.contiguous()
     q = torch.empty((rows, cols), dtype=torch.float8_e4m3fn, device=x.device)
     scales = torch.empty((cols // BLOCK, rows), dtype=torch.float32, device=x.device)
