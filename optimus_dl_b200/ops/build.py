@@ -100,6 +100,9 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     return LIB_PATH
 
 
+def main() -> None:
+    print(build(verbose="-v" in sys.argv, force="-f" in sys.argv))
+
+
 if __name__ == "__main__":
-    path = build(verbose="-v" in sys.argv, force="-f" in sys.argv)
-    print(path)
+    main()
