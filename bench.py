@@ -100,7 +100,9 @@ def main() -> None:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (with sequence parallelism and the sharded "
                                                       "loss); the remaining ranks form the sharded data-parallel group")
-    ap.add_argument("--fp8", action="store_true", help="block-scaled e4m3 GEMMs for the transformer blocks' linear layers")
+    ap.add_argument("--fp8", action="store_true", help="e4m3 GEMMs for the transformer blocks' linear layers")
+    ap.add_argument("--fp8-recipe", default="blockwise", choices=["blockwise", "tensorwise", "delayed"],
+                    help="scaling scheme of --fp8 (1x128 / 128x128 blocks, per tensor, per tensor from a history)")
     ap.add_argument("--acc-steps", type=int, default=1, help="micro-batches accumulated per optimizer step")
     ap.add_argument("--packed-docs", action="store_true", help="each sequence is packed from documents with exponential "
                     "lengths (mean 2048, min 32) and attends block-diagonally")
@@ -191,12 +193,13 @@ def main() -> None:
 
     import contextlib
 
-    from optimus_dl_b200.amp.fp8 import FP8Recipe
+    from optimus_dl_b200.amp.fp8 import FP8Recipe, Fp8Format, parse_fp8_recipe
 
-    fp8_recipe = FP8Recipe() if args.fp8 else None
+    fp8_recipe = FP8Recipe(Fp8Format.E4M3, parse_fp8_recipe(args.fp8_recipe)) if args.fp8 else None
 
     def train_step(ids: torch.Tensor) -> torch.Tensor:
-        with (fp8_recipe.autocast(True) if fp8_recipe is not None else contextlib.nullcontext()):
+        # the backward context is the autocast context plus the delayed-scaling history update on exit
+        with (fp8_recipe.backward(True) if fp8_recipe is not None else contextlib.nullcontext()):
             return _train_step(ids)
 
     def _train_step(ids: torch.Tensor) -> torch.Tensor:
@@ -277,7 +280,7 @@ def main() -> None:
             else f"{args.model} bf16 train tokens/s (device-timed, max/rank)",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "fp8 e4m3 block-scaled GEMMs, bf16 elsewhere" if args.fp8 else "bf16",
+            "dtype": f"fp8 e4m3 {args.fp8_recipe} GEMMs, bf16 elsewhere" if args.fp8 else "bf16",
             "data": "synthetic uniform-random token ids, random-init weights",
             "impl": "ours",
             "config": {"model": args.model, "global_batch": dp * mb * acc, "seq_len": seq,

@@ -1,12 +1,14 @@
 """FP8 recipe surface (optimus_dl/modules/amp/fp8.py:40-523).
 
-The reference drives NVIDIA Transformer Engine recipes; here FP8 means this package's own
-block-scaled e4m3 GEMM path (``ops/fp8.py``): activations are quantised per 1x128 block, weights per
-128x128 block, products accumulate in fp32 and are written in bf16. ``FP8Recipe.autocast()`` switches
-the linear layers converted by the ``transformer_engine`` model transform to that path for the
-duration of the context (forward and, through ``backward()``, the backward pass). Enum names and
-string parsers follow the reference; ``delayed`` / ``tensorwise`` / ``mxfp8`` recipes are accepted and
-mapped onto the block-scaled implementation, which needs no amax history.
+The reference drives NVIDIA Transformer Engine recipes; here FP8 means this package's own e4m3 GEMM
+paths (``ops/fp8.py``). ``blockwise``: activations quantised per 1x128 block, weights per 128x128 block,
+products scaled per 128-wide k-block. ``tensorwise``: one scale per tensor from its own maximum
+(current scaling). ``delayed``: one scale per tensor from a history of maxima (``amax_history_len``,
+``amax_compute_algo`` in {``max``, ``most_recent``}, ``margin``), refreshed once per backward pass.
+``mxfp8`` is served by the ``blockwise`` implementation (the closest fine-grained scheme built here).
+``FP8Recipe.autocast()`` switches the linear layers converted by the ``transformer_engine`` model
+transform to the FP8 path for the duration of the context (forward and, through ``backward()``, the
+backward pass). Enum names and string parsers follow the reference.
 """
 
 from __future__ import annotations
@@ -69,6 +71,12 @@ def fp8_enabled() -> bool:
 class FP8Recipe:
     def __init__(self, fmt: Fp8Format = Fp8Format.E4M3, recipe: Fp8RecipeType = Fp8RecipeType.BLOCKWISE, **options: Any):
         self.format, self.recipe, self.options = fmt, recipe, options
+        self.delayed_state = None
+        if recipe == Fp8RecipeType.DELAYED:
+            from ..ops.fp8 import DelayedScaling
+
+            self.delayed_state = DelayedScaling(history=int(options.get("amax_history_len", 16) or 16),
+                                                algo=str(options.get("amax_compute_algo", "max") or "max"))
 
     @contextlib.contextmanager
     def autocast(self, enabled: bool = True):
@@ -79,8 +87,13 @@ class FP8Recipe:
         finally:
             _state.update(prev)
 
+    @contextlib.contextmanager
     def backward(self, enabled: bool = True):
-        return self.autocast(enabled)
+        """Context for the backward pass; on exit the delayed-scaling histories take this pass's maxima."""
+        with self.autocast(enabled):
+            yield self
+        if enabled and self.delayed_state is not None:
+            self.delayed_state.update(float(2.0 ** int(self.options.get("margin", 0) or 0)))
 
     def __repr__(self) -> str:
         return f"FP8Recipe(format={self.format.value}, recipe={self.recipe.value})"
@@ -94,9 +107,10 @@ def create_fp8_recipe(cfg: Any) -> FP8Recipe | None:
         logger.warning("fp8 requested but no CUDA device is present; running without fp8")
         return None
     fmt, rec = parse_fp8_format(cfg.get("format", "e4m3")), parse_fp8_recipe(cfg.get("recipe", "blockwise"))
-    if rec != Fp8RecipeType.BLOCKWISE:
-        logger.info("fp8 recipe %s is served by the block-scaled e4m3 implementation", rec.value)
-    return FP8Recipe(fmt, rec, margin=cfg.get("margin", 0))
+    if rec == Fp8RecipeType.MXFP8:
+        logger.info("fp8 recipe mxfp8 is served by the block-scaled (1x128 / 128x128) e4m3 implementation")
+    return FP8Recipe(fmt, rec, margin=cfg.get("margin", 0), amax_history_len=cfg.get("amax_history_len", 1024),
+                     amax_compute_algo=cfg.get("amax_compute_algo", "max"))
 
 
 @contextlib.contextmanager

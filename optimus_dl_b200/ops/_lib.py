@@ -189,7 +189,11 @@ def _declare(l: ctypes.CDLL) -> None:
     sig("ob_gemm_rs_bf16", [P, L, I, P, L, I, P, PP, I, I, I, L, I, I, I, I, P, P])
     sig("ob_gemm_fp8_block", [P, L, P, L, P, L, P, P, L, I, I, I, P, P])
     sig("ob_quant_fp8_rowwise", [P, L, P, L, P, L, I, I, P])
-    sig("ob_quant_fp8_block", [P, L, P, L, P, L, P, P, I, I, P])
+    sig("ob_quant_fp8_block", [P, L, P, L, P, L, P, P, I, I, P, P])
+    sig("ob_gemm_fp8_tensor", [P, L, P, P, L, P, P, L, I, I, I, P, P])
+    sig("ob_fp8_amax_scale", [P, L, I, I, P, P, F, P])
+    sig("ob_quant_fp8_tensor", [P, L, P, L, P, P, I, I, P])
+    sig("ob_fp8_delayed_update", [P, I, I, I, F, I, P])
     sig("ob_attn_decode", [P, L, P, P, L, P, P, L, L, L, P, P, L, P, P, I, I, I, I, I, I, F, I, P])
     sig("ob_sample", [P, I, L, I, I, F, I, F, I, ctypes.c_uint64, ctypes.c_uint64, P, P])
     sig("ob_embedding_push", [P, I, P, I, I, I, PP, I, I, P])

@@ -97,6 +97,13 @@ def bench_gemm_fp8(t: Timer, sizes) -> None:
         msq = t(lambda: fp8.quantize_rowwise(a))
         _emit("gemm_fp8_block", dict(M=M, N=N, K=K), ms, flops=2.0 * M * N * K, quant_rowwise_ms=round(msq, 4),
               quant_gbs=round(M * K * 3 / msq / 1e6, 1))
+        t8, st = fp8.quantize_tensor(a)
+        w8, sw, _ = fp8.quantize_weight_tensor(b)
+        ms = t(lambda: fp8.gemm_fp8_tensor(t8, st, w8, sw, out=out))
+        ms_cur = t(lambda: fp8.quantize_tensor(a))
+        ms_del = t(lambda: fp8.quantize_tensor(a, scale=st))
+        _emit("gemm_fp8_tensor", dict(M=M, N=N, K=K), ms, flops=2.0 * M * N * K, quant_current_ms=round(ms_cur, 4),
+              quant_given_scale_ms=round(ms_del, 4), quant_given_scale_gbs=round(M * K * 3 / ms_del / 1e6, 1))
 
 
 def bench_attention(t: Timer, cases) -> None:

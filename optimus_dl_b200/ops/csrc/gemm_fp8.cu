@@ -59,6 +59,10 @@ __device__ __forceinline__ void tile_of(int tile, int tiles_m, int tiles_n, int&
   tn = r / gm;
 }
 
+// PER_TENSOR = false: block-scaled product (each 128-wide k-block is drained from TMEM and scaled in registers).
+// PER_TENSOR = true: one scale per operand (p.sa[0] * p.sb[0]); the tensor core accumulates over all of K in
+// TMEM and the epilogue drains each tile once, so the main loop runs at the plain e4m3 rate.
+template <bool PER_TENSOR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -124,8 +128,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       int slot = 0; uint32_t slot_phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (PER_TENSOR) ok = mbar_wait(&part_empty[slot], slot_phase ^ 1, abort_flag, p.status);
         for (int kb = 0; kb < k_blocks && ok; ++kb) {
-          ok = mbar_wait(&part_empty[slot], slot_phase ^ 1, abort_flag, p.status);
+          if (!PER_TENSOR) ok = mbar_wait(&part_empty[slot], slot_phase ^ 1, abort_flag, p.status);
           if (!ok) break;
           ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status);
           if (!ok) break;
@@ -137,12 +142,14 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           for (int kk = 0; kk < BK / UMMA_K; ++kk) {
             const uint64_t da = make_smem_desc_sw128(sA + kk * 32, 16, 1024);
             const uint64_t db = make_smem_desc_sw128(sB + kk * 32, 16, 1024);
-            umma_f8_ss(d_tmem, da, db, idesc, kk ? 1u : 0u);
+            umma_f8_ss(d_tmem, da, db, idesc, (kk != 0 || (PER_TENSOR && kb != 0)) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);
-          umma_commit(&part_full[slot]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
-          if (++slot == SLOTS) { slot = 0; slot_phase ^= 1; }
+          if (!PER_TENSOR || kb == k_blocks - 1) {
+            umma_commit(&part_full[slot]);
+            if (++slot == SLOTS) { slot = 0; slot_phase ^= 1; }
+          }
         }
       }
     }
@@ -153,6 +160,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     int slot = 0; uint32_t slot_phase = 0;
     bool ok = true;
     const int sb_ld = k_blocks;
+    const int drains = PER_TENSOR ? 1 : k_blocks;
+    const float tensor_scale = PER_TENSOR ? p.sa[0] * p.sb[0] : 0.f;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int tm, tn;
       tile_of(tile, tiles_m, tiles_n, tm, tn);
@@ -160,19 +169,19 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const int col0 = tn * BN + chunk * EPI_COLS;
       const bool row_ok = row < p.M;
       const bool cols_ok = col0 < p.N;
-      const float* sa_row = p.sa + (row_ok ? row : 0);
-      const float* sb_row = p.sb + (long long)(cols_ok ? col0 / 128 : 0) * sb_ld;
+      const float* sa_row = p.sa + (row_ok && !PER_TENSOR ? row : 0);
+      const float* sb_row = p.sb + (PER_TENSOR ? 0 : (long long)(cols_ok ? col0 / 128 : 0) * sb_ld);
       float acc[EPI_COLS];
 #pragma unroll
       for (int j = 0; j < EPI_COLS; ++j) acc[j] = 0.f;
       // scales are fetched two k-blocks ahead: their global-load latency must not sit between the barrier
       // and the first use
       float sa0 = sa_row[0], sb0 = sb_row[0];
-      float sa1 = k_blocks > 1 ? sa_row[p.sa_ld] : 0.f, sb1 = k_blocks > 1 ? sb_row[1] : 0.f;
-      for (int kb = 0; kb < k_blocks; ++kb) {
-        const float s = sa0 * sb0;
+      float sa1 = drains > 1 ? sa_row[p.sa_ld] : 0.f, sb1 = drains > 1 ? sb_row[1] : 0.f;
+      for (int kb = 0; kb < drains; ++kb) {
+        const float s = PER_TENSOR ? tensor_scale : sa0 * sb0;
         sa0 = sa1; sb0 = sb1;
-        if (kb + 2 < k_blocks) { sa1 = sa_row[(long long)(kb + 2) * p.sa_ld]; sb1 = sb_row[kb + 2]; }
+        if (kb + 2 < drains) { sa1 = sa_row[(long long)(kb + 2) * p.sa_ld]; sb1 = sb_row[kb + 2]; }
         ok = mbar_wait(&part_full[slot], slot_phase, abort_flag, p.status);
         if (!ok) break;
         tc_fence_after();
@@ -266,11 +275,12 @@ quant_rowwise_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t
 
 // 128 x 128 blocks of w [rows, cols]: one CTA (256 threads) per block.  Writes q [rows, cols] and,
 // when qt != nullptr, the transposed copy qt [cols, rows]; scales [rows/128][cols/128] and the
-// transposed table scales_t [cols/128][rows/128].
+// transposed table scales_t [cols/128][rows/128].  With tensor_scale != nullptr every block uses that one scale
+// (per-tensor scaling) and no scale table is written.
 __global__ void __launch_bounds__(256)
 quant_block_kernel(const __nv_bfloat16* __restrict__ w, long long ldw, uint8_t* __restrict__ q, long long ldq,
                    uint8_t* __restrict__ qt, long long ldqt, float* __restrict__ scales, float* __restrict__ scales_t,
-                   int rows, int cols) {
+                   int rows, int cols, const float* __restrict__ tensor_scale) {
   __shared__ float s_red[8];
   __shared__ uint8_t tile[128][132];
   const int bc = blockIdx.x, br = blockIdx.y;
@@ -297,9 +307,9 @@ quant_block_kernel(const __nv_bfloat16* __restrict__ w, long long ldw, uint8_t* 
   amax = s_red[0];
 #pragma unroll
   for (int i = 1; i < 8; ++i) amax = fmaxf(amax, s_red[i]);
-  const float scale = amax > 0.f ? amax / E4M3_MAX : 1.0f;
+  const float scale = tensor_scale ? *tensor_scale : (amax > 0.f ? amax / E4M3_MAX : 1.0f);
   const float inv = 1.0f / scale;
-  if (tid == 0) {
+  if (tid == 0 && scales) {
     scales[(long long)br * gridDim.x + bc] = scale;
     if (scales_t) scales_t[(long long)bc * gridDim.y + br] = scale;
   }
@@ -329,6 +339,111 @@ quant_block_kernel(const __nv_bfloat16* __restrict__ w, long long ldw, uint8_t* 
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Per-tensor scaling: one fp32 scale for the whole tensor (current scaling: from this tensor's own maximum;
+// delayed scaling: from a history of earlier maxima).
+
+__device__ __forceinline__ float amax8(const uint4& raw) {
+  const float2 a = unpack_bf16x2(raw.x), b = unpack_bf16x2(raw.y), c = unpack_bf16x2(raw.z), d = unpack_bf16x2(raw.w);
+  return fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y))),
+               fmaxf(fmaxf(fabsf(c.x), fabsf(c.y)), fmaxf(fabsf(d.x), fabsf(d.y))));
+}
+
+__device__ __forceinline__ float block_max_256(float v, float* s_red) {
+  v = warp_max(v);
+  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float m = s_red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) m = fmaxf(m, s_red[i]);
+  return m;
+}
+
+// |x| maximum of x [rows, cols] -> *scale_out = max / 448 * margin_mul (1 when the tensor is all zero).
+// ws = {running maximum (float bits), ticket}; both are zero on entry and are left zero by the last block.
+__global__ void __launch_bounds__(256)
+amax_scale_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int rows, int cols, unsigned* __restrict__ ws,
+                  float* __restrict__ scale_out, float margin_mul) {
+  __shared__ float s_red[8];
+  const int vec_per_row = cols / 8;
+  const long long total = (long long)rows * vec_per_row;
+  float m = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int row = (int)(i / vec_per_row);
+    const int v = (int)(i - (long long)row * vec_per_row);
+    m = fmaxf(m, amax8(*reinterpret_cast<const uint4*>(x + (long long)row * ldx + v * 8)));
+  }
+  m = block_max_256(m, s_red);
+  if (threadIdx.x == 0) {
+    atomicMax(&ws[0], __float_as_uint(m));     // non-negative floats order like their bit patterns
+    __threadfence();
+    const unsigned ticket = atomicAdd(&ws[1], 1u);
+    if (ticket == gridDim.x - 1) {
+      __threadfence();
+      const float amax = __uint_as_float(atomicExch(&ws[0], 0u));
+      ws[1] = 0u;
+      *scale_out = amax > 0.f ? amax / E4M3_MAX * margin_mul : 1.0f;
+    }
+  }
+}
+
+// q = e4m3(x / *scale); when amax_rec != nullptr the tensor's |x| maximum is also folded into *amax_rec
+// (float bits, atomic maximum) for the delayed-scaling history.
+__global__ void __launch_bounds__(256)
+quant_tensor_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ q, long long ldq,
+                    const float* __restrict__ scale, unsigned* __restrict__ amax_rec, int rows, int cols) {
+  __shared__ float s_red[8];
+  const int vec_per_row = cols / 8;
+  const long long total = (long long)rows * vec_per_row;
+  const float inv = 1.0f / *scale;
+  float m = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int row = (int)(i / vec_per_row);
+    const int v = (int)(i - (long long)row * vec_per_row);
+    const uint4 raw = *reinterpret_cast<const uint4*>(x + (long long)row * ldx + v * 8);
+    if (amax_rec) m = fmaxf(m, amax8(raw));
+    const float2 a = unpack_bf16x2(raw.x), b = unpack_bf16x2(raw.y), c = unpack_bf16x2(raw.z), d = unpack_bf16x2(raw.w);
+    uint2 packed;
+    packed.x = (uint32_t)to_e4m3(a.x * inv) | ((uint32_t)to_e4m3(a.y * inv) << 8) |
+               ((uint32_t)to_e4m3(b.x * inv) << 16) | ((uint32_t)to_e4m3(b.y * inv) << 24);
+    packed.y = (uint32_t)to_e4m3(c.x * inv) | ((uint32_t)to_e4m3(c.y * inv) << 8) |
+               ((uint32_t)to_e4m3(d.x * inv) << 16) | ((uint32_t)to_e4m3(d.y * inv) << 24);
+    *reinterpret_cast<uint2*>(q + (long long)row * ldq + v * 8) = packed;
+  }
+  if (amax_rec) {
+    m = block_max_256(m, s_red);
+    if (threadIdx.x == 0 && m > 0.f) atomicMax(amax_rec, __float_as_uint(m));
+  }
+}
+
+// Delayed-scaling bookkeeping, one block per tensor.  state[i] = {scale, recorded maximum (float bits), hist[H]}:
+// the recorded maximum moves into hist[pos], is cleared, and the scale becomes max(hist) / 448 * margin_mul
+// (use_max) or the newest maximum / 448 * margin_mul; a tensor that recorded nothing keeps its scale.
+__global__ void __launch_bounds__(128)
+delayed_update_kernel(float* __restrict__ state, int H, int pos, float margin_mul, int use_max) {
+  __shared__ float s_red[4];
+  float* st = state + (long long)blockIdx.x * (2 + H);
+  if (threadIdx.x == 0) {
+    st[2 + pos] = __uint_as_float(reinterpret_cast<unsigned*>(st)[1]);
+    reinterpret_cast<unsigned*>(st)[1] = 0u;
+  }
+  __syncthreads();
+  float m = 0.f;
+  if (use_max) {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) m = fmaxf(m, st[2 + i]);
+  } else if (threadIdx.x == 0) {
+    m = st[2 + pos];
+  }
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    m = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
+    if (m > 0.f) st[0] = m / E4M3_MAX * margin_mul;
+  }
+}
+
 }  // namespace fp8
 }  // namespace ob
 
@@ -337,9 +452,9 @@ using namespace ob::fp8;
 
 // C[M,N] bf16 from e4m3 A8 [M,K], B8 [N,K] with scales sa [K/128][sa_ld], sb [ceil(N/128)][K/128].
 // K must be a multiple of 128; lda/ldb multiples of 16 bytes.
-extern "C" int ob_gemm_fp8_block(const void* A8, long long lda, const void* sa, long long sa_ld, const void* B8,
-                                 long long ldb, const void* sb, void* C, long long ldc, int M, int N, int K,
-                                 int* status, cudaStream_t stream) {
+template <bool PER_TENSOR>
+static int launch_fp8(const void* A8, long long lda, const void* sa, long long sa_ld, const void* B8, long long ldb,
+                      const void* sb, void* C, long long ldc, int M, int N, int K, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (K % BK != 0) return -1;
   CUtensorMap ta, tb;
@@ -352,7 +467,8 @@ extern "C" int ob_gemm_fp8_block(const void* A8, long long lda, const void* sa, 
   p.sb = (const float*)sb; p.status = status;
   static bool configured = false;
   if (!configured) {
-    OB_CUDA_CHECK(cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    OB_CUDA_CHECK(cudaFuncSetAttribute(gemm_fp8_kernel<PER_TENSOR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       SMEM_BYTES));
     configured = true;
   }
   int dev = 0, sms = 148;
@@ -360,7 +476,55 @@ extern "C" int ob_gemm_fp8_block(const void* A8, long long lda, const void* sa, 
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   int grid = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   if (grid > sms) grid = sms;
-  gemm_fp8_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  gemm_fp8_kernel<PER_TENSOR><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ob_gemm_fp8_block(const void* A8, long long lda, const void* sa, long long sa_ld, const void* B8,
+                                 long long ldb, const void* sb, void* C, long long ldc, int M, int N, int K,
+                                 int* status, cudaStream_t stream) {
+  return launch_fp8<false>(A8, lda, sa, sa_ld, B8, ldb, sb, C, ldc, M, N, K, status, stream);
+}
+
+// C[M,N] bf16 = (*sa * *sb) * A8 [M,K] . B8 [N,K]^T with one device-resident fp32 scale per operand.
+extern "C" int ob_gemm_fp8_tensor(const void* A8, long long lda, const void* sa, const void* B8, long long ldb,
+                                  const void* sb, void* C, long long ldc, int M, int N, int K, int* status,
+                                  cudaStream_t stream) {
+  return launch_fp8<true>(A8, lda, sa, 0, B8, ldb, sb, C, ldc, M, N, K, status, stream);
+}
+
+static int quant_grid(long long vecs) {
+  long long blocks = (vecs + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  return (int)blocks;
+}
+
+// *scale_out = max|x| / 448 * margin_mul.  ws: two zeroed 32-bit words reused from call to call (per stream).
+extern "C" int ob_fp8_amax_scale(const void* x, long long ldx, int rows, int cols, void* ws, void* scale_out,
+                                 float margin_mul, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return -1;
+  if (cols % 8 != 0 || ldx % 8 != 0) return -1;
+  amax_scale_kernel<<<quant_grid((long long)rows * (cols / 8)), 256, 0, stream>>>(
+      (const __nv_bfloat16*)x, ldx, rows, cols, (unsigned*)ws, (float*)scale_out, margin_mul);
+  return (int)cudaGetLastError();
+}
+
+// q = e4m3(x / *scale); optional amax_rec (see quant_tensor_kernel).
+extern "C" int ob_quant_fp8_tensor(const void* x, long long ldx, void* q, long long ldq, const void* scale,
+                                   void* amax_rec, int rows, int cols, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if (cols % 8 != 0 || ldx % 8 != 0 || ldq % 8 != 0) return -1;
+  quant_tensor_kernel<<<quant_grid((long long)rows * (cols / 8)), 256, 0, stream>>>(
+      (const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq, (const float*)scale, (unsigned*)amax_rec, rows, cols);
+  return (int)cudaGetLastError();
+}
+
+// state [n][2 + H] fp32 (see delayed_update_kernel); pos in [0, H).
+extern "C" int ob_fp8_delayed_update(void* state, int n, int H, int pos, float margin_mul, int use_max,
+                                     cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (H <= 0 || pos < 0 || pos >= H) return -1;
+  delayed_update_kernel<<<n, 128, 0, stream>>>((float*)state, H, pos, margin_mul, use_max);
   return (int)cudaGetLastError();
 }
 
@@ -378,13 +542,16 @@ extern "C" int ob_quant_fp8_rowwise(const void* x, long long ldx, void* q, long 
 }
 
 // w [rows, cols] bf16 -> q [rows, cols], optional transposed qt [cols, rows], scales [ceil(rows/128)][ceil(cols/128)],
-// optional scales_t (transposed table).  cols % 16 == 0 and rows % 16 == 0.
+// optional scales_t (transposed table); or, with tensor_scale, one given scale and no tables.  cols % 16 == 0 and
+// rows % 16 == 0.
 extern "C" int ob_quant_fp8_block(const void* w, long long ldw, void* q, long long ldq, void* qt, long long ldqt,
-                                  void* scales, void* scales_t, int rows, int cols, cudaStream_t stream) {
+                                  void* scales, void* scales_t, int rows, int cols, const void* tensor_scale,
+                                  cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return 0;
   if (cols % 16 != 0 || rows % 16 != 0 || ldw % 8 != 0 || ldq % 16 != 0 || (qt && ldqt % 16 != 0)) return -1;
   dim3 grid((cols + 127) / 128, (rows + 127) / 128);
   quant_block_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)w, ldw, (uint8_t*)q, ldq, (uint8_t*)qt, ldqt,
-                                               (float*)scales, (float*)scales_t, rows, cols);
+                                               (float*)scales, (float*)scales_t, rows, cols,
+                                               (const float*)tensor_scale);
   return (int)cudaGetLastError();
 }

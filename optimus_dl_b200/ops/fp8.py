@@ -1,4 +1,4 @@
-"""Block-scaled e4m3 matrix products (``csrc/gemm_fp8.cu``).
+"""e4m3 matrix products with block or per-tensor scales (``csrc/gemm_fp8.cu``).
 
 Scaling follows the fine-grained scheme used for FP8 training of large models: activations (and
 output gradients) carry one scale per ``1 x 128`` block along the reduction dimension, weights one
@@ -6,6 +6,12 @@ scale per ``128 x 128`` block; products accumulate in fp32 per 128-wide k-block,
 summed in registers, and leave the kernel in bf16. This is the path the reference reaches through
 Transformer Engine's ``Float8BlockScaling`` recipe (optimus_dl/modules/amp/fp8.py:180-315); here it is
 a hand-written tcgen05 kernel.
+
+Per-tensor scaling (the reference's ``tensorwise`` = TE ``Float8CurrentScaling`` and ``delayed`` =
+TE ``DelayedScaling`` recipes) uses one fp32 scale per operand: the tensor core then accumulates over
+the whole reduction dimension in TMEM and the kernel runs at the plain e4m3 rate. ``tensorwise`` takes
+the scale from the tensor's own maximum (one extra read pass); ``delayed`` takes it from a history of
+maxima recorded by the quantiser in earlier steps, so quantising is a single pass.
 
 ``fp8_linear`` is the autograd function behind FP8 linear layers: forward ``y = q(x) q(W)^T`` and
 input gradient ``dx = q(dy) q(W^T)^T`` in FP8, weight gradient ``dW = dy^T x`` in bf16 (it feeds the
@@ -94,7 +100,7 @@ def quantize_block(w: torch.Tensor, with_transpose: bool = False):
         qt = torch.empty((cols, rows), dtype=torch.float8_e4m3fn, device=w.device)
         st = torch.empty((C, R), dtype=torch.float32, device=w.device)
     rc = _lib.lib().ob_quant_fp8_block(_lib.ptr(w), w.stride(0), _lib.ptr(q), cols, _lib.ptr(qt), rows, _lib.ptr(s),
-                                       _lib.ptr(st), rows, cols, _lib.stream())
+                                       _lib.ptr(st), rows, cols, _lib.ptr(None), _lib.stream())
     _lib.check(rc, "ob_quant_fp8_block")
     return (q, s, qt, st) if with_transpose else (q, s)
 
@@ -119,6 +125,184 @@ def gemm_fp8(a8: torch.Tensor, sa: torch.Tensor, b8: torch.Tensor, sb: torch.Ten
     return out
 
 
+# ---------------------------------------------------------------------- per-tensor scaling
+def scaling_mode() -> str:
+    """``block`` | ``tensor`` | ``delayed``: how the active recipe scales operands (``block`` outside a recipe)."""
+    from ..amp import fp8 as amp_fp8
+
+    rec = amp_fp8._state.get("recipe")
+    kind = getattr(getattr(rec, "recipe", None), "value", "blockwise")
+    return {"tensorwise": "tensor", "delayed": "delayed"}.get(kind, "block")
+
+
+def _margin_mul() -> float:
+    from ..amp import fp8 as amp_fp8
+
+    rec = amp_fp8._state.get("recipe")
+    return float(2.0 ** int((getattr(rec, "options", None) or {}).get("margin", 0) or 0))
+
+
+def quantize_tensor_ref(x: torch.Tensor, scale: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """``x`` -> (e4m3 values, fp32 scale ``[1]``) with one scale for the whole tensor."""
+    if scale is None:
+        amax = x.float().abs().amax()
+        scale = torch.where(amax > 0, amax / E4M3_MAX, torch.ones_like(amax)).reshape(1)
+    q = (x.float() / scale).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn)
+    return q, scale
+
+
+def gemm_fp8_tensor_ref(a8: torch.Tensor, sa: torch.Tensor, b8: torch.Tensor, sb: torch.Tensor) -> torch.Tensor:
+    return (a8.float() @ b8.float().t()) * (sa.float() * sb.float())
+
+
+_workspaces: dict = {}
+
+
+def _amax_ws(device: torch.device) -> torch.Tensor:
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None:
+        ws = torch.zeros(2, dtype=torch.int32, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def _rows_ok(x: torch.Tensor) -> torch.Tensor:
+    if x.stride(1) != 1 or x.stride(0) % 8 != 0 or x.data_ptr() % 16 != 0:
+        x = x.contiguous()
+    return x
+
+
+def tensor_scale(x: torch.Tensor, out: torch.Tensor | None = None, margin_mul: float = 1.0) -> torch.Tensor:
+    """fp32 ``[1]``: ``max|x| / 448 * margin_mul`` (1 for an all-zero tensor), computed on the device."""
+    x = _rows_ok(x.reshape(-1, x.shape[-1]))
+    out = out if out is not None else torch.empty(1, dtype=torch.float32, device=x.device)
+    rc = _lib.lib().ob_fp8_amax_scale(_lib.ptr(x), x.stride(0), x.shape[0], x.shape[1], _lib.ptr(_amax_ws(x.device)),
+                                      _lib.ptr(out), float(margin_mul), _lib.stream())
+    _lib.check(rc, "ob_fp8_amax_scale")
+    return out
+
+
+def quantize_tensor(x: torch.Tensor, scale: torch.Tensor | None = None, amax_rec: torch.Tensor | None = None,
+                    margin_mul: float = 1.0) -> tuple[torch.Tensor, torch.Tensor]:
+    """``x [rows, cols]`` -> (e4m3 ``[rows, cols]``, scale ``[1]``). With ``scale`` given the tensor is read once;
+    ``amax_rec`` (one 32-bit word) receives the running ``max|x|`` for a delayed-scaling history."""
+    x = x.reshape(-1, x.shape[-1])
+    rows, cols = x.shape
+    if not kernel_ok(x) or cols % 8 != 0:
+        return quantize_tensor_ref(x, scale)
+    x = _rows_ok(x)
+    if scale is None:
+        scale = tensor_scale(x, margin_mul=margin_mul)
+    q = torch.empty((rows, cols), dtype=torch.float8_e4m3fn, device=x.device)
+    rc = _lib.lib().ob_quant_fp8_tensor(_lib.ptr(x), x.stride(0), _lib.ptr(q), cols, _lib.ptr(scale), _lib.ptr(amax_rec),
+                                        rows, cols, _lib.stream())
+    _lib.check(rc, "ob_quant_fp8_tensor")
+    return q, scale
+
+
+def quantize_weight_tensor(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """``w [rows, cols]`` -> (e4m3 ``w``, scale ``[1]``, e4m3 ``w^T``), one scale for the matrix."""
+    rows, cols = w.shape
+    if not kernel_ok(w) or rows % 16 != 0 or cols % 16 != 0 or not w.is_contiguous():
+        q, s = quantize_tensor_ref(w)
+        return q, s, q.t().contiguous()
+    s = tensor_scale(w)
+    q = torch.empty((rows, cols), dtype=torch.float8_e4m3fn, device=w.device)
+    qt = torch.empty((cols, rows), dtype=torch.float8_e4m3fn, device=w.device)
+    rc = _lib.lib().ob_quant_fp8_block(_lib.ptr(w), w.stride(0), _lib.ptr(q), cols, _lib.ptr(qt), rows, _lib.ptr(None),
+                                       _lib.ptr(None), rows, cols, _lib.ptr(s), _lib.stream())
+    _lib.check(rc, "ob_quant_fp8_block")
+    return q, s, qt
+
+
+def gemm_fp8_tensor(a8: torch.Tensor, sa: torch.Tensor, b8: torch.Tensor, sb: torch.Tensor,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+    """``C[M,N] = sa * sb * (A8 . B8^T)`` in bf16; ``sa`` / ``sb`` are fp32 ``[1]`` tensors on the device."""
+    M, K = a8.shape
+    N = b8.shape[0]
+    if not (a8.is_cuda and _lib.available()) or K % BLOCK != 0:
+        r = gemm_fp8_tensor_ref(a8, sa, b8, sb).to(torch.bfloat16)
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a8.device)
+    rc = _lib.lib().ob_gemm_fp8_tensor(_lib.ptr(a8), a8.stride(0), _lib.ptr(sa), _lib.ptr(b8), b8.stride(0), _lib.ptr(sb),
+                                       _lib.ptr(out), out.stride(0), M, N, K, _lib.ptr(_lib.status_word(a8.device)),
+                                       _lib.stream())
+    _lib.check(rc, "ob_gemm_fp8_tensor")
+    return out
+
+
+class DelayedScaling:
+    """Amax histories for the ``delayed`` recipe: one row ``[scale, recorded max, hist[H]]`` per (weight, role).
+
+    A row is created on first use and seeded with the tensor's own maximum (so the first step behaves like
+    current scaling); afterwards quantising uses the stored scale and records the maximum it saw, and
+    :meth:`update` (once per backward pass) rolls every history and refreshes every scale with one launch.
+    """
+
+    def __init__(self, history: int = 16, algo: str = "max", capacity: int = 1024):
+        self.H, self.use_max, self.capacity = max(1, int(history)), algo != "most_recent", capacity
+        self.state: torch.Tensor | None = None
+        self.rows: dict = {}
+        self.pos = 0
+
+    def row(self, holder: torch.Tensor, role: str, x: torch.Tensor, margin_mul: float) -> tuple[torch.Tensor, torch.Tensor]:
+        """``(scale [1], amax word [1])`` views for this tensor role, seeded from ``x`` on first use."""
+        if self.state is None:
+            self.state = torch.zeros((self.capacity, 2 + self.H), dtype=torch.float32, device=x.device)
+        key = (id(holder), role)
+        i = self.rows.get(key)
+        fresh = i is None
+        if fresh:
+            i = len(self.rows)
+            if i >= self.capacity:
+                raise RuntimeError("delayed-scaling state is full; raise DelayedScaling(capacity=...)")
+            self.rows[key] = i
+        st = self.state[i]
+        if fresh:
+            tensor_scale(x, out=st[0:1], margin_mul=margin_mul)
+        return st[0:1], st[1:2]
+
+    def update(self, margin_mul: float = 1.0) -> None:
+        if self.state is None or not self.rows:
+            return
+        rc = _lib.lib().ob_fp8_delayed_update(_lib.ptr(self.state), len(self.rows), self.H, self.pos, float(margin_mul),
+                                              int(self.use_max), _lib.stream())
+        _lib.check(rc, "ob_fp8_delayed_update")
+        self.pos = (self.pos + 1) % self.H
+
+
+def _delayed() -> "DelayedScaling | None":
+    from ..amp import fp8 as amp_fp8
+
+    rec = amp_fp8._state.get("recipe")
+    return getattr(rec, "delayed_state", None)
+
+
+def _quantize_activation(x2: torch.Tensor, holder: torch.Tensor, role: str) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per-tensor quantisation of an activation / output gradient under the active recipe."""
+    mm = _margin_mul()
+    ds = _delayed() if scaling_mode() == "delayed" else None
+    if ds is None or not kernel_ok(x2):
+        return quantize_tensor(x2, margin_mul=mm)
+    scale, rec = ds.row(holder, role, x2, mm)
+    return quantize_tensor(x2, scale=scale, amax_rec=rec)
+
+
+def _cached_weight_tensor(w: torch.Tensor, holder: torch.Tensor | None = None):
+    holder = holder if holder is not None else w
+    key = (w.data_ptr(), holder._version, tuple(w.shape))
+    hit = getattr(holder, "_fp8_cache_t", None)
+    if hit is None or hit[0] != key:
+        hit = (key, *quantize_weight_tensor(w.detach()))
+        holder._fp8_cache_t = hit
+    return hit[1:]
+
+
 # ---------------------------------------------------------------------- autograd
 def _cached_weight(w: torch.Tensor, holder: torch.Tensor | None = None):
     """Quantised weight and transpose, re-made when the parameter's version counter moves. ``holder`` is
@@ -133,20 +317,36 @@ def _cached_weight(w: torch.Tensor, holder: torch.Tensor | None = None):
     return hit[1:]
 
 
+def _fwd(x2: torch.Tensor, w: torch.Tensor, holder: torch.Tensor) -> torch.Tensor:
+    if scaling_mode() == "block":
+        wq, ws, _, _ = _cached_weight(w, holder)
+        xq, xs = quantize_rowwise(x2)
+        return gemm_fp8(xq, xs, wq, ws)
+    wq, ws, _ = _cached_weight_tensor(w, holder)
+    xq, xs = _quantize_activation(x2, holder, "x")
+    return gemm_fp8_tensor(xq, xs, wq, ws)
+
+
+def _dgrad(dy2: torch.Tensor, w: torch.Tensor, holder: torch.Tensor) -> torch.Tensor:
+    if scaling_mode() == "block":
+        _, _, wqt, wst = _cached_weight(w, holder)
+        dq, ds = quantize_rowwise(dy2)
+        return gemm_fp8(dq, ds, wqt, wst)
+    _, ws, wqt = _cached_weight_tensor(w, holder)
+    dq, ds = _quantize_activation(dy2, holder, "dy")
+    return gemm_fp8_tensor(dq, ds, wqt, ws)
+
+
 def forward_product(x2: torch.Tensor, owners: list[torch.Tensor]) -> torch.Tensor:
     """``x2 @ cat(owners)^T`` with both operands quantised (no autograd); ``owners`` adjacent or single."""
     w = owners[0] if len(owners) == 1 else lin_ops._fused_view(list(owners))
-    wq, ws, _, _ = _cached_weight(w, owners[0])
-    xq, xs = quantize_rowwise(x2)
-    return gemm_fp8(xq, xs, wq, ws)
+    return _fwd(x2, w, owners[0])
 
 
 def dgrad_product(dy2: torch.Tensor, owners: list[torch.Tensor]) -> torch.Tensor:
     """``dy2 @ cat(owners)`` (input gradient of :func:`forward_product`) with both operands quantised."""
     w = owners[0] if len(owners) == 1 else lin_ops._fused_view(list(owners))
-    _, _, wqt, wst = _cached_weight(w, owners[0])
-    dq, ds = quantize_rowwise(dy2)
-    return gemm_fp8(dq, ds, wqt, wst)
+    return _dgrad(dy2, w, owners[0])
 
 
 def usable(x2: torch.Tensor, owners: list[torch.Tensor]) -> bool:
@@ -166,9 +366,7 @@ class _Fp8Linear(torch.autograd.Function):
         if not x2.is_contiguous():
             x2 = x2.contiguous()
         w = owners[0] if len(owners) == 1 else lin_ops._fused_view(list(owners))
-        wq, ws, _, _ = _cached_weight(w, owners[0])
-        xq, xs = quantize_rowwise(x2)
-        y = gemm_fp8(xq, xs, wq, ws)
+        y = _fwd(x2, w, owners[0])
         if bias is not None:
             y = y + bias
         ctx.save_for_backward(x2, *owners)
@@ -187,9 +385,7 @@ class _Fp8Linear(torch.autograd.Function):
         dx = db = None
         if ctx.needs_input_grad[0]:
             w = owners[0] if len(owners) == 1 else lin_ops._fused_view(list(owners))
-            _, _, wqt, wst = _cached_weight(w, owners[0])
-            dq, ds = quantize_rowwise(dy2)
-            dx = gemm_fp8(dq, ds, wqt, wst).view(ctx.x_shape)
+            dx = _dgrad(dy2, w, owners[0]).view(ctx.x_shape)
         dws: list = [None] * len(owners)
         o = 0
         for i, p in enumerate(owners):

@@ -118,3 +118,122 @@ def test_fp8_training_tracks_bf16():
     assert got[-1] < got[0] - 0.5, got
     assert abs(got[-1] - ref[-1]) < 0.25, (ref[-1], got[-1])
     assert abs(got[0] - ref[0]) < 0.05
+
+
+def test_tensor_quantiser_and_scale():
+    from optimus_dl_b200.ops import fp8
+
+    torch.manual_seed(0)
+    x = (torch.randn(300, 520, device="cuda") * 3).bfloat16()
+    q, s = fp8.quantize_tensor(x)
+    qr, sr = fp8.quantize_tensor_ref(x)
+    assert s.shape == (1,) and torch.allclose(s, sr, rtol=1e-6)
+    assert (q.float() == qr.float()).float().mean() > 0.999
+    # the workspace is left clean: a second tensor gets its own maximum
+    y = (x * 0.01).bfloat16()
+    _, s2 = fp8.quantize_tensor(y)
+    assert torch.allclose(s2, y.float().abs().amax().reshape(1) / 448.0, rtol=1e-6)
+    # given scale + recorded maximum
+    rec = torch.zeros(1, dtype=torch.int32, device="cuda")
+    q3, _ = fp8.quantize_tensor(x, scale=s, amax_rec=rec)
+    assert torch.equal(q3.float(), q.float())
+    assert rec.view(torch.float32).item() == x.float().abs().max().item()
+    z = torch.zeros(16, 64, device="cuda", dtype=torch.bfloat16)
+    assert fp8.quantize_tensor(z)[1].item() == 1.0
+
+
+def test_weight_tensor_quantiser_transpose():
+    from optimus_dl_b200.ops import fp8
+
+    torch.manual_seed(0)
+    w = (torch.randn(400, 384, device="cuda") * 0.05).bfloat16()
+    q, s, qt = fp8.quantize_weight_tensor(w)
+    qr, sr = fp8.quantize_tensor_ref(w)
+    assert torch.allclose(s, sr, rtol=1e-6)
+    assert (q.float() == qr.float()).float().mean() > 0.999
+    assert torch.equal(qt.float(), q.float().t())
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (512, 1024, 1024), (300, 400, 384), (4096, 4096, 4096), (77, 130, 256)])
+def test_fp8_tensor_gemm(M, N, K):
+    from optimus_dl_b200.ops import _lib, fp8
+
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
+    a8, sa = fp8.quantize_tensor_ref(a)
+    b8, sb = fp8.quantize_tensor_ref(b)
+    out = fp8.gemm_fp8_tensor(a8, sa, b8, sb)
+    torch.cuda.synchronize()
+    _lib.check_status(torch.device("cuda"))
+    ref = fp8.gemm_fp8_tensor_ref(a8, sa, b8, sb)
+    err = (out.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-9)
+    assert err < 1e-2, err
+    exact = a.float() @ b.float().t()
+    assert (out.float() - exact).norm() / exact.norm() < 0.07
+
+
+@pytest.mark.parametrize("kind", ["tensorwise", "delayed"])
+def test_fp8_linear_per_tensor_recipes(kind):
+    from optimus_dl_b200.amp.fp8 import FP8Recipe, Fp8Format, parse_fp8_recipe
+    from optimus_dl_b200.ops import fp8
+
+    torch.manual_seed(0)
+    recipe = FP8Recipe(Fp8Format.E4M3, parse_fp8_recipe(kind), amax_history_len=4)
+    x = torch.randn(2, 192, 512, device="cuda").bfloat16().requires_grad_(True)
+    w = (torch.randn(768, 512, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    xf, wf = (t.detach().float().requires_grad_(True) for t in (x, w))
+    rel = lambda a, r: ((a.float() - r).norm() / r.norm()).item()  # noqa: E731
+    for step in range(3):
+        x.grad = w.grad = xf.grad = wf.grad = None
+        with recipe.backward(True):
+            assert fp8.scaling_mode() == ("tensor" if kind == "tensorwise" else "delayed")
+            y = fp8.fp8_linear(x, w)
+            dy = torch.randn_like(y) * (1.0 + step)
+            y.backward(dy)
+        yr = torch.nn.functional.linear(xf, wf)
+        yr.backward(dy.float())
+        assert rel(y, yr) < 0.06, (step, rel(y, yr))
+        assert rel(x.grad, xf.grad) < 0.07, (step, rel(x.grad, xf.grad))
+        assert rel(w.grad, wf.grad) < 0.02
+    if kind == "delayed":
+        ds = recipe.delayed_state
+        assert len(ds.rows) == 2 and ds.pos == 3
+        st = ds.state[:2].cpu()
+        assert (st[:, 1] == 0).all()                     # recorded maxima were consumed
+        assert (st[:, 2:5] > 0).all()                    # three history entries filled
+        assert torch.allclose(st[:, 0], st[:, 2:].amax(1) / 448.0)
+
+
+def test_fp8_training_per_tensor_tracks_bf16():
+    from optimus_dl_b200.amp.fp8 import FP8Recipe, Fp8Format, parse_fp8_recipe
+    from optimus_dl_b200.criterion.cross_entropy import CrossEntropyCriterion, CrossEntropyCriterionConfig
+    from optimus_dl_b200.model_transforms.transformer_engine import mark_fp8_linears
+    from optimus_dl_b200.models.llama2 import Llama, LlamaConfig
+
+    def run(kind):
+        torch.manual_seed(0)
+        cfg = LlamaConfig(n_layer=2, n_head=4, n_kv_head=2, n_embd=256, vocab_size=512, sequence_length=128,
+                          intermediate_size=512, tie_word_embeddings=False)
+        model = Llama(cfg).to(device="cuda", dtype=torch.bfloat16)
+        if kind:
+            mark_fp8_linears(model)
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+        crit = CrossEntropyCriterion(CrossEntropyCriterionConfig())
+        recipe = FP8Recipe(Fp8Format.E4M3, parse_fp8_recipe(kind or "blockwise"))
+        ids = torch.randint(0, 512, (4, 129), device="cuda", generator=torch.Generator(device="cuda").manual_seed(1))
+        losses = []
+        for _ in range(12):
+            opt.zero_grad()
+            with recipe.backward(bool(kind)):
+                loss, _ = crit(model, {"input_ids": ids})
+                loss.backward()
+            opt.step()
+            losses.append(loss.item())
+        return losses
+
+    ref = run(None)
+    for kind in ("tensorwise", "delayed"):
+        got = run(kind)
+        assert got[-1] < got[0] - 0.5, (kind, got)
+        assert abs(got[-1] - ref[-1]) < 0.3, (kind, ref[-1], got[-1])
