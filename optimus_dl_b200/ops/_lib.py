@@ -189,8 +189,8 @@ def _declare(l: ctypes.CDLL) -> None:
     sig("ob_gemm_rs_bf16", [P, L, I, P, L, I, P, PP, I, I, I, L, I, I, I, I, P, P])
     sig("ob_gemm_fp8_block", [P, L, P, L, P, L, P, P, L, I, I, I, P, P])
     sig("ob_quant_fp8_rowwise", [P, L, P, L, P, L, I, I, P])
-    sig("ob_quant_fp8_block", [P, L, P, L, P, L, P, P, I, I, P, P])
-    sig("ob_gemm_fp8_tensor", [P, L, P, P, L, P, P, L, I, I, I, P, P])
+    sig("ob_quant_fp8_block", [P, L, P, L, P, L, P, P, I, I, P, P, P])
+    sig("ob_gemm_fp8_tensor", [P, L, P, P, L, P, P, L, I, I, I, I, P, P])
     sig("ob_fp8_amax_scale", [P, L, I, I, P, P, F, P])
     sig("ob_quant_fp8_tensor", [P, L, P, L, P, P, I, I, P])
     sig("ob_fp8_delayed_update", [P, I, I, I, F, I, P])

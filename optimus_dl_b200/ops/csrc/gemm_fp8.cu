@@ -47,6 +47,7 @@ struct Params {
   long long sa_ld;    // >= M
   const float* sb;    // [ceil(N/128)][K/128]
   int* status;
+  int accumulate;     // C += product (C is read in the epilogue)
 };
 
 __device__ __forceinline__ void tile_of(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
@@ -206,6 +207,13 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         if (vec) {
 #pragma unroll
           for (int q = 0; q < EPI_COLS / 8; ++q) {
+            if (p.accumulate) {
+              const uint4 old = *reinterpret_cast<const uint4*>(crow + 8 * q);
+              const float2 o0 = unpack_bf16x2(old.x), o1 = unpack_bf16x2(old.y), o2 = unpack_bf16x2(old.z),
+                           o3 = unpack_bf16x2(old.w);
+              acc[8 * q] += o0.x; acc[8 * q + 1] += o0.y; acc[8 * q + 2] += o1.x; acc[8 * q + 3] += o1.y;
+              acc[8 * q + 4] += o2.x; acc[8 * q + 5] += o2.y; acc[8 * q + 6] += o3.x; acc[8 * q + 7] += o3.y;
+            }
             uint4 o = make_uint4(pack_bf16x2(acc[8 * q], acc[8 * q + 1]), pack_bf16x2(acc[8 * q + 2], acc[8 * q + 3]),
                                  pack_bf16x2(acc[8 * q + 4], acc[8 * q + 5]), pack_bf16x2(acc[8 * q + 6], acc[8 * q + 7]));
             *reinterpret_cast<uint4*>(crow + 8 * q) = o;
@@ -213,7 +221,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         } else {
 #pragma unroll
           for (int j = 0; j < EPI_COLS; ++j)
-            if (col0 + j < p.N) crow[j] = __float2bfloat16(acc[j]);
+            if (col0 + j < p.N) crow[j] = __float2bfloat16(acc[j] + (p.accumulate ? __bfloat162float(crow[j]) : 0.f));
         }
       }
     }
@@ -276,11 +284,12 @@ quant_rowwise_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t
 // 128 x 128 blocks of w [rows, cols]: one CTA (256 threads) per block.  Writes q [rows, cols] and,
 // when qt != nullptr, the transposed copy qt [cols, rows]; scales [rows/128][cols/128] and the
 // transposed table scales_t [cols/128][rows/128].  With tensor_scale != nullptr every block uses that one scale
-// (per-tensor scaling) and no scale table is written.
+// (per-tensor scaling) and no scale table is written; amax_rec then receives the tensor's |w| maximum (float
+// bits, atomic maximum).
 __global__ void __launch_bounds__(256)
 quant_block_kernel(const __nv_bfloat16* __restrict__ w, long long ldw, uint8_t* __restrict__ q, long long ldq,
                    uint8_t* __restrict__ qt, long long ldqt, float* __restrict__ scales, float* __restrict__ scales_t,
-                   int rows, int cols, const float* __restrict__ tensor_scale) {
+                   int rows, int cols, const float* __restrict__ tensor_scale, unsigned* __restrict__ amax_rec) {
   __shared__ float s_red[8];
   __shared__ uint8_t tile[128][132];
   const int bc = blockIdx.x, br = blockIdx.y;
@@ -309,6 +318,7 @@ quant_block_kernel(const __nv_bfloat16* __restrict__ w, long long ldw, uint8_t* 
   for (int i = 1; i < 8; ++i) amax = fmaxf(amax, s_red[i]);
   const float scale = tensor_scale ? *tensor_scale : (amax > 0.f ? amax / E4M3_MAX : 1.0f);
   const float inv = 1.0f / scale;
+  if (tid == 0 && amax_rec && amax > 0.f) atomicMax(amax_rec, __float_as_uint(amax));
   if (tid == 0 && scales) {
     scales[(long long)br * gridDim.x + bc] = scale;
     if (scales_t) scales_t[(long long)bc * gridDim.y + br] = scale;
@@ -454,7 +464,8 @@ using namespace ob::fp8;
 // K must be a multiple of 128; lda/ldb multiples of 16 bytes.
 template <bool PER_TENSOR>
 static int launch_fp8(const void* A8, long long lda, const void* sa, long long sa_ld, const void* B8, long long ldb,
-                      const void* sb, void* C, long long ldc, int M, int N, int K, int* status, cudaStream_t stream) {
+                      const void* sb, void* C, long long ldc, int M, int N, int K, int accumulate, int* status,
+                      cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (K % BK != 0) return -1;
   CUtensorMap ta, tb;
@@ -464,7 +475,7 @@ static int launch_fp8(const void* A8, long long lda, const void* sa, long long s
   if (rc) return rc;
   Params p{};
   p.M = M; p.N = N; p.K = K; p.C = (__nv_bfloat16*)C; p.ldc = ldc; p.sa = (const float*)sa; p.sa_ld = sa_ld;
-  p.sb = (const float*)sb; p.status = status;
+  p.sb = (const float*)sb; p.status = status; p.accumulate = accumulate;
   static bool configured = false;
   if (!configured) {
     OB_CUDA_CHECK(cudaFuncSetAttribute(gemm_fp8_kernel<PER_TENSOR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -483,14 +494,14 @@ static int launch_fp8(const void* A8, long long lda, const void* sa, long long s
 extern "C" int ob_gemm_fp8_block(const void* A8, long long lda, const void* sa, long long sa_ld, const void* B8,
                                  long long ldb, const void* sb, void* C, long long ldc, int M, int N, int K,
                                  int* status, cudaStream_t stream) {
-  return launch_fp8<false>(A8, lda, sa, sa_ld, B8, ldb, sb, C, ldc, M, N, K, status, stream);
+  return launch_fp8<false>(A8, lda, sa, sa_ld, B8, ldb, sb, C, ldc, M, N, K, 0, status, stream);
 }
 
-// C[M,N] bf16 = (*sa * *sb) * A8 [M,K] . B8 [N,K]^T with one device-resident fp32 scale per operand.
+// C[M,N] bf16 (+)= (*sa * *sb) * A8 [M,K] . B8 [N,K]^T with one device-resident fp32 scale per operand.
 extern "C" int ob_gemm_fp8_tensor(const void* A8, long long lda, const void* sa, const void* B8, long long ldb,
-                                  const void* sb, void* C, long long ldc, int M, int N, int K, int* status,
-                                  cudaStream_t stream) {
-  return launch_fp8<true>(A8, lda, sa, 0, B8, ldb, sb, C, ldc, M, N, K, status, stream);
+                                  const void* sb, void* C, long long ldc, int M, int N, int K, int accumulate,
+                                  int* status, cudaStream_t stream) {
+  return launch_fp8<true>(A8, lda, sa, 0, B8, ldb, sb, C, ldc, M, N, K, accumulate, status, stream);
 }
 
 static int quant_grid(long long vecs) {
@@ -546,12 +557,12 @@ extern "C" int ob_quant_fp8_rowwise(const void* x, long long ldx, void* q, long 
 // rows % 16 == 0.
 extern "C" int ob_quant_fp8_block(const void* w, long long ldw, void* q, long long ldq, void* qt, long long ldqt,
                                   void* scales, void* scales_t, int rows, int cols, const void* tensor_scale,
-                                  cudaStream_t stream) {
+                                  void* amax_rec, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return 0;
   if (cols % 16 != 0 || rows % 16 != 0 || ldw % 8 != 0 || ldq % 16 != 0 || (qt && ldqt % 16 != 0)) return -1;
   dim3 grid((cols + 127) / 128, (rows + 127) / 128);
   quant_block_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)w, ldw, (uint8_t*)q, ldq, (uint8_t*)qt, ldqt,
                                                (float*)scales, (float*)scales_t, rows, cols,
-                                               (const float*)tensor_scale);
+                                               (const float*)tensor_scale, (unsigned*)amax_rec);
   return (int)cudaGetLastError();
 }

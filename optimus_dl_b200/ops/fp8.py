@@ -100,7 +100,7 @@ def quantize_block(w: torch.Tensor, with_transpose: bool = False):
         qt = torch.empty((cols, rows), dtype=torch.float8_e4m3fn, device=w.device)
         st = torch.empty((C, R), dtype=torch.float32, device=w.device)
     rc = _lib.lib().ob_quant_fp8_block(_lib.ptr(w), w.stride(0), _lib.ptr(q), cols, _lib.ptr(qt), rows, _lib.ptr(s),
-                                       _lib.ptr(st), rows, cols, _lib.ptr(None), _lib.stream())
+                                       _lib.ptr(st), rows, cols, _lib.ptr(None), _lib.ptr(None), _lib.stream())
     _lib.check(rc, "ob_quant_fp8_block")
     return (q, s, qt, st) if with_transpose else (q, s)
 
@@ -201,37 +201,46 @@ def quantize_tensor(x: torch.Tensor, scale: torch.Tensor | None = None, amax_rec
     return q, scale
 
 
-def quantize_weight_tensor(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """``w [rows, cols]`` -> (e4m3 ``w``, scale ``[1]``, e4m3 ``w^T``), one scale for the matrix."""
+def quantize_tensor_t(w: torch.Tensor, scale: torch.Tensor | None = None, amax_rec: torch.Tensor | None = None,
+                      margin_mul: float = 1.0) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """``w [rows, cols]`` -> (e4m3 ``w``, scale ``[1]``, e4m3 ``w^T``) with one scale for the matrix: both
+    layouts from one read of ``w`` (weights for forward / dgrad; activations and output gradients for
+    forward-or-dgrad / wgrad)."""
     rows, cols = w.shape
-    if not kernel_ok(w) or rows % 16 != 0 or cols % 16 != 0 or not w.is_contiguous():
-        q, s = quantize_tensor_ref(w)
+    if not kernel_ok(w) or rows % 16 != 0 or cols % 16 != 0:
+        q, s = quantize_tensor_ref(w, scale)
         return q, s, q.t().contiguous()
-    s = tensor_scale(w)
+    w = _rows_ok(w)
+    s = scale if scale is not None else tensor_scale(w, margin_mul=margin_mul)
     q = torch.empty((rows, cols), dtype=torch.float8_e4m3fn, device=w.device)
     qt = torch.empty((cols, rows), dtype=torch.float8_e4m3fn, device=w.device)
     rc = _lib.lib().ob_quant_fp8_block(_lib.ptr(w), w.stride(0), _lib.ptr(q), cols, _lib.ptr(qt), rows, _lib.ptr(None),
-                                       _lib.ptr(None), rows, cols, _lib.ptr(s), _lib.stream())
+                                       _lib.ptr(None), rows, cols, _lib.ptr(s), _lib.ptr(amax_rec), _lib.stream())
     _lib.check(rc, "ob_quant_fp8_block")
     return q, s, qt
 
 
+def quantize_weight_tensor(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    return quantize_tensor_t(w)
+
+
 def gemm_fp8_tensor(a8: torch.Tensor, sa: torch.Tensor, b8: torch.Tensor, sb: torch.Tensor,
-                    out: torch.Tensor | None = None) -> torch.Tensor:
-    """``C[M,N] = sa * sb * (A8 . B8^T)`` in bf16; ``sa`` / ``sb`` are fp32 ``[1]`` tensors on the device."""
+                    out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
+    """``C[M,N] (+)= sa * sb * (A8 . B8^T)`` in bf16; ``sa`` / ``sb`` are fp32 ``[1]`` tensors on the device."""
     M, K = a8.shape
     N = b8.shape[0]
-    if not (a8.is_cuda and _lib.available()) or K % BLOCK != 0:
-        r = gemm_fp8_tensor_ref(a8, sa, b8, sb).to(torch.bfloat16)
+    assert not accumulate or out is not None
+    if not (a8.is_cuda and _lib.available()) or K % BLOCK != 0 or a8.stride(0) % 16 != 0 or b8.stride(0) % 16 != 0:
+        r = gemm_fp8_tensor_ref(a8, sa, b8, sb)
         if out is not None:
-            out.copy_(r)
+            out.copy_(out.float() + r if accumulate else r)
             return out
-        return r
+        return r.to(torch.bfloat16)
     if out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=a8.device)
     rc = _lib.lib().ob_gemm_fp8_tensor(_lib.ptr(a8), a8.stride(0), _lib.ptr(sa), _lib.ptr(b8), b8.stride(0), _lib.ptr(sb),
-                                       _lib.ptr(out), out.stride(0), M, N, K, _lib.ptr(_lib.status_word(a8.device)),
-                                       _lib.stream())
+                                       _lib.ptr(out), out.stride(0), M, N, K, int(accumulate),
+                                       _lib.ptr(_lib.status_word(a8.device)), _lib.stream())
     _lib.check(rc, "ob_gemm_fp8_tensor")
     return out
 
@@ -291,6 +300,24 @@ def _quantize_activation(x2: torch.Tensor, holder: torch.Tensor, role: str) -> t
         return quantize_tensor(x2, margin_mul=mm)
     scale, rec = ds.row(holder, role, x2, mm)
     return quantize_tensor(x2, scale=scale, amax_rec=rec)
+
+
+def _quantize_activation_t(x2: torch.Tensor, holder: torch.Tensor, role: str):
+    """Like :func:`_quantize_activation` but also returns the transposed e4m3 copy (for the wgrad product)."""
+    mm = _margin_mul()
+    ds = _delayed() if scaling_mode() == "delayed" else None
+    if ds is None or not kernel_ok(x2):
+        return quantize_tensor_t(x2, margin_mul=mm)
+    scale, rec = ds.row(holder, role, x2, mm)
+    return quantize_tensor_t(x2, scale=scale, amax_rec=rec)
+
+
+def fp8_wgrad_enabled() -> bool:
+    """Weight gradients in FP8 too: per-tensor recipes unless the recipe was built with ``wgrad=False``."""
+    from ..amp import fp8 as amp_fp8
+
+    rec = amp_fp8._state.get("recipe")
+    return scaling_mode() != "block" and bool((getattr(rec, "options", None) or {}).get("wgrad", True))
 
 
 def _cached_weight_tensor(w: torch.Tensor, holder: torch.Tensor | None = None):
@@ -366,10 +393,21 @@ class _Fp8Linear(torch.autograd.Function):
         if not x2.is_contiguous():
             x2 = x2.contiguous()
         w = owners[0] if len(owners) == 1 else lin_ops._fused_view(list(owners))
-        y = _fwd(x2, w, owners[0])
+        T = x2.shape[0]
+        # FP8 weight gradient: the transposed e4m3 copy of x (made in the same pass as the forward operand) is
+        # what the backward keeps, instead of x itself
+        ctx.fp8_wgrad = (fp8_wgrad_enabled() and T % BLOCK == 0 and x2.shape[1] % 16 == 0
+                         and any(ctx.needs_input_grad[2:]))
+        if ctx.fp8_wgrad:
+            wq, ws, _ = _cached_weight_tensor(w, owners[0])
+            xq, xs, xqt = _quantize_activation_t(x2, owners[0], "x")
+            y = gemm_fp8_tensor(xq, xs, wq, ws)
+            ctx.save_for_backward(xqt, xs, *owners)
+        else:
+            y = _fwd(x2, w, owners[0])
+            ctx.save_for_backward(x2, *owners)
         if bias is not None:
             y = y + bias
-        ctx.save_for_backward(x2, *owners)
         ctx.owners = owners
         ctx.has_bias = bias is not None
         ctx.x_shape = shp
@@ -377,16 +415,38 @@ class _Fp8Linear(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        x2 = ctx.saved_tensors[0]
         owners = ctx.owners
         dy2 = dy.reshape(-1, dy.shape[-1])
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
         dx = db = None
-        if ctx.needs_input_grad[0]:
-            w = owners[0] if len(owners) == 1 else lin_ops._fused_view(list(owners))
-            dx = _dgrad(dy2, w, owners[0]).view(ctx.x_shape)
+        w = owners[0] if len(owners) == 1 else lin_ops._fused_view(list(owners))
         dws: list = [None] * len(owners)
+        if ctx.fp8_wgrad:
+            xqt, xs = ctx.saved_tensors[0], ctx.saved_tensors[1]
+            dq, ds, dqt = _quantize_activation_t(dy2, owners[0], "dy")
+            if ctx.needs_input_grad[0]:
+                _, ws, wqt = _cached_weight_tensor(w, owners[0])
+                dx = gemm_fp8_tensor(dq, ds, wqt, ws).view(ctx.x_shape)
+            o = 0
+            for i, p in enumerate(owners):
+                rows = p.shape[0]
+                if ctx.needs_input_grad[2 + i]:
+                    mg = lin_ops.main_grad_of(p)
+                    if mg is not None and mg.dtype == torch.bfloat16 and mg.stride(-1) == 1:
+                        gemm_fp8_tensor(dqt[o:o + rows], ds, xqt, xs, out=mg, accumulate=lin_ops.main_grad_write(p))
+                    elif mg is not None:
+                        g = gemm_fp8_tensor(dqt[o:o + rows], ds, xqt, xs)
+                        mg.add_(g) if lin_ops.main_grad_write(p) else mg.copy_(g)
+                    else:
+                        dws[i] = gemm_fp8_tensor(dqt[o:o + rows], ds, xqt, xs)
+                o += rows
+            if ctx.has_bias:
+                db = dy2.float().sum(0).to(dy.dtype)
+            return (dx, db, *dws)
+        x2 = ctx.saved_tensors[0]
+        if ctx.needs_input_grad[0]:
+            dx = _dgrad(dy2, w, owners[0]).view(ctx.x_shape)
         o = 0
         for i, p in enumerate(owners):
             rows = p.shape[0]
