@@ -102,8 +102,10 @@ def bench_gemm_fp8(t: Timer, sizes) -> None:
         ms = t(lambda: fp8.gemm_fp8_tensor(t8, st, w8, sw, out=out))
         ms_cur = t(lambda: fp8.quantize_tensor(a))
         ms_del = t(lambda: fp8.quantize_tensor(a, scale=st))
+        ms_t = t(lambda: fp8.quantize_tensor_t(a, scale=st))
         _emit("gemm_fp8_tensor", dict(M=M, N=N, K=K), ms, flops=2.0 * M * N * K, quant_current_ms=round(ms_cur, 4),
-              quant_given_scale_ms=round(ms_del, 4), quant_given_scale_gbs=round(M * K * 3 / ms_del / 1e6, 1))
+              quant_given_scale_ms=round(ms_del, 4), quant_given_scale_gbs=round(M * K * 3 / ms_del / 1e6, 1),
+              quant_with_transpose_ms=round(ms_t, 4), quant_with_transpose_gbs=round(M * K * 4 / ms_t / 1e6, 1))
 
 
 def bench_attention(t: Timer, cases) -> None:

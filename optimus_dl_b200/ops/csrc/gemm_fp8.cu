@@ -427,6 +427,84 @@ quant_tensor_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t*
   }
 }
 
+// Per-tensor quantiser that also writes the transposed copy: q [rows, cols] and qt [cols, rows] from one read of
+// x, with the given scale.  One CTA per 128 x 128 tile in two 64-row passes; a thread converts a 4 x 8 patch
+// (four 16-byte loads), stores its four 8-byte rows of q, transposes the patch in registers (byte permutes)
+// into eight 32-bit words (4 rows of one column each) and parks them in shared memory [col][row / 4]; after
+// both passes every qt row of the tile leaves as one 128-byte segment.  rows % 16 == 0, cols % 8 == 0.
+__device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+
+constexpr int QT_PITCH = 33;   // words per column row of the staging tile (32 + 1: column neighbours shift one bank)
+
+__global__ void __launch_bounds__(256)
+quant_tensor_t_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ q, long long ldq,
+                      uint8_t* __restrict__ qt, long long ldqt, const float* __restrict__ scale,
+                      unsigned* __restrict__ amax_rec, int rows, int cols) {
+  __shared__ uint32_t tile[128 * QT_PITCH];
+  __shared__ float s_red[8];
+  const int tid = threadIdx.x;
+  const int r0 = blockIdx.y * 128, c0 = blockIdx.x * 128;
+  const float inv = 1.0f / *scale;
+  const int ci = tid & 15;          // 8-column group
+  const int rg = tid >> 4;          // 4-row group within a pass (0..15)
+  const int col = c0 + ci * 8;
+  const int sw = (ci >> 2) & 3;     // word swizzle: the four column groups that would share a bank take different words
+  float amax = 0.f;
+#pragma unroll
+  for (int pass = 0; pass < 2; ++pass) {
+    const int rgg = pass * 16 + rg;           // 4-row group within the tile (0..31)
+    const int row = r0 + rgg * 4;
+    uint32_t lo[4], hi[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      uint4 raw = make_uint4(0, 0, 0, 0);
+      const bool ok = row + r < rows && col < cols;
+      if (ok) raw = *reinterpret_cast<const uint4*>(x + (long long)(row + r) * ldx + col);
+      const float2 a = unpack_bf16x2(raw.x), b = unpack_bf16x2(raw.y), c = unpack_bf16x2(raw.z), d = unpack_bf16x2(raw.w);
+      if (amax_rec)
+        amax = fmaxf(amax, fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y))),
+                                 fmaxf(fmaxf(fabsf(c.x), fabsf(c.y)), fmaxf(fabsf(d.x), fabsf(d.y)))));
+      lo[r] = e4m3x4(a.x * inv, a.y * inv, b.x * inv, b.y * inv);
+      hi[r] = e4m3x4(c.x * inv, c.y * inv, d.x * inv, d.y * inv);
+      if (ok) *reinterpret_cast<uint2*>(q + (long long)(row + r) * ldq + col) = make_uint2(lo[r], hi[r]);
+    }
+    // 4 x 4 byte transposes: word k holds rows 0..3 of column k
+    uint32_t w[8];
+    {
+      const uint32_t t0 = __byte_perm(lo[0], lo[1], 0x5140), t1 = __byte_perm(lo[2], lo[3], 0x5140);
+      const uint32_t t2 = __byte_perm(lo[0], lo[1], 0x7362), t3 = __byte_perm(lo[2], lo[3], 0x7362);
+      w[0] = __byte_perm(t0, t1, 0x5410); w[1] = __byte_perm(t0, t1, 0x7632);
+      w[2] = __byte_perm(t2, t3, 0x5410); w[3] = __byte_perm(t2, t3, 0x7632);
+      const uint32_t u0 = __byte_perm(hi[0], hi[1], 0x5140), u1 = __byte_perm(hi[2], hi[3], 0x5140);
+      const uint32_t u2 = __byte_perm(hi[0], hi[1], 0x7362), u3 = __byte_perm(hi[2], hi[3], 0x7362);
+      w[4] = __byte_perm(u0, u1, 0x5410); w[5] = __byte_perm(u0, u1, 0x7632);
+      w[6] = __byte_perm(u2, u3, 0x5410); w[7] = __byte_perm(u2, u3, 0x7632);
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) tile[(ci * 8 + k) * QT_PITCH + (rgg ^ sw)] = w[k];
+  }
+  __syncthreads();
+  // transposed rows: 8 lanes x 16 bytes = the tile's 128 rows of one column
+  const int l8 = tid & 7;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int c = (tid >> 3) + 32 * i;
+    const int s = (c >> 5) & 3;
+    const uint32_t* src = tile + c * QT_PITCH;
+    const uint4 v = make_uint4(src[(4 * l8 + 0) ^ s], src[(4 * l8 + 1) ^ s], src[(4 * l8 + 2) ^ s], src[(4 * l8 + 3) ^ s]);
+    if (c0 + c < cols && r0 + 16 * l8 < rows)
+      *reinterpret_cast<uint4*>(qt + (long long)(c0 + c) * ldqt + r0 + 16 * l8) = v;
+  }
+  if (amax_rec) {
+    amax = block_max_256(amax, s_red);
+    if (tid == 0 && amax > 0.f) atomicMax(amax_rec, __float_as_uint(amax));
+  }
+}
+
 // Delayed-scaling bookkeeping, one block per tensor.  state[i] = {scale, recorded maximum (float bits), hist[H]}:
 // the recorded maximum moves into hist[pos], is cleared, and the scale becomes max(hist) / 448 * margin_mul
 // (use_max) or the newest maximum / 448 * margin_mul; a tensor that recorded nothing keeps its scale.
@@ -527,6 +605,17 @@ extern "C" int ob_quant_fp8_tensor(const void* x, long long ldx, void* q, long l
   if (cols % 8 != 0 || ldx % 8 != 0 || ldq % 8 != 0) return -1;
   quant_tensor_kernel<<<quant_grid((long long)rows * (cols / 8)), 256, 0, stream>>>(
       (const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq, (const float*)scale, (unsigned*)amax_rec, rows, cols);
+  return (int)cudaGetLastError();
+}
+
+// q [rows, cols] and qt [cols, rows] = e4m3(x / *scale); optional amax_rec.  rows % 16 == 0, cols % 16 == 0.
+extern "C" int ob_quant_fp8_tensor_t(const void* x, long long ldx, void* q, long long ldq, void* qt, long long ldqt,
+                                     const void* scale, void* amax_rec, int rows, int cols, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if (cols % 16 != 0 || rows % 16 != 0 || ldx % 8 != 0 || ldq % 8 != 0 || ldqt % 16 != 0) return -1;
+  dim3 grid((cols + 127) / 128, (rows + 127) / 128);
+  quant_tensor_t_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq, (uint8_t*)qt, ldqt,
+                                                  (const float*)scale, (unsigned*)amax_rec, rows, cols);
   return (int)cudaGetLastError();
 }
 

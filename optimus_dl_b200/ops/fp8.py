@@ -214,9 +214,9 @@ def quantize_tensor_t(w: torch.Tensor, scale: torch.Tensor | None = None, amax_r
     s = scale if scale is not None else tensor_scale(w, margin_mul=margin_mul)
     q = torch.empty((rows, cols), dtype=torch.float8_e4m3fn, device=w.device)
     qt = torch.empty((cols, rows), dtype=torch.float8_e4m3fn, device=w.device)
-    rc = _lib.lib().ob_quant_fp8_block(_lib.ptr(w), w.stride(0), _lib.ptr(q), cols, _lib.ptr(qt), rows, _lib.ptr(None),
-                                       _lib.ptr(None), rows, cols, _lib.ptr(s), _lib.ptr(amax_rec), _lib.stream())
-    _lib.check(rc, "ob_quant_fp8_block")
+    rc = _lib.lib().ob_quant_fp8_tensor_t(_lib.ptr(w), w.stride(0), _lib.ptr(q), cols, _lib.ptr(qt), rows, _lib.ptr(s),
+                                          _lib.ptr(amax_rec), rows, cols, _lib.stream())
+    _lib.check(rc, "ob_quant_fp8_tensor_t")
     return q, s, qt
 
 
@@ -322,7 +322,7 @@ def fp8_wgrad_enabled() -> bool:
 
 def _cached_weight_tensor(w: torch.Tensor, holder: torch.Tensor | None = None):
     holder = holder if holder is not None else w
-    key = (w.data_ptr(), holder._version, tuple(w.shape))
+    key = (w.data_ptr(), holder._version, tuple(w.shape), _weights_epoch)
     hit = getattr(holder, "_fp8_cache_t", None)
     if hit is None or hit[0] != key:
         hit = (key, *quantize_weight_tensor(w.detach()))
@@ -331,11 +331,21 @@ def _cached_weight_tensor(w: torch.Tensor, holder: torch.Tensor | None = None):
 
 
 # ---------------------------------------------------------------------- autograd
+_weights_epoch = 0
+
+
+def weights_changed() -> None:
+    """Invalidate every cached quantised weight. Called by optimizers that update parameters through raw
+    pointers (the fused reduce-scatter + AdamW kernel), where the autograd version counter does not move."""
+    global _weights_epoch
+    _weights_epoch += 1
+
+
 def _cached_weight(w: torch.Tensor, holder: torch.Tensor | None = None):
     """Quantised weight and transpose, re-made when the parameter's version counter moves. ``holder`` is
     the long-lived tensor the cache is attached to when ``w`` is a temporary view of several parameters."""
     holder = holder if holder is not None else w
-    key = (w.data_ptr(), holder._version, tuple(w.shape))
+    key = (w.data_ptr(), holder._version, tuple(w.shape), _weights_epoch)
     hit = getattr(holder, "_fp8_cache", None)
     if hit is None or hit[0] != key:
         q, s, qt, st = quantize_block(w.detach(), with_transpose=True)

@@ -307,6 +307,9 @@ class ShardGroup:
             if real:
                 o = inf.flat_off + self.rank * inf.piece_numel
                 self.flat_param[o: o + real].copy_(self.master[inf.shard_off: inf.shard_off + real])
+        from ..ops import fp8 as fp8_ops
+
+        fp8_ops.weights_changed()
 
 
 @dataclass
@@ -641,6 +644,11 @@ class ShardedAdamW(torch.optim.Optimizer):
                            sumsq=eng.sumsq if self.max_norm > 0 else None)
                 g.gathered = eng.world == 1
         self.step_count += 1
+        # the update kernels write parameters through raw pointers (no autograd version bump): tell the caches
+        # of derived weight forms (quantised copies) that every parameter changed
+        from ..ops import fp8 as fp8_ops
+
+        fp8_ops.weights_changed()
         return None
 
     def grad_norm(self) -> torch.Tensor:
