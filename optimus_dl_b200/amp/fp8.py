@@ -110,7 +110,7 @@ def create_fp8_recipe(cfg: Any) -> FP8Recipe | None:
     if rec == Fp8RecipeType.MXFP8:
         logger.info("fp8 recipe mxfp8 is served by the block-scaled (1x128 / 128x128) e4m3 implementation")
     return FP8Recipe(fmt, rec, margin=cfg.get("margin", 0), amax_history_len=cfg.get("amax_history_len", 1024),
-                     amax_compute_algo=cfg.get("amax_compute_algo", "max"))
+                     amax_compute_algo=cfg.get("amax_compute_algo", "max"), wgrad=bool(cfg.get("wgrad", True)))
 
 
 @contextlib.contextmanager

@@ -8,9 +8,11 @@ from typing import Any
 
 @dataclass
 class Fp8Config:
-    """FP8 settings. ``recipe: blockwise`` with ``format: e4m3`` selects this package's block-scaled e4m3
-    GEMMs (1x128 activation scales, 128x128 weight scales). Fields the reference declares but never
-    reads (``param``, ``wgrad``, ``first_last_layers_bf16``, ``tp_only_amax_red``) are accepted."""
+    """FP8 settings. ``recipe: blockwise`` selects the block-scaled e4m3 GEMMs (1x128 activation scales,
+    128x128 weight scales); ``tensorwise`` / ``delayed`` select per-tensor scales (``margin``,
+    ``amax_history_len``, ``amax_compute_algo`` apply to ``delayed``; ``wgrad`` chooses FP8 or bf16 weight
+    gradients for both). Fields the reference declares but never reads (``param``,
+    ``first_last_layers_bf16``, ``tp_only_amax_red``) are accepted."""
 
     enabled: bool = False
     format: str = "hybrid"            # hybrid | e4m3 | e5m2
