@@ -18,11 +18,15 @@
 // Warp roles (576 threads): warp 0 TMA producer, warp 1 MMA issuer / TMEM owner, warps 2..17 epilogue.
 #include <cuda_fp8.h>
 
+#include "comm.cuh"
 #include "common.cuh"
+#include "gemm_core.cuh"
 #include "tensormap.cuh"
 
 namespace ob {
 namespace fp8 {
+
+using gemm::wait_flag;
 
 constexpr int BM = 128;
 constexpr int BN = 256;
@@ -48,9 +52,20 @@ struct Params {
   const float* sb;    // [ceil(N/128)][K/128]
   int* status;
   int accumulate;     // C += product (C is read in the epilogue)
+  // Gathered-A mode: rows of A8 (and their scales) are being written by other CTAs / other GPUs during this
+  // launch; a_flags[m / 128] >= a_flag_value publishes a 128-row group.  Tiles then run m-major, starting at
+  // m-tile first_m_tile (the rows that arrive first).
+  const int* a_flags;
+  int a_flag_value;
+  int first_m_tile;
 };
 
-__device__ __forceinline__ void tile_of(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+__device__ __forceinline__ void tile_of(const Params& p, int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  if (p.a_flags) {   // m-major, rotated so that the rows that are ready first come first
+    tm = (tile / tiles_n + p.first_m_tile) % tiles_m;
+    tn = tile % tiles_n;
+    return;
+  }
   const int per_group = GROUP_M * tiles_n;
   const int g = tile / per_group;
   const int first_m = g * GROUP_M;
@@ -64,9 +79,10 @@ __device__ __forceinline__ void tile_of(int tile, int tiles_m, int tiles_n, int&
 // PER_TENSOR = true: one scale per operand (p.sa[0] * p.sb[0]); the tensor core accumulates over all of K in
 // TMEM and the epilogue drains each tile once, so the main loop runs at the plain e4m3 rate.
 template <bool PER_TENSOR>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
-  extern __shared__ uint8_t smem_raw[];
+__device__ __forceinline__ void fp8_cta(const CUtensorMap* tmA_p, const CUtensorMap* tmB_p, const Params& p,
+                                        const int cta, const int n_ctas, uint8_t* smem_raw) {
+  const CUtensorMap& tmA = *tmA_p;
+  const CUtensorMap& tmB = *tmB_p;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
   uint64_t* full_bar = bars;
@@ -104,9 +120,14 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       tma_prefetch_desc(&tmB);
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = cta; tile < num_tiles && ok; tile += n_ctas) {
         int tm, tn;
-        tile_of(tile, tiles_m, tiles_n, tm, tn);
+        tile_of(p, tile, tiles_m, tiles_n, tm, tn);
+        if (p.a_flags) {
+          ok = wait_flag(p.a_flags + tm, p.a_flag_value, abort_flag, p.status);
+          if (!ok) break;
+          asm volatile("fence.proxy.async.global;" ::: "memory");   // rows written by plain stores, read by TMA
+        }
         for (int kb = 0; kb < k_blocks && ok; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status);
           if (!ok) break;
@@ -128,7 +149,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       int stage = 0; uint32_t phase = 0;
       int slot = 0; uint32_t slot_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = cta; tile < num_tiles && ok; tile += n_ctas) {
         if (PER_TENSOR) ok = mbar_wait(&part_empty[slot], slot_phase ^ 1, abort_flag, p.status);
         for (int kb = 0; kb < k_blocks && ok; ++kb) {
           if (!PER_TENSOR) ok = mbar_wait(&part_empty[slot], slot_phase ^ 1, abort_flag, p.status);
@@ -163,9 +184,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int sb_ld = k_blocks;
     const int drains = PER_TENSOR ? 1 : k_blocks;
     const float tensor_scale = PER_TENSOR ? p.sa[0] * p.sb[0] : 0.f;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    for (int tile = cta; tile < num_tiles && ok; tile += n_ctas) {
       int tm, tn;
-      tile_of(tile, tiles_m, tiles_n, tm, tn);
+      tile_of(p, tile, tiles_m, tiles_n, tm, tn);
       const int row = tm * BM + quarter * 32 + lane;
       const int col0 = tn * BN + chunk * EPI_COLS;
       const bool row_ok = row < p.M;
@@ -175,6 +196,13 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       float acc[EPI_COLS];
 #pragma unroll
       for (int j = 0; j < EPI_COLS; ++j) acc[j] = 0.f;
+      if (!PER_TENSOR && p.a_flags) {
+        // the row group's scales were written by the same remote stores as its values: acquire before reading
+        int okf = 1;
+        if (lane == 0) okf = wait_flag(p.a_flags + tm, p.a_flag_value, abort_flag, p.status) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, okf, 0) != 0;
+        if (!ok) break;
+      }
       // scales are fetched two k-blocks ahead: their global-load latency must not sit between the barrier
       // and the first use
       float sa0 = sa_row[0], sb0 = sb_row[0];
@@ -233,6 +261,13 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
+}
+
+template <bool PER_TENSOR>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  fp8_cta<PER_TENSOR>(&tmA, &tmB, p, blockIdx.x, gridDim.x, smem_raw);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -532,6 +567,112 @@ delayed_update_kernel(float* __restrict__ state, int H, int pos, float margin_mu
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// All-gather of a sequence-parallel activation fused with its quantisation and the FP8 GEMM that consumes it.
+//
+// Every rank holds `rows` rows of the bf16 activation.  The first n_copy CTAs of the launch quantise this rank's
+// rows 128 at a time (1 x 128 scales, or one given scale in per-tensor mode), store the e4m3 values -- and in
+// block mode the scales -- into EVERY rank's gathered operand (this rank's own included) with plain peer
+// stores, and then release that row group's flag on each rank.  The remaining CTAs run the GEMM over the
+// gathered operand, m-major from this rank's own rows, and acquire a row group's flag before its first TMA
+// load.  NVLink carries one byte per element instead of two, and no separate quantiser launch is needed.
+struct AgQuant {
+  const __nv_bfloat16* x;   // this rank's rows [rows, K], row stride ldx
+  long long ldx;
+  int rows, K, me, world;
+  comm::PeerPtrs a8;        // gathered e4m3 operand [world * rows, K] on every rank
+  comm::PeerPtrs sa;        // scale table [K / 128][sa_ld] on every rank (block mode)
+  long long sa_ld;
+  comm::PeerPtrs flags;     // one int per 128 rows of the gathered operand, on every rank
+  int epoch;
+  const float* tensor_scale;   // per-tensor mode: the scale to use
+  unsigned* amax_rec;          // per-tensor mode, optional: receives max|x| of this rank's rows
+};
+
+template <bool PER_TENSOR>
+__device__ __forceinline__ void quant_push(const AgQuant& a, int first, int stride, uint8_t* smem_raw) {
+  float* s_scales = reinterpret_cast<float*>(smem_raw);   // [K / 128][128] (block mode)
+  __shared__ float s_red[8];
+  const int tid = threadIdx.x;
+  const bool worker = tid < 512;            // 16 warps quantise; the rest of the block only joins the barriers
+  const int kbs = a.K / 128;
+  const int lane16 = tid & 15;
+  const int blk = tid >> 4;                 // 0..31: which 1 x 128 block of the current group of 32
+  const float inv_t = PER_TENSOR ? 1.0f / *a.tensor_scale : 0.f;
+  float amax_all = 0.f;
+  const int chunks = a.rows / 128;
+  for (int ch = first; ch < chunks; ch += stride) {
+    const int row0 = ch * 128;                       // within this rank's rows
+    const long long grow0 = (long long)a.me * a.rows + row0;   // within the gathered operand
+    const int n_blocks = 128 * kbs;
+    if (worker) {
+      for (int b0 = 0; b0 < n_blocks; b0 += 32) {
+        const int b = b0 + blk;                      // blocks run along K first: 32 of them are 8 KB of one row
+        const int r = b / kbs, kb = b - r * kbs;
+        const uint4 raw = *reinterpret_cast<const uint4*>(a.x + (long long)(row0 + r) * a.ldx + kb * 128 + lane16 * 8);
+        const float2 f0 = unpack_bf16x2(raw.x), f1 = unpack_bf16x2(raw.y), f2 = unpack_bf16x2(raw.z), f3 = unpack_bf16x2(raw.w);
+        float inv = inv_t;
+        if (!PER_TENSOR || a.amax_rec) {
+          float amax = fmaxf(fmaxf(fmaxf(fabsf(f0.x), fabsf(f0.y)), fmaxf(fabsf(f1.x), fabsf(f1.y))),
+                             fmaxf(fmaxf(fabsf(f2.x), fabsf(f2.y)), fmaxf(fabsf(f3.x), fabsf(f3.y))));
+          if (PER_TENSOR) {
+            amax_all = fmaxf(amax_all, amax);
+          } else {
+#pragma unroll
+            for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            const float scale = amax > 0.f ? amax / E4M3_MAX : 1.0f;
+            inv = 1.0f / scale;
+            if (lane16 == 0) s_scales[kb * 128 + r] = scale;
+          }
+        }
+        uint2 packed;
+        packed.x = e4m3x4(f0.x * inv, f0.y * inv, f1.x * inv, f1.y * inv);
+        packed.y = e4m3x4(f2.x * inv, f2.y * inv, f3.x * inv, f3.y * inv);
+        const long long off = (grow0 + r) * (long long)a.K + kb * 128 + lane16 * 8;
+        for (int pr = 0; pr < a.world; ++pr)
+          *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(a.a8.p[pr]) + off) = packed;
+      }
+    }
+    if (!PER_TENSOR) {
+      __syncthreads();
+      // scale rows: 128 consecutive floats per k-block and rank
+      if (worker) {
+        for (int i = tid; i < kbs * 128; i += 512) {
+          const int kb = i >> 7, r = i & 127;
+          const float v = s_scales[i];
+          for (int pr = 0; pr < a.world; ++pr)
+            reinterpret_cast<float*>(a.sa.p[pr])[(long long)kb * a.sa_ld + grow0 + r] = v;
+        }
+      }
+    }
+    // all of this CTA's stores for the group are visible system-wide before the flags go out
+    __threadfence_system();
+    __syncthreads();
+    if (tid < a.world) {
+      int* f = reinterpret_cast<int*>(a.flags.p[tid]) + (int)(grow0 / 128);
+      asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(f), "r"(a.epoch) : "memory");
+    }
+    __syncthreads();   // s_scales is reused by the next group
+  }
+  if (PER_TENSOR && a.amax_rec) {
+    amax_all = warp_max(amax_all);
+    if (worker && (tid & 31) == 0 && amax_all > 0.f) atomicMax(a.amax_rec, __float_as_uint(amax_all));
+  }
+  (void)s_red;
+}
+
+template <bool PER_TENSOR>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_fp8_ag_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p,
+                   const AgQuant a, const int n_copy) {
+  extern __shared__ uint8_t smem_raw[];
+  if ((int)blockIdx.x < n_copy) {
+    quant_push<PER_TENSOR>(a, blockIdx.x, n_copy, smem_raw);
+    return;
+  }
+  fp8_cta<PER_TENSOR>(&tmA, &tmB, p, blockIdx.x - n_copy, gridDim.x - n_copy, smem_raw);
+}
+
 }  // namespace fp8
 }  // namespace ob
 
@@ -580,6 +721,67 @@ extern "C" int ob_gemm_fp8_tensor(const void* A8, long long lda, const void* sa,
                                   const void* sb, void* C, long long ldc, int M, int N, int K, int accumulate,
                                   int* status, cudaStream_t stream) {
   return launch_fp8<true>(A8, lda, sa, 0, B8, ldb, sb, C, ldc, M, N, K, accumulate, status, stream);
+}
+
+// Fused quantise + all-gather + FP8 GEMM (see gemm_fp8_ag_kernel).  x: this rank's bf16 rows [rows, K];
+// a8_ptrs / sa_ptrs / flag_ptrs: every rank's gathered operand, scale table and flag words (index `me` = local);
+// C [world * rows, N] = gathered(x) . B8^T.  per_tensor != 0: scales are *tensor_scale (the same value on every
+// rank) and *sb; otherwise 1 x 128 scales travel with the rows and sb is the 128 x 128 table of B.
+// rows % 128 == 0, K % 128 == 0.
+extern "C" int ob_gemm_fp8_ag(const void* x, long long ldx, int rows, const void* const* a8_ptrs,
+                              const void* const* sa_ptrs, long long sa_ld, const void* const* flag_ptrs, int world,
+                              int me, int epoch, const void* B8, long long ldb, const void* sb, void* C, long long ldc,
+                              int N, int K, int per_tensor, const void* tensor_scale, void* amax_rec, int n_copy,
+                              int* status, cudaStream_t stream) {
+  if (rows <= 0 || N <= 0 || K <= 0) return 0;
+  if (rows % 128 != 0 || K % BK != 0 || ldx % 8 != 0 || world < 1 || world > comm::MAX_RANKS || me < 0 || me >= world)
+    return -1;
+  if ((long long)K * 4 > (long long)STAGES * STAGE_BYTES) return -1;   // scale staging of one row group
+  const int M = rows * world;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d(&ta, a8_ptrs[me], M, K, K, BM, BK, 1);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tb, B8, N, K, ldb, BN, BK, 1);
+  if (rc) return rc;
+  Params p{};
+  p.M = M; p.N = N; p.K = K; p.C = (__nv_bfloat16*)C; p.ldc = ldc;
+  p.sa = per_tensor ? (const float*)tensor_scale : (const float*)sa_ptrs[me];
+  p.sa_ld = sa_ld; p.sb = (const float*)sb; p.status = status; p.accumulate = 0;
+  p.a_flags = (const int*)flag_ptrs[me]; p.a_flag_value = epoch; p.first_m_tile = (me * rows) / BM;
+  AgQuant a{};
+  a.x = (const __nv_bfloat16*)x; a.ldx = ldx; a.rows = rows; a.K = K; a.me = me; a.world = world;
+  for (int i = 0; i < world; ++i) {
+    a.a8.p[i] = const_cast<void*>(a8_ptrs[i]);
+    a.sa.p[i] = per_tensor ? nullptr : const_cast<void*>(sa_ptrs[i]);
+    a.flags.p[i] = const_cast<void*>(flag_ptrs[i]);
+  }
+  a.sa_ld = sa_ld; a.epoch = epoch; a.tensor_scale = (const float*)tensor_scale; a.amax_rec = (unsigned*)amax_rec;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (n_copy < 1) n_copy = 1;
+  if (n_copy > rows / 128) n_copy = rows / 128;
+  if (n_copy > sms / 2) n_copy = sms / 2;
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  int gemm_ctas = sms - n_copy;
+  if (gemm_ctas > tiles) gemm_ctas = tiles;
+  // every CTA of the launch must be resident at once (GEMM CTAs wait for copy CTAs): grid <= SM count, one CTA per SM
+  if (per_tensor) {
+    static bool configured = false;
+    if (!configured) {
+      OB_CUDA_CHECK(cudaFuncSetAttribute(gemm_fp8_ag_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+      configured = true;
+    }
+    gemm_fp8_ag_kernel<true><<<n_copy + gemm_ctas, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p, a, n_copy);
+  } else {
+    static bool configured = false;
+    if (!configured) {
+      OB_CUDA_CHECK(cudaFuncSetAttribute(gemm_fp8_ag_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+      configured = true;
+    }
+    gemm_fp8_ag_kernel<false><<<n_copy + gemm_ctas, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p, a, n_copy);
+  }
+  return (int)cudaGetLastError();
 }
 
 static int quant_grid(long long vecs) {

@@ -154,6 +154,60 @@ class _Site:
         dist.barrier(group=tp.group)   # zeroed flags are in place everywhere before anybody publishes into them
 
 
+class _Fp8Site:
+    """Gathered e4m3 operand ``[M, K]``, its 1x128 scale table ``[K / 128, M]`` and row flags of one call site,
+    all in symmetric memory: every rank's quantise-and-push CTAs write into every rank's copy
+    (``ob_gemm_fp8_ag``)."""
+
+    def __init__(self, tp: "TPState", M: int, K: int):
+        heap = tp.heap()
+        self.a8 = heap.empty(M * K, torch.uint8)
+        self.sa = heap.empty((K // 128) * M, torch.float32)
+        self.flags = heap.empty(max(M // 128, 16), torch.int32, zero=True)
+        self.M, self.K, self.epoch = M, K, 0
+        torch.cuda.synchronize(tp.device)
+        dist.barrier(group=tp.group)
+
+
+def ag_gemm_fp8(tp: "TPState", x_local: torch.Tensor, owners: list, site_key: Any):
+    """Quantise this rank's rows, all-gather them in e4m3 and multiply by the (cached) quantised weight in one
+    launch. Returns ``y [P * rows, N]`` (bf16), or ``None`` when the shapes do not fit the fused kernel.
+
+    Block recipe: 1x128 scales travel with the rows. Per-tensor recipes: one scale for the gathered tensor, the
+    maximum over the group of each rank's own scale (so every rank quantises alike)."""
+    rows, K = x_local.shape
+    if not (tp.fused and x_local.is_cuda and x_local.dtype == torch.bfloat16 and rows % 128 == 0 and K % 128 == 0
+            and K * 4 <= 196608):
+        return None
+    M = rows * tp.size
+    w = owners[0] if len(owners) == 1 else lin_ops._fused_view(list(owners))
+    N = w.shape[0]
+    x_local = x_local if (x_local.stride(1) == 1 and x_local.stride(0) % 8 == 0) else x_local.contiguous()
+    mode = fp8_ops.scaling_mode()
+    scale = None
+    if mode == "block":
+        wq, wscale, _, _ = fp8_ops._cached_weight(w, owners[0])
+    else:
+        wq, wscale, _ = fp8_ops._cached_weight_tensor(w, owners[0])
+        scale = fp8_ops.tensor_scale(x_local, margin_mul=fp8_ops._margin_mul())
+        dist.all_reduce(scale, op=dist.ReduceOp.MAX, group=tp.group)
+    key = ("fp8", site_key, M, K)
+    site = tp._sites.get(key)
+    if site is None:
+        site = tp._sites[key] = _Fp8Site(tp, M, K)
+    site.epoch += 1
+    # every rank is done reading this site's previous contents once all ranks have arrived here
+    tp.barrier()
+    dev = x_local.device
+    y = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    rc = _lib.lib().ob_gemm_fp8_ag(
+        _lib.ptr(x_local), x_local.stride(0), rows, site.a8.peers.c, site.sa.peers.c, M, site.flags.peers.c, tp.size,
+        tp.rank, site.epoch, _lib.ptr(wq), wq.stride(0), _lib.ptr(wscale), _lib.ptr(y), N, N, K,
+        int(mode != "block"), _lib.ptr(scale), _lib.ptr(None), tp.n_push, _lib.ptr(_lib.status_word(dev)), _lib.stream())
+    _lib.check(rc, "ob_gemm_fp8_ag")
+    return y
+
+
 def _site_of(tp: "TPState", key: Any, numel: int, n_flags: int) -> "_Site":
     site = tp._sites.get(key)
     if site is None or site.numel < numel or site.n_flags < n_flags:
@@ -383,10 +437,15 @@ class _ColumnParallel(torch.autograd.Function):
         bias = None if bs[0] is None else lin_ops._fused_bias(bs)
         wf = _cat_weights(ws)
         use_fp8 = fp8_ops.usable(x, ws)
+        regather = False
         if use_fp8:
-            # FP8 context: block-scaled e4m3 products; the collectives run as separate library calls here
-            x_full = all_gather_rows(tp, x) if sp else x
-            y = fp8_ops.forward_product(x_full, ws)
+            y = ag_gemm_fp8(tp, x, ws, ("col", id(ws[0]))) if sp else None
+            if y is not None:
+                # fused quantise + e4m3 all-gather + GEMM; the bf16 rows are gathered again for the weight gradient
+                x_full, regather = x, True
+            else:
+                x_full = all_gather_rows(tp, x) if sp else x
+                y = fp8_ops.forward_product(x_full, ws)
             if bias is not None:
                 y = y + bias
         elif sp:
@@ -394,7 +453,7 @@ class _ColumnParallel(torch.autograd.Function):
         else:
             x_full, y = x, gemm.gemm(x, wf, bias=bias)
         ctx.save_for_backward(x_full, *ws)
-        ctx.use_fp8 = use_fp8
+        ctx.use_fp8, ctx.regather = use_fp8, regather
         ctx.tp, ctx.sp, ctx.n, ctx.params, ctx.has_bias = tp, sp, n, ws, bias is not None
         ctx.sizes = [w.shape[0] for w in ws]
         return y
@@ -403,6 +462,8 @@ class _ColumnParallel(torch.autograd.Function):
     def backward(ctx, dy):
         x_full, *ws = ctx.saved_tensors
         tp, n = ctx.tp, ctx.n
+        if ctx.regather:
+            x_full = all_gather_rows(tp, x_full)
         dy2 = dy if dy.is_contiguous() else dy.contiguous()
         wf = _cat_weights(ws)
         dx = None

@@ -65,3 +65,9 @@ def test_tensor_parallel_pull_all_gather(unique_port, kind):
     out = _run("_mp_tp_check.py", 2, unique_port, "nccl", kind, "1", str(unique_port),
                extra_env={"OB_TP_PUSH_MIN_WORLD": "99"})
     assert "TP_OK" in out, out[-4000:]
+
+
+def test_fp8_all_gather_gemm_fused(unique_port):
+    """Quantise + e4m3 all-gather + GEMM in one launch equals the unfused sequence (block and per-tensor scales)."""
+    out = _run("_mp_fp8_ag_check.py", 2, unique_port, str(unique_port))
+    assert "FP8_AG_OK" in out
