@@ -216,6 +216,15 @@ def bench_tp(op: str, t: Timer, cases) -> None:
             def base():   # bf16 all-gather, quantiser launch, FP8 GEMM
                 xf = T.all_gather_rows(state, x)
                 return fp8.forward_product(xf, [w])
+        elif op == "tp_gemm_rs_fp8":
+            from . import fp8
+
+            x = torch.randn(M, K, device="cuda").bfloat16()
+            w = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
+            fused = lambda: T.gemm_rs_fp8(state, x, [w])  # noqa: E731
+
+            def base():
+                return T.reduce_scatter_rows(state, fp8.forward_product(x, [w]))
         else:
             x = torch.randn(M, K, device="cuda").bfloat16()
             w = torch.randn(N, K, device="cuda").bfloat16()
@@ -224,7 +233,7 @@ def bench_tp(op: str, t: Timer, cases) -> None:
             def base():
                 return T.reduce_scatter_rows(state, gemm.gemm(x, w))
 
-        x_plain = x if op == "tp_gemm_rs" else torch.randn(M, K, device="cuda").bfloat16()
+        x_plain = x if op in ("tp_gemm_rs", "tp_gemm_rs_fp8") else torch.randn(M, K, device="cuda").bfloat16()
 
         def stream_time(fn, reps: int = 10) -> float:
             """Per-call milliseconds of ``reps`` calls issued back to back: ranks stay in lockstep through the
@@ -243,7 +252,7 @@ def bench_tp(op: str, t: Timer, cases) -> None:
             torch.cuda.synchronize()
             return a.elapsed_time(b) / reps
 
-        if op == "tp_ag_gemm_fp8":
+        if op in ("tp_ag_gemm_fp8", "tp_gemm_rs_fp8"):
             a8, sa = fp8.quantize_rowwise(x_plain)
             w8, sw, _, _ = fp8._cached_weight(w)
             ms_plain = stream_time(lambda: fp8.gemm_fp8(a8, sa, w8, sw))
@@ -252,7 +261,7 @@ def bench_tp(op: str, t: Timer, cases) -> None:
         vals = torch.tensor([stream_time(fused), stream_time(base), ms_plain], device="cuda")
         dist.all_reduce(vals, op=dist.ReduceOp.MAX)
         if dist.get_rank() == 0:
-            link_bytes = (world - 1) / world * M * (N * 2 if op == "tp_gemm_rs" else K * (1 if op == "tp_ag_gemm_fp8" else 2))
+            link_bytes = (world - 1) / world * M * (N * 2 if op in ("tp_gemm_rs", "tp_gemm_rs_fp8") else K * (1 if op == "tp_ag_gemm_fp8" else 2))
             roof_ms = max(2.0 * M * N * K / (_peaks().get("bf16_tflops", 1590.0) * 1e9), link_bytes / 770e6)
             _emit(op, dict(M=M, N=N, K=K, world=world), float(vals[0]), flops=2.0 * M * N * K,
                   nccl_then_gemm_ms=round(float(vals[1]), 4), gemm_only_ms=round(float(vals[2]), 4),
@@ -266,7 +275,7 @@ def bench_tp(op: str, t: Timer, cases) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", required=True, choices=["gemm_bf16", "gemm_skinny", "gemm_fp8", "attention", "decode", "sampler", "elementwise",
-                                                    "tp_ag_gemm", "tp_gemm_rs", "tp_ag_gemm_fp8"])
+                                                    "tp_ag_gemm", "tp_gemm_rs", "tp_ag_gemm_fp8", "tp_gemm_rs_fp8"])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--small", action="store_true", help="one small case (for profiler captures)")
     args = ap.parse_args()

@@ -58,10 +58,19 @@ struct Params {
   const int* a_flags;
   int a_flag_value;
   int first_m_tile;
+  int m_major;        // tiles run m-major starting at first_m_tile (gathered-A and reduce-scatter modes)
+  // Reduce-scatter mode (rs_rows > 0, a multiple of 128): the bf16 tile goes to rank (row / rs_rows)'s staging
+  // buffer, slot rs_me, instead of C: rs_dst[owner] + (rs_me * rs_rows + row % rs_rows) * ldc + col.
+  void* rs_dst[comm::MAX_RANKS];
+  int rs_rows;
+  int rs_me;
 };
 
+constexpr int RS_STAGE_PER_WARP = 2048;   // 32 rows x 64 bytes, staged per epilogue warp
+constexpr int SMEM_RS_BYTES = SMEM_BYTES + EPI_WARPS * RS_STAGE_PER_WARP;
+
 __device__ __forceinline__ void tile_of(const Params& p, int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
-  if (p.a_flags) {   // m-major, rotated so that the rows that are ready first come first
+  if (p.m_major) {   // m-major, rotated so that the rows that are ready (or wanted) first come first
     tm = (tile / tiles_n + p.first_m_tile) % tiles_m;
     tn = tile % tiles_n;
     return;
@@ -78,7 +87,7 @@ __device__ __forceinline__ void tile_of(const Params& p, int tile, int tiles_m, 
 // PER_TENSOR = false: block-scaled product (each 128-wide k-block is drained from TMEM and scaled in registers).
 // PER_TENSOR = true: one scale per operand (p.sa[0] * p.sb[0]); the tensor core accumulates over all of K in
 // TMEM and the epilogue drains each tile once, so the main loop runs at the plain e4m3 rate.
-template <bool PER_TENSOR>
+template <bool PER_TENSOR, bool RS = false>
 __device__ __forceinline__ void fp8_cta(const CUtensorMap* tmA_p, const CUtensorMap* tmB_p, const Params& p,
                                         const int cta, const int n_ctas, uint8_t* smem_raw) {
   const CUtensorMap& tmA = *tmA_p;
@@ -229,7 +238,37 @@ __device__ __forceinline__ void fp8_cta(const CUtensorMap* tmA_p, const CUtensor
         if (++slot == SLOTS) { slot = 0; slot_phase ^= 1; }
       }
       if (!ok) break;
-      if (row_ok && cols_ok) {
+      if (RS) {
+        // Each lane holds 64 columns of its own row.  Sending them as they are would make every 16-byte store
+        // its own NVLink transaction, so the warp stages 32 columns at a time in shared memory (chunks swizzled
+        // by row pair: conflict-free both ways) and sends 64-byte row segments, eight rows per instruction.
+        uint8_t* stg = smem + STAGES * STAGE_BYTES + 256 + e * RS_STAGE_PER_WARP;
+        const int tile_row0 = tm * BM;
+        const int owner = tile_row0 / p.rs_rows;
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.rs_dst[owner]) +
+                             ((long long)p.rs_me * p.rs_rows + (tile_row0 - owner * p.rs_rows)) * p.ldc;
+#pragma unroll
+        for (int h = 0; h < EPI_COLS / 32; ++h) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int j = 32 * h + 8 * q;
+            const uint4 o = make_uint4(pack_bf16x2(acc[j], acc[j + 1]), pack_bf16x2(acc[j + 2], acc[j + 3]),
+                                       pack_bf16x2(acc[j + 4], acc[j + 5]), pack_bf16x2(acc[j + 6], acc[j + 7]));
+            *reinterpret_cast<uint4*>(stg + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)) = o;
+          }
+          __syncwarp();
+#pragma unroll
+          for (int it = 0; it < 4; ++it) {
+            const int r = 8 * it + (lane >> 2), c = lane & 3;
+            const uint4 v = *reinterpret_cast<const uint4*>(stg + r * 64 + ((c ^ ((r >> 1) & 3)) << 4));
+            const int lrow = quarter * 32 + r;
+            const int col = col0 + 32 * h + 8 * c;
+            if (tile_row0 + lrow < p.M && col < p.N)
+              *reinterpret_cast<uint4*>(dst + (long long)lrow * p.ldc + col) = v;
+          }
+          __syncwarp();
+        }
+      } else if (row_ok && cols_ok) {
         __nv_bfloat16* crow = p.C + (long long)row * p.ldc + col0;
         const bool vec = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && col0 + EPI_COLS <= p.N;
         if (vec) {
@@ -663,6 +702,13 @@ __device__ __forceinline__ void quant_push(const AgQuant& a, int first, int stri
 
 template <bool PER_TENSOR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_fp8_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
+  extern __shared__ uint8_t smem_raw[];   // SMEM_RS_BYTES: the ring plus the epilogue warps' staging
+  fp8_cta<PER_TENSOR, true>(&tmA, &tmB, p, blockIdx.x, gridDim.x, smem_raw);
+}
+
+template <bool PER_TENSOR>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_fp8_ag_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p,
                    const AgQuant a, const int n_copy) {
   extern __shared__ uint8_t smem_raw[];
@@ -747,7 +793,7 @@ extern "C" int ob_gemm_fp8_ag(const void* x, long long ldx, int rows, const void
   p.M = M; p.N = N; p.K = K; p.C = (__nv_bfloat16*)C; p.ldc = ldc;
   p.sa = per_tensor ? (const float*)tensor_scale : (const float*)sa_ptrs[me];
   p.sa_ld = sa_ld; p.sb = (const float*)sb; p.status = status; p.accumulate = 0;
-  p.a_flags = (const int*)flag_ptrs[me]; p.a_flag_value = epoch; p.first_m_tile = (me * rows) / BM;
+  p.a_flags = (const int*)flag_ptrs[me]; p.a_flag_value = epoch; p.first_m_tile = (me * rows) / BM; p.m_major = 1;
   AgQuant a{};
   a.x = (const __nv_bfloat16*)x; a.ldx = ldx; a.rows = rows; a.K = K; a.me = me; a.world = world;
   for (int i = 0; i < world; ++i) {
@@ -780,6 +826,51 @@ extern "C" int ob_gemm_fp8_ag(const void* x, long long ldx, int rows, const void
       configured = true;
     }
     gemm_fp8_ag_kernel<false><<<n_copy + gemm_ctas, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p, a, n_copy);
+  }
+  return (int)cudaGetLastError();
+}
+
+// Row-parallel FP8 GEMM whose epilogue is the send half of a reduce-scatter: the bf16 partial product
+// A8 [M,K] . B8 [N,K]^T of this rank goes, tile by tile, into slot `me` of the owner rank's staging buffer
+// (dst_ptrs[owner], [world][rows_per_rank][ldc]); a following ob_rs_sum adds the slots.  per_tensor selects
+// the scale scheme as in ob_gemm_fp8_tensor / ob_gemm_fp8_block.  rows_per_rank % 128 == 0, N % 8 == 0.
+extern "C" int ob_gemm_fp8_rs(const void* A8, long long lda, const void* sa, long long sa_ld, const void* B8,
+                              long long ldb, const void* sb, const void* const* dst_ptrs, int world, int me,
+                              int rows_per_rank, long long ldc, int M, int N, int K, int per_tensor,
+                              int first_tile_shift, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (K % BK != 0 || rows_per_rank % BM != 0 || N % 8 != 0 || ldc % 8 != 0 || world < 1 || world > comm::MAX_RANKS ||
+      M != rows_per_rank * world)
+    return -1;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d(&ta, A8, M, K, lda, BM, BK, 1);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tb, B8, N, K, ldb, BN, BK, 1);
+  if (rc) return rc;
+  Params p{};
+  p.M = M; p.N = N; p.K = K; p.C = nullptr; p.ldc = ldc; p.sa = (const float*)sa; p.sa_ld = sa_ld;
+  p.sb = (const float*)sb; p.status = status;
+  p.m_major = 1; p.first_m_tile = first_tile_shift; p.rs_rows = rows_per_rank; p.rs_me = me;
+  for (int i = 0; i < world; ++i) p.rs_dst[i] = const_cast<void*>(dst_ptrs[i]);
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int grid = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  if (grid > sms) grid = sms;
+  if (per_tensor) {
+    static bool configured = false;
+    if (!configured) {
+      OB_CUDA_CHECK(cudaFuncSetAttribute(gemm_fp8_rs_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_RS_BYTES));
+      configured = true;
+    }
+    gemm_fp8_rs_kernel<true><<<grid, NUM_THREADS, SMEM_RS_BYTES, stream>>>(ta, tb, p);
+  } else {
+    static bool configured = false;
+    if (!configured) {
+      OB_CUDA_CHECK(cudaFuncSetAttribute(gemm_fp8_rs_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_RS_BYTES));
+      configured = true;
+    }
+    gemm_fp8_rs_kernel<false><<<grid, NUM_THREADS, SMEM_RS_BYTES, stream>>>(ta, tb, p);
   }
   return (int)cudaGetLastError();
 }

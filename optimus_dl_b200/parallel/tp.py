@@ -386,6 +386,44 @@ def gemm_rs(tp: TPState, a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False
     return out
 
 
+def gemm_rs_fp8(tp: TPState, x2: torch.Tensor, owners: list, *, transpose_w: bool = False,
+                residual: torch.Tensor | None = None) -> torch.Tensor | None:
+    """``reduce_scatter_rows(q(x2) q(W)^T) + residual`` (``q(x2) q(W^T)^T`` with ``transpose_w``: the input gradient
+    of a column-parallel layer) with the send half in the FP8 GEMM's epilogue. ``None`` when shapes do not fit."""
+    M, K = x2.shape
+    rows = M // tp.size
+    w = owners[0] if len(owners) == 1 else lin_ops._fused_view(list(owners))
+    N = w.shape[1] if transpose_w else w.shape[0]
+    if not (tp.fused and x2.is_cuda and x2.dtype == torch.bfloat16 and M % tp.size == 0 and rows % 128 == 0
+            and K % 128 == 0 and N % 8 == 0 and (residual is None or residual.is_contiguous())):
+        return None
+    mode = fp8_ops.scaling_mode()
+    if mode == "block":
+        wq, ws, wqt, wst = fp8_ops._cached_weight(w, owners[0])
+        b8, sb = (wqt, wst) if transpose_w else (wq, ws)
+        a8, sa = fp8_ops.quantize_rowwise(x2)
+        sa_ld = sa.stride(0)
+    else:
+        wq, ws, wqt = fp8_ops._cached_weight_tensor(w, owners[0])
+        b8, sb = (wqt if transpose_w else wq), ws
+        a8, sa = fp8_ops._quantize_activation(x2, owners[0], "dy" if transpose_w else "x")
+        sa_ld = 0
+    stage = tp.next_stage(tp.size * rows * N)
+    shift = (((tp.rank + 1) % tp.size) * rows) // 128   # the next rank's rows first, this rank's own last
+    dev = x2.device
+    rc = _lib.lib().ob_gemm_fp8_rs(_lib.ptr(a8), a8.stride(0), _lib.ptr(sa), sa_ld, _lib.ptr(b8), b8.stride(0),
+                                   _lib.ptr(sb), stage.peers.c, tp.size, tp.rank, rows, N, M, N, K, int(mode != "block"),
+                                   shift, _lib.ptr(_lib.status_word(dev)), _lib.stream())
+    _lib.check(rc, "ob_gemm_fp8_rs")
+    out = torch.empty((rows, N), dtype=torch.bfloat16, device=dev)
+    epoch = tp.next_barrier_epoch()
+    rc = _lib.lib().ob_rs_sum(tp._barrier.buf.peers.c, tp.rank, tp.size, epoch, _lib.ptr(stage.tensor), rows, N, N,
+                              _lib.ptr(residual), N, _lib.ptr(out), N, 0, _lib.ptr(_lib.status_word(dev)),
+                              _lib.stream())
+    _lib.check(rc, "ob_rs_sum")
+    return out
+
+
 # ====================================================================== autograd functions
 def _weight_grads(params: list, dy2: torch.Tensor, x2: torch.Tensor, sizes: list[int], need: list[bool]) -> list:
     """``dW_i = dy_i^T x`` for column slices of ``dy2``; writes into ``main_grad`` where a parameter has one."""
@@ -469,11 +507,13 @@ class _ColumnParallel(torch.autograd.Function):
         dx = None
         if ctx.needs_input_grad[2]:
             if ctx.use_fp8:
-                dx = fp8_ops.dgrad_product(dy2, ctx.params)
-                if ctx.sp:
-                    dx = reduce_scatter_rows(tp, dx)
-                else:
-                    dist.all_reduce(dx, group=tp.group)
+                dx = gemm_rs_fp8(tp, dy2, ctx.params, transpose_w=True) if ctx.sp else None
+                if dx is None:
+                    dx = fp8_ops.dgrad_product(dy2, ctx.params)
+                    if ctx.sp:
+                        dx = reduce_scatter_rows(tp, dx)
+                    else:
+                        dist.all_reduce(dx, group=tp.group)
             elif ctx.sp:
                 dx = gemm_rs(tp, dy2, wf, b_mn=True)
             else:
@@ -536,15 +576,18 @@ class _RowParallel(torch.autograd.Function):
         use_fp8 = fp8_ops.usable(x, [w])
         ctx.use_fp8 = use_fp8
         if use_fp8:
-            y = fp8_ops.forward_product(x if x.is_contiguous() else x.contiguous(), [w])
-            if sp:
-                y = reduce_scatter_rows(tp, y)
-            else:
-                dist.all_reduce(y, group=tp.group)
+            xc = x if x.is_contiguous() else x.contiguous()
+            y = gemm_rs_fp8(tp, xc, [w], residual=residual) if sp else None
+            if y is None:
+                y = fp8_ops.forward_product(xc, [w])
+                if sp:
+                    y = reduce_scatter_rows(tp, y)
+                else:
+                    dist.all_reduce(y, group=tp.group)
+                if residual is not None:
+                    y = y + residual
             if bias is not None:
                 y = y + bias
-            if residual is not None:
-                y = y + residual
         elif sp:
             y = gemm_rs(tp, x, w, residual=residual)
             if bias is not None:
