@@ -645,31 +645,46 @@ __device__ __forceinline__ void quant_push(const AgQuant& a, int first, int stri
     const long long grow0 = (long long)a.me * a.rows + row0;   // within the gathered operand
     const int n_blocks = 128 * kbs;
     if (worker) {
-      for (int b0 = 0; b0 < n_blocks; b0 += 32) {
-        const int b = b0 + blk;                      // blocks run along K first: 32 of them are 8 KB of one row
-        const int r = b / kbs, kb = b - r * kbs;
-        const uint4 raw = *reinterpret_cast<const uint4*>(a.x + (long long)(row0 + r) * a.ldx + kb * 128 + lane16 * 8);
-        const float2 f0 = unpack_bf16x2(raw.x), f1 = unpack_bf16x2(raw.y), f2 = unpack_bf16x2(raw.z), f3 = unpack_bf16x2(raw.w);
-        float inv = inv_t;
-        if (!PER_TENSOR || a.amax_rec) {
-          float amax = fmaxf(fmaxf(fmaxf(fabsf(f0.x), fabsf(f0.y)), fmaxf(fabsf(f1.x), fabsf(f1.y))),
-                             fmaxf(fmaxf(fabsf(f2.x), fabsf(f2.y)), fmaxf(fabsf(f3.x), fabsf(f3.y))));
-          if (PER_TENSOR) {
-            amax_all = fmaxf(amax_all, amax);
-          } else {
+      constexpr int U = 8;   // loads in flight per thread: the copy CTAs are few, so each must keep many bytes moving
+      for (int b0 = 0; b0 < n_blocks; b0 += 32 * U) {
+        uint4 raw[U];
 #pragma unroll
-            for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-            const float scale = amax > 0.f ? amax / E4M3_MAX : 1.0f;
-            inv = 1.0f / scale;
-            if (lane16 == 0) s_scales[kb * 128 + r] = scale;
-          }
+        for (int u = 0; u < U; ++u) {
+          const int b = b0 + 32 * u + blk;             // blocks run along K first: 32 of them are 8 KB of one row
+          const int r = b / kbs, kb = b - r * kbs;
+          raw[u] = make_uint4(0, 0, 0, 0);
+          if (b < n_blocks)
+            raw[u] = *reinterpret_cast<const uint4*>(a.x + (long long)(row0 + r) * a.ldx + kb * 128 + lane16 * 8);
         }
-        uint2 packed;
-        packed.x = e4m3x4(f0.x * inv, f0.y * inv, f1.x * inv, f1.y * inv);
-        packed.y = e4m3x4(f2.x * inv, f2.y * inv, f3.x * inv, f3.y * inv);
-        const long long off = (grow0 + r) * (long long)a.K + kb * 128 + lane16 * 8;
-        for (int pr = 0; pr < a.world; ++pr)
-          *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(a.a8.p[pr]) + off) = packed;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int b = b0 + 32 * u + blk;
+          const bool live = b < n_blocks;                // uniform per half-warp (a block is 16 lanes)
+          const int r = live ? b / kbs : 0, kb = live ? b - r * kbs : 0;
+          const float2 f0 = unpack_bf16x2(raw[u].x), f1 = unpack_bf16x2(raw[u].y), f2 = unpack_bf16x2(raw[u].z),
+                       f3 = unpack_bf16x2(raw[u].w);
+          float inv = inv_t;
+          if (!PER_TENSOR || a.amax_rec) {
+            float amax = fmaxf(fmaxf(fmaxf(fabsf(f0.x), fabsf(f0.y)), fmaxf(fabsf(f1.x), fabsf(f1.y))),
+                               fmaxf(fmaxf(fabsf(f2.x), fabsf(f2.y)), fmaxf(fabsf(f3.x), fabsf(f3.y))));
+            if (PER_TENSOR) {
+              amax_all = fmaxf(amax_all, amax);
+            } else {
+#pragma unroll
+              for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+              const float scale = amax > 0.f ? amax / E4M3_MAX : 1.0f;
+              inv = 1.0f / scale;
+              if (live && lane16 == 0) s_scales[kb * 128 + r] = scale;
+            }
+          }
+          uint2 packed;
+          packed.x = e4m3x4(f0.x * inv, f0.y * inv, f1.x * inv, f1.y * inv);
+          packed.y = e4m3x4(f2.x * inv, f2.y * inv, f3.x * inv, f3.y * inv);
+          const long long off = (grow0 + r) * (long long)a.K + kb * 128 + lane16 * 8;
+          if (live)
+            for (int pr = 0; pr < a.world; ++pr)
+              *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(a.a8.p[pr]) + off) = packed;
+        }
       }
     }
     if (!PER_TENSOR) {

@@ -203,7 +203,8 @@ def ag_gemm_fp8(tp: "TPState", x_local: torch.Tensor, owners: list, site_key: An
     rc = _lib.lib().ob_gemm_fp8_ag(
         _lib.ptr(x_local), x_local.stride(0), rows, site.a8.peers.c, site.sa.peers.c, M, site.flags.peers.c, tp.size,
         tp.rank, site.epoch, _lib.ptr(wq), wq.stride(0), _lib.ptr(wscale), _lib.ptr(y), N, N, K,
-        int(mode != "block"), _lib.ptr(scale), _lib.ptr(None), tp.n_push, _lib.ptr(_lib.status_word(dev)), _lib.stream())
+        int(mode != "block"), _lib.ptr(scale), _lib.ptr(None), 2 * tp.n_push, _lib.ptr(_lib.status_word(dev)),
+        _lib.stream())
     _lib.check(rc, "ob_gemm_fp8_ag")
     return y
 
