@@ -193,7 +193,7 @@ def _declare(l: ctypes.CDLL) -> None:
     sig("ob_gemm_fp8_tensor", [P, L, P, P, L, P, P, L, I, I, I, I, P, P])
     sig("ob_fp8_amax_scale", [P, L, I, I, P, P, F, P])
     sig("ob_quant_fp8_tensor", [P, L, P, L, P, P, I, I, P])
-    sig("ob_gemm_fp8_ag", [P, L, I, PP, PP, PP, I, I, I, P, L, P, P, L, I, I, I, P, P, I, P, P])
+    sig("ob_gemm_fp8_ag", [P, L, I, PP, PP, L, PP, I, I, I, P, L, P, P, L, I, I, I, P, P, I, P, P])
     sig("ob_gemm_fp8_rs", [P, L, P, L, P, L, P, PP, I, I, I, L, I, I, I, I, I, P, P])
     sig("ob_quant_fp8_tensor_t", [P, L, P, L, P, L, P, P, I, I, P])
     sig("ob_fp8_delayed_update", [P, I, I, I, F, I, P])

@@ -47,9 +47,8 @@ struct Params {
   int M, N, K;
   __nv_bfloat16* C;
   long long ldc;
-  const float* sa;    // scale of (row, kb) at sa[row * sa_rs + kb * sa_ld]: [K/128][sa_ld] tables have sa_rs = 1,
-  long long sa_ld;    // row-major [M][K/128] tables (gathered-A mode) have sa_rs = K/128, sa_ld = 1
-  long long sa_rs;
+  const float* sa;    // [K/128][sa_ld]
+  long long sa_ld;    // >= M
   const float* sb;    // [ceil(N/128)][K/128]
   int* status;
   int accumulate;     // C += product (C is read in the epilogue)
@@ -201,7 +200,7 @@ __device__ __forceinline__ void fp8_cta(const CUtensorMap* tmA_p, const CUtensor
       const int col0 = tn * BN + chunk * EPI_COLS;
       const bool row_ok = row < p.M;
       const bool cols_ok = col0 < p.N;
-      const float* sa_row = p.sa + (row_ok && !PER_TENSOR ? (long long)row * p.sa_rs : 0);
+      const float* sa_row = p.sa + (row_ok && !PER_TENSOR ? row : 0);
       const float* sb_row = p.sb + (PER_TENSOR ? 0 : (long long)(cols_ok ? col0 / 128 : 0) * sb_ld);
       float acc[EPI_COLS];
 #pragma unroll
@@ -610,29 +609,29 @@ delayed_update_kernel(float* __restrict__ state, int H, int pos, float margin_mu
 // ---------------------------------------------------------------------------------------------
 // All-gather of a sequence-parallel activation fused with its quantisation and the FP8 GEMM that consumes it.
 //
-// Every rank holds `rows` rows of the bf16 activation.  The first n_copy CTAs of the launch (n_copy divides 128)
-// quantise this rank's rows: for each 128-row group every copy CTA takes 128 / n_copy of its rows, so a group is
-// complete after a few microseconds rather than after one CTA has walked all of it.  The e4m3 values -- and in
-// block mode the 1 x 128 scales -- go into EVERY rank's gathered operand (this rank's own included) with plain
-// peer stores; each CTA then adds 1 to that group's flag on every rank (release, system scope).  Flags only
-// count up: group g of use number `epoch` is complete when its flag reaches epoch * n_copy.  The remaining CTAs
-// run the GEMM over the gathered operand, m-major from this rank's own rows, and acquire a group's flag before
-// its first TMA load.  NVLink carries one byte per element instead of two, and no separate quantiser launch is
-// needed.  Scales are stored row-major ([M][K / 128]) so that a CTA's share of a group is one contiguous run.
+// Every rank holds `rows` rows of the bf16 activation.  The first n_copy CTAs of the launch quantise this rank's
+// rows 128 at a time (1 x 128 scales, or one given scale in per-tensor mode), store the e4m3 values -- and in
+// block mode the scales -- into EVERY rank's gathered operand (this rank's own included) with plain peer
+// stores, and then release that row group's flag on each rank.  The remaining CTAs run the GEMM over the
+// gathered operand, m-major from this rank's own rows, and acquire a row group's flag before its first TMA
+// load.  NVLink carries one byte per element instead of two, and no separate quantiser launch is needed.
 struct AgQuant {
   const __nv_bfloat16* x;   // this rank's rows [rows, K], row stride ldx
   long long ldx;
   int rows, K, me, world;
   comm::PeerPtrs a8;        // gathered e4m3 operand [world * rows, K] on every rank
-  comm::PeerPtrs sa;        // scale table [world * rows][K / 128] on every rank (block mode)
+  comm::PeerPtrs sa;        // scale table [K / 128][sa_ld] on every rank (block mode)
+  long long sa_ld;
   comm::PeerPtrs flags;     // one int per 128 rows of the gathered operand, on every rank
+  int epoch;
   const float* tensor_scale;   // per-tensor mode: the scale to use
   unsigned* amax_rec;          // per-tensor mode, optional: receives max|x| of this rank's rows
 };
 
 template <bool PER_TENSOR>
-__device__ __forceinline__ void quant_push(const AgQuant& a, int part, int parts, uint8_t* smem_raw) {
-  float* s_scales = reinterpret_cast<float*>(smem_raw);   // [rows_part][K / 128] (block mode)
+__device__ __forceinline__ void quant_push(const AgQuant& a, int first, int stride, uint8_t* smem_raw) {
+  float* s_scales = reinterpret_cast<float*>(smem_raw);   // [K / 128][128] (block mode)
+  __shared__ float s_red[8];
   const int tid = threadIdx.x;
   const bool worker = tid < 512;            // 16 warps quantise; the rest of the block only joins the barriers
   const int kbs = a.K / 128;
@@ -640,12 +639,11 @@ __device__ __forceinline__ void quant_push(const AgQuant& a, int part, int parts
   const int blk = tid >> 4;                 // 0..31: which 1 x 128 block of the current group of 32
   const float inv_t = PER_TENSOR ? 1.0f / *a.tensor_scale : 0.f;
   float amax_all = 0.f;
-  const int rows_part = 128 / parts;
-  const int n_blocks = rows_part * kbs;
   const int chunks = a.rows / 128;
-  for (int ch = 0; ch < chunks; ++ch) {
-    const int row0 = ch * 128 + part * rows_part;              // within this rank's rows
+  for (int ch = first; ch < chunks; ch += stride) {
+    const int row0 = ch * 128;                       // within this rank's rows
     const long long grow0 = (long long)a.me * a.rows + row0;   // within the gathered operand
+    const int n_blocks = 128 * kbs;
     if (worker) {
       constexpr int U = 8;   // loads in flight per thread: the copy CTAs are few, so each must keep many bytes moving
       for (int b0 = 0; b0 < n_blocks; b0 += 32 * U) {
@@ -676,7 +674,7 @@ __device__ __forceinline__ void quant_push(const AgQuant& a, int part, int parts
               for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
               const float scale = amax > 0.f ? amax / E4M3_MAX : 1.0f;
               inv = 1.0f / scale;
-              if (live && lane16 == 0) s_scales[b] = scale;   // b = r * kbs + kb: row-major like the destination
+              if (live && lane16 == 0) s_scales[kb * 128 + r] = scale;
             }
           }
           uint2 packed;
@@ -691,20 +689,22 @@ __device__ __forceinline__ void quant_push(const AgQuant& a, int part, int parts
     }
     if (!PER_TENSOR) {
       __syncthreads();
-      // this CTA's scales of the group: one contiguous run of rows_part * kbs floats on every rank
+      // scale rows: 128 consecutive floats per k-block and rank
       if (worker) {
-        for (int i = tid; i < n_blocks; i += 512) {
+        for (int i = tid; i < kbs * 128; i += 512) {
+          const int kb = i >> 7, r = i & 127;
           const float v = s_scales[i];
-          for (int pr = 0; pr < a.world; ++pr) reinterpret_cast<float*>(a.sa.p[pr])[grow0 * kbs + i] = v;
+          for (int pr = 0; pr < a.world; ++pr)
+            reinterpret_cast<float*>(a.sa.p[pr])[(long long)kb * a.sa_ld + grow0 + r] = v;
         }
       }
     }
-    // all of this CTA's stores for the group are visible system-wide before its arrival is counted
+    // all of this CTA's stores for the group are visible system-wide before the flags go out
     __threadfence_system();
     __syncthreads();
     if (tid < a.world) {
-      int* f = reinterpret_cast<int*>(a.flags.p[tid]) + (int)(((long long)a.me * a.rows + ch * 128) / 128);
-      asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(f) : "memory");
+      int* f = reinterpret_cast<int*>(a.flags.p[tid]) + (int)(grow0 / 128);
+      asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(f), "r"(a.epoch) : "memory");
     }
     __syncthreads();   // s_scales is reused by the next group
   }
@@ -712,6 +712,7 @@ __device__ __forceinline__ void quant_push(const AgQuant& a, int part, int parts
     amax_all = warp_max(amax_all);
     if (worker && (tid & 31) == 0 && amax_all > 0.f) atomicMax(a.amax_rec, __float_as_uint(amax_all));
   }
+  (void)s_red;
 }
 
 template <bool PER_TENSOR>
@@ -754,7 +755,7 @@ static int launch_fp8(const void* A8, long long lda, const void* sa, long long s
   if (rc) return rc;
   Params p{};
   p.M = M; p.N = N; p.K = K; p.C = (__nv_bfloat16*)C; p.ldc = ldc; p.sa = (const float*)sa; p.sa_ld = sa_ld;
-  p.sa_rs = 1; p.sb = (const float*)sb; p.status = status; p.accumulate = accumulate;
+  p.sb = (const float*)sb; p.status = status; p.accumulate = accumulate;
   static bool configured = false;
   if (!configured) {
     OB_CUDA_CHECK(cudaFuncSetAttribute(gemm_fp8_kernel<PER_TENSOR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -786,22 +787,17 @@ extern "C" int ob_gemm_fp8_tensor(const void* A8, long long lda, const void* sa,
 // Fused quantise + all-gather + FP8 GEMM (see gemm_fp8_ag_kernel).  x: this rank's bf16 rows [rows, K];
 // a8_ptrs / sa_ptrs / flag_ptrs: every rank's gathered operand, scale table and flag words (index `me` = local);
 // C [world * rows, N] = gathered(x) . B8^T.  per_tensor != 0: scales are *tensor_scale (the same value on every
-// rank) and *sb; otherwise 1 x 128 scales travel with the rows (row-major table [world * rows][K / 128]) and sb
-// is the 128 x 128 table of B.  `epoch` counts the uses of these flag words (1, 2, ...); n_copy must be the
-// same for every use of them.  rows % 128 == 0, K % 128 == 0.
+// rank) and *sb; otherwise 1 x 128 scales travel with the rows and sb is the 128 x 128 table of B.
+// rows % 128 == 0, K % 128 == 0.
 extern "C" int ob_gemm_fp8_ag(const void* x, long long ldx, int rows, const void* const* a8_ptrs,
-                              const void* const* sa_ptrs, const void* const* flag_ptrs, int world,
+                              const void* const* sa_ptrs, long long sa_ld, const void* const* flag_ptrs, int world,
                               int me, int epoch, const void* B8, long long ldb, const void* sb, void* C, long long ldc,
                               int N, int K, int per_tensor, const void* tensor_scale, void* amax_rec, int n_copy,
                               int* status, cudaStream_t stream) {
   if (rows <= 0 || N <= 0 || K <= 0) return 0;
   if (rows % 128 != 0 || K % BK != 0 || ldx % 8 != 0 || world < 1 || world > comm::MAX_RANKS || me < 0 || me >= world)
     return -1;
-  // copy CTAs: a power of two that divides 128 (each takes 128 / n_copy rows of every group)
-  int nc = 8;
-  while (nc * 2 <= n_copy && nc < 32) nc *= 2;
-  n_copy = nc;
-  if ((long long)(128 / n_copy) * (K / 128) * 4 > (long long)STAGES * STAGE_BYTES) return -1;   // scale staging
+  if ((long long)K * 4 > (long long)STAGES * STAGE_BYTES) return -1;   // scale staging of one row group
   const int M = rows * world;
   CUtensorMap ta, tb;
   int rc = make_tmap_2d(&ta, a8_ptrs[me], M, K, K, BM, BK, 1);
@@ -811,9 +807,8 @@ extern "C" int ob_gemm_fp8_ag(const void* x, long long ldx, int rows, const void
   Params p{};
   p.M = M; p.N = N; p.K = K; p.C = (__nv_bfloat16*)C; p.ldc = ldc;
   p.sa = per_tensor ? (const float*)tensor_scale : (const float*)sa_ptrs[me];
-  p.sa_ld = per_tensor ? 0 : 1; p.sa_rs = per_tensor ? 0 : K / BK;
-  p.sb = (const float*)sb; p.status = status; p.accumulate = 0;
-  p.a_flags = (const int*)flag_ptrs[me]; p.a_flag_value = epoch * n_copy; p.first_m_tile = (me * rows) / BM; p.m_major = 1;
+  p.sa_ld = sa_ld; p.sb = (const float*)sb; p.status = status; p.accumulate = 0;
+  p.a_flags = (const int*)flag_ptrs[me]; p.a_flag_value = epoch; p.first_m_tile = (me * rows) / BM; p.m_major = 1;
   AgQuant a{};
   a.x = (const __nv_bfloat16*)x; a.ldx = ldx; a.rows = rows; a.K = K; a.me = me; a.world = world;
   for (int i = 0; i < world; ++i) {
@@ -821,10 +816,13 @@ extern "C" int ob_gemm_fp8_ag(const void* x, long long ldx, int rows, const void
     a.sa.p[i] = per_tensor ? nullptr : const_cast<void*>(sa_ptrs[i]);
     a.flags.p[i] = const_cast<void*>(flag_ptrs[i]);
   }
-  a.tensor_scale = (const float*)tensor_scale; a.amax_rec = (unsigned*)amax_rec;
+  a.sa_ld = sa_ld; a.epoch = epoch; a.tensor_scale = (const float*)tensor_scale; a.amax_rec = (unsigned*)amax_rec;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (n_copy < 1) n_copy = 1;
+  if (n_copy > rows / 128) n_copy = rows / 128;
+  if (n_copy > sms / 2) n_copy = sms / 2;
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int gemm_ctas = sms - n_copy;
   if (gemm_ctas > tiles) gemm_ctas = tiles;
@@ -865,7 +863,7 @@ extern "C" int ob_gemm_fp8_rs(const void* A8, long long lda, const void* sa, lon
   rc = make_tmap_2d(&tb, B8, N, K, ldb, BN, BK, 1);
   if (rc) return rc;
   Params p{};
-  p.M = M; p.N = N; p.K = K; p.C = nullptr; p.ldc = ldc; p.sa = (const float*)sa; p.sa_ld = sa_ld; p.sa_rs = 1;
+  p.M = M; p.N = N; p.K = K; p.C = nullptr; p.ldc = ldc; p.sa = (const float*)sa; p.sa_ld = sa_ld;
   p.sb = (const float*)sb; p.status = status;
   p.m_major = 1; p.first_m_tile = first_tile_shift; p.rs_rows = rows_per_rank; p.rs_me = me;
   for (int i = 0; i < world; ++i) p.rs_dst[i] = const_cast<void*>(dst_ptrs[i]);

@@ -155,10 +155,9 @@ class _Site:
 
 
 class _Fp8Site:
-    """Gathered e4m3 operand ``[M, K]``, its 1x128 scale table ``[M, K / 128]`` and row-group arrival counters of
-    one call site, all in symmetric memory: every rank's quantise-and-push CTAs write into every rank's copy
-    (``ob_gemm_fp8_ag``). The counters only grow (use ``epoch`` is complete at ``epoch * copy CTAs``), so the
-    number of copy CTAs is fixed per site."""
+    """Gathered e4m3 operand ``[M, K]``, its 1x128 scale table ``[K / 128, M]`` and row flags of one call site,
+    all in symmetric memory: every rank's quantise-and-push CTAs write into every rank's copy
+    (``ob_gemm_fp8_ag``)."""
 
     def __init__(self, tp: "TPState", M: int, K: int):
         heap = tp.heap()
@@ -202,7 +201,7 @@ def ag_gemm_fp8(tp: "TPState", x_local: torch.Tensor, owners: list, site_key: An
     dev = x_local.device
     y = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
     rc = _lib.lib().ob_gemm_fp8_ag(
-        _lib.ptr(x_local), x_local.stride(0), rows, site.a8.peers.c, site.sa.peers.c, site.flags.peers.c, tp.size,
+        _lib.ptr(x_local), x_local.stride(0), rows, site.a8.peers.c, site.sa.peers.c, M, site.flags.peers.c, tp.size,
         tp.rank, site.epoch, _lib.ptr(wq), wq.stride(0), _lib.ptr(wscale), _lib.ptr(y), N, N, K,
         int(mode != "block"), _lib.ptr(scale), _lib.ptr(None), 2 * tp.n_push, _lib.ptr(_lib.status_word(dev)),
         _lib.stream())
