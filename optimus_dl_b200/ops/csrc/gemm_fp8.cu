@@ -795,15 +795,18 @@ extern "C" int ob_gemm_fp8_ag(const void* x, long long ldx, int rows, const void
                               int N, int K, int per_tensor, const void* tensor_scale, void* amax_rec, int n_copy,
                               int* status, cudaStream_t stream) {
   if (rows <= 0 || N <= 0 || K <= 0) return 0;
-  if (rows % 128 != 0 || K % BK != 0 || ldx % 8 != 0 || world < 1 || world > comm::MAX_RANKS || me < 0 || me >= world)
-    return -1;
-  if ((long long)K * 4 > (long long)STAGES * STAGE_BYTES) return -1;   // scale staging of one row group
+  // distinct codes per failed precondition: the caller reports the number
+  if (rows % 128 != 0) return -11;
+  if (K % BK != 0) return -12;
+  if (ldx % 8 != 0) return -13;
+  if (world < 1 || world > comm::MAX_RANKS || me < 0 || me >= world) return -14;
+  if ((long long)K * 4 > (long long)STAGES * STAGE_BYTES) return -15;   // scale staging of one row group
   const int M = rows * world;
   CUtensorMap ta, tb;
   int rc = make_tmap_2d(&ta, a8_ptrs[me], M, K, K, BM, BK, 1);
-  if (rc) return rc;
+  if (rc) return rc - 1000;
   rc = make_tmap_2d(&tb, B8, N, K, ldb, BN, BK, 1);
-  if (rc) return rc;
+  if (rc) return rc - 2000;
   Params p{};
   p.M = M; p.N = N; p.K = K; p.C = (__nv_bfloat16*)C; p.ldc = ldc;
   p.sa = per_tensor ? (const float*)tensor_scale : (const float*)sa_ptrs[me];
