@@ -156,7 +156,7 @@ def main() -> None:
         model = build_model(mcfg)
     torch.set_default_dtype(prev)
     if args.fp8:
-        model = build_model_transform({"_name": "transformer_engine", "replace_norm": False}).apply(model)
+        model = build_model_transform({"_name": "transformer_engine", "replace_norm": True}).apply(model)
     if tp > 1:
         model = build_model_transform({"_name": "tensor_parallel", "custom_model_kwargs": {
             "sequence_parallel": True, "loss_parallel": True}}).apply(model, collective=collective, device=device)

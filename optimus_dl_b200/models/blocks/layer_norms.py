@@ -32,7 +32,14 @@ class RMSNorm(nn.Module):
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None):
         """``rmsnorm(x) * w``; with ``residual`` returns ``(rmsnorm(x + residual) * w, x + residual)``."""
-        return norm_ops.rms_norm(x, self.weight, self.eps, residual)
+        emit = False
+        if getattr(self, "_fp8_out", False) and x.is_cuda:
+            # marked by the transformer_engine transform: the consumers are FP8 linear layers with 1x128 scales
+            from ...amp.fp8 import fp8_enabled
+            from ...ops import fp8 as fp8_ops
+
+            emit = fp8_enabled() and fp8_ops.scaling_mode() == "block"
+        return norm_ops.rms_norm(x, self.weight, self.eps, residual, emit_fp8=emit)
 
     def extra_repr(self) -> str:
         return f"{self.weight.numel()}, eps={self.eps}"

@@ -10,6 +10,8 @@
 //             second kernel adds the partials in a fixed order (bitwise reproducible).
 // Math follows the fp32 ("gemma" casting) convention of the reference's RMSNorm
 // (optimus_dl/modules/model/blocks/layer_norms.py:86-120).
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 
 namespace ob {
@@ -29,12 +31,17 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return t;
 }
 
-template <bool LAYERNORM, int NVEC>
+// QUANT: besides y the kernel writes e4m3(y) with one scale per 1 x 128 block (q [rows, D], scales
+// [D / 128][scale_ld]): a block is 16 consecutive threads' vectors, so its maximum is a half-warp reduction of
+// values the thread already holds, and the linear layer that consumes y needs no quantiser pass.  The quantised
+// values are taken from y as stored (rounded to bf16), exactly what a separate quantiser would read.  D % 128 == 0.
+template <bool LAYERNORM, int NVEC, bool QUANT = false>
 __global__ void __launch_bounds__(THREADS, NVEC <= 2 ? 6 : 2)
 norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
                 const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ b,
                 __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ h_out, float* __restrict__ rstd_out,
-                float* __restrict__ mean_out, int rows, int D, float eps) {
+                float* __restrict__ mean_out, int rows, int D, float eps, uint8_t* __restrict__ q = nullptr,
+                float* __restrict__ scales = nullptr, long long scale_ld = 0) {
   __shared__ float red[THREADS / 32];
   const int nvec = D / 8;
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -88,6 +95,7 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
 #pragma unroll
     for (int i = 0; i < NVEC; ++i) {
       const int idx = threadIdx.x + i * THREADS;
+      uint4 packed = make_uint4(0, 0, 0, 0);
       if (idx < nvec) {
         uint4 wu = reinterpret_cast<const uint4*>(w)[idx];
         float2 w0 = unpack_bf16x2(wu.x), w1 = unpack_bf16x2(wu.y), w2 = unpack_bf16x2(wu.z), w3 = unpack_bf16x2(wu.w);
@@ -101,8 +109,30 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
         float o[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mean) * rstd * ww[j] + bb[j];
-        yr[idx] = make_uint4(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]), pack_bf16x2(o[4], o[5]),
-                             pack_bf16x2(o[6], o[7]));
+        packed = make_uint4(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]), pack_bf16x2(o[4], o[5]),
+                            pack_bf16x2(o[6], o[7]));
+        yr[idx] = packed;
+      }
+      if (QUANT) {
+        // nvec is a multiple of 16 here, so a half-warp is wholly inside or wholly outside the row; all 32 lanes
+        // take part in the shuffles either way
+        const float2 f0 = unpack_bf16x2(packed.x), f1 = unpack_bf16x2(packed.y), f2 = unpack_bf16x2(packed.z),
+                     f3 = unpack_bf16x2(packed.w);
+        float amax = fmaxf(fmaxf(fmaxf(fabsf(f0.x), fabsf(f0.y)), fmaxf(fabsf(f1.x), fabsf(f1.y))),
+                           fmaxf(fmaxf(fabsf(f2.x), fabsf(f2.y)), fmaxf(fabsf(f3.x), fabsf(f3.y))));
+#pragma unroll
+        for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        const float scale = amax > 0.f ? amax / 448.0f : 1.0f;
+        const float inv = 1.0f / scale;
+        if (idx < nvec) {
+          uint2 e;
+          e.x = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(f0.x * inv, f0.y * inv), __NV_SATFINITE, __NV_E4M3) |
+                ((uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(f1.x * inv, f1.y * inv), __NV_SATFINITE, __NV_E4M3) << 16);
+          e.y = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(f2.x * inv, f2.y * inv), __NV_SATFINITE, __NV_E4M3) |
+                ((uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(f3.x * inv, f3.y * inv), __NV_SATFINITE, __NV_E4M3) << 16);
+          reinterpret_cast<uint2*>(q + (size_t)row * D)[idx] = e;
+          if ((idx & 15) == 0) scales[(long long)(idx >> 4) * scale_ld + row] = scale;
+        }
       }
     }
   }
@@ -264,6 +294,23 @@ extern "C" int ob_rmsnorm_fwd(const void* x, const void* residual, const void* w
   if (rows == 0) return 0;
   OB_NORM_FWD_LAUNCH(false, D, norm_fwd_grid(rows), (const __nv_bfloat16*)x, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)w, nullptr, (__nv_bfloat16*)y,
       (__nv_bfloat16*)h_out, (float*)rstd, nullptr, rows, D, eps);
+  return (int)cudaGetLastError();
+}
+
+// As ob_rmsnorm_fwd, and also q = e4m3(y) with 1 x 128 scales [D / 128][scale_ld] (scale_ld >= rows).  D % 128 == 0.
+extern "C" int ob_rmsnorm_fwd_fp8(const void* x, const void* residual, const void* w, void* y, void* h_out, void* rstd,
+                                  void* q, void* scales, long long scale_ld, int rows, int D, float eps,
+                                  cudaStream_t stream) {
+  if (!norm_args_ok(D) || D % 128 != 0 || scale_ld < rows) return -1;
+  if (rows == 0) return 0;
+  const int grid = norm_fwd_grid(rows);
+#define OB_NORM_FP8_ARGS                                                                                             \
+  (const __nv_bfloat16*)x, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)w, nullptr, (__nv_bfloat16*)y,      \
+      (__nv_bfloat16*)h_out, (float*)rstd, nullptr, rows, D, eps, (uint8_t*)q, (float*)scales, scale_ld
+  if (D <= THREADS * 8) norm_fwd_kernel<false, 1, true><<<grid, THREADS, 0, stream>>>(OB_NORM_FP8_ARGS);
+  else if (D <= THREADS * 16) norm_fwd_kernel<false, 2, true><<<grid, THREADS, 0, stream>>>(OB_NORM_FP8_ARGS);
+  else norm_fwd_kernel<false, 4, true><<<grid, THREADS, 0, stream>>>(OB_NORM_FP8_ARGS);
+#undef OB_NORM_FP8_ARGS
   return (int)cudaGetLastError();
 }
 

@@ -70,6 +70,9 @@ def gemm_fp8_ref(a8: torch.Tensor, sa: torch.Tensor, b8: torch.Tensor, sb: torch
 
 # ---------------------------------------------------------------------- kernels
 def quantize_rowwise(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    pre = getattr(x, "_fp8_rowwise", None)   # left by a producer that quantised in its own launch (RMSNorm)
+    if pre is not None and pre[0].shape[-1] == x.shape[-1] and pre[0].numel() == x.numel():
+        return pre
     x = x.reshape(-1, x.shape[-1])
     rows, cols = x.shape
     if not kernel_ok(x) or cols % BLOCK != 0:
@@ -402,6 +405,9 @@ class _Fp8Linear(torch.autograd.Function):
         x2 = x.reshape(-1, shp[-1])
         if not x2.is_contiguous():
             x2 = x2.contiguous()
+        pre = getattr(x, "_fp8_rowwise", None)
+        if pre is not None and x2 is not x:
+            x2._fp8_rowwise = pre          # quantised by the producing norm launch
         w = owners[0] if len(owners) == 1 else lin_ops._fused_view(list(owners))
         T = x2.shape[0]
         # FP8 weight gradient: the transposed e4m3 copy of x (made in the same pass as the forward operand) is

@@ -32,7 +32,7 @@ def _bf16(t: torch.Tensor | None) -> torch.Tensor | None:
 
 class _RMSNorm(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, residual, eps):
+    def forward(ctx, x, weight, residual, eps, emit_fp8=False):
         shp = x.shape
         D = shp[-1]
         x2 = x.reshape(-1, D).contiguous()
@@ -42,16 +42,29 @@ class _RMSNorm(torch.autograd.Function):
         y = torch.empty_like(x2)
         h = torch.empty_like(x2) if res2 is not None else None
         rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
-        rc = _lib.lib().ob_rmsnorm_fwd(_lib.ptr(x2), _lib.ptr(res2), _lib.ptr(w), _lib.ptr(y), _lib.ptr(h),
-                                       _lib.ptr(rstd), rows, D, float(eps), _lib.stream())
-        _lib.check(rc, "ob_rmsnorm_fwd")
+        q = scales = None
+        if emit_fp8 and D % 128 == 0:
+            # the consumer is an FP8 linear layer: its 1x128-quantised input comes out of this launch
+            q = torch.empty((rows, D), dtype=torch.float8_e4m3fn, device=x.device)
+            scales = torch.empty((D // 128, rows), dtype=torch.float32, device=x.device)
+            rc = _lib.lib().ob_rmsnorm_fwd_fp8(_lib.ptr(x2), _lib.ptr(res2), _lib.ptr(w), _lib.ptr(y), _lib.ptr(h),
+                                               _lib.ptr(rstd), _lib.ptr(q), _lib.ptr(scales), rows, rows, D, float(eps),
+                                               _lib.stream())
+            _lib.check(rc, "ob_rmsnorm_fwd_fp8")
+        else:
+            rc = _lib.lib().ob_rmsnorm_fwd(_lib.ptr(x2), _lib.ptr(res2), _lib.ptr(w), _lib.ptr(y), _lib.ptr(h),
+                                           _lib.ptr(rstd), rows, D, float(eps), _lib.stream())
+            _lib.check(rc, "ob_rmsnorm_fwd")
         ctx.save_for_backward(h if h is not None else x2, w, rstd)
         ctx.has_res = residual is not None
         ctx.wdtype = weight.dtype
         ctx.shape = shp
+        yv = y.view(shp)
+        if q is not None:
+            yv._fp8_rowwise = (q, scales)   # picked up by ops.fp8.quantize_rowwise
         if h is not None:
-            return y.view(shp), h.view(shp)
-        return y.view(shp), None
+            return yv, h.view(shp)
+        return yv, None
 
     @staticmethod
     def backward(ctx, dy, dh):
@@ -68,13 +81,16 @@ class _RMSNorm(torch.autograd.Function):
                               _lib.ptr(partial), _lib.ptr(dw), None, 0, rows, D, _lib.stream())
         _lib.check(rc, "ob_rmsnorm_bwd")
         dxv = dx.view(ctx.shape)
-        return dxv, dw.to(ctx.wdtype), (dxv if ctx.has_res else None), None
+        return dxv, dw.to(ctx.wdtype), (dxv if ctx.has_res else None), None, None
 
 
-def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5, residual: torch.Tensor | None = None):
-    """``y = rmsnorm(x + residual) * weight``. Returns ``y`` or ``(y, x + residual)`` when a residual is given."""
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5, residual: torch.Tensor | None = None,
+             emit_fp8: bool = False):
+    """``y = rmsnorm(x + residual) * weight``. Returns ``y`` or ``(y, x + residual)`` when a residual is given.
+    ``emit_fp8``: also produce the 1x128 block-quantised e4m3 form of ``y`` in the same launch and attach it to
+    ``y`` (``y._fp8_rowwise``) for the FP8 linear layer that consumes it."""
     if _kernel_ok(x) and (residual is None or (residual.dtype == x.dtype and residual.shape == x.shape)):
-        y, h = _RMSNorm.apply(x, weight, residual, eps)
+        y, h = _RMSNorm.apply(x, weight, residual, eps, emit_fp8)
         return y if residual is None else (y, h)
     if residual is not None:
         h = x + residual

@@ -982,6 +982,9 @@ def apply_tensor_parallel(model: nn.Module, mesh: Any, loss_parallel: bool = Fal
     tied = model.transformer.wte.weight is model.lm_head.weight
     model.to(tp.device)
     sp = sequence_parallel
+    for m in model.modules():
+        if getattr(m, "_fp8_out", False):
+            m._fp8_out = False   # under TP the fused all-gather kernel quantises; a norm-side copy would go unused
     for block in model.transformer.h:
         attn = block.attn
         _shard_linears_adjacent([attn.wq, attn.wk, attn.wv], 0, tp)
