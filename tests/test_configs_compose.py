@@ -53,3 +53,10 @@ def test_transformer_engine_variants_parse():
 
     for key in cfg.keys():
         assert build_model_transform(cfg[key]) is not None
+
+
+@pytest.mark.parametrize("preset,recipe", [("fp8_delayed", "delayed"), ("fp8_tensorwise", "tensorwise")])
+def test_fp8_amp_presets_compose(preset, recipe):
+    cfg = compose.compose([os.path.join(ROOT, "train")], "train_llama_fp8", [f"optimization/amp={preset}"], apply_env=False)
+    fp8 = cfg["optimization"]["amp"]["fp8"]
+    assert fp8["enabled"] and fp8["recipe"] == recipe and fp8["wgrad"]
