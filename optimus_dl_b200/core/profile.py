@@ -17,6 +17,40 @@ import torch
 logger = logging.getLogger(__name__)
 
 
+# ---------------------------------------------------------------------- NVTX ranges
+_NVTX = None
+
+
+def nvtx_enabled() -> bool:
+    """NVTX ranges are emitted when ``OPTIMUS_NVTX=1`` and a CUDA device exists (off by default: zero cost)."""
+    global _NVTX
+    if _NVTX is None:
+        import os
+
+        _NVTX = os.environ.get("OPTIMUS_NVTX", "0") not in ("", "0", "false", "False") and torch.cuda.is_available()
+    return _NVTX
+
+
+class nvtx_range:
+    """``with nvtx_range("train/forward"):`` marks a phase for timeline tools; a no-op unless enabled.
+    Ranges are placed around the train step's phases and around every transformer block."""
+
+    __slots__ = ("name", "on")
+
+    def __init__(self, name: str):
+        self.name, self.on = name, nvtx_enabled()
+
+    def __enter__(self):
+        if self.on:
+            torch.cuda.nvtx.range_push(self.name)
+        return self
+
+    def __exit__(self, *exc):
+        if self.on:
+            torch.cuda.nvtx.range_pop()
+        return False
+
+
 def measured_next(it: Iterator) -> tuple[float, Any]:
     t0 = time.perf_counter()
     v = next(it)

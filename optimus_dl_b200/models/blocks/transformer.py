@@ -6,6 +6,7 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
+from ...core.profile import nvtx_range
 from .attention import RotarySelfAttention
 from .layer_norms import RMSNorm
 from .mlp import build_mlp
@@ -28,8 +29,10 @@ class RotaryTransformerBlock(nn.Module):
 
     def forward(self, x: torch.Tensor, *, freqs_cis: torch.Tensor | None = None, seq_lens=None, document_ids=None,
                 position_ids=None, cu_seqlens=None, max_seqlen=None, doc_start=None) -> torch.Tensor:
-        a = self.attn(self.ln_1(x), freqs_cis=freqs_cis, seq_lens=seq_lens, document_ids=document_ids,
-                      position_ids=position_ids, cu_seqlens=cu_seqlens, max_seqlen=max_seqlen, doc_start=doc_start)
-        # second norm fuses the residual add: h = x + a, y = norm(h)
-        y, h = self.ln_2(a, residual=x)
-        return self.mlp(y, residual=h)
+        with nvtx_range("block/attention"):
+            a = self.attn(self.ln_1(x), freqs_cis=freqs_cis, seq_lens=seq_lens, document_ids=document_ids,
+                          position_ids=position_ids, cu_seqlens=cu_seqlens, max_seqlen=max_seqlen, doc_start=doc_start)
+        with nvtx_range("block/mlp"):
+            # second norm fuses the residual add: h = x + a, y = norm(h)
+            y, h = self.ln_2(a, residual=x)
+            return self.mlp(y, residual=h)

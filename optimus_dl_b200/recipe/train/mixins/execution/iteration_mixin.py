@@ -16,7 +16,7 @@ from typing import Any
 
 import torch
 
-from .....core.profile import get_sm_metrics, measured_next
+from .....core.profile import get_sm_metrics, measured_next, nvtx_range
 from .....metrics.base import meters_group
 from .....metrics.common import log_averaged, log_summed
 from .....model_transforms.distributed import accumulation_context
@@ -60,21 +60,22 @@ class TrainingIterationMixin:
                 last = mb == acc_steps - 1
                 with accumulation_context(model, last):
                     t0 = time.perf_counter()
-                    with training_context["amp_ctx"]():
+                    with training_context["amp_ctx"](), nvtx_range("train/forward"):
                         loss, exposed = criterion(model, batch, requested_protocols=requested)
                     loss = loss / acc_steps
                     t_fwd += (time.perf_counter() - t0) * 1e3
                     if metric_engine is not None and should_log:
                         metric_engine.update(dict(model=model, batch=batch), exposed)
                     t0 = time.perf_counter()
-                    with training_context["fp8_backward_ctx"]():
+                    with training_context["fp8_backward_ctx"](), nvtx_range("train/backward"):
                         (scaler.scale(loss) if scaler is not None else loss).backward()
                     t_bwd += (time.perf_counter() - t0) * 1e3
             log_averaged("perf/batch_get", t_get, round=2)
             log_averaged("perf/forward", t_fwd, round=2)
             log_averaged("perf/backward", t_bwd, round=2)
             t0 = time.perf_counter()
-            skipped = self._optimizer_step(model, optimizer, scaler, clip_grad_norm)
+            with nvtx_range("train/optimizer"):
+                skipped = self._optimizer_step(model, optimizer, scaler, clip_grad_norm)
             log_averaged("perf/optimizer", (time.perf_counter() - t0) * 1e3, round=2)
             if ev1 is not None:
                 ev1.record()
