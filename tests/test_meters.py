@@ -1,0 +1,174 @@
+"""Meter classes, the group registry and cross-rank merging (optimus_dl/modules/metrics/base.py:30-745,
+optimus_dl/modules/metrics/common.py:29-766)."""
+
+import math
+import time
+
+import pytest
+
+from optimus_dl_b200.metrics import base as mb
+from optimus_dl_b200.metrics import common as mc
+
+
+def test_average_meter_weights_rounding_and_merge():
+    m = mc.AverageMeter(round=2)
+    assert m.compute() == 0.0
+    m.log(1.0, 1.0)
+    m.log(4.0, 3.0)
+    assert m.compute() == round(13.0 / 4.0, 2)
+    other = mc.AverageMeter()
+    other.log(10.0, 4.0)
+    m.merge(other.state_dict())
+    assert m.compute() == round(53.0 / 8.0, 2)
+    clone = mc.AverageMeter()
+    clone.load_state_dict(m.state_dict())
+    assert clone.compute() == m.compute()
+
+
+def test_summed_max_min_meters():
+    s = mc.SummedMeter()
+    for v in (1, 2.5, 3):
+        s.log(v)
+    assert s.compute() == 6.5
+    hi, lo = mc.MaxMeter(), mc.MinMeter()
+    assert hi.compute() == 0.0 and lo.compute() == 0.0
+    for v in (3, -1, 7):
+        hi.log(v)
+        lo.log(v)
+    assert hi.compute() == 7 and lo.compute() == -1
+    other = mc.MaxMeter()
+    other.log(11)
+    hi.merge(other.state_dict())
+    assert hi.compute() == 11
+    empty = mc.MinMeter()
+    lo.merge(empty.state_dict())                  # a rank that logged nothing does not disturb the result
+    assert lo.compute() == -1
+
+
+def test_exponent_meter_is_exp_of_weighted_mean_and_saturates():
+    m = mc.AveragedExponentMeter()
+    m.log(1.0, 2.0)
+    m.log(2.0, 2.0)
+    assert abs(m.compute() - math.exp(1.5)) < 1e-9
+    big = mc.AveragedExponentMeter()
+    big.log(1e6, 1.0)
+    assert big.compute() == float("inf")
+
+
+def test_stopwatch_and_frequency_meters_measure_milliseconds():
+    sw = mc.StopwatchMeter()
+    sw.end()                                      # an end without a start is ignored
+    assert sw.compute() == 0.0
+    sw.log("start")
+    time.sleep(0.02)
+    sw.log("end")
+    assert 15.0 < sw.compute() < 200.0
+    with pytest.raises(ValueError):
+        sw.log("pause")
+    fq = mc.FrequencyMeter()
+    fq.log()
+    assert fq.compute() == 0.0                    # one occurrence: no interval yet
+    time.sleep(0.01)
+    fq.log()
+    assert 5.0 < fq.compute() < 200.0
+    restored = mc.FrequencyMeter()
+    restored.load_state_dict(fq.state_dict())
+    assert restored._last is None and restored.compute() == fq.compute()
+
+
+def test_gather_meter_collects_and_merges():
+    g = mc.GatherMeter()
+    g.log({"a": 1})
+    g.log([2])
+    other = mc.GatherMeter()
+    other.log("x")
+    g.merge(other.state_dict())
+    assert g.compute() == [{"a": 1}, [2], "x"]
+
+
+def test_logging_outside_a_group_is_dropped_and_lazy_values_run_only_on_log_steps():
+    mc.log_summed("orphan", 1.0)                  # no active group: nothing is created
+    assert mb.get_group("train") is None
+    calls = []
+
+    def lazy():
+        calls.append(1)
+        return 5.0
+
+    for step in range(4):
+        with mb.meters_group("train", log_freq=2) as should_log:
+            assert should_log == (step % 2 == 1)
+            mc.log_averaged("v", lazy)
+        mb.step_meters("train")
+    assert len(calls) == 2                        # evaluated on the two logging steps only
+    assert mb.compute_meters("train")["v"] == 5.0
+
+
+def test_priority_orders_keys_and_reset_keeps_persistent_meters():
+    with mb.meters_group("g", log_freq=1, log_logger_overhead=False):
+        mc.log_summed("zeta", 1.0, priority=0)
+        mc.log_summed("alpha", 1.0, priority=5)
+        mc.log_summed("beta", 1.0, priority=5)
+        mc.log_summed("forever", 2.0, reset=False)
+    assert list(mb.compute_meters("g")) == ["zeta", "alpha", "beta", "forever"]
+    mb.reset_meters("g")
+    assert list(mb.compute_meters("g")) == ["forever"]
+    with mb.meters_group("g"):
+        mc.log_summed("forever", 3.0, reset=False)
+    assert mb.compute_meters("g")["forever"] == 5.0
+
+
+def test_nested_and_sibling_groups_receive_the_same_log_call():
+    with mb.meters_group("outer", log_freq=1):
+        with mb.meters_group("inner", log_freq=1):
+            mc.log_summed("x", 1.0)
+        mc.log_summed("x", 10.0)
+    assert mb.compute_meters("inner")["x"] == 1.0
+    assert mb.compute_meters("outer")["x"] == 11.0
+
+
+def test_group_state_round_trip_restores_iteration_and_values():
+    for _ in range(3):
+        with mb.meters_group("train", log_freq=5):
+            mc.log_summed("tokens", 4.0, reset=False)
+        mb.step_meters("train")
+    sd = mb.state_dict()
+    mb.clear_all()
+    assert mb.compute_meters("train") == {}
+    mb.load_state_dict(sd)
+    g = mb.get_group("train")
+    assert g._iteration == 3 and g.log_freq == 5
+    with mb.meters_group("train") as should_log:
+        assert not should_log                     # iteration 4 of 5
+    mb.step_meters("train")
+    with mb.meters_group("train") as should_log:
+        assert should_log                         # iteration 5 of 5
+
+
+class _TwoRanks:
+    """Collective stand-in whose object all-gather returns this rank's state plus a prepared peer state."""
+
+    world_size = 2
+
+    def __init__(self, peer_states):
+        self.peer = peer_states
+
+    def all_gather_objects(self, obj):
+        return [obj, self.peer]
+
+
+def test_aggregation_merges_every_rank_including_keys_only_a_peer_has():
+    with mb.meters_group("eval", log_freq=1):
+        mc.log_averaged("loss", 2.0, weight=10.0, priority=0)
+        mc.log_summed("tokens", 10.0)
+    peer_loss, peer_tok, peer_only = mc.AverageMeter(), mc.SummedMeter(), mc.MaxMeter()
+    peer_loss.log(4.0, 30.0)
+    peer_tok.log(30.0)
+    peer_only.log(9.0)
+    peer = {"loss": mb.MeterEntry(peer_loss, True, 0).state_dict(), "tokens": mb.MeterEntry(peer_tok, True, 100).state_dict(),
+            "peak": mb.MeterEntry(peer_only, True, 100).state_dict()}
+    assert "ms_spent_logging" in mb.compute_meters("eval")   # the group accounts for its own logging time
+    out = mb.compute_meters("eval", aggregate=True, collective=_TwoRanks(peer))
+    assert abs(out["loss"] - 3.5) < 1e-9 and out["tokens"] == 40.0 and out["peak"] == 9.0
+    assert list(out)[0] == "loss"
+    assert mb.compute_meters("eval")["tokens"] == 10.0       # local values are untouched by aggregation
