@@ -1,0 +1,192 @@
+"""Datasets and transforms not covered by the pipeline tests: synthetic and loop datasets, tokenising, chunking,
+skipping, shuffling, prefetching, composition, and exact state resume of each
+(optimus_dl/modules/data/datasets/*.py, optimus_dl/modules/data/transforms/*.py)."""
+
+import numpy as np
+import pytest
+import torch
+import torchdata.nodes as tn
+
+from optimus_dl_b200.data.datasets import build_dataset
+from optimus_dl_b200.data.transforms import build_transform
+
+
+class _Range(tn.BaseNode):
+    def __init__(self, n, make=lambda i: {"input_ids": [i]}):
+        super().__init__()
+        self.n, self.i, self.make = n, 0, make
+
+    def reset(self, initial_state=None):
+        super().reset(initial_state)
+        self.i = initial_state["i"] if initial_state else 0
+
+    def get_state(self):
+        return {"i": self.i}
+
+    def next(self):
+        if self.i >= self.n:
+            raise StopIteration
+        self.i += 1
+        return self.make(self.i - 1)
+
+
+def _drain(node, limit=10_000):
+    out = []
+    for _ in range(limit):
+        try:
+            out.append(next(node))
+        except StopIteration:
+            break
+    return out
+
+
+def _resume_equals_straight(make_node, consume, total):
+    """Run ``total`` items straight; run ``consume``, snapshot, rebuild, restore, run the rest: same items."""
+    a = make_node()
+    a.reset()
+    straight = [next(a) for _ in range(total)]
+    b = make_node()
+    b.reset()
+    head = [next(b) for _ in range(consume)]
+    state = b.state_dict()
+    c = make_node()
+    c.reset(state)
+    tail = [next(c) for _ in range(total - consume)]
+    return straight, head + tail
+
+
+def _same(a, b):
+    if isinstance(a, dict):
+        return a.keys() == b.keys() and all(_same(a[k], b[k]) for k in a)
+    if isinstance(a, (list, tuple)):
+        return len(a) == len(b) and all(_same(x, y) for x, y in zip(a, b))
+    if isinstance(a, (np.ndarray, torch.Tensor)):
+        return np.array_equal(np.asarray(a), np.asarray(b))
+    return a == b
+
+
+def test_synthetic_tokens_is_deterministic_per_rank_and_resumable():
+    cfg = {"_name": "synthetic_tokens", "vocab_size": 50, "length": 9, "num_documents": 6, "seed": 3}
+    d0 = build_dataset(cfg, rank=0, world_size=2, seed=1)
+    d0.reset()
+    docs = _drain(d0)
+    assert len(docs) == 6 and all(d["input_ids"].shape == (9,) and d["input_ids"].max() < 50 for d in docs)
+    again = build_dataset(cfg, rank=0, world_size=2, seed=1)
+    again.reset()
+    assert _same(docs, _drain(again))
+    other = build_dataset(cfg, rank=1, world_size=2, seed=1)
+    other.reset()
+    assert not _same(docs, _drain(other))               # ranks draw different documents
+    straight, resumed = _resume_equals_straight(lambda: build_dataset(cfg, rank=0, world_size=2, seed=1), 4, 6)
+    assert _same(straight, resumed)
+    lens_cfg = {"_name": "synthetic_tokens", "vocab_size": 50, "mean_length": 40.0, "min_length": 8, "max_length": 64,
+                "num_documents": 200}
+    d = build_dataset(lens_cfg)
+    d.reset()
+    lens = [len(x["input_ids"]) for x in _drain(d)]
+    assert min(lens) >= 8 and max(lens) <= 64 and len(set(lens)) > 10
+
+
+def test_loop_restarts_the_inner_dataset_and_counts_epochs():
+    cfg = {"_name": "loop", "inner": {"_name": "synthetic_tokens", "vocab_size": 9, "length": 3, "num_documents": 4}}
+    d = build_dataset(cfg)
+    d.reset()
+    items = [next(d) for _ in range(10)]
+    assert _same(items[:4], items[4:8]) and _same(items[:2], items[8:10])
+    assert d.get_state()["epoch"] == 2
+    straight, resumed = _resume_equals_straight(lambda: build_dataset(cfg), 6, 11)
+    assert _same(straight, resumed)
+    empty = build_dataset({"_name": "loop", "inner": {"_name": "synthetic_tokens", "num_documents": 0}})
+    empty.reset()
+    with pytest.raises(RuntimeError):
+        next(empty)
+
+
+def test_tokenize_maps_text_and_can_keep_it():
+    texts = ["ab", "", "héllo"]
+    src = lambda: _Range(3, lambda i: {"text": texts[i], "meta": i})  # noqa: E731
+    base = {"_name": "tokenize", "tokenizer_config": {"_name": "char_tokenize"}, "worker_cfg": {"num_workers": 0}}
+    node = build_transform(base).build(src())
+    node.reset()
+    out = _drain(node)
+    assert [list(o["input_ids"]) for o in out][0] == [256, 97, 98, 257]        # BOS, bytes, EOS
+    assert list(out[1]["input_ids"]) == [256, 257]
+    assert len(out[2]["input_ids"]) == 2 + len("héllo".encode())               # UTF-8 bytes, not characters
+    assert all("text" not in o and o["meta"] == i for i, o in enumerate(out))
+    keep = build_transform({**base, "keep_text": True, "output_field": "ids"}).build(src())
+    keep.reset()
+    k = next(keep)
+    assert k["text"] == "ab" and list(k["ids"]) == [256, 97, 98, 257]
+
+
+def test_chunk_tokens_splits_long_documents_with_shift_overlap_budget():
+    docs = [{"input_ids": list(range(10))}, {"input_ids": list(range(100, 103))}]
+    node = build_transform({"_name": "chunk_tokens", "max_seq_len": 4}).build(_Range(2, lambda i: docs[i]))
+    node.reset()
+    chunks = [list(c["input_ids"]) for c in _drain(node)]
+    assert chunks == [[0, 1, 2, 3, 4], [5, 6, 7, 8, 9], [100, 101, 102]]        # max_seq_len + 1 tokens for the shift
+    node = build_transform({"_name": "chunk_tokens", "max_seq_len": 4, "add_one_for_shift": False, "max_chunks": 2}).build(
+        _Range(2, lambda i: docs[i]))
+    node.reset()
+    chunks = [list(c["input_ids"]) for c in _drain(node)]
+    assert chunks == [[0, 1, 2, 3], [4, 5, 6, 7], [100, 101, 102]]              # at most two chunks per document
+    make = lambda: build_transform({"_name": "chunk_tokens", "max_seq_len": 3}).build(  # noqa: E731
+        _Range(5, lambda i: {"input_ids": list(range(10 * i, 10 * i + 9))}))
+    straight, resumed = _resume_equals_straight(make, 4, 11)                    # snapshot in the middle of a document
+    assert _same(straight, resumed)
+
+
+def test_skip_transforms_partition_the_stream():
+    keep0 = build_transform({"_name": "skip_interleaved", "keep_every": 3, "offset": 0}).build(_Range(10))
+    keep1 = build_transform({"_name": "skip_interleaved", "keep_every": 3, "offset": 1}).build(_Range(10))
+    keep0.reset(), keep1.reset()
+    assert [x["input_ids"][0] for x in _drain(keep0)] == [0, 3, 6, 9]
+    assert [x["input_ids"][0] for x in _drain(keep1)] == [1, 4, 7]
+    a = build_transform({"_name": "skip_random", "keep_probability": 0.3, "seed": 5}).build(_Range(200))
+    b = build_transform({"_name": "skip_random", "keep_probability": 0.3, "seed": 5, "invert": True}).build(_Range(200))
+    a.reset(), b.reset()
+    ka, kb = [x["input_ids"][0] for x in _drain(a)], [x["input_ids"][0] for x in _drain(b)]
+    assert sorted(ka + kb) == list(range(200)) and not set(ka) & set(kb)        # a train / held-out split
+    assert 30 < len(ka) < 90
+    make = lambda: build_transform({"_name": "skip_random", "keep_probability": 0.5, "seed": 1}).build(_Range(100))  # noqa: E731
+    straight, resumed = _resume_equals_straight(make, 7, 30)
+    assert _same(straight, resumed)
+
+
+def test_shuffle_is_a_seeded_permutation_within_the_buffer_and_resumes_exactly():
+    make = lambda seed=0: build_transform({"_name": "shuffle", "buffer_size": 8}, seed=seed).build(_Range(40))  # noqa: E731
+    n = make()
+    n.reset()
+    out = [x["input_ids"][0] for x in _drain(n)]
+    assert sorted(out) == list(range(40)) and out != list(range(40))
+    assert all(abs(v - i) < 40 for i, v in enumerate(out)) and max(out[:8]) < 16   # early items come from the first buffers
+    n2 = make()
+    n2.reset()
+    assert [x["input_ids"][0] for x in _drain(n2)] == out                          # same seed, same order
+    straight, resumed = _resume_equals_straight(make, 13, 40)
+    assert _same(straight, resumed)
+
+
+def test_prefetch_and_composition_preserve_order_and_state():
+    cfg = {"_name": "compose", "transforms": [
+        {"_name": "chunk_tokens", "max_seq_len": 2, "add_one_for_shift": False},
+        {"_name": "skip_interleaved", "keep_every": 2, "offset": 1},
+        {"_name": "prefetch", "prefetch_factor": 2},
+    ]}
+    src = lambda: _Range(6, lambda i: {"input_ids": [10 * i, 10 * i + 1, 10 * i + 2, 10 * i + 3]})  # noqa: E731
+    node = build_transform(cfg).build(src())
+    node.reset()
+    got = [list(x["input_ids"]) for x in _drain(node)]
+    assert got == [[10 * i + 2, 10 * i + 3] for i in range(6)]                   # second chunk of every document
+    straight, resumed = _resume_equals_straight(lambda: build_transform(cfg).build(src()), 2, 6)
+    assert _same(straight, resumed)
+    assert build_transform({"_name": "compose", "transforms": []}).build(src()) is not None
+
+
+def test_to_device_converts_arrays_and_leaves_scalars():
+    item = {"input_ids": np.arange(6).reshape(2, 3), "seq_lens": [3, 2], "max_seqlen": 3, "name": "x"}
+    node = build_transform({"_name": "to_device"}, device=torch.device("cpu")).build(_Range(1, lambda i: item))
+    node.reset()
+    out = next(node)
+    assert isinstance(out["input_ids"], torch.Tensor) and out["input_ids"].dtype == torch.int64
+    assert out["max_seqlen"] == 3 and out["name"] == "x"
