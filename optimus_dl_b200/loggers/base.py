@@ -7,9 +7,14 @@ from typing import Any
 
 
 class RunStatus(str, enum.Enum):
-    FINISHED = "FINISHED"
-    FAILED = "FAILED"
-    INTERRUPTED = "INTERRUPTED"
+    """How a run ended (names and values of optimus_dl/modules/loggers/base.py:18-23; ``FINISHED`` / ``FAILED``
+    are aliases of ``SUCCESS`` / ``FAILURE``)."""
+
+    SUCCESS = "success"
+    FAILURE = "failure"
+    INTERRUPTED = "interrupted"
+    FINISHED = "success"
+    FAILED = "failure"
 
 
 class BaseMetricsLogger:

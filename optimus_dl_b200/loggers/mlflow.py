@@ -113,7 +113,7 @@ class MlflowLogger(BaseMetricsLogger):
             self._mlflow.log_metrics(flat, step=step)
 
     def finished(self, status: RunStatus = RunStatus.FINISHED) -> None:
-        self._status = {"FINISHED": "FINISHED", "FAILED": "FAILED", "INTERRUPTED": "KILLED"}[str(getattr(status, "value", status))]
+        self._status = {"success": "FINISHED", "failure": "FAILED", "interrupted": "KILLED"}[str(getattr(status, "value", status))]
 
     def close(self) -> None:
         if self._active:
