@@ -1,0 +1,175 @@
+"""Checkpoint manager: path resolution, save cadence, on-disk layout, latest links, load strategies and
+model-only loading (optimus_dl/modules/checkpoint/checkpoint_manager.py:106-814, load_strategy.py:15-85)."""
+
+import os
+
+import pytest
+import torch
+
+from optimus_dl_b200.checkpoint.checkpoint_manager import CheckpointManager
+from optimus_dl_b200.checkpoint.load_strategy import LoadStrategy
+from optimus_dl_b200.lr_scheduler import build_lr_scheduler
+from optimus_dl_b200.metrics import base as mb
+from optimus_dl_b200.metrics import common as mc
+from optimus_dl_b200.models import build_model
+
+MODEL = dict(_name="llama2", n_layer=1, n_head=2, n_kv_head=1, n_embd=32, vocab_size=61, sequence_length=16, multiple_of=8)
+
+
+class _Loader:
+    def __init__(self, pos=0):
+        self.pos = pos
+
+    def state_dict(self):
+        return {"pos": self.pos}
+
+    def load_state_dict(self, s):
+        self.pos = s["pos"]
+
+
+def _setup(seed=0, lr=0.1):
+    torch.manual_seed(seed)
+    model = build_model(MODEL)
+    opt = torch.optim.AdamW(model.parameters(), lr=lr)
+    sched = build_lr_scheduler({"_name": "wsd", "warmup_steps": 2}, optimizer=opt, iterations=20)
+    return model, opt, sched
+
+
+def _train(model, opt, sched, steps):
+    for _ in range(steps):
+        loss = model(torch.randint(0, 61, (2, 8)))["logits"].float().logsumexp(-1).mean()
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        sched.step()
+
+
+def _save(mgr, it, model, opt, sched, **kw):
+    mgr.save_checkpoint(iteration=it, model=model, optimizer=opt, lr_scheduler=sched, full_config={"model": MODEL}, **kw)
+
+
+def test_layout_links_and_path_resolution(tmp_path):
+    out = tmp_path / "run"
+    mgr = CheckpointManager(output_path=str(out))
+    assert not mgr.is_restart() and mgr.get_checkpoint(str(out)) is None
+    model, opt, sched = _setup()
+    _train(model, opt, sched, 2)
+    _save(mgr, 5, model, opt, sched, data_loaders={"train": _Loader(7)})
+    names = set(os.listdir(out))
+    assert {"checkpoint_000000005", "metadata_000000005.pt", "per_rank_metadata_0_000000005.pt", "checkpoint_latest",
+            "metadata_latest.pt", "per_rank_metadata_0_latest.pt"} <= names
+    assert not [n for n in names if n.endswith(".tmp")]
+    assert os.path.islink(out / "metadata_latest.pt") and os.readlink(out / "metadata_latest.pt") == "metadata_000000005.pt"
+    assert os.path.exists(out / "checkpoint_000000005" / ".metadata")
+    assert mgr.is_restart()
+    meta = torch.load(out / "metadata_000000005.pt", weights_only=False)
+    assert meta["iteration"] == 5 and meta["world_size"] == 1 and meta["config"]["model"]["n_embd"] == 32
+    assert meta["lr_scheduler"]["step_count"] == 2
+    # every accepted spelling of "this checkpoint" resolves to the same pair
+    want = (str(out / "metadata_000000005.pt"), str(out / "checkpoint_000000005"))
+    assert tuple(mgr.get_checkpoint(out / "checkpoint_000000005")) == want
+    assert tuple(mgr.get_checkpoint(out / "metadata_000000005.pt")) == want
+    latest = mgr.get_checkpoint(out)
+    assert latest.metadata.endswith("metadata_latest.pt") and latest.checkpoint.endswith("checkpoint_latest")
+    assert tuple(mgr.get_checkpoint(out / "metadata_latest.pt")) == (latest.metadata, latest.checkpoint)
+    assert mgr.get_checkpoint(tmp_path / "missing") is None
+    with pytest.raises(FileNotFoundError):
+        mgr.load_checkpoint(str(tmp_path / "missing"))
+
+
+def test_save_cadence_persistent_versus_rolling(tmp_path):
+    out = tmp_path / "run"
+    mgr = CheckpointManager(output_path=str(out))
+    model, opt, sched = _setup()
+    saved = [it for it in range(1, 13) if mgr.save_checkpoint_if_needed(
+        it, save_freq=6, last_save_freq=4, model=model, optimizer=opt, lr_scheduler=sched, full_config={})]
+    assert saved == [4, 6, 8, 12]
+    names = set(os.listdir(out))
+    assert {"checkpoint_000000006", "checkpoint_000000012"} <= names
+    assert "checkpoint_000000004" not in names and "checkpoint_000000008" not in names     # rolling saves reuse "latest"
+    assert torch.load(out / "metadata_latest.pt", weights_only=False)["iteration"] == 12
+    assert not mgr.save_checkpoint_if_needed(13, save_freq=6, last_save_freq=4)
+    assert mgr.save_checkpoint_if_needed(13, save_freq=6, last_save_freq=4, force_save=True, model=model, optimizer=opt,
+                                         lr_scheduler=sched, full_config={})
+    assert "checkpoint_000000013" in os.listdir(out)
+
+
+def test_full_round_trip_restores_model_optimizer_schedule_loaders_and_meters(tmp_path):
+    mgr = CheckpointManager(output_path=str(tmp_path))
+    model, opt, sched = _setup()
+    _train(model, opt, sched, 3)
+    with mb.meters_group("train", log_freq=10):
+        mc.log_summed("total_tokens", 123.0, reset=False)
+    _save(mgr, 3, model, opt, sched, data_loaders={"train": _Loader(11)})
+    want = {k: v.clone() for k, v in model.state_dict().items()}
+    mb.clear_all()
+    m2, o2, s2 = _setup(seed=1, lr=0.5)
+    loader = _Loader()
+    start, meta = mgr.load_checkpoint_if_exists(model=m2, optimizer=o2, lr_scheduler=s2, data_loaders={"train": loader})
+    assert start == 4 and meta["iteration"] == 3
+    assert all(torch.equal(want[k], v) for k, v in m2.state_dict().items())
+    assert s2.last_epoch == 3 and o2.param_groups[0]["lr"] == opt.param_groups[0]["lr"]
+    assert loader.pos == 11 and mb.compute_meters("train")["total_tokens"] == 123.0
+    st1, st2 = opt.state_dict()["state"], o2.state_dict()["state"]
+    assert st1.keys() == st2.keys() and all(torch.equal(st1[k]["exp_avg"], st2[k]["exp_avg"]) for k in st1)
+    # both copies now take the same next step
+    torch.manual_seed(5)
+    _train(model, opt, sched, 1)
+    torch.manual_seed(5)
+    _train(m2, o2, s2, 1)
+    assert all(torch.equal(a, b) for a, b in zip(model.state_dict().values(), m2.state_dict().values()))
+
+
+def test_load_strategy_switches_each_part_off(tmp_path):
+    mgr = CheckpointManager(output_path=str(tmp_path))
+    model, opt, sched = _setup()
+    _train(model, opt, sched, 3)
+    with mb.meters_group("train"):
+        mc.log_summed("total_tokens", 9.0, reset=False)
+    _save(mgr, 3, model, opt, sched, data_loaders={"train": _Loader(4)})
+    mb.clear_all()
+    m2, o2, s2 = _setup(seed=1)
+    before = {k: v.clone() for k, v in m2.state_dict().items()}
+    loader = _Loader()
+    strat = LoadStrategy(load_model=True, load_optimizer=False, load_scheduler=False, load_dataloaders=False,
+                         load_metrics=False, load_iteration=False)
+    meta = mgr.load_checkpoint(str(tmp_path), model=m2, optimizer=o2, lr_scheduler=s2, data_loaders={"train": loader},
+                               strategy=strat)
+    assert meta["iteration"] == 0                          # a fine-tune starts counting from zero
+    assert any(not torch.equal(before[k], v) for k, v in m2.state_dict().items())          # weights did load
+    assert s2.last_epoch == 0 and loader.pos == 0 and not o2.state_dict()["state"] and mb.compute_meters("train") == {}
+    m3, o3, s3 = _setup(seed=2)
+    keep = m3.transformer.ln_f.weight.detach().clone()
+    assert not torch.equal(model.transformer.ln_f.weight, keep)
+    mgr.load_checkpoint(str(tmp_path), model=m3, strategy={"load_optimizer": False, "extra_ignore_keys": ["ln_f"]})
+    assert torch.equal(m3.transformer.ln_f.weight, keep)   # ignored keys keep their fresh initialisation
+    assert torch.equal(m3.transformer.h[0].attn.wq.weight, model.transformer.h[0].attn.wq.weight)
+
+
+def test_metadata_only_save_keeps_the_weights_of_the_full_save(tmp_path):
+    mgr = CheckpointManager(output_path=str(tmp_path))
+    model, opt, sched = _setup()
+    _save(mgr, 2, model, opt, sched)
+    stamp = os.path.getmtime(tmp_path / "checkpoint_000000002" / ".metadata")
+    mgr.save_checkpoint(iteration=2, lr_scheduler=sched, full_config={"model": MODEL}, metadata_only=True,
+                        extra_metadata={"eval_finished": True})
+    meta = torch.load(tmp_path / "metadata_000000002.pt", weights_only=False)
+    assert meta["eval_finished"] is True
+    assert os.path.getmtime(tmp_path / "checkpoint_000000002" / ".metadata") == stamp
+    assert os.path.exists(tmp_path / "per_rank_metadata_0_000000002.pt")
+
+
+def test_model_can_be_rebuilt_from_the_checkpoint_alone(tmp_path):
+    mgr = CheckpointManager(output_path=str(tmp_path))
+    model, opt, sched = _setup()
+    _train(model, opt, sched, 1)
+    _save(mgr, 1, model, opt, sched)
+    rebuilt, meta = CheckpointManager().build_model_from_checkpoint(str(tmp_path))
+    assert meta["iteration"] == 1 and type(rebuilt) is type(model)
+    x = torch.randint(0, 61, (1, 8))
+    assert torch.equal(rebuilt.eval()(x)["logits"], model.eval()(x)["logits"])
+    plain = tmp_path / "weights.pt"
+    torch.save(model.state_dict(), plain)
+    other = build_model(MODEL)
+    CheckpointManager().load_model_state_dict(other, str(plain))
+    assert torch.equal(other.lm_head.weight, model.lm_head.weight)
