@@ -8,3 +8,135 @@ def test_nvtx_range_is_a_noop_without_cuda(monkeypatch):
     with profile.nvtx_range("phase") as r:       # no CUDA device here: enabled flag resolves to False
         assert r.on == profile.nvtx_enabled()
     monkeypatch.setattr(profile, "_NVTX", None)
+
+
+# ---------------------------------------------------------------------- small core utilities
+def test_instantiate_helpers():
+    from optimus_dl_b200.core import instantiate as I
+
+    assert I.merge_dicts({"a": 1, "b": 2}, None, {"b": 3}, c=4) == {"a": 1, "b": 3, "c": 4}
+    assert I.cond(True, "x", "y") == "x" and I.cond(0, "x", "y") == "y" and I.cond(False, "x") is None
+    rep = I.repeat({"k": [1]}, 3)
+    rep[0]["k"].append(2)
+    assert rep[1] == {"k": [1]} and len(rep) == 3            # deep copies, not aliases
+    assert I.concat_lists([1], None, (2, 3), []) == [1, 2, 3]
+    assert I.get_item({"a": 5}, "a") == 5 and I.get_item([7, 8], 1) == 8
+    assert I.get_item({"a": 5}, "b", "dflt") == "dflt" and I.get_item([1], 4) is None
+    assert I.get_item(complex(1, 2), "imag") == 2.0          # attribute access as a fallback
+    assert I.compose(lambda x: x + 1, lambda x: x * 10)(2) == 30 and I.compose()(9) == 9
+
+
+def test_dtype_names_and_fp8_helpers():
+    import torch
+
+    from optimus_dl_b200.core import dtype as D
+
+    for name, want in (("bfloat16", torch.bfloat16), ("torch.float16", torch.float16), (" FP64 ", torch.float64),
+                       ("long", torch.int64), ("e4m3", torch.float8_e4m3fn), ("torch.float8_e5m2", torch.float8_e5m2),
+                       (torch.int8, torch.int8)):
+        assert D.str_to_dtype(name) is want
+    import pytest
+
+    with pytest.raises(ValueError):
+        D.str_to_dtype("float7")
+    assert D.is_fp8_dtype("fp8") and D.is_fp8_dtype(torch.float8_e5m2) and not D.is_fp8_dtype("bfloat16")
+    assert not D.is_fp8_dtype("nonsense")
+    assert D.get_fp8_format_from_dtype("float8_e4m3fn") == "e4m3" and D.get_fp8_format_from_dtype("e5m2") == "e5m2"
+    with pytest.raises(ValueError):
+        D.get_fp8_format_from_dtype("float32")
+
+
+def test_env_readers_fall_through_launchers_and_reject_garbage(monkeypatch):
+    import pytest
+
+    from optimus_dl_b200.core import env as E
+    from optimus_dl_b200.core.environment import EnvironmentVariable
+
+    for k in ("WORLD_SIZE", "OMPI_COMM_WORLD_SIZE", "SLURM_NTASKS", "RANK", "OMPI_COMM_WORLD_RANK", "SLURM_PROCID",
+              "LOCAL_RANK", "OMPI_COMM_WORLD_LOCAL_RANK", "SLURM_LOCALID", "LOCAL_WORLD_SIZE", "OMPI_COMM_WORLD_LOCAL_SIZE"):
+        monkeypatch.delenv(k, raising=False)
+    assert (E.get_world_size(), E.get_rank(), E.get_local_rank(), E.get_local_world_size()) == (1, 0, 0, 1)
+    monkeypatch.setenv("SLURM_NTASKS", "16")
+    monkeypatch.setenv("OMPI_COMM_WORLD_RANK", "5")
+    assert E.get_world_size() == 16 and E.get_rank() == 5 and E.get_local_world_size() == 16
+    monkeypatch.setenv("WORLD_SIZE", "8")                     # torchrun's variables win
+    monkeypatch.setenv("LOCAL_WORLD_SIZE", "4")
+    assert E.get_world_size() == 8 and E.get_local_world_size() == 4
+    monkeypatch.setenv("RANK", "three")
+    with pytest.raises(E.InvalidEnvironmentVariableError):
+        E.get_rank()
+    assert E.get_int_from_env("NOPE_NOT_SET", 42) == 42
+    flag = EnvironmentVariable("T_FLAG", False, bool)
+    assert not flag and not flag.is_set()
+    monkeypatch.setenv("T_FLAG", "Yes")
+    assert flag and flag.is_set() and flag.get() is True
+    num = EnvironmentVariable("T_NUM", 30.0, float)
+    assert num.get() == 30.0
+    monkeypatch.setenv("T_NUM", "2.5")
+    assert num.get() == 2.5
+
+
+def test_numerical_and_parameter_counting():
+    import numpy as np
+    import torch
+
+    from optimus_dl_b200.core.model_utils import get_num_parameters
+    from optimus_dl_b200.core.numerical import get_item, safe_round
+
+    assert get_item(torch.tensor(3.5)) == 3.5 and get_item(np.float32(2.0)) == 2.0 and get_item("s") == "s"
+    assert safe_round(torch.tensor(1.23456), 2) == 1.23 and safe_round(1.23456) == 1.23456
+    assert safe_round("text", 2) == "text" and safe_round(float("inf"), 2) == float("inf")
+    lin = torch.nn.Linear(4, 3)
+    tied = torch.nn.ModuleList([lin, lin, torch.nn.Linear(3, 2, bias=False)])
+    assert get_num_parameters(tied) == 4 * 3 + 3 + 3 * 2      # a shared module is counted once
+    lin.bias.requires_grad_(False)
+    assert get_num_parameters(tied, only_trainable=True) == 4 * 3 + 3 * 2
+
+
+def test_seed_makes_every_generator_reproducible():
+    import random
+
+    import numpy as np
+    import torch
+
+    from optimus_dl_b200.core.seed import set_seed
+
+    def draw():
+        return random.random(), float(np.random.rand()), torch.rand(3).tolist()
+
+    set_seed(11)
+    a = draw()
+    set_seed(11)
+    b = draw()
+    set_seed(12)
+    c = draw()
+    assert a == b and a != c
+    set_seed(11, deterministic=True)
+    assert torch.are_deterministic_algorithms_enabled()
+    torch.use_deterministic_algorithms(False)
+
+
+def test_log_once_and_bootstrap(caplog, tmp_path, monkeypatch):
+    import logging
+    import sys
+
+    from optimus_dl_b200.core.bootstrap import bootstrap_module
+    from optimus_dl_b200.core.log import info_once, warn_once
+
+    lg = logging.getLogger("t_once")
+    with caplog.at_level(logging.INFO, logger="t_once"):
+        for _ in range(3):
+            warn_once(lg, "only once please")
+            info_once(lg, "another line")
+    assert caplog.text.count("only once please") == 1 and caplog.text.count("another line") == 1
+    pkg = tmp_path / "bootpkg"
+    (pkg / "sub").mkdir(parents=True)
+    (pkg / "notapkg").mkdir()
+    for rel, body in (("__init__.py", ""), ("alpha.py", "X = 1\n"), ("_private.py", "raise RuntimeError('private')\n"),
+                      ("test_alpha.py", "raise RuntimeError('test file')\n"), ("sub/__init__.py", ""),
+                      ("sub/beta.py", "Y = 2\n"), ("notapkg/gamma.py", "raise RuntimeError('no __init__')\n")):
+        (pkg / rel).write_text(body)
+    monkeypatch.syspath_prepend(str(tmp_path))
+    names = bootstrap_module("bootpkg")
+    assert names == ["bootpkg.alpha", "bootpkg.sub", "bootpkg.sub.beta"]
+    assert sys.modules["bootpkg.sub.beta"].Y == 2
