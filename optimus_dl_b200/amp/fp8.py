@@ -14,6 +14,7 @@ backward pass). Enum names and string parsers follow the reference.
 from __future__ import annotations
 
 import contextlib
+import dataclasses
 import enum
 import logging
 from typing import Any
@@ -60,6 +61,49 @@ def parse_fp8_recipe(s: Any) -> Fp8RecipeType:
     raise ValueError(f"unknown fp8 recipe {s!r}; expected one of {[r.value for r in Fp8RecipeType]}")
 
 
+def get_fp8_format_from_string(format_str: str) -> Fp8Format:
+    """Reference name of :func:`parse_fp8_format` (optimus_dl/modules/amp/fp8.py:96-119)."""
+    return parse_fp8_format(format_str)
+
+
+def get_fp8_recipe_type_from_string(recipe_str: str) -> Fp8RecipeType:
+    """Reference name of :func:`parse_fp8_recipe` (optimus_dl/modules/amp/fp8.py:122-147)."""
+    return parse_fp8_recipe(recipe_str)
+
+
+def is_transformer_engine_available() -> bool:
+    """Whether NVIDIA Transformer Engine can be imported. Nothing here depends on it: the FP8 path is this
+    package's own kernels and works either way."""
+    import importlib.util
+
+    return importlib.util.find_spec("transformer_engine") is not None
+
+
+def get_transformer_engine_version() -> str | None:
+    if not is_transformer_engine_available():
+        return None
+    try:
+        import transformer_engine
+
+        return getattr(transformer_engine, "__version__", None)
+    except Exception:
+        return None
+
+
+@dataclasses.dataclass
+class Fp8RecipeConfig:
+    """Arguments of :func:`create_fp8_recipe` as a dataclass (optimus_dl/modules/amp/fp8.py:150-178)."""
+
+    recipe_type: str = "delayed"
+    format: str = "hybrid"
+    margin: int = 0
+    amax_history_len: int = 1024
+    amax_compute_algo: str = "max"
+    reduce_amax: bool = True
+    fp8_dpa: bool = False
+    fp8_mha: bool = False
+
+
 _state = {"enabled": False, "recipe": None}
 
 
@@ -99,8 +143,17 @@ class FP8Recipe:
         return f"FP8Recipe(format={self.format.value}, recipe={self.recipe.value})"
 
 
-def create_fp8_recipe(cfg: Any) -> FP8Recipe | None:
-    """Recipe from an ``Fp8Config``-like mapping; ``None`` when FP8 is off or no CUDA device exists."""
+def create_fp8_recipe(cfg: Any = None, format: Any = None, **kwargs: Any) -> FP8Recipe | None:
+    """Recipe from an ``Fp8Config``-like mapping, or -- the reference's call form -- from
+    ``(recipe_type, format, margin=..., amax_history_len=..., ...)`` / an :class:`Fp8RecipeConfig`.
+    ``None`` when FP8 is off or no CUDA device exists."""
+    if isinstance(cfg, Fp8RecipeConfig):
+        cfg = dict(dataclasses.asdict(cfg), enabled=True)
+        cfg["recipe"] = cfg.pop("recipe_type")
+    elif isinstance(cfg, (str, Fp8RecipeType)) or (cfg is None and (format is not None or kwargs)):
+        cfg = dict(kwargs, enabled=True, recipe=cfg if cfg is not None else kwargs.pop("recipe_type", "delayed"),
+                   format=format if format is not None else "hybrid")
+        cfg.pop("recipe_type", None)
     if cfg is None or not cfg.get("enabled", False):
         return None
     if not torch.cuda.is_available():

@@ -140,3 +140,27 @@ def test_log_once_and_bootstrap(caplog, tmp_path, monkeypatch):
     names = bootstrap_module("bootpkg")
     assert names == ["bootpkg.alpha", "bootpkg.sub", "bootpkg.sub.beta"]
     assert sys.modules["bootpkg.sub.beta"].Y == 2
+
+
+def test_env_readers_accept_an_explicit_mapping_like_the_reference():
+    import pytest
+    import torch
+
+    from optimus_dl_b200.core import env as E
+
+    env = {"WORLD_SIZE": "4", "RANK": "0", "LOCAL_RANK": "3", "OUT": "/tmp/x", "DEV": "cuda:1", "BAD": "x1", "ZERO": "0",
+           "NEG": "-2", "BADDEV": "gpu??"}
+    assert (E.get_world_size(env), E.get_rank(env), E.get_local_rank(env), E.get_local_world_size(env)) == (4, 0, 3, 1)
+    assert E.get_world_size({}) == 1 and E.get_rank({}) == 0
+    assert E.get_int_from_env(env, "WORLD_SIZE") == 4 and E.get_int_from_env(env, "MISSING") is None
+    assert E.get_int_from_env(env, "ZERO", allow_zero=True) == 0 and E.get_int_from_env(env, "ZERO", True) == 0
+    for name, kw in (("ZERO", {}), ("NEG", {"allow_zero": True}), ("BAD", {})):
+        with pytest.raises(E.InvalidEnvironmentVariableError) as err:
+            E.get_int_from_env(env, name, **kw)
+        assert err.value.name == name
+    with pytest.raises(E.InvalidEnvironmentVariableError):
+        E.get_world_size({"WORLD_SIZE": "0"})
+    assert str(E.get_path_from_env(env, "OUT")) == "/tmp/x" and E.get_path_from_env(env, "MISSING") is None
+    assert E.get_device_from_env(env, "DEV") == torch.device("cuda", 1) and E.get_device_from_env(env, "MISSING") is None
+    with pytest.raises(E.InvalidEnvironmentVariableError):
+        E.get_device_from_env(env, "BADDEV")

@@ -36,3 +36,21 @@ def test_recipe_selects_scaling_mode():
     with d.backward(True):        # no state yet: the update on exit is a no-op
         pass
     assert d.delayed_state.pos == 0
+
+
+def test_reference_call_forms_of_the_fp8_helpers(monkeypatch):
+    from optimus_dl_b200.amp import fp8 as A
+
+    assert A.get_fp8_format_from_string("Hybrid") is A.Fp8Format.HYBRID
+    assert A.get_fp8_recipe_type_from_string("MXFP8") is A.Fp8RecipeType.MXFP8
+    assert A.get_transformer_engine_version() is None or isinstance(A.get_transformer_engine_version(), str)
+    assert A.create_fp8_recipe("delayed", "hybrid") is None            # no CUDA device here
+    monkeypatch.setattr(A.torch.cuda, "is_available", lambda: True)
+    r = A.create_fp8_recipe("delayed", "e4m3", margin=2, amax_history_len=8, amax_compute_algo="most_recent")
+    assert r.recipe is A.Fp8RecipeType.DELAYED and r.format is A.Fp8Format.E4M3 and r.options["margin"] == 2
+    assert r.delayed_state.H == 8 and not r.delayed_state.use_max
+    r = A.create_fp8_recipe(A.Fp8RecipeConfig(recipe_type="tensorwise"))
+    assert r.recipe is A.Fp8RecipeType.TENSORWISE and r.delayed_state is None
+    r = A.create_fp8_recipe({"enabled": True, "recipe": "blockwise", "wgrad": False})
+    assert r.recipe is A.Fp8RecipeType.BLOCKWISE and r.options["wgrad"] is False
+    assert A.create_fp8_recipe({"enabled": False, "recipe": "blockwise"}) is None
