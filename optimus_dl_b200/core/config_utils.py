@@ -112,3 +112,8 @@ def non_resolving_instantiate(config: Any, lazy: bool = True) -> Any:
     if not lazy:
         _force(cfg)
     return cfg
+
+
+# public names of the resolvers, as the reference exports them (optimus_dl/core/omegaconf_utils.py:95-118)
+hash_resolver = _hash_resolver
+conf_hash_resolver = _config_hash_resolver

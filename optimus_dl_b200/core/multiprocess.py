@@ -80,3 +80,9 @@ def finalize_process(exit_timeout: float | None = None) -> None:
     t = OPTIMUS_EXIT_TIMEOUT.get() if exit_timeout is None else exit_timeout
     if t and t > 0:
         _watchdog(float(t))
+
+
+# names the reference exports for the individual teardown steps (optimus_dl/core/multiprocess.py:101-151)
+force_terminate_joblib = _kill_loky_workers
+finish_wandb = _finish_wandb
+finish_mlflow = _finish_mlflow

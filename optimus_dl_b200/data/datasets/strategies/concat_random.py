@@ -59,3 +59,8 @@ class ConcatRandomStrategy(BaseStrategy):
             start = take
             d += 1
         return segs
+
+
+# the reference's class names for this strategy
+ConcatAndChunkFullRandom = ConcatRandomStrategy
+ConcatAndChunkFullRandomConfig = ConcatRandomStrategyConfig

@@ -49,3 +49,6 @@ class MapperConfig:
 @dataclass
 class ProcessMapperConfig(MapperConfig):
     method: str = "process"
+
+
+ThreadedMapperConfig = MapperConfig   # the reference's name for the thread-pool mapper settings

@@ -57,3 +57,6 @@ class ChunkTokensNode(BaseNode):
 class ChunkTransform(BaseTransform):
     def build(self, source: BaseNode) -> BaseNode:
         return ChunkTokensNode(source, self.cfg)
+
+
+ChunkTransformNode = ChunkTokensNode   # the reference's name

@@ -66,3 +66,6 @@ class ShuffleTransform(BaseTransform):
 
     def build(self, source: BaseNode) -> BaseNode:
         return ShuffleNode(source, self.cfg.buffer_size, self.seed)
+
+
+ShuffleTransformNode = ShuffleNode   # the reference's name

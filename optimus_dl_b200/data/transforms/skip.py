@@ -93,3 +93,9 @@ class SkipRandom(BaseTransform):
 
     def build(self, source: BaseNode) -> BaseNode:
         return SkipRandomNode(source, self.cfg.keep_probability, self.cfg.seed, self.cfg.invert)
+
+
+# the reference's class names
+SkipInterleavedTransform, SkipInterleavedTransformConfig, SkipInterleavedTransformNode = (
+    SkipInterleaved, SkipInterleavedConfig, SkipInterleavedNode)
+SkipRandomTransform, SkipRandomTransformConfig, SkipRandomTransformNode = SkipRandom, SkipRandomConfig, SkipRandomNode

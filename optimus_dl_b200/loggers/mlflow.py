@@ -47,6 +47,15 @@ def flatten_params(cfg: Any, prefix: str = "") -> dict[str, str]:
     return out
 
 
+def get_git_remote() -> str | None:
+    """URL of ``origin`` of the working directory's repository, if any."""
+    try:
+        return subprocess.check_output(["git", "config", "--get", "remote.origin.url"], stderr=subprocess.DEVNULL,
+                                       text=True).strip() or None
+    except Exception:
+        return None
+
+
 def _git_commit() -> str | None:
     try:
         return subprocess.check_output(["git", "rev-parse", "HEAD"], stderr=subprocess.DEVNULL, text=True).strip()
@@ -125,3 +134,6 @@ class MlflowLogger(BaseMetricsLogger):
 
     def load_state_dict(self, state: dict[str, Any]) -> None:
         self.run_id = state.get("run_id", self.run_id)
+
+
+get_git_commit_hash = _git_commit   # the reference's name

@@ -80,3 +80,7 @@ class LossMetric(Metric):
     def __call__(self, sources_data):
         loss = sources_data[P.LOSS]
         return {"loss": {"value": loss.item() if isinstance(loss, torch.Tensor) else float(loss), "weight": 1.0}}
+
+
+# per-metric config names of the reference (all carry the same fields here)
+AccuracyMetricConfig = PerplexityMetricConfig = LossMetricConfig = MetricConfig

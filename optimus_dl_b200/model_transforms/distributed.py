@@ -79,10 +79,27 @@ class MixedPrecisionConfig:
 
 
 @dataclass
+class OffloadConfig:
+    """CPU offload policy of the reference's config tree (optimus_dl/modules/model_transforms/distributed.py:172-182).
+    ``cpu_offload: true`` is refused: parameters and optimizer state live sharded in HBM here."""
+
+    cpu_offload: bool = False
+    pin_memory: bool = True
+
+
+def _wants_cpu_offload(value: Any) -> bool:
+    """``offload`` may be a bool (this package's short form) or the reference's nested ``{cpu_offload, pin_memory}``."""
+    if value is None or isinstance(value, bool):
+        return bool(value)
+    getter = value.get if hasattr(value, "get") else (lambda k, d=None: getattr(value, k, d))
+    return bool(getter("cpu_offload", False))
+
+
+@dataclass
 class FullyShardTransformConfig(RegistryConfig):
     reshard_after_forward: Any = False
     mixed_precision: MixedPrecisionConfig | None = None
-    offload: bool = False
+    offload: Any = None
     pin_memory: bool = True
     sync_grad_accum: bool = False
     use_hybrid_sharding: bool = True
@@ -96,7 +113,7 @@ class FullyShardTransform(BaseModelTransform):
     def apply(self, model: nn.Module, collective: Any = None, device: Any = None, **kwargs: Any) -> nn.Module:
         from ..parallel.fsdp import FSDPConfig, fully_shard_model
 
-        if bool(self.cfg.offload):
+        if _wants_cpu_offload(self.cfg.offload):
             raise ValueError("fully_shard: CPU offload is not supported; optimizer state is sharded in HBM")
         mp = self.cfg.get("mixed_precision")
         if mp is not None and mp.get("param_dtype") not in (None, "bfloat16", "bf16", "torch.bfloat16"):
@@ -124,6 +141,9 @@ class FullyShardTransform(BaseModelTransform):
         engine = fully_shard_model(model, group, device, cfg)
         engine.replicate_group, engine.replicate_world = rep_group, rep_world
         return model
+
+
+BaseDistributedTransform = BaseModelTransform   # the reference's name for the common base of ddp / fully_shard
 
 
 def accumulation_context(model: nn.Module, is_last_microbatch: bool):

@@ -38,3 +38,6 @@ class LoadWeightsTransform(BaseModelTransform):
         mgr.load_model_state_dict(model, cp.checkpoint if cp is not None else path, strict=bool(self.cfg.strict))
         logger.info("loaded weights from %s", path)
         return model
+
+
+LoadWeightsTransformConfig = LoadWeightsConfig   # the reference's name

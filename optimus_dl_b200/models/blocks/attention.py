@@ -16,6 +16,22 @@ from ...ops import linear as lin_ops
 from .layer_norms import RMSNorm
 
 
+def attention_mask_fn(b, _, q_idx, kv_idx, window_size=None, seq_lens=None, document_ids=None):
+    """The visibility rule of every attention path, as a predicate over index tensors (same arguments as
+    optimus_dl/modules/model/blocks/attention.py:44-65): key ``kv_idx`` is visible to query ``q_idx`` of sample ``b``
+    when it is not in the future, lies inside the sliding window, both positions are inside the sample's length,
+    and both belong to the same document. The kernels do not evaluate this function; they derive the same set from
+    one ``doc_start`` index per token (``ops.attention.build_doc_start``), and tests compare the two."""
+    visible = kv_idx <= q_idx
+    if window_size is not None:
+        visible = visible & (q_idx - kv_idx < window_size)
+    if seq_lens is not None:
+        visible = visible & (q_idx < seq_lens[b]) & (kv_idx < seq_lens[b])
+    if document_ids is not None:
+        visible = visible & (document_ids[b, q_idx] == document_ids[b, kv_idx])
+    return visible
+
+
 class BaseSelfAttention(nn.Module):
     use_rope = False
 

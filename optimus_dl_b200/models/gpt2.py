@@ -177,3 +177,6 @@ class GPT(BaseModel):
 @GPT.register_arch("124m")
 def gpt2_124m():
     return GPTConfig(n_layer=12, n_head=12, n_embd=768)
+
+
+MLP = GELUMLP   # the reference keeps GPT-2's feed-forward block under this name in this module

@@ -20,7 +20,7 @@ import logging
 import os
 from abc import ABC, abstractmethod
 from dataclasses import dataclass
-from typing import Any
+from typing import Any, NamedTuple
 
 import torch
 import torch.distributed as dist
@@ -174,6 +174,14 @@ class FakeCollective(Collective):
         pass
 
 
+class Meshes(NamedTuple):
+    """The two device meshes of a run (optimus_dl/modules/distributed/mesh.py:29-38): ``parallel_mesh`` with dimensions
+    ``(dp_replicate, dp_shard, tp)`` and ``physical_mesh`` with ``(nodes, local_ranks)``."""
+
+    parallel_mesh: Any
+    physical_mesh: Any
+
+
 class MeshCollective(Collective):
     """``torch.distributed`` backed collective with (dp_replicate, dp_shard, tp) topology."""
 
@@ -264,6 +272,10 @@ class MeshCollective(Collective):
     @property
     def parallel_mesh(self):
         return self._parallel_mesh
+
+    @property
+    def meshes(self) -> "Meshes":
+        return Meshes(self._parallel_mesh, self._physical_mesh)
 
     @property
     def physical_mesh(self):

@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import logging
 import time
-from typing import Any
+from typing import Any, NamedTuple
 
 import torch
 
@@ -23,6 +23,20 @@ from .....model_transforms.distributed import accumulation_context
 from .....parallel.fsdp import ShardedAdamW
 
 logger = logging.getLogger(__name__)
+
+
+class ForwardPassResult(NamedTuple):
+    """Shape of one forward pass's outcome in the reference's step API
+    (optimus_dl/recipe/train/mixins/execution/iteration_mixin.py:41-49); kept for code written against it."""
+
+    loss: torch.Tensor
+    exposed_protocols: dict[str, Any]
+    elapsed_time: float
+
+
+class OptimizerStepResult(NamedTuple):
+    elapsed_time: float
+    grad_norm: torch.Tensor | None
 
 
 class TrainingIterationMixin:

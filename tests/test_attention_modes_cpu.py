@@ -161,3 +161,21 @@ def test_sequence_longer_than_the_configured_length_is_refused():
     m = _model("llama2")
     with pytest.raises(AssertionError):
         m(torch.randint(0, V, (1, 65)))
+
+
+def test_doc_start_masks_equal_the_visibility_predicate():
+    from optimus_dl_b200.models.blocks.attention import attention_mask_fn
+
+    B, T, w = 2, 10, 4
+    docs = torch.tensor([[0, 0, 0, 1, 1, 1, 1, 2, 2, 2], [3, 3, 3, 3, 3, 3, 3, 3, 3, 3]])
+    q = torch.arange(T)[:, None].expand(T, T)
+    k = torch.arange(T)[None, :].expand(T, T)
+    for window in (None, w):
+        got = mask_from_doc_start(build_doc_start(B, T, docs.device, document_ids=docs), window=window)
+        for b in range(B):
+            want = attention_mask_fn(b, None, q, k, window_size=window, document_ids=docs)
+            assert torch.equal(got[b * T:(b + 1) * T, b * T:(b + 1) * T], want), (window, b)
+        assert not got[:T, T:].any() and not got[T:, :T].any()      # samples of a batch never see each other
+    lens = torch.tensor([10, 6])
+    pred = torch.stack([attention_mask_fn(b, None, q, k, seq_lens=lens) for b in range(B)])
+    assert pred[1, 5, :6].all() and not pred[1, 7].any() and not pred[1, :, 6:].any() and pred[0].equal(k <= q)

@@ -164,3 +164,40 @@ def test_env_readers_accept_an_explicit_mapping_like_the_reference():
     assert E.get_device_from_env(env, "DEV") == torch.device("cuda", 1) and E.get_device_from_env(env, "MISSING") is None
     with pytest.raises(E.InvalidEnvironmentVariableError):
         E.get_device_from_env(env, "BADDEV")
+
+
+def test_names_the_reference_exports_resolve_here_too():
+    """Code written against the reference imports these names; each must exist and be the working object."""
+    import importlib
+
+    wanted = {
+        "optimus_dl_b200.core.env": ["get_int_from_env", "get_path_from_env", "get_device_from_env", "get_world_size"],
+        "optimus_dl_b200.core.multiprocess": ["finalize_process", "force_terminate_joblib", "finish_wandb", "finish_mlflow"],
+        "optimus_dl_b200.core.config_utils": ["non_resolving_instantiate", "hash_resolver", "conf_hash_resolver"],
+        "optimus_dl_b200.amp.fp8": ["Fp8Format", "Fp8RecipeType", "Fp8RecipeConfig", "FP8Recipe", "create_fp8_recipe",
+                                    "fp8_autocast", "fp8_backward", "get_fp8_format_from_string",
+                                    "get_fp8_recipe_type_from_string", "get_transformer_engine_version"],
+        "optimus_dl_b200.model_transforms.distributed": ["BaseDistributedTransform", "DDPWrappedModel", "OffloadConfig",
+                                                        "MixedPrecisionConfig", "FullyShardTransformConfig"],
+        "optimus_dl_b200.model_transforms.load_weights": ["LoadWeightsTransformConfig"],
+        "optimus_dl_b200.parallel.collective": ["Collective", "FakeCollective", "MeshCollective", "Meshes", "DistributedConfig"],
+        "optimus_dl_b200.models.blocks.attention": ["attention_mask_fn", "BaseSelfAttention", "CausalSelfAttention",
+                                                   "RotarySelfAttention"],
+        "optimus_dl_b200.models.gpt2": ["GPT", "GPTConfig", "Block", "MLP"],
+        "optimus_dl_b200.criterion.config": ["CriterionConfig"],
+        "optimus_dl_b200.metrics.metrics": ["AccuracyMetricConfig", "PerplexityMetricConfig", "LossMetricConfig"],
+        "optimus_dl_b200.data.transforms.skip": ["SkipInterleavedTransform", "SkipRandomTransform", "SkipRandomTransformNode"],
+        "optimus_dl_b200.data.transforms.base": ["ThreadedMapperConfig", "MapperConfig"],
+        "optimus_dl_b200.data.datasets.strategies.concat_random": ["ConcatAndChunkFullRandom", "ConcatAndChunkFullRandomConfig"],
+        "optimus_dl_b200.loggers.base": ["RunStatus", "BaseMetricsLogger"],
+        "optimus_dl_b200.loggers.mlflow": ["get_git_commit_hash", "get_git_remote"],
+        "optimus_dl_b200.recipe.train.mixins.execution.iteration_mixin": ["ForwardPassResult", "OptimizerStepResult",
+                                                                         "TrainingIterationMixin"],
+    }
+    for mod, names in wanted.items():
+        m = importlib.import_module(mod)
+        missing = [n for n in names if not hasattr(m, n)]
+        assert not missing, (mod, missing)
+    from optimus_dl_b200.model_transforms.distributed import OffloadConfig, _wants_cpu_offload
+
+    assert not _wants_cpu_offload({"cpu_offload": False, "pin_memory": True}) and _wants_cpu_offload(OffloadConfig(cpu_offload=True))
