@@ -15,9 +15,11 @@ from .base import BaseTransform
 @dataclass
 class PrefetchTransformConfig(RegistryConfigStrict):
     prefetch_factor: int = 8
+    snapshot_frequency: int = 128
 
 
 @register_transform("prefetch", PrefetchTransformConfig)
 class PrefetchTransform(BaseTransform):
     def build(self, source: BaseNode) -> BaseNode:
-        return Prefetcher(source, prefetch_factor=int(self.cfg.prefetch_factor))
+        return Prefetcher(source, prefetch_factor=int(self.cfg.prefetch_factor),
+                          snapshot_frequency=int(self.cfg.snapshot_frequency))

@@ -18,6 +18,9 @@ from .base import BaseTransform
 class SkipInterleavedConfig(RegistryConfigStrict):
     keep_every: int = 2      # keep one item out of this many
     offset: int = 0          # index (mod keep_every) of the kept item
+    # the reference's spelling (optimus_dl/modules/data/transforms/skip.py:15-22): the first item is produced, then
+    # ``skip_count`` items are dropped before each further one, i.e. keep_every = skip_count + 1 with offset 0
+    skip_count: int | None = None
 
 
 class SkipInterleavedNode(BaseNode):
@@ -50,6 +53,8 @@ class SkipInterleavedNode(BaseNode):
 @register_transform("skip_interleaved", SkipInterleavedConfig)
 class SkipInterleaved(BaseTransform):
     def build(self, source: BaseNode) -> BaseNode:
+        if self.cfg.skip_count is not None:
+            return SkipInterleavedNode(source, int(self.cfg.skip_count) + 1, 0)
         return SkipInterleavedNode(source, self.cfg.keep_every, self.cfg.offset)
 
 
@@ -58,12 +63,16 @@ class SkipRandomConfig(RegistryConfigStrict):
     keep_probability: float = 0.5
     seed: int = 0
     invert: bool = False     # keep exactly the items the non-inverted transform drops
+    # the reference's spelling (optimus_dl/modules/data/transforms/skip.py:85-92): probability that an item is dropped;
+    # an item is then dropped exactly when the draw is below it, as there
+    probability: float | None = None
 
 
 class SkipRandomNode(BaseNode):
     def __init__(self, node: BaseNode, p: float, seed: int, invert: bool):
         super().__init__()
         self.node, self.p, self.seed, self.invert = node, float(p), int(seed), bool(invert)
+        self.drop_below: float | None = None     # set when configured through ``probability``
         self.rng = random.Random(self.seed)
 
     def reset(self, initial_state: dict | None = None):
@@ -81,7 +90,8 @@ class SkipRandomNode(BaseNode):
     def next(self) -> Any:
         while True:
             item = next(self.node)
-            keep = self.rng.random() < self.p
+            r = self.rng.random()
+            keep = r >= self.drop_below if self.drop_below is not None else r < self.p
             if keep != self.invert:
                 return item
 
@@ -92,7 +102,10 @@ class SkipRandom(BaseTransform):
         super().__init__(cfg)
 
     def build(self, source: BaseNode) -> BaseNode:
-        return SkipRandomNode(source, self.cfg.keep_probability, self.cfg.seed, self.cfg.invert)
+        node = SkipRandomNode(source, self.cfg.keep_probability, self.cfg.seed, self.cfg.invert)
+        if self.cfg.probability is not None:
+            node.drop_below = float(self.cfg.probability)
+        return node
 
 
 # the reference's class names

@@ -21,6 +21,10 @@ class ToDeviceTransformConfig(RegistryConfigStrict):
     pin_memory: bool = True
     prefetch_factor: int = 2
     non_blocking: bool = True
+    # the reference's fields (optimus_dl/modules/data/transforms/to_device.py:22-33)
+    properties: list[str] | None = None        # keys to convert and move; None = every value
+    pin_prefetch_factor: int | None = None     # same role as prefetch_factor; wins when set
+    pin_snapshot_frequency: int = 128
 
 
 def _to_tensor(batch: Any) -> Any:
@@ -51,13 +55,19 @@ class ToDeviceTransform(BaseTransform):
         self.device = torch.device(dev) if dev is not None else torch.device("cuda" if torch.cuda.is_available() else "cpu")
 
     def build(self, source: BaseNode) -> BaseNode:
-        node: BaseNode = Mapper(source, _to_tensor)
+        props = list(self.cfg.properties) if self.cfg.properties is not None else None
+        if props is None:
+            node: BaseNode = Mapper(source, _to_tensor)
+        else:
+            node = Mapper(source, lambda b, _p=frozenset(props): {k: (_to_tensor(v) if k in _p else v) for k, v in b.items()}
+                          if isinstance(b, dict) else _to_tensor(b))
+        depth = self.cfg.pin_prefetch_factor if self.cfg.pin_prefetch_factor is not None else self.cfg.prefetch_factor
         if self.device.type == "cuda":
             if self.cfg.pin_memory:
                 node = PinMemory(node, pin_memory_device="cuda")
             node = Mapper(node, _Mover(self.device, bool(self.cfg.non_blocking)))
-            if self.cfg.prefetch_factor and self.cfg.prefetch_factor > 0:
-                node = Prefetcher(node, prefetch_factor=int(self.cfg.prefetch_factor))
+            if depth and depth > 0:
+                node = Prefetcher(node, prefetch_factor=int(depth), snapshot_frequency=int(self.cfg.pin_snapshot_frequency))
         elif self.device.type != "cpu":
             node = Mapper(node, _Mover(self.device, False))
         return node

@@ -15,11 +15,12 @@ from ..source import MetricSource, MetricSourceConfig, StandardProtocols as P, r
 
 @dataclass
 class GenerationSourceConfig(MetricSourceConfig):
-    max_new_tokens: int = 32
+    max_new_tokens: int = 50
     temperature: float = 1.0
     top_k: int | None = None
     top_p: float | None = None
-    greedy: bool = False
+    do_sample: bool = False          # the reference's switch: False = greedy search (its default)
+    greedy: bool | None = None       # explicit override; None = derived from do_sample
     eos_token_id: int | None = None
     prompt_length: int | None = None
     use_kv_cache: bool = True
@@ -55,6 +56,6 @@ class GenerationSource(MetricSource):
         from ...recipe.generation import generate
 
         out = generate(model, ids, max_new_tokens=int(self.cfg.max_new_tokens), temperature=float(self.cfg.temperature),
-                       top_k=self.cfg.top_k, top_p=self.cfg.top_p, greedy=bool(self.cfg.greedy),
+                       top_k=self.cfg.top_k, top_p=self.cfg.top_p, greedy=(bool(self.cfg.greedy) if self.cfg.greedy is not None else not bool(self.cfg.do_sample)),
                        eos_token_id=self.cfg.eos_token_id, use_kv_cache=bool(self.cfg.use_kv_cache))
         return {P.GENERATED_TOKENS: out}

@@ -30,6 +30,7 @@ class ActivationCheckpointConfig(RegistryConfig):
     layer_classes: list[str] = field(default_factory=list)
     ops_to_save: list[str] = field(default_factory=list)
     every_nth: int = 1
+    use_reentrant: bool = False
 
 
 def _policy(ops: list[Any]):
@@ -62,7 +63,7 @@ class ActivationCheckpointTransform(BaseModelTransform):
                 if not torch.is_grad_enabled():
                     return _orig(*a, **k)
                 extra = {"context_fn": ctx_fn} if ctx_fn is not None else {}
-                return checkpoint(_orig, *a, use_reentrant=False, **extra, **k)
+                return checkpoint(_orig, *a, use_reentrant=bool(self.cfg.get("use_reentrant", False)), **extra, **k)
 
             m.forward = wrapped
             count += 1

@@ -76,6 +76,8 @@ class MixedPrecisionConfig:
     reduce_dtype: str | None = "float32"
     output_dtype: str | None = None
     cast_forward_inputs: bool = True
+    fp8_enabled: bool = False        # informational, as in the reference: FP8 is driven by optimization.amp.fp8
+    fp8_format: str | None = None
 
 
 @dataclass

@@ -19,7 +19,8 @@ logger = logging.getLogger(__name__)
 
 @dataclass
 class LoadWeightsConfig(RegistryConfig):
-    path: str = "???"
+    path: str | None = None
+    checkpoint_path: str | None = None   # the reference's name for ``path``
     strict: bool = True
     skip_on_restart: bool = True
 
@@ -33,7 +34,10 @@ class LoadWeightsTransform(BaseModelTransform):
         from ..checkpoint import CheckpointManager
 
         mgr = checkpoint_manager or CheckpointManager()
-        path = str(self.cfg.path)
+        path = self.cfg.checkpoint_path if self.cfg.checkpoint_path is not None else self.cfg.path
+        if path is None:
+            raise ValueError("load_weights: set checkpoint_path (or path)")
+        path = str(path)
         cp = mgr.get_checkpoint(path)
         mgr.load_model_state_dict(model, cp.checkpoint if cp is not None else path, strict=bool(self.cfg.strict))
         logger.info("loaded weights from %s", path)

@@ -72,6 +72,61 @@ class TrainRecipe(TrainingContextMixin, TrainingIterationMixin, TrainingInterrup
     def _full_config(self) -> Any:
         return conf.to_container(self.cfg, resolve=True)
 
+    # ------------------------------------------------------------------ delegation surface
+    # One-line forwards to the injected builders and managers, under the names the reference's recipe exposes
+    # (optimus_dl/recipe/train/base.py:168-262), so subclasses and scripts written against it keep working.
+    def build_model(self, *args: Any, **kwargs: Any):
+        return self.model_builder.build_model(*args, **kwargs)
+
+    def build_optimizer(self, *args: Any, **kwargs: Any):
+        return self.optimizer_builder.build_optimizer(*args, **kwargs)
+
+    def build_lr_scheduler(self, *args: Any, **kwargs: Any):
+        return self.scheduler_builder.build_lr_scheduler(*args, **kwargs)
+
+    def build_criterion(self, *args: Any, **kwargs: Any):
+        return self.criterion_builder.build_criterion(*args, **kwargs)
+
+    def build_train_data(self, *args: Any, **kwargs: Any):
+        return self.data_builder.build_train_data(*args, **kwargs)
+
+    def build_eval_data(self, *args: Any, **kwargs: Any):
+        return self.data_builder.build_eval_data(*args, **kwargs)
+
+    def build_loggers(self, *args: Any, **kwargs: Any):
+        return self.logger_manager.build_loggers(*args, **kwargs)
+
+    def setup_loggers(self, experiment_name: str, full_config: dict | None = None, **_: Any):
+        return self.logger_manager.setup_loggers(experiment_name, full_config if full_config is not None else self._full_config())
+
+    def log_metrics_to_loggers(self, *args: Any, **kwargs: Any):
+        return self.logger_manager.log_metrics_to_loggers(*args, **kwargs)
+
+    def close_loggers(self, run_status: RunStatus = RunStatus.SUCCESS, *args: Any, **kwargs: Any):
+        self.logger_manager.finished(run_status)
+        return self.logger_manager.close_loggers(*args, **kwargs)
+
+    def save_checkpoint_if_needed(self, *args: Any, **kwargs: Any):
+        return self.checkpoint_manager.save_checkpoint_if_needed(*args, **kwargs)
+
+    def save_checkpoint(self, *args: Any, **kwargs: Any):
+        return self.checkpoint_manager.save_checkpoint(*args, **kwargs)
+
+    def load_checkpoint_if_exists(self, *args: Any, **kwargs: Any):
+        return self.checkpoint_manager.load_checkpoint_if_exists(*args, **kwargs)
+
+    def load_checkpoint(self, *args: Any, **kwargs: Any):
+        return self.checkpoint_manager.load_checkpoint(*args, **kwargs)
+
+    def validate_config(self) -> None:
+        """Refuse configurations that cannot train (same checks as the reference's recipe)."""
+        cfg = self.cfg
+        for key in ("model", "data", "criterion", "optimization"):
+            assert cfg.get(key) is not None, f"{key.capitalize()} configuration is required"
+        assert int(cfg.optimization.iterations) > 0, "iterations must be positive"
+        assert int(cfg.optimization.acc_steps) > 0, "acc_steps must be positive"
+        assert int(cfg.common.log_freq) > 0, "log_freq must be positive"
+
     def _save(self, iteration: int, *, model, optimizer, lr_scheduler, collective, train_loader, persistent=True,
               metadata_only=False, extra=None) -> None:
         self.checkpoint_manager.save_checkpoint(
@@ -83,6 +138,7 @@ class TrainRecipe(TrainingContextMixin, TrainingIterationMixin, TrainingInterrup
     # ------------------------------------------------------------------ run
     def run(self) -> None:
         cfg, c = self.cfg, self.cfg.common
+        self.validate_config()
         self.setup_context()
         is_restart = self.checkpoint_manager.is_restart()
         with meters_group("init", log_freq=1):
@@ -183,6 +239,10 @@ class TrainRecipe(TrainingContextMixin, TrainingIterationMixin, TrainingInterrup
                 collective.close()
             except Exception as e:
                 logger.debug("collective.close: %s", e)
+
+    def evaluate_and_log(self, iteration, model, criterion, eval_datapipeline, collective, device=None) -> dict:
+        """Reference argument order for :meth:`_evaluate_and_log` (always evaluates)."""
+        return self._evaluate_and_log(model, criterion, eval_datapipeline, iteration, collective, force=True)
 
     def _evaluate_and_log(self, model, criterion, eval_data, iteration, collective, force: bool = False) -> dict:
         results = self.evaluator.run_evaluation(model, criterion, eval_data, iteration, collective=collective,

@@ -14,6 +14,7 @@ from ...parallel.collective import DistributedConfig
 @dataclass
 class TrainRecipeConfig:
     exp_name: str = "optimus-dl-run-${config_hash:}"
+    exp_description: str | None = None
     exp_tags: list[str] = field(default_factory=list)
     log_freq: int = 16
     seed: int = 42

@@ -13,12 +13,15 @@ from ..config import BaseTokenizerConfig
 
 @dataclass
 class CharTokenizerConfig(BaseTokenizerConfig):
-    pass
+    vocab_size: int = 256        # byte values; the two special ids follow
+    bos_token_id: int = 256
+    eos_token_id: int = 257
 
 
 @register_tokenizer("char_tokenize", CharTokenizerConfig)
 class CharTokenizer(BaseTokenizer):
-    BOS, EOS = 256, 257
+    """UTF-8 bytes as tokens; the special ids and the reported vocabulary size come from the config
+    (optimus_dl/modules/tokenizer/implementations/char.py)."""
 
     def __init__(self, config, **kwargs: Any):
         super().__init__(config)
@@ -26,9 +29,13 @@ class CharTokenizer(BaseTokenizer):
     def encode(self, text: str) -> list[int]:
         ids = list(text.encode("utf-8"))
         if self.config.add_bos:
-            ids.insert(0, self.BOS)
+            if self.bos_token_id is None:
+                raise ValueError("Tokenizer does not have a BOS token ID, but add_bos is True.")
+            ids.insert(0, self.bos_token_id)
         if self.config.add_eos:
-            ids.append(self.EOS)
+            if self.eos_token_id is None:
+                raise ValueError("Tokenizer does not have an EOS token ID, but add_eos is True.")
+            ids.append(self.eos_token_id)
         return ids
 
     def decode(self, ids: list[int]) -> str:
@@ -36,12 +43,12 @@ class CharTokenizer(BaseTokenizer):
 
     @property
     def vocab_size(self) -> int:
-        return 258
+        return max(int(self.config.vocab_size), int(self.config.eos_token_id or 0) + 1, int(self.config.bos_token_id or 0) + 1)
 
     @property
-    def bos_token_id(self) -> int:
-        return self.BOS
+    def bos_token_id(self) -> int | None:
+        return self.config.bos_token_id
 
     @property
-    def eos_token_id(self) -> int:
-        return self.EOS
+    def eos_token_id(self) -> int | None:
+        return self.config.eos_token_id

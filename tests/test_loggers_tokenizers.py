@@ -22,8 +22,8 @@ def _lines(path):
 
 
 def test_jsonl_writes_one_file_per_group_and_dumps_the_config(tmp_path):
-    lg = build_metrics_logger({"_name": "jsonl", "output_dir": str(tmp_path / "logs")})
-    lg.setup("exp", {"model": {"n_layer": 2}, "lr": 1e-3, "dtype": torch.bfloat16})
+    lg = build_metrics_logger({"_name": "jsonl", "output_dir": str(tmp_path / "logs"), "flush_every": 1})
+    lg.setup("exp", {"model": {"n_layer": 2}, "lr": 1e-3, "dtype": torch.bfloat16}, logs_parent_path=None, start_iteration=1)
     lg.log_metrics({"loss": torch.tensor(2.5), "nested": {"a": 1}, "items": (1, 2)}, step=1)
     lg.log_metrics({"loss": 2.0}, step=2)
     lg.log_metrics({"accuracy": 0.5}, step=2, group="eval/tiny")
@@ -32,39 +32,62 @@ def test_jsonl_writes_one_file_per_group_and_dumps_the_config(tmp_path):
     d = tmp_path / "logs"
     train = _lines(d / "metrics.jsonl")
     assert [r["step"] for r in train] == [1, 2] and train[0]["loss"] == 2.5 and train[0]["group"] == "train"
-    assert train[0]["nested"] == {"a": 1} and train[0]["items"] == [1, 2] and "time" in train[0]
+    assert train[0]["nested_a"] == 1 and train[0]["items"] == [1, 2]            # dictionaries flatten one level
+    assert "T" in train[0]["timestamp"] and list(train[0])[:3] == ["step", "group", "timestamp"]
     ev = _lines(d / "metrics_eval_tiny.jsonl")
-    assert ev == [dict(ev[0], accuracy=0.5, step=2, group="eval/tiny")]
-    assert _lines(d / "metrics_final.jsonl")[0]["status"] == "success"
+    assert len(ev) == 1 and ev[0]["accuracy"] == 0.5 and ev[0]["group"] == "eval/tiny"
+    final = _lines(d / "metrics_final.jsonl")[0]
+    assert final["status"] == "success" and final["group"] == "final" and final["step"] is None
     assert RunStatus.FINISHED is RunStatus.SUCCESS and RunStatus.FAILED is RunStatus.FAILURE
     assert RunStatus("interrupted") is RunStatus.INTERRUPTED
-    cfg_json = json.load(open(d / "config.json"))
+    cfg_json = json.load(open(d / "exp_config.json"))
     assert cfg_json["model"]["n_layer"] == 2 and cfg_json["dtype"] == "torch.bfloat16"
-    assert yaml.safe_load(open(d / "config.yaml"))["lr"] == 1e-3
+    assert yaml.safe_load(open(d / "exp_config.yaml"))["lr"] == 1e-3
 
 
-def test_jsonl_rotates_by_size_and_resumes_at_the_current_part(tmp_path):
-    cfg = {"_name": "jsonl", "output_dir": str(tmp_path), "max_file_size_mb": 0.001, "dump_config": False}
+def test_jsonl_options_single_file_no_timestamp_sorted_truncate(tmp_path):
+    cfg = {"_name": "jsonl", "output_dir": str(tmp_path), "filename": "run.log", "include_group_in_filename": False,
+           "include_timestamp": False, "sort_keys": True, "dump_config": False, "append_mode": False}
+    (tmp_path / "run.log").write_text("stale\n")
     lg = build_metrics_logger(cfg)
     lg.setup("exp", {})
-    for step in range(40):
+    lg.log_metrics({"z": 1, "a": 2}, step=1)
+    lg.log_metrics({"b": 3}, step=1, group="eval")
+    lg.close()
+    text = (tmp_path / "run.log").read_text().splitlines()
+    assert text == ['{"a": 2, "group": "train", "step": 1, "z": 1}', '{"b": 3, "group": "eval", "step": 1}']
+    assert sorted(os.listdir(tmp_path)) == ["run.log"]
+
+
+def test_jsonl_rotation_keeps_the_newest_lines_in_the_plain_file(tmp_path):
+    cfg = {"_name": "jsonl", "output_dir": str(tmp_path), "max_file_size_mb": 0.001, "max_rotated_files": 2,
+           "dump_config": False, "include_timestamp": False}
+    lg = build_metrics_logger(cfg)
+    lg.setup("exp", {})
+    for step in range(60):
         lg.log_metrics({"loss": float(step), "pad": "x" * 100}, step=step)
     lg.close()
-    parts = sorted(p for p in os.listdir(tmp_path) if p.startswith("metrics"))
-    assert len(parts) >= 3 and "metrics.jsonl" in parts and "metrics.1.jsonl" in parts
-    steps = []
-    for i in range(len(parts)):
-        steps += [r["step"] for r in _lines(tmp_path / ("metrics.jsonl" if i == 0 else f"metrics.{i}.jsonl"))]
-    assert steps == list(range(40))                      # nothing lost or duplicated across parts
-    state = lg.state_dict()
-    assert state["rotation"]["train"] == len(parts) - 1 or state["rotation"]["train"] == len(parts)
-    again = build_metrics_logger(cfg, state_dict=state)
+    parts = sorted(os.listdir(tmp_path))
+    assert parts == ["metrics.1.jsonl", "metrics.2.jsonl", "metrics.jsonl"]       # older parts were dropped
+    newest = [r["step"] for r in _lines(tmp_path / "metrics.jsonl")]
+    mid = [r["step"] for r in _lines(tmp_path / "metrics.1.jsonl")]
+    old = [r["step"] for r in _lines(tmp_path / "metrics.2.jsonl")]
+    assert newest[-1] == 59 and old + mid + newest == list(range(old[0], 60))      # contiguous, newest last
+    again = build_metrics_logger(cfg)                                               # a restart appends to the plain file
     again.setup("exp", {})
-    again.log_metrics({"loss": -1.0}, step=40)
+    again.log_metrics({"loss": -1.0}, step=60)
     again.close()
-    newest = tmp_path / f"metrics.{state['rotation']['train']}.jsonl"
-    assert _lines(newest)[-1]["step"] == 40
-    assert not os.path.exists(tmp_path / "config.json")
+    assert _lines(tmp_path / "metrics.jsonl")[-1]["step"] == 60
+    unlimited = build_metrics_logger({**cfg, "output_dir": str(tmp_path / "u"), "max_rotated_files": -1})
+    unlimited.setup("exp", {})
+    for step in range(60):
+        unlimited.log_metrics({"loss": float(step), "pad": "x" * 100}, step=step)
+    unlimited.close()
+    all_steps = []
+    files = sorted(os.listdir(tmp_path / "u"), key=lambda n: -int(n.split(".")[1]) if n.count(".") == 2 else 1)
+    for n in files:
+        all_steps += [r["step"] for r in _lines(tmp_path / "u" / n)]
+    assert all_steps == list(range(60)) and len(files) > 3                          # nothing is ever deleted
 
 
 def test_disabled_logger_writes_nothing(tmp_path):
@@ -119,11 +142,25 @@ def test_logger_manager_isolates_failures_keys_state_by_id_and_times_itself(tmp_
     mgr.close_loggers()                                  # the failing logger never stops the others
     assert _lines(tmp_path / "a" / "metrics.jsonl")[0]["step"] == 3 and _lines(tmp_path / "b" / "metrics.jsonl")[0]["loss"] == 1.0
     sd = mgr.state_dict()
-    assert set(sd) == {"jsonl", "second", "boom"} and sd["boom"] == {"k": 1}
-    fresh = LoggerManager(loggers_config=[{"_name": "jsonl", "id": "second", "output_dir": str(tmp_path / "b")}])
-    fresh.load_state_dict({"second": {"rotation": {"train": 2}}})
+    assert set(sd) == {"jsonl", "second", "boom"} and sd["boom"] == {"k": 1} and sd["jsonl"] == {}
+    seen = {}
+    from optimus_dl_b200.loggers import register_metrics_logger
+    from optimus_dl_b200.loggers.base import BaseMetricsLogger
+    from optimus_dl_b200.loggers.config import MetricsLoggerConfig
+
+    class _Remember(BaseMetricsLogger):
+        def __init__(self, cfg, state_dict=None, **kw):
+            super().__init__(cfg)
+            seen["state"] = state_dict
+
+    try:
+        register_metrics_logger("t_remember", MetricsLoggerConfig)(_Remember)
+    except (AssertionError, ValueError, KeyError):
+        pass
+    fresh = LoggerManager(loggers_config=[{"_name": "t_remember", "id": "second"}])
+    fresh.load_state_dict({"second": {"run_id": "abc"}})
     fresh.build_loggers()                                # state given before building reaches the constructor
-    assert fresh.loggers[0].state_dict() == {"rotation": {"train": 2}}
+    assert seen["state"] == {"run_id": "abc"}
 
 
 def test_char_tokenizer_round_trips_utf8_and_reserves_bos_eos():
