@@ -28,6 +28,7 @@ class TokenizedDatasetConfig(RegistryConfig):
     index_file: str = "index.json"
     strategy: Any = field(default_factory=lambda: {"_name": "document"})
     limit_documents: int | None = None
+    limit: int | None = None        # the reference's name for limit_documents
 
 
 @register_dataset("tokenized_dataset", TokenizedDatasetConfig)
@@ -45,8 +46,9 @@ class TokenizedDataset(BaseDataset):
             lens.append(np.asarray(l, dtype=np.int64))
             self.shard_doc_start.append(self.shard_doc_start[-1] + len(l))
         self.doc_lens = np.concatenate(lens) if lens else np.zeros(0, dtype=np.int64)
-        if cfg.limit_documents is not None:
-            self.doc_lens = self.doc_lens[: int(cfg.limit_documents)]
+        limit = cfg.get("limit") if cfg.get("limit") is not None else cfg.limit_documents
+        if limit is not None:
+            self.doc_lens = self.doc_lens[: int(limit)]
         self.shard_tok_start = [np.concatenate([[0], np.cumsum(l)]) for l in lens]
         self.strategy = build_strategy(cfg.strategy, rank=rank, world_size=world_size, seed=seed)
         self.strategy.global_seed = seed

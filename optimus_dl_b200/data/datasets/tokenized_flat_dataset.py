@@ -23,6 +23,7 @@ class TokenizedFlatDatasetConfig(RegistryConfigStrict):
     batch_size: int = 1
     seq_len: int = 1024
     header_bytes: int = 0
+    offset: int | None = None       # the reference's name for header_bytes (bytes skipped at the start of raw files)
     add_one_for_shift: bool = True
 
 
@@ -39,7 +40,10 @@ class TokenizedFlatDataset(BaseDataset):
             if f.endswith(".npy"):
                 self.maps.append(np.load(f, mmap_mode="r"))
             else:
-                self.maps.append(np.memmap(f, dtype=np.dtype(cfg.dtype), mode="r", offset=int(cfg.header_bytes)))
+                skip = cfg.offset if cfg.offset is not None else cfg.header_bytes
+                name = str(cfg.dtype)
+                name = name[3:] if name.startswith("np.") else name        # "np.uint16" and "uint16" both name the type
+                self.maps.append(np.memmap(f, dtype=np.dtype(name), mode="r", offset=int(skip)))
         self.cum = np.concatenate([[0], np.cumsum([len(m) for m in self.maps])]).astype(np.int64)
         total = int(self.cum[-1])
         per = total // world_size

@@ -3,6 +3,7 @@
 
 from __future__ import annotations
 
+import logging
 from dataclasses import dataclass, field
 from typing import Any
 
@@ -12,6 +13,8 @@ from ...core.registry import RegistryConfig
 from . import register_transform
 from .base import BaseTransform, MapperConfig
 
+logger = logging.getLogger(__name__)
+
 
 @dataclass
 class TokenizeTransformConfig(RegistryConfig):
@@ -20,13 +23,15 @@ class TokenizeTransformConfig(RegistryConfig):
     input_field: str = "text"
     output_field: str = "input_ids"
     keep_text: bool = False
+    debug_samples: int = 0          # log this many tokenised samples (text and ids) for inspection
 
 
 class _Tokenize:
     """Picklable callable; the tokenizer is built lazily inside each worker."""
 
-    def __init__(self, tok_cfg: Any, in_f: str, out_f: str, keep: bool):
+    def __init__(self, tok_cfg: Any, in_f: str, out_f: str, keep: bool, debug_samples: int = 0):
         self.tok_cfg, self.in_f, self.out_f, self.keep = tok_cfg, in_f, out_f, keep
+        self.debug_samples, self._shown = int(debug_samples), 0
         self._tok = None
 
     def __call__(self, item: dict) -> dict:
@@ -36,10 +41,14 @@ class _Tokenize:
             self._tok = build_tokenizer(self.tok_cfg)
         out = dict(item) if self.keep else {k: v for k, v in item.items() if k != self.in_f}
         out[self.out_f] = self._tok.encode(item[self.in_f])
+        if self._shown < self.debug_samples:
+            self._shown += 1
+            logger.info("tokenize sample %d: %r -> %s", self._shown, str(item[self.in_f])[:200], list(out[self.out_f])[:64])
         return out
 
     def __getstate__(self):
-        return {"tok_cfg": self.tok_cfg, "in_f": self.in_f, "out_f": self.out_f, "keep": self.keep, "_tok": None}
+        return {"tok_cfg": self.tok_cfg, "in_f": self.in_f, "out_f": self.out_f, "keep": self.keep, "_tok": None,
+                "debug_samples": self.debug_samples, "_shown": self._shown}
 
 
 @register_transform("tokenize", TokenizeTransformConfig)
@@ -52,7 +61,8 @@ class TokenizeTransform(BaseTransform):
 
         tok_cfg = conf.to_container(self.cfg.tokenizer_config, resolve=True) if conf.is_config(self.cfg.tokenizer_config) \
             else self.cfg.tokenizer_config
-        fn = _Tokenize(tok_cfg, self.cfg.input_field, self.cfg.output_field, bool(self.cfg.keep_text))
+        fn = _Tokenize(tok_cfg, self.cfg.input_field, self.cfg.output_field, bool(self.cfg.keep_text),
+                       int(self.cfg.get("debug_samples", 0) or 0))
         w = self.cfg.worker_cfg
         if not w.num_workers:
             return Mapper(source, fn)

@@ -22,7 +22,8 @@ class BaseMetricsLogger:
         self.cfg = cfg
         self.enabled = bool(cfg.get("enabled", True)) if cfg is not None else True
 
-    def setup(self, experiment_name: str, config: dict[str, Any]) -> None:
+    def setup(self, experiment_name: str, config: dict[str, Any], logs_parent_path: str | None = None,
+              start_iteration: int | None = None) -> None:
         """Called once on the master rank before training starts."""
 
     def log_metrics(self, metrics: dict[str, Any], step: int, group: str = "train") -> None:

@@ -28,6 +28,15 @@ class MlflowLoggerConfig(MetricsLoggerConfig):
     tracking_uri: str | None = None
     experiment_name: str | None = None
     run_name: str | None = None
+    # the reference's names (optimus_dl/modules/loggers/mlflow.py:55-66): ``project`` is the MLflow experiment,
+    # ``name`` the run name; both win over the two fields above when set
+    project: str | None = None
+    name: str | None = None
+    workspace: str | None = None
+    artifact_location: str | None = None
+    max_retries: int = 10
+    backoff_factor: int = 2
+    timeout: int = 15
     async_logging: bool = True
     log_system_metrics: bool = False
     log_config_artifacts: bool = True
@@ -71,7 +80,8 @@ class MlflowLogger(BaseMetricsLogger):
         self._mlflow = None
         self._active = False
 
-    def setup(self, experiment_name: str, config: dict[str, Any]) -> None:
+    def setup(self, experiment_name: str, config: dict[str, Any], logs_parent_path: str | None = None,
+              start_iteration: int | None = None) -> None:
         if not self.enabled:
             return
         try:
@@ -83,13 +93,29 @@ class MlflowLogger(BaseMetricsLogger):
         self._mlflow = mlflow
         if self.cfg.tracking_uri:
             mlflow.set_tracking_uri(self.cfg.tracking_uri)
-        mlflow.set_experiment(self.cfg.experiment_name or experiment_name)
+        for var, value in (("MLFLOW_HTTP_REQUEST_MAX_RETRIES", self.cfg.max_retries),
+                           ("MLFLOW_HTTP_REQUEST_BACKOFF_FACTOR", self.cfg.backoff_factor),
+                           ("MLFLOW_HTTP_REQUEST_TIMEOUT", self.cfg.timeout)):
+            try:
+                getattr(mlflow.environment_variables, var).set(value)
+            except Exception:
+                os.environ[var] = str(value)
+        workspace = self.cfg.workspace or os.getenv("MLFLOW_WORKSPACE")
+        if workspace and hasattr(mlflow, "set_workspace"):
+            try:
+                mlflow.set_workspace(workspace)
+            except Exception as e:
+                logger.error("could not set the MLflow workspace: %s", e)
+        exp_name = self.cfg.project or self.cfg.experiment_name or os.getenv("MLFLOW_EXPERIMENT_NAME") or experiment_name
+        if self.cfg.artifact_location and mlflow.get_experiment_by_name(exp_name) is None:
+            mlflow.create_experiment(exp_name, artifact_location=self.cfg.artifact_location)
+        mlflow.set_experiment(exp_name)
         if self.cfg.async_logging:
             try:
                 mlflow.config.enable_async_logging(True)
             except Exception:
                 pass
-        run = mlflow.start_run(run_id=self.run_id, run_name=self.cfg.run_name or experiment_name,
+        run = mlflow.start_run(run_id=self.run_id, run_name=self.cfg.name or self.cfg.run_name or experiment_name,
                                log_system_metrics=bool(self.cfg.log_system_metrics) or None)
         self.run_id = run.info.run_id
         self._active = True

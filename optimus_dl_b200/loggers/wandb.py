@@ -22,6 +22,7 @@ class WandbLoggerConfig(MetricsLoggerConfig):
     entity: str | None = None
     group: str | None = None
     name: str | None = None
+    job_type: str | None = "train"
     mode: str | None = None            # "online" | "offline" | "disabled"
     save_code: bool = False
     log_dir_artifact: str | None = None
@@ -36,7 +37,8 @@ class WandbLogger(BaseMetricsLogger):
         self.run_id = (state_dict or {}).get("run_id")
         self._wandb = None
 
-    def setup(self, experiment_name: str, config: dict[str, Any]) -> None:
+    def setup(self, experiment_name: str, config: dict[str, Any], logs_parent_path: str | None = None,
+              start_iteration: int | None = None) -> None:
         if not self.enabled:
             return
         try:
@@ -48,7 +50,8 @@ class WandbLogger(BaseMetricsLogger):
         self._wandb = wandb
         kw: dict[str, Any] = dict(project=self.cfg.project, entity=self.cfg.entity, group=self.cfg.group,
                                   name=self.cfg.name or experiment_name, config=config, tags=list(self.cfg.tags or []),
-                                  notes=self.cfg.notes, save_code=bool(self.cfg.save_code), dir=self.cfg.dir)
+                                  notes=self.cfg.notes, save_code=bool(self.cfg.save_code), dir=self.cfg.dir,
+                                  job_type=self.cfg.get("job_type"))
         if self.cfg.mode:
             kw["mode"] = self.cfg.mode
         if self.run_id:

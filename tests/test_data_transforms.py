@@ -190,3 +190,35 @@ def test_to_device_converts_arrays_and_leaves_scalars():
     out = next(node)
     assert isinstance(out["input_ids"], torch.Tensor) and out["input_ids"].dtype == torch.int64
     assert out["max_seqlen"] == 3 and out["name"] == "x"
+
+
+def test_reference_spellings_of_transform_and_dataset_options(tmp_path, caplog):
+    import logging
+
+    node = build_transform({"_name": "skip_interleaved", "skip_count": 2}).build(_Range(10))
+    node.reset()
+    assert [x["input_ids"][0] for x in _drain(node)] == [0, 3, 6, 9]          # first item, then two dropped each time
+    a = build_transform({"_name": "skip_random", "probability": 0.25, "seed": 3}).build(_Range(400))
+    a.reset()
+    kept = len(_drain(a))
+    assert 260 < kept < 340                                                     # an item is dropped with probability 0.25
+    for cfg in ({"_name": "prefetch", "prefetch_factor": 2, "snapshot_frequency": 4},
+                {"_name": "to_device", "pin_prefetch_factor": 1, "pin_snapshot_frequency": 8, "properties": ["input_ids"]}):
+        n = build_transform(cfg, device=torch.device("cpu")).build(_Range(3, lambda i: {"input_ids": np.arange(3), "other": np.arange(2)}))
+        n.reset()
+        out = _drain(n)
+        assert len(out) == 3
+    assert isinstance(out[0]["input_ids"], torch.Tensor) and isinstance(out[0]["other"], np.ndarray)   # only listed keys move
+    with caplog.at_level(logging.INFO):
+        tok = build_transform({"_name": "tokenize", "tokenizer_config": {"_name": "char_tokenize"}, "debug_samples": 1,
+                               "worker_cfg": {"num_workers": 0}}).build(_Range(3, lambda i: {"text": "ab"}))
+        tok.reset()
+        _drain(tok)
+    assert caplog.text.count("tokenize sample") == 1
+    raw = tmp_path / "tokens.bin"
+    np.concatenate([np.zeros(4, np.uint16), np.arange(40, dtype=np.uint16)]).tofile(raw)
+    flat = build_dataset({"_name": "tokenized_flat", "files": [str(raw)], "dtype": "np.uint16", "seq_len": 4, "batch_size": 2,
+                          "offset": 8})
+    flat.reset()
+    first = next(flat)
+    assert np.asarray(first["input_ids"])[0, 0] == 0 and np.asarray(first["input_ids"]).shape[0] == 2
