@@ -60,3 +60,38 @@ def test_fp8_amp_presets_compose(preset, recipe):
     cfg = compose.compose([os.path.join(ROOT, "train")], "train_llama_fp8", [f"optimization/amp={preset}"], apply_env=False)
     fp8 = cfg["optimization"]["amp"]["fp8"]
     assert fp8["enabled"] and fp8["recipe"] == recipe and fp8["wgrad"]
+
+
+@pytest.mark.parametrize("name", sorted(f[:-5] for f in os.listdir(os.path.join(ROOT, "train"))
+                                        if f.startswith("train_") and f.endswith(".yaml")))
+def test_train_configs_build_their_components(name, monkeypatch):
+    """Every train root config yields a buildable model (on the meta device), criterion, schedule, model transforms,
+    data transform and metric engines: no key in the shipped YAML is unknown to the code."""
+    import torch
+
+    from optimus_dl_b200.core.config_utils import non_resolving_instantiate
+    from optimus_dl_b200.criterion import build_criterion
+    from optimus_dl_b200.data.transforms import build_transform
+    from optimus_dl_b200.lr_scheduler import build_lr_scheduler
+    from optimus_dl_b200.metrics.engine import MetricEngine
+    from optimus_dl_b200.model_transforms import build_model_transform
+    from optimus_dl_b200.models import build_model
+
+    monkeypatch.setenv("SCRATCH_HOME", "/tmp/optimus-test")
+    monkeypatch.setenv("PERSISTENT_PATH", "/tmp/optimus-test")
+    cfg = non_resolving_instantiate(compose.compose([os.path.join(ROOT, "train")], name, [], apply_env=False))
+    with torch.device("meta"):
+        model = build_model(cfg.model)
+    assert sum(p.numel() for p in model.parameters()) > 0
+    build_criterion(cfg.criterion)
+    opt = torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=1.0)
+    build_lr_scheduler(cfg.lr_scheduler, optimizer=opt, iterations=int(cfg.optimization.iterations))
+    for t in (cfg.get("model_transforms") or []):
+        build_model_transform(t)
+    train = cfg.data.get("train_datasets", {})
+    if train and train.get("transform") is not None:
+        build_transform(train.transform, device=torch.device("cpu"))
+    metrics = cfg.get("metrics")
+    if metrics and hasattr(metrics, "items"):
+        for group, configs in metrics.items():
+            MetricEngine(group, configs)
