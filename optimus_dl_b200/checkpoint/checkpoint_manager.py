@@ -42,8 +42,19 @@ class CheckpointManagerConfig(RegistryConfig):
 
 
 class CheckpointPath(NamedTuple):
+    """``metadata`` file and ``checkpoint`` (weights) path of one save."""
+
     metadata: str
     checkpoint: str
+
+    def per_rank_metadata(self, rank: int) -> str:
+        """Path of ``rank``'s per-rank metadata file that belongs to this save."""
+        p = Path(self.metadata)
+        return str(p.with_name(p.name.replace("metadata_", f"per_rank_metadata_{rank}_", 1)))
+
+    def is_dcp_checkpoint(self) -> bool:
+        """A directory holds a sharded (``torch.distributed.checkpoint``) save; a file is a plain ``torch.save``."""
+        return Path(self.checkpoint).is_dir()
 
 
 def dcp_save(state_dict: dict, path: str, process_group: Any = None) -> None:

@@ -25,6 +25,10 @@ class EvaluationCheckpointManager:
     def _dir(self, iteration: int) -> Path:
         return self.root / f"eval_checkpoints_iter_{iteration}"
 
+    def get_eval_checkpoints_dir(self, iteration: int) -> Path:
+        """Directory that holds the mid-evaluation states of ``iteration``."""
+        return self._dir(iteration)
+
     def _file(self, iteration: int, eval_name: str) -> Path:
         safe = eval_name.replace("/", "_")
         return self._dir(iteration) / f"{safe}_rank_{self.rank}.pt"
@@ -50,8 +54,12 @@ class EvaluationCheckpointManager:
             meters.load_state_dict({group_name: state["meters"]})
         return state
 
-    def cleanup(self, exclude_iteration: int | None = None) -> None:
+    def cleanup(self, iteration: int | None = None, exclude_iteration: int | None = None) -> None:
+        """Remove the states of ``iteration``, or of every iteration except ``exclude_iteration``."""
         if not self.root.exists():
+            return
+        if iteration is not None:
+            shutil.rmtree(self._dir(iteration), ignore_errors=True)
             return
         for d in self.root.glob("eval_checkpoints_iter_*"):
             if exclude_iteration is not None and d.name == f"eval_checkpoints_iter_{exclude_iteration}":

@@ -118,6 +118,9 @@ class TrainRecipe(TrainingContextMixin, TrainingIterationMixin, TrainingInterrup
     def load_checkpoint(self, *args: Any, **kwargs: Any):
         return self.checkpoint_manager.load_checkpoint(*args, **kwargs)
 
+    def run_evaluation_if_needed(self, *args: Any, **kwargs: Any):
+        return self.evaluator.run_evaluation_if_needed(*args, **kwargs)
+
     def validate_config(self) -> None:
         """Refuse configurations that cannot train (same checks as the reference's recipe)."""
         cfg = self.cfg

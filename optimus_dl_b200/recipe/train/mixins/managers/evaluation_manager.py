@@ -48,6 +48,26 @@ class Evaluator:
     def any_due(self, iteration: int, eval_data: dict[str, Any]) -> bool:
         return any(self.should_evaluate(iteration, p) for p in eval_data.values())
 
+    def should_run_evaluation(self, iteration: int, eval_data_dict: dict[str, Any]) -> bool:
+        """Whether any dataset is due at ``iteration`` (reference name of :meth:`any_due`; ``None`` entries are skipped)."""
+        return self.any_due(iteration, {k: v for k, v in eval_data_dict.items() if v is not None})
+
+    def run_evaluation_if_needed(self, iteration: int, model: torch.nn.Module, criterion: Any, eval_data_dict: dict[str, Any],
+                                 device: Any = None, collective: Any = None, all_metrics_configs: Any = None,
+                                 training_context: dict[str, Any] | None = None) -> dict | None:
+        """Evaluate the datasets that are due at ``iteration``; ``None`` when none is
+        (argument order of optimus_dl/recipe/train/mixins/managers/evaluation_manager.py:172-181)."""
+        data = {k: v for k, v in eval_data_dict.items() if v is not None}
+        if not self.any_due(iteration, data):
+            return None
+        if all_metrics_configs is not None:
+            self.metrics_config = all_metrics_configs
+        return self.run_evaluation(model, criterion, data, iteration, collective=collective, training_context=training_context)
+
+    def cleanup_all_eval_checkpoints(self, iteration: int | None = None, exclude_iteration: int | None = None) -> None:
+        if self.eval_ckpt is not None:
+            self.eval_ckpt.cleanup(iteration=iteration, exclude_iteration=exclude_iteration)
+
     def forward_context(self, training_context: dict[str, Any] | None):
         if training_context is None:
             return contextlib.nullcontext()

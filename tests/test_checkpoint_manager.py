@@ -173,3 +173,25 @@ def test_model_can_be_rebuilt_from_the_checkpoint_alone(tmp_path):
     other = build_model(MODEL)
     CheckpointManager().load_model_state_dict(other, str(plain))
     assert torch.equal(other.lm_head.weight, model.lm_head.weight)
+
+
+def test_checkpoint_path_helpers_and_eval_state_cleanup(tmp_path):
+    from optimus_dl_b200.checkpoint.eval_checkpoint_manager import EvaluationCheckpointManager
+
+    mgr = CheckpointManager(output_path=str(tmp_path))
+    model, opt, sched = _setup()
+    _save(mgr, 4, model, opt, sched)
+    cp = mgr.get_checkpoint(tmp_path / "metadata_000000004.pt")
+    assert cp.is_dcp_checkpoint() and cp.per_rank_metadata(0) == str(tmp_path / "per_rank_metadata_0_000000004.pt")
+    assert os.path.exists(cp.per_rank_metadata(0)) and cp.per_rank_metadata(3).endswith("per_rank_metadata_3_000000004.pt")
+    ev = EvaluationCheckpointManager(str(tmp_path), rank=0)
+    for it in (10, 20, 30):
+        ev.save_iteration_state(it, "tiny", "eval/tiny", {"pos": it}, processed=2)
+    assert ev.get_eval_checkpoints_dir(20).name == "eval_checkpoints_iter_20" and ev.get_eval_checkpoints_dir(20).is_dir()
+    assert ev.load_iteration_state(20, "tiny", "eval/tiny")["dataloader"] == {"pos": 20}
+    ev.cleanup(iteration=10)
+    assert not ev.get_eval_checkpoints_dir(10).exists() and ev.get_eval_checkpoints_dir(20).exists()
+    ev.cleanup(exclude_iteration=30)
+    assert not ev.get_eval_checkpoints_dir(20).exists() and ev.get_eval_checkpoints_dir(30).exists()
+    ev.cleanup()
+    assert not ev.get_eval_checkpoints_dir(30).exists()
