@@ -128,3 +128,47 @@ def test_soap_descends_and_merges_dims():
     q = opt.state[w]["Q"]
     assert torch.allclose(q[0].t() @ q[0], torch.eye(20), atol=1e-4)
     assert opt.state[b]["GG"] == [None]
+
+
+# ---------------------------------------------------------------------- adamw factory and the optimizer builder
+def test_adamw_factory_accepts_named_groups_and_matches_torch_on_cpu():
+    from optimus_dl_b200.models import build_model
+    from optimus_dl_b200.optim import build_optimizer
+
+    torch.manual_seed(0)
+    cfg = dict(_name="llama2", n_layer=1, n_head=2, n_kv_head=1, n_embd=32, vocab_size=53, sequence_length=16, multiple_of=8)
+    a, b = build_model(cfg), build_model(cfg)
+    b.load_state_dict(a.state_dict())
+    groups = a.make_parameter_groups()
+    assert all(isinstance(p, tuple) and isinstance(p[0], str) for g in groups for p in g["params"])   # named parameters
+    decay = {n for n, _ in groups[0]["params"]}
+    assert "transformer.h.0.attn.wq.weight" in decay and not any("ln_" in n for n in decay)
+    opt = build_optimizer({"_name": "adamw", "lr": 1e-2, "betas": [0.9, 0.95], "weight_decay": 0.1}, params=groups)
+    wd = sorted(g["weight_decay"] for g in opt.param_groups)
+    assert wd == [0.0, 0.1] and all(g["lr"] == 1e-2 and tuple(g["betas"]) == (0.9, 0.95) for g in opt.param_groups)
+    names = dict(b.named_parameters())
+    ref = torch.optim.AdamW([{"params": [names[n] for n, _ in g["params"]], "weight_decay": g.get("weight_decay", 0.1)}
+                             for g in b.make_parameter_groups()], lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1)
+    for step in range(3):
+        x = torch.randint(0, 53, (2, 8), generator=torch.Generator().manual_seed(step))
+        for model, o in ((a, opt), (b, ref)):
+            o.zero_grad()
+            model(x)["logits"].float().logsumexp(-1).mean().backward()
+            o.step()
+    for (n, p), q in zip(a.named_parameters(), b.parameters()):
+        assert torch.allclose(p, q, atol=1e-6), n
+    with pytest.raises(Exception):
+        build_optimizer({"_name": "adamw", "learning_rate": 1.0}, params=groups)      # strict config: unknown key
+
+
+def test_optimizer_builder_counts_parameters_and_passes_the_clip_value():
+    from optimus_dl_b200.core import conf
+    from optimus_dl_b200.metrics import base as mb
+    from optimus_dl_b200.recipe.train.builders.optimizer_builder import OptimizerBuilder
+
+    lin = torch.nn.Linear(4, 3)
+    cfg = conf.create({"optimizer": {"_name": "adamw", "lr": 0.5}, "clip_grad_norm": 2.0})
+    with mb.meters_group("init", log_freq=1):
+        opt = OptimizerBuilder(optimization_config=cfg).build_optimizer(list(lin.named_parameters()))
+        assert mb.compute_meters("init")["optimized_params"] == 15
+    assert opt.param_groups[0]["lr"] == 0.5 and len(opt.param_groups[0]["params"]) == 2
