@@ -91,6 +91,11 @@ class PipelineProfiler:
         return "\n".join(lines)
 
 
+    def print_report(self) -> None:
+        """Log the report (the reference's entry point for the periodic summary)."""
+        logger.info("%s", self.report())
+
+
 class PipelineTracer:
     """Prints the tree of nodes of a pipeline (debug aid)."""
 
@@ -143,3 +148,6 @@ def maybe_profile(node: BaseNode, name: str) -> BaseNode:
     if prof is None or isinstance(node, ProfilingProxyNode):
         return node
     return ProfilingProxyNode(node, name, prof)
+
+
+get_active_profiler = current_profiler   # the reference's name

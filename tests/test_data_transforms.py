@@ -222,3 +222,51 @@ def test_reference_spellings_of_transform_and_dataset_options(tmp_path, caplog):
     flat.reset()
     first = next(flat)
     assert np.asarray(first["input_ids"])[0, 0] == 0 and np.asarray(first["input_ids"]).shape[0] == 2
+
+
+def test_pipeline_profiler_attributes_time_to_the_slow_stage():
+    import time
+
+    from optimus_dl_b200.data import build_data_pipeline
+    from optimus_dl_b200.data.profiling import PipelineProfiler, ProfilingProxyNode, get_active_profiler, scope_profiler
+
+    class _Slow(tn.BaseNode):
+        def __init__(self, node, delay):
+            super().__init__()
+            self.node, self.delay = node, delay
+
+        def reset(self, initial_state=None):
+            super().reset(initial_state)
+            self.node.reset(initial_state)
+
+        def get_state(self):
+            return self.node.state_dict()
+
+        def next(self):
+            item = next(self.node)
+            time.sleep(self.delay)
+            return item
+
+    prof = PipelineProfiler("t", report_freq=1000)
+    assert get_active_profiler() is None
+    with scope_profiler(prof):
+        assert get_active_profiler() is prof
+    src = ProfilingProxyNode(_Range(5), "source", prof)
+    slow = ProfilingProxyNode(_Slow(src, 0.01), "slow_stage", prof)
+    top = ProfilingProxyNode(_Slow(slow, 0.0), "top", prof)
+    top.reset()
+    assert len(_drain(top)) == 5
+    by_name = {s.name: s for s in prof.stats.values()}
+    assert by_name["slow_stage"].calls >= 5 and by_name["top"].total >= by_name["slow_stage"].total >= by_name["source"].total
+    assert by_name["slow_stage"].self_time > 5 * 0.008 and by_name["top"].self_time < by_name["slow_stage"].self_time
+    report = prof.report()
+    assert "bottleneck: slow_stage" in report and "source" in report
+    state = top.state_dict()
+    top.reset(state)                                    # the proxies are transparent for state
+    # the builder attaches a profiler when the config asks for one
+    cfg = {"source": {"_name": "synthetic_tokens", "vocab_size": 11, "length": 5, "num_documents": 8},
+           "transform": {"_name": "basic_batcher", "batch_size": 2, "pad_token_id": 0}, "profile": True, "report_freq": 2}
+    pipe = build_data_pipeline(cfg, profile_name="train")
+    loader = pipe.dataloader if hasattr(pipe, "dataloader") else pipe
+    it = iter(loader)
+    assert np.asarray(next(it)["input_ids"]).shape[0] == 2
