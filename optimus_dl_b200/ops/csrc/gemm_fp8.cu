@@ -1,4 +1,12 @@
-// Block-scaled e4m3 GEMM for sm_100a and the quantisers that feed it.
+// e4m3 GEMMs for sm_100a (block-scaled and per-tensor-scaled), their quantisers, and the tensor-parallel forms that
+// fuse the GEMM with its collective.  Contents:
+//   gemm_fp8_kernel<PER_TENSOR>      the GEMM itself (description below; PER_TENSOR accumulates all of K in TMEM)
+//   gemm_fp8_ag_kernel               quantise + e4m3 all-gather (peer stores, flags) + GEMM in one launch
+//   gemm_fp8_rs_kernel               GEMM whose epilogue sends bf16 partial tiles to the owner rank (reduce-scatter)
+//   quant_rowwise / quant_block      1 x 128 and 128 x 128 block quantisers
+//   amax_scale / quant_tensor / quant_tensor_t / delayed_update   per-tensor scaling (current and delayed)
+//
+// Block-scaled product:
 //
 //   C[M,N] (bf16) = sum over 128-wide k-blocks kb of
 //                   sa[kb][m] * sb[n / 128][kb] * ( A8[m, kb] . B8[n, kb] )
