@@ -187,3 +187,32 @@ def test_gpt2_small_cpu_oracle_loss_decreases():
         opt.step()
         losses.append(loss.item())
     assert abs(losses[0] - 10.9) < 0.3 and losses[-1] < losses[0]
+
+
+def test_recipe_exposes_its_builders_and_validates_the_config(tmp_path, monkeypatch):
+    """The recipe forwards build / save / load / log calls to its injected parts and refuses a run that cannot train."""
+    from optimus_dl_b200.core import compose
+    from optimus_dl_b200.core.config_utils import non_resolving_instantiate
+    from optimus_dl_b200.core.registry import build
+
+    monkeypatch.setenv("SCRATCH_HOME", str(tmp_path))
+    raw = compose.compose([str(ROOT / "configs" / "train")], "train_synthetic", ["common.exp_name=r", *TINY], apply_env=False)
+    recipe = build("train_recipe", non_resolving_instantiate(raw))
+    recipe.validate_config()
+    crit = recipe.build_criterion()
+    model = recipe.build_model(recipe.cfg.model, device=torch.device("cpu"))
+    opt = recipe.build_optimizer(model.make_parameter_groups())
+    assert type(crit).__name__ == "CrossEntropyCriterion" and sum(p.numel() for p in model.parameters()) > 0
+    assert len(opt.param_groups) >= 1
+    recipe.build_loggers()
+    recipe.setup_loggers("r")
+    recipe.log_metrics_to_loggers({"loss": 1.0}, 1, "train")
+    recipe.close_loggers()
+    logs = [p for p in Path(recipe.output_path).rglob("metrics*.jsonl")]
+    assert logs and any("final" in p.name for p in logs)
+    assert recipe.save_checkpoint_if_needed(3, save_freq=5) is False
+    assert recipe.load_checkpoint_if_exists()[0] == 1          # nothing saved yet: start at iteration 1
+    bad = compose.compose([str(ROOT / "configs" / "train")], "train_synthetic",
+                          ["common.exp_name=r2", *TINY, "optimization.acc_steps=0"], apply_env=False)
+    with pytest.raises(AssertionError, match="acc_steps"):
+        build("train_recipe", non_resolving_instantiate(bad)).validate_config()
