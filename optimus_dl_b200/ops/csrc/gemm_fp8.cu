@@ -326,39 +326,60 @@ __device__ __forceinline__ uint8_t to_e4m3(float x) {
   return (uint8_t)__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
 }
 
+// four values -> four e4m3 bytes (a in the low byte) with two paired conversions
+__device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+
+// Thread layout shared by the row-streaming quantisers: a 256-thread block covers 256 / tpr rows with tpr threads
+// each (tpr = 16 .. 256, a power of two, chosen by the host from the row width), so no index needs a division.
+struct RowTiling {
+  int tpr_log2;   // log2(threads per row)
+};
+
+static RowTiling row_tiling(int vec_per_row) {
+  int l = 4;                                  // at least one 16-lane group per row
+  while (l < 8 && (1 << (l + 1)) <= vec_per_row) ++l;
+  return RowTiling{l};
+}
+
 // 1 x 128 blocks along the contiguous dimension of x [rows, cols]: 16 threads per block, 8 elements (one
 // 16-byte load) per thread, block maximum by four shuffles inside the half-warp.
 // q [rows, cols] e4m3; scales stored [cols/128][scale_ld].
 __global__ void __launch_bounds__(256)
 quant_rowwise_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ q, long long ldq,
-                     float* __restrict__ scales, long long scale_ld, int rows, int cols) {
-  const int vec_per_row = cols / 8;
-  const long long total = (long long)rows * vec_per_row;   // a multiple of 16 (cols % 128 == 0)
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  const int lane = threadIdx.x & 31;
-  // the loop bound is uniform per warp (all 32 lanes take part in the shuffles); a half-warp past the end idles
-  for (long long base = (long long)blockIdx.x * blockDim.x + (threadIdx.x - lane); base < total; base += stride) {
-    const long long i = base + lane;
-    const bool live = i < total;
-    const int row = live ? (int)(i / vec_per_row) : 0;
-    const int v = live ? (int)(i - (long long)row * vec_per_row) : 0;
-    uint4 raw = make_uint4(0, 0, 0, 0);
-    if (live) raw = *reinterpret_cast<const uint4*>(x + (long long)row * ldx + v * 8);
-    const float2 a = unpack_bf16x2(raw.x), b = unpack_bf16x2(raw.y), c = unpack_bf16x2(raw.z), d = unpack_bf16x2(raw.w);
-    float amax = fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y))),
-                       fmaxf(fmaxf(fabsf(c.x), fabsf(c.y)), fmaxf(fabsf(d.x), fabsf(d.y))));
+                     float* __restrict__ scales, long long scale_ld, int rows, int cols, RowTiling t) {
+  const int vec_per_row = cols >> 3;          // a multiple of 16 (cols % 128 == 0)
+  const int tpr = 1 << t.tpr_log2;
+  const int tx = threadIdx.x & (tpr - 1), ty = threadIdx.x >> t.tpr_log2;
+  const int rows_per_block = 256 >> t.tpr_log2;
+  // loop bounds are uniform per warp (all 32 lanes take part in the shuffles); lanes past the end idle
+  for (int row0 = blockIdx.x * rows_per_block; row0 < rows; row0 += gridDim.x * rows_per_block) {
+    const int row = row0 + ty;
+    const bool row_live = row < rows;
+    const __nv_bfloat16* xr = x + (long long)(row_live ? row : 0) * ldx;
+    uint8_t* qr = q + (long long)(row_live ? row : 0) * ldq;
+    for (int v0 = 0; v0 < vec_per_row; v0 += tpr) {
+      const int v = v0 + tx;
+      const bool live = row_live && v < vec_per_row;
+      uint4 raw = make_uint4(0, 0, 0, 0);
+      if (live) raw = *reinterpret_cast<const uint4*>(xr + v * 8);
+      const float2 a = unpack_bf16x2(raw.x), b = unpack_bf16x2(raw.y), c = unpack_bf16x2(raw.z), d = unpack_bf16x2(raw.w);
+      float amax = fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y))),
+                         fmaxf(fmaxf(fabsf(c.x), fabsf(c.y)), fmaxf(fabsf(d.x), fabsf(d.y))));
 #pragma unroll
-    for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    const float scale = amax > 0.f ? amax / E4M3_MAX : 1.0f;
-    const float inv = 1.0f / scale;
-    uint2 packed;
-    packed.x = (uint32_t)to_e4m3(a.x * inv) | ((uint32_t)to_e4m3(a.y * inv) << 8) |
-               ((uint32_t)to_e4m3(b.x * inv) << 16) | ((uint32_t)to_e4m3(b.y * inv) << 24);
-    packed.y = (uint32_t)to_e4m3(c.x * inv) | ((uint32_t)to_e4m3(c.y * inv) << 8) |
-               ((uint32_t)to_e4m3(d.x * inv) << 16) | ((uint32_t)to_e4m3(d.y * inv) << 24);
-    if (live) {
-      *reinterpret_cast<uint2*>(q + (long long)row * ldq + v * 8) = packed;
-      if ((v & 15) == 0) scales[(long long)(v >> 4) * scale_ld + row] = scale;
+      for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      const float scale = amax > 0.f ? amax / E4M3_MAX : 1.0f;
+      const float inv = 1.0f / scale;
+      if (live) {
+        uint2 packed;
+        packed.x = e4m3x4(a.x * inv, a.y * inv, b.x * inv, b.y * inv);
+        packed.y = e4m3x4(c.x * inv, c.y * inv, d.x * inv, d.y * inv);
+        *reinterpret_cast<uint2*>(qr + v * 8) = packed;
+        if ((v & 15) == 0) scales[(long long)(v >> 4) * scale_ld + row] = scale;
+      }
     }
   }
 }
@@ -456,15 +477,16 @@ __device__ __forceinline__ float block_max_256(float v, float* s_red) {
 // ws = {running maximum (float bits), ticket}; both are zero on entry and are left zero by the last block.
 __global__ void __launch_bounds__(256)
 amax_scale_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int rows, int cols, unsigned* __restrict__ ws,
-                  float* __restrict__ scale_out, float margin_mul) {
+                  float* __restrict__ scale_out, float margin_mul, RowTiling t) {
   __shared__ float s_red[8];
-  const int vec_per_row = cols / 8;
-  const long long total = (long long)rows * vec_per_row;
+  const int vec_per_row = cols >> 3;
+  const int tpr = 1 << t.tpr_log2;
+  const int tx = threadIdx.x & (tpr - 1), ty = threadIdx.x >> t.tpr_log2;
+  const int rows_per_block = 256 >> t.tpr_log2;
   float m = 0.f;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int row = (int)(i / vec_per_row);
-    const int v = (int)(i - (long long)row * vec_per_row);
-    m = fmaxf(m, amax8(*reinterpret_cast<const uint4*>(x + (long long)row * ldx + v * 8)));
+  for (int row = blockIdx.x * rows_per_block + ty; row < rows; row += gridDim.x * rows_per_block) {
+    const __nv_bfloat16* xr = x + (long long)row * ldx;
+    for (int v = tx; v < vec_per_row; v += tpr) m = fmaxf(m, amax8(*reinterpret_cast<const uint4*>(xr + v * 8)));
   }
   m = block_max_256(m, s_red);
   if (threadIdx.x == 0) {
@@ -484,24 +506,27 @@ amax_scale_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int rows, 
 // (float bits, atomic maximum) for the delayed-scaling history.
 __global__ void __launch_bounds__(256)
 quant_tensor_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ q, long long ldq,
-                    const float* __restrict__ scale, unsigned* __restrict__ amax_rec, int rows, int cols) {
+                    const float* __restrict__ scale, unsigned* __restrict__ amax_rec, int rows, int cols,
+                    RowTiling t) {
   __shared__ float s_red[8];
-  const int vec_per_row = cols / 8;
-  const long long total = (long long)rows * vec_per_row;
+  const int vec_per_row = cols >> 3;
+  const int tpr = 1 << t.tpr_log2;
+  const int tx = threadIdx.x & (tpr - 1), ty = threadIdx.x >> t.tpr_log2;
+  const int rows_per_block = 256 >> t.tpr_log2;
   const float inv = 1.0f / *scale;
   float m = 0.f;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int row = (int)(i / vec_per_row);
-    const int v = (int)(i - (long long)row * vec_per_row);
-    const uint4 raw = *reinterpret_cast<const uint4*>(x + (long long)row * ldx + v * 8);
-    if (amax_rec) m = fmaxf(m, amax8(raw));
-    const float2 a = unpack_bf16x2(raw.x), b = unpack_bf16x2(raw.y), c = unpack_bf16x2(raw.z), d = unpack_bf16x2(raw.w);
-    uint2 packed;
-    packed.x = (uint32_t)to_e4m3(a.x * inv) | ((uint32_t)to_e4m3(a.y * inv) << 8) |
-               ((uint32_t)to_e4m3(b.x * inv) << 16) | ((uint32_t)to_e4m3(b.y * inv) << 24);
-    packed.y = (uint32_t)to_e4m3(c.x * inv) | ((uint32_t)to_e4m3(c.y * inv) << 8) |
-               ((uint32_t)to_e4m3(d.x * inv) << 16) | ((uint32_t)to_e4m3(d.y * inv) << 24);
-    *reinterpret_cast<uint2*>(q + (long long)row * ldq + v * 8) = packed;
+  for (int row = blockIdx.x * rows_per_block + ty; row < rows; row += gridDim.x * rows_per_block) {
+    const __nv_bfloat16* xr = x + (long long)row * ldx;
+    uint8_t* qr = q + (long long)row * ldq;
+    for (int v = tx; v < vec_per_row; v += tpr) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(xr + v * 8);
+      if (amax_rec) m = fmaxf(m, amax8(raw));
+      const float2 a = unpack_bf16x2(raw.x), b = unpack_bf16x2(raw.y), c = unpack_bf16x2(raw.z), d = unpack_bf16x2(raw.w);
+      uint2 packed;
+      packed.x = e4m3x4(a.x * inv, a.y * inv, b.x * inv, b.y * inv);
+      packed.y = e4m3x4(c.x * inv, c.y * inv, d.x * inv, d.y * inv);
+      *reinterpret_cast<uint2*>(qr + v * 8) = packed;
+    }
   }
   if (amax_rec) {
     m = block_max_256(m, s_red);
@@ -514,11 +539,6 @@ quant_tensor_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t*
 // (four 16-byte loads), stores its four 8-byte rows of q, transposes the patch in registers (byte permutes)
 // into eight 32-bit words (4 rows of one column each) and parks them in shared memory [col][row / 4]; after
 // both passes every qt row of the tile leaves as one 128-byte segment.  rows % 16 == 0, cols % 8 == 0.
-__device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
-  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
-  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
-  return lo | (hi << 16);
-}
 
 constexpr int QT_PITCH = 33;   // words per column row of the staging tile (32 + 1: column neighbours shift one bank)
 
@@ -901,8 +921,9 @@ extern "C" int ob_gemm_fp8_rs(const void* A8, long long lda, const void* sa, lon
   return (int)cudaGetLastError();
 }
 
-static int quant_grid(long long vecs) {
-  long long blocks = (vecs + 255) / 256;
+static int quant_grid(int rows, const RowTiling& t) {
+  const int rows_per_block = 256 >> t.tpr_log2;
+  long long blocks = ((long long)rows + rows_per_block - 1) / rows_per_block;
   if (blocks > 148 * 8) blocks = 148 * 8;
   return (int)blocks;
 }
@@ -912,8 +933,9 @@ extern "C" int ob_fp8_amax_scale(const void* x, long long ldx, int rows, int col
                                  float margin_mul, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return -1;
   if (cols % 8 != 0 || ldx % 8 != 0) return -1;
-  amax_scale_kernel<<<quant_grid((long long)rows * (cols / 8)), 256, 0, stream>>>(
-      (const __nv_bfloat16*)x, ldx, rows, cols, (unsigned*)ws, (float*)scale_out, margin_mul);
+  const RowTiling t = row_tiling(cols / 8);
+  amax_scale_kernel<<<quant_grid(rows, t), 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, rows, cols, (unsigned*)ws,
+                                                             (float*)scale_out, margin_mul, t);
   return (int)cudaGetLastError();
 }
 
@@ -922,8 +944,9 @@ extern "C" int ob_quant_fp8_tensor(const void* x, long long ldx, void* q, long l
                                    void* amax_rec, int rows, int cols, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return 0;
   if (cols % 8 != 0 || ldx % 8 != 0 || ldq % 8 != 0) return -1;
-  quant_tensor_kernel<<<quant_grid((long long)rows * (cols / 8)), 256, 0, stream>>>(
-      (const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq, (const float*)scale, (unsigned*)amax_rec, rows, cols);
+  const RowTiling t = row_tiling(cols / 8);
+  quant_tensor_kernel<<<quant_grid(rows, t), 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq,
+                                                               (const float*)scale, (unsigned*)amax_rec, rows, cols, t);
   return (int)cudaGetLastError();
 }
 
@@ -952,11 +975,12 @@ extern "C" int ob_quant_fp8_rowwise(const void* x, long long ldx, void* q, long 
                                     long long scale_ld, int rows, int cols, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return 0;
   if (cols % 128 != 0 || ldx % 8 != 0 || ldq % 8 != 0) return -1;
-  const long long vecs = (long long)rows * (cols / 8);
-  long long blocks = (vecs + 255) / 256;
+  const RowTiling t = row_tiling(cols / 8);
+  const int rows_per_block = 256 >> t.tpr_log2;
+  long long blocks = ((long long)rows + rows_per_block - 1) / rows_per_block;
   if (blocks > 148 * 16) blocks = 148 * 16;
   quant_rowwise_kernel<<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq, (float*)scales,
-                                                        scale_ld, rows, cols);
+                                                        scale_ld, rows, cols, t);
   return (int)cudaGetLastError();
 }
 
