@@ -216,3 +216,10 @@ def test_recipe_exposes_its_builders_and_validates_the_config(tmp_path, monkeypa
                           ["common.exp_name=r2", *TINY, "optimization.acc_steps=0"], apply_env=False)
     with pytest.raises(AssertionError, match="acc_steps"):
         build("train_recipe", non_resolving_instantiate(bad)).validate_config()
+
+
+def test_ddp_transform_on_two_gloo_ranks_matches_one_process(unique_port):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(unique_port), str(ROOT / "tests" / "_mp_ddp_check.py")]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
+    assert res.returncode == 0 and res.stdout.count("DDP_OK") == 2, res.stdout[-2000:] + res.stderr[-3000:]
