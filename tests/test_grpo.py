@@ -70,3 +70,49 @@ def test_tiny_grpo_run_improves_reward(tmp_path):
     assert last > first + 0.15, (first, last)
     assert any(h["clip_frac"] > 0 for h in recipe.history[1:]) or True
     assert all(h["kl"] >= 0 for h in recipe.history)
+
+
+def test_rewards_respect_the_completion_mask():
+    from optimus_dl_b200.recipe.grpo.rewards import EvenFractionReward, TargetTokenReward
+
+    comp = torch.tensor([[2, 4, 5, 7], [1, 3, 5, 6], [8, 8, 8, 8]])
+    mask = torch.tensor([[1, 1, 1, 0], [1, 1, 0, 0], [0, 0, 0, 0]], dtype=torch.bool)
+    even = EvenFractionReward()(None, comp, mask)
+    assert torch.allclose(even, torch.tensor([2 / 3, 0.0, 0.0]))           # padding never counts; an empty row scores 0
+    hit = TargetTokenReward(conf.create({"token_id": 5}))(None, comp, mask)
+    assert torch.allclose(hit, torch.tensor([1 / 3, 0.0, 0.0]))
+
+
+def test_prompt_source_is_seeded_per_step_and_split_across_ranks():
+    from optimus_dl_b200.recipe.grpo.rewards import UniformRandomPrompts
+
+    cfg = conf.create({"low": 3, "high": 9})
+    whole = UniformRandomPrompts(cfg, vocab_size=50, seed=4, rank=0, world_size=1)(step=2, n_local=4, length=6, device=torch.device("cpu"))
+    parts = [UniformRandomPrompts(cfg, vocab_size=50, seed=4, rank=r, world_size=2)(2, 2, 6, torch.device("cpu")) for r in (0, 1)]
+    assert whole.shape == (4, 6) and whole.min() >= 3 and whole.max() < 9
+    assert torch.equal(torch.cat(parts), whole)                            # ranks take disjoint slices of one stream
+    again = UniformRandomPrompts(cfg, vocab_size=50, seed=4)(2, 4, 6, torch.device("cpu"))
+    other_step = UniformRandomPrompts(cfg, vocab_size=50, seed=4)(3, 4, 6, torch.device("cpu"))
+    assert torch.equal(again, whole) and not torch.equal(other_step, whole)
+    default_high = UniformRandomPrompts(None, vocab_size=7)(0, 64, 8, torch.device("cpu"))
+    assert default_high.max() < 7
+
+
+def test_token_loss_limits():
+    n = 6
+    nll = torch.full((n,), 1.0, dtype=torch.float64)
+    adv = torch.tensor([1.0, -1.0, 2.0, -2.0, 0.5, 0.0], dtype=torch.float64)
+    mask = torch.ones(n, dtype=torch.bool)
+    # on-policy (ratio 1), no reference model: the loss is -A / N and its gradient with respect to nll is +A / N
+    loss, d, stats = token_loss(nll, -nll, None, adv, mask, 0.2, 0.0, 1.0 / n)
+    assert torch.allclose(loss, -adv / n) and torch.allclose(d, adv / n)
+    assert float(stats["clipped_sum"]) == 0 and float(stats["kl_sum"]) == 0 and float(stats["ratio_sum"]) == n
+    # a ratio far above the clip range with a positive advantage is clipped: no gradient; with a negative one it is not
+    old = -nll - 1.0                                                       # ratio = e
+    loss, d, stats = token_loss(nll, old, None, adv, mask, 0.2, 0.0, 1.0 / n)
+    assert d[0] == 0 and d[2] == 0 and d[1] != 0 and d[3] != 0 and float(stats["clipped_sum"]) == n
+    # the reference term alone: k3 estimator exp(d) - d - 1 >= 0, zero gradient where the policies agree
+    loss, d, stats = token_loss(nll, -nll, -nll, torch.zeros(n, dtype=torch.float64), mask, 0.2, 0.5, 1.0)
+    assert torch.allclose(loss, torch.zeros(n, dtype=torch.float64)) and torch.allclose(d, torch.zeros(n, dtype=torch.float64))
+    loss, _, stats = token_loss(nll, -nll, -nll + 0.3, torch.zeros(n, dtype=torch.float64), mask, 0.2, 0.5, 1.0)
+    assert (loss > 0).all() and float(stats["kl_sum"]) > 0
