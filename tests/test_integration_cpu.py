@@ -223,3 +223,20 @@ def test_ddp_transform_on_two_gloo_ranks_matches_one_process(unique_port):
            "--master-port", str(unique_port), str(ROOT / "tests" / "_mp_ddp_check.py")]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
     assert res.returncode == 0 and res.stdout.count("DDP_OK") == 2, res.stdout[-2000:] + res.stderr[-3000:]
+
+
+def test_bench_reference_arm_reports_unavailable_and_exits_zero():
+    res = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "3"],
+                         capture_output=True, text=True, timeout=120)
+    assert res.returncode == 0, res.stderr[-2000:]
+    line = json.loads(res.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and isinstance(line["unavailable"], str) and line["unavailable"]
+
+
+def test_graft_entry_exposes_build_and_smoke():
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("graft_entry", ROOT / "__graft_entry__.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    assert callable(mod.build) and callable(mod.smoke)
