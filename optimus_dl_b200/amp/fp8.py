@@ -120,7 +120,8 @@ class FP8Recipe:
             from ..ops.fp8 import DelayedScaling
 
             self.delayed_state = DelayedScaling(history=int(options.get("amax_history_len", 16) or 16),
-                                                algo=str(options.get("amax_compute_algo", "max") or "max"))
+                                                algo=str(options.get("amax_compute_algo", "max") or "max"),
+                                                reduce_amax=bool(options.get("reduce_amax", True)))
 
     @contextlib.contextmanager
     def autocast(self, enabled: bool = True):
@@ -163,7 +164,8 @@ def create_fp8_recipe(cfg: Any = None, format: Any = None, **kwargs: Any) -> FP8
     if rec == Fp8RecipeType.MXFP8:
         logger.info("fp8 recipe mxfp8 is served by the block-scaled (1x128 / 128x128) e4m3 implementation")
     return FP8Recipe(fmt, rec, margin=cfg.get("margin", 0), amax_history_len=cfg.get("amax_history_len", 1024),
-                     amax_compute_algo=cfg.get("amax_compute_algo", "max"), wgrad=bool(cfg.get("wgrad", True)))
+                     amax_compute_algo=cfg.get("amax_compute_algo", "max"), wgrad=bool(cfg.get("wgrad", True)),
+                     reduce_amax=bool(cfg.get("reduce_amax", True)))
 
 
 @contextlib.contextmanager

@@ -21,6 +21,8 @@ weight and its transpose are cached per parameter version, i.e. re-made once per
 
 from __future__ import annotations
 
+from typing import Any
+
 import torch
 
 from . import _lib, gemm
@@ -248,6 +250,19 @@ def gemm_fp8_tensor(a8: torch.Tensor, sa: torch.Tensor, b8: torch.Tensor, sb: to
     return out
 
 
+def reduce_recorded_maxima(state: torch.Tensor, n_rows: int, group: Any = None) -> None:
+    """Maximum over the ranks of ``group`` (default: all ranks) of the recorded ``max|x|`` column of the first
+    ``n_rows`` state rows, in place: every rank then derives the same scales (the reference's ``reduce_amax``).
+    Every rank must call it with the same ``n_rows``; a no-op without an initialised multi-rank process group."""
+    import torch.distributed as dist
+
+    if n_rows <= 0 or not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return
+    col = state[:n_rows, 1].contiguous()       # non-negative floats: their maximum is the maximum of the bit patterns
+    dist.all_reduce(col, op=dist.ReduceOp.MAX, group=group)
+    state[:n_rows, 1].copy_(col)
+
+
 class DelayedScaling:
     """Amax histories for the ``delayed`` recipe: one row ``[scale, recorded max, hist[H]]`` per (weight, role).
 
@@ -256,8 +271,9 @@ class DelayedScaling:
     :meth:`update` (once per backward pass) rolls every history and refreshes every scale with one launch.
     """
 
-    def __init__(self, history: int = 16, algo: str = "max", capacity: int = 1024):
+    def __init__(self, history: int = 16, algo: str = "max", capacity: int = 1024, reduce_amax: bool = True):
         self.H, self.use_max, self.capacity = max(1, int(history)), algo != "most_recent", capacity
+        self.reduce_amax = bool(reduce_amax)
         self.state: torch.Tensor | None = None
         self.rows: dict = {}
         self.pos = 0
@@ -279,9 +295,11 @@ class DelayedScaling:
             tensor_scale(x, out=st[0:1], margin_mul=margin_mul)
         return st[0:1], st[1:2]
 
-    def update(self, margin_mul: float = 1.0) -> None:
+    def update(self, margin_mul: float = 1.0, group: Any = None) -> None:
         if self.state is None or not self.rows:
             return
+        if self.reduce_amax:
+            reduce_recorded_maxima(self.state, len(self.rows), group)
         rc = _lib.lib().ob_fp8_delayed_update(_lib.ptr(self.state), len(self.rows), self.H, self.pos, float(margin_mul),
                                               int(self.use_max), _lib.stream())
         _lib.check(rc, "ob_fp8_delayed_update")

@@ -54,3 +54,43 @@ def test_reference_call_forms_of_the_fp8_helpers(monkeypatch):
     r = A.create_fp8_recipe({"enabled": True, "recipe": "blockwise", "wgrad": False})
     assert r.recipe is A.Fp8RecipeType.BLOCKWISE and r.options["wgrad"] is False
     assert A.create_fp8_recipe({"enabled": False, "recipe": "blockwise"}) is None
+
+
+_REDUCE_WORKER = '''
+import os, sys
+sys.path.insert(0, sys.argv[1])
+import torch, torch.distributed as dist
+from optimus_dl_b200.ops.fp8 import reduce_recorded_maxima
+dist.init_process_group("gloo")
+r = dist.get_rank()
+state = torch.zeros(4, 2 + 3)
+state[:, 0] = 9.0                                   # scales are not touched
+state[:3, 1] = torch.tensor([1.0, 5.0, 0.0]) if r == 0 else torch.tensor([4.0, 2.0, 0.5])
+state[3, 1] = 100.0 + r                             # beyond n_rows: left alone
+reduce_recorded_maxima(state, 3)
+assert state[:3, 1].tolist() == [4.0, 5.0, 0.5], state
+assert state[3, 1].item() == 100.0 + r and (state[:, 0] == 9.0).all()
+reduce_recorded_maxima(state, 0)
+dist.barrier()
+print("REDUCE_OK", r)
+dist.destroy_process_group()
+'''
+
+
+def test_recorded_maxima_are_reduced_over_ranks(tmp_path, unique_port):
+    import os
+    import subprocess
+    import sys
+
+    from optimus_dl_b200.ops.fp8 import reduce_recorded_maxima
+
+    lone = torch.tensor([[1.0, 3.0, 0.0]])
+    reduce_recorded_maxima(lone, 1)                     # no process group: nothing happens
+    assert lone.tolist() == [[1.0, 3.0, 0.0]]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "w.py"
+    script.write_text(_REDUCE_WORKER)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(unique_port), str(script), root]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
+    assert res.returncode == 0 and res.stdout.count("REDUCE_OK") == 2, res.stdout[-2000:] + res.stderr[-3000:]
