@@ -27,7 +27,7 @@ def test_token_loss_derivative_matches_autograd():
     loss, d, stats = token_loss(nll, old, ref, adv, mask, 0.2, 0.04, 1.0 / 100)
     (g,) = torch.autograd.grad(loss.sum(), nll)
     assert torch.allclose(g, d.to(g.dtype), atol=1e-9)
-    assert float(stats["clipped_sum"]) > 0 and float(stats["kl_sum"]) > 0
+    assert float(stats["clipped_sum"].detach()) > 0 and float(stats["kl_sum"].detach()) > 0
     assert torch.all(d[~mask] == 0)
 
 
