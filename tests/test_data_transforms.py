@@ -270,3 +270,34 @@ def test_pipeline_profiler_attributes_time_to_the_slow_stage():
     loader = pipe.dataloader if hasattr(pipe, "dataloader") else pipe
     it = iter(loader)
     assert np.asarray(next(it)["input_ids"]).shape[0] == 2
+
+
+def test_tokenized_flat_streams_files_as_one_sequence_with_equal_spans_per_rank(tmp_path):
+    a, b = tmp_path / "a.bin", tmp_path / "b.npy"
+    np.arange(0, 50, dtype=np.uint16).tofile(a)
+    np.save(b, np.arange(50, 120, dtype=np.uint16))
+    cfg = {"_name": "tokenized_flat", "files": [str(a), str(b)], "dtype": "uint16", "batch_size": 2, "seq_len": 8}
+    whole = build_dataset(cfg)
+    whole.reset()
+    batches = _drain(whole)
+    first = np.asarray(batches[0]["input_ids"])
+    assert first.shape == (2, 9)                                  # one extra token per row for the shifted targets
+    assert first[0].tolist() == list(range(0, 9)) and first[1].tolist() == list(range(8, 17))
+    flat = np.concatenate([np.asarray(x["input_ids"])[:, :8].reshape(-1) for x in batches])
+    assert flat.tolist() == list(range(len(flat))) and len(flat) >= 96   # crosses the file boundary without a seam
+    halves = []
+    for rank in (0, 1):
+        d = build_dataset(cfg, rank=rank, world_size=2)
+        d.reset()
+        halves.append([np.asarray(x["input_ids"])[:, :8].reshape(-1) for x in _drain(d)])
+    starts = [h[0][0] for h in halves]
+    assert starts == [0, 60] and len(halves[0]) == len(halves[1])   # ranks read disjoint, equally long spans
+    straight, resumed = _resume_equals_straight(lambda: build_dataset(cfg), 2, 5)
+    assert _same(straight, resumed)
+    no_shift = build_dataset({**cfg, "add_one_for_shift": False})
+    no_shift.reset()
+    assert np.asarray(next(no_shift)["input_ids"]).shape == (2, 8)
+    glob_cfg = {**cfg, "files": str(tmp_path / "*.bin")}
+    g = build_dataset(glob_cfg)
+    g.reset()
+    assert np.asarray(next(g)["input_ids"])[0, 0] == 0
