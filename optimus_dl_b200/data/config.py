@@ -13,7 +13,7 @@ class DataPipelineConfig:
     source: Any = None            # dataset registry config
     transform: Any = None         # transform registry config
     profile: bool = False
-    report_freq: int = 500
+    report_freq: int = 100
 
 
 @dataclass

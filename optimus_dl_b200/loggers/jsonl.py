@@ -36,7 +36,7 @@ class JsonlLoggerConfig(MetricsLoggerConfig):
     include_timestamp: bool = True
     include_group_in_filename: bool = True   # one file per group other than "train"
     max_file_size_mb: float | None = 200     # rotate beyond this size; None / 0 = never
-    max_rotated_files: int = 5               # numbered parts kept; <= 0 keeps all
+    max_rotated_files: int = -1              # numbered parts kept; <= 0 keeps all
     indent: int | None = None
     sort_keys: bool = False
     dump_config: bool = True                 # write the run config next to the metrics at setup
@@ -103,7 +103,7 @@ class JsonlLogger(BaseMetricsLogger):
             self._files.pop(g)
         stem, ext, parent = path.stem, path.suffix, path.parent
         numbered = lambda i: parent / f"{stem}.{i}{ext}"  # noqa: E731
-        keep = int(self.cfg.get("max_rotated_files", 5) or 0)
+        keep = int(self.cfg.get("max_rotated_files", -1) or 0)
         if keep > 0:
             numbered(keep).unlink(missing_ok=True)
             top = keep - 1

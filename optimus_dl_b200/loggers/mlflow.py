@@ -38,7 +38,7 @@ class MlflowLoggerConfig(MetricsLoggerConfig):
     backoff_factor: int = 2
     timeout: int = 15
     async_logging: bool = True
-    log_system_metrics: bool = False
+    log_system_metrics: bool = True
     log_config_artifacts: bool = True
 
 

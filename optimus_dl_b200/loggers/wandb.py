@@ -18,13 +18,13 @@ logger = logging.getLogger(__name__)
 
 @dataclass
 class WandbLoggerConfig(MetricsLoggerConfig):
-    project: str = "optimus-dl"
+    project: str | None = None
     entity: str | None = None
     group: str | None = None
     name: str | None = None
     job_type: str | None = "train"
-    mode: str | None = None            # "online" | "offline" | "disabled"
-    save_code: bool = False
+    mode: str | None = "online"        # "online" | "offline" | "disabled"
+    save_code: bool = True
     log_dir_artifact: str | None = None
     dir: str | None = None
 

@@ -25,7 +25,7 @@ logger = logging.getLogger(__name__)
 @dataclass
 class CompileTransformConfig(RegistryConfig):
     compile_kwargs: dict = field(default_factory=dict)
-    activation_memory_budget: float | None = None
+    activation_memory_budget: float | None = 1.0
     use_inductor: bool = False
     enabled: bool = True
 

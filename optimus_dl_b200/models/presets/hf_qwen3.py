@@ -16,7 +16,7 @@ logger = logging.getLogger(__name__)
 
 @dataclass
 class HFQwen3Config(Qwen3Config):
-    hf_model_name: str = "Qwen/Qwen3-0.6B"
+    hf_model_name: str = "Qwen/Qwen3-4B-Thinking-2507"
     load_weights: bool = True
 
 

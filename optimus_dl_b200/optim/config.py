@@ -26,8 +26,8 @@ class Fp8Config:
     fp8_dpa: bool = False
     fp8_mha: bool = False
     first_last_layers_bf16: bool = False
-    num_layers_at_start_in_bf16: int = 0
-    num_layers_at_end_in_bf16: int = 0
+    num_layers_at_start_in_bf16: int = 1
+    num_layers_at_end_in_bf16: int = 1
     tp_only_amax_red: bool = False
 
 
@@ -35,7 +35,7 @@ class Fp8Config:
 class AmpConfig:
     enabled: bool = False
     dtype: str = "bfloat16"
-    enable_scaler: Any = "${eval:'\"${.dtype}\" in (\"float16\", \"fp16\", \"half\")'}"
+    enable_scaler: Any = "${eval:'\"${.dtype}\" in (\"float16\", \"fp16\", \"half\", \"torch.float16\", \"torch.half\")'}"
     init_scale: float = 65536.0
     growth_factor: float = 2.0
     backoff_factor: float = 0.5
@@ -46,7 +46,7 @@ class AmpConfig:
 @dataclass
 class OptimizationConfig:
     optimizer: Any = "???"
-    iterations: int = "???"  # type: ignore[assignment]
+    iterations: int = 1000
     acc_steps: int = 1
     clip_grad_norm: float | None = None
     amp: AmpConfig = field(default_factory=AmpConfig)
