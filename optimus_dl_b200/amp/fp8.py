@@ -160,7 +160,7 @@ def create_fp8_recipe(cfg: Any = None, format: Any = None, **kwargs: Any) -> FP8
     if not torch.cuda.is_available():
         logger.warning("fp8 requested but no CUDA device is present; running without fp8")
         return None
-    fmt, rec = parse_fp8_format(cfg.get("format", "e4m3")), parse_fp8_recipe(cfg.get("recipe", "blockwise"))
+    fmt, rec = parse_fp8_format(cfg.get("format", "e4m3")), parse_fp8_recipe(cfg.get("recipe") or "delayed")
     if rec == Fp8RecipeType.MXFP8:
         logger.info("fp8 recipe mxfp8 is served by the block-scaled (1x128 / 128x128) e4m3 implementation")
     return FP8Recipe(fmt, rec, margin=cfg.get("margin", 0), amax_history_len=cfg.get("amax_history_len", 1024),
