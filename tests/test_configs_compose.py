@@ -36,7 +36,8 @@ def test_train_configs_compose(name):
 
 @pytest.mark.parametrize("group,name,overrides", [
     ("eval", "quick", ["common.checkpoint_path=null"]), ("metrics", "default", []), ("serve", "char_shakespeare", []),
-    ("serve", "tinyllama", []), ("prepare_data", "default", []), ("grpo", "default", [])])
+    ("serve", "tinyllama", []), ("prepare_data", "default", []), ("grpo", "default", []),
+    ("eval", "quick_pretrained", []), ("metrics", "tinystories_test", [])])
 def test_other_configs_compose(group, name, overrides):
     cfg = compose.compose([os.path.join(ROOT, group)], name, overrides)
     assert conf.is_config(cfg)
@@ -44,6 +45,15 @@ def test_other_configs_compose(group, name, overrides):
         assert cfg.tokenizer._name == "tiktoken" and cfg.processing.dtype == "uint16"
     if group == "grpo":
         assert conf.to_container(cfg, resolve=True)["grpo"]["group_size"] == 8
+    if name == "quick_pretrained":                      # inherits the task list of ``quick`` and names a hub model
+        plain = conf.to_container(cfg, resolve=True)
+        assert plain["lm_eval"]["tasks"] == ["hellaswag", "arc_easy"] and plain["common"]["checkpoint_path"] is None
+        assert plain["common"]["tokenizer"]["name"] == plain["common"]["model"]["hf_model_name"]
+    if name == "tinystories_test":
+        plain = conf.to_container(cfg, resolve=True)
+        assert [m["_name"] for m in plain["metrics"]["tinystories"]] == ["accuracy", "perplexity", "loss"]
+        assert plain["data"]["eval_datasets"]["tinystories"]["transform"]["transforms"][2]["batch_size"] == 4
+        assert plain["loggers"][0]["output_dir"].startswith(plain["common"]["output_path"])
 
 
 def test_transformer_engine_variants_parse():
