@@ -370,7 +370,40 @@ class ListNode(Node, MutableSequence):
 _SIMPLE = re.compile(r"^\$\{([^${}]+)\}$")
 
 
+def _find_matching_quoted(s: str, start: int) -> int:
+    """Index of the ``}`` that closes the ``${`` at ``start``, reading quoted text inside an interpolation as text:
+    a ``}`` or ``{`` between quotes closes or opens nothing, while ``${...}`` between quotes is still an interpolation.
+    Returns -1 when the quotes do not pair up (an apostrophe in an unquoted argument, say)."""
+    ctx: list[str] = []                    # "$" for an open interpolation, else the quote character that is open
+    i = start
+    while i < len(s):
+        if s.startswith("${", i):
+            ctx.append("$")
+            i += 2
+            continue
+        c = s[i]
+        top = ctx[-1] if ctx else ""
+        if top == "$":
+            if c == "}":
+                ctx.pop()
+                if not ctx:
+                    return i
+            elif c in "\"'":
+                ctx.append(c)
+        elif top:
+            if c == "\\" and i + 1 < len(s):
+                i += 2
+                continue
+            if c == top:
+                ctx.pop()
+        i += 1
+    return -1
+
+
 def _find_matching(s: str, start: int) -> int:
+    j = _find_matching_quoted(s, start)
+    if j >= 0:
+        return j
     depth = 0
     i = start
     while i < len(s):

@@ -107,7 +107,8 @@ def non_resolving_instantiate(config: Any, lazy: bool = True) -> Any:
     cfg = conf.create(config) if not conf.is_config(config) else conf.create(config)
     if isinstance(cfg, DictNode) and "_target_" in cfg._data:
         _convert(cfg)
-        return LazyTarget(cfg).get()
+        built = LazyTarget(cfg).get()
+        return conf.to_container(built, resolve=True) if conf.is_config(built) else built   # a plain dict / list at the root
     _convert(cfg)
     if not lazy:
         _force(cfg)

@@ -1,3 +1,6 @@
+import pytest
+
+
 
 
 def test_nvtx_range_is_a_noop_without_cuda(monkeypatch):
@@ -21,8 +24,9 @@ def test_instantiate_helpers():
     assert rep[1] == {"k": [1]} and len(rep) == 3            # deep copies, not aliases
     assert I.concat_lists([1], None, (2, 3), []) == [1, 2, 3]
     assert I.get_item({"a": 5}, "a") == 5 and I.get_item([7, 8], 1) == 8
-    assert I.get_item({"a": 5}, "b", "dflt") == "dflt" and I.get_item([1], 4) is None
-    assert I.get_item(complex(1, 2), "imag") == 2.0          # attribute access as a fallback
+    assert I.get_item({"a": 5}, "b", "dflt") == "dflt" and I.get_item("a", {"a": 5}) == 5
+    with pytest.raises(KeyError):
+        I.get_item([1], 4)                                   # no default: a missing key is an error
     assert I.compose(lambda x: x + 1, lambda x: x * 10)(2) == 30 and I.compose()(9) == 9
 
 

@@ -101,10 +101,57 @@ def test_to_container_keeps_definitions_unresolved_and_resolves_on_request():
 
 
 def test_helpers_are_usable_as_targets():
-    c = nri({"sizes": {"_target_": "optimus_dl_b200.core.instantiate.repeat", "value": 64, "times": 3},
+    c = nri({"sizes": {"_target_": "optimus_dl_b200.core.instantiate.repeat", "item": 64, "times": 3},
              "all": {"_target_": "optimus_dl_b200.core.instantiate.concat_lists", "_args_": ["${sizes}", [1]]},
-             "pick": {"_target_": "optimus_dl_b200.core.instantiate.cond", "condition": "${flag}", "if_true": "yes", "if_false": "no"},
+             "pick": {"_target_": "optimus_dl_b200.core.instantiate.cond", "condition": "${flag}", "true_val": "yes", "false_val": "no"},
              "flag": False})
     assert c.sizes == [64, 64, 64] and c["all"] == [64, 64, 64, 1] and c.pick == "no"
     c.flag = True
     assert c.pick == "yes"
+
+
+def test_helper_signatures_and_semantics():
+    """Call forms of optimus_dl/core/instantiate.py:19-175."""
+    from optimus_dl_b200.core.instantiate import compose, concat_lists, cond, get_item, merge_dicts, repeat
+
+    merged = merge_dicts({"a": 1, "b": {"c": 2}}, {"b": {"d": 3}, "e": 4}, conf.create({"a": 10, "f": 5}))
+    assert merged == {"a": 10, "b": {"c": 2, "d": 3}, "e": 4, "f": 5}                 # deep merge, later arguments win
+    assert cond(True, "foo", "bar") == "foo" and cond(False, "foo", "bar") == "bar" and cond(True, {"a": 1}, [1, 2]) == {"a": 1}
+    assert cond(False, if_true=1, if_false=2) == 2
+    base = {"_target_": "module", "layer": 1}
+    copies = repeat(3, base)
+    copies[0]["layer"] = 2
+    assert len(copies) == 3 and copies[1] == base and copies[2]["layer"] == 1          # independent deep copies
+    assert repeat(value=7, times=2) == [7, 7] and repeat([1], 2) == [[1], [1]]
+    assert concat_lists([1, 2, 3], conf.create([4, 5]), [6]) == [1, 2, 3, 4, 5, 6]
+    with pytest.raises(ValueError):
+        concat_lists([1], {"a": 1})
+    table = {"adam": "AdamW", "sgd": "SGD"}
+    assert get_item("adam", table) == "AdamW" and get_item("sgd", conf.create(table)) == "SGD"
+    assert get_item("rmsprop", table, default="Missing") == "Missing" and get_item(table, "adam") == "AdamW"
+    with pytest.raises(KeyError):
+        get_item("rmsprop", table)
+    pipeline = compose(lambda x: x + 1, lambda x: x * 2, str)
+    assert pipeline(3) == "8" and compose()(42) == 42
+    assert compose(lambda a, b=2: {"a": a, "b": b}, lambda d: d["b"])(5, b=10) == 10   # the first function gets every argument
+    with pytest.raises(ValueError):
+        compose()(1, 2)
+
+
+def test_braces_between_quotes_do_not_close_an_interpolation():
+    """optimus_dl/core/omegaconf_utils.py (_extract_interpolations): quoted text inside ``${...}`` is text."""
+    c = nri(conf.create({"a": "}", "obj": {"_target_": "builtins.dict", "val": "${eval:'\"}\"'}"}}))
+    assert c.obj["val"] == "}"
+    c = nri(conf.create({"x": "hello", "obj": {"_target_": "builtins.dict", "val": '${eval:\'"} " + "${x}" + " {"\'}'}}))
+    assert c.obj["val"] == "} hello {"
+    c.x = "bye"
+    assert c.obj["val"] == "} bye {"                                                    # the dependency inside the quotes is tracked
+    plain = conf.create({"h": "it's", "v": "${oc.env:OPTIMUS_NO_SUCH_VARIABLE,it's}", "w": "a ${h} b ${eval:'1+1'}"})
+    assert plain.v == "it's" and plain.w == "a it's b 2"                                # a lone apostrophe is still text
+
+
+def test_relative_reference_to_a_sibling_key_of_the_target_and_root_targets():
+    c = nri(conf.create({"a": {"b": {"c": {"_target_": "builtins.dict", "val": "${.d}", "d": 42}}}}))
+    assert c.a.b.c["val"] == 42
+    root = nri(conf.create({"_target_": "builtins.dict", "key": "value"}))
+    assert isinstance(root, dict) and not conf.is_config(root) and root == {"key": "value"}
