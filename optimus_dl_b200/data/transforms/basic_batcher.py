@@ -51,7 +51,7 @@ class BasicBatcherNode(BaseNode):
             self.node.reset()
 
     def get_state(self) -> dict[str, Any]:
-        return {"source_state": self.node.state_dict(), "_peeked_item": copy.deepcopy(self._peeked)}
+        return {"cfg": copy.deepcopy(self.cfg), "source_state": self.node.state_dict(), "_peeked_item": copy.deepcopy(self._peeked)}
 
     def _collect(self) -> list[dict]:
         items: list[dict] = []

@@ -76,7 +76,7 @@ class FlatTokensBatcherNode(BaseNode):
 
     def get_state(self) -> dict[str, Any]:
         st = {k: list(getattr(self, k)) for k in self._BUFS}
-        st.update(next_doc=self.next_doc, source_state=self.node.state_dict())
+        st.update(next_doc=self.next_doc, cfg=self.cfg, source_state=self.node.state_dict())
         return copy.deepcopy(st)
 
     def next(self) -> dict[str, Any]:

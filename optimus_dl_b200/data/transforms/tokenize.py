@@ -56,13 +56,22 @@ class TokenizeTransform(BaseTransform):
     def __init__(self, cfg, **kwargs: Any):
         super().__init__(cfg)
 
-    def build(self, source: BaseNode) -> BaseNode:
+    def _callable(self) -> _Tokenize:
         from ...core import conf
 
         tok_cfg = conf.to_container(self.cfg.tokenizer_config, resolve=True) if conf.is_config(self.cfg.tokenizer_config) \
             else self.cfg.tokenizer_config
-        fn = _Tokenize(tok_cfg, self.cfg.input_field, self.cfg.output_field, bool(self.cfg.keep_text),
-                       int(self.cfg.get("debug_samples", 0) or 0))
+        return _Tokenize(tok_cfg, self.cfg.input_field, self.cfg.output_field, bool(self.cfg.keep_text),
+                         int(self.cfg.get("debug_samples", 0) or 0))
+
+    def _map(self, item: dict) -> dict:
+        """Tokenise one sample in this process (what the mapper node calls per item)."""
+        if getattr(self, "_fn", None) is None:
+            self._fn = self._callable()
+        return self._fn(item)
+
+    def build(self, source: BaseNode) -> BaseNode:
+        fn = self._callable()
         w = self.cfg.worker_cfg
         if not w.num_workers:
             return Mapper(source, fn)

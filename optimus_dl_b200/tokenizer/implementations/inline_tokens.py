@@ -39,6 +39,7 @@ class InlineTokensTokenizer(BaseTokenizer):
         strat = config.unk_strategy
         self.unk_strategy = strat if isinstance(strat, UnkStrategy) else UnkStrategy(str(strat).split(".")[-1].lower())
         self._unk = n + 2 if self.unk_strategy == UnkStrategy.UNK else None
+        self._unk_token_id = self._unk
         self._vocab = n + 2 + (1 if self._unk is not None else 0)
 
     def encode(self, text: str) -> list[int]:
@@ -49,7 +50,7 @@ class InlineTokensTokenizer(BaseTokenizer):
             if piece in self._ids:
                 ids.append(self._ids[piece])
             elif self.unk_strategy == UnkStrategy.RAISE:
-                raise ValueError(f"text {piece!r} is not covered by the vocabulary")
+                raise ValueError(f"Unknown token/characters encountered: {piece!r} is not covered by the vocabulary")
             elif self.unk_strategy == UnkStrategy.UNK:
                 ids.append(self._unk)
         if self.config.add_eos:
@@ -62,7 +63,9 @@ class InlineTokensTokenizer(BaseTokenizer):
             if 0 <= i < len(self.tokens):
                 out.append(self.tokens[i])
             elif self._unk is not None and i == self._unk:
-                out.append("<unk>")
+                out.append("<UNK>")
+            elif i not in (self._bos, self._eos):
+                raise ValueError(f"Invalid token ID: {i}")
         return "".join(out)
 
     @property

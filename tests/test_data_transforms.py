@@ -301,3 +301,33 @@ def test_tokenized_flat_streams_files_as_one_sequence_with_equal_spans_per_rank(
     g = build_dataset(glob_cfg)
     g.reset()
     assert np.asarray(next(g)["input_ids"])[0, 0] == 0
+
+
+def test_tokenize_single_item_call_and_batcher_state_carries_its_config():
+    """``TokenizeTransform._map`` (optimus_dl/modules/data/transforms/tokenize.py) and the ``cfg`` entry of the batcher
+    states (optimus_dl/modules/data/transforms/basic_batcher.py:71-79, flat_tokens_batcher.py:109-121)."""
+    from optimus_dl_b200.data.transforms.basic_batcher import BasicBatcherConfig, BasicBatcherNode
+    from optimus_dl_b200.data.transforms.flat_tokens_batcher import FlatTokensBatcherConfig, FlatTokensBatcherNode
+    from optimus_dl_b200.data.transforms.tokenize import TokenizeTransform, TokenizeTransformConfig
+    from optimus_dl_b200.tokenizer.implementations.char import CharTokenizerConfig
+
+    plain = TokenizeTransform(TokenizeTransformConfig(tokenizer_config=CharTokenizerConfig(_name="char_tokenize", add_bos=False, add_eos=False)))
+    assert plain._map({"text": "abc"})["input_ids"] == [97, 98, 99]
+    marked = TokenizeTransform(TokenizeTransformConfig(tokenizer_config=CharTokenizerConfig(_name="char_tokenize")))
+    assert marked._map({"text": "€"})["input_ids"] == [256, 226, 130, 172, 257]        # UTF-8 bytes between BOS and EOS
+
+    docs = [{"input_ids": [1]}, {"input_ids": [2]}, {"input_ids": [3]}]
+    cfg = BasicBatcherConfig(batch_size=1, pad_token_id=0)
+    node = BasicBatcherNode(tn.IterableWrapper(docs), cfg)
+    node.reset()
+    node.next()
+    state = node.get_state()
+    assert state["cfg"] == cfg and "source_state" in state
+    again = BasicBatcherNode(tn.IterableWrapper(docs), cfg)
+    again.reset(state)
+    np.testing.assert_array_equal(again.next()["input_ids"], np.array([[2]]))
+    fcfg = FlatTokensBatcherConfig(batch_size=1, seq_len=4)
+    flat = FlatTokensBatcherNode(tn.IterableWrapper([{"input_ids": np.arange(50)}]), fcfg)
+    flat.reset()
+    flat.next()
+    assert flat.get_state()["cfg"] == fcfg

@@ -192,6 +192,13 @@ def test_inline_tokens_longest_match_and_unknown_policies():
     unk = build_tokenizer({"_name": "inline_tokens_tokenizer", "tokens": vocab, "unk_strategy": "unk", "add_bos": False,
                            "add_eos": False})
     assert unk.vocab_size == 8 and unk.encode("a?b+") == [0, 7, 7, 4] or unk.encode("a?b+") == [0, 7, 4]
-    assert "<unk>" in unk.decode(unk.encode("a?+"))
+    assert "<UNK>" in unk.decode(unk.encode("a?+")) and unk._unk_token_id == 7 and tok._unk_token_id is None
+    with pytest.raises(ValueError, match="Invalid token ID: 99"):
+        tok.decode([5, 99, 6])
+    with pytest.raises(ValueError, match="Unknown token/characters encountered"):
+        tok.encode("abXYZ")
+    wide = build_tokenizer({"_name": "inline_tokens_tokenizer", "tokens": ["A", "B", "C", "AB", "BC", "word", "!"], "unk_strategy": "unk"})
+    assert wide.encode("$A$") == [7, 9, 0, 9, 8] and wide.encode("ABXYZC") == [7, 3, 9, 2, 8]   # a run of unknown text is one UNK
+    assert wide.decode([7, 3, 9, 2, 8]) == "AB<UNK>C"
     dotted = build_tokenizer({"_name": "inline_tokens_tokenizer", "tokens": [".", "*", "a"], "add_bos": False, "add_eos": False})
     assert dotted.encode("a.*") == [2, 0, 1]                          # vocabulary entries are literals, not patterns
