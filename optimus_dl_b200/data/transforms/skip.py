@@ -24,22 +24,36 @@ class SkipInterleavedConfig(RegistryConfigStrict):
 
 
 class SkipInterleavedNode(BaseNode):
-    def __init__(self, node: BaseNode, keep_every: int, offset: int):
+    """``SkipInterleavedNode(node, cfg)`` or ``SkipInterleavedNode(node, keep_every, offset)``. ``counter`` is the number
+    of source items consumed so far; the state stores it under ``counter``."""
+
+    def __init__(self, node: BaseNode, keep_every: Any, offset: int = 0):
         super().__init__()
+        self.cfg = None
+        if not isinstance(keep_every, int):
+            self.cfg = cfg = keep_every
+            if cfg.skip_count is not None:
+                keep_every, offset = int(cfg.skip_count) + 1, 0
+            else:
+                keep_every, offset = cfg.keep_every, cfg.offset
         self.node, self.keep_every, self.offset = node, max(1, int(keep_every)), int(offset)
         self.count = 0
+
+    @property
+    def counter(self) -> int:
+        return self.count
 
     def reset(self, initial_state: dict | None = None):
         super().reset(initial_state)
         if initial_state:
-            self.count = initial_state["count"]
+            self.count = initial_state["counter"] if "counter" in initial_state else initial_state["count"]
             self.node.reset(initial_state["source_state"])
         else:
             self.count = 0
             self.node.reset()
 
     def get_state(self) -> dict[str, Any]:
-        return {"count": self.count, "source_state": self.node.state_dict()}
+        return {"counter": self.count, "source_state": self.node.state_dict()}
 
     def next(self) -> Any:
         while True:
@@ -53,9 +67,7 @@ class SkipInterleavedNode(BaseNode):
 @register_transform("skip_interleaved", SkipInterleavedConfig)
 class SkipInterleaved(BaseTransform):
     def build(self, source: BaseNode) -> BaseNode:
-        if self.cfg.skip_count is not None:
-            return SkipInterleavedNode(source, int(self.cfg.skip_count) + 1, 0)
-        return SkipInterleavedNode(source, self.cfg.keep_every, self.cfg.offset)
+        return SkipInterleavedNode(source, self.cfg)
 
 
 @dataclass
@@ -69,10 +81,19 @@ class SkipRandomConfig(RegistryConfigStrict):
 
 
 class SkipRandomNode(BaseNode):
-    def __init__(self, node: BaseNode, p: float, seed: int, invert: bool):
+    """``SkipRandomNode(node, cfg, seed=...)`` or ``SkipRandomNode(node, keep_probability, seed, invert)``."""
+
+    def __init__(self, node: BaseNode, p: Any, seed: int | None = None, invert: bool = False):
         super().__init__()
-        self.node, self.p, self.seed, self.invert = node, float(p), int(seed), bool(invert)
+        self.cfg = None
         self.drop_below: float | None = None     # set when configured through ``probability``
+        if not isinstance(p, (int, float)):
+            self.cfg = cfg = p
+            p, invert = cfg.keep_probability, cfg.invert
+            seed = cfg.seed if seed is None else seed
+            if cfg.probability is not None:
+                self.drop_below = float(cfg.probability)
+        self.node, self.p, self.seed, self.invert = node, float(p), int(seed or 0), bool(invert)
         self.rng = random.Random(self.seed)
 
     def reset(self, initial_state: dict | None = None):
@@ -98,14 +119,13 @@ class SkipRandomNode(BaseNode):
 
 @register_transform("skip_random", SkipRandomConfig)
 class SkipRandom(BaseTransform):
-    def __init__(self, cfg, seed: int = 0, **kwargs: Any):
+    def __init__(self, cfg, seed: int | None = None, **kwargs: Any):
         super().__init__(cfg)
+        self.seed = seed                          # the pipeline's data seed; the config's own seed is added to it
 
     def build(self, source: BaseNode) -> BaseNode:
-        node = SkipRandomNode(source, self.cfg.keep_probability, self.cfg.seed, self.cfg.invert)
-        if self.cfg.probability is not None:
-            node.drop_below = float(self.cfg.probability)
-        return node
+        seed = int(self.cfg.seed) if self.seed is None else int(self.seed) + int(self.cfg.seed)
+        return SkipRandomNode(source, self.cfg, seed=seed)
 
 
 # the reference's class names

@@ -331,3 +331,60 @@ def test_tokenize_single_item_call_and_batcher_state_carries_its_config():
     flat.reset()
     flat.next()
     assert flat.get_state()["cfg"] == fcfg
+
+
+def _drain(node):
+    out = []
+    try:
+        while True:
+            out.append(next(node))
+    except StopIteration:
+        return out
+
+
+def test_skip_nodes_take_their_config_and_resume_from_their_counters():
+    """Call forms and state keys of optimus_dl/modules/data/transforms/skip.py (node(source, cfg), ``counter``, ``seed``)."""
+    from optimus_dl_b200.data.transforms.skip import (SkipInterleavedTransform, SkipInterleavedTransformConfig,
+                                                     SkipInterleavedTransformNode, SkipRandomTransform,
+                                                     SkipRandomTransformConfig, SkipRandomTransformNode)
+
+    src = lambda n: tn.IterableWrapper(list(range(n)))  # noqa: E731
+    one = SkipInterleavedTransformNode(src(10), SkipInterleavedTransformConfig(skip_count=1))
+    one.reset()
+    assert _drain(one) == [0, 2, 4, 6, 8]
+    two = SkipInterleavedTransformNode(src(10), SkipInterleavedTransformConfig(skip_count=2))
+    two.reset()
+    assert _drain(two) == [0, 3, 6, 9]
+    cfg = SkipInterleavedTransformConfig(skip_count=1)
+    first = SkipInterleavedTransformNode(src(10), cfg)
+    first.reset()
+    assert [next(first), next(first)] == [0, 2]
+    state = first.get_state()
+    assert state["counter"] == 3 and first.counter == 3
+    second = SkipInterleavedTransformNode(src(10), cfg)
+    second.reset(state)
+    assert second.counter == 3 and [next(second), next(second)] == [4, 6]
+    source = src(10)
+    built = SkipInterleavedTransform(cfg).build(source)
+    assert isinstance(built, SkipInterleavedTransformNode) and built.cfg == cfg
+
+    half = SkipRandomTransformConfig(probability=0.5)
+    a = SkipRandomTransformNode(src(100), half, seed=42)
+    b = SkipRandomTransformNode(src(100), half, seed=42)
+    a.reset(), b.reset()
+    kept = _drain(a)
+    assert kept == _drain(b) and 0 < len(kept) < 100
+    part = SkipRandomTransformNode(src(100), half, seed=42)
+    part.reset()
+    head = [next(part) for _ in range(10)]
+    state = part.get_state()
+    rest = _drain(part)
+    resumed = SkipRandomTransformNode(src(100), half, seed=42)
+    resumed.reset(state)
+    assert _drain(resumed) == rest and head + rest == kept
+    none = SkipRandomTransformNode(src(10), SkipRandomTransformConfig(probability=0.0), seed=42)
+    every = SkipRandomTransformNode(src(10), SkipRandomTransformConfig(probability=1.0), seed=42)
+    none.reset(), every.reset()
+    assert _drain(none) == list(range(10)) and _drain(every) == []
+    node = SkipRandomTransform(half, seed=42).build(src(10))
+    assert isinstance(node, SkipRandomTransformNode) and node.cfg == half and node.seed == 42
