@@ -53,9 +53,24 @@ class ToDeviceTransform(BaseTransform):
         super().__init__(cfg)
         dev = cfg.device if cfg.device is not None else device
         self.device = torch.device(dev) if dev is not None else torch.device("cuda" if torch.cuda.is_available() else "cpu")
+        self.properties = list(cfg.properties) if cfg.properties is not None else None
+
+    def _map(self, sample: Any) -> Any:
+        """Convert and move one sample in the calling thread. With ``properties`` set, only those keys are touched
+        (lists among them become tensors); without, every array / tensor value moves."""
+        if isinstance(sample, dict) and self.properties is not None:
+            out = dict(sample)
+            for k in self.properties:
+                if k in out:
+                    v = _to_tensor(out[k])
+                    if not isinstance(v, (torch.Tensor, dict)):
+                        v = torch.as_tensor(v)
+                    out[k] = _Mover(self.device, bool(self.cfg.non_blocking))(v)
+            return out
+        return _Mover(self.device, bool(self.cfg.non_blocking))(_to_tensor(sample))
 
     def build(self, source: BaseNode) -> BaseNode:
-        props = list(self.cfg.properties) if self.cfg.properties is not None else None
+        props = list(self.properties) if self.properties is not None else None
         if props is None:
             node: BaseNode = Mapper(source, _to_tensor)
         else:

@@ -388,3 +388,18 @@ def test_skip_nodes_take_their_config_and_resume_from_their_counters():
     assert _drain(none) == list(range(10)) and _drain(every) == []
     node = SkipRandomTransform(half, seed=42).build(src(10))
     assert isinstance(node, SkipRandomTransformNode) and node.cfg == half and node.seed == 42
+
+
+def test_to_device_single_sample_call_touches_only_the_listed_properties():
+    """``ToDeviceTransform._map`` and ``properties`` (optimus_dl/modules/data/transforms/to_device.py:21-119)."""
+    from optimus_dl_b200.data.transforms.to_device import ToDeviceTransform, ToDeviceTransformConfig
+
+    cpu = torch.device("cpu")
+    t = ToDeviceTransform(ToDeviceTransformConfig(pin_memory=False), cpu)
+    t.properties = ["input_ids"]
+    out = t._map({"input_ids": torch.tensor([1, 2, 3]), "other": "string"})
+    assert out["input_ids"].device == cpu and out["other"] == "string"
+    listed = ToDeviceTransform(ToDeviceTransformConfig(properties=["a"]), cpu)._map({"a": [1, 2, 3], "b": [4, 5, 6]})
+    assert torch.is_tensor(listed["a"]) and listed["a"].tolist() == [1, 2, 3] and listed["b"] == [4, 5, 6]
+    every = ToDeviceTransform(ToDeviceTransformConfig(), cpu)._map({"x": np.arange(3), "n": 5})
+    assert torch.is_tensor(every["x"]) and every["n"] == 5
