@@ -83,14 +83,13 @@ def build_data_pipeline(cfg: Any, profile_name: str | None = None, eval_pipeline
     if cfg is None:
         return None
     dataset = build_dataset(_get(cfg, "source"), **kwargs)
+    dataset_class = type(dataset).__name__
     dataset = LoggingDataNode(name=profile_name or repr(dataset), source=dataset)
     pipeline: Any = dataset
     profiler = None
     if _get(cfg, "profile", False):
         profiler = PipelineProfiler(name=profile_name or repr(dataset), report_freq=_get(cfg, "report_freq", 500))
-        pipeline = ProfilingProxyNode(pipeline, name=repr(dataset), profiler=profiler)
-        if _get(cfg, "transform") is None:
-            profiler.root_nodes.append(pipeline)
+        pipeline = ProfilingProxyNode(pipeline, name=dataset_class, profiler=profiler)
     with scope_profiler(profiler):
         tcfg = _get(cfg, "transform")
         if tcfg is not None:

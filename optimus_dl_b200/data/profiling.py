@@ -46,8 +46,18 @@ class NodeStats:
         self.parent_threads: set[int] = set()
 
 
+class NodeSummary:
+    """What ``_analyze_bottlenecks`` reports per node: call count, wall time inside ``next()`` and the part of it not
+    spent in upstream nodes on the same thread."""
+    __slots__ = ("name", "calls", "total_time", "compute_time", "is_async_boundary")
+
+    def __init__(self, name: str, calls: int, total_time: float, compute_time: float, is_async_boundary: bool):
+        self.name, self.calls, self.total_time, self.compute_time = name, calls, total_time, compute_time
+        self.is_async_boundary = is_async_boundary
+
+
 class PipelineProfiler:
-    def __init__(self, name: str, report_freq: int = 500):
+    def __init__(self, name: str = "pipeline", report_freq: int = 500):
         self.name, self.report_freq = name, max(1, int(report_freq))
         self.stats: dict[int, NodeStats] = {}
         self.root_nodes: list[Any] = []
@@ -73,7 +83,7 @@ class PipelineProfiler:
             else:
                 due = False
         if due:
-            logger.info("%s", self.report())
+            self.print_report()
 
     def is_async_boundary(self, st: NodeStats) -> bool:
         return bool(st.threads and st.parent_threads and not (st.threads & st.parent_threads))
@@ -92,12 +102,75 @@ class PipelineProfiler:
 
 
     def print_report(self) -> None:
-        """Log the report (the reference's entry point for the periodic summary)."""
-        logger.info("%s", self.report())
+        """Log the report (the periodic summary's entry point)."""
+        logger.info("Data Pipeline Profiling Report: %s\n%s", self.name, self.report())
+
+    def _analyze_bottlenecks(self) -> dict[str, "NodeSummary"]:
+        """Per-node summary keyed by node name (a second node of the same name gets ``#2``, ...); nodes that were
+        never called are left out."""
+        out: dict[str, NodeSummary] = {}
+        with self._lock:
+            rows = list(self.stats.values())
+        for st in rows:
+            if not st.calls:
+                continue
+            key, k = st.name, 1
+            while key in out:
+                k += 1
+                key = f"{st.name}#{k}"
+            out[key] = NodeSummary(st.name, st.calls, st.total, st.self_time, self.is_async_boundary(st))
+        return out
+
+    def pipeline_tree(self) -> str:
+        """The chain of nodes below each root, one per line: proxies by the name they were registered under (the
+        transform or dataset that built them), the nodes between them by class."""
+        lines: list[str] = []
+
+        def walk(node: Any, depth: int) -> None:
+            if depth > 64 or node is None:
+                return
+            if isinstance(node, ProfilingProxyNode):
+                lines.append("  " * depth + "[" + " > ".join([*node._enclosing, node._name]) + "]")
+                walk(node.node, depth + 1)
+                return
+            lines.append("  " * depth + type(node).__name__)
+            for attr in ("node", "source", "inner", "dataset"):
+                child = getattr(node, attr, None)
+                if isinstance(child, BaseNode):
+                    walk(child, depth + 1)
+                    return
+            for attr in ("nodes", "source_nodes", "sources"):
+                kids = getattr(node, attr, None)
+                if isinstance(kids, dict):
+                    kids = list(kids.values())
+                if isinstance(kids, (list, tuple)) and kids and all(isinstance(c, BaseNode) for c in kids):
+                    for c in kids:
+                        walk(c, depth + 1)
+                    return
+
+        for root in self.root_nodes:
+            walk(root, 0)
+        return "\n".join(lines)
+
+    def print_pipeline_tree(self) -> None:
+        logger.info("Data Pipeline Structure: %s\n%s", self.name, self.pipeline_tree())
 
 
 class PipelineTracer:
-    """Prints the tree of nodes of a pipeline (debug aid)."""
+    """``with PipelineTracer(name) as profiler:`` makes ``profiler`` the active one, so transforms built inside the
+    block proxy their nodes into it. ``describe`` prints the chain of nodes below one node (debug aid)."""
+
+    def __init__(self, name: str = "pipeline", report_freq: int = 500, profiler: "PipelineProfiler | None" = None):
+        self.profiler = profiler if profiler is not None else PipelineProfiler(name, report_freq)
+        self._token: Any = None
+
+    def __enter__(self) -> "PipelineProfiler":
+        self._token = _current_profiler.set(self.profiler)
+        return self.profiler
+
+    def __exit__(self, *exc: Any) -> None:
+        _current_profiler.reset(self._token)
+        self._token = None
 
     @staticmethod
     def describe(node: Any, depth: int = 0) -> str:
@@ -111,12 +184,28 @@ class PipelineTracer:
 
 
 class ProfilingProxyNode(BaseNode):
-    def __init__(self, node: BaseNode, name: str, profiler: PipelineProfiler):
+    def __init__(self, node: BaseNode, name: str, profiler: PipelineProfiler, is_root: bool = False):
         super().__init__()
         self.node, self.name, self.profiler = node, name, profiler
-        self._is_root = False
+        self._name, self._profiler = name, profiler
+        self._enclosing: list[str] = []
         self._creator_thread: int | None = None
         profiler.register(id(self), name)
+        self._is_root = False
+        if is_root:
+            self._is_root = True
+
+    @property
+    def _is_root(self) -> bool:
+        return self.__dict__.get("_root", False)
+
+    @_is_root.setter
+    def _is_root(self, value: bool) -> None:
+        """The root is the node whose batches are counted for ``report_freq`` and where the printed tree starts."""
+        self.__dict__["_root"] = bool(value)
+        roots = self.profiler.root_nodes
+        if value and not any(r is self for r in roots):
+            roots.append(self)
 
     def reset(self, initial_state: dict | None = None):
         super().reset(initial_state)
@@ -145,7 +234,11 @@ class ProfilingProxyNode(BaseNode):
 
 def maybe_profile(node: BaseNode, name: str) -> BaseNode:
     prof = current_profiler()
-    if prof is None or isinstance(node, ProfilingProxyNode):
+    if prof is None:
+        return node
+    if isinstance(node, ProfilingProxyNode):
+        if name != node._name:
+            node._enclosing.insert(0, name)      # a transform made of transforms: shown in the tree, timed once
         return node
     return ProfilingProxyNode(node, name, prof)
 

@@ -403,3 +403,83 @@ def test_to_device_single_sample_call_touches_only_the_listed_properties():
     assert torch.is_tensor(listed["a"]) and listed["a"].tolist() == [1, 2, 3] and listed["b"] == [4, 5, 6]
     every = ToDeviceTransform(ToDeviceTransformConfig(), cpu)._map({"x": np.arange(3), "n": 5})
     assert torch.is_tensor(every["x"]) and every["n"] == 5
+
+
+def test_profiler_tracer_scope_summaries_tree_and_periodic_report():
+    """Surface of optimus_dl/modules/data/profiling.py:16-389: the tracer scope, per-node summaries, the printed tree
+    and the report every ``report_freq`` root batches."""
+    import io
+    import logging
+    import time
+
+    from optimus_dl_b200.data import build_data_pipeline
+    from optimus_dl_b200.data.profiling import PipelineProfiler, PipelineTracer, ProfilingProxyNode, get_active_profiler
+
+    class Slow(tn.BaseNode):
+        def __init__(self, delay):
+            super().__init__()
+            self.delay, self.n = delay, 0
+
+        def next(self):
+            time.sleep(self.delay)
+            self.n += 1
+            return self.n
+
+        def reset(self, state=None):
+            super().reset(state)
+            self.n = 0
+
+    class Above(tn.BaseNode):
+        def __init__(self, inner, delay):
+            super().__init__()
+            self.inner, self.delay = inner, delay
+
+        def next(self):
+            item = next(self.inner)
+            time.sleep(self.delay)
+            return item
+
+        def reset(self, state=None):
+            super().reset(state)
+
+    assert get_active_profiler() is None
+    with PipelineTracer() as scoped:
+        assert get_active_profiler() is scoped
+    assert get_active_profiler() is None
+
+    prof = PipelineProfiler("nested")
+    child = ProfilingProxyNode(Slow(0.03), name="Child", profiler=prof)
+    assert "Child" not in prof._analyze_bottlenecks()                    # never called: not listed
+    parent = ProfilingProxyNode(Above(child, 0.06), name="Parent", profiler=prof)
+    assert next(parent) == 1
+    stats = prof._analyze_bottlenecks()
+    assert stats["Child"].calls == 1 and stats["Child"].total_time >= 0.027
+    assert stats["Parent"].total_time >= 0.08 and abs(stats["Parent"].compute_time - 0.06) < 0.03   # self time excludes the child
+
+    p1, p2 = PipelineProfiler("p1"), PipelineProfiler("p2")               # two profilers do not share counters
+    n1, n2 = ProfilingProxyNode(Slow(0), name="Node", profiler=p1), ProfilingProxyNode(Slow(0), name="Node", profiler=p2)
+    next(n1), next(n2), next(n2)
+    assert p1._analyze_bottlenecks()["Node"].calls == 1 and p2._analyze_bottlenecks()["Node"].calls == 2
+
+    stream = io.StringIO()
+    handler = logging.StreamHandler(stream)
+    log = logging.getLogger("optimus_dl_b200.data.profiling")
+    old_level = log.level
+    log.addHandler(handler), log.setLevel(logging.INFO)
+    try:
+        every2 = PipelineProfiler("freq", report_freq=2)
+        root = ProfilingProxyNode(Slow(0), name="FreqNode", profiler=every2, is_root=True)
+        next(root)
+        assert "Data Pipeline Profiling Report" not in stream.getvalue()
+        next(root)
+        assert "Data Pipeline Profiling Report: freq" in stream.getvalue() and "FreqNode" in stream.getvalue()
+        pipe = build_data_pipeline({"source": {"_name": "synthetic_tokens", "vocab_size": 11, "length": 4, "num_documents": 8},
+                                    "transform": {"_name": "compose", "transforms": [{"_name": "prefetch", "prefetch_factor": 2}]},
+                                    "profile": True, "report_freq": 10}, profile_name="tree", rank=0, world_size=1, seed=1)
+        assert isinstance(pipe.dataloader, ProfilingProxyNode)
+        pipe.dataloader._profiler.print_pipeline_tree()
+        text = stream.getvalue()
+        for word in ("Data Pipeline Structure: tree", "CompositeTransform", "Prefetcher", "SyntheticTokens"):
+            assert word in text, word
+    finally:
+        log.removeHandler(handler), log.setLevel(old_level)
