@@ -176,16 +176,20 @@ def generate_stream(model: nn.Module, input_ids: torch.Tensor, max_new_tokens: i
                     generator: torch.Generator | None = None, use_graph: bool = True) -> Iterator[torch.Tensor]:
     """Yield the new tokens ``[B]`` step by step (finished sequences yield the padding id)."""
     root = unwrap(model)
-    was_training = root.training
-    root.eval()
+    is_module = isinstance(root, nn.Module)      # any callable returning {"logits": ...} can be sampled from, uncached
+    was_training = root.training if is_module else False
+    if is_module:
+        root.eval()
     B, T0 = input_ids.shape
-    limit = getattr(root.config, "sequence_length", None) or getattr(root.config, "block_size", None) or (T0 + max_new_tokens)
+    mcfg = getattr(root, "config", None) if is_module else None
+    limit = next((int(v) for v in (getattr(mcfg, "sequence_length", None), getattr(mcfg, "block_size", None))
+                  if isinstance(v, int) and v > 0), T0 + max_new_tokens)
     pad = eos_token_id if eos_token_id is not None else 0
     finished = torch.zeros(B, dtype=torch.bool, device=input_ids.device)
     pick = lambda lg, i: dec_ops.sample(lg, temperature, top_k, top_p, greedy, seed=seed, offset=i,  # noqa: E731
                                         generator=generator)
     try:
-        cached = use_kv_cache and supports_kv_cache(root) and T0 + max_new_tokens <= limit
+        cached = use_kv_cache and is_module and supports_kv_cache(root) and T0 + max_new_tokens <= limit
         if cached:
             with DecodeSession(root, B, T0 + max_new_tokens) as sess:
                 logits = sess.prefill(input_ids)
@@ -202,7 +206,7 @@ def generate_stream(model: nn.Module, input_ids: torch.Tensor, max_new_tokens: i
             cur = input_ids
             for i in range(max_new_tokens):
                 ctx = cur[:, -limit:]
-                logits = model(ctx)["logits"][:, -1, :]
+                logits = model(input_ids=ctx)["logits"][:, -1, :]
                 nxt = pick(logits, i)
                 if eos_token_id is not None:
                     nxt = torch.where(finished, torch.full_like(nxt, pad), nxt)
@@ -212,7 +216,8 @@ def generate_stream(model: nn.Module, input_ids: torch.Tensor, max_new_tokens: i
                     break
                 cur = torch.cat([cur, nxt[:, None]], dim=1)
     finally:
-        root.train(was_training)
+        if is_module:
+            root.train(was_training)
 
 
 @torch.no_grad()

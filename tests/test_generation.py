@@ -61,3 +61,30 @@ def test_sampling_follows_distribution():
     freq = torch.bincount(s, minlength=4).float() / s.numel()
     assert torch.allclose(freq, torch.softmax(z[0], -1), atol=0.03)
     assert torch.equal(dec_ops.sample(z[:4], greedy=True), torch.full((4,), 2))
+
+
+def test_generation_source_drives_any_callable_that_returns_logits():
+    """``GenerationSource`` (optimus_dl/modules/metrics/sources/generation.py:20-177) with a stand-in model: called once
+    per new token with ``input_ids=``, greedy by default, per-sequence EOS with padding."""
+    from optimus_dl_b200.metrics.source import StandardProtocols
+    from optimus_dl_b200.metrics.sources.generation import GenerationSource, GenerationSourceConfig
+
+    calls = {"n": 0}
+
+    def successor(**kw):                                  # next token = last token + 1 (mod 20)
+        calls["n"] += 1
+        ids = kw["input_ids"]
+        logits = torch.zeros(*ids.shape, 20)
+        logits.scatter_(2, ((ids + 1) % 20)[..., None], 10.0)
+        return {"logits": logits}
+
+    out = GenerationSource(GenerationSourceConfig(max_new_tokens=5, do_sample=False))(
+        dependencies={}, model=successor, batch={"input_ids": torch.tensor([[1, 2, 3]])})[StandardProtocols.GENERATED_TOKENS]
+    assert torch.equal(out, torch.tensor([[4, 5, 6, 7, 8]])) and calls["n"] == 5
+    out = GenerationSource(GenerationSourceConfig(max_new_tokens=10, do_sample=False, eos_token_id=7))(
+        dependencies={}, model=successor, batch={"input_ids": torch.tensor([[1, 2, 3], [10, 11, 12]])})[StandardProtocols.GENERATED_TOKENS]
+    assert out.shape == (2, 10) and out[0].tolist() == [4, 5, 6, 7] + [7] * 6 and out[1, 0].item() == 13
+    noisy = lambda **kw: {"logits": torch.randn(1, kw["input_ids"].shape[1], 20)}  # noqa: E731
+    out = GenerationSource(GenerationSourceConfig(max_new_tokens=2, do_sample=True, temperature=0.8, top_k=5, top_p=0.9))(
+        dependencies={}, model=noisy, batch={"input_ids": torch.tensor([[1, 2, 3]])})[StandardProtocols.GENERATED_TOKENS]
+    assert out.shape == (1, 2)
