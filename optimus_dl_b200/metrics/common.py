@@ -41,14 +41,18 @@ class SummedMeter(BaseMeter):
 
 
 class MaxMeter(BaseMeter):
+    _EMPTY = -float("inf")
+
     def __init__(self, round: int | None = None):
-        self.round, self.value = round, None
+        self.round, self.value = round, self._EMPTY
 
     def log(self, value: float) -> None:
         self.value = value if self.value is None else max(self.value, value)
 
     def compute(self) -> float:
-        return safe_round(self.value, self.round) if self.value is not None else 0.0
+        if self.value is None or self.value == self._EMPTY:
+            return 0.0
+        return safe_round(self.value, self.round)
 
     def merge(self, other_state: dict[str, Any]) -> None:
         if other_state["value"] is not None:
@@ -56,68 +60,74 @@ class MaxMeter(BaseMeter):
 
 
 class MinMeter(MaxMeter):
+    _EMPTY = float("inf")
+
     def log(self, value: float) -> None:
         self.value = value if self.value is None else min(self.value, value)
 
 
-class FrequencyMeter(BaseMeter):
-    """Mean time between occurrences of an event, in milliseconds."""
+class _IntervalMeter(BaseMeter):
+    """Shared state of the two timing meters: ``elapsed`` nanoseconds over ``counter`` intervals; the result is the mean
+    interval in milliseconds. The wall-clock anchor is not part of the state that survives a restart."""
+
+    _ANCHOR = "start"
 
     def __init__(self, round: int | None = None):
-        self.round, self.total_ms, self.count, self._last = round, 0.0, 0, None
+        self.round, self.elapsed, self.counter = round, 0, 0
+        setattr(self, self._ANCHOR, None)
+
+    def compute(self) -> float:
+        return safe_round(self.elapsed / self.counter / 1e6, self.round) if self.counter else 0
+
+    def merge(self, other_state: dict[str, Any]) -> None:
+        self.elapsed += other_state["elapsed"]
+        self.counter += other_state["counter"]
+
+    def state_dict(self) -> dict[str, Any]:
+        return {"round": self.round, "elapsed": self.elapsed, "counter": self.counter}
+
+    def load_state_dict(self, state_dict: dict[str, Any]) -> None:
+        self.round = state_dict.get("round")
+        if "total_ms" in state_dict:            # states written before the fields were renamed
+            self.elapsed, self.counter = int(state_dict["total_ms"] * 1e6), int(state_dict.get("count", 0))
+        else:
+            self.elapsed, self.counter = state_dict.get("elapsed", 0), state_dict.get("counter", 0)
+        setattr(self, self._ANCHOR, None)
+
+
+class FrequencyMeter(_IntervalMeter):
+    """Mean time between occurrences of an event, in milliseconds. The first occurrence only sets the anchor."""
+
+    _ANCHOR = "start"
 
     def log(self) -> None:
-        now = time.perf_counter()
-        if self._last is not None:
-            self.total_ms += (now - self._last) * 1e3
-            self.count += 1
-        self._last = now
-
-    def compute(self) -> float:
-        return safe_round(self.total_ms / self.count, self.round) if self.count else 0.0
-
-    def merge(self, other_state: dict[str, Any]) -> None:
-        self.total_ms += other_state["total_ms"]
-        self.count += other_state["count"]
-
-    def load_state_dict(self, state_dict: dict[str, Any]) -> None:
-        super().load_state_dict(state_dict)
-        self._last = None  # wall-clock anchors do not survive a restart
+        now = time.perf_counter_ns()
+        if self.start is not None:
+            self.elapsed += now - self.start
+            self.counter += 1
+        self.start = now
 
 
-class StopwatchMeter(BaseMeter):
+class StopwatchMeter(_IntervalMeter):
     """Mean duration between ``start`` and ``end`` events, in milliseconds."""
 
-    def __init__(self, round: int | None = None):
-        self.round, self.total_ms, self.count, self._t0 = round, 0.0, 0, None
+    _ANCHOR = "_start"
 
     def log(self, mode: str) -> None:
+        assert mode in ("start", "end"), f"Unknown mode {mode!r}"
         if mode == "start":
             self.start()
-        elif mode == "end":
+        elif self._start is not None:           # an "end" event whose start was lost to a restart is dropped
             self.end()
-        else:
-            raise ValueError(f"unknown stopwatch mode {mode!r}")
 
     def start(self) -> None:
-        self._t0 = time.perf_counter()
+        self._start = time.perf_counter_ns()
 
     def end(self) -> None:
-        if self._t0 is not None:
-            self.total_ms += (time.perf_counter() - self._t0) * 1e3
-            self.count += 1
-            self._t0 = None
-
-    def compute(self) -> float:
-        return safe_round(self.total_ms / self.count, self.round) if self.count else 0.0
-
-    def merge(self, other_state: dict[str, Any]) -> None:
-        self.total_ms += other_state["total_ms"]
-        self.count += other_state["count"]
-
-    def load_state_dict(self, state_dict: dict[str, Any]) -> None:
-        super().load_state_dict(state_dict)
-        self._t0 = None
+        assert self._start is not None, "Stopwatch was never started"
+        self.elapsed += time.perf_counter_ns() - self._start
+        self.counter += 1
+        self._start = None
 
 
 class AveragedExponentMeter(BaseMeter):

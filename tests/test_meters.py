@@ -57,14 +57,19 @@ def test_exponent_meter_is_exp_of_weighted_mean_and_saturates():
 
 def test_stopwatch_and_frequency_meters_measure_milliseconds():
     sw = mc.StopwatchMeter()
-    sw.end()                                      # an end without a start is ignored
-    assert sw.compute() == 0.0
+    with pytest.raises(AssertionError, match="Stopwatch was never started"):
+        sw.end()
+    sw.log("end")                                 # as an event, an end whose start was lost (a restart) is dropped
+    assert sw.compute() == 0 and sw.counter == 0 and sw._start is None
     sw.log("start")
     time.sleep(0.02)
     sw.log("end")
     assert 15.0 < sw.compute() < 200.0
-    with pytest.raises(ValueError):
+    with pytest.raises(AssertionError, match="Unknown mode"):
         sw.log("pause")
+    known = mc.StopwatchMeter()
+    known.elapsed, known.counter = 4_000_000, 2   # nanoseconds over two intervals
+    assert known.compute() == 2.0
     fq = mc.FrequencyMeter()
     fq.log()
     assert fq.compute() == 0.0                    # one occurrence: no interval yet
@@ -73,7 +78,13 @@ def test_stopwatch_and_frequency_meters_measure_milliseconds():
     assert 5.0 < fq.compute() < 200.0
     restored = mc.FrequencyMeter()
     restored.load_state_dict(fq.state_dict())
-    assert restored._last is None and restored.compute() == fq.compute()
+    assert restored.start is None and restored.compute() == fq.compute() and fq.counter == 1
+    a, b = mc.FrequencyMeter(), mc.FrequencyMeter()
+    a.elapsed, a.counter, b.elapsed, b.counter = 1_000_000, 1, 2_000_000, 2
+    a.merge(b.state_dict())
+    assert (a.elapsed, a.counter, a.compute()) == (3_000_000, 3, 1.0)
+    assert mc.MaxMeter(round=2).value == -float("inf") and mc.MinMeter().value == float("inf")
+    assert mc.MaxMeter().compute() == 0.0         # nothing logged yet
 
 
 def test_gather_meter_collects_and_merges():
