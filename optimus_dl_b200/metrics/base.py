@@ -41,20 +41,34 @@ class BaseMeter(ABC):
         return m
 
 
+def _meter_class(name: str) -> type:
+    """Meter class by the name a state was saved under: the bare class name of any ``BaseMeter`` subclass that has
+    been imported, or a dotted path."""
+    if "." in name:
+        from ..core.conf import locate
+
+        return locate(name)
+    from . import common  # noqa: F401  (defines the stock meters)
+
+    todo = list(BaseMeter.__subclasses__())
+    while todo:
+        cls = todo.pop()
+        if cls.__name__ == name:
+            return cls
+        todo.extend(cls.__subclasses__())
+    raise KeyError(f"unknown meter class {name!r}")
+
+
 class MeterEntry:
-    def __init__(self, meter: BaseMeter, reset: bool = True, priority: int = 100):
+    def __init__(self, meter: BaseMeter, reset: bool = False, priority: int = 0):
         self.meter, self.reset, self.priority = meter, reset, priority
 
     def state_dict(self) -> dict[str, Any]:
-        cls = type(self.meter)
-        return {"meter_class": f"{cls.__module__}.{cls.__qualname__}", "meter": self.meter.state_dict(),
+        return {"meter_class": type(self.meter).__name__, "meter": self.meter.state_dict(),
                 "reset": self.reset, "priority": self.priority}
 
     def load_state_dict(self, sd: dict[str, Any]) -> None:
-        from ..core.conf import locate
-
-        cls = locate(sd["meter_class"])
-        self.meter = cls.from_state_dict(sd["meter"])
+        self.meter = _meter_class(sd["meter_class"]).from_state_dict(sd["meter"])
         self.reset, self.priority = sd["reset"], sd["priority"]
 
     @classmethod
@@ -67,7 +81,7 @@ class MeterEntry:
 class MeterGroup:
     def __init__(self, name: str, log_freq: int | None = None, log_logger_overhead: bool | None = None):
         self.name = name
-        self.log_freq = log_freq
+        self.log_freq = 1 if log_freq is None else log_freq
         self.log_logger_overhead = True if log_logger_overhead is None else log_logger_overhead
         self._meters: "OrderedDict[str, MeterEntry]" = OrderedDict()
         self._iteration = 0
@@ -76,16 +90,25 @@ class MeterGroup:
     def meters(self) -> "OrderedDict[str, MeterEntry]":
         return self._meters
 
+    @property
+    def _keys_sorted(self) -> list[str]:
+        """Meter names in reporting order (priority, then name)."""
+        return list(self._meters)
+
+    @property
+    def _iteration_counter(self) -> int:
+        return self._iteration
+
     def should_log(self) -> bool:
+        """Whether the current step is a logging step: the first one, and every ``log_freq``-th after it."""
         if not self.log_freq:
             return True
-        return (self._iteration + 1) % self.log_freq == 0
+        return self._iteration % self.log_freq == 0
 
     def step(self) -> bool:
-        """Advance the iteration counter; returns whether the step that just ended was a logging step."""
-        logged = self.should_log()
+        """Advance the iteration counter; returns whether the step that now begins is a logging step."""
         self._iteration += 1
-        return logged
+        return self.should_log()
 
     def add_meter(self, name: str, entry: MeterEntry) -> None:
         self._meters[name] = entry

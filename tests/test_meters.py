@@ -108,7 +108,7 @@ def test_logging_outside_a_group_is_dropped_and_lazy_values_run_only_on_log_step
 
     for step in range(4):
         with mb.meters_group("train", log_freq=2) as should_log:
-            assert should_log == (step % 2 == 1)
+            assert should_log == (step % 2 == 0)    # the first step logs, then every second one
             mc.log_averaged("v", lazy)
         mb.step_meters("train")
     assert len(calls) == 2                        # evaluated on the two logging steps only
@@ -150,10 +150,11 @@ def test_group_state_round_trip_restores_iteration_and_values():
     g = mb.get_group("train")
     assert g._iteration == 3 and g.log_freq == 5
     with mb.meters_group("train") as should_log:
-        assert not should_log                     # iteration 4 of 5
+        assert not should_log                     # counter 3: not a multiple of 5
+    mb.step_meters("train")
     mb.step_meters("train")
     with mb.meters_group("train") as should_log:
-        assert should_log                         # iteration 5 of 5
+        assert should_log                         # counter 5
 
 
 class _TwoRanks:
@@ -183,3 +184,30 @@ def test_aggregation_merges_every_rank_including_keys_only_a_peer_has():
     assert abs(out["loss"] - 3.5) < 1e-9 and out["tokens"] == 40.0 and out["peak"] == 9.0
     assert list(out)[0] == "loss"
     assert mb.compute_meters("eval")["tokens"] == 10.0       # local values are untouched by aggregation
+
+
+def test_entry_and_group_structure():
+    """Defaults, state keys and cadence of optimus_dl/modules/metrics/base.py (MeterEntry, MeterGroup)."""
+    entry = mb.MeterEntry(meter=mc.AverageMeter())
+    assert entry.reset is False and entry.priority == 0
+    state = mb.MeterEntry(meter=mc.AverageMeter(), reset=True, priority=10).state_dict()
+    assert state["meter_class"] == "AverageMeter" and state["reset"] is True and state["priority"] == 10
+    entry.load_state_dict({"meter": {"sum": 10.0, "count": 1.0, "round": None}, "reset": True, "priority": 5,
+                           "meter_class": "AverageMeter"})
+    assert isinstance(entry.meter, mc.AverageMeter) and entry.meter.compute() == 10.0 and entry.priority == 5
+    dotted = mb.MeterEntry.from_state_dict({"meter": {"round": None, "sum": 2.0}, "reset": False, "priority": 1,
+                                            "meter_class": "optimus_dl_b200.metrics.common.SummedMeter"})
+    assert isinstance(dotted.meter, mc.SummedMeter)
+
+    group = mb.MeterGroup("g", log_freq=3)
+    assert mb.MeterGroup("d").log_freq == 1 and group._iteration_counter == 0 and len(group._meters) == 0
+    assert group.should_log()                                   # counter 0 is a logging step
+    assert not group.step() and not group.should_log()          # 1
+    assert not group.step()                                     # 2
+    assert group.step() and group.should_log()                  # 3
+    group.add_meter("high", mb.MeterEntry(meter=mc.AverageMeter(), priority=10))
+    group.add_meter("low", mb.MeterEntry(meter=mc.SummedMeter(), priority=1, reset=True))
+    group.add_meter("mid", mb.MeterEntry(meter=mc.AverageMeter(), priority=5))
+    assert group._keys_sorted == ["low", "mid", "high"] and group.get_meter("none") is None
+    group.reset()
+    assert group._keys_sorted == ["mid", "high"]                # only reset=True meters are dropped

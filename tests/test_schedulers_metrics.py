@@ -63,7 +63,7 @@ def test_meter_groups_lazy_values_reset_and_state():
     calls = []
     for it in range(4):
         with meters_group("g", log_freq=2) as should_log:
-            assert should_log == (it % 2 == 1)
+            assert should_log == (it % 2 == 0)
             log_averaged("loss", lambda: calls.append(it) or float(it), weight=2, round=3)
             log_summed("total", 1.0, reset=False)
         if should_log:
@@ -71,7 +71,7 @@ def test_meter_groups_lazy_values_reset_and_state():
             assert out["loss"] == float(it) and out["total"] == it + 1
             reset_meters("g")
         step_meters("g")
-    assert calls == [1, 3]           # lazy values are only evaluated on logging steps
+    assert calls == [0, 2]           # lazy values are only evaluated on logging steps
     sd = state_dict()
     mb.clear_all()
     load_state_dict(sd)
