@@ -125,12 +125,12 @@ class MeterGroup:
             del self._meters[k]
 
     def state_dict(self) -> dict[str, Any]:
-        return {"name": self.name, "log_freq": self.log_freq, "iteration": self._iteration,
+        return {"name": self.name, "log_freq": self.log_freq, "iteration_counter": self._iteration,
                 "meters": {k: e.state_dict() for k, e in self._meters.items()}}
 
     def load_state_dict(self, sd: dict[str, Any]) -> None:
         self.log_freq = sd.get("log_freq", self.log_freq)
-        self._iteration = sd.get("iteration", 0)
+        self._iteration = sd.get("iteration_counter", sd.get("iteration", 0))
         self._meters = OrderedDict((k, MeterEntry.from_state_dict(v)) for k, v in sd.get("meters", {}).items())
 
 
