@@ -11,6 +11,7 @@ first) and ``composite_optimizer_name``.
 
 from __future__ import annotations
 
+import dataclasses
 import re
 from dataclasses import dataclass, field
 from typing import Any, Callable, Iterable
@@ -131,7 +132,12 @@ def make_composite_optimizer(cfg: Any, params: Any, **kwargs: Any) -> CompositeO
     entries = dict(cfg.optimizers)
 
     def regexp_of(entry: Any) -> str | None:  # an explicit ``None`` means "everything that is left"
+        if dataclasses.is_dataclass(entry):
+            return getattr(entry, "params_regexp", ".*")
         return entry["params_regexp"] if "params_regexp" in entry else ".*"
+
+    def optimizer_config_of(entry: Any) -> Any:
+        return entry.optimizer_config if dataclasses.is_dataclass(entry) else entry["optimizer_config"]
 
     assert sum(1 for e in entries.values() if regexp_of(e) is None) <= 1, \
         "Only one optimizer can have params_regexp set to None (match all remaining)."
@@ -151,7 +157,7 @@ def make_composite_optimizer(cfg: Any, params: Any, **kwargs: Any) -> CompositeO
             if id(t) in claimed:
                 raise ValueError(f"Parameter '{n}' is matched by more than one optimizer (second match: '{name}').")
             claimed.add(id(t))
-        built[name] = build_optimizer(entry.optimizer_config, params=sub, **kwargs)
+        built[name] = build_optimizer(optimizer_config_of(entry), params=sub, **kwargs)
     missing = [n for i, n in names.items() if i not in claimed]
     if missing:
         raise ValueError(f"Parameters not matched by any optimizer: {missing[:8]}{' ...' if len(missing) > 8 else ''}")

@@ -172,3 +172,35 @@ def test_optimizer_builder_counts_parameters_and_passes_the_clip_value():
         opt = OptimizerBuilder(optimization_config=cfg).build_optimizer(list(lin.named_parameters()))
         assert mb.compute_meters("init")["optimized_params"] == 15
     assert opt.param_groups[0]["lr"] == 0.5 and len(opt.param_groups[0]["params"]) == 2
+
+
+def test_composite_accepts_config_dataclasses_and_a_catch_all_entry():
+    """``CompositeOptimizerConfigEntry`` instances as entries (optimus_dl/modules/optim/composite.py), ``params_regexp:
+    None`` as "everything that is left", and live ``param_groups`` of the sub-optimizers."""
+    import torch.nn as nn
+
+    from optimus_dl_b200.optim.composite import (CompositeOptimizer, CompositeOptimizerConfig, CompositeOptimizerConfigEntry,
+                                                 make_composite_optimizer)
+
+    for weight_cfg in ({"_name": "adamw", "lr": 1e-2}, {"_name": "muon", "lr": 1e-2}):
+        model = nn.Linear(10, 5)
+        cfg = CompositeOptimizerConfig(optimizers={
+            "weight_opt": CompositeOptimizerConfigEntry(params_regexp=".*weight", optimizer_config=weight_cfg),
+            "bias_opt": CompositeOptimizerConfigEntry(params_regexp=".*bias", optimizer_config={"_name": "adamw", "lr": 1e-3})})
+        opt = make_composite_optimizer(cfg, params=model.named_parameters())
+        assert isinstance(opt, CompositeOptimizer) and set(opt.optimizers) == {"weight_opt", "bias_opt"}
+        assert opt.optimizers["weight_opt"].param_groups[0]["lr"] == 1e-2 and opt.optimizers["bias_opt"].param_groups[0]["lr"] == 1e-3
+        for group in opt.param_groups:
+            if group["composite_optimizer_name"] == "weight_opt":
+                group["lr"] = 5e-2
+        assert opt.optimizers["weight_opt"].param_groups[0]["lr"] == 5e-2      # the same dict, not a copy
+        model(torch.randn(3, 10)).sum().backward()
+        before = model.weight.detach().clone()
+        opt.step()
+        assert not torch.equal(before, model.weight)
+    model = nn.Linear(10, 5)
+    rest = make_composite_optimizer(CompositeOptimizerConfig(optimizers={
+        "w": CompositeOptimizerConfigEntry(params_regexp=".*weight", optimizer_config={"_name": "adamw", "lr": 1e-2}),
+        "rest": CompositeOptimizerConfigEntry(params_regexp=None, optimizer_config={"_name": "adamw", "lr": 1e-3})}),
+        params=model.named_parameters())
+    assert len(rest.optimizers["rest"].param_groups[0]["params"]) == 1
