@@ -81,13 +81,19 @@ class _FakeColl:
 
 
 class CheckpointManager:
-    def __init__(self, cfg: Any = None, output_path: str | None = None, **kwargs: Any):
+    def __init__(self, cfg: Any = None, output_path: str | None = None, checkpoint_path: str | os.PathLike | None = None,
+                 save_freq: int | None = None, last_save_freq: int | None = None, **kwargs: Any):
+        """``checkpoint_path`` is the reference's name for ``output_path``; ``save_freq`` / ``last_save_freq`` given
+        here are the defaults of ``save_checkpoint_if_needed``."""
         self.cfg = cfg
+        output_path = output_path if output_path is not None else checkpoint_path
         self.output_path = Path(output_path) if output_path is not None else None
+        self.save_freq, self.last_save_freq = save_freq, last_save_freq
 
     # ------------------------------------------------------------------ discovery
-    def is_restart(self) -> bool:
-        return self.output_path is not None and (self.output_path / "metadata_latest.pt").exists()
+    def is_restart(self, checkpoint_path: str | os.PathLike | None = None) -> bool:
+        root = Path(checkpoint_path) if checkpoint_path is not None else self.output_path
+        return root is not None and (root / "metadata_latest.pt").exists()
 
     def get_checkpoint(self, path: str | os.PathLike) -> CheckpointPath | None:
         """Accepts an output dir, a ``checkpoint_*`` dir, a ``metadata_*.pt`` file or ``metadata_latest.pt``."""
@@ -106,13 +112,27 @@ class CheckpointManager:
         return None
 
     # ------------------------------------------------------------------ save
-    def save_checkpoint_if_needed(self, iteration: int, save_freq: int | None = None, last_save_freq: int | None = None,
-                                  force_save: bool = False, **kwargs: Any) -> bool:
+    def save_checkpoint_if_needed(self, iteration: int, *positional: Any, save_freq: int | None = None,
+                                  last_save_freq: int | None = None, force_save: bool = False, **kwargs: Any) -> bool:
+        """``(iteration, save_freq, last_save_freq, force_save, **save_kwargs)`` or, as the reference calls it,
+        ``(iteration, collective, checkpoint_path, save_freq=..., last_save_freq=..., force_save=..., **save_kwargs)``.
+        A numbered (persistent) checkpoint every ``save_freq`` iterations, a ``*_latest`` one every ``last_save_freq``."""
+        if positional and (positional[0] is None or isinstance(positional[0], (int, bool))):
+            names = ("save_freq", "last_save_freq", "force_save")
+            given = dict(zip(names, positional))
+            save_freq = given.get("save_freq", save_freq)
+            last_save_freq = given.get("last_save_freq", last_save_freq)
+            force_save = given.get("force_save", force_save)
+        elif positional:
+            kwargs.update(zip(("collective", "checkpoint_path"), positional))
+        save_freq = self.save_freq if save_freq is None else save_freq
+        last_save_freq = self.last_save_freq if last_save_freq is None else last_save_freq
         persistent = bool(save_freq) and save_freq > 0 and iteration % save_freq == 0
         last = bool(last_save_freq) and last_save_freq > 0 and iteration % last_save_freq == 0
         if not (persistent or last or force_save):
             return False
-        self.save_checkpoint(iteration=iteration, persistent=persistent or (force_save and not last), **kwargs)
+        persistent = persistent or (force_save and not last)
+        self.save_checkpoint(iteration=iteration, is_save_persistent=persistent, is_save_last=True, **kwargs)
         return True
 
     def _names(self, iteration: int, rank: int, persistent: bool) -> dict[str, Path]:
@@ -121,10 +141,18 @@ class CheckpointManager:
         return {"ckpt": out / f"checkpoint_{tag}", "meta": out / f"metadata_{tag}.pt",
                 "rank": out / f"per_rank_metadata_{rank}_{tag}.pt"}
 
-    def save_checkpoint(self, iteration: int, model: torch.nn.Module | None = None, optimizer: Any = None,
+    def save_checkpoint(self, iteration: int = 0, model: Any = None, optimizer: Any = None,
                         lr_scheduler: Any = None, collective: Any = None, full_config: Any = None,
                         persistent: bool = True, metadata_only: bool = False, extra_metadata: dict | None = None,
-                        data_loaders: dict | None = None, **stateful: Any) -> None:
+                        data_loaders: dict | None = None, checkpoint_path: str | os.PathLike | None = None,
+                        is_save_persistent: bool | None = None, is_save_last: bool | None = None, **stateful: Any) -> None:
+        """Called with keywords. ``checkpoint_path`` overrides the manager's output path; ``is_save_persistent`` is
+        the reference's name for ``persistent`` (a numbered checkpoint that ``*_latest`` links
+        point at); without it the checkpoint is written under the ``*_latest`` names themselves."""
+        if is_save_persistent is not None:
+            persistent = bool(is_save_persistent)
+        if checkpoint_path is not None:
+            self.output_path = Path(checkpoint_path)
         assert self.output_path is not None, "checkpoint manager has no output path"
         coll = collective or _FakeColl()
         out = self.output_path
@@ -184,16 +212,23 @@ class CheckpointManager:
         logger.info("saved %s checkpoint at iteration %d to %s", "metadata-only" if metadata_only else "full", iteration, out)
 
     # ------------------------------------------------------------------ load
-    def load_checkpoint_if_exists(self, **kwargs: Any) -> tuple[int, dict | None]:
-        """Resume from ``output_path`` when it holds a checkpoint; returns ``(start_iteration, metadata)``."""
-        if not self.is_restart():
+    def load_checkpoint_if_exists(self, checkpoint_path: str | os.PathLike | None = None, **kwargs: Any) -> tuple[int, dict | None]:
+        """Resume from ``checkpoint_path`` (default: the manager's output path) when it holds a checkpoint; returns
+        ``(start_iteration, metadata)``."""
+        root = Path(checkpoint_path) if checkpoint_path is not None else self.output_path
+        if not self.is_restart(root):
             return 1, None
-        metadata = self.load_checkpoint(str(self.output_path), **kwargs)
+        metadata = self.load_checkpoint(str(root), **kwargs)
         return int(metadata["iteration"]) + 1, metadata
 
-    def load_checkpoint(self, path: str, model: torch.nn.Module | None = None, optimizer: Any = None,
+    def load_checkpoint(self, path: str | os.PathLike | None = None, model: torch.nn.Module | None = None, optimizer: Any = None,
                         lr_scheduler: Any = None, collective: Any = None, strategy: LoadStrategy | None = None,
-                        data_loaders: dict | None = None, **stateful: Any) -> dict:
+                        data_loaders: dict | None = None, checkpoint_path: str | os.PathLike | None = None,
+                        load_strategy: LoadStrategy | None = None, **stateful: Any) -> dict:
+        """``checkpoint_path`` / ``load_strategy`` are the reference's names for ``path`` / ``strategy``."""
+        path = path if path is not None else checkpoint_path
+        strategy = strategy if strategy is not None else load_strategy
+        assert path is not None, "load_checkpoint needs a path"
         coll = collective or _FakeColl()
         strategy = LoadStrategy.from_cfg(strategy)
         cp = self.get_checkpoint(path)
@@ -255,8 +290,10 @@ class CheckpointManager:
         return metadata
 
     # ------------------------------------------------------------------ model-only helpers
-    def build_model_from_checkpoint(self, path: str, device: Any = "cpu", **build_kwargs: Any):
+    def build_model_from_checkpoint(self, path: str | os.PathLike | None = None, device: Any = "cpu",
+                                    checkpoint_path: str | os.PathLike | None = None, **build_kwargs: Any):
         """Rebuild the model from the config stored in the checkpoint's metadata and load its weights."""
+        path = str(path if path is not None else checkpoint_path)
         from ..models import build_model
 
         cp = self.get_checkpoint(path)
@@ -267,8 +304,10 @@ class CheckpointManager:
         self.load_model_state_dict(model, cp.checkpoint)
         return model.to(device), metadata
 
-    def load_model_state_dict(self, model: torch.nn.Module, path: str, strict: bool = True) -> None:
+    def load_model_state_dict(self, model: torch.nn.Module, path: str | os.PathLike | None = None, strict: bool = True,
+                              checkpoint_path: str | os.PathLike | None = None) -> None:
         """Load weights from a DCP directory (converted through a temporary torch.save file) or a ``.pt`` file."""
+        path = str(path if path is not None else checkpoint_path)
         p = Path(path)
         if p.is_dir():
             import tempfile

@@ -195,3 +195,42 @@ def test_checkpoint_path_helpers_and_eval_state_cleanup(tmp_path):
     assert not ev.get_eval_checkpoints_dir(20).exists() and ev.get_eval_checkpoints_dir(30).exists()
     ev.cleanup()
     assert not ev.get_eval_checkpoints_dir(30).exists()
+
+
+def test_reference_call_forms_of_the_manager(tmp_path):
+    """Keyword names of optimus_dl/modules/checkpoint/checkpoint_manager.py:78-835: ``checkpoint_path``,
+    ``is_save_persistent`` / ``is_save_last``, ``load_strategy``, and ``(iteration, collective, path)`` positionally."""
+    from unittest.mock import patch
+
+    from optimus_dl_b200.parallel.collective import FakeCollective
+
+    coll = FakeCollective(rank=0, world_size=1)
+    mgr = CheckpointManager()
+    with patch.object(mgr, "save_checkpoint") as save:
+        assert mgr.save_checkpoint_if_needed(10, coll, "tmp", save_freq=10, last_save_freq=None)
+        kw = save.call_args.kwargs
+        assert kw["is_save_persistent"] is True and kw["is_save_last"] is True and kw["checkpoint_path"] == "tmp"
+        save.reset_mock()
+        assert not mgr.save_checkpoint_if_needed(5, coll, "tmp", save_freq=10, last_save_freq=None)
+        save.assert_not_called()
+        assert mgr.save_checkpoint_if_needed(5, coll, "tmp", save_freq=10, last_save_freq=5)
+        assert save.call_args.kwargs["is_save_persistent"] is False and save.call_args.kwargs["is_save_last"] is True
+    model = torch.nn.Linear(4, 4)
+    opt = torch.optim.SGD(model.parameters(), lr=0.1)
+    root = tmp_path / "checkpoints"
+    mgr.save_checkpoint(checkpoint_path=root, model=model, optimizer=opt, collective=coll, full_config={},
+                        is_save_persistent=True, is_save_last=True, iteration=10)
+    assert (root / "checkpoint_latest").is_symlink() and (root / "metadata_latest.pt").is_symlink()
+    assert (root / "per_rank_metadata_0_latest.pt").is_symlink() and os.readlink(root / "checkpoint_latest") == "checkpoint_000000010"
+    other = tmp_path / "last_only"
+    mgr.save_checkpoint(checkpoint_path=other, model=model, optimizer=opt, collective=coll, full_config={},
+                        is_save_persistent=False, is_save_last=True, iteration=15)
+    assert (other / "checkpoint_latest").is_dir() and not (other / "checkpoint_latest").is_symlink()
+    assert not list(other.glob("checkpoint_0*")) and (other / "metadata_latest.pt").exists()
+    fresh = torch.nn.Linear(4, 4)
+    loader = CheckpointManager()
+    assert loader.is_restart(other) and not loader.is_restart(tmp_path / "nothing")
+    start, meta = loader.load_checkpoint_if_exists(checkpoint_path=other, model=fresh, optimizer=None, collective=coll,
+                                                    load_strategy=None)
+    assert start == 16 and meta["iteration"] == 15 and torch.equal(fresh.weight, model.weight)
+    assert loader.load_checkpoint_if_exists(checkpoint_path=tmp_path / "nothing", model=fresh) == (1, None)
