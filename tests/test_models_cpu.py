@@ -92,3 +92,27 @@ def test_cross_entropy_shift_smoothing_padding_and_meters():
     assert torch.allclose(cap, ref3, atol=1e-5)
     one, _ = crit(m, {"input_ids": ids[:, :2]})
     assert torch.isfinite(one)
+
+
+def test_rope_table_and_broadcast_helper():
+    """``precompute_freqs_cis`` / ``apply_rotary_emb`` / ``_reshape_for_broadcast`` (optimus_dl/modules/model/blocks/rope.py)."""
+    import pytest
+    import torch
+
+    from optimus_dl_b200.models.blocks.rope import _reshape_for_broadcast, apply_rotary_emb, precompute_freqs_cis
+
+    table = precompute_freqs_cis(64, 100)
+    assert table.shape == (100, 32, 2) and table.dtype == torch.float32
+    assert torch.allclose(table.norm(dim=-1), torch.ones(100, 32), atol=1e-6)        # unit (cos, sin) pairs
+    assert precompute_freqs_cis(32, 50, 1000.0).shape == (50, 16, 2)
+    q, k = torch.randn(2, 10, 8, 64), torch.randn(2, 10, 8, 64)
+    q_rot, k_rot = apply_rotary_emb(q, k, precompute_freqs_cis(64, 10))
+    assert q_rot.shape == q.shape and k_rot.dtype == k.dtype and not torch.allclose(q_rot, q)
+    assert torch.allclose(q_rot.norm(dim=-1), q.norm(dim=-1), atol=1e-4)             # a rotation keeps lengths
+    flat = torch.randn(10, 32, dtype=torch.complex64)
+    with pytest.raises(AssertionError):
+        _reshape_for_broadcast(flat, torch.randn(32, dtype=torch.complex64))
+    with pytest.raises(AssertionError):
+        _reshape_for_broadcast(flat, torch.randn(2, 5, 16, dtype=torch.complex64))
+    assert _reshape_for_broadcast(torch.randn(2, 10, 32, 2), torch.randn(2, 10, 8, 32, 2)).shape == (2, 10, 1, 32, 2)
+    assert _reshape_for_broadcast(precompute_freqs_cis(64, 10), torch.randn(2, 10, 8, 32, 2)).shape == (1, 10, 1, 32, 2)
