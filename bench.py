@@ -10,8 +10,8 @@ synchronize, max over ranks) over exactly ``--steps`` optimizer steps, each a fu
 backward, gradient reduce-scatter and sharded AdamW update of the named model on synthetic
 uniform-random token ids with random-init weights. ``e2e`` repeats the measurement through the
 same public calls a training script makes, adding the per-step host->device copy of the batch from
-pinned memory and the device->host read of the loss. ``--impl reference`` reports why the
-unmodified reference cannot run on this image.
+pinned memory and the device->host read of the loss. ``--impl reference`` runs the unmodified
+reference framework on the same config (baseline/reference_arm.py) and prints the same keys.
 """
 
 from __future__ import annotations
@@ -23,10 +23,6 @@ import statistics
 import subprocess
 import sys
 import time
-
-REF_UNAVAILABLE = ("reference not installable offline: pip --no-deps yields only optimus_dl/__init__.py "
-                   "(its pyproject lists packages=['optimus_dl'] without sub-packages) and omegaconf, hydra-core, "
-                   "colorlog are absent from the wheelhouse, so `import optimus_dl` fails")
 
 MODELS = {
     "llama3-8b": dict(_name="llama2", n_layer=32, n_head=32, n_kv_head=8, n_embd=4096, intermediate_size=14336,
@@ -110,11 +106,22 @@ def main() -> None:
                                                        "(JSON lines) to this file")
     ap.add_argument("--n-layer", type=int, default=None, help="override the layer count (profiling only; the "
                     "reported metric then says so)")
+    ap.add_argument("--ref-variant", default=None, help="reference arm only: comma-separated list tried in order, from "
+                    "'stock' and 'stock+activation_checkpoint' (default: stock, then on one GPU the checkpointed form if "
+                    "the stock form runs out of device memory)")
+    ap.add_argument("--ref-compile", action="store_true", help="reference arm only: append the reference's `compile` "
+                    "transform (torch.compile of the whole model, as configs/train/train_llama.yaml lists it)")
     args = ap.parse_args()
 
     if args.impl == "reference":
-        if int(os.environ.get("RANK", "0")) == 0:
-            print(json.dumps({"impl": "reference", "unavailable": REF_UNAVAILABLE}))
+        # the unmodified reference, in this process, with none of this package imported (baseline/reference_arm.py)
+        import importlib.util
+
+        spec = importlib.util.spec_from_file_location(
+            "_reference_arm", os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "reference_arm.py"))
+        arm = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(arm)
+        arm.run(args, MODELS, ClockSampler)
         return
 
     import torch

@@ -70,7 +70,7 @@ class _CountingLib:
         return counted
 
 
-_NO_LAUNCH = {"ob_norm_bwd_grid", "ob_rope_grid", "ob_bind_thread"}
+_NO_LAUNCH = {"ob_norm_bwd_grid", "ob_rope_grid", "ob_bind_thread", "ob_set_flag_wait_iters"}
 _tls = threading.local()
 
 
@@ -139,8 +139,41 @@ def check_status(device: torch.device | None = None) -> None:
     code = int(buf.item())
     if code != 0:
         buf.zero_()
-        names = {1: "mbarrier wait timed out", 2: "flag wait timed out", 3: "bad arguments"}
-        raise KernelError(f"kernel status {code}: {names.get(code, 'unknown')}")
+        raise KernelError(f"kernel status {code}: {_STATUS_NAMES.get(code, 'unknown')}")
+
+
+_STATUS_NAMES = {1: "mbarrier wait timed out", 2: "flag wait timed out", 3: "bad arguments"}
+
+
+class DeferredStatus:
+    """Status word read without stalling the stream: ``post()`` queues a copy of the word to pinned host memory,
+    ``check()`` (usually one step later) waits for that copy only and raises if a kernel had reported a failure."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.host = torch.zeros(1, dtype=torch.int32).pin_memory() if torch.cuda.is_available() else torch.zeros(1, dtype=torch.int32)
+        self.event: torch.cuda.Event | None = None
+
+    def post(self) -> None:
+        self.host.copy_(status_word(self.device), non_blocking=True)
+        self.event = torch.cuda.Event()
+        self.event.record()
+
+    def check(self) -> None:
+        if self.event is None:
+            return
+        self.event.synchronize()
+        self.event = None
+        code = int(self.host[0])
+        if code != 0:
+            status_word(self.device).zero_()
+            raise KernelError(f"kernel status {code}: {_STATUS_NAMES.get(code, 'unknown')} (the optimizer update of that "
+                              "step was skipped; parameters and optimizer state are those of the last good step)")
+
+
+def set_flag_wait_iters(iters: int) -> None:
+    """Poll limit of the cross-GPU barrier waits on the current device (0 = default, about two seconds)."""
+    check(lib().ob_set_flag_wait_iters(int(iters)), "ob_set_flag_wait_iters")
 
 
 def check(rc: int, what: str) -> None:
@@ -183,7 +216,8 @@ def _declare(l: ctypes.CDLL) -> None:
     PP = ctypes.POINTER(c_void_p)
     sig("ob_barrier", [PP, I, I, I, P, P])
     sig("ob_pull", [P, I, PP, I, P, P, I, I, P])
-    sig("ob_rs_adamw", [I, P, I, PP, I, P, P, P, P, P, F, F, F, F, F, F, F, F, P, P, P, I, P])
+    sig("ob_rs_adamw", [I, P, I, PP, I, P, P, P, P, P, F, F, F, F, F, F, F, F, P, P, P, I, P, P])
+    sig("ob_set_flag_wait_iters", [ctypes.c_uint])
     sig("ob_gemm_ag_bf16", [P, L, P, L, P, L, I, I, I, P, P, I, PP, I, P, P, I, I, I, I, I, P, P])
     sig("ob_gemm_ag_act_bf16", [P, L, P, P, L, I, P, P, P, L, I, I, I, P, P, I, PP, I, P, P, I, I, I, I, P, P])
     sig("ob_gemm_ag_push_bf16", [P, L, P, L, P, P, L, I, P, P, P, L, I, I, I, P, P, I, PP, PP, I, P, I, I, I, I, P, P])

@@ -9,6 +9,10 @@
 namespace ob {
 namespace comm {
 
+// Poll limit of the cross-GPU flag waits in this file (about 100 ns per poll: the default is roughly two seconds).
+// The host may lower it (ob_set_flag_wait_iters) so that a test can let a wait run out quickly.
+__device__ unsigned int g_flag_wait_iters = 1u << 24;
+
 // flags: this rank's symmetric int array [MAX_RANKS]; peers.p[r] = rank r's array.
 // Rank `me` writes `epoch` into slot `me` of every rank, then waits for all slots of its own array.
 __global__ void barrier_kernel(PeerPtrs peers, int me, int world, int epoch, int* status) {
@@ -19,7 +23,8 @@ __global__ void barrier_kernel(PeerPtrs peers, int me, int world, int epoch, int
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
   const int* mine = reinterpret_cast<const int*>(peers.p[me]) + r;
   bool ok = false;
-  for (uint32_t it = 0; it < (1u << 24); ++it) {
+  const uint32_t limit = g_flag_wait_iters;
+  for (uint32_t it = 0; it < limit; ++it) {
     int v;
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
     if (v >= epoch) { ok = true; break; }
@@ -62,7 +67,10 @@ __global__ void __launch_bounds__(256)
 rs_adamw_kernel(const Segment* __restrict__ segs, int n_segs, PeerPtrs grads, int world,
                 float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
                 float* __restrict__ grad_shard, __nv_bfloat16* __restrict__ param_out, AdamArgs a,
-                float* __restrict__ sq_partials) {
+                float* __restrict__ sq_partials, const int* __restrict__ status) {
+  // A step whose barrier (or any earlier kernel) reported a failed wait must not be committed: the peers'
+  // gradient buffers may be half written. The status word is sticky until the host reads and clears it.
+  if (MODE != kReduceOnly && status != nullptr && *reinterpret_cast<const volatile int*>(status) != kStatusOk) return;
   float scale = a.grad_scale;
   if (MODE != kReduceOnly && a.sumsq_in && a.max_norm > 0.f) {
     const float norm = sqrtf(*a.sumsq_in) * a.grad_scale;
@@ -188,7 +196,8 @@ rs_sum_kernel(PeerPtrs flag_peers, int me, int world, int epoch, const __nv_bflo
     if ((int)threadIdx.x < world) {
       const int* mine = reinterpret_cast<const int*>(flag_peers.p[me]) + threadIdx.x;
       bool ok = false;
-      for (uint32_t it = 0; it < (1u << 24); ++it) {
+      const uint32_t limit = g_flag_wait_iters;
+      for (uint32_t it = 0; it < limit; ++it) {
         int v;
         asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
         if (v >= epoch) { ok = true; break; }
@@ -256,6 +265,12 @@ static PeerPtrs make_peers(const void* const* ptrs, int world) {
   return p;
 }
 
+// Poll limit of ob_barrier / ob_rs_sum waits on the current device (0 restores the default).
+extern "C" int ob_set_flag_wait_iters(unsigned int iters) {
+  if (iters == 0) iters = 1u << 24;
+  return (int)cudaMemcpyToSymbol(g_flag_wait_iters, &iters, sizeof(iters));
+}
+
 extern "C" int ob_barrier(const void* const* flag_ptrs, int me, int world, int epoch, int* status,
                           cudaStream_t stream) {
   if (world > MAX_RANKS) return -1;
@@ -280,7 +295,8 @@ extern "C" int ob_pull(const void* tasks, int n_tasks, const void* const* src_pt
 extern "C" int ob_rs_adamw(int mode, const void* segs, int n_segs, const void* const* grad_ptrs, int world,
                            void* master, void* m, void* v, void* grad_shard, void* param_out, float lr, float beta1,
                            float beta2, float eps, float bc1, float bc2, float grad_scale, float max_norm,
-                           const void* sumsq_in, void* sq_scratch, void* sumsq_out, int n_ctas, cudaStream_t stream) {
+                           const void* sumsq_in, void* sq_scratch, void* sumsq_out, int n_ctas, const int* status,
+                           cudaStream_t stream) {
   if (world > MAX_RANKS) return -1;
   if (n_segs == 0) return 0;
   if (n_ctas <= 0) n_ctas = 148 * 2;
@@ -289,16 +305,16 @@ extern "C" int ob_rs_adamw(int mode, const void* segs, int n_segs, const void* c
   if (mode == kFused)
     rs_adamw_kernel<kFused><<<n_ctas, 256, 0, stream>>>((const Segment*)segs, n_segs, g, world, (float*)master,
                                                         (float*)m, (float*)v, nullptr, (__nv_bfloat16*)param_out, a,
-                                                        nullptr);
+                                                        nullptr, status);
   else if (mode == kReduceOnly) {
     rs_adamw_kernel<kReduceOnly><<<n_ctas, 256, 0, stream>>>((const Segment*)segs, n_segs, g, world, nullptr, nullptr,
                                                              nullptr, (float*)grad_shard, nullptr, a,
-                                                             (float*)sq_scratch);
+                                                             (float*)sq_scratch, status);
     if (sumsq_out) sum_partials_kernel<<<1, 32, 0, stream>>>((const float*)sq_scratch, n_ctas, (float*)sumsq_out, 1);
   } else
     rs_adamw_kernel<kUpdateOnly><<<n_ctas, 256, 0, stream>>>((const Segment*)segs, n_segs, g, world, (float*)master,
                                                              (float*)m, (float*)v, (float*)grad_shard,
-                                                             (__nv_bfloat16*)param_out, a, nullptr);
+                                                             (__nv_bfloat16*)param_out, a, nullptr, status);
   return (int)cudaGetLastError();
 }
 
