@@ -192,6 +192,8 @@ def _declare(l: ctypes.CDLL) -> None:
 
     sig("ob_gemm_bf16", [P, L, I, P, L, I, P, L, I, I, I, I, I, P, I, F, P, I, I, P, I, I, I, I, I, P, P])
     sig("ob_gemm_swiglu_bf16", [P, L, P, P, L, P, P, P, L, I, I, I, P, P])
+    sig("ob_gemm2_bf16", [P, L, I, P, L, I, P, L, I, I, I, I, I, P, I, F, I, P, P])
+    sig("ob_gemm2_swiglu_bf16", [P, L, P, P, L, P, P, P, L, I, I, I, P, P])
     sig("ob_rmsnorm_fwd", [P, P, P, P, P, P, I, I, F, P])
     sig("ob_rmsnorm_fwd_fp8", [P, P, P, P, P, P, P, P, L, I, I, F, P])
     sig("ob_rmsnorm_bwd", [P, P, P, P, P, P, P, P, P, I, I, I, P])
@@ -216,7 +218,7 @@ def _declare(l: ctypes.CDLL) -> None:
     PP = ctypes.POINTER(c_void_p)
     sig("ob_barrier", [PP, I, I, I, P, P])
     sig("ob_pull", [P, I, PP, I, P, P, I, I, P])
-    sig("ob_rs_adamw", [I, P, I, PP, I, P, P, P, P, P, F, F, F, F, F, F, F, F, P, P, P, I, P, P])
+    sig("ob_rs_adamw", [I, P, I, PP, I, P, P, P, P, P, F, F, F, F, F, F, F, F, P, I, I, P, P])
     sig("ob_set_flag_wait_iters", [ctypes.c_uint])
     sig("ob_gemm_ag_bf16", [P, L, P, L, P, L, I, I, I, P, P, I, PP, I, P, P, I, I, I, I, I, P, P])
     sig("ob_gemm_ag_act_bf16", [P, L, P, P, L, I, P, P, P, L, I, I, I, P, P, I, PP, I, P, P, I, I, I, I, P, P])

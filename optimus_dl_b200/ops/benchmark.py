@@ -73,15 +73,52 @@ def _emit(op: str, case: dict, ms: float, flops: float = 0.0, bytes_: float = 0.
 
 
 def bench_gemm_bf16(t: Timer, sizes) -> None:
+    """Forward layout (A and B reduction-major) for every size, then the dgrad (B read MN-major) and wgrad (both
+    operands MN-major, K = tokens) layouts of the flagship MLP shapes; each against ``torch.matmul`` on the same
+    operands, and with the one-SM kernel for comparison where the two-SM kernel is the default."""
     from . import gemm
+
+    def run(tag, M, N, K, a, b, a_mn, b_mn, ref):
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        ms = t(lambda: gemm.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out))
+        saved, gemm.USE_2SM = gemm.USE_2SM, False
+        ms1 = t(lambda: gemm.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out))
+        gemm.USE_2SM = saved
+        ms_ref = t(lambda: ref(out))
+        _emit("gemm_bf16", dict(layout=tag, M=M, N=N, K=K), ms, flops=2.0 * M * N * K, one_sm_kernel_ms=round(ms1, 4),
+              cublas_ms=round(ms_ref, 4), vs_cublas=round(ms_ref / ms, 3))
 
     for M, N, K in sizes:
         a = torch.randn(M, K, device="cuda").bfloat16()
         b = torch.randn(N, K, device="cuda").bfloat16()
-        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-        ms = t(lambda: gemm.gemm(a, b, out=out))
-        ms_ref = t(lambda: torch.matmul(a, b.t(), out=out))
-        _emit("gemm_bf16", dict(M=M, N=N, K=K), ms, flops=2.0 * M * N * K, cublas_ms=round(ms_ref, 4))
+        run("fwd  x[M,K] w[N,K]^T", M, N, K, a, b, False, False, lambda o: torch.matmul(a, b.t(), out=o))
+    if len(sizes) > 1:
+        for M, N, K in [(8192, 14336, 4096), (8192, 4096, 14336)]:
+            a = torch.randn(M, K, device="cuda").bfloat16()
+            w = torch.randn(K, N, device="cuda").bfloat16()      # dgrad: dy[M,K] @ W[K,N], W read MN-major
+            run("dgrad dy[M,K] w[K,N]", M, N, K, a, w, False, True, lambda o: torch.matmul(a, w, out=o))
+        for M, N, K in [(14336, 4096, 8192), (4096, 14336, 8192), (6144, 4096, 8192)]:
+            dy = torch.randn(K, M, device="cuda").bfloat16()     # wgrad: dy[K,M]^T @ x[K,N]
+            x = torch.randn(K, N, device="cuda").bfloat16()
+            run("wgrad dy[K,M]^T x[K,N]", M, N, K, dy, x, True, True, lambda o: torch.matmul(dy.t(), x, out=o))
+        M, N, K = 8192, 14336, 4096
+        x = torch.randn(M, K, device="cuda").bfloat16()
+        w1 = torch.randn(N, K, device="cuda").bfloat16()
+        w2 = torch.randn(N, K, device="cuda").bfloat16()
+        ms = t(lambda: gemm.swiglu_gemm(x, w1, w2))
+        saved, gemm.USE_2SM = gemm.USE_2SM, False
+        ms1 = t(lambda: gemm.swiglu_gemm(x, w1, w2))
+        gemm.USE_2SM = saved
+        g = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        u = torch.empty_like(g)
+
+        def lib():
+            torch.matmul(x, w1.t(), out=g)
+            torch.matmul(x, w2.t(), out=u)
+            return torch.nn.functional.silu(g) * u
+
+        _emit("gemm_swiglu_dual_b", dict(M=M, N=N, K=K), ms, flops=4.0 * M * N * K, one_sm_kernel_ms=round(ms1, 4),
+              cublas_plus_eager_ms=round(t(lib), 4))
 
 
 def bench_gemm_fp8(t: Timer, sizes) -> None:
@@ -127,6 +164,36 @@ def bench_attention(t: Timer, cases) -> None:
 
         ms_fb = t(fb)
         _emit("attention_fwd_bwd", dict(T=T, Hq=Hq, Hk=Hk, hd=hd), ms_fb, flops=flops_f * 3.5)
+        # the kernels the reference reaches for the same problem (optimus_dl/modules/model/blocks/attention.py:
+        # flash_attn_varlen_func at 390-401, scaled_dot_product_attention at 511-520), same harness
+        q = torch.randn(1, T, Hq, hd, device="cuda").bfloat16().requires_grad_(True)
+        k = torch.randn(1, T, Hk, hd, device="cuda").bfloat16().requires_grad_(True)
+        v = torch.randn(1, T, Hk, hd, device="cuda").bfloat16().requires_grad_(True)
+        do = torch.randn(1, T, Hq, hd, device="cuda").bfloat16()
+        libs = {}
+        try:
+            from flash_attn import flash_attn_func
+
+            libs["flash_attn"] = lambda: flash_attn_func(q, k, v, causal=True)
+        except Exception:  # noqa: BLE001
+            pass
+        qt, kt, vt = (x.transpose(1, 2) for x in (q, k, v))
+        libs["torch_sdpa"] = lambda: torch.nn.functional.scaled_dot_product_attention(qt, kt, vt, is_causal=True, enable_gqa=True)
+        for name, fwd in libs.items():
+            try:
+                with torch.no_grad():
+                    ms_lf = t(fwd)
+
+                def lfb():
+                    q.grad = k.grad = v.grad = None
+                    o = fwd()
+                    o.backward(do if o.shape == do.shape else do.transpose(1, 2))
+
+                ms_lfb = t(lfb)
+                _emit(f"attention_library_{name}", dict(T=T, Hq=Hq, Hk=Hk, hd=hd), ms_lfb, flops=flops_f * 3.5,
+                      fwd_ms=round(ms_lf, 4), fwd_tflops=round(flops_f / ms_lf / 1e9, 1))
+            except Exception as e:  # noqa: BLE001
+                print(json.dumps({"op": f"attention_library_{name}", "error": str(e)[:200]}), flush=True)
 
 
 def bench_decode(t: Timer, cases) -> None:

@@ -2,7 +2,7 @@
 //   ob_barrier       : bounded cross-GPU barrier on a symmetric flag array
 //   ob_pull          : all-gather as P2P pulls of copy tasks (no staging, lands in place)
 //   ob_rs_adamw      : gradient reduce-scatter fused with bf16->fp32 cast, scaling, optional
-//                      squared-norm partial and the sharded AdamW update (three modes)
+//                      fp32 accumulation and the sharded AdamW update (three modes)
 // The GEMM that overlaps an all-gather with its own tiles lives in gemm_ag.cu.
 #include "comm.cuh"
 
@@ -39,10 +39,11 @@ pull_kernel(const CopyTask* __restrict__ tasks, int n_tasks, PeerPtrs src, __nv_
   run_copy_tasks(tasks, n_tasks, blockIdx.x, gridDim.x, src, dst, flags, epoch);
 }
 
-// One owned slice of a parameter: `numel` elements that sit at `flat_off` in the (symmetric) flat
-// gradient / parameter buffers and at `shard_off` in this rank's fp32 shard state.
+// One owned slice of a parameter: `numel` elements that sit at `grad_off` in every rank's (symmetric) gradient
+// buffer, at `param_off` in this rank's bf16 parameter shard and at `shard_off` in its fp32 shard state.
 struct Segment {
-  long long flat_off;
+  long long grad_off;
+  long long param_off;
   long long shard_off;
   int numel;
   float weight_decay;
@@ -59,15 +60,35 @@ struct AdamArgs {
 
 enum Mode : int { kFused = 0, kReduceOnly = 1, kUpdateOnly = 2 };
 
-// MODE kFused     : g = sum_r peer_grad[r][flat]  -> AdamW -> master/m/v, bf16 param out
-// MODE kReduceOnly: g -> grad_shard (fp32), per-block partial of sum g^2 (for the global norm)
-// MODE kUpdateOnly: g = grad_shard -> AdamW (with clip) -> master/m/v, bf16 param out
+// Sum of the ranks' bf16 gradients for 8 consecutive elements, in fixed rank order (every owner adds in the same
+// order, so results are reproducible).  The loads of up to four ranks are issued before the first add; they are
+// weak, non-allocating loads: the data was published before the barrier this launch is ordered after.
+__device__ __forceinline__ void reduce_peers_8(const PeerPtrs& grads, int world, long long off, int i, float* g) {
+  for (int r0 = 0; r0 < world; r0 += 4) {
+    uint4 u[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (r0 + j < world)
+        u[j] = ld_peer_bulk_16(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(grads.p[r0 + j]) + off) + i);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (r0 + j < world) {
+        const float2 a0 = unpack_bf16x2(u[j].x), a1 = unpack_bf16x2(u[j].y), a2 = unpack_bf16x2(u[j].z), a3 = unpack_bf16x2(u[j].w);
+        g[0] += a0.x; g[1] += a0.y; g[2] += a1.x; g[3] += a1.y; g[4] += a2.x; g[5] += a2.y; g[6] += a3.x; g[7] += a3.y;
+      }
+  }
+}
+
+// MODE kFused     : g = [grad_shard +] sum_r peer_grad[r]  -> AdamW -> master/m/v, bf16 shard out
+// MODE kReduceOnly: grad_shard = [grad_shard +] sum_r peer_grad[r]            (fp32 accumulation over micro-batches)
+// MODE kUpdateOnly: g = grad_shard -> AdamW (with clip) -> master/m/v, bf16 shard out
+// `acc_in` selects the bracketed term.
 template <int MODE>
 __global__ void __launch_bounds__(256)
 rs_adamw_kernel(const Segment* __restrict__ segs, int n_segs, PeerPtrs grads, int world,
                 float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
-                float* __restrict__ grad_shard, __nv_bfloat16* __restrict__ param_out, AdamArgs a,
-                float* __restrict__ sq_partials, const int* __restrict__ status) {
+                float* __restrict__ grad_shard, __nv_bfloat16* __restrict__ param_out, AdamArgs a, int acc_in,
+                const int* __restrict__ status) {
   // A step whose barrier (or any earlier kernel) reported a failed wait must not be committed: the peers'
   // gradient buffers may be half written. The status word is sticky until the host reads and clears it.
   if (MODE != kReduceOnly && status != nullptr && *reinterpret_cast<const volatile int*>(status) != kStatusOk) return;
@@ -77,36 +98,27 @@ rs_adamw_kernel(const Segment* __restrict__ segs, int n_segs, PeerPtrs grads, in
     scale *= fminf(1.0f, a.max_norm / (norm + 1e-6f));
   }
   const float inv_sqrt_bc2 = rsqrtf(a.bc2);
-  float sq = 0.f;
   for (int s = 0; s < n_segs; ++s) {
     const Segment seg = segs[s];
-    const bool aligned = (seg.flat_off % 8 == 0) && (seg.shard_off % 4 == 0);
+    const bool aligned = (seg.grad_off % 8 == 0) && (seg.param_off % 8 == 0) && (seg.shard_off % 4 == 0);
     const int nvec = aligned ? seg.numel / 8 : 0;
     const float lr = a.lr * seg.lr_scale;
     const float step = lr / a.bc1;
     const float decay = 1.0f - lr * seg.weight_decay;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += gridDim.x * blockDim.x) {
       float g[8];
-      if (MODE == kUpdateOnly) {
-        const float4 g0 = reinterpret_cast<const float4*>(grad_shard + seg.shard_off)[2 * i];
-        const float4 g1 = reinterpret_cast<const float4*>(grad_shard + seg.shard_off)[2 * i + 1];
+      float4* gs = reinterpret_cast<float4*>(grad_shard + seg.shard_off) + 2 * i;
+      if (MODE == kUpdateOnly || acc_in) {
+        const float4 g0 = gs[0], g1 = gs[1];
         g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w; g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
       } else {
 #pragma unroll
         for (int j = 0; j < 8; ++j) g[j] = 0.f;
-        // fixed rank order: every owner adds in the same order, so results are reproducible
-        for (int r = 0; r < world; ++r) {
-          const uint4 u = ld_peer_16(reinterpret_cast<const uint4*>(
-                                         reinterpret_cast<const __nv_bfloat16*>(grads.p[r]) + seg.flat_off) + i);
-          const float2 a0 = unpack_bf16x2(u.x), a1 = unpack_bf16x2(u.y), a2 = unpack_bf16x2(u.z), a3 = unpack_bf16x2(u.w);
-          g[0] += a0.x; g[1] += a0.y; g[2] += a1.x; g[3] += a1.y; g[4] += a2.x; g[5] += a2.y; g[6] += a3.x; g[7] += a3.y;
-        }
       }
+      if (MODE != kUpdateOnly) reduce_peers_8(grads, world, seg.grad_off, i, g);
       if (MODE == kReduceOnly) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) sq += g[j] * g[j];
-        reinterpret_cast<float4*>(grad_shard + seg.shard_off)[2 * i] = make_float4(g[0], g[1], g[2], g[3]);
-        reinterpret_cast<float4*>(grad_shard + seg.shard_off)[2 * i + 1] = make_float4(g[4], g[5], g[6], g[7]);
+        gs[0] = make_float4(g[0], g[1], g[2], g[3]);
+        gs[1] = make_float4(g[4], g[5], g[6], g[7]);
         continue;
       }
       float4* mp = reinterpret_cast<float4*>(master + seg.shard_off) + 2 * i;
@@ -126,47 +138,25 @@ rs_adamw_kernel(const Segment* __restrict__ segs, int n_segs, PeerPtrs grads, in
       mp[0] = make_float4(p[0], p[1], p[2], p[3]); mp[1] = make_float4(p[4], p[5], p[6], p[7]);
       mm[0] = make_float4(mo[0], mo[1], mo[2], mo[3]); mm[1] = make_float4(mo[4], mo[5], mo[6], mo[7]);
       vv[0] = make_float4(vo[0], vo[1], vo[2], vo[3]); vv[1] = make_float4(vo[4], vo[5], vo[6], vo[7]);
-      reinterpret_cast<uint4*>(param_out + seg.flat_off)[i] =
+      reinterpret_cast<uint4*>(param_out + seg.param_off)[i] =
           make_uint4(pack_bf16x2(p[0], p[1]), pack_bf16x2(p[2], p[3]), pack_bf16x2(p[4], p[5]), pack_bf16x2(p[6], p[7]));
     }
     // scalar tail (segments whose length is not a multiple of 8)
     for (int i = nvec * 8 + blockIdx.x * blockDim.x + threadIdx.x; i < seg.numel; i += gridDim.x * blockDim.x) {
-      float g = 0.f;
-      if (MODE == kUpdateOnly) {
-        g = grad_shard[seg.shard_off + i];
-      } else {
-        for (int r = 0; r < world; ++r)
-          g += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(grads.p[r])[seg.flat_off + i]);
-      }
-      if (MODE == kReduceOnly) { sq += g * g; grad_shard[seg.shard_off + i] = g; continue; }
-      const float gj = g * scale;
       const long long k = seg.shard_off + i;
+      float g = (MODE == kUpdateOnly || acc_in) ? grad_shard[k] : 0.f;
+      if (MODE != kUpdateOnly) {
+        for (int r = 0; r < world; ++r)
+          g += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(grads.p[r])[seg.grad_off + i]);
+      }
+      if (MODE == kReduceOnly) { grad_shard[k] = g; continue; }
+      const float gj = g * scale;
       const float mo = a.beta1 * m[k] + (1.0f - a.beta1) * gj;
       const float vo = a.beta2 * v[k] + (1.0f - a.beta2) * gj * gj;
       const float p = master[k] * decay - step * mo / (sqrtf(vo) * inv_sqrt_bc2 + a.eps);
       master[k] = p; m[k] = mo; v[k] = vo;
-      param_out[seg.flat_off + i] = __float2bfloat16(p);
+      param_out[seg.param_off + i] = __float2bfloat16(p);
     }
-  }
-  if (MODE == kReduceOnly && sq_partials) {
-    __shared__ float red[8];
-    sq = warp_sum(sq);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      float t = 0.f;
-      for (int w = 0; w < 8; ++w) t += red[w];
-      sq_partials[blockIdx.x] = t;
-    }
-  }
-}
-
-// out (+)= sum of partials in index order (single thread: a few hundred values)
-__global__ void sum_partials_kernel(const float* __restrict__ partials, int n, float* __restrict__ out, int accumulate) {
-  if (threadIdx.x == 0 && blockIdx.x == 0) {
-    float t = 0.f;
-    for (int i = 0; i < n; ++i) t += partials[i];
-    *out = accumulate ? *out + t : t;
   }
 }
 
@@ -290,31 +280,30 @@ extern "C" int ob_pull(const void* tasks, int n_tasks, const void* const* src_pt
   return (int)cudaGetLastError();
 }
 
-// mode: 0 fused reduce+AdamW, 1 reduce only (writes grad_shard, adds sum of squares to *sumsq_out),
-//       2 AdamW from grad_shard.  sq_scratch: >= n_ctas floats (mode 1).
+// mode: 0 reduce + AdamW in one pass, 1 reduce into the fp32 gradient shard, 2 AdamW from the gradient shard.
+// acc_in (modes 0 and 1): start from the gradient shard instead of zero (gradient accumulation in fp32).
+// The update modes do nothing while *status is non-zero (a failed wait earlier in the step).
 extern "C" int ob_rs_adamw(int mode, const void* segs, int n_segs, const void* const* grad_ptrs, int world,
                            void* master, void* m, void* v, void* grad_shard, void* param_out, float lr, float beta1,
                            float beta2, float eps, float bc1, float bc2, float grad_scale, float max_norm,
-                           const void* sumsq_in, void* sq_scratch, void* sumsq_out, int n_ctas, const int* status,
-                           cudaStream_t stream) {
+                           const void* sumsq_in, int acc_in, int n_ctas, const int* status, cudaStream_t stream) {
   if (world > MAX_RANKS) return -1;
   if (n_segs == 0) return 0;
-  if (n_ctas <= 0) n_ctas = 148 * 2;
+  if ((mode != kFused || acc_in) && grad_shard == nullptr) return -2;
+  if (n_ctas <= 0) n_ctas = 148 * 6;
   AdamArgs a{lr, beta1, beta2, eps, bc1, bc2, grad_scale, max_norm, (const float*)sumsq_in};
   PeerPtrs g = make_peers(grad_ptrs, world);
   if (mode == kFused)
     rs_adamw_kernel<kFused><<<n_ctas, 256, 0, stream>>>((const Segment*)segs, n_segs, g, world, (float*)master,
-                                                        (float*)m, (float*)v, nullptr, (__nv_bfloat16*)param_out, a,
-                                                        nullptr, status);
-  else if (mode == kReduceOnly) {
+                                                        (float*)m, (float*)v, (float*)grad_shard,
+                                                        (__nv_bfloat16*)param_out, a, acc_in, status);
+  else if (mode == kReduceOnly)
     rs_adamw_kernel<kReduceOnly><<<n_ctas, 256, 0, stream>>>((const Segment*)segs, n_segs, g, world, nullptr, nullptr,
-                                                             nullptr, (float*)grad_shard, nullptr, a,
-                                                             (float*)sq_scratch, status);
-    if (sumsq_out) sum_partials_kernel<<<1, 32, 0, stream>>>((const float*)sq_scratch, n_ctas, (float*)sumsq_out, 1);
-  } else
+                                                             nullptr, (float*)grad_shard, nullptr, a, acc_in, status);
+  else
     rs_adamw_kernel<kUpdateOnly><<<n_ctas, 256, 0, stream>>>((const Segment*)segs, n_segs, g, world, (float*)master,
                                                              (float*)m, (float*)v, (float*)grad_shard,
-                                                             (__nv_bfloat16*)param_out, a, nullptr, status);
+                                                             (__nv_bfloat16*)param_out, a, 0, status);
   return (int)cudaGetLastError();
 }
 

@@ -15,11 +15,12 @@ struct PeerPtrs {
   void* p[MAX_RANKS];
 };
 
-// One unit of copy work: `numel` bf16 elements at element offset `offset` (same offset on both
-// sides: buffers are symmetric) pulled from rank `peer`.  `flag` >= 0 names a readiness flag that
-// is set to the launch's epoch when the chunk has landed.
+// One unit of copy work: `numel` bf16 elements pulled from element offset `src_offset` of rank `peer`'s buffer
+// to element offset `offset` of the local one (the push form uses `offset` on the peer's side).  `flag` >= 0
+// names a readiness flag that is set to the launch's epoch when the chunk has landed.
 struct CopyTask {
   long long offset;
+  long long src_offset;
   int numel;
   short peer;
   short pad;
@@ -54,9 +55,9 @@ __device__ __forceinline__ void run_copy_tasks(const CopyTask* tasks, int n_task
                                                const PeerPtrs& src, __nv_bfloat16* dst, int* flags, int epoch) {
   for (int t = first; t < n_tasks; t += stride) {
     const CopyTask task = tasks[t];
-    const __nv_bfloat16* s = reinterpret_cast<const __nv_bfloat16*>(src.p[task.peer]) + task.offset;
+    const __nv_bfloat16* s = reinterpret_cast<const __nv_bfloat16*>(src.p[task.peer]) + task.src_offset;
     __nv_bfloat16* d = dst + task.offset;
-    const int nvec = (task.offset % 8 == 0) ? task.numel / 8 : 0;
+    const int nvec = (task.offset % 8 == 0 && task.src_offset % 8 == 0) ? task.numel / 8 : 0;
     int i = threadIdx.x;
     for (; i + (UNROLL - 1) * (int)blockDim.x < nvec; i += UNROLL * blockDim.x) {
       uint4 v[UNROLL];

@@ -145,6 +145,157 @@ __device__ __forceinline__ float apply_act(float x, int act) {
   }
 }
 
+// Epilogue of one 128 x 256 accumulator tile, executed by one epilogue warp for its 32 TMEM lanes:
+// `t_row` is the TMEM address of the warp's first lane at the tile's first column, (m0, n0) the tile origin in C.
+template <int SWIGLU>
+__device__ __forceinline__ void epilogue_tile(const Params& p, int m0, int n0, uint32_t t_row, int warp, int lane,
+                                              bool vec_ok, __nv_bfloat16* rs_stage_base) {
+  const int quarter = warp & 3;
+  const int row = m0 + quarter * 32 + lane;
+  if (SWIGLU) {
+    // columns [0,128) hold the gate product, [128,256) the up product
+#pragma unroll 1
+    for (int c = 0; c < 128; c += 32) {
+      uint32_t g[32], u[32];
+      tmem_ld_32x32(t_row + c, g);
+      tmem_ld_32x32(t_row + 128 + c, u);
+      tmem_ld_wait();
+      if (row < p.M) {
+        const int col = n0 + c;
+        __nv_bfloat16* hrow = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col;
+        __nv_bfloat16* grow = p.G ? reinterpret_cast<__nv_bfloat16*>(p.G) + (long long)row * p.ldc + col : nullptr;
+        __nv_bfloat16* urow = p.U ? reinterpret_cast<__nv_bfloat16*>(p.U) + (long long)row * p.ldc + col : nullptr;
+        if (vec_ok && col + 32 <= p.N) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint32_t hp[4], gp[4], up[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              // round the gate and up products to bf16 first, as the unfused path does
+              float g0 = __bfloat162float(__float2bfloat16(__uint_as_float(g[v * 8 + 2 * j])));
+              float g1 = __bfloat162float(__float2bfloat16(__uint_as_float(g[v * 8 + 2 * j + 1])));
+              float u0 = __bfloat162float(__float2bfloat16(__uint_as_float(u[v * 8 + 2 * j])));
+              float u1 = __bfloat162float(__float2bfloat16(__uint_as_float(u[v * 8 + 2 * j + 1])));
+              gp[j] = pack_bf16x2(g0, g1);
+              up[j] = pack_bf16x2(u0, u1);
+              hp[j] = pack_bf16x2(g0 / (1.0f + __expf(-g0)) * u0, g1 / (1.0f + __expf(-g1)) * u1);
+            }
+            *reinterpret_cast<uint4*>(hrow + v * 8) = make_uint4(hp[0], hp[1], hp[2], hp[3]);
+            if (grow) *reinterpret_cast<uint4*>(grow + v * 8) = make_uint4(gp[0], gp[1], gp[2], gp[3]);
+            if (urow) *reinterpret_cast<uint4*>(urow + v * 8) = make_uint4(up[0], up[1], up[2], up[3]);
+          }
+        } else {
+          for (int j = 0; j < 32; ++j) {
+            if (col + j < p.N) {
+              float g0 = __bfloat162float(__float2bfloat16(__uint_as_float(g[j])));
+              float u0 = __bfloat162float(__float2bfloat16(__uint_as_float(u[j])));
+              hrow[j] = __float2bfloat16(g0 / (1.0f + __expf(-g0)) * u0);
+              if (grow) grow[j] = __float2bfloat16(g0);
+              if (urow) urow[j] = __float2bfloat16(u0);
+            }
+          }
+        }
+      }
+    }
+  } else {
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 32) {
+      const int col = n0 + c;
+      if (col >= p.N) break;   // warp-uniform
+      uint32_t r[32];
+      tmem_ld_32x32(t_row + c, r);
+      tmem_ld_wait();
+      if (row < p.M) {
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+        if (p.bias) {
+          const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(p.bias) + col;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) if (col + j < p.N) v[j] += __bfloat162float(b[j]);
+        }
+        if (p.act != kActNone) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.act);
+        }
+        if (p.out_fp32) {
+          float* crow = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col;
+          if ((p.ldc % 4 == 0) && col + 32 <= p.N && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0)) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              float4 o = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+              if (p.accumulate) {
+                float4 old = *reinterpret_cast<float4*>(crow + 4 * q);
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              *reinterpret_cast<float4*>(crow + 4 * q) = o;
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (col + j < p.N) crow[j] = p.accumulate ? crow[j] + v[j] : v[j];
+          }
+        } else {
+          __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col;
+          // with `accumulate` the addend is always read from the local C, also in reduce-scatter mode
+          const __nv_bfloat16* srow = crow;
+          if (p.rs_rows > 0) {
+            // reduce-scatter mode: park the 32 columns in this warp's staging rows; the flush below
+            // (outside the row guard, all lanes take part) sends them as 128-byte segments
+            if (p.accumulate) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col + j < p.N) v[j] += __bfloat162float(srow[j]);
+            }
+            __nv_bfloat16* st = rs_stage_base + ((warp & 3) * 32 + lane) * RS_ROW_ELEMS + ((c >> 5) & 1) * 32;
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              *reinterpret_cast<uint4*>(st + 8 * q) =
+                  make_uint4(pack_bf16x2(v[8 * q], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
+                             pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+          } else
+          if (vec_ok && col + 32 <= p.N) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (p.accumulate) {
+                uint4 old = *reinterpret_cast<const uint4*>(srow + 8 * q);
+                float2 a0 = unpack_bf16x2(old.x), a1 = unpack_bf16x2(old.y), a2 = unpack_bf16x2(old.z),
+                       a3 = unpack_bf16x2(old.w);
+                v[8 * q] += a0.x; v[8 * q + 1] += a0.y; v[8 * q + 2] += a1.x; v[8 * q + 3] += a1.y;
+                v[8 * q + 4] += a2.x; v[8 * q + 5] += a2.y; v[8 * q + 6] += a3.x; v[8 * q + 7] += a3.y;
+              }
+              uint4 o = make_uint4(pack_bf16x2(v[8 * q], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
+                                   pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+              *reinterpret_cast<uint4*>(crow + 8 * q) = o;
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (col + j < p.N)
+                crow[j] = __float2bfloat16(p.accumulate ? __bfloat162float(srow[j]) + v[j] : v[j]);
+          }
+        }
+      }
+      if (p.rs_rows > 0 && (((c >> 5) & 1) == 1 || c + 32 >= BN || n0 + c + 32 >= p.N)) {
+        __syncwarp();
+        const __nv_bfloat16* stw = rs_stage_base + (warp & 3) * 32 * RS_ROW_ELEMS;
+        const int seg = lane & 7;
+        const int colg = n0 + (c & ~63) + seg * 8;
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int rr = it * 4 + (lane >> 3);
+          const int rowg = m0 + quarter * 32 + rr;
+          if (rowg < p.M && colg < p.N && (colg < n0 + c + 32)) {
+            const int owner = rowg / p.rs_rows;
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.rs_dst[owner]) +
+                                 ((long long)p.rs_me * p.rs_rows + (rowg - owner * p.rs_rows)) * p.ldc + colg;
+            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(stw + rr * RS_ROW_ELEMS + seg * 8);
+          }
+        }
+        __syncwarp();
+      }
+    }
+  }
+}
+
 // One CTA's share of the persistent GEMM. `first_tile`/`tile_stride` give the static
 // tile schedule (callers with extra non-GEMM CTAs pass the GEMM CTA index and count).
 template <int A_MN, int B_MN, int SWIGLU>
@@ -285,150 +436,8 @@ __device__ __forceinline__ void gemm_cta(const CUtensorMap* tmA, const CUtensorM
       ok = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status);
       if (!ok) break;
       tc_fence_after();
-      const int row = m0 + quarter * 32 + lane;
-      const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
-      if (SWIGLU) {
-        // columns [0,128) hold the gate product, [128,256) the up product
-#pragma unroll 1
-        for (int c = 0; c < 128; c += 32) {
-          uint32_t g[32], u[32];
-          tmem_ld_32x32(t_row + c, g);
-          tmem_ld_32x32(t_row + 128 + c, u);
-          tmem_ld_wait();
-          if (row < p.M) {
-            const int col = n0 + c;
-            __nv_bfloat16* hrow = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col;
-            __nv_bfloat16* grow = p.G ? reinterpret_cast<__nv_bfloat16*>(p.G) + (long long)row * p.ldc + col : nullptr;
-            __nv_bfloat16* urow = p.U ? reinterpret_cast<__nv_bfloat16*>(p.U) + (long long)row * p.ldc + col : nullptr;
-            if (vec_ok && col + 32 <= p.N) {
-#pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                uint32_t hp[4], gp[4], up[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  // round the gate and up products to bf16 first, as the unfused path does
-                  float g0 = __bfloat162float(__float2bfloat16(__uint_as_float(g[v * 8 + 2 * j])));
-                  float g1 = __bfloat162float(__float2bfloat16(__uint_as_float(g[v * 8 + 2 * j + 1])));
-                  float u0 = __bfloat162float(__float2bfloat16(__uint_as_float(u[v * 8 + 2 * j])));
-                  float u1 = __bfloat162float(__float2bfloat16(__uint_as_float(u[v * 8 + 2 * j + 1])));
-                  gp[j] = pack_bf16x2(g0, g1);
-                  up[j] = pack_bf16x2(u0, u1);
-                  hp[j] = pack_bf16x2(g0 / (1.0f + __expf(-g0)) * u0, g1 / (1.0f + __expf(-g1)) * u1);
-                }
-                *reinterpret_cast<uint4*>(hrow + v * 8) = make_uint4(hp[0], hp[1], hp[2], hp[3]);
-                if (grow) *reinterpret_cast<uint4*>(grow + v * 8) = make_uint4(gp[0], gp[1], gp[2], gp[3]);
-                if (urow) *reinterpret_cast<uint4*>(urow + v * 8) = make_uint4(up[0], up[1], up[2], up[3]);
-              }
-            } else {
-              for (int j = 0; j < 32; ++j) {
-                if (col + j < p.N) {
-                  float g0 = __bfloat162float(__float2bfloat16(__uint_as_float(g[j])));
-                  float u0 = __bfloat162float(__float2bfloat16(__uint_as_float(u[j])));
-                  hrow[j] = __float2bfloat16(g0 / (1.0f + __expf(-g0)) * u0);
-                  if (grow) grow[j] = __float2bfloat16(g0);
-                  if (urow) urow[j] = __float2bfloat16(u0);
-                }
-              }
-            }
-          }
-        }
-      } else {
-#pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
-          const int col = n0 + c;
-          if (col >= p.N) break;   // warp-uniform
-          uint32_t r[32];
-          tmem_ld_32x32(t_row + c, r);
-          tmem_ld_wait();
-          if (row < p.M) {
-            float v[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
-            if (p.bias) {
-              const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(p.bias) + col;
-#pragma unroll
-              for (int j = 0; j < 32; ++j) if (col + j < p.N) v[j] += __bfloat162float(b[j]);
-            }
-            if (p.act != kActNone) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.act);
-            }
-            if (p.out_fp32) {
-              float* crow = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col;
-              if ((p.ldc % 4 == 0) && col + 32 <= p.N && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0)) {
-#pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                  float4 o = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-                  if (p.accumulate) {
-                    float4 old = *reinterpret_cast<float4*>(crow + 4 * q);
-                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                  }
-                  *reinterpret_cast<float4*>(crow + 4 * q) = o;
-                }
-              } else {
-                for (int j = 0; j < 32; ++j)
-                  if (col + j < p.N) crow[j] = p.accumulate ? crow[j] + v[j] : v[j];
-              }
-            } else {
-              __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col;
-              // with `accumulate` the addend is always read from the local C, also in reduce-scatter mode
-              const __nv_bfloat16* srow = crow;
-              if (p.rs_rows > 0) {
-                // reduce-scatter mode: park the 32 columns in this warp's staging rows; the flush below
-                // (outside the row guard, all lanes take part) sends them as 128-byte segments
-                if (p.accumulate) {
-#pragma unroll
-                  for (int j = 0; j < 32; ++j)
-                    if (col + j < p.N) v[j] += __bfloat162float(srow[j]);
-                }
-                __nv_bfloat16* st = rs_stage_base + ((warp & 3) * 32 + lane) * RS_ROW_ELEMS + ((c >> 5) & 1) * 32;
-#pragma unroll
-                for (int q = 0; q < 4; ++q)
-                  *reinterpret_cast<uint4*>(st + 8 * q) =
-                      make_uint4(pack_bf16x2(v[8 * q], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
-                                 pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
-              } else
-              if (vec_ok && col + 32 <= p.N) {
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  if (p.accumulate) {
-                    uint4 old = *reinterpret_cast<const uint4*>(srow + 8 * q);
-                    float2 a0 = unpack_bf16x2(old.x), a1 = unpack_bf16x2(old.y), a2 = unpack_bf16x2(old.z),
-                           a3 = unpack_bf16x2(old.w);
-                    v[8 * q] += a0.x; v[8 * q + 1] += a0.y; v[8 * q + 2] += a1.x; v[8 * q + 3] += a1.y;
-                    v[8 * q + 4] += a2.x; v[8 * q + 5] += a2.y; v[8 * q + 6] += a3.x; v[8 * q + 7] += a3.y;
-                  }
-                  uint4 o = make_uint4(pack_bf16x2(v[8 * q], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
-                                       pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
-                  *reinterpret_cast<uint4*>(crow + 8 * q) = o;
-                }
-              } else {
-                for (int j = 0; j < 32; ++j)
-                  if (col + j < p.N)
-                    crow[j] = __float2bfloat16(p.accumulate ? __bfloat162float(srow[j]) + v[j] : v[j]);
-              }
-            }
-          }
-          if (p.rs_rows > 0 && (((c >> 5) & 1) == 1 || c + 32 >= BN || n0 + c + 32 >= p.N)) {
-            __syncwarp();
-            const __nv_bfloat16* stw = rs_stage_base + (warp & 3) * 32 * RS_ROW_ELEMS;
-            const int seg = lane & 7;
-            const int colg = n0 + (c & ~63) + seg * 8;
-#pragma unroll
-            for (int it = 0; it < 8; ++it) {
-              const int rr = it * 4 + (lane >> 3);
-              const int rowg = m0 + quarter * 32 + rr;
-              if (rowg < p.M && colg < p.N && (colg < n0 + c + 32)) {
-                const int owner = rowg / p.rs_rows;
-                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.rs_dst[owner]) +
-                                     ((long long)p.rs_me * p.rs_rows + (rowg - owner * p.rs_rows)) * p.ldc + colg;
-                *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(stw + rr * RS_ROW_ELEMS + seg * 8);
-              }
-            }
-            __syncwarp();
-          }
-        }
-      }
+      epilogue_tile<SWIGLU>(p, m0, n0, tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN, warp, lane, vec_ok,
+                            rs_stage_base);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);

@@ -17,7 +17,14 @@ from __future__ import annotations
 
 import torch
 
+import os
+
 from . import _lib
+
+# Products with at least this many 256 x 256 tiles run on the two-SM kernel (csrc/gemm_2sm.cu): one tile per SM pair
+# and wave. OB_GEMM_2SM=0 keeps everything on the one-SM kernel (kept for A/B measurements in ops/benchmark.py).
+PAIR_MIN_TILES = 74
+USE_2SM = os.environ.get("OB_GEMM_2SM", "1") != "0"
 
 ACT = {"none": 0, "gelu": 1, "relu2": 2, "silu": 3}
 SKINNY_M = 64   # inference-only products with at most this many rows use the library GEMM (see gemm())
@@ -103,6 +110,16 @@ def gemm(
             out.add_(bias)
         return out
     l = _lib.lib()
+    if (USE_2SM and b_flags is None and a_flags is None and tile_order == 0
+            and ((M + 255) // 256) * ((N + 255) // 256) >= PAIR_MIN_TILES):
+        rc = l.ob_gemm2_bf16(
+            _lib.ptr(a), a.stride(0), int(a_mn), _lib.ptr(b), b.stride(0), int(b_mn),
+            _lib.ptr(out), out.stride(0), M, N, K, int(out.dtype == torch.float32), int(accumulate),
+            _lib.ptr(bias), ACT[act], float(alpha), int(max_ctas),
+            _lib.ptr(_lib.status_word(a.device)), _lib.stream(),
+        )
+        _lib.check(rc, "ob_gemm2_bf16")
+        return out
     rc = l.ob_gemm_bf16(
         _lib.ptr(a), a.stride(0), int(a_mn), _lib.ptr(b), b.stride(0), int(b_mn),
         _lib.ptr(out), out.stride(0), M, N, K, int(out.dtype == torch.float32), int(accumulate),
@@ -144,7 +161,9 @@ def swiglu_gemm(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, save_gu: bo
     h = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
     g = torch.empty_like(h) if save_gu else None
     u = torch.empty_like(h) if save_gu else None
-    rc = _lib.lib().ob_gemm_swiglu_bf16(
+    l = _lib.lib()
+    fn = l.ob_gemm2_swiglu_bf16 if (USE_2SM and ((M + 255) // 256) * ((N + 127) // 128) >= PAIR_MIN_TILES) else l.ob_gemm_swiglu_bf16
+    rc = fn(
         _lib.ptr(x2), x2.stride(0), _lib.ptr(w1), _lib.ptr(w2), w1.stride(0), _lib.ptr(h), _lib.ptr(g), _lib.ptr(u),
         h.stride(0), M, N, K, _lib.ptr(_lib.status_word(x.device)), _lib.stream(),
     )

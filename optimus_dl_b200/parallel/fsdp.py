@@ -289,7 +289,8 @@ class ShardGroup:
                                     _lib.ptr(self.grad_shard), _lib.ptr(self.flat_param), float(hp["lr"]), float(b1),
                                     float(b2), float(hp["eps"]), bc1, bc2, float(grad_scale), float(max_norm),
                                     _lib.ptr(sumsq) if mode == 2 else None, _lib.ptr(scratch),
-                                    _lib.ptr(sumsq) if mode == 1 else None, n_ctas, _lib.stream())
+                                    _lib.ptr(sumsq) if mode == 1 else None, n_ctas,
+                                    _lib.ptr(_lib.status_word(self.device)), _lib.stream())
         _lib.check(rc, "ob_rs_adamw")
 
     # ---------------------------------------------------------------- state dict helpers

@@ -105,23 +105,25 @@ class DeviceBarrier:
         _lib.check(rc, "ob_barrier")
 
 
-COPY_TASK_DTYPE = np.dtype([("offset", "<i8"), ("numel", "<i4"), ("peer", "<i2"), ("pad", "<i2"), ("flag", "<i4"),
-                            ("pad2", "<i4")])
-SEGMENT_DTYPE = np.dtype([("flat_off", "<i8"), ("shard_off", "<i8"), ("numel", "<i4"), ("weight_decay", "<f4"),
-                          ("lr_scale", "<f4"), ("pad", "<i4")])
+COPY_TASK_DTYPE = np.dtype([("offset", "<i8"), ("src_offset", "<i8"), ("numel", "<i4"), ("peer", "<i2"), ("pad", "<i2"),
+                            ("flag", "<i4"), ("pad2", "<i4")])
+SEGMENT_DTYPE = np.dtype([("grad_off", "<i8"), ("param_off", "<i8"), ("shard_off", "<i8"), ("numel", "<i4"),
+                          ("weight_decay", "<f4"), ("lr_scale", "<f4"), ("pad", "<i4")])
 
 
-def tasks_to_device(tasks: list[tuple[int, int, int, int]], device: torch.device) -> torch.Tensor:
-    """``[(offset, numel, peer, flag)]`` -> device byte tensor laid out as ``CopyTask[]``."""
+def tasks_to_device(tasks: list[tuple], device: torch.device) -> torch.Tensor:
+    """``[(offset, numel, peer, flag)]`` or ``[(offset, numel, peer, flag, src_offset)]`` -> device byte tensor laid
+    out as ``CopyTask[]`` (without a source offset the chunk sits at the same offset on both sides)."""
     arr = np.zeros(len(tasks), dtype=COPY_TASK_DTYPE)
-    for i, (off, n, peer, flag) in enumerate(tasks):
-        arr[i] = (off, n, peer, 0, flag, 0)
+    for i, t in enumerate(tasks):
+        off, n, peer, flag = t[:4]
+        arr[i] = (off, t[4] if len(t) > 4 else off, n, peer, 0, flag, 0)
     return torch.from_numpy(arr.view(np.uint8).copy()).to(device)
 
 
-def segments_to_device(segs: list[tuple[int, int, int, float, float]], device: torch.device) -> torch.Tensor:
-    """``[(flat_off, shard_off, numel, weight_decay, lr_scale)]`` -> device byte tensor of ``Segment[]``."""
+def segments_to_device(segs: list[tuple[int, int, int, int, float, float]], device: torch.device) -> torch.Tensor:
+    """``[(grad_off, param_off, shard_off, numel, weight_decay, lr_scale)]`` -> device byte tensor of ``Segment[]``."""
     arr = np.zeros(len(segs), dtype=SEGMENT_DTYPE)
-    for i, (fo, so, n, wd, ls) in enumerate(segs):
-        arr[i] = (fo, so, n, wd, ls, 0)
+    for i, (go, po, so, n, wd, ls) in enumerate(segs):
+        arr[i] = (go, po, so, n, wd, ls, 0)
     return torch.from_numpy(arr.view(np.uint8).copy()).to(device)
