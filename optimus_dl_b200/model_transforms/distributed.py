@@ -2,13 +2,16 @@
 
 ``fully_shard`` hands the model to this package's sharding engine (``parallel/fsdp.py``): one group
 per transformer block plus a root group, bf16 compute parameters, fp32 master shards, gradient
-averaging over the data-parallel ranks. The reference's knobs are accepted:
-``reshard_after_forward`` (parameters stay resident either way: the flat buffers are symmetric
-allocations that peers read), ``mixed_precision`` (``param_dtype`` must be bf16, ``reduce_dtype`` is
-fp32 inside the reduce kernel), ``offload`` (rejected: optimizer state lives in HBM),
-``sync_grad_accum`` and ``use_hybrid_sharding`` (the shard group is the ``dp_shard`` mesh dimension;
-replicas across ``dp_replicate`` are averaged with NCCL after the in-kernel reduce).
-``accumulation_context(model, is_last)`` toggles gradient synchronisation for micro-batches.
+averaging over the data-parallel ranks. The reference's knobs:
+``reshard_after_forward`` (``true`` or a positive int: a block's gathered parameters live in a small
+pool of buffers and are gathered again for its backward; together with the model's
+``shard_every_ith_layer`` only every i-th block does so), ``mixed_precision`` (``param_dtype`` must be
+bf16 and ``reduce_dtype`` fp32, which is what the reduce kernel does; ``output_dtype`` is refused, the
+blocks return bf16), ``offload`` (``cpu_offload: true`` is refused: optimizer state lives sharded in
+HBM), ``sync_grad_accum`` (gradients are reduced after every micro-batch in either setting: no rank
+keeps full-size gradients) and ``use_hybrid_sharding`` (the shard group is the ``dp_shard`` mesh
+dimension; replicas across ``dp_replicate`` are averaged with NCCL after the in-kernel reduce).
+``accumulation_context(model, is_last)`` tells the engine which micro-batch ends the step.
 """
 
 from __future__ import annotations
@@ -108,6 +111,7 @@ class FullyShardTransformConfig(RegistryConfig):
     fuse_optimizer_in_backward: bool = True
     copy_ctas: int = 16
     pull_ctas: int = 24
+    param_slots: int = 2         # pool size for resharded blocks (reshard_after_forward)
 
 
 @register_model_transform("fully_shard", FullyShardTransformConfig)
@@ -120,6 +124,13 @@ class FullyShardTransform(BaseModelTransform):
         mp = self.cfg.get("mixed_precision")
         if mp is not None and mp.get("param_dtype") not in (None, "bfloat16", "bf16", "torch.bfloat16"):
             raise ValueError("fully_shard: compute parameters are bf16 on this engine")
+        if mp is not None and mp.get("reduce_dtype") not in (None, "float32", "fp32", "torch.float32"):
+            raise ValueError("fully_shard: gradients are reduced and accumulated in fp32 on this engine "
+                             f"(mixed_precision.reduce_dtype={mp.get('reduce_dtype')!r} is not available)")
+        if mp is not None and mp.get("output_dtype") not in (None, "bfloat16", "bf16", "torch.bfloat16"):
+            raise ValueError("fully_shard: block outputs are bf16 on this engine (mixed_precision.output_dtype)")
+        if mp is not None and mp.get("cast_forward_inputs", True) is False:
+            logger.warning("fully_shard: cast_forward_inputs=false has no effect (token ids are the only model inputs)")
         device = device if device is not None else torch.device("cuda" if torch.cuda.is_available() else "cpu")
         if device.type != "cuda":
             logger.warning("fully_shard: no CUDA device; model left unsharded (fp32, single process semantics)")
@@ -136,7 +147,11 @@ class FullyShardTransform(BaseModelTransform):
                 else:
                     # one flat shard group over every data-parallel rank
                     group = mesh["dp_replicate", "dp_shard"]._flatten("dp").get_group()
-        cfg = FSDPConfig(reshard_after_forward=bool(self.cfg.reshard_after_forward),
+        raf = self.cfg.reshard_after_forward
+        if isinstance(raf, int) and not isinstance(raf, bool) and raf > 1:
+            logger.warning("fully_shard: reshard_after_forward=%d (reshard to a smaller group) is treated as true: "
+                           "gathered parameters are freed completely after use", raf)
+        cfg = FSDPConfig(reshard_after_forward=bool(raf), param_slots=int(self.cfg.get("param_slots", 2) or 2),
                          fuse_optimizer_in_backward=bool(self.cfg.fuse_optimizer_in_backward),
                          copy_ctas=int(self.cfg.copy_ctas), pull_ctas=int(self.cfg.pull_ctas),
                          sync_grad_accum=bool(self.cfg.sync_grad_accum))
@@ -158,7 +173,7 @@ def accumulation_context(model: nn.Module, is_last_microbatch: bool):
 
     @contextlib.contextmanager
     def ctx():
-        eng.set_requires_gradient_sync(is_last_microbatch or eng.cfg.sync_grad_accum)
+        eng.set_requires_gradient_sync(is_last_microbatch)
         try:
             yield
         finally:

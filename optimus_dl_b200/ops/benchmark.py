@@ -345,6 +345,8 @@ def main() -> None:
                                                     "tp_ag_gemm", "tp_gemm_rs", "tp_ag_gemm_fp8", "tp_gemm_rs_fp8"])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--small", action="store_true", help="one small case (for profiler captures)")
+    ap.add_argument("--mid", action="store_true", help="attention: one case that fills every SM but holds little memory "
+                                                        "(T 4096, 32 / 8 heads), for profiler captures")
     args = ap.parse_args()
     t = Timer(args.iters)
     if args.op == "gemm_bf16":
@@ -356,7 +358,8 @@ def main() -> None:
         bench_gemm_fp8(t, [(4096, 4096, 4096)] if args.small else [(8192, 8192, 8192), (8192, 6144, 4096), (8192, 4096, 14336),
                                                                    (8192, 28672, 4096)])
     elif args.op == "attention":
-        bench_attention(t, [(4096, 8, 2, 128)] if args.small else [(8192, 32, 8, 128), (16384, 40, 8, 128)])
+        bench_attention(t, [(4096, 32, 8, 128)] if args.mid else [(4096, 8, 2, 128)] if args.small
+                        else [(8192, 32, 8, 128), (16384, 40, 8, 128)])
     elif args.op == "decode":
         bench_decode(t, [(64, 768, 16, 8, 128)] if args.small else [(64, 768, 16, 8, 128), (512, 768, 16, 8, 128),
                                                                      (1, 8192, 32, 8, 128), (8, 4096, 32, 8, 128)])

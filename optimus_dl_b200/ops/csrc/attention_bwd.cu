@@ -91,34 +91,42 @@ __device__ __forceinline__ void store_row_bf16(__nv_bfloat16* drow, const uint32
 }
 
 // ============================================================================ dQ kernel
+// Q and dO of the CTA's query tile never change, so they live in TMEM as the A operands of S = Q K^T and
+// dP = dO V^T (each thread loads its own row from global memory once and stores it with tcgen05.st).  Every
+// product of this kernel then reads only its B operand (a K or V half tile) from shared memory, half of what the
+// two-operand form reads, which is what lets 64-key half tiles run at the full tensor rate; the shared memory
+// that the Q / dO tiles would take holds a deeper K / V ring instead.
+constexpr int DQ_STAGES = 3;
+
 template <int HD>
 struct SmemQ {
   static constexpr int TILE = BM * HD * 2;
-  static constexpr int Q_OFF = 0, DO_OFF = TILE, K_OFF = 2 * TILE, V_OFF = K_OFF + STAGES * TILE;
-  static constexpr int BAR_OFF = V_OFF + STAGES * TILE;
+  static constexpr int K_OFF = 0, V_OFF = K_OFF + DQ_STAGES * TILE;
+  static constexpr int BAR_OFF = V_OFF + DQ_STAGES * TILE;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
-// TMEM columns: S_a [0,64) S_b [64,128) dP_a [128,192) dP_b [192,256) dQ [256,256+HD)
+// TMEM columns: S_a [0,64) S_b [64,128) dP_a [128,192) dP_b [192,256) dQ [256,256+HD) Q [384,384+HD/2) dO [448,448+HD/2)
 template <int HD>
 __global__ void __launch_bounds__(THREADS, 1)
-attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
-                   const BwdParams p) {
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                   const __nv_bfloat16* __restrict__ qg, long long q_stride, const __nv_bfloat16* __restrict__ dog,
+                   long long do_stride, const BwdParams p) {
   using L = SmemQ<HD>;
   constexpr int SLABS = HD / 64;
   constexpr int SLAB_BYTES = BM * 128;
   constexpr int HALF_BYTES = HALF * 128;     // 64 rows of one slab
+  constexpr int T_DQ = 2 * BN, T_QA = 384, T_DOA = 448;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
-  uint64_t* qdo_full = bars;
-  uint64_t* k_full = bars + 1; uint64_t* k_empty = bars + 3;
-  uint64_t* v_full = bars + 5; uint64_t* v_empty = bars + 7;
-  uint64_t* sdp_full = bars + 9;      // [2] per half
-  uint64_t* ds_ready = bars + 11;     // [2] per half
-  uint64_t* dq_final = bars + 13;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* k_full = bars; uint64_t* k_empty = bars + DQ_STAGES;
+  uint64_t* v_full = bars + 2 * DQ_STAGES; uint64_t* v_empty = bars + 3 * DQ_STAGES;
+  uint64_t* sdp_full = bars + 4 * DQ_STAGES;      // [2] per half
+  uint64_t* ds_ready = sdp_full + 2;              // [2] per half
+  uint64_t* dq_final = sdp_full + 4;
+  uint64_t* a_ready = sdp_full + 5;               // Q and dO rows are in TMEM (8 warps arrive)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sdp_full + 6);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -134,10 +142,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int n_steps = 2 * n_tiles;
 
   if (threadIdx.x == 0) {
-    mbar_init(qdo_full, 1);
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+    for (int s = 0; s < DQ_STAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
     for (int s = 0; s < 2; ++s) { mbar_init(&sdp_full[s], 1); mbar_init(&ds_ready[s], 4); }
     mbar_init(dq_final, 1);
+    mbar_init(a_ready, 8);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -150,16 +158,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      mbar_arrive_expect_tx(qdo_full, 2 * L::TILE);
-#pragma unroll
-      for (int s = 0; s < SLABS; ++s) {
-        tma_load_2d(smem + L::Q_OFF + s * SLAB_BYTES, &tmQ, qdo_full, h * HD + s * 64, q_lo);
-        tma_load_2d(smem + L::DO_OFF + s * SLAB_BYTES, &tmDO, qdo_full, h * HD + s * 64, q_lo);
-      }
       bool ok = true;
       for (int t = 0; t < n_tiles && ok; ++t) {
-        const int st = t % STAGES, j = j_lo + t;
-        const uint32_t ph = (t / STAGES) & 1;
+        const int st = t % DQ_STAGES, j = j_lo + t;
+        const uint32_t ph = (t / DQ_STAGES) & 1;
         ok = mbar_wait(&k_empty[st], ph ^ 1, abort_flag, p.status);
         if (!ok) break;
         mbar_arrive_expect_tx(&k_full[st], L::TILE);
@@ -179,14 +181,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(BM, HALF, 0, 0);
       constexpr uint32_t idesc_dq = make_idesc_bf16(BM, HD, 0, 1);
-      const uint32_t sQ = smem_u32(smem + L::Q_OFF), sDO = smem_u32(smem + L::DO_OFF);
       const uint32_t sK = smem_u32(smem + L::K_OFF), sV = smem_u32(smem + L::V_OFF);
-      bool ok = mbar_wait(qdo_full, 0, abort_flag, p.status);
+      bool ok = mbar_wait(a_ready, 0, abort_flag, p.status);
 
       auto issue_sdp = [&](int s) -> bool {
-        const int hf = s & 1, t = s >> 1, st = t % STAGES;
+        const int hf = s & 1, t = s >> 1, st = t % DQ_STAGES;
         if (hf == 0) {
-          const uint32_t ph = (t / STAGES) & 1;
+          const uint32_t ph = (t / DQ_STAGES) & 1;
           if (!mbar_wait(&k_full[st], ph, abort_flag, p.status)) return false;
           if (!mbar_wait(&v_full[st], ph, abort_flag, p.status)) return false;
         }
@@ -194,13 +195,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk / 4) * SLAB_BYTES + (kk % 4) * 32;
-          umma_f16_ss(tmem_base + hf * HALF, make_smem_desc_sw128(sQ + off, 16, 1024),
+          umma_f16_ts(tmem_base + hf * HALF, tmem_base + T_QA + kk * 8,
                       make_smem_desc_sw128(sK + st * L::TILE + hf * HALF_BYTES + off, 16, 1024), idesc_s, kk ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk / 4) * SLAB_BYTES + (kk % 4) * 32;
-          umma_f16_ss(tmem_base + BN + hf * HALF, make_smem_desc_sw128(sDO + off, 16, 1024),
+          umma_f16_ts(tmem_base + BN + hf * HALF, tmem_base + T_DOA + kk * 8,
                       make_smem_desc_sw128(sV + st * L::TILE + hf * HALF_BYTES + off, 16, 1024), idesc_s, kk ? 1u : 0u);
         }
         umma_commit(&sdp_full[hf]);
@@ -211,13 +212,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (ok) ok = issue_sdp(0);
       if (ok) ok = issue_sdp(1);
       for (int s = 0; s < n_steps && ok; ++s) {
-        const int hf = s & 1, t = s >> 1, st = t % STAGES;
+        const int hf = s & 1, t = s >> 1, st = t % DQ_STAGES;
         ok = mbar_wait(&ds_ready[hf], t & 1, abort_flag, p.status);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < HALF / 16; ++kk)
-          umma_f16_ts(tmem_base + 2 * BN, tmem_base + hf * HALF + kk * 8,
+          umma_f16_ts(tmem_base + T_DQ, tmem_base + hf * HALF + kk * 8,
                       make_smem_desc_sw128(sK + st * L::TILE + hf * HALF_BYTES + kk * 2048, SLAB_BYTES, 1024), idesc_dq,
                       (s > 0 || kk) ? 1u : 0u);
         if (hf == 1) umma_commit(&k_empty[st]);
@@ -232,6 +233,28 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int row = quarter * 32 + lane;
     const int qi = q_lo + row;
     const bool row_valid = qi < p.N;
+    const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16);
+    {
+      // warpgroup 0 stages the Q rows, warpgroup 1 the dO rows: 16 bf16 pairs per tcgen05.st, zeros past the end
+      const __nv_bfloat16* src = hf == 0 ? qg + (long long)qi * q_stride + (long long)h * HD
+                                         : dog + (long long)qi * do_stride + (long long)h * HD;
+      const uint32_t t_dst = t_row + (hf == 0 ? T_QA : T_DOA);
+#pragma unroll
+      for (int c = 0; c < HD / 2; c += 16) {
+        uint32_t r[16];
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          uint4 u = make_uint4(0u, 0u, 0u, 0u);
+          if (row_valid) u = *reinterpret_cast<const uint4*>(src + 2 * c + 8 * v);
+          r[4 * v] = u.x; r[4 * v + 1] = u.y; r[4 * v + 2] = u.z; r[4 * v + 3] = u.w;
+        }
+        tmem_st_32x16(t_dst + c, r);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(a_ready);
+    }
     int lo_row = 0;
     float lse2 = 0.f, dl = 0.f;
     if (row_valid) {
@@ -240,7 +263,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       lse2 = p.lse[(long long)h * p.N + qi] * LOG2E;
       dl = p.delta[(long long)h * p.N + qi];
     }
-    const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16);
     const uint32_t t_s = t_row + hf * HALF, t_dp = t_row + BN + hf * HALF;
     bool ok = true;
     for (int t = 0; t < n_tiles && ok; ++t) {
@@ -288,7 +310,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
       for (int c = hf * (HD / 2); c < (hf + 1) * (HD / 2); c += 32) {
         uint32_t o[32];
-        tmem_ld_32x32(t_row + 2 * BN + c, o);
+        tmem_ld_32x32(t_row + T_DQ + c, o);
         tmem_ld_wait();
         if (row_valid) store_row_bf16(drow + c, o, p.scale);
       }
@@ -541,6 +563,7 @@ using namespace ob::attnb;
 
 template <int HD>
 static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+                      const __nv_bfloat16* qg, long long q_stride, const __nv_bfloat16* dog, long long do_stride,
                       const BwdParams& p, cudaStream_t stream) {
   auto kq = attn_bwd_dq_kernel<HD>;
   auto kkv = attn_bwd_dkv_kernel<HD>;
@@ -552,7 +575,7 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
   }
   const int n_qtiles = (p.N + BM - 1) / BM, n_ktiles = (p.N + BN - 1) / BN;
   kkv<<<n_ktiles * p.Hk, THREADS, SmemKV<HD>::TOTAL, stream>>>(tq, tk, tv, tdo, p);
-  kq<<<n_qtiles * p.Hq, THREADS, SmemQ<HD>::TOTAL, stream>>>(tq, tk, tv, tdo, p);
+  kq<<<n_qtiles * p.Hq, THREADS, SmemQ<HD>::TOTAL, stream>>>(tk, tv, qg, q_stride, dog, do_stride, p);
   return (int)cudaGetLastError();
 }
 
@@ -583,5 +606,8 @@ extern "C" int ob_attn_bwd(const void* q, const void* k, const void* v, const vo
   kv_last_q_kernel<<<(n_ktiles + 127) / 128, 128, 0, stream>>>((const int*)doc_start, N, window, (int*)kv_last, n_ktiles);
   BwdParams p{N, Hq, Hk, window, scale, scale * LOG2E, (const int*)doc_start, (const float*)lse, (const float*)delta,
               (__nv_bfloat16*)dq, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, dqkv_stride, (const int*)kv_last, status};
-  return hd == 128 ? launch_bwd<128>(tq, tk, tv, tdo, p, stream) : launch_bwd<64>(tq, tk, tv, tdo, p, stream);
+  const __nv_bfloat16* qg = (const __nv_bfloat16*)q;
+  const __nv_bfloat16* dog = (const __nv_bfloat16*)dout;
+  return hd == 128 ? launch_bwd<128>(tq, tk, tv, tdo, qg, qkv_stride, dog, out_stride, p, stream)
+                   : launch_bwd<64>(tq, tk, tv, tdo, qg, qkv_stride, dog, out_stride, p, stream);
 }

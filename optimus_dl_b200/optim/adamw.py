@@ -32,6 +32,16 @@ class AdamWConfig(RegistryConfigStrict):
     fused: bool = True
 
 
+def refuse_sharded(param_groups: list, who: str) -> None:
+    """Optimizers that need the whole gradient of a parameter cannot run on parameters of the sharding engine:
+    their gradients are reduced straight into per-rank fp32 shards and ``p.grad`` stays empty."""
+    for group in param_groups:
+        for p in group["params"]:
+            if getattr(p, "_shard_group", None) is not None:
+                raise ValueError(f"{who} needs full gradients and cannot be combined with the fully_shard transform "
+                                 "(use ddp or a single GPU, or adamw with fully_shard)")
+
+
 def strip_names(params: Any) -> Any:
     """Accept ``(name, param)`` tuples anywhere a parameter is expected."""
     def plain(p):

@@ -23,7 +23,7 @@ from ..core.conf import II
 from ..core.registry import RegistryConfigStrict
 from ..ops import gemm
 from . import build_optimizer, register_optimizer
-from .adamw import strip_names
+from .adamw import refuse_sharded, strip_names
 from .composite import CompositeOptimizer, get_subgroup
 
 DEFAULT_NS_COEFFICIENTS = (3.4445, -4.7750, 2.0315)
@@ -87,6 +87,7 @@ class Muon(Optimizer):
         defaults = dict(lr=lr, weight_decay=weight_decay, momentum=momentum, nesterov=nesterov,
                         ns_coefficients=tuple(ns_coefficients), eps=eps, ns_steps=ns_steps, adjust_lr_fn=adjust_lr_fn)
         super().__init__(strip_names(params), defaults)
+        refuse_sharded(self.param_groups, "Muon")
         for group in self.param_groups:
             for p in group["params"]:
                 if p.dim() != 2:

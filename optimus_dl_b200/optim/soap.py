@@ -20,7 +20,7 @@ from torch.optim.optimizer import Optimizer
 
 from ..core.registry import RegistryConfigStrict
 from . import register_optimizer
-from .adamw import strip_names
+from .adamw import refuse_sharded, strip_names
 
 
 @dataclass
@@ -78,6 +78,7 @@ class SOAP(Optimizer):
                         merge_dims=merge_dims, precondition_1d=precondition_1d, normalize_grads=normalize_grads,
                         correct_bias=correct_bias)
         super().__init__(strip_names(params), defaults)
+        refuse_sharded(self.param_groups, "SOAP")
         self._data_format = data_format
 
     # ------------------------------------------------------------------ geometry

@@ -125,15 +125,12 @@ def after_model_load(model: nn.Module) -> None:
         return
     for g in eng.groups:
         g.refresh_lp_from_master()
-        g.gathered = eng.world == 1
     if eng.world > 1:
-        torch.cuda.synchronize(eng.device)
-        import torch.distributed as dist
-
-        dist.barrier(group=eng.pg)
-        eng.gather_all()
-        torch.cuda.synchronize(eng.device)
-        dist.barrier(group=eng.pg)
+        # every rank has rewritten its shard rows before any peer gathers them again
+        eng.host_sync()
+        if not any(g.pooled for g in eng.groups):
+            eng.gather_all()
+            eng.host_sync()
 
 
 def optimizer_state_dict(model: nn.Module, optimizer: Any, mesh: Any = None) -> dict[str, Any]:

@@ -132,6 +132,19 @@ class TrainRecipe(TrainingContextMixin, TrainingIterationMixin, TrainingInterrup
 
     def _save(self, iteration: int, *, model, optimizer, lr_scheduler, collective, train_loader, persistent=True,
               metadata_only=False, extra=None) -> None:
+        # nothing is persisted from a step in which a kernel's bounded wait ran out (the sharding engine keeps the
+        # last good state in that case); afterwards the ranks meet on the host, because writing a checkpoint takes
+        # a different time on every rank and the device-side waits of the next step are bounded
+        engine = getattr(getattr(model, "module", model), "_sharding_engine", None)
+        if engine is not None:
+            engine.verify()
+        self._save_checkpoint(iteration, model=model, optimizer=optimizer, lr_scheduler=lr_scheduler, collective=collective,
+                              train_loader=train_loader, persistent=persistent, metadata_only=metadata_only, extra=extra)
+        if engine is not None:
+            engine.host_sync()
+
+    def _save_checkpoint(self, iteration: int, *, model, optimizer, lr_scheduler, collective, train_loader, persistent=True,
+                         metadata_only=False, extra=None) -> None:
         self.checkpoint_manager.save_checkpoint(
             iteration=iteration, model=model, optimizer=optimizer, lr_scheduler=lr_scheduler, collective=collective,
             full_config=self._full_config(), persistent=persistent, metadata_only=metadata_only, extra_metadata=extra,
@@ -257,4 +270,7 @@ class TrainRecipe(TrainingContextMixin, TrainingIterationMixin, TrainingInterrup
                             {k: v for k, v in metrics.items() if k in ("loss", "perplexity", "accuracy")})
         if self.evaluator.eval_ckpt is not None:
             self.evaluator.eval_ckpt.cleanup()
+        engine = getattr(getattr(model, "module", model), "_sharding_engine", None)
+        if engine is not None:
+            engine.host_sync()      # evaluation length differs per rank: meet on the host before the next train step
         return results

@@ -28,6 +28,20 @@ def test_fsdp_matches_single_process(unique_port, clip):
     assert "MP_FSDP_OK" in out, out[-4000:]
 
 
+def test_resharded_modes_equal_resident_mode(unique_port):
+    """reshard_after_forward (pooled slots), shard_every_ith_layer and checkpointing on top give the same numbers."""
+    n = 4 if torch.cuda.device_count() >= 4 else 2
+    out = _run("_mp_fsdp_modes.py", n, unique_port, timeout=900)
+    assert "MP_MODES_OK" in out, out[-4000:]
+
+
+def test_missing_rank_makes_the_step_raise(unique_port):
+    """Host-made failure: one rank skips a step; the other's bounded barrier waits run out, its step raises and its
+    optimizer state stays untouched."""
+    out = _run("_mp_fsdp_timeout.py", 2, unique_port)
+    assert "MP_TIMEOUT_OK" in out, out[-4000:]
+
+
 def test_hybrid_sharding_replicas_stay_in_sync(unique_port):
     """Two replicas of a one-rank shard group: gradients are summed over the replicate group before the update."""
     out = _run("_mp_fsdp_check.py", 2, unique_port, "0.5", "1")

@@ -204,3 +204,18 @@ def test_composite_accepts_config_dataclasses_and_a_catch_all_entry():
         "rest": CompositeOptimizerConfigEntry(params_regexp=None, optimizer_config={"_name": "adamw", "lr": 1e-3})}),
         params=model.named_parameters())
     assert len(rest.optimizers["rest"].param_groups[0]["params"]) == 1
+
+
+def test_muon_and_soap_refuse_parameters_of_the_sharding_engine():
+    import pytest
+    import torch
+
+    from optimus_dl_b200.optim.muon import Muon
+    from optimus_dl_b200.optim.soap import SOAP
+
+    p = torch.nn.Parameter(torch.zeros(4, 4))
+    p._shard_group = object()       # what the fully_shard transform leaves on a parameter
+    with pytest.raises(ValueError, match="fully_shard"):
+        Muon([p])
+    with pytest.raises(ValueError, match="fully_shard"):
+        SOAP([p])
