@@ -90,6 +90,9 @@ def run(args, models: dict, clock_sampler_cls) -> None:
     import torch
     import torch.distributed as dist
 
+    if not torch.cuda.is_available():
+        _print_unavailable("no CUDA device on this machine (the reference arm runs on a B200 like the framework's own arm)")
+        return
     logging.disable(logging.INFO)
     try:
         import optimus_dl  # noqa: F401  (bootstraps every registry of the reference)

@@ -129,10 +129,14 @@ class CheckpointManager:
         last_save_freq = self.last_save_freq if last_save_freq is None else last_save_freq
         persistent = bool(save_freq) and save_freq > 0 and iteration % save_freq == 0
         last = bool(last_save_freq) and last_save_freq > 0 and iteration % last_save_freq == 0
-        if not (persistent or last or force_save):
+        if last_save_freq is None or not last_save_freq:
+            last = persistent       # without a separate cadence the rolling checkpoint follows the numbered one
+        # a forced save is always a numbered one (optimus_dl/modules/checkpoint/checkpoint_manager.py: force_save
+        # makes the save persistent), with the *_latest names pointing at it
+        persistent = persistent or bool(force_save)
+        if not (persistent or last):
             return False
-        persistent = persistent or (force_save and not last)
-        self.save_checkpoint(iteration=iteration, is_save_persistent=persistent, is_save_last=True, **kwargs)
+        self.save_checkpoint(iteration=iteration, is_save_persistent=persistent, is_save_last=last or persistent, **kwargs)
         return True
 
     def _names(self, iteration: int, rank: int, persistent: bool) -> dict[str, Path]:
@@ -151,6 +155,11 @@ class CheckpointManager:
         point at); without it the checkpoint is written under the ``*_latest`` names themselves."""
         if is_save_persistent is not None:
             persistent = bool(is_save_persistent)
+        # a numbered checkpoint normally becomes the target of the *_latest links; ``is_save_last=False`` writes the
+        # numbered files only, and asking for neither kind is a caller error
+        link_latest = True if is_save_last is None else bool(is_save_last)
+        if is_save_persistent is not None and is_save_last is not None and not persistent and not link_latest:
+            raise ValueError("save_checkpoint: neither a persistent nor a latest checkpoint was requested")
         if checkpoint_path is not None:
             self.output_path = Path(checkpoint_path)
         assert self.output_path is not None, "checkpoint manager has no output path"
@@ -201,7 +210,7 @@ class CheckpointManager:
             _remove(names["rank"])
             tmp["rank"].rename(names["rank"])
         coll.barrier()
-        if persistent:
+        if persistent and link_latest:
             if coll.is_master:
                 _symlink(names["meta"].name, out / "metadata_latest.pt")
                 if not metadata_only or not (out / "checkpoint_latest").exists():
@@ -264,8 +273,8 @@ class CheckpointManager:
         rank_file = Path(cp.metadata).parent / f"per_rank_metadata_{coll.rank}_{suffix}"
         per_rank = torch.load(rank_file, map_location="cpu", weights_only=False) if rank_file.exists() else {}
         if per_rank and per_rank.get("iteration") != metadata.get("iteration"):
-            logger.warning("per-rank metadata is from iteration %s, checkpoint from %s", per_rank.get("iteration"),
-                           metadata.get("iteration"))
+            raise RuntimeError(f"checkpoint corrupted: per-rank metadata of rank {coll.rank} is from iteration "
+                               f"{per_rank.get('iteration')}, the checkpoint from {metadata.get('iteration')}")
         # tensor-parallel peers must read identical data: take the state of the group's first rank
         if strategy.load_dataloaders and data_loaders:
             states = per_rank.get("data_loaders", {})

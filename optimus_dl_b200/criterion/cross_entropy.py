@@ -17,12 +17,14 @@ the loss and their gradients run in the chunked fused kernels of ``ops.cross_ent
 
 from __future__ import annotations
 
+import logging
 from dataclasses import dataclass
 from typing import Any
 
 import torch
 import torch.nn.functional as F
 
+from ..core.log import warn_once
 from ..core.registry import RegistryConfigStrict
 from ..metrics.common import cached_lambda, log_averaged, log_averaged_exponent, log_summed
 from ..ops import cross_entropy as ce_ops
@@ -30,6 +32,9 @@ from . import register_criterion
 from .base import BaseCriterion
 
 LOGIT_PROTOCOLS = {"logits", "logits_targets", "logits_mask", "classification"}
+
+
+logger = logging.getLogger(__name__)
 
 
 @dataclass
@@ -64,12 +69,18 @@ class CrossEntropyCriterion(BaseCriterion):
             targets = batch.pop("labels")
             return batch, targets
         ids = batch["input_ids"]
+        # the shift below drops one token per ROW; a flat (packed) batch described by cu_seqlens would need one
+        # dropped per DOCUMENT, which only the batcher can do (it then supplies ``labels``)
+        assert "cu_seqlens" not in batch, "If input is flat, we cannot generate labels and inputs efficiently"
+        assert ids.ndim == 2, "Input must be 2D for automatic causal shifting"
         targets = ids[:, 1:]
         T = ids.shape[1]
         out: dict[str, Any] = {}
         for k, v in batch.items():
             if k == "seq_lens" and isinstance(v, torch.Tensor):
-                out[k] = v - 1
+                if bool((v < 1).any()):
+                    warn_once(logger, "seq_lens contains empty sequences; their shifted length is clamped to 0")
+                out[k] = torch.clamp(v - 1, min=0)
             elif isinstance(v, torch.Tensor) and v.dim() >= 2 and v.shape[0] == ids.shape[0] and v.shape[1] == T:
                 out[k] = v[:, :-1]
             else:

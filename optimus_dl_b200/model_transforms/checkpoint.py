@@ -42,6 +42,21 @@ def _policy(ops: list[Any]):
     return policy
 
 
+def checkpoint_module(m: nn.Module, ctx_fn: Any = None, use_reentrant: bool = False) -> None:
+    """Make ``m`` recompute its forward during backward (its ``forward`` is wrapped in place, so hooks registered on
+    the module keep firing once per outer call and not during the recomputation)."""
+    orig = m.forward
+
+    def wrapped(*a, _orig=orig, **k):
+        if not torch.is_grad_enabled():
+            return _orig(*a, **k)
+        extra = {"context_fn": ctx_fn} if ctx_fn is not None else {}
+        return checkpoint(_orig, *a, use_reentrant=use_reentrant, **extra, **k)
+
+    m.forward = wrapped
+    m._activation_checkpointed = True
+
+
 @register_model_transform("activation_checkpoint", ActivationCheckpointConfig)
 class ActivationCheckpointTransform(BaseModelTransform):
     def apply(self, model: nn.Module, **kwargs: Any) -> nn.Module:
@@ -57,15 +72,7 @@ class ActivationCheckpointTransform(BaseModelTransform):
         for i, m in enumerate([m for m in model.modules() if type(m).__name__ in names]):
             if i % max(1, int(self.cfg.every_nth)) != 0:
                 continue
-            orig = m.forward
-
-            def wrapped(*a, _orig=orig, **k):
-                if not torch.is_grad_enabled():
-                    return _orig(*a, **k)
-                extra = {"context_fn": ctx_fn} if ctx_fn is not None else {}
-                return checkpoint(_orig, *a, use_reentrant=bool(self.cfg.get("use_reentrant", False)), **extra, **k)
-
-            m.forward = wrapped
+            checkpoint_module(m, ctx_fn, bool(self.cfg.get("use_reentrant", False)))
             count += 1
         logger.info("activation checkpointing enabled on %d modules", count)
         return model

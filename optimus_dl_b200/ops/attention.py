@@ -31,6 +31,11 @@ def build_doc_start(B: int, T: int, device: torch.device, document_ids: torch.Te
     """Flat ``int32 [B*T]`` index of the first token of each token's document."""
     idx = torch.arange(B * T, device=device, dtype=torch.int64).view(B, T)
     if cu_seqlens is not None:
+        if not cu_seqlens.is_cuda and cu_seqlens.numel() > 0:
+            # host-side boundaries can be checked without a device synchronisation: they must cover the batch exactly
+            if int(cu_seqlens[0]) != 0 or int(cu_seqlens[-1]) != B * T:
+                raise ValueError(f"cu_seqlens must start at 0 and end at the number of tokens ({B * T}); "
+                                 f"got {int(cu_seqlens[0])} .. {int(cu_seqlens[-1])}")
         cu = cu_seqlens.to(device=device, dtype=torch.int64)
         flat = idx.view(-1)
         seg = torch.searchsorted(cu, flat, right=True) - 1

@@ -91,42 +91,48 @@ __device__ __forceinline__ void store_row_bf16(__nv_bfloat16* drow, const uint32
 }
 
 // ============================================================================ dQ kernel
-// Q and dO of the CTA's query tile never change, so they live in TMEM as the A operands of S = Q K^T and
-// dP = dO V^T (each thread loads its own row from global memory once and stores it with tcgen05.st).  Every
-// product of this kernel then reads only its B operand (a K or V half tile) from shared memory, half of what the
-// two-operand form reads, which is what lets 64-key half tiles run at the full tensor rate; the shared memory
-// that the Q / dO tiles would take holds a deeper K / V ring instead.
+// Measured on B200: one tcgen05.mma takes about 70 cycles when it extends the accumulation chain of the MMA before
+// it, and never less than about 49, whatever its width; a 128-wide MMA needs 64 cycles of tensor time anyway, a
+// 64-wide one only 32.  So every product here is 128 wide, and the two independent products of a tile (S and dP)
+// are issued alternately, k-step by k-step, so that neither waits for its own previous step.
+//
+// Per key tile: S = Q K^T and dP = dO V^T land in TMEM; the two compute warpgroups (64 key columns each) pull
+// their halves into registers and release the two regions at once, so the MMA warp issues the NEXT tile's S / dP
+// while this tile's dS = P * (dP - delta) is still being computed; dS goes to its own TMEM columns and feeds
+// dQ += dS K.  Q lives in TMEM as an A operand (each thread stores its own row once).
 constexpr int DQ_STAGES = 3;
 
 template <int HD>
 struct SmemQ {
   static constexpr int TILE = BM * HD * 2;
-  static constexpr int K_OFF = 0, V_OFF = K_OFF + DQ_STAGES * TILE;
+  static constexpr int DO_OFF = 0, K_OFF = TILE, V_OFF = K_OFF + DQ_STAGES * TILE;
   static constexpr int BAR_OFF = V_OFF + DQ_STAGES * TILE;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
-// TMEM columns: S_a [0,64) S_b [64,128) dP_a [128,192) dP_b [192,256) dQ [256,256+HD) Q [384,384+HD/2) dO [448,448+HD/2)
+// TMEM columns: S [0,128) dP [128,256) dQ [256,256+HD) dS (bf16 pairs) [384,448) Q (bf16 pairs) [448,448+HD/2)
 template <int HD>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                   const __nv_bfloat16* __restrict__ qg, long long q_stride, const __nv_bfloat16* __restrict__ dog,
-                   long long do_stride, const BwdParams p) {
+                   const __grid_constant__ CUtensorMap tmDO, const __nv_bfloat16* __restrict__ qg, long long q_stride,
+                   const BwdParams p) {
   using L = SmemQ<HD>;
   constexpr int SLABS = HD / 64;
   constexpr int SLAB_BYTES = BM * 128;
-  constexpr int HALF_BYTES = HALF * 128;     // 64 rows of one slab
-  constexpr int T_DQ = 2 * BN, T_QA = 384, T_DOA = 448;
+  constexpr int T_S = 0, T_DP = BN, T_DQ = 2 * BN, T_DS = 384, T_QA = 448;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   uint64_t* k_full = bars; uint64_t* k_empty = bars + DQ_STAGES;
   uint64_t* v_full = bars + 2 * DQ_STAGES; uint64_t* v_empty = bars + 3 * DQ_STAGES;
-  uint64_t* sdp_full = bars + 4 * DQ_STAGES;      // [2] per half
-  uint64_t* ds_ready = sdp_full + 2;              // [2] per half
-  uint64_t* dq_final = sdp_full + 4;
-  uint64_t* a_ready = sdp_full + 5;               // Q and dO rows are in TMEM (8 warps arrive)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sdp_full + 6);
+  uint64_t* misc = bars + 4 * DQ_STAGES;
+  uint64_t* sdp_full = misc;          // S and dP of a tile are complete (one commit per tile)
+  uint64_t* sdp_free = misc + 1;      // both warpgroups hold their halves in registers (8 warps)
+  uint64_t* ds_ready = misc + 2;      // dS of a tile is in TMEM (8 warps)
+  uint64_t* dq_done = misc + 3;       // the dQ product of a tile has read dS and K (one commit per tile)
+  uint64_t* a_ready = misc + 4;       // Q rows are in TMEM (4 warps)
+  uint64_t* do_full = misc + 5;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc + 6);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -139,13 +145,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   if (p.window > 0) { lo_first = max(lo_first, q_lo - p.window + 1); lo_last = max(lo_last, q_hi - p.window + 1); }
   const int j_lo = lo_first / BN, j_hi = q_hi / BN;
   const int n_tiles = j_hi - j_lo + 1;
-  const int n_steps = 2 * n_tiles;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < DQ_STAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&sdp_full[s], 1); mbar_init(&ds_ready[s], 4); }
-    mbar_init(dq_final, 1);
-    mbar_init(a_ready, 8);
+    mbar_init(sdp_full, 1); mbar_init(sdp_free, 8); mbar_init(ds_ready, 8); mbar_init(dq_done, 1);
+    mbar_init(a_ready, 4); mbar_init(do_full, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -158,6 +162,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      mbar_arrive_expect_tx(do_full, L::TILE);
+#pragma unroll
+      for (int s = 0; s < SLABS; ++s) tma_load_2d(smem + L::DO_OFF + s * SLAB_BYTES, &tmDO, do_full, h * HD + s * 64, q_lo);
       bool ok = true;
       for (int t = 0; t < n_tiles && ok; ++t) {
         const int st = t % DQ_STAGES, j = j_lo + t;
@@ -179,66 +186,62 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(BM, HALF, 0, 0);
+      constexpr uint32_t idesc_s = make_idesc_bf16(BM, BN, 0, 0);
       constexpr uint32_t idesc_dq = make_idesc_bf16(BM, HD, 0, 1);
+      const uint32_t sDO = smem_u32(smem + L::DO_OFF);
       const uint32_t sK = smem_u32(smem + L::K_OFF), sV = smem_u32(smem + L::V_OFF);
       bool ok = mbar_wait(a_ready, 0, abort_flag, p.status);
+      if (ok) ok = mbar_wait(do_full, 0, abort_flag, p.status);
 
-      auto issue_sdp = [&](int s) -> bool {
-        const int hf = s & 1, t = s >> 1, st = t % DQ_STAGES;
-        if (hf == 0) {
-          const uint32_t ph = (t / DQ_STAGES) & 1;
-          if (!mbar_wait(&k_full[st], ph, abort_flag, p.status)) return false;
-          if (!mbar_wait(&v_full[st], ph, abort_flag, p.status)) return false;
-        }
+      auto issue_sdp = [&](int t) -> bool {
+        const int st = t % DQ_STAGES;
+        const uint32_t ph = (t / DQ_STAGES) & 1;
+        if (!mbar_wait(&k_full[st], ph, abort_flag, p.status)) return false;
+        if (!mbar_wait(&v_full[st], ph, abort_flag, p.status)) return false;
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk / 4) * SLAB_BYTES + (kk % 4) * 32;
-          umma_f16_ts(tmem_base + hf * HALF, tmem_base + T_QA + kk * 8,
-                      make_smem_desc_sw128(sK + st * L::TILE + hf * HALF_BYTES + off, 16, 1024), idesc_s, kk ? 1u : 0u);
+          umma_f16_ts(tmem_base + T_S, tmem_base + T_QA + kk * 8,
+                      make_smem_desc_sw128(sK + st * L::TILE + off, 16, 1024), idesc_s, kk ? 1u : 0u);
+          umma_f16_ss(tmem_base + T_DP, make_smem_desc_sw128(sDO + off, 16, 1024),
+                      make_smem_desc_sw128(sV + st * L::TILE + off, 16, 1024), idesc_s, kk ? 1u : 0u);
         }
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (kk / 4) * SLAB_BYTES + (kk % 4) * 32;
-          umma_f16_ts(tmem_base + BN + hf * HALF, tmem_base + T_DOA + kk * 8,
-                      make_smem_desc_sw128(sV + st * L::TILE + hf * HALF_BYTES + off, 16, 1024), idesc_s, kk ? 1u : 0u);
-        }
-        umma_commit(&sdp_full[hf]);
-        if (hf == 1) umma_commit(&v_empty[st]);
+        umma_commit(sdp_full);
+        umma_commit(&v_empty[st]);
         return true;
       };
 
       if (ok) ok = issue_sdp(0);
-      if (ok) ok = issue_sdp(1);
-      for (int s = 0; s < n_steps && ok; ++s) {
-        const int hf = s & 1, t = s >> 1, st = t % DQ_STAGES;
-        ok = mbar_wait(&ds_ready[hf], t & 1, abort_flag, p.status);
+      for (int t = 0; t < n_tiles && ok; ++t) {
+        const int st = t % DQ_STAGES;
+        if (t + 1 < n_tiles) {
+          ok = mbar_wait(sdp_free, t & 1, abort_flag, p.status);
+          if (ok) ok = issue_sdp(t + 1);
+          if (!ok) break;
+        }
+        ok = mbar_wait(ds_ready, t & 1, abort_flag, p.status);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < HALF / 16; ++kk)
-          umma_f16_ts(tmem_base + T_DQ, tmem_base + hf * HALF + kk * 8,
-                      make_smem_desc_sw128(sK + st * L::TILE + hf * HALF_BYTES + kk * 2048, SLAB_BYTES, 1024), idesc_dq,
-                      (s > 0 || kk) ? 1u : 0u);
-        if (hf == 1) umma_commit(&k_empty[st]);
-        if (s + 2 < n_steps) ok = issue_sdp(s + 2);
+        for (int kk = 0; kk < BN / 16; ++kk)
+          umma_f16_ts(tmem_base + T_DQ, tmem_base + T_DS + kk * 8,
+                      make_smem_desc_sw128(sK + st * L::TILE + kk * 2048, SLAB_BYTES, 1024), idesc_dq, (t > 0 || kk) ? 1u : 0u);
+        umma_commit(dq_done);
+        umma_commit(&k_empty[st]);
       }
-      umma_commit(dq_final);
     }
   } else {
     // ------------------------------------------------------------------ compute warpgroups
-    const int hf = warp >> 2;                 // which half of every key tile this warpgroup owns
+    const int hf = warp >> 2;                 // which 64 key columns of every tile this warpgroup owns
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const int qi = q_lo + row;
     const bool row_valid = qi < p.N;
     const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16);
-    {
-      // warpgroup 0 stages the Q rows, warpgroup 1 the dO rows: 16 bf16 pairs per tcgen05.st, zeros past the end
-      const __nv_bfloat16* src = hf == 0 ? qg + (long long)qi * q_stride + (long long)h * HD
-                                         : dog + (long long)qi * do_stride + (long long)h * HD;
-      const uint32_t t_dst = t_row + (hf == 0 ? T_QA : T_DOA);
+    if (hf == 0) {
+      // Q rows into TMEM as the A operand of S = Q K^T: 16 bf16 pairs per tcgen05.st, zeros past the end
+      const __nv_bfloat16* src = qg + (long long)qi * q_stride + (long long)h * HD;
 #pragma unroll
       for (int c = 0; c < HD / 2; c += 16) {
         uint32_t r[16];
@@ -248,7 +251,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
           if (row_valid) u = *reinterpret_cast<const uint4*>(src + 2 * c + 8 * v);
           r[4 * v] = u.x; r[4 * v + 1] = u.y; r[4 * v + 2] = u.z; r[4 * v + 3] = u.w;
         }
-        tmem_st_32x16(t_dst + c, r);
+        tmem_st_32x16(t_row + T_QA + c, r);
       }
       tmem_st_wait();
       tc_fence_before();
@@ -263,10 +266,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       lse2 = p.lse[(long long)h * p.N + qi] * LOG2E;
       dl = p.delta[(long long)h * p.N + qi];
     }
-    const uint32_t t_s = t_row + hf * HALF, t_dp = t_row + BN + hf * HALF;
+    const uint32_t t_s = t_row + T_S + hf * HALF, t_dp = t_row + T_DP + hf * HALF, t_ds = t_row + T_DS + hf * (HALF / 2);
     bool ok = true;
     for (int t = 0; t < n_tiles && ok; ++t) {
-      ok = mbar_wait(&sdp_full[hf], t & 1, abort_flag, p.status);
+      ok = mbar_wait(sdp_full, t & 1, abort_flag, p.status);
       if (!ok) break;
       tc_fence_after();
       uint32_t s[HALF], dp[HALF], pk[HALF / 2];
@@ -275,6 +278,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       tmem_ld_32x32(t_dp, dp);
       tmem_ld_32x32(t_dp + 32, dp + 32);
       tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sdp_free);     // the S / dP columns may be overwritten by the next tile
       const int k0 = (j_lo + t) * BN + hf * HALF;
       const bool need_mask = (k0 + HALF - 1 > q_lo) || (k0 < lo_last);
       if (need_mask) {
@@ -295,14 +301,19 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
           pk[e / 2] = pack_bf16x2(p0 * (__uint_as_float(dp[e]) - dl), p1 * (__uint_as_float(dp[e + 1]) - dl));
         }
       }
-      tmem_st_32x16(t_s, pk);
-      tmem_st_32x16(t_s + 16, pk + 16);
+      if (t > 0) {                               // the previous tile's dQ product has finished reading dS
+        ok = mbar_wait(dq_done, (t - 1) & 1, abort_flag, p.status);
+        if (!ok) break;
+        tc_fence_after();
+      }
+      tmem_st_32x16(t_ds, pk);
+      tmem_st_32x16(t_ds + 16, pk + 16);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&ds_ready[hf]);
+      if (lane == 0) mbar_arrive(ds_ready);
     }
-    if (ok) ok = mbar_wait(dq_final, 0, abort_flag, p.status);
+    if (ok) ok = mbar_wait(dq_done, (n_tiles - 1) & 1, abort_flag, p.status);
     if (ok) {
       tc_fence_after();
       // the two warpgroups split the head dimension of the output
@@ -322,6 +333,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
 }
 
 // ============================================================================ dK/dV kernel
+// Transposed problem (key rows in TMEM lanes).  All 512 TMEM columns are taken by the two accumulators and the
+// S^T / dP^T of one 128-query tile, so the tile is processed as two 64-query halves with their own columns and
+// barriers: while one warpgroup turns its half into P^T / dS^T the tensor cores run the other half's products.
+// (A form with 128-wide S^T / dP^T and nothing else in flight measured 16 % slower: the round trips between the
+// MMA warp and the compute warps, a few hundred cycles each, were then all on the critical path.)
 template <int HD>
 struct SmemKV {
   static constexpr int TILE = BM * HD * 2;
@@ -414,14 +430,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (hf == 0 && !mbar_wait(&q_full[st], (it / STAGES) & 1, abort_flag, p.status)) return false;
         tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
+        for (int kk = 0; kk < HD / 16; ++kk) {      // the two independent chains alternate (see the dQ kernel)
           const uint32_t off = (kk / 4) * SLAB_BYTES + (kk % 4) * 32;
           umma_f16_ss(tmem_base + hf * HALF, make_smem_desc_sw128(sK + off, 16, 1024),
                       make_smem_desc_sw128(sQ + st * L::TILE + hf * HALF_BYTES + off, 16, 1024), idesc_s, kk ? 1u : 0u);
-        }
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (kk / 4) * SLAB_BYTES + (kk % 4) * 32;
           umma_f16_ss(tmem_base + BM + hf * HALF, make_smem_desc_sw128(sV + off, 16, 1024),
                       make_smem_desc_sw128(sDO + st * L::TILE + hf * HALF_BYTES + off, 16, 1024), idesc_s, kk ? 1u : 0u);
         }
@@ -437,15 +449,14 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < HALF / 16; ++kk)   // dV += P^T dO
-          umma_f16_ts(tmem_base + 2 * BM, tmem_base + hf * HALF + kk * 8,
+        for (int kk = 0; kk < HALF / 16; ++kk) {
+          umma_f16_ts(tmem_base + 2 * BM, tmem_base + hf * HALF + kk * 8,          // dV += P^T dO
                       make_smem_desc_sw128(sDO + st * L::TILE + hf * HALF_BYTES + kk * 2048, SLAB_BYTES, 1024), idesc_o,
                       (s > 0 || kk) ? 1u : 0u);
-#pragma unroll
-        for (int kk = 0; kk < HALF / 16; ++kk)   // dK += dS^T Q
-          umma_f16_ts(tmem_base + 3 * BM, tmem_base + BM + hf * HALF + kk * 8,
+          umma_f16_ts(tmem_base + 3 * BM, tmem_base + BM + hf * HALF + kk * 8,     // dK += dS^T Q
                       make_smem_desc_sw128(sQ + st * L::TILE + hf * HALF_BYTES + kk * 2048, SLAB_BYTES, 1024), idesc_o,
                       (s > 0 || kk) ? 1u : 0u);
+        }
         if (hf == 1) umma_commit(&q_empty[st]);
         if (s + 2 < n_steps) ok = issue_sdp(s + 2);
       }
@@ -575,7 +586,7 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
   }
   const int n_qtiles = (p.N + BM - 1) / BM, n_ktiles = (p.N + BN - 1) / BN;
   kkv<<<n_ktiles * p.Hk, THREADS, SmemKV<HD>::TOTAL, stream>>>(tq, tk, tv, tdo, p);
-  kq<<<n_qtiles * p.Hq, THREADS, SmemQ<HD>::TOTAL, stream>>>(tk, tv, qg, q_stride, dog, do_stride, p);
+  kq<<<n_qtiles * p.Hq, THREADS, SmemQ<HD>::TOTAL, stream>>>(tk, tv, tdo, qg, q_stride, p);
   return (int)cudaGetLastError();
 }
 

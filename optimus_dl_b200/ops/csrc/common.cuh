@@ -80,12 +80,15 @@ __device__ __forceinline__ unsigned long long mbar_now_ns() {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* status) {
   if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = mbar_now_ns();
+  // the clock is first read after 256 failed probes (each probe already suspends the thread for a while), so the
+  // common short wait costs nothing but the probes
+  unsigned long long t0 = 0;
   for (uint32_t it = 0;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 0xff) == 0xff) {
       if (*abort_flag) return false;
-      if (mbar_now_ns() - t0 > OB_MBAR_WAIT_NS) break;
+      if (it == 0xff) t0 = mbar_now_ns();
+      else if (mbar_now_ns() - t0 > OB_MBAR_WAIT_NS) break;
     }
   }
   *abort_flag = 1;

@@ -396,7 +396,11 @@ int partials_for_current_device(float** out) {
 
 extern "C" int ob_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const void* rstd, void* dx,
                                       void* dw_bf16, int rows, int D, cudaStream_t stream) {
-  if (rows < 0 || D <= 0 || !norm_args_ok(D)) {
+  if (rows < 0) {
+    std::fprintf(stderr, "ob_rmsnorm_bwd_noalloc: negative row count %d\n", rows);
+    return OB_RMSNORM_NOALLOC_ERR_SHAPE;
+  }
+  if (D <= 0 || !norm_args_ok(D)) {
     std::fprintf(stderr, "ob_rmsnorm_bwd_noalloc: unsupported width D=%d (need D %% 8 == 0 and D <= %d)\n", D,
                  THREADS * 8 * MAX_VEC);
     return OB_RMSNORM_NOALLOC_ERR_SHAPE;

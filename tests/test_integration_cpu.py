@@ -225,7 +225,11 @@ def test_ddp_transform_on_two_gloo_ranks_matches_one_process(unique_port):
     assert res.returncode == 0 and res.stdout.count("DDP_OK") == 2, res.stdout[-2000:] + res.stderr[-3000:]
 
 
-def test_bench_reference_arm_reports_unavailable_and_exits_zero():
+def test_bench_reference_arm_without_a_gpu_says_so_and_exits_zero():
+    """On a machine without a CUDA device the reference arm prints its one-line reason and exits 0 (on a GPU box it
+    runs the unmodified reference; tests/test_reference_arm.py covers the parts that need no GPU)."""
+    if torch.cuda.is_available():
+        pytest.skip("needs a machine without a GPU")
     res = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "3"],
                          capture_output=True, text=True, timeout=120)
     assert res.returncode == 0, res.stderr[-2000:]

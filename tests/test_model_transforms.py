@@ -122,3 +122,35 @@ def test_model_builder_applies_transforms_in_list_order(tmp_path):
     assert torch.equal(model.lm_head.weight, src.lm_head.weight)
     assert any(getattr(p, "_fp8", False) for p in model.parameters())
     _loss(model, torch.randint(0, 61, (1, 8))).backward()
+
+
+def test_compile_budget_turns_on_block_recomputation(caplog):
+    """The reference's 7B recipe sets compile.activation_memory_budget: 0.3; without a compiler the budget is
+    honoured by recomputing that share of the blocks, loudly."""
+    import logging
+
+    from optimus_dl_b200.model_transforms import build_model_transform
+    from optimus_dl_b200.models import build_model
+
+    model = build_model(dict(_name="llama2", n_layer=10, n_head=4, n_kv_head=2, n_embd=64, intermediate_size=128,
+                             vocab_size=128, sequence_length=32, tie_word_embeddings=False))
+    with caplog.at_level(logging.WARNING):
+        out = build_model_transform({"_name": "compile", "activation_memory_budget": 0.3}).apply(model)
+    assert out is model
+    marked = [getattr(b, "_activation_checkpointed", False) for b in model.transformer.h]
+    assert sum(marked) == 7
+    assert any("recomputing 7 of 10" in r.message for r in caplog.records)
+    import torch
+
+    ids = torch.randint(0, 128, (2, 17))
+    ref = build_model(dict(_name="llama2", n_layer=10, n_head=4, n_kv_head=2, n_embd=64, intermediate_size=128,
+                           vocab_size=128, sequence_length=32, tie_word_embeddings=False))
+    ref.load_state_dict(model.state_dict())
+    la = model(input_ids=ids)["logits"].float().sum()
+    lb = ref(input_ids=ids)["logits"].float().sum()
+    la.backward()
+    lb.backward()
+    for (n, p), (_, q) in zip(model.named_parameters(), ref.named_parameters()):
+        assert torch.allclose(p.grad, q.grad, atol=1e-5), n
+    again = build_model_transform({"_name": "compile", "activation_memory_budget": 1.0}).apply(ref)
+    assert not any(getattr(b, "_activation_checkpointed", False) for b in again.transformer.h)
