@@ -31,18 +31,62 @@ def SI(s: str) -> str:
     return s
 
 
+def _defaults_of(cls: Any) -> dict:
+    fields = {}
+    for f in dataclasses.fields(cls):
+        if f.default is not dataclasses.MISSING:
+            fields[f.name] = f.default
+        elif f.default_factory is not dataclasses.MISSING:
+            fields[f.name] = f.default_factory()
+        else:
+            fields[f.name] = MISSING
+    return fields
+
+
 def _structured(obj: Any) -> Any:
-    if isinstance(obj, type) and dataclasses.is_dataclass(obj):
-        fields = {}
-        for f in dataclasses.fields(obj):
-            if f.default is not dataclasses.MISSING:
-                fields[f.name] = f.default
-            elif f.default_factory is not dataclasses.MISSING:
-                fields[f.name] = f.default_factory()
-            else:
-                fields[f.name] = MISSING
-        return _conf.create(fields)
+    """Config node from a dataclass type or instance; the node remembers the type so that a later merge can fill
+    nested dataclass fields (declared ``X | None = None``) with X's defaults, as a structured config does."""
+    cls = obj if isinstance(obj, type) else type(obj)
+    if dataclasses.is_dataclass(cls):
+        node = _conf.create(_defaults_of(cls) if isinstance(obj, type) else obj)
+        node._flags["struct_type"] = cls
+        return node
     return _conf.create(obj)
+
+
+def _dataclass_in(hint: Any) -> Any:
+    """The dataclass type inside ``X``, ``Optional[X]`` or ``X | None`` (None when there is none)."""
+    import types
+    import typing
+
+    if isinstance(hint, type) and dataclasses.is_dataclass(hint):
+        return hint
+    if typing.get_origin(hint) in (typing.Union, types.UnionType):
+        for a in typing.get_args(hint):
+            if isinstance(a, type) and dataclasses.is_dataclass(a):
+                return a
+    return None
+
+
+def _typed_fill(cls: Any, data: Any) -> Any:
+    """``data`` (a plain mapping about to be merged into a node of dataclass type ``cls``) with every nested
+    mapping that targets a dataclass-typed field completed from that dataclass's defaults."""
+    import typing
+
+    if not isinstance(data, dict) or cls is None:
+        return data
+    try:
+        hints = typing.get_type_hints(cls)
+    except Exception:  # noqa: BLE001
+        return data
+    out = dict(data)
+    for k, v in data.items():
+        sub = _dataclass_in(hints.get(k))
+        if sub is not None and isinstance(v, dict):
+            base = _conf.to_container(_conf.create(_defaults_of(sub)), resolve=False)
+            base.update(_typed_fill(sub, v))
+            out[k] = base
+    return out
 
 
 class OmegaConf:
@@ -60,7 +104,15 @@ class OmegaConf:
 
     @staticmethod
     def merge(*cfgs: Any) -> Any:
-        return _conf.merge(*[_structured(c) if (dataclasses.is_dataclass(c)) else c for c in cfgs])
+        nodes = [_structured(c) if dataclasses.is_dataclass(c) else c for c in cfgs]
+        cls = nodes[0]._flags.get("struct_type") if _conf.is_config(nodes[0]) else None
+        if cls is not None:
+            nodes = [nodes[0]] + [
+                _typed_fill(cls, _conf.to_container(n, resolve=False) if _conf.is_config(n) else n) for n in nodes[1:]]
+        out = _conf.merge(*nodes)
+        if cls is not None and _conf.is_config(out):
+            out._flags["struct_type"] = cls
+        return out
 
     @staticmethod
     def to_container(cfg: Any, resolve: bool = False, throw_on_missing: bool = False, **_: Any) -> Any:

@@ -104,6 +104,8 @@ def main() -> None:
                     "lengths (mean 2048, min 32) and attends block-diagonally")
     ap.add_argument("--timeline", default=None, help="write a per-launcher device-time breakdown of one extra step "
                                                        "(JSON lines) to this file")
+    ap.add_argument("--reshard", action="store_true", help="reshard_after_forward: gathered block parameters live in a "
+                    "small pool and are gathered again for the backward pass (the memory mode for models that do not fit)")
     ap.add_argument("--n-layer", type=int, default=None, help="override the layer count (profiling only; the "
                     "reported metric then says so)")
     ap.add_argument("--ref-variant", default=None, help="reference arm only: comma-separated list tried in order, from "
@@ -168,7 +170,7 @@ def main() -> None:
         model = build_model_transform({"_name": "tensor_parallel", "custom_model_kwargs": {
             "sequence_parallel": True, "loss_parallel": True}}).apply(model, collective=collective, device=device)
     if tp == 1 or dp > 1:
-        model = build_model_transform({"_name": "fully_shard", "reshard_after_forward": False}).apply(
+        model = build_model_transform({"_name": "fully_shard", "reshard_after_forward": bool(args.reshard)}).apply(
             model, collective=collective, device=device)
     criterion = build_criterion({"_name": "cross_entropy"}, collective=collective)
     optimizer = build_optimizer({"_name": "adamw", "lr": 3e-4, "betas": [0.9, 0.95], "weight_decay": 0.1},
@@ -283,8 +285,12 @@ def main() -> None:
         step_device(total_steps - 1)   # keep the ranks in lockstep for the collectives of that extra step
     if rank == 0:
         out = {
-            "metric": "Llama-3-8B FSDP2 bf16 train tokens/s (device-timed, max/rank)" if (args.model == "llama3-8b" and args.n_layer is None)
-            else f"{args.model} bf16 train tokens/s (device-timed, max/rank)",
+            "metric": "Llama-3-8B FSDP2 bf16 train tokens/s (device-timed, max/rank)"
+            if (args.model == "llama3-8b" and args.n_layer is None and tp == 1 and not args.fp8 and not args.reshard)
+            else (f"{args.model}{'' if args.n_layer is None else f' ({args.n_layer} layers)'} "
+                  f"{'tp' + str(tp) + '+sp x fsdp' + str(dp) if tp > 1 else 'fsdp' + str(dp)}"
+                  f"{' resharded' if args.reshard else ''} {'fp8 ' + args.fp8_recipe if args.fp8 else 'bf16'} "
+                  "train tokens/s (device-timed, max/rank)"),
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": f"fp8 e4m3 {args.fp8_recipe} GEMMs, bf16 elsewhere" if args.fp8 else "bf16",
@@ -300,6 +306,9 @@ def main() -> None:
             "final_loss": float(last_loss["v"].item()) if "v" in last_loss else None,
             "peak_mem_gb": torch.cuda.max_memory_allocated(device) / 2**30,
         }
+        eng = getattr(model, "_sharding_engine", None)
+        if eng is not None:
+            out["engine_memory_gb"] = {k: round(v / 2**30, 3) for k, v in eng.memory_bytes().items() if not k.startswith("_")}
         print(json.dumps(out))
     if world > 1:
         collective.close()

@@ -221,6 +221,7 @@ def _declare(l: ctypes.CDLL) -> None:
     sig("ob_rs_adamw", [I, P, I, PP, I, P, P, P, P, P, F, F, F, F, F, F, F, F, P, I, I, P, P])
     sig("ob_set_flag_wait_iters", [ctypes.c_uint])
     sig("ob_gemm_ag_bf16", [P, L, P, L, P, L, I, I, I, P, P, I, PP, I, P, P, I, I, I, I, I, P, P])
+    sig("ob_gemm2_ag_bf16", [P, L, P, L, P, L, I, I, I, P, P, I, PP, I, P, P, I, I, I, I, P, P])
     sig("ob_gemm_ag_act_bf16", [P, L, P, P, L, I, P, P, P, L, I, I, I, P, P, I, PP, I, P, P, I, I, I, I, P, P])
     sig("ob_gemm_ag_push_bf16", [P, L, P, L, P, P, L, I, P, P, P, L, I, I, I, P, P, I, PP, PP, I, P, I, I, I, I, P, P])
     sig("ob_gemm_rs_bf16", [P, L, I, P, L, I, P, PP, I, I, I, L, I, I, I, I, P, P])

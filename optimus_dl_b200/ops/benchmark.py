@@ -339,15 +339,170 @@ def bench_tp(op: str, t: Timer, cases) -> None:
     dist.destroy_process_group()
 
 
+def bench_fsdp(op: str, cases) -> None:
+    """The two fused kernels of the fully-sharded engine on one Llama-3-8B-sized transformer block, against the
+    library sequence they replace (launch with torchrun; maximum over ranks):
+
+    * ``fsdp_ag_gemm``: the rows of the fused QKV weight are pulled from their owners by copy CTAs inside the QKV GEMM
+      launch (``ob_gemm_ag_bf16``) vs NCCL all-gather of the weight followed by this package's GEMM;
+    * ``fsdp_rs_adamw``: cross-GPU barrier + reduce-scatter of the block's bf16 gradients in fp32 + AdamW on the fp32
+      shard + bf16 parameter refresh in one kernel (``ob_rs_adamw``) vs NCCL reduce-scatter + the stand-alone fused
+      AdamW kernel (``ob_adamw``).
+
+    Roofline = the slower of (FLOPs at the measured GEMM peak | HBM bytes at the measured copy bandwidth) and the
+    bytes that must cross NVLink into this GPU at 770 GB/s."""
+    import torch.distributed as dist
+    import torch.nn as nn
+
+    from ..parallel import fsdp
+    from . import gemm
+    from . import optim as optim_ops
+
+    rank = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", device_id=dev)
+    world = dist.get_world_size()
+    pk = _peaks()
+    peak_tf, peak_bw, link = pk.get("bf16_tflops", 1590.0), pk.get("hbm_gbs", 6650.0), 770.0
+
+    class Attn(nn.Module):
+        def __init__(self, d, hq, hk, hd):
+            super().__init__()
+            self.wq = nn.Linear(d, hq * hd, bias=False)
+            self.wk = nn.Linear(d, hk * hd, bias=False)
+            self.wv = nn.Linear(d, hk * hd, bias=False)
+            self.wo = nn.Linear(hq * hd, d, bias=False)
+
+    class Block(nn.Module):
+        def __init__(self, d, hq, hk, hd, f):
+            super().__init__()
+            self.attn = Attn(d, hq, hk, hd)
+            self.w1 = nn.Linear(d, f, bias=False)
+            self.w2 = nn.Linear(d, f, bias=False)
+            self.c_proj = nn.Linear(f, d, bias=False)
+            self.ln_1 = nn.Parameter(torch.ones(d))
+            self.ln_2 = nn.Parameter(torch.ones(d))
+
+    class Net(nn.Module):
+        def __init__(self, *a):
+            super().__init__()
+            self.h = nn.ModuleList([Block(*a)])
+
+        def fully_shard(self, **_):
+            return list(self.h)
+
+    def stream_time(fn, reps: int = 10) -> float:
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    for T, d, hq, hk, hd, f in cases:
+        torch.manual_seed(0)
+        with torch.device(dev):
+            net = Net(d, hq, hk, hd, f).to(torch.bfloat16)
+        eng = fsdp.fully_shard_model(net, dist.group.WORLD if world > 1 else None, dev, fsdp.FSDPConfig())
+        g = eng.groups[0]
+        P = sum(i.param.numel() for i in g.infos)
+        if op == "fsdp_ag_gemm":
+            x = torch.randn(T, d, device=dev).bfloat16()
+            nq = (hq + 2 * hk) * hd
+
+            def fused():
+                g.invalidate()
+                g.slot.owner = g
+                g.epoch += 1
+                job = fsdp.AGJob(g, eng.cfg.copy_ctas)
+                return job.run(x, None) if world > 1 else gemm.gemm(x, g.fused_weight())
+
+            shard_rows = torch.randn(nq // world, d, device=dev).bfloat16()
+            full = torch.empty(nq, d, device=dev, dtype=torch.bfloat16)
+
+            def base():
+                if world > 1:
+                    dist.all_gather_into_tensor(full, shard_rows)
+                return gemm.gemm(x, full)
+
+            ms_gemm = stream_time(lambda: gemm.gemm(x, full))
+            vals = torch.tensor([stream_time(fused), stream_time(base), ms_gemm], device=dev)
+            dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+            flops = 2.0 * T * nq * d
+            link_bytes = (world - 1) / world * nq * d * 2
+            roof = max(flops / (peak_tf * 1e9), link_bytes / (link * 1e6))
+            if dist.get_rank() == 0:
+                _emit(op, dict(tokens=T, qkv_rows=nq, d_model=d, world=world), float(vals[0]), flops=flops,
+                      nccl_all_gather_then_gemm_ms=round(float(vals[1]), 4), gemm_only_ms=round(float(vals[2]), 4),
+                      roofline_ms=round(roof, 4), of_roofline=round(roof / float(vals[0]), 3))
+        else:
+            g.ensure_state()
+            hp = dict(lr=1e-4, betas=(0.9, 0.95), eps=1e-8)
+            g.grad_slot.tensor.normal_(0, 1e-3)
+            state = {"n": 0}
+
+            def fused():
+                state["n"] += 1
+                eng.barrier()
+                g.rs_adamw(0, hp, state["n"], 1.0 / world)
+
+            shard_g = torch.empty(g.flat_numel // world, device=dev, dtype=torch.bfloat16)
+            gfull = g.grad_slot.tensor[: g.flat_numel // world * world]
+            m = torch.zeros(shard_g.numel(), device=dev)
+            v = torch.zeros_like(m)
+            w32 = torch.zeros_like(m)
+            wlp = torch.empty_like(shard_g)
+
+            def base():
+                state["n"] += 1
+                if world > 1:
+                    dist.reduce_scatter_tensor(shard_g, gfull)
+                src = shard_g if world > 1 else gfull
+                optim_ops.adamw_step_(w32, m, v, src, wlp, lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0,
+                                      step=state["n"], grad_scale=1.0 / world)
+
+            vals = torch.tensor([stream_time(fused), stream_time(base)], device=dev)
+            dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+            shard = P / world
+            hbm_bytes = shard * 28.0 + (world - 1) / world * P * 2.0      # own shard state + serving the peers' reads
+            link_bytes = (world - 1) * shard * 2.0                        # this rank's rows pulled from every peer
+            roof = max(hbm_bytes / (peak_bw * 1e6), link_bytes / (link * 1e6))
+            if dist.get_rank() == 0:
+                _emit(op, dict(block_params=P, world=world), float(vals[0]), bytes_=hbm_bytes,
+                      nccl_reduce_scatter_then_adamw_ms=round(float(vals[1]), 4), nvlink_bytes_in=int(link_bytes),
+                      roofline_ms=round(roof, 4), of_roofline=round(roof / float(vals[0]), 3))
+        _lib_check(dev)
+        del eng, net
+    torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _lib_check(dev) -> None:
+    from . import _lib
+
+    _lib.check_status(dev)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", required=True, choices=["gemm_bf16", "gemm_skinny", "gemm_fp8", "attention", "decode", "sampler", "elementwise",
-                                                    "tp_ag_gemm", "tp_gemm_rs", "tp_ag_gemm_fp8", "tp_gemm_rs_fp8"])
+                                                    "tp_ag_gemm", "tp_gemm_rs", "tp_ag_gemm_fp8", "tp_gemm_rs_fp8",
+                                                    "fsdp_ag_gemm", "fsdp_rs_adamw"])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--small", action="store_true", help="one small case (for profiler captures)")
     ap.add_argument("--mid", action="store_true", help="attention: one case that fills every SM but holds little memory "
                                                         "(T 4096, 32 / 8 heads), for profiler captures")
     args = ap.parse_args()
+    if "LOCAL_RANK" in os.environ:
+        torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
     t = Timer(args.iters)
     if args.op == "gemm_bf16":
         bench_gemm_bf16(t, [(4096, 4096, 4096)] if args.small else [(8192, 8192, 8192), (8192, 6144, 4096), (8192, 4096, 14336),
@@ -367,6 +522,9 @@ def main() -> None:
         bench_elementwise(t)
     elif args.op == "sampler":
         bench_sampler(t, [(64, 151936)] if args.small else [(64, 151936), (512, 151936)])
+    elif args.op in ("fsdp_ag_gemm", "fsdp_rs_adamw"):
+        # one Llama-3-8B block: 8192 tokens, d_model 4096, 32 / 8 heads of 128, FFN 14336
+        bench_fsdp(args.op, [(8192, 4096, 32, 8, 128, 14336)])
     else:
         bench_tp(args.op, t, [(8192, 6144, 4096), (16384, 5120, 17408 // 2), (16384, 17408 // 2, 5120)])
 

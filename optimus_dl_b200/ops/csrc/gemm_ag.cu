@@ -12,6 +12,7 @@
 // transfer overlaps the tensor-core work tile by tile.  Both weight-gathered (FSDP: B operand)
 // and activation-gathered (sequence parallel: A operand) forms are provided.
 #include "comm.cuh"
+#include "gemm_2sm.cuh"
 #include "gemm_core.cuh"
 #include "tensormap.cuh"
 
@@ -109,10 +110,82 @@ static int launch_ag(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
 }
 
 }  // namespace gemm
+
+namespace gemm2 {
+
+// Weight-gathered form on the two-SM GEMM: the grid is made of CTA pairs (clusters of two); the first n_copy / 2
+// pairs pull remote rows of B with plain peer loads and raise the row-group flags, the other pairs run the paired
+// GEMM whose producers wait for the flags of the 128 B rows each of them stages.
+constexpr int AG2_THREADS = 512;
+
+__global__ void __launch_bounds__(AG2_THREADS, 1)
+ag_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const gemm::Params p,
+                const comm::CopyTask* __restrict__ tasks, int n_tasks, comm::PeerPtrs src, __nv_bfloat16* dst, int* flags,
+                int epoch, int n_copy) {
+  extern __shared__ uint8_t smem_raw[];
+  if ((int)blockIdx.x < n_copy) {
+    comm::run_copy_tasks<16>(tasks, n_tasks, blockIdx.x, n_copy, src, dst, flags, epoch);
+    return;
+  }
+  if (threadIdx.x >= NUM_THREADS) return;  // spare warps of a GEMM CTA
+  gemm2_cta<0, 0, 0>(&tmA, &tmB, &tmB, p, ((int)blockIdx.x - n_copy) >> 1, ((int)gridDim.x - n_copy) >> 1, smem_raw);
+}
+
+}  // namespace gemm2
 }  // namespace ob
 
 using namespace ob;
 using namespace ob::gemm;
+
+// Two-SM form of ob_gemm_ag_bf16 for a gathered B operand (FSDP: the fused QKV weight).  Same arguments; n_copy is
+// rounded up to an even number of copy CTAs.
+extern "C" int ob_gemm2_ag_bf16(const void* A, long long lda, const void* B, long long ldb, void* C, long long ldc,
+                                int M, int N, int K, const void* bias, const void* tasks, int n_tasks,
+                                const void* const* src_ptrs, int world, void* dst, int* flags, int flag_rows,
+                                int epoch, int first_tile_shift, int n_copy, int* status, cudaStream_t stream) {
+  if (world > comm::MAX_RANKS) return -1;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d(&ta, A, M, K, lda, 128, gemm2::BK, 2);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tb, B, N, K, ldb, 128, gemm2::BK, 2);
+  if (rc) return rc;
+  Params p{};
+  p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.alpha = 1.0f; p.bias = bias; p.status = status;
+  p.a_flag_rows = 1;
+  p.b_flags = flags; p.flag_rows = flag_rows > 0 ? flag_rows : 1; p.flag_value = epoch; p.tile_order = 1;
+  p.first_tile_shift = first_tile_shift;
+  auto kern = gemm2::ag_gemm2_kernel;
+  static int max_pairs = 0;
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(gemm2::AG2_THREADS); cfg.dynamicSmemBytes = gemm2::SMEM_BYTES; cfg.stream = stream;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  if (max_pairs == 0) {
+    OB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm2::SMEM_BYTES));
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cfg.gridDim = dim3(sms & ~1);
+    int n = 0;
+    OB_CUDA_CHECK(cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
+    if (n <= 0) return -4;
+    max_pairs = n < sms / 2 ? n : sms / 2;
+  }
+  if (n_tasks == 0) n_copy = 0;
+  n_copy = (n_copy + 1) & ~1;
+  if (n_copy / 2 > max_pairs / 2) n_copy = (max_pairs / 2) * 2;
+  const int tiles = ((M + gemm2::TM - 1) / gemm2::TM) * ((N + gemm2::TN - 1) / gemm2::TN);
+  int pairs = max_pairs - n_copy / 2;
+  if (pairs > tiles) pairs = tiles;
+  if (pairs < 1) return -5;
+  comm::PeerPtrs src{};
+  for (int i = 0; i < world; ++i) src.p[i] = const_cast<void*>(src_ptrs[i]);
+  cfg.gridDim = dim3(n_copy + 2 * pairs);
+  return (int)cudaLaunchKernelEx(&cfg, kern, ta, tb, p, (const comm::CopyTask*)tasks, n_tasks, src, (__nv_bfloat16*)dst,
+                                 flags, epoch, n_copy);
+}
 
 // C[M,N] = A[M,K] B[N,K]^T where B (gather_a = 0) or A (gather_a = 1) is being gathered by this
 // same launch.  `dst` is the local buffer that holds the gathered operand (and possibly more:

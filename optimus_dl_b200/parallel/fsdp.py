@@ -55,6 +55,7 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from ..ops import _lib
+from ..ops import gemm as gemm_ops
 from ..ops import optim as optim_ops
 from . import symm
 
@@ -720,11 +721,20 @@ class AGJob:
         # start with the n-tile that holds this rank's first locally owned row
         first_local = (g.first_gemm_infos[0].flat_off + g.rank * g.first_gemm_infos[0].piece_numel - g.fused_base) // g.fused_k
         shift = (first_local // 256) % max(tiles_n, 1)
-        rc = _lib.lib().ob_gemm_ag_bf16(_lib.ptr(x2), x2.stride(0), _lib.ptr(w), w.stride(0), _lib.ptr(out),
-                                        out.stride(0), M, N, K, _lib.ptr(bias), _lib.ptr(g.first_tasks), g.n_first_tasks,
-                                        g.shard_buf.peers.c, g.world, _lib.ptr(g.slot.tensor), _lib.ptr(g.flags),
-                                        g.flag_rows, g.epoch, 0, shift, self.copy_ctas,
-                                        _lib.ptr(_lib.status_word(x2.device)), _lib.stream())
+        l = _lib.lib()
+        if gemm_ops.USE_2SM and ((M + 255) // 256) * tiles_n >= gemm_ops.PAIR_MIN_TILES - self.copy_ctas // 2:
+            # two-SM tiles, copy CTAs in pairs (csrc/gemm_ag.cu: ob_gemm2_ag_bf16)
+            rc = l.ob_gemm2_ag_bf16(_lib.ptr(x2), x2.stride(0), _lib.ptr(w), w.stride(0), _lib.ptr(out), out.stride(0),
+                                    M, N, K, _lib.ptr(bias), _lib.ptr(g.first_tasks), g.n_first_tasks,
+                                    g.shard_buf.peers.c, g.world, _lib.ptr(g.slot.tensor), _lib.ptr(g.flags),
+                                    g.flag_rows, g.epoch, shift, self.copy_ctas,
+                                    _lib.ptr(_lib.status_word(x2.device)), _lib.stream())
+        else:
+            rc = l.ob_gemm_ag_bf16(_lib.ptr(x2), x2.stride(0), _lib.ptr(w), w.stride(0), _lib.ptr(out),
+                                   out.stride(0), M, N, K, _lib.ptr(bias), _lib.ptr(g.first_tasks), g.n_first_tasks,
+                                   g.shard_buf.peers.c, g.world, _lib.ptr(g.slot.tensor), _lib.ptr(g.flags),
+                                   g.flag_rows, g.epoch, 0, shift, self.copy_ctas,
+                                   _lib.ptr(_lib.status_word(x2.device)), _lib.stream())
         _lib.check(rc, "ob_gemm_ag_bf16")
         self.done = True
         for inf in g.first_gemm_infos:
