@@ -294,11 +294,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
           pk[e / 2] = pack_bf16x2(p0 * (__uint_as_float(dp[e]) - dl), p1 * (__uint_as_float(dp[e + 1]) - dl));
         }
       } else {
+        // packed pairs: one fused multiply-add, one add and one multiply per TWO scores around the two exponentials
+        const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nl2 = make_float2(-lse2, -lse2), nd2 = make_float2(-dl, -dl);
 #pragma unroll
         for (int e = 0; e < HALF; e += 2) {
-          const float p0 = exp2f(fmaf(__uint_as_float(s[e]), p.scale_log2, -lse2));
-          const float p1 = exp2f(fmaf(__uint_as_float(s[e + 1]), p.scale_log2, -lse2));
-          pk[e / 2] = pack_bf16x2(p0 * (__uint_as_float(dp[e]) - dl), p1 * (__uint_as_float(dp[e + 1]) - dl));
+          const float2 t = ffma2(u2f2(s[e], s[e + 1]), sc2, nl2);
+          const float2 pr = make_float2(exp2f(t.x), exp2f(t.y));
+          const float2 r = fmul2(pr, fadd2(u2f2(dp[e], dp[e + 1]), nd2));
+          pk[e / 2] = pack_bf16x2(r.x, r.y);
         }
       }
       if (t > 0) {                               // the previous tile's dQ product has finished reading dS
@@ -470,7 +473,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const bool key_valid = kj < p.N;
     const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16);
     const uint32_t t_s = t_row + hf * HALF, t_dp = t_row + BM + hf * HALF;
-    float* vb = vec + warp * 3 * HALF;          // this warp's copy: lse*log2e, delta, lowest key
+    float* vb = vec + warp * 3 * HALF;          // this warp's copy: -lse*log2e, -delta, lowest key
     int* lo_s = reinterpret_cast<int*>(vb + 2 * HALF);
     bool ok = true;
     for (int it = 0; it < n_iter && ok; ++it) {
@@ -488,7 +491,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           lo = p.doc_start[qi];
           if (p.window > 0) lo = max(lo, qi - p.window + 1);
         }
-        vb[cc] = l2; vb[HALF + cc] = dl; lo_s[cc] = lo;
+        vb[cc] = -l2; vb[HALF + cc] = -dl; lo_s[cc] = lo;
       }
       __syncwarp();
       ok = mbar_wait(&sdp_full[hf], it & 1, abort_flag, p.status);
@@ -514,26 +517,26 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           for (int u = 0; u < 4; ++u) {
             const int qi = q_first + e + u;
             const bool valid = key_valid && kj <= qi && kj >= lov[u];
-            pr[u] = valid ? exp2f(fmaf(__uint_as_float(s[e + u]), p.scale_log2, -lv[u])) : 0.f;
-            ds[u] = pr[u] * (__uint_as_float(dp[e + u]) - dv4[u]);
+            pr[u] = valid ? exp2f(fmaf(__uint_as_float(s[e + u]), p.scale_log2, lv[u])) : 0.f;
+            ds[u] = pr[u] * (__uint_as_float(dp[e + u]) + dv4[u]);
           }
           pk[e / 2] = pack_bf16x2(pr[0], pr[1]); pk[e / 2 + 1] = pack_bf16x2(pr[2], pr[3]);
           dk_[e / 2] = pack_bf16x2(ds[0], ds[1]); dk_[e / 2 + 1] = pack_bf16x2(ds[2], ds[3]);
         }
       } else {
+        // vb holds -lse*log2e and -delta of the 64 query columns, so that both enter packed add / fma forms directly
+        const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
 #pragma unroll
         for (int e = 0; e < HALF; e += 4) {
           const float4 l4 = *reinterpret_cast<const float4*>(vb + e);
           const float4 d4 = *reinterpret_cast<const float4*>(vb + HALF + e);
-          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv4[4] = {d4.x, d4.y, d4.z, d4.w};
-          float pr[4], ds[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            pr[u] = exp2f(fmaf(__uint_as_float(s[e + u]), p.scale_log2, -lv[u]));
-            ds[u] = pr[u] * (__uint_as_float(dp[e + u]) - dv4[u]);
-          }
-          pk[e / 2] = pack_bf16x2(pr[0], pr[1]); pk[e / 2 + 1] = pack_bf16x2(pr[2], pr[3]);
-          dk_[e / 2] = pack_bf16x2(ds[0], ds[1]); dk_[e / 2 + 1] = pack_bf16x2(ds[2], ds[3]);
+          const float2 t0 = ffma2(u2f2(s[e], s[e + 1]), sc2, make_float2(l4.x, l4.y));
+          const float2 t1 = ffma2(u2f2(s[e + 2], s[e + 3]), sc2, make_float2(l4.z, l4.w));
+          const float2 p0 = make_float2(exp2f(t0.x), exp2f(t0.y)), p1 = make_float2(exp2f(t1.x), exp2f(t1.y));
+          const float2 r0 = fmul2(p0, fadd2(u2f2(dp[e], dp[e + 1]), make_float2(d4.x, d4.y)));
+          const float2 r1 = fmul2(p1, fadd2(u2f2(dp[e + 2], dp[e + 3]), make_float2(d4.z, d4.w)));
+          pk[e / 2] = pack_bf16x2(p0.x, p0.y); pk[e / 2 + 1] = pack_bf16x2(p1.x, p1.y);
+          dk_[e / 2] = pack_bf16x2(r0.x, r0.y); dk_[e / 2 + 1] = pack_bf16x2(r1.x, r1.y);
         }
       }
       tmem_st_32x16(t_s, pk);

@@ -239,19 +239,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_ld_wait();
         const int k0 = j * BN;
         const bool need_mask = (k0 + BN - 1 > r.q_lo) || (k0 < r.lo_last);
+        // Unmasked tiles work on the raw scores: the maximum commutes with the (positive) scale, and scale and
+        // reference maximum fold into one fused multiply-add per PAIR of scores in front of the exponential.
         float mx = -INFINITY;
         if (need_mask) {
 #pragma unroll
           for (int c = 0; c < BN; ++c) {
             const int kj = k0 + c;
             const bool valid = row_valid && kj <= qi && kj >= lo_row;
-            s[c] = valid ? s[c] * p.scale_log2 : -INFINITY;
+            s[c] = valid ? s[c] : -INFINITY;
             mx = fmaxf(mx, s[c]);
           }
         } else {
+          float mx2 = -INFINITY;
 #pragma unroll
-          for (int c = 0; c < BN; ++c) { s[c] *= p.scale_log2; mx = fmaxf(mx, s[c]); }
+          for (int c = 0; c < BN; c += 4) { mx = fmax3(mx, s[c], s[c + 1]); mx2 = fmax3(mx2, s[c + 2], s[c + 3]); }
+          mx = fmaxf(mx, mx2);
         }
+        mx *= p.scale_log2;          // -inf stays -inf
         // lazy rescale: keep the old reference max unless the new one is much larger
         float alpha = 1.0f;
         const float m_new = fmaxf(m_run, mx);
@@ -262,14 +267,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           l_run *= alpha;
         }
         const float m_use = (m_run == -INFINITY) ? 0.0f : m_run;
-        float sum = 0.f;
+        const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-m_use, -m_use);
+        float2 sum2 = make_float2(0.f, 0.f), sum2b = make_float2(0.f, 0.f);   // two chains of packed adds
         uint32_t pk[BN / 2];
 #pragma unroll
-        for (int c = 0; c < BN; c += 2) {
-          const float p0 = exp2f(s[c] - m_use), p1 = exp2f(s[c + 1] - m_use);
-          sum += p0 + p1;
-          pk[c / 2] = pack_bf16x2(p0, p1);
+        for (int c = 0; c < BN; c += 4) {
+          const float2 t0 = ffma2(make_float2(s[c], s[c + 1]), sc2, nm2);     // masked scores: -inf * scale = -inf
+          const float2 t1 = ffma2(make_float2(s[c + 2], s[c + 3]), sc2, nm2);
+          const float2 e0 = make_float2(exp2f(t0.x), exp2f(t0.y));
+          const float2 e1 = make_float2(exp2f(t1.x), exp2f(t1.y));
+          sum2 = fadd2(sum2, e0);
+          sum2b = fadd2(sum2b, e1);
+          pk[c / 2] = pack_bf16x2(e0.x, e0.y);
+          pk[c / 2 + 1] = pack_bf16x2(e1.x, e1.y);
         }
+        sum2 = fadd2(sum2, sum2b);
+        const float sum = sum2.x + sum2.y;
         l_run += sum;
         if (j > r.lo && __any_sync(0xffffffffu, bump)) {
           // O of this tile was produced with the old reference max: scale it (whole warp takes part)
