@@ -70,7 +70,7 @@ class _CountingLib:
         return counted
 
 
-_NO_LAUNCH = {"ob_norm_bwd_grid", "ob_rope_grid", "ob_bind_thread", "ob_set_flag_wait_iters"}
+_NO_LAUNCH = {"ob_norm_bwd_grid", "ob_rope_grid", "ob_bind_thread", "ob_set_flag_wait_iters", "ob_gemm_skinny_splits"}
 _tls = threading.local()
 
 
@@ -192,6 +192,8 @@ def _declare(l: ctypes.CDLL) -> None:
 
     sig("ob_gemm_bf16", [P, L, I, P, L, I, P, L, I, I, I, I, I, P, I, F, P, I, I, P, I, I, I, I, I, P, P])
     sig("ob_gemm_swiglu_bf16", [P, L, P, P, L, P, P, P, L, I, I, I, P, P])
+    sig("ob_gemm_skinny_bf16", [P, L, P, L, P, L, I, I, I, P, I, P, P])
+    sig("ob_gemm_skinny_splits", [I, I])
     sig("ob_gemm2_bf16", [P, L, I, P, L, I, P, L, I, I, I, I, I, P, I, F, I, P, P])
     sig("ob_gemm2_swiglu_bf16", [P, L, P, P, L, P, P, P, L, I, I, I, P, P])
     sig("ob_rmsnorm_fwd", [P, P, P, P, P, P, I, I, F, P])

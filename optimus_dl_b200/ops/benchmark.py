@@ -121,6 +121,22 @@ def bench_gemm_bf16(t: Timer, sizes) -> None:
               cublas_plus_eager_ms=round(t(lib), 4))
 
 
+def bench_gemm_skinny(t: Timer, sizes) -> None:
+    """Decode-step products (M <= 64 rows): the weight-streaming kernel against ``torch.matmul``; the rate is the
+    weight bytes over the time, to be read against the measured copy bandwidth."""
+    from . import gemm
+
+    for M, N, K in sizes:
+        a = torch.randn(M, K, device="cuda").bfloat16()
+        b = torch.randn(N, K, device="cuda").bfloat16()
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        with torch.no_grad():
+            ms = t(lambda: gemm.gemm(a, b, out=out))
+            ms_ref = t(lambda: torch.matmul(a, b.t(), out=out))
+        _emit("gemm_skinny", dict(M=M, N=N, K=K), ms, bytes_=2.0 * N * K + 2.0 * M * (N + K), cublas_ms=round(ms_ref, 4),
+              vs_cublas=round(ms_ref / ms, 3))
+
+
 def bench_gemm_fp8(t: Timer, sizes) -> None:
     from . import fp8
 
@@ -508,7 +524,7 @@ def main() -> None:
         bench_gemm_bf16(t, [(4096, 4096, 4096)] if args.small else [(8192, 8192, 8192), (8192, 6144, 4096), (8192, 4096, 14336),
                                                                     (8192, 28672, 4096)])
     elif args.op == "gemm_skinny":   # decode-step shapes of a 1.7B model at batch 64: weight-streaming bound
-        bench_gemm_bf16(t, [(64, 4096, 2048), (64, 12288, 2048), (64, 2048, 6144), (64, 151936, 2048), (8, 4096, 4096)])
+        bench_gemm_skinny(t, [(64, 4096, 2048), (64, 12288, 2048), (64, 2048, 6144), (64, 151936, 2048), (8, 4096, 4096)])
     elif args.op == "gemm_fp8":
         bench_gemm_fp8(t, [(4096, 4096, 4096)] if args.small else [(8192, 8192, 8192), (8192, 6144, 4096), (8192, 4096, 14336),
                                                                    (8192, 28672, 4096)])

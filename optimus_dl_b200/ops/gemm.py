@@ -27,7 +27,12 @@ PAIR_MIN_TILES = 74
 USE_2SM = os.environ.get("OB_GEMM_2SM", "1") != "0"
 
 ACT = {"none": 0, "gelu": 1, "relu2": 2, "silu": 3}
-SKINNY_M = 64   # inference-only products with at most this many rows use the library GEMM (see gemm())
+SKINNY_M = 64   # inference-only products with at most this many rows are weight-streaming problems (see gemm())
+# ... and go to csrc/gemm_skinny.cu when the weight has at least this many elements. Measured on B200 inside a CUDA-graph
+# replay of a decode step: the kernel's fixed cost per launch (barrier set-up, TMEM allocation, first TMA round trip,
+# cluster barrier of the split form) makes it 1.3x slower than the library on the 4 to 25 MB weights of a 1.7B model,
+# and it reaches 0.83 of the library's time on the 622 MB vocabulary projection. Smaller weights use torch.matmul.
+SKINNY_MIN_WEIGHT = int(os.environ.get("OB_SKINNY_MIN_WEIGHT", 16 * 1024 * 1024))
 
 
 def _use_kernel(*ts: torch.Tensor) -> bool:
@@ -100,14 +105,23 @@ def gemm(
         else:
             out.copy_(r.to(out.dtype))
         return out
-    if (M <= SKINNY_M and not a_mn and not accumulate and act == "none" and alpha == 1.0 and out.dtype == torch.bfloat16
-            and b_flags is None and a_flags is None and out.is_contiguous() and not torch.is_grad_enabled()):
-        # single-token decode steps: a handful of rows against a whole weight matrix is a weight-streaming
-        # problem that wants split-K / narrow tiles over all SMs, not 128 x 256 output tiles; this plain
-        # product (no fused epilogue, no collective) goes to the library
+    skinny = (M <= SKINNY_M and not a_mn and not accumulate and act == "none" and alpha == 1.0
+              and out.dtype == torch.bfloat16 and b_flags is None and a_flags is None and not torch.is_grad_enabled())
+    if skinny and (b_mn or N * K < SKINNY_MIN_WEIGHT) and out.is_contiguous():
         torch.matmul(a, b if b_mn else b.t(), out=out)
         if bias is not None:
             out.add_(bias)
+        return out
+    if skinny and not b_mn:
+        # single-token decode steps: a handful of rows against a whole weight matrix is a weight-streaming
+        # problem; csrc/gemm_skinny.cu puts 128 weight rows on the M side of the tensor-core product, the token
+        # rows on its N side, and splits the reduction over the CTAs of a cluster when the weight has few row tiles
+        l = _lib.lib()
+        splits = int(l.ob_gemm_skinny_splits(N, K))
+        rc = l.ob_gemm_skinny_bf16(_lib.ptr(a), a.stride(0), _lib.ptr(b), b.stride(0), _lib.ptr(out), out.stride(0),
+                                   M, N, K, _lib.ptr(bias), splits,
+                                   _lib.ptr(_lib.status_word(a.device)), _lib.stream())
+        _lib.check(rc, "ob_gemm_skinny_bf16")
         return out
     l = _lib.lib()
     if (USE_2SM and b_flags is None and a_flags is None and tile_order == 0

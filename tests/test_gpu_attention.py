@@ -93,3 +93,58 @@ def test_qkv_attention_forward_backward(hd, use_norm, N, lens, window):
     assert rel(dx_k, dx_r) < 5e-2, rel(dx_k, dx_r)
     if use_norm:
         assert rel(da_k, da_r) < 8e-2 and rel(db_k, db_r) < 8e-2, (rel(da_k, da_r), rel(db_k, db_r))
+
+
+def _exp_doc_lengths(total, seed=0, mean=2048, lo=32):
+    g = torch.Generator().manual_seed(seed)
+    lens, n = [], 0
+    while n < total:
+        l = max(lo, int(torch.empty(1).exponential_(1.0 / mean, generator=g).item()))
+        lens.append(min(l, total - n))
+        n += lens[-1]
+    return lens
+
+
+@pytest.mark.parametrize("T,Hq,Hk,packed", [(8192, 32, 8, False), (8192, 32, 8, True), (16384, 40, 8, True)])
+def test_attention_at_flagship_shapes(T, Hq, Hk, packed):
+    """Full sequence lengths of the benchmark configs (hundreds of key tiles, document boundaries inside 128-row
+    tiles at large offsets): forward and backward of the kernels against an fp32 masked-softmax reference evaluated
+    completely for the query heads of two key/value groups."""
+    from optimus_dl_b200.ops import _lib
+    from optimus_dl_b200.ops.attention import build_doc_start, mask_from_doc_start, qkv_attention
+
+    torch.manual_seed(0)
+    dev = torch.device("cuda", 0)
+    hd, G = 128, Hq // Hk
+    qkv = (torch.randn(1, T, (Hq + 2 * Hk) * hd, device=dev) * 0.7).bfloat16().requires_grad_(True)
+    ds = _docs(T, _exp_doc_lengths(T), dev) if packed else build_doc_start(1, T, dev)
+    dout = torch.randn(1, T, Hq * hd, device=dev).bfloat16()
+    out = qkv_attention(qkv, n_head=Hq, n_kv_head=Hk, head_dim=hd, doc_start=ds)
+    out.backward(dout)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    dqkv = qkv.grad[0]
+    scale = 1.0 / math.sqrt(hd)
+    mask = mask_from_doc_start(ds)
+    flat = qkv.detach()[0]
+    for kvh in (1, Hk - 1):
+        kf = flat[:, (Hq + kvh) * hd:(Hq + kvh + 1) * hd].float().requires_grad_(True)
+        vf = flat[:, (Hq + Hk + kvh) * hd:(Hq + Hk + kvh + 1) * hd].float().requires_grad_(True)
+        for h in range(kvh * G, (kvh + 1) * G):
+            qf = flat[:, h * hd:(h + 1) * hd].float().requires_grad_(True)
+            s = (qf @ kf.t()) * scale
+            p = torch.softmax(s.masked_fill(~mask, float("-inf")), dim=-1)
+            o = p @ vf
+            del s, p
+            o.backward(dout[0, :, h * hd:(h + 1) * hd].float())
+            got_o = out[0, :, h * hd:(h + 1) * hd].float()
+            assert (got_o - o.detach()).abs().max().item() < 3e-2, f"out head {h}"
+            got_dq = dqkv[:, h * hd:(h + 1) * hd].float()
+            tol = 2e-2 * qf.grad.abs().max().item() + 1e-3
+            assert (got_dq - qf.grad).abs().max().item() < tol, f"dq head {h}"
+            del o, qf
+        for name, ref_g, off in (("dk", kf.grad, Hq + kvh), ("dv", vf.grad, Hq + Hk + kvh)):
+            got = dqkv[:, off * hd:(off + 1) * hd].float()
+            tol = 2e-2 * ref_g.abs().max().item() + 1e-3
+            assert (got - ref_g).abs().max().item() < tol, f"{name} group {kvh}"
+        del kf, vf

@@ -84,6 +84,61 @@ def test_gemm_two_sm_epilogues_and_swiglu():
     _lib.check_status()
 
 
+@pytest.mark.parametrize("layout", ["fwd", "dgrad", "wgrad"])
+def test_gemm_at_flagship_shapes(layout):
+    """The MLP products of the 8B config at full size (8192 tokens, 4096 x 14336), in the three operand layouts of
+    a linear layer, checked on sampled rows against fp32."""
+    from optimus_dl_b200.ops import _lib, gemm
+
+    torch.manual_seed(5)
+    T, D, F = 8192, 4096, 14336
+    if layout == "fwd":        # h[T,F] W[D,F]^T
+        a = torch.randn(T, F, device=_dev()).bfloat16()
+        b = (torch.randn(D, F, device=_dev()) * 0.05).bfloat16()
+        out = gemm.gemm(a, b)
+        rows = torch.randint(0, T, (96,), device=_dev())
+        ref = a[rows].float() @ b.float().t()
+    elif layout == "dgrad":    # dy[T,D] W[D,F]  (W read MN-major)
+        a = torch.randn(T, D, device=_dev()).bfloat16()
+        b = (torch.randn(D, F, device=_dev()) * 0.05).bfloat16()
+        out = gemm.gemm(a, b, b_mn=True)
+        rows = torch.randint(0, T, (96,), device=_dev())
+        ref = a[rows].float() @ b.float()
+    else:                      # dy[T,F]^T x[T,D]  (both MN-major, K = tokens)
+        a = torch.randn(T, F, device=_dev()).bfloat16()
+        b = torch.randn(T, D, device=_dev()).bfloat16()
+        out = gemm.gemm(a, b, a_mn=True, b_mn=True)
+        rows = torch.randint(0, F, (96,), device=_dev())
+        ref = a[:, rows].float().t() @ b.float()
+    torch.cuda.synchronize()
+    _lib.check_status()
+    _close(out[rows], ref, 1e-2, 1e-2, f"{layout} at flagship size")
+
+
+@pytest.mark.parametrize("M", [1, 8, 33, 64])
+@pytest.mark.parametrize("N,K", [(4104, 2048), (1000, 200), (151936, 512)])
+def test_gemm_skinny_decode_shapes(M, N, K, monkeypatch):
+    """At most 64 rows without gradients: the weight-streaming kernel (weight rows on the M side of the MMA, the
+    reduction split over the CTAs of a cluster when there are few weight tiles), with and without bias. The size
+    threshold below which the library is used is lowered so that every shape reaches the kernel."""
+    from optimus_dl_b200.ops import _lib, gemm
+
+    monkeypatch.setattr(gemm, "SKINNY_MIN_WEIGHT", 0)
+    torch.manual_seed(3)
+    x = torch.randn(M, K, device=_dev(), dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device=_dev()) * 0.1).to(torch.bfloat16)
+    bias = torch.randn(N, device=_dev(), dtype=torch.bfloat16)
+    before = _lib.launch_count()
+    with torch.no_grad():
+        y = gemm.gemm(x, w)
+        yb = gemm.gemm(x, w, bias=bias)
+    assert _lib.launch_count() - before == 2      # both products went through this library's launcher, not a library GEMM
+    ref = x.float() @ w.float().t()
+    _lib.check_status()
+    _close(y, ref, 1e-2, 1e-2, "skinny")
+    _close(yb, ref + bias.float(), 1e-2, 1e-2, "skinny + bias")
+
+
 def test_gemm_epilogues():
     from optimus_dl_b200.ops import _lib, gemm
 
