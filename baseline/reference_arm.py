@@ -12,7 +12,9 @@ timed is the reference's own code, reached through its public registries:
   policy (bf16 parameters, fp32 gradient reduction); on one rank the reference itself skips the wrapping;
 * `CrossEntropyCriterion` (optimus_dl/modules/criterion/cross_entropy.py:42);
 * `adamw` with `fused=True` (optimus_dl/modules/optim/adamw.py:42);
-* bf16 autocast as built by the train recipe (optimus_dl/recipe/train/mixins/execution/context_mixin.py:136).
+* bf16 autocast as built by the train recipe (optimus_dl/recipe/train/mixins/execution/context_mixin.py:136);
+* the `compile` transform (optimus_dl/modules/model_transforms/compile.py:33) last, as configs/train/train_llama.yaml
+  lists it; if `torch.compile` fails on this image the same model runs eagerly and the printed line says which ran.
 
 This module imports nothing from `optimus_dl_b200` and loads none of its native libraries.
 The training step, the synthetic data, warm-up, CUDA-event timing and max-over-ranks are the same as in
@@ -124,11 +126,15 @@ def run(args, models: dict, clock_sampler_cls) -> None:
     vocab = mcfg["vocab_size"]
     total_steps = warmup + args.steps
 
-    variants = [v for v in (args.ref_variant or "").split(",") if v] or (
+    names = [v for v in (args.ref_variant or "").split(",") if v] or (
         ["stock", "stock+activation_checkpoint"] if world == 1 else ["stock"])
-    use_compile = bool(args.ref_compile)
+    # the reference's own training config lists the `compile` transform after `fully_shard`
+    # (configs/train/train_llama.yaml), so that is the form measured first; if torch.compile fails on this image the
+    # same variant runs eagerly and the JSON line says so
+    compile_modes = [False] if args.ref_no_compile else [True, False]
+    variants = [(n, c) for n in names for c in compile_modes]
 
-    def build(variant: str):
+    def build(variant: str, use_compile: bool):
         transforms = [{"_name": "fully_shard", "reshard_after_forward": False,
                        "mixed_precision": {"param_dtype": "bfloat16", "reduce_dtype": "float32"}}]
         if "activation_checkpoint" in variant:
@@ -156,10 +162,10 @@ def run(args, models: dict, clock_sampler_cls) -> None:
 
     result = None
     tried = []
-    for variant in variants:
+    for variant, use_compile in variants:
         model = criterion = optimizer = None
         try:
-            model, criterion, optimizer = build(variant)
+            model, criterion, optimizer = build(variant, use_compile)
             amp_ctx = lambda: torch.autocast(device.type, dtype=torch.bfloat16, enabled=True)  # noqa: E731
             accumulation = getattr(model, "accumulation_context", None)
 
@@ -217,15 +223,25 @@ def run(args, models: dict, clock_sampler_cls) -> None:
                 e2e = {"value": tokens_per_step * args.steps / (ms2 / 1e3), "unit": "tokens/s",
                        "h2d_bytes_per_step": int(host_batches[0].numel() * host_batches.element_size()),
                        "d2h_bytes_per_step": 4, "ms_per_step": ms2 / args.steps, "final_loss": last.get("f")}
-            result = dict(variant=variant, ms=ms, value=value, clocks=clocks, e2e=e2e,
+            result = dict(variant=variant, compiled=use_compile, ms=ms, value=value, clocks=clocks, e2e=e2e,
                           final_loss=float(last["v"].item()), wall_s=time.time() - t0)
             break
         except torch.OutOfMemoryError as err:
-            tried.append(f"{variant}: out of device memory ({str(err)[:80]})")
+            tried.append(f"{variant}{' + compile' if use_compile else ''}: out of device memory ({str(err)[:80]})")
             # every rank takes the same branch: memory use is symmetric across ranks
             model = criterion = optimizer = None
             gc.collect()
             torch.cuda.empty_cache()
+            continue
+        except Exception as err:  # noqa: BLE001
+            if not use_compile:
+                raise
+            tried.append(f"{variant} + compile: {type(err).__name__}: {str(err)[:120]}")
+            model = criterion = optimizer = None
+            gc.collect()
+            torch.cuda.empty_cache()
+            if world > 1:
+                dist.barrier(device_ids=[local_rank])
             continue
 
     if rank == 0:
@@ -244,8 +260,8 @@ def run(args, models: dict, clock_sampler_cls) -> None:
                            "parallelism": (f"fsdp{world}" if world > 1 else "single GPU (the reference skips FSDP wrapping on one rank)"),
                            "packed_docs": False,
                            "optimizer": "torch.optim.AdamW(fused=True) on fp32 parameters" + (" sharded by FSDP2" if world > 1 else ""),
-                           "reference_variant": result["variant"], "variants_out_of_memory": tried,
-                           "torch_compile": use_compile,
+                           "reference_variant": result["variant"], "variants_that_failed": tried,
+                           "torch_compile": result["compiled"],
                            "precision": ("FSDP2 MixedPrecisionPolicy(param bf16, reduce fp32) + bf16 autocast" if world > 1
                                          else "fp32 parameters + bf16 autocast (the reference's AMP path)"),
                            "reference_tree_sha256": tree_digest(os.path.join(root, "optimus_dl")),

@@ -111,8 +111,9 @@ def main() -> None:
     ap.add_argument("--ref-variant", default=None, help="reference arm only: comma-separated list tried in order, from "
                     "'stock' and 'stock+activation_checkpoint' (default: stock, then on one GPU the checkpointed form if "
                     "the stock form runs out of device memory)")
-    ap.add_argument("--ref-compile", action="store_true", help="reference arm only: append the reference's `compile` "
-                    "transform (torch.compile of the whole model, as configs/train/train_llama.yaml lists it)")
+    ap.add_argument("--ref-no-compile", action="store_true", help="reference arm only: leave out the reference's `compile` "
+                    "transform (torch.compile of the whole model, which configs/train/train_llama.yaml lists and the arm "
+                    "applies by default, falling back to eager execution if compilation fails)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -308,7 +309,11 @@ def main() -> None:
         }
         eng = getattr(model, "_sharding_engine", None)
         if eng is not None:
-            out["engine_memory_gb"] = {k: round(v / 2**30, 3) for k, v in eng.memory_bytes().items() if not k.startswith("_")}
+            mem = eng.memory_bytes()
+            out["engine_memory_gb"] = {k: round(v / 2**30, 3) for k, v in mem.items() if not k.startswith("_")}
+            # symmetric allocations (shards, gradient slots) do not go through the caching allocator's statistics
+            symmetric = (mem["bf16_shards"] + mem["gradient_slots"]) if world > 1 else 0
+            out["peak_mem_incl_symmetric_gb"] = out["peak_mem_gb"] + symmetric / 2**30
         print(json.dumps(out))
     if world > 1:
         collective.close()

@@ -126,6 +126,7 @@ def bench_gemm_skinny(t: Timer, sizes) -> None:
     weight bytes over the time, to be read against the measured copy bandwidth."""
     from . import gemm
 
+    gemm.SKINNY_MIN_WEIGHT = 0      # measure the kernel at every size (gemm() sends small weights to the library)
     for M, N, K in sizes:
         a = torch.randn(M, K, device="cuda").bfloat16()
         b = torch.randn(N, K, device="cuda").bfloat16()
