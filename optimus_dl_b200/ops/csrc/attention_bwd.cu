@@ -28,7 +28,7 @@ constexpr int BM = 128;
 constexpr int BN = 128;
 constexpr int HALF = 64;
 constexpr int STAGES = 2;
-constexpr int THREADS = 320;      // 8 compute warps + TMA warp + MMA warp
+constexpr int THREADS = 384;      // 8 compute warps + TMA warp + MMA warp + 2 warps that only give up registers
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct BwdParams {
@@ -159,80 +159,86 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 8) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      mbar_arrive_expect_tx(do_full, L::TILE);
+  // The third warpgroup (two single-thread roles and two idle warps) hands registers to the two compute
+  // warpgroups, whose threads hold a whole row of a tile.
+  if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+    if (warp == 8) {
+      // ------------------------------------------------------------------ TMA producer
+      if (lane == 0) {
+        mbar_arrive_expect_tx(do_full, L::TILE);
 #pragma unroll
-      for (int s = 0; s < SLABS; ++s) tma_load_2d(smem + L::DO_OFF + s * SLAB_BYTES, &tmDO, do_full, h * HD + s * 64, q_lo);
-      bool ok = true;
-      for (int t = 0; t < n_tiles && ok; ++t) {
-        const int st = t % DQ_STAGES, j = j_lo + t;
-        const uint32_t ph = (t / DQ_STAGES) & 1;
-        ok = mbar_wait(&k_empty[st], ph ^ 1, abort_flag, p.status);
-        if (!ok) break;
-        mbar_arrive_expect_tx(&k_full[st], L::TILE);
-#pragma unroll
-        for (int s = 0; s < SLABS; ++s)
-          tma_load_2d(smem + L::K_OFF + st * L::TILE + s * SLAB_BYTES, &tmK, &k_full[st], kvh * HD + s * 64, j * BN);
-        ok = mbar_wait(&v_empty[st], ph ^ 1, abort_flag, p.status);
-        if (!ok) break;
-        mbar_arrive_expect_tx(&v_full[st], L::TILE);
-#pragma unroll
-        for (int s = 0; s < SLABS; ++s)
-          tma_load_2d(smem + L::V_OFF + st * L::TILE + s * SLAB_BYTES, &tmV, &v_full[st], kvh * HD + s * 64, j * BN);
-      }
-    }
-  } else if (warp == 9) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(BM, BN, 0, 0);
-      constexpr uint32_t idesc_dq = make_idesc_bf16(BM, HD, 0, 1);
-      const uint32_t sDO = smem_u32(smem + L::DO_OFF);
-      const uint32_t sK = smem_u32(smem + L::K_OFF), sV = smem_u32(smem + L::V_OFF);
-      bool ok = mbar_wait(a_ready, 0, abort_flag, p.status);
-      if (ok) ok = mbar_wait(do_full, 0, abort_flag, p.status);
-
-      auto issue_sdp = [&](int t) -> bool {
-        const int st = t % DQ_STAGES;
-        const uint32_t ph = (t / DQ_STAGES) & 1;
-        if (!mbar_wait(&k_full[st], ph, abort_flag, p.status)) return false;
-        if (!mbar_wait(&v_full[st], ph, abort_flag, p.status)) return false;
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (kk / 4) * SLAB_BYTES + (kk % 4) * 32;
-          umma_f16_ts(tmem_base + T_S, tmem_base + T_QA + kk * 8,
-                      make_smem_desc_sw128(sK + st * L::TILE + off, 16, 1024), idesc_s, kk ? 1u : 0u);
-          umma_f16_ss(tmem_base + T_DP, make_smem_desc_sw128(sDO + off, 16, 1024),
-                      make_smem_desc_sw128(sV + st * L::TILE + off, 16, 1024), idesc_s, kk ? 1u : 0u);
-        }
-        umma_commit(sdp_full);
-        umma_commit(&v_empty[st]);
-        return true;
-      };
-
-      if (ok) ok = issue_sdp(0);
-      for (int t = 0; t < n_tiles && ok; ++t) {
-        const int st = t % DQ_STAGES;
-        if (t + 1 < n_tiles) {
-          ok = mbar_wait(sdp_free, t & 1, abort_flag, p.status);
-          if (ok) ok = issue_sdp(t + 1);
+        for (int s = 0; s < SLABS; ++s) tma_load_2d(smem + L::DO_OFF + s * SLAB_BYTES, &tmDO, do_full, h * HD + s * 64, q_lo);
+        bool ok = true;
+        for (int t = 0; t < n_tiles && ok; ++t) {
+          const int st = t % DQ_STAGES, j = j_lo + t;
+          const uint32_t ph = (t / DQ_STAGES) & 1;
+          ok = mbar_wait(&k_empty[st], ph ^ 1, abort_flag, p.status);
           if (!ok) break;
-        }
-        ok = mbar_wait(ds_ready, t & 1, abort_flag, p.status);
-        if (!ok) break;
-        tc_fence_after();
+          mbar_arrive_expect_tx(&k_full[st], L::TILE);
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk)
-          umma_f16_ts(tmem_base + T_DQ, tmem_base + T_DS + kk * 8,
-                      make_smem_desc_sw128(sK + st * L::TILE + kk * 2048, SLAB_BYTES, 1024), idesc_dq, (t > 0 || kk) ? 1u : 0u);
-        umma_commit(dq_done);
-        umma_commit(&k_empty[st]);
+          for (int s = 0; s < SLABS; ++s)
+            tma_load_2d(smem + L::K_OFF + st * L::TILE + s * SLAB_BYTES, &tmK, &k_full[st], kvh * HD + s * 64, j * BN);
+          ok = mbar_wait(&v_empty[st], ph ^ 1, abort_flag, p.status);
+          if (!ok) break;
+          mbar_arrive_expect_tx(&v_full[st], L::TILE);
+#pragma unroll
+          for (int s = 0; s < SLABS; ++s)
+            tma_load_2d(smem + L::V_OFF + st * L::TILE + s * SLAB_BYTES, &tmV, &v_full[st], kvh * HD + s * 64, j * BN);
+        }
+      }
+    } else if (warp == 9) {
+      // ------------------------------------------------------------------ MMA issuer
+      if (lane == 0) {
+        constexpr uint32_t idesc_s = make_idesc_bf16(BM, BN, 0, 0);
+        constexpr uint32_t idesc_dq = make_idesc_bf16(BM, HD, 0, 1);
+        const uint32_t sDO = smem_u32(smem + L::DO_OFF);
+        const uint32_t sK = smem_u32(smem + L::K_OFF), sV = smem_u32(smem + L::V_OFF);
+        bool ok = mbar_wait(a_ready, 0, abort_flag, p.status);
+        if (ok) ok = mbar_wait(do_full, 0, abort_flag, p.status);
+
+        auto issue_sdp = [&](int t) -> bool {
+          const int st = t % DQ_STAGES;
+          const uint32_t ph = (t / DQ_STAGES) & 1;
+          if (!mbar_wait(&k_full[st], ph, abort_flag, p.status)) return false;
+          if (!mbar_wait(&v_full[st], ph, abort_flag, p.status)) return false;
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < HD / 16; ++kk) {
+            const uint32_t off = (kk / 4) * SLAB_BYTES + (kk % 4) * 32;
+            umma_f16_ts(tmem_base + T_S, tmem_base + T_QA + kk * 8,
+                        make_smem_desc_sw128(sK + st * L::TILE + off, 16, 1024), idesc_s, kk ? 1u : 0u);
+            umma_f16_ss(tmem_base + T_DP, make_smem_desc_sw128(sDO + off, 16, 1024),
+                        make_smem_desc_sw128(sV + st * L::TILE + off, 16, 1024), idesc_s, kk ? 1u : 0u);
+          }
+          umma_commit(sdp_full);
+          umma_commit(&v_empty[st]);
+          return true;
+        };
+
+        if (ok) ok = issue_sdp(0);
+        for (int t = 0; t < n_tiles && ok; ++t) {
+          const int st = t % DQ_STAGES;
+          if (t + 1 < n_tiles) {
+            ok = mbar_wait(sdp_free, t & 1, abort_flag, p.status);
+            if (ok) ok = issue_sdp(t + 1);
+            if (!ok) break;
+          }
+          ok = mbar_wait(ds_ready, t & 1, abort_flag, p.status);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < BN / 16; ++kk)
+            umma_f16_ts(tmem_base + T_DQ, tmem_base + T_DS + kk * 8,
+                        make_smem_desc_sw128(sK + st * L::TILE + kk * 2048, SLAB_BYTES, 1024), idesc_dq, (t > 0 || kk) ? 1u : 0u);
+          umma_commit(dq_done);
+          umma_commit(&k_empty[st]);
+        }
       }
     }
   } else {
     // ------------------------------------------------------------------ compute warpgroups
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
     const int hf = warp >> 2;                 // which 64 key columns of every tile this warpgroup owns
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
@@ -397,75 +403,80 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 8) {
-    if (lane == 0) {
-      mbar_arrive_expect_tx(kv_full, 2 * L::TILE);
-#pragma unroll
-      for (int s = 0; s < SLABS; ++s) {
-        tma_load_2d(smem + L::K_OFF + s * SLAB_BYTES, &tmK, kv_full, kvh * HD + s * 64, k0);
-        tma_load_2d(smem + L::V_OFF + s * SLAB_BYTES, &tmV, kv_full, kvh * HD + s * 64, k0);
-      }
-      bool ok = true;
-      for (int it = 0; it < n_iter && ok; ++it) {
-        const int g = it / n_i, i = i_lo + it % n_i, h = kvh * G + g;
-        const int st = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1;
-        ok = mbar_wait(&q_empty[st], ph ^ 1, abort_flag, p.status);
-        if (!ok) break;
-        mbar_arrive_expect_tx(&q_full[st], 2 * L::TILE);
+  // As in the dQ kernel: the third warpgroup hands registers to the two compute warpgroups.
+  if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+    if (warp == 8) {
+      if (lane == 0) {
+        mbar_arrive_expect_tx(kv_full, 2 * L::TILE);
 #pragma unroll
         for (int s = 0; s < SLABS; ++s) {
-          tma_load_2d(smem + L::Q_OFF + st * L::TILE + s * SLAB_BYTES, &tmQ, &q_full[st], h * HD + s * 64, i * BM);
-          tma_load_2d(smem + L::DO_OFF + st * L::TILE + s * SLAB_BYTES, &tmDO, &q_full[st], h * HD + s * 64, i * BM);
+          tma_load_2d(smem + L::K_OFF + s * SLAB_BYTES, &tmK, kv_full, kvh * HD + s * 64, k0);
+          tma_load_2d(smem + L::V_OFF + s * SLAB_BYTES, &tmV, kv_full, kvh * HD + s * 64, k0);
+        }
+        bool ok = true;
+        for (int it = 0; it < n_iter && ok; ++it) {
+          const int g = it / n_i, i = i_lo + it % n_i, h = kvh * G + g;
+          const int st = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          ok = mbar_wait(&q_empty[st], ph ^ 1, abort_flag, p.status);
+          if (!ok) break;
+          mbar_arrive_expect_tx(&q_full[st], 2 * L::TILE);
+#pragma unroll
+          for (int s = 0; s < SLABS; ++s) {
+            tma_load_2d(smem + L::Q_OFF + st * L::TILE + s * SLAB_BYTES, &tmQ, &q_full[st], h * HD + s * 64, i * BM);
+            tma_load_2d(smem + L::DO_OFF + st * L::TILE + s * SLAB_BYTES, &tmDO, &q_full[st], h * HD + s * 64, i * BM);
+          }
         }
       }
-    }
-  } else if (warp == 9) {
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(BN, HALF, 0, 0);
-      constexpr uint32_t idesc_o = make_idesc_bf16(BN, HD, 0, 1);
-      const uint32_t sK = smem_u32(smem + L::K_OFF), sV = smem_u32(smem + L::V_OFF);
-      const uint32_t sQ = smem_u32(smem + L::Q_OFF), sDO = smem_u32(smem + L::DO_OFF);
-      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status);
+    } else if (warp == 9) {
+      if (lane == 0) {
+        constexpr uint32_t idesc_s = make_idesc_bf16(BN, HALF, 0, 0);
+        constexpr uint32_t idesc_o = make_idesc_bf16(BN, HD, 0, 1);
+        const uint32_t sK = smem_u32(smem + L::K_OFF), sV = smem_u32(smem + L::V_OFF);
+        const uint32_t sQ = smem_u32(smem + L::Q_OFF), sDO = smem_u32(smem + L::DO_OFF);
+        bool ok = mbar_wait(kv_full, 0, abort_flag, p.status);
 
-      auto issue_sdp = [&](int s) -> bool {
-        const int hf = s & 1, it = s >> 1, st = it % STAGES;
-        if (hf == 0 && !mbar_wait(&q_full[st], (it / STAGES) & 1, abort_flag, p.status)) return false;
-        tc_fence_after();
+        auto issue_sdp = [&](int s) -> bool {
+          const int hf = s & 1, it = s >> 1, st = it % STAGES;
+          if (hf == 0 && !mbar_wait(&q_full[st], (it / STAGES) & 1, abort_flag, p.status)) return false;
+          tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {      // the two independent chains alternate (see the dQ kernel)
-          const uint32_t off = (kk / 4) * SLAB_BYTES + (kk % 4) * 32;
-          umma_f16_ss(tmem_base + hf * HALF, make_smem_desc_sw128(sK + off, 16, 1024),
-                      make_smem_desc_sw128(sQ + st * L::TILE + hf * HALF_BYTES + off, 16, 1024), idesc_s, kk ? 1u : 0u);
-          umma_f16_ss(tmem_base + BM + hf * HALF, make_smem_desc_sw128(sV + off, 16, 1024),
-                      make_smem_desc_sw128(sDO + st * L::TILE + hf * HALF_BYTES + off, 16, 1024), idesc_s, kk ? 1u : 0u);
-        }
-        umma_commit(&sdp_full[hf]);
-        return true;
-      };
+          for (int kk = 0; kk < HD / 16; ++kk) {      // the two independent chains alternate (see the dQ kernel)
+            const uint32_t off = (kk / 4) * SLAB_BYTES + (kk % 4) * 32;
+            umma_f16_ss(tmem_base + hf * HALF, make_smem_desc_sw128(sK + off, 16, 1024),
+                        make_smem_desc_sw128(sQ + st * L::TILE + hf * HALF_BYTES + off, 16, 1024), idesc_s, kk ? 1u : 0u);
+            umma_f16_ss(tmem_base + BM + hf * HALF, make_smem_desc_sw128(sV + off, 16, 1024),
+                        make_smem_desc_sw128(sDO + st * L::TILE + hf * HALF_BYTES + off, 16, 1024), idesc_s, kk ? 1u : 0u);
+          }
+          umma_commit(&sdp_full[hf]);
+          return true;
+        };
 
-      if (ok) ok = issue_sdp(0);
-      if (ok && n_steps > 1) ok = issue_sdp(1);
-      for (int s = 0; s < n_steps && ok; ++s) {
-        const int hf = s & 1, it = s >> 1, st = it % STAGES;
-        ok = mbar_wait(&pds_ready[hf], it & 1, abort_flag, p.status);
-        if (!ok) break;
-        tc_fence_after();
+        if (ok) ok = issue_sdp(0);
+        if (ok && n_steps > 1) ok = issue_sdp(1);
+        for (int s = 0; s < n_steps && ok; ++s) {
+          const int hf = s & 1, it = s >> 1, st = it % STAGES;
+          ok = mbar_wait(&pds_ready[hf], it & 1, abort_flag, p.status);
+          if (!ok) break;
+          tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < HALF / 16; ++kk) {
-          umma_f16_ts(tmem_base + 2 * BM, tmem_base + hf * HALF + kk * 8,          // dV += P^T dO
-                      make_smem_desc_sw128(sDO + st * L::TILE + hf * HALF_BYTES + kk * 2048, SLAB_BYTES, 1024), idesc_o,
-                      (s > 0 || kk) ? 1u : 0u);
-          umma_f16_ts(tmem_base + 3 * BM, tmem_base + BM + hf * HALF + kk * 8,     // dK += dS^T Q
-                      make_smem_desc_sw128(sQ + st * L::TILE + hf * HALF_BYTES + kk * 2048, SLAB_BYTES, 1024), idesc_o,
-                      (s > 0 || kk) ? 1u : 0u);
+          for (int kk = 0; kk < HALF / 16; ++kk) {
+            umma_f16_ts(tmem_base + 2 * BM, tmem_base + hf * HALF + kk * 8,          // dV += P^T dO
+                        make_smem_desc_sw128(sDO + st * L::TILE + hf * HALF_BYTES + kk * 2048, SLAB_BYTES, 1024), idesc_o,
+                        (s > 0 || kk) ? 1u : 0u);
+            umma_f16_ts(tmem_base + 3 * BM, tmem_base + BM + hf * HALF + kk * 8,     // dK += dS^T Q
+                        make_smem_desc_sw128(sQ + st * L::TILE + hf * HALF_BYTES + kk * 2048, SLAB_BYTES, 1024), idesc_o,
+                        (s > 0 || kk) ? 1u : 0u);
+          }
+          if (hf == 1) umma_commit(&q_empty[st]);
+          if (s + 2 < n_steps) ok = issue_sdp(s + 2);
         }
-        if (hf == 1) umma_commit(&q_empty[st]);
-        if (s + 2 < n_steps) ok = issue_sdp(s + 2);
+        umma_commit(final_bar);
       }
-      umma_commit(final_bar);
     }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
     const int hf = warp >> 2;
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;        // key row == TMEM lane

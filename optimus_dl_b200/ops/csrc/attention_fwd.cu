@@ -24,7 +24,7 @@ constexpr int BM = 128;       // query rows per tile
 constexpr int BN = 128;       // keys per tile
 constexpr int NQ = 2;         // query tiles per CTA
 constexpr int KV_STAGES = 2;
-constexpr int THREADS = 320;
+constexpr int THREADS = 384;      // 8 softmax warps + TMA warp + MMA warp + 2 warps that only give up registers
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 constexpr float RESCALE_THRESHOLD = 8.0f;   // in log2 units
@@ -116,101 +116,107 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
   for (int q = 0; q < NQ; ++q) if (tr[q].lo <= tr[q].hi) { jmin = min(jmin, tr[q].lo); jmax = max(jmax, tr[q].hi); }
 
-  if (warp == 8) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0 && jmax >= jmin) {
-      tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
-      mbar_arrive_expect_tx(q_full, NQ * L::TILE);
+  // The third warpgroup (two single-thread roles and two idle warps) hands registers to the two compute
+  // warpgroups, whose threads hold a whole row of a tile.
+  if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+    if (warp == 8) {
+      // ------------------------------------------------------------------ TMA producer
+      if (lane == 0 && jmax >= jmin) {
+        tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+        mbar_arrive_expect_tx(q_full, NQ * L::TILE);
 #pragma unroll
-      for (int q = 0; q < NQ; ++q)
+        for (int q = 0; q < NQ; ++q)
 #pragma unroll
-        for (int s = 0; s < SLABS; ++s)
-          tma_load_2d(smem + L::Q_OFF + q * L::TILE + s * SLAB_BYTES, &tmQ, q_full, h * HD + s * 64, q0 + q * BM);
-      bool ok = true;
-      for (int j = jmin; j <= jmax && ok; ++j) {
-        const int t = j - jmin, st = t % KV_STAGES;
-        const uint32_t ph = (t / KV_STAGES) & 1;
-        ok = mbar_wait(&k_empty[st], ph ^ 1, abort_flag, p.status);
-        if (!ok) break;
-        mbar_arrive_expect_tx(&k_full[st], L::TILE);
+          for (int s = 0; s < SLABS; ++s)
+            tma_load_2d(smem + L::Q_OFF + q * L::TILE + s * SLAB_BYTES, &tmQ, q_full, h * HD + s * 64, q0 + q * BM);
+        bool ok = true;
+        for (int j = jmin; j <= jmax && ok; ++j) {
+          const int t = j - jmin, st = t % KV_STAGES;
+          const uint32_t ph = (t / KV_STAGES) & 1;
+          ok = mbar_wait(&k_empty[st], ph ^ 1, abort_flag, p.status);
+          if (!ok) break;
+          mbar_arrive_expect_tx(&k_full[st], L::TILE);
 #pragma unroll
-        for (int s = 0; s < SLABS; ++s)
-          tma_load_2d(smem + L::K_OFF + st * L::TILE + s * SLAB_BYTES, &tmK, &k_full[st], kvh * HD + s * 64, j * BN);
-        ok = mbar_wait(&v_empty[st], ph ^ 1, abort_flag, p.status);
-        if (!ok) break;
-        mbar_arrive_expect_tx(&v_full[st], L::TILE);
+          for (int s = 0; s < SLABS; ++s)
+            tma_load_2d(smem + L::K_OFF + st * L::TILE + s * SLAB_BYTES, &tmK, &k_full[st], kvh * HD + s * 64, j * BN);
+          ok = mbar_wait(&v_empty[st], ph ^ 1, abort_flag, p.status);
+          if (!ok) break;
+          mbar_arrive_expect_tx(&v_full[st], L::TILE);
 #pragma unroll
-        for (int s = 0; s < SLABS; ++s)
-          tma_load_2d(smem + L::V_OFF + st * L::TILE + s * SLAB_BYTES, &tmV, &v_full[st], kvh * HD + s * 64, j * BN);
-      }
-    }
-  } else if (warp == 9) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0 && jmax >= jmin) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(BM, BN, 0, 0);
-      constexpr uint32_t idesc_pv = make_idesc_bf16(BM, HD, 0, 1);
-      const uint32_t sQ = smem_u32(smem + L::Q_OFF), sK = smem_u32(smem + L::K_OFF), sV = smem_u32(smem + L::V_OFF);
-      uint32_t p_phase[NQ] = {0, 0};
-      bool ok = mbar_wait(q_full, 0, abort_flag, p.status);
-
-      auto issue_s = [&](int q, int j) {
-        const int st = (j - jmin) % KV_STAGES;
-        const uint32_t a0 = sQ + q * L::TILE, b0 = sK + st * L::TILE;
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (kk / 4) * SLAB_BYTES + (kk % 4) * 32;
-          umma_f16_ss(tmem_base + q * BN, make_smem_desc_sw128(a0 + off, 16, 1024),
-                      make_smem_desc_sw128(b0 + off, 16, 1024), idesc_s, kk ? 1u : 0u);
+          for (int s = 0; s < SLABS; ++s)
+            tma_load_2d(smem + L::V_OFF + st * L::TILE + s * SLAB_BYTES, &tmV, &v_full[st], kvh * HD + s * 64, j * BN);
         }
-        umma_commit(&s_full[q]);
-      };
-      auto issue_pv = [&](int q, int j, bool accumulate) {
-        const int st = (j - jmin) % KV_STAGES;
-        const uint32_t b0 = sV + st * L::TILE;
-#pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk) {
-          // A: P in TMEM, 16 bf16 per 8 columns; B: V tile read MN-major (hd contiguous), 16 keys = 2048 bytes
-          umma_f16_ts(tmem_base + 2 * BN + q * BN, tmem_base + q * BN + kk * 8,
-                      make_smem_desc_sw128(b0 + kk * 2048, SLAB_BYTES, 1024), idesc_pv, (accumulate || kk) ? 1u : 0u);
-        }
-      };
-      auto active = [&](int q, int j) { return tr[q].lo <= tr[q].hi && j >= tr[q].lo && j <= tr[q].hi; };
-      auto kv_wait = [&](uint64_t* bar, int j) {
-        const int t = j - jmin;
-        return mbar_wait(&bar[t % KV_STAGES], (t / KV_STAGES) & 1, abort_flag, p.status);
-      };
-
-      if (ok) ok = kv_wait(k_full, jmin);
-      if (ok) {
-        tc_fence_after();
-#pragma unroll
-        for (int q = 0; q < NQ; ++q) if (active(q, jmin)) issue_s(q, jmin);
-        umma_commit(&k_empty[0]);
       }
-      for (int j = jmin; j <= jmax && ok; ++j) {
-        ok = kv_wait(v_full, j);
-        if (ok && j + 1 <= jmax) ok = kv_wait(k_full, j + 1);
-        if (!ok) break;
+    } else if (warp == 9) {
+      // ------------------------------------------------------------------ MMA issuer
+      if (lane == 0 && jmax >= jmin) {
+        constexpr uint32_t idesc_s = make_idesc_bf16(BM, BN, 0, 0);
+        constexpr uint32_t idesc_pv = make_idesc_bf16(BM, HD, 0, 1);
+        const uint32_t sQ = smem_u32(smem + L::Q_OFF), sK = smem_u32(smem + L::K_OFF), sV = smem_u32(smem + L::V_OFF);
+        uint32_t p_phase[NQ] = {0, 0};
+        bool ok = mbar_wait(q_full, 0, abort_flag, p.status);
+
+        auto issue_s = [&](int q, int j) {
+          const int st = (j - jmin) % KV_STAGES;
+          const uint32_t a0 = sQ + q * L::TILE, b0 = sK + st * L::TILE;
 #pragma unroll
-        for (int q = 0; q < NQ; ++q) {
-          if (active(q, j)) {
-            ok = mbar_wait(&p_ready[q], p_phase[q], abort_flag, p.status);
-            if (!ok) break;
-            p_phase[q] ^= 1;
-            tc_fence_after();
-            issue_pv(q, j, j > tr[q].lo);
+          for (int kk = 0; kk < HD / 16; ++kk) {
+            const uint32_t off = (kk / 4) * SLAB_BYTES + (kk % 4) * 32;
+            umma_f16_ss(tmem_base + q * BN, make_smem_desc_sw128(a0 + off, 16, 1024),
+                        make_smem_desc_sw128(b0 + off, 16, 1024), idesc_s, kk ? 1u : 0u);
           }
-          if (j + 1 <= jmax && active(q, j + 1)) issue_s(q, j + 1);
-        }
-        if (!ok) break;
-        umma_commit(&v_empty[(j - jmin) % KV_STAGES]);
-        if (j + 1 <= jmax) umma_commit(&k_empty[(j + 1 - jmin) % KV_STAGES]);
-      }
+          umma_commit(&s_full[q]);
+        };
+        auto issue_pv = [&](int q, int j, bool accumulate) {
+          const int st = (j - jmin) % KV_STAGES;
+          const uint32_t b0 = sV + st * L::TILE;
 #pragma unroll
-      for (int q = 0; q < NQ; ++q) if (tr[q].lo <= tr[q].hi) umma_commit(&o_final[q]);
+          for (int kk = 0; kk < BN / 16; ++kk) {
+            // A: P in TMEM, 16 bf16 per 8 columns; B: V tile read MN-major (hd contiguous), 16 keys = 2048 bytes
+            umma_f16_ts(tmem_base + 2 * BN + q * BN, tmem_base + q * BN + kk * 8,
+                        make_smem_desc_sw128(b0 + kk * 2048, SLAB_BYTES, 1024), idesc_pv, (accumulate || kk) ? 1u : 0u);
+          }
+        };
+        auto active = [&](int q, int j) { return tr[q].lo <= tr[q].hi && j >= tr[q].lo && j <= tr[q].hi; };
+        auto kv_wait = [&](uint64_t* bar, int j) {
+          const int t = j - jmin;
+          return mbar_wait(&bar[t % KV_STAGES], (t / KV_STAGES) & 1, abort_flag, p.status);
+        };
+
+        if (ok) ok = kv_wait(k_full, jmin);
+        if (ok) {
+          tc_fence_after();
+#pragma unroll
+          for (int q = 0; q < NQ; ++q) if (active(q, jmin)) issue_s(q, jmin);
+          umma_commit(&k_empty[0]);
+        }
+        for (int j = jmin; j <= jmax && ok; ++j) {
+          ok = kv_wait(v_full, j);
+          if (ok && j + 1 <= jmax) ok = kv_wait(k_full, j + 1);
+          if (!ok) break;
+#pragma unroll
+          for (int q = 0; q < NQ; ++q) {
+            if (active(q, j)) {
+              ok = mbar_wait(&p_ready[q], p_phase[q], abort_flag, p.status);
+              if (!ok) break;
+              p_phase[q] ^= 1;
+              tc_fence_after();
+              issue_pv(q, j, j > tr[q].lo);
+            }
+            if (j + 1 <= jmax && active(q, j + 1)) issue_s(q, j + 1);
+          }
+          if (!ok) break;
+          umma_commit(&v_empty[(j - jmin) % KV_STAGES]);
+          if (j + 1 <= jmax) umma_commit(&k_empty[(j + 1 - jmin) % KV_STAGES]);
+        }
+#pragma unroll
+        for (int q = 0; q < NQ; ++q) if (tr[q].lo <= tr[q].hi) umma_commit(&o_final[q]);
+      }
     }
   } else {
     // ------------------------------------------------------------------ softmax warpgroups
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
     const int q = warp >> 2;                 // query tile of this warpgroup
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;     // row inside the tile == TMEM lane
