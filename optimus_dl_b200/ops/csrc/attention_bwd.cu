@@ -28,6 +28,7 @@ constexpr int BM = 128;
 constexpr int BN = 128;
 constexpr int HALF = 64;
 constexpr int STAGES = 2;
+constexpr uint32_t DESC_HI = smem_desc_hi_sw128(1024);   // every operand tile: 128-byte swizzle, 8-row groups of 1024 bytes
 constexpr int THREADS = 384;      // 8 compute warps + TMA warp + MMA warp + 2 warps that only give up registers
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -203,13 +204,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
           if (!mbar_wait(&k_full[st], ph, abort_flag, p.status)) return false;
           if (!mbar_wait(&v_full[st], ph, abort_flag, p.status)) return false;
           tc_fence_after();
+          const uint32_t k_lo = smem_desc_lo(sK + st * L::TILE, 16), v_lo = smem_desc_lo(sV + st * L::TILE, 16);
+          const uint32_t do_lo = smem_desc_lo(sDO, 16);
 #pragma unroll
           for (int kk = 0; kk < HD / 16; ++kk) {
-            const uint32_t off = (kk / 4) * SLAB_BYTES + (kk % 4) * 32;
-            umma_f16_ts(tmem_base + T_S, tmem_base + T_QA + kk * 8,
-                        make_smem_desc_sw128(sK + st * L::TILE + off, 16, 1024), idesc_s, kk ? 1u : 0u);
-            umma_f16_ss(tmem_base + T_DP, make_smem_desc_sw128(sDO + off, 16, 1024),
-                        make_smem_desc_sw128(sV + st * L::TILE + off, 16, 1024), idesc_s, kk ? 1u : 0u);
+            const uint32_t off = ((kk / 4) * SLAB_BYTES + (kk % 4) * 32) >> 4;
+            umma_f16_ts_lh(tmem_base + T_S, tmem_base + T_QA + kk * 8, k_lo + off, DESC_HI, idesc_s, kk ? 1u : 0u);
+            umma_f16_ss_lh(tmem_base + T_DP, do_lo + off, v_lo + off, DESC_HI, idesc_s, kk ? 1u : 0u);
           }
           umma_commit(sdp_full);
           umma_commit(&v_empty[st]);
@@ -227,10 +228,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
           ok = mbar_wait(ds_ready, t & 1, abort_flag, p.status);
           if (!ok) break;
           tc_fence_after();
+          const uint32_t kt_lo = smem_desc_lo(sK + st * L::TILE, SLAB_BYTES);     // K read MN-major: 16 keys = 2048 bytes
 #pragma unroll
           for (int kk = 0; kk < BN / 16; ++kk)
-            umma_f16_ts(tmem_base + T_DQ, tmem_base + T_DS + kk * 8,
-                        make_smem_desc_sw128(sK + st * L::TILE + kk * 2048, SLAB_BYTES, 1024), idesc_dq, (t > 0 || kk) ? 1u : 0u);
+            umma_f16_ts_lh(tmem_base + T_DQ, tmem_base + T_DS + kk * 8, kt_lo + ((kk * 2048) >> 4), DESC_HI, idesc_dq,
+                           (t > 0 || kk) ? 1u : 0u);
           umma_commit(dq_done);
           umma_commit(&k_empty[st]);
         }
@@ -441,13 +443,14 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           const int hf = s & 1, it = s >> 1, st = it % STAGES;
           if (hf == 0 && !mbar_wait(&q_full[st], (it / STAGES) & 1, abort_flag, p.status)) return false;
           tc_fence_after();
+          const uint32_t k_lo = smem_desc_lo(sK, 16), v_lo = smem_desc_lo(sV, 16);
+          const uint32_t q_lo_d = smem_desc_lo(sQ + st * L::TILE + hf * HALF_BYTES, 16);
+          const uint32_t do_lo = smem_desc_lo(sDO + st * L::TILE + hf * HALF_BYTES, 16);
 #pragma unroll
           for (int kk = 0; kk < HD / 16; ++kk) {      // the two independent chains alternate (see the dQ kernel)
-            const uint32_t off = (kk / 4) * SLAB_BYTES + (kk % 4) * 32;
-            umma_f16_ss(tmem_base + hf * HALF, make_smem_desc_sw128(sK + off, 16, 1024),
-                        make_smem_desc_sw128(sQ + st * L::TILE + hf * HALF_BYTES + off, 16, 1024), idesc_s, kk ? 1u : 0u);
-            umma_f16_ss(tmem_base + BM + hf * HALF, make_smem_desc_sw128(sV + off, 16, 1024),
-                        make_smem_desc_sw128(sDO + st * L::TILE + hf * HALF_BYTES + off, 16, 1024), idesc_s, kk ? 1u : 0u);
+            const uint32_t off = ((kk / 4) * SLAB_BYTES + (kk % 4) * 32) >> 4;
+            umma_f16_ss_lh(tmem_base + hf * HALF, k_lo + off, q_lo_d + off, DESC_HI, idesc_s, kk ? 1u : 0u);
+            umma_f16_ss_lh(tmem_base + BM + hf * HALF, v_lo + off, do_lo + off, DESC_HI, idesc_s, kk ? 1u : 0u);
           }
           umma_commit(&sdp_full[hf]);
           return true;
@@ -460,14 +463,15 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           ok = mbar_wait(&pds_ready[hf], it & 1, abort_flag, p.status);
           if (!ok) break;
           tc_fence_after();
+          const uint32_t dot_lo = smem_desc_lo(sDO + st * L::TILE + hf * HALF_BYTES, SLAB_BYTES);   // MN-major reads
+          const uint32_t qt_lo = smem_desc_lo(sQ + st * L::TILE + hf * HALF_BYTES, SLAB_BYTES);
 #pragma unroll
           for (int kk = 0; kk < HALF / 16; ++kk) {
-            umma_f16_ts(tmem_base + 2 * BM, tmem_base + hf * HALF + kk * 8,          // dV += P^T dO
-                        make_smem_desc_sw128(sDO + st * L::TILE + hf * HALF_BYTES + kk * 2048, SLAB_BYTES, 1024), idesc_o,
-                        (s > 0 || kk) ? 1u : 0u);
-            umma_f16_ts(tmem_base + 3 * BM, tmem_base + BM + hf * HALF + kk * 8,     // dK += dS^T Q
-                        make_smem_desc_sw128(sQ + st * L::TILE + hf * HALF_BYTES + kk * 2048, SLAB_BYTES, 1024), idesc_o,
-                        (s > 0 || kk) ? 1u : 0u);
+            const uint32_t off = (kk * 2048) >> 4;
+            umma_f16_ts_lh(tmem_base + 2 * BM, tmem_base + hf * HALF + kk * 8, dot_lo + off, DESC_HI, idesc_o,         // dV += P^T dO
+                           (s > 0 || kk) ? 1u : 0u);
+            umma_f16_ts_lh(tmem_base + 3 * BM, tmem_base + BM + hf * HALF + kk * 8, qt_lo + off, DESC_HI, idesc_o,    // dK += dS^T Q
+                           (s > 0 || kk) ? 1u : 0u);
           }
           if (hf == 1) umma_commit(&q_empty[st]);
           if (s + 2 < n_steps) ok = issue_sdp(s + 2);

@@ -157,26 +157,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         uint32_t p_phase[NQ] = {0, 0};
         bool ok = mbar_wait(q_full, 0, abort_flag, p.status);
 
+        constexpr uint32_t DESC_HI = smem_desc_hi_sw128(1024);
         auto issue_s = [&](int q, int j) {
           const int st = (j - jmin) % KV_STAGES;
-          const uint32_t a0 = sQ + q * L::TILE, b0 = sK + st * L::TILE;
+          const uint32_t a_lo = smem_desc_lo(sQ + q * L::TILE, 16), b_lo = smem_desc_lo(sK + st * L::TILE, 16);
 #pragma unroll
           for (int kk = 0; kk < HD / 16; ++kk) {
-            const uint32_t off = (kk / 4) * SLAB_BYTES + (kk % 4) * 32;
-            umma_f16_ss(tmem_base + q * BN, make_smem_desc_sw128(a0 + off, 16, 1024),
-                        make_smem_desc_sw128(b0 + off, 16, 1024), idesc_s, kk ? 1u : 0u);
+            const uint32_t off = ((kk / 4) * SLAB_BYTES + (kk % 4) * 32) >> 4;
+            umma_f16_ss_lh(tmem_base + q * BN, a_lo + off, b_lo + off, DESC_HI, idesc_s, kk ? 1u : 0u);
           }
           umma_commit(&s_full[q]);
         };
         auto issue_pv = [&](int q, int j, bool accumulate) {
           const int st = (j - jmin) % KV_STAGES;
-          const uint32_t b0 = sV + st * L::TILE;
+          // A: P in TMEM, 16 bf16 per 8 columns; B: V tile read MN-major (hd contiguous), 16 keys = 2048 bytes
+          const uint32_t b_lo = smem_desc_lo(sV + st * L::TILE, SLAB_BYTES);
 #pragma unroll
-          for (int kk = 0; kk < BN / 16; ++kk) {
-            // A: P in TMEM, 16 bf16 per 8 columns; B: V tile read MN-major (hd contiguous), 16 keys = 2048 bytes
-            umma_f16_ts(tmem_base + 2 * BN + q * BN, tmem_base + q * BN + kk * 8,
-                        make_smem_desc_sw128(b0 + kk * 2048, SLAB_BYTES, 1024), idesc_pv, (accumulate || kk) ? 1u : 0u);
-          }
+          for (int kk = 0; kk < BN / 16; ++kk)
+            umma_f16_ts_lh(tmem_base + 2 * BN + q * BN, tmem_base + q * BN + kk * 8, b_lo + ((kk * 2048) >> 4), DESC_HI,
+                           idesc_pv, (accumulate || kk) ? 1u : 0u);
         };
         auto active = [&](int q, int j) { return tr[q].lo <= tr[q].hi && j >= tr[q].lo && j <= tr[q].hi; };
         auto kv_wait = [&](uint64_t* bar, int j) {
