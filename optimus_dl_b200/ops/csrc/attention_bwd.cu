@@ -190,7 +190,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       }
     } else if (warp == 9) {
       // ------------------------------------------------------------------ MMA issuer
-      if (lane == 0) {
+      {   // all 32 lanes run the issue loop; the MMA and commit forms elect one lane
         constexpr uint32_t idesc_s = make_idesc_bf16(BM, BN, 0, 0);
         constexpr uint32_t idesc_dq = make_idesc_bf16(BM, HD, 0, 1);
         const uint32_t sDO = smem_u32(smem + L::DO_OFF);
@@ -212,8 +212,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
             umma_f16_ts_lh(tmem_base + T_S, tmem_base + T_QA + kk * 8, k_lo + off, DESC_HI, idesc_s, kk ? 1u : 0u);
             umma_f16_ss_lh(tmem_base + T_DP, do_lo + off, v_lo + off, DESC_HI, idesc_s, kk ? 1u : 0u);
           }
-          umma_commit(sdp_full);
-          umma_commit(&v_empty[st]);
+          umma_commit_elect(sdp_full);
+          umma_commit_elect(&v_empty[st]);
           return true;
         };
 
@@ -233,8 +233,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
           for (int kk = 0; kk < BN / 16; ++kk)
             umma_f16_ts_lh(tmem_base + T_DQ, tmem_base + T_DS + kk * 8, kt_lo + ((kk * 2048) >> 4), DESC_HI, idesc_dq,
                            (t > 0 || kk) ? 1u : 0u);
-          umma_commit(dq_done);
-          umma_commit(&k_empty[st]);
+          umma_commit_elect(dq_done);
+          umma_commit_elect(&k_empty[st]);
         }
       }
     }
@@ -432,7 +432,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
       }
     } else if (warp == 9) {
-      if (lane == 0) {
+      {   // all 32 lanes run the issue loop; the MMA and commit forms elect one lane
         constexpr uint32_t idesc_s = make_idesc_bf16(BN, HALF, 0, 0);
         constexpr uint32_t idesc_o = make_idesc_bf16(BN, HD, 0, 1);
         const uint32_t sK = smem_u32(smem + L::K_OFF), sV = smem_u32(smem + L::V_OFF);
@@ -452,7 +452,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             umma_f16_ss_lh(tmem_base + hf * HALF, k_lo + off, q_lo_d + off, DESC_HI, idesc_s, kk ? 1u : 0u);
             umma_f16_ss_lh(tmem_base + BM + hf * HALF, v_lo + off, do_lo + off, DESC_HI, idesc_s, kk ? 1u : 0u);
           }
-          umma_commit(&sdp_full[hf]);
+          umma_commit_elect(&sdp_full[hf]);
           return true;
         };
 
@@ -473,10 +473,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             umma_f16_ts_lh(tmem_base + 3 * BM, tmem_base + BM + hf * HALF + kk * 8, qt_lo + off, DESC_HI, idesc_o,    // dK += dS^T Q
                            (s > 0 || kk) ? 1u : 0u);
           }
-          if (hf == 1) umma_commit(&q_empty[st]);
+          if (hf == 1) umma_commit_elect(&q_empty[st]);
           if (s + 2 < n_steps) ok = issue_sdp(s + 2);
         }
-        umma_commit(final_bar);
+        umma_commit_elect(final_bar);
       }
     }
   } else {

@@ -150,7 +150,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     } else if (warp == 9) {
       // ------------------------------------------------------------------ MMA issuer
-      if (lane == 0 && jmax >= jmin) {
+      if (jmax >= jmin) {   // all 32 lanes run the issue loop; the MMA and commit forms elect one lane
         constexpr uint32_t idesc_s = make_idesc_bf16(BM, BN, 0, 0);
         constexpr uint32_t idesc_pv = make_idesc_bf16(BM, HD, 0, 1);
         const uint32_t sQ = smem_u32(smem + L::Q_OFF), sK = smem_u32(smem + L::K_OFF), sV = smem_u32(smem + L::V_OFF);
@@ -166,7 +166,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             const uint32_t off = ((kk / 4) * SLAB_BYTES + (kk % 4) * 32) >> 4;
             umma_f16_ss_lh(tmem_base + q * BN, a_lo + off, b_lo + off, DESC_HI, idesc_s, kk ? 1u : 0u);
           }
-          umma_commit(&s_full[q]);
+          umma_commit_elect(&s_full[q]);
         };
         auto issue_pv = [&](int q, int j, bool accumulate) {
           const int st = (j - jmin) % KV_STAGES;
@@ -188,7 +188,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tc_fence_after();
 #pragma unroll
           for (int q = 0; q < NQ; ++q) if (active(q, jmin)) issue_s(q, jmin);
-          umma_commit(&k_empty[0]);
+          umma_commit_elect(&k_empty[0]);
         }
         for (int j = jmin; j <= jmax && ok; ++j) {
           ok = kv_wait(v_full, j);
@@ -206,11 +206,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             if (j + 1 <= jmax && active(q, j + 1)) issue_s(q, j + 1);
           }
           if (!ok) break;
-          umma_commit(&v_empty[(j - jmin) % KV_STAGES]);
-          if (j + 1 <= jmax) umma_commit(&k_empty[(j + 1 - jmin) % KV_STAGES]);
+          umma_commit_elect(&v_empty[(j - jmin) % KV_STAGES]);
+          if (j + 1 <= jmax) umma_commit_elect(&k_empty[(j + 1 - jmin) % KV_STAGES]);
         }
 #pragma unroll
-        for (int q = 0; q < NQ; ++q) if (tr[q].lo <= tr[q].hi) umma_commit(&o_final[q]);
+        for (int q = 0; q < NQ; ++q) if (tr[q].lo <= tr[q].hi) umma_commit_elect(&o_final[q]);
       }
     }
   } else {

@@ -215,14 +215,20 @@ __device__ __forceinline__ uint32_t smem_desc_lo(uint32_t smem_addr, uint32_t lb
 __host__ __device__ constexpr uint32_t smem_desc_hi_sw128(uint32_t sbo_bytes) {
   return ((sbo_bytes >> 4) & 0x3FFF) | (1u << 14) | (2u << 29);
 }
+// The *_lh forms and umma_commit_elect are for an issuing warp whose 32 lanes all run the issue loop (no branch on
+// the lane index around it): one lane is elected inside the instruction sequence itself.  The operands are then
+// the same in every lane and the compiler can keep them in the uniform datapath, which the MMA instruction reads;
+// with the loop inside `if (lane == 0)` every operand of every MMA took a transfer from the vector registers, and
+// 128-wide MMAs cost 80 to 90 cycles of issue instead of their 64 of execution.
 __device__ __forceinline__ void umma_f16_ss_lh(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc,
                                                uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "{\n\t.reg .pred p, e;\n\t.reg .b64 da, db;\n\t"
       "setp.ne.b32 p, %5, 0;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
       "mov.b64 da, {%1, %3};\n\t"
       "mov.b64 db, {%2, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}\n"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}\n"
       :
       : "r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
       : "memory");
@@ -230,12 +236,20 @@ __device__ __forceinline__ void umma_f16_ss_lh(uint32_t tmem_d, uint32_t a_lo, u
 __device__ __forceinline__ void umma_f16_ts_lh(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t hi, uint32_t idesc,
                                                uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "{\n\t.reg .pred p, e;\n\t.reg .b64 db;\n\t"
       "setp.ne.b32 p, %5, 0;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
       "mov.b64 db, {%2, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}\n"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}\n"
       :
       : "r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_elect(uint64_t* bar) {
+  asm volatile(
+      "{\n\t.reg .pred e;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}\n" ::"r"(smem_u32(bar))
       : "memory");
 }
 // Instruction descriptor for kind::f16 with bf16 inputs and fp32 accumulation.
