@@ -491,24 +491,37 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     float* vb = vec + warp * 3 * HALF;          // this warp's copy: -lse*log2e, -delta, lowest key
     int* lo_s = reinterpret_cast<int*>(vb + 2 * HALF);
     bool ok = true;
-    for (int it = 0; it < n_iter && ok; ++it) {
+    // Per-query vectors of a tile half (-lse*log2e, -delta, lowest key): fetched from global memory one iteration
+    // ahead into registers, so that their latency falls under the previous tile's arithmetic.
+    constexpr int VPL = HALF / 32;               // values per lane
+    float nx_l2[VPL], nx_dl[VPL];
+    int nx_lo[VPL];
+    auto fetch_vec = [&](int it) {
       const int g = it / n_i, i = i_lo + it % n_i, h = kvh * G + g;
-      const int q_first = i * BM + hf * HALF;
-      __syncwarp();
 #pragma unroll
-      for (int cc = lane; cc < HALF; cc += 32) {
-        const int qi = q_first + cc;
-        float l2 = 0.f, dl = 0.f;
-        int lo = 0x7fffffff;
+      for (int u = 0; u < VPL; ++u) {
+        const int qi = i * BM + hf * HALF + lane + 32 * u;
+        nx_l2[u] = 0.f; nx_dl[u] = 0.f; nx_lo[u] = 0x7fffffff;
         if (qi < p.N) {
-          l2 = p.lse[(long long)h * p.N + qi] * LOG2E;
-          dl = p.delta[(long long)h * p.N + qi];
-          lo = p.doc_start[qi];
-          if (p.window > 0) lo = max(lo, qi - p.window + 1);
+          nx_l2[u] = p.lse[(long long)h * p.N + qi];
+          nx_dl[u] = p.delta[(long long)h * p.N + qi];
+          nx_lo[u] = p.doc_start[qi];
+          if (p.window > 0) nx_lo[u] = max(nx_lo[u], qi - p.window + 1);
         }
-        vb[cc] = -l2; vb[HALF + cc] = -dl; lo_s[cc] = lo;
+      }
+    };
+    if (n_iter > 0) fetch_vec(0);
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int i = i_lo + it % n_i;
+      const int q_first = i * BM + hf * HALF;
+      __syncwarp();                              // the previous iteration's reads of vb are done
+#pragma unroll
+      for (int u = 0; u < VPL; ++u) {
+        const int cc = lane + 32 * u;
+        vb[cc] = -nx_l2[u] * LOG2E; vb[HALF + cc] = -nx_dl[u]; lo_s[cc] = nx_lo[u];
       }
       __syncwarp();
+      if (it + 1 < n_iter) fetch_vec(it + 1);
       ok = mbar_wait(&sdp_full[hf], it & 1, abort_flag, p.status);
       if (!ok) break;
       tc_fence_after();

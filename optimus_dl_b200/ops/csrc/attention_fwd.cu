@@ -274,17 +274,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const float m_use = (m_run == -INFINITY) ? 0.0f : m_run;
         const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-m_use, -m_use);
         float2 sum2 = make_float2(0.f, 0.f), sum2b = make_float2(0.f, 0.f);   // two chains of packed adds
-        uint32_t pk[BN / 2];
+        // P (bf16) goes back over S in four stores of 16 columns as it is produced: the thread holds all of S in
+        // registers by now, and at most 16 packed results at a time
 #pragma unroll
-        for (int c = 0; c < BN; c += 4) {
-          const float2 t0 = ffma2(make_float2(s[c], s[c + 1]), sc2, nm2);     // masked scores: -inf * scale = -inf
-          const float2 t1 = ffma2(make_float2(s[c + 2], s[c + 3]), sc2, nm2);
-          const float2 e0 = make_float2(exp2f(t0.x), exp2f(t0.y));
-          const float2 e1 = make_float2(exp2f(t1.x), exp2f(t1.y));
-          sum2 = fadd2(sum2, e0);
-          sum2b = fadd2(sum2b, e1);
-          pk[c / 2] = pack_bf16x2(e0.x, e0.y);
-          pk[c / 2 + 1] = pack_bf16x2(e1.x, e1.y);
+        for (int cc = 0; cc < BN; cc += 32) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int c = cc; c < cc + 32; c += 4) {
+            const float2 t0 = ffma2(make_float2(s[c], s[c + 1]), sc2, nm2);     // masked scores: -inf * scale = -inf
+            const float2 t1 = ffma2(make_float2(s[c + 2], s[c + 3]), sc2, nm2);
+            const float2 e0 = make_float2(exp2f(t0.x), exp2f(t0.y));
+            const float2 e1 = make_float2(exp2f(t1.x), exp2f(t1.y));
+            sum2 = fadd2(sum2, e0);
+            sum2b = fadd2(sum2b, e1);
+            pk[(c - cc) / 2] = pack_bf16x2(e0.x, e0.y);
+            pk[(c - cc) / 2 + 1] = pack_bf16x2(e1.x, e1.y);
+          }
+          tmem_st_32x16(t_s + cc / 2, pk);
         }
         sum2 = fadd2(sum2, sum2b);
         const float sum = sum2.x + sum2.y;
@@ -301,8 +307,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             tmem_st_32x16(t_o + c, o);
           }
         }
-#pragma unroll
-        for (int c = 0; c < BN / 2; c += 16) tmem_st_32x16(t_s + c, pk + c);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
