@@ -349,12 +349,20 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
 // barriers: while one warpgroup turns its half into P^T / dS^T the tensor cores run the other half's products.
 // (A form with 128-wide S^T / dP^T and nothing else in flight measured 16 % slower: the round trips between the
 // MMA warp and the compute warps, a few hundred cycles each, were then all on the critical path.)
+// The per-query terms of P^T = exp2(S^T scale log2e - lse log2e) and dS^T = P^T (dP^T - delta) enter through the
+// tensor core: one more K step appends to K and V a block of ones (three columns) and to Q and dO the three-way
+// bf16 split of -lse / scale and of -delta, so that the accumulators already hold S^T - lse / scale and
+// dP^T - delta.  The compute warps then need one multiply, one exponential and one multiply per element; reading
+// the two vectors from shared memory inside that loop had doubled its time (the reads share the issue path of the
+// exponentials).
 template <int HD>
 struct SmemKV {
   static constexpr int TILE = BM * HD * 2;
   static constexpr int K_OFF = 0, V_OFF = TILE, Q_OFF = 2 * TILE, DO_OFF = Q_OFF + STAGES * TILE;
-  static constexpr int VEC_OFF = DO_OFF + STAGES * TILE;            // [8 warps][3][HALF] 4-byte values
-  static constexpr int BAR_OFF = VEC_OFF + 8 * 3 * HALF * 4;
+  static constexpr int VEC_OFF = DO_OFF + STAGES * TILE;            // [8 warps][HALF] lowest attendable key per query
+  static constexpr int ONES_OFF = VEC_OFF + 8 * HALF * 4;           // [BN x 16] bf16, columns 0..2 = 1 (no swizzle)
+  static constexpr int AUG_OFF = ONES_OFF + BN * 32;                // [2][BM x 16] bf16: -lse/scale and -delta, split
+  static constexpr int BAR_OFF = AUG_OFF + 2 * BM * 32;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
@@ -376,9 +384,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint64_t* sdp_full = bars + 5;      // [2]
   uint64_t* pds_ready = bars + 7;     // [2]
   uint64_t* final_bar = bars + 9;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* aug_init = bars + 10;     // ones block and the first tile's vectors are in shared memory (8 warps)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* vec = reinterpret_cast<float*>(smem + L::VEC_OFF);
+  int* vec = reinterpret_cast<int*>(smem + L::VEC_OFF);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kvh = blockIdx.x % p.Hk;
@@ -396,6 +405,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     for (int s = 0; s < STAGES; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
     for (int s = 0; s < 2; ++s) { mbar_init(&sdp_full[s], 1); mbar_init(&pds_ready[s], 4); }
     mbar_init(final_bar, 1);
+    mbar_init(aug_init, 8);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -437,13 +447,19 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         constexpr uint32_t idesc_o = make_idesc_bf16(BN, HD, 0, 1);
         const uint32_t sK = smem_u32(smem + L::K_OFF), sV = smem_u32(smem + L::V_OFF);
         const uint32_t sQ = smem_u32(smem + L::Q_OFF), sDO = smem_u32(smem + L::DO_OFF);
+        const uint32_t sOnes = smem_u32(smem + L::ONES_OFF), sAug = smem_u32(smem + L::AUG_OFF);
+        constexpr uint32_t DESC_HI_AUG = smem_desc_hi_noswizzle(256);
         bool ok = mbar_wait(kv_full, 0, abort_flag, p.status);
+        if (ok) ok = mbar_wait(aug_init, 0, abort_flag, p.status);
 
         auto issue_sdp = [&](int s) -> bool {
           const int hf = s & 1, it = s >> 1, st = it % STAGES;
           if (hf == 0 && !mbar_wait(&q_full[st], (it / STAGES) & 1, abort_flag, p.status)) return false;
           tc_fence_after();
           const uint32_t k_lo = smem_desc_lo(sK, 16), v_lo = smem_desc_lo(sV, 16);
+          const uint32_t ones_lo = smem_desc_lo(sOnes, 128);
+          const uint32_t augl_lo = smem_desc_lo(sAug + hf * (HALF / 8) * 256, 128);
+          const uint32_t augd_lo = smem_desc_lo(sAug + BM * 32 + hf * (HALF / 8) * 256, 128);
           const uint32_t q_lo_d = smem_desc_lo(sQ + st * L::TILE + hf * HALF_BYTES, 16);
           const uint32_t do_lo = smem_desc_lo(sDO + st * L::TILE + hf * HALF_BYTES, 16);
 #pragma unroll
@@ -452,6 +468,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             umma_f16_ss_lh(tmem_base + hf * HALF, k_lo + off, q_lo_d + off, DESC_HI, idesc_s, kk ? 1u : 0u);
             umma_f16_ss_lh(tmem_base + BM + hf * HALF, v_lo + off, do_lo + off, DESC_HI, idesc_s, kk ? 1u : 0u);
           }
+          // the appended K step: ones x (-lse / scale) and ones x (-delta)
+          umma_f16_ss_lh(tmem_base + hf * HALF, ones_lo, augl_lo, DESC_HI_AUG, idesc_s, 1u);
+          umma_f16_ss_lh(tmem_base + BM + hf * HALF, ones_lo, augd_lo, DESC_HI_AUG, idesc_s, 1u);
           umma_commit_elect(&sdp_full[hf]);
           return true;
         };
@@ -488,37 +507,63 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const bool key_valid = kj < p.N;
     const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16);
     const uint32_t t_s = t_row + hf * HALF, t_dp = t_row + BM + hf * HALF;
-    float* vb = vec + warp * 3 * HALF;          // this warp's copy: -lse*log2e, -delta, lowest key
-    int* lo_s = reinterpret_cast<int*>(vb + 2 * HALF);
+    int* lo_s = vec + warp * HALF;              // this warp's copy of the lowest attendable key of each query
     bool ok = true;
-    // Per-query vectors of a tile half (-lse*log2e, -delta, lowest key): fetched from global memory one iteration
-    // ahead into registers, so that their latency falls under the previous tile's arithmetic.
+    // Per-query values of a tile half, fetched from global memory one iteration ahead into registers.  Every lane
+    // keeps the lowest attendable key of two queries (masked tiles); in addition thread (quarter, lane) owns ONE
+    // row of the appended operand block: quarters 0 / 1 write -lse / scale of queries lane / 32 + lane, quarters
+    // 2 / 3 write -delta of the same queries.
     constexpr int VPL = HALF / 32;               // values per lane
-    float nx_l2[VPL], nx_dl[VPL];
     int nx_lo[VPL];
+    float nx_val;
+    const int aug_q = (quarter & 1) * 32 + lane;                     // query inside the half
+    const int aug_row = hf * HALF + aug_q;                           // row of the appended block
+    uint8_t* aug_dst = smem + L::AUG_OFF + (quarter >> 1) * (BM * 32) + (aug_row / 8) * 256 + (aug_row % 8) * 16;
+    const float inv_scale = 1.0f / p.scale;
     auto fetch_vec = [&](int it) {
       const int g = it / n_i, i = i_lo + it % n_i, h = kvh * G + g;
 #pragma unroll
       for (int u = 0; u < VPL; ++u) {
         const int qi = i * BM + hf * HALF + lane + 32 * u;
-        nx_l2[u] = 0.f; nx_dl[u] = 0.f; nx_lo[u] = 0x7fffffff;
-        if (qi < p.N) {
-          nx_l2[u] = p.lse[(long long)h * p.N + qi];
-          nx_dl[u] = p.delta[(long long)h * p.N + qi];
-          nx_lo[u] = p.doc_start[qi];
-          if (p.window > 0) nx_lo[u] = max(nx_lo[u], qi - p.window + 1);
-        }
+        nx_lo[u] = 0x7fffffff;
+        if (qi < p.N) nx_lo[u] = p.doc_start[qi];
       }
+      const int qa = i * BM + hf * HALF + aug_q;
+      nx_val = 0.f;       // raw value: nothing may depend on the load before write_aug(), a whole tile later
+      if (qa < p.N) nx_val = (quarter < 2) ? p.lse[(long long)h * p.N + qa] : p.delta[(long long)h * p.N + qa];
     };
-    if (n_iter > 0) fetch_vec(0);
+    auto write_aug = [&]() {                     // three-way bf16 split: the products with 1.0 add up in fp32
+      const float x = (quarter < 2) ? -nx_val * inv_scale : -nx_val;
+      const __nv_bfloat16 b0 = __float2bfloat16(x);
+      const float r1 = x - __bfloat162float(b0);
+      const __nv_bfloat16 b1 = __float2bfloat16(r1);
+      const __nv_bfloat16 b2 = __float2bfloat16(r1 - __bfloat162float(b1));
+      const uint32_t w0 = (uint32_t)__bfloat16_as_ushort(b0) | ((uint32_t)__bfloat16_as_ushort(b1) << 16);
+      *reinterpret_cast<uint4*>(aug_dst) = make_uint4(w0, (uint32_t)__bfloat16_as_ushort(b2), 0u, 0u);
+    };
+    {
+      // once per CTA: the ones block (row = TMEM lane of this thread's quarter / lane, written by warpgroup 0), the
+      // zero upper halves of the appended rows, and the first tile's vectors
+      if (hf == 0) {
+        uint8_t* o = smem + L::ONES_OFF + (row / 8) * 256 + (row % 8) * 16;
+        *reinterpret_cast<uint4*>(o) = make_uint4(0x3f803f80u, 0x00003f80u, 0u, 0u);
+        *reinterpret_cast<uint4*>(o + 128) = make_uint4(0u, 0u, 0u, 0u);
+      }
+      *reinterpret_cast<uint4*>(aug_dst + 128) = make_uint4(0u, 0u, 0u, 0u);
+      if (n_iter > 0) { fetch_vec(0); write_aug(); }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(aug_init);
+    }
     for (int it = 0; it < n_iter && ok; ++it) {
       const int i = i_lo + it % n_i;
       const int q_first = i * BM + hf * HALF;
-      __syncwarp();                              // the previous iteration's reads of vb are done
+      __syncwarp();                              // the previous iteration's reads of lo_s are done
 #pragma unroll
       for (int u = 0; u < VPL; ++u) {
-        const int cc = lane + 32 * u;
-        vb[cc] = -nx_l2[u] * LOG2E; vb[HALF + cc] = -nx_dl[u]; lo_s[cc] = nx_lo[u];
+        int lo = nx_lo[u];
+        if (p.window > 0 && lo != 0x7fffffff) lo = max(lo, q_first + lane + 32 * u - p.window + 1);
+        lo_s[lane + 32 * u] = lo;
       }
       __syncwarp();
       if (it + 1 < n_iter) fetch_vec(it + 1);
@@ -532,41 +577,37 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tmem_ld_32x32(t_dp + 32, dp + 32);
       tmem_ld_wait();
       const bool need_mask = (q_first < k0 + BN - 1) || (lo_s[HALF - 1] > k0) || (k0 + BN > p.N);
+      // the accumulators hold S^T - lse / scale and dP^T - delta
       if (need_mask) {
 #pragma unroll
         for (int e = 0; e < HALF; e += 4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(vb + e);
-          const float4 d4 = *reinterpret_cast<const float4*>(vb + HALF + e);
           const int4 lo4 = *reinterpret_cast<const int4*>(lo_s + e);
-          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv4[4] = {d4.x, d4.y, d4.z, d4.w};
           const int lov[4] = {lo4.x, lo4.y, lo4.z, lo4.w};
           float pr[4], ds[4];
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int qi = q_first + e + u;
             const bool valid = key_valid && kj <= qi && kj >= lov[u];
-            pr[u] = valid ? exp2f(fmaf(__uint_as_float(s[e + u]), p.scale_log2, lv[u])) : 0.f;
-            ds[u] = pr[u] * (__uint_as_float(dp[e + u]) + dv4[u]);
+            pr[u] = valid ? exp2f(__uint_as_float(s[e + u]) * p.scale_log2) : 0.f;
+            ds[u] = pr[u] * __uint_as_float(dp[e + u]);
           }
           pk[e / 2] = pack_bf16x2(pr[0], pr[1]); pk[e / 2 + 1] = pack_bf16x2(pr[2], pr[3]);
           dk_[e / 2] = pack_bf16x2(ds[0], ds[1]); dk_[e / 2 + 1] = pack_bf16x2(ds[2], ds[3]);
         }
       } else {
-        // vb holds -lse*log2e and -delta of the 64 query columns, so that both enter packed add / fma forms directly
         const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
 #pragma unroll
-        for (int e = 0; e < HALF; e += 4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(vb + e);
-          const float4 d4 = *reinterpret_cast<const float4*>(vb + HALF + e);
-          const float2 t0 = ffma2(u2f2(s[e], s[e + 1]), sc2, make_float2(l4.x, l4.y));
-          const float2 t1 = ffma2(u2f2(s[e + 2], s[e + 3]), sc2, make_float2(l4.z, l4.w));
-          const float2 p0 = make_float2(exp2f(t0.x), exp2f(t0.y)), p1 = make_float2(exp2f(t1.x), exp2f(t1.y));
-          const float2 r0 = fmul2(p0, fadd2(u2f2(dp[e], dp[e + 1]), make_float2(d4.x, d4.y)));
-          const float2 r1 = fmul2(p1, fadd2(u2f2(dp[e + 2], dp[e + 3]), make_float2(d4.z, d4.w)));
-          pk[e / 2] = pack_bf16x2(p0.x, p0.y); pk[e / 2 + 1] = pack_bf16x2(p1.x, p1.y);
-          dk_[e / 2] = pack_bf16x2(r0.x, r0.y); dk_[e / 2 + 1] = pack_bf16x2(r1.x, r1.y);
+        for (int e = 0; e < HALF; e += 2) {
+          const float2 t = fmul2(u2f2(s[e], s[e + 1]), sc2);
+          const float2 pr = make_float2(exp2f(t.x), exp2f(t.y));
+          const float2 r = fmul2(pr, u2f2(dp[e], dp[e + 1]));
+          pk[e / 2] = pack_bf16x2(pr.x, pr.y);
+          dk_[e / 2] = pack_bf16x2(r.x, r.y);
         }
       }
+      // the next tile's vectors for this half: the products that read the current ones have completed (sdp_full),
+      // and the arrival below orders these writes in front of the next S^T / dP^T of this half
+      if (it + 1 < n_iter) { write_aug(); fence_proxy_async(); }
       tmem_st_32x16(t_s, pk);
       tmem_st_32x16(t_s + 16, pk + 16);
       tmem_st_32x16(t_dp, dk_);

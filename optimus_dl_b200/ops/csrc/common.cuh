@@ -220,6 +220,11 @@ __host__ __device__ constexpr uint32_t smem_desc_hi_sw128(uint32_t sbo_bytes) {
 // the same in every lane and the compiler can keep them in the uniform datapath, which the MMA instruction reads;
 // with the loop inside `if (lane == 0)` every operand of every MMA took a transfer from the vector registers, and
 // 128-wide MMAs cost 80 to 90 cycles of issue instead of their 64 of execution.
+// High word for an operand tile WITHOUT swizzle: 8-row x 16-byte core matrices of 128 contiguous bytes; element
+// (r, k) of a K-major 16-bit tile sits at (r / 8) * sbo + (k / 8) * lbo + (r % 8) * 16 + (k % 8) * 2.
+__host__ __device__ constexpr uint32_t smem_desc_hi_noswizzle(uint32_t sbo_bytes) {
+  return ((sbo_bytes >> 4) & 0x3FFF) | (1u << 14);
+}
 __device__ __forceinline__ void umma_f16_ss_lh(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc,
                                                uint32_t accumulate) {
   asm volatile(
