@@ -162,7 +162,7 @@ def bench_gemm_fp8(t: Timer, sizes) -> None:
               quant_with_transpose_ms=round(ms_t, 4), quant_with_transpose_gbs=round(M * K * 4 / ms_t / 1e6, 1))
 
 
-def bench_attention(t: Timer, cases) -> None:
+def bench_attention(t: Timer, cases, library_rows: bool = True) -> None:
     from . import attention as A
 
     for T, Hq, Hk, hd in cases:
@@ -181,6 +181,8 @@ def bench_attention(t: Timer, cases) -> None:
 
         ms_fb = t(fb)
         _emit("attention_fwd_bwd", dict(T=T, Hq=Hq, Hk=Hk, hd=hd), ms_fb, flops=flops_f * 3.5)
+        if not library_rows:
+            continue
         # the kernels the reference reaches for the same problem (optimus_dl/modules/model/blocks/attention.py:
         # flash_attn_varlen_func at 390-401, scaled_dot_product_attention at 511-520), same harness
         q = torch.randn(1, T, Hq, hd, device="cuda").bfloat16().requires_grad_(True)
@@ -517,6 +519,8 @@ def main() -> None:
     ap.add_argument("--small", action="store_true", help="one small case (for profiler captures)")
     ap.add_argument("--mid", action="store_true", help="attention: one case that fills every SM but holds little memory "
                                                         "(T 4096, 32 / 8 heads), for profiler captures")
+    ap.add_argument("--no-library-rows", action="store_true", help="attention: skip the flash-attn / SDPA comparison rows "
+                                                                    "(profiler captures of this package's kernels only)")
     args = ap.parse_args()
     if "LOCAL_RANK" in os.environ:
         torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
@@ -531,7 +535,7 @@ def main() -> None:
                                                                    (8192, 28672, 4096)])
     elif args.op == "attention":
         bench_attention(t, [(4096, 32, 8, 128)] if args.mid else [(4096, 8, 2, 128)] if args.small
-                        else [(8192, 32, 8, 128), (16384, 40, 8, 128)])
+                        else [(8192, 32, 8, 128), (16384, 40, 8, 128)], library_rows=not args.no_library_rows)
     elif args.op == "decode":
         bench_decode(t, [(64, 768, 16, 8, 128)] if args.small else [(64, 768, 16, 8, 128), (512, 768, 16, 8, 128),
                                                                      (1, 8192, 32, 8, 128), (8, 4096, 32, 8, 128)])
