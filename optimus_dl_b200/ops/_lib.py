@@ -196,6 +196,7 @@ def _declare(l: ctypes.CDLL) -> None:
     sig("ob_gemm_skinny_splits", [I, I])
     sig("ob_gemm2_bf16", [P, L, I, P, L, I, P, L, I, I, I, I, I, P, I, F, I, P, P])
     sig("ob_gemm2_swiglu_bf16", [P, L, P, P, L, P, P, P, L, I, I, I, P, P])
+    sig("ob_gemm2_swiglu_bwd_bf16", [P, L, P, L, P, P, L, I, I, I, P, P])
     sig("ob_rmsnorm_fwd", [P, P, P, P, P, P, I, I, F, P])
     sig("ob_rmsnorm_fwd_fp8", [P, P, P, P, P, P, P, P, L, I, I, F, P])
     sig("ob_rmsnorm_bwd", [P, P, P, P, P, P, P, P, P, I, I, I, P])

@@ -13,7 +13,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   gemm2_cta<A_MN, B_MN, SWIGLU>(&tmA, &tmB, &tmB2, p, blockIdx.x >> 1, gridDim.x >> 1, smem_raw);
 }
 
-static int g_max_pairs[4][2] = {{0, 0}, {0, 0}, {0, 0}, {0, 0}};
+static int g_max_pairs[4][3] = {};
 
 template <int A_MN, int B_MN, int SWIGLU>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const Params& p, int max_ctas,
@@ -37,7 +37,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMa
     if (n <= 0) return -4;
     max_pairs = n < sms / 2 ? n : sms / 2;
   }
-  constexpr int bn = SWIGLU ? TN / 2 : TN;
+  constexpr int bn = SWIGLU == 1 ? TN / 2 : TN;
   const int tiles = ((p.M + TM - 1) / TM) * ((p.N + bn - 1) / bn);
   int pairs = tiles < max_pairs ? tiles : max_pairs;
   if (max_ctas > 1 && pairs > max_ctas / 2) pairs = max_ctas / 2;
@@ -89,4 +89,21 @@ extern "C" int ob_gemm2_swiglu_bf16(const void* X, long long ldx, const void* W1
   p.M = M; p.N = N; p.K = K; p.C = H; p.ldc = ldh; p.G = G; p.U = U; p.alpha = 1.0f; p.status = status;
   p.flag_rows = 1; p.a_flag_rows = 1;
   return gemm2::launch<0, 0, 1>(ta, tb1, tb2, p, 0, stream);
+}
+
+// Input gradient of the SwiGLU feed-forward's down projection fused with the activation's backward:
+// dh = DY[M, K] WC[K, N] (WC read MN-major) never reaches memory; the epilogue turns it, with g and u read at the
+// output coordinates, into dg and du written over g and u (row stride ldg).
+extern "C" int ob_gemm2_swiglu_bwd_bf16(const void* DY, long long lddy, const void* WC, long long ldw, void* G, void* U,
+                                        long long ldg, int M, int N, int K, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d(&ta, DY, M, K, lddy, 128, gemm2::BK, 2);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tb, WC, K, N, ldw, gemm2::BK, 64, 2);
+  if (rc) return rc;
+  gemm::Params p{};
+  p.M = M; p.N = N; p.K = K; p.C = nullptr; p.ldc = ldg; p.G = G; p.U = U; p.act = gemm::kActSwigluBwd; p.alpha = 1.0f;
+  p.status = status; p.flag_rows = 1; p.a_flag_rows = 1;
+  return gemm2::launch<0, 1, 2>(ta, tb, tb, p, 0, stream);
 }

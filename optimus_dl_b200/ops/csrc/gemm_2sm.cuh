@@ -109,7 +109,8 @@ __device__ __forceinline__ void gemm2_cta(const CUtensorMap* tmA_, const CUtenso
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
-  constexpr int bn = SWIGLU ? TN / 2 : TN;             // output columns per tile
+  constexpr bool DUAL = SWIGLU == 1;                   // 1: dual-B SwiGLU forward, 2: SwiGLU-backward epilogue
+  constexpr int bn = DUAL ? TN / 2 : TN;               // output columns per tile
   const int tiles_m = (p.M + TM - 1) / TM;
   const int tiles_n = (p.N + bn - 1) / bn;
   const int num_tiles = tiles_m * tiles_n;
@@ -136,15 +137,15 @@ __device__ __forceinline__ void gemm2_cta(const CUtensorMap* tmA_, const CUtenso
     if (lane == 0) {
       tma_prefetch_desc(&tmA);
       tma_prefetch_desc(&tmB);
-      if (SWIGLU) tma_prefetch_desc(&tmB2);
+      if (DUAL) tma_prefetch_desc(&tmB2);
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
         const TileCoord tc = gemm::tile_coord(tile, tiles_m, tiles_n, p);
         const int m0 = tc.m * TM + (int)rank * 128;          // this CTA's rows of A
         const int n0 = tc.n * bn;
-        const int nb = SWIGLU ? n0 : n0 + (int)rank * 128;   // this CTA's rows of B
-        const CUtensorMap* tb = (SWIGLU && rank == 1) ? &tmB2 : &tmB;
+        const int nb = DUAL ? n0 : n0 + (int)rank * 128;     // this CTA's rows of B
+        const CUtensorMap* tb = (DUAL && rank == 1) ? &tmB2 : &tmB;
         if (p.b_flags) {
           // rows of B that another part of this launch is still landing in local memory (fused all-gather)
           const int f0 = nb / p.flag_rows;
@@ -165,7 +166,7 @@ __device__ __forceinline__ void gemm2_cta(const CUtensorMap* tmA_, const CUtenso
           } else {
             tma_load_2d_pair(sA, &tmA, &full_bar[stage], k0, m0);
           }
-          if (B_MN && !SWIGLU) {
+          if (B_MN && !DUAL) {
             tma_load_2d_pair(sB, tb, &full_bar[stage], nb, k0);
             tma_load_2d_pair(sB + 8192, tb, &full_bar[stage], nb + 64, k0);
           } else {
@@ -183,7 +184,7 @@ __device__ __forceinline__ void gemm2_cta(const CUtensorMap* tmA_, const CUtenso
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (leader && lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(TM, TN, A_MN, B_MN && !SWIGLU);
+      constexpr uint32_t idesc = make_idesc_bf16(TM, TN, A_MN, B_MN && !DUAL);
       int stage = 0; uint32_t phase = 0;
       int acc = 0; uint32_t acc_phase = 0;
       bool ok = true;
@@ -202,7 +203,7 @@ __device__ __forceinline__ void gemm2_cta(const CUtensorMap* tmA_, const CUtenso
           for (int kk = 0; kk < BK / UMMA_K; ++kk) {
             const uint64_t da = A_MN ? make_smem_desc_sw128(sA + kk * 2048, 8192, 1024)
                                      : make_smem_desc_sw128(sA + kk * 32, 16, 1024);
-            const uint64_t db = (B_MN && !SWIGLU) ? make_smem_desc_sw128(sB + kk * 2048, 8192, 1024)
+            const uint64_t db = (B_MN && !DUAL) ? make_smem_desc_sw128(sB + kk * 2048, 8192, 1024)
                                                   : make_smem_desc_sw128(sB + kk * 32, 16, 1024);
             umma2_f16_ss(d_tmem, da, db, idesc, (kt | kk) ? 1u : 0u);
           }
@@ -225,11 +226,32 @@ __device__ __forceinline__ void gemm2_cta(const CUtensorMap* tmA_, const CUtenso
     const int quarter = warp & 3;
     int acc = 0; uint32_t acc_phase = 0;
     bool ok = true;
-    const bool vec_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+    const bool vec_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(SWIGLU == 2 ? p.G : p.C) & 15) == 0) &&
+                        (SWIGLU != 2 || (reinterpret_cast<uintptr_t>(p.U) & 15) == 0);
+    // SwiGLU-backward epilogue: g and u of a tile are read by thread = row in 64-byte pieces, which DRAM serves
+    // badly (one short burst per 28 KB-strided row).  Each thread therefore asks L2 for the whole 512-byte extent
+    // of its row one tile ahead, while the tensor cores still work on that tile; the epilogue's reads then hit L2.
+    auto prefetch_gu = [&](int t) {
+      if (SWIGLU != 2 || t >= num_tiles) return;
+      const TileCoord pc = gemm::tile_coord(t, tiles_m, tiles_n, p);
+      const int prow = pc.m * TM + (int)rank * 128 + quarter * 32 + lane, pn0 = pc.n * bn;
+      if (prow >= p.M) return;
+      const __nv_bfloat16* pg = reinterpret_cast<const __nv_bfloat16*>(p.G) + (long long)prow * p.ldc + pn0;
+      const __nv_bfloat16* pu = reinterpret_cast<const __nv_bfloat16*>(p.U) + (long long)prow * p.ldc + pn0;
+#pragma unroll
+      for (int c = 0; c < TN; c += 64) {
+        if (pn0 + c < p.N) {
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(pg + c));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(pu + c));
+        }
+      }
+    };
+    prefetch_gu(pair);
     for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
       const TileCoord tc = gemm::tile_coord(tile, tiles_m, tiles_n, p);
       const int m0 = tc.m * TM + (int)rank * 128;
       const int n0 = tc.n * bn;
+      prefetch_gu(tile + n_pairs);
       ok = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status);
       if (!ok) break;
       tc_fence_after();

@@ -37,7 +37,7 @@ constexpr int RS_STAGE_BYTES = 4 * 32 * RS_ROW_ELEMS * 2;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + RS_STAGE_BYTES;
 constexpr int GROUP_M = 16;
 
-enum Act : int { kActNone = 0, kActGelu = 1, kActRelu2 = 2, kActSilu = 3 };
+enum Act : int { kActNone = 0, kActGelu = 1, kActRelu2 = 2, kActSilu = 3, kActSwigluBwd = 4 };
 
 struct Params {
   int M, N, K;
@@ -50,6 +50,9 @@ struct Params {
   float alpha;           // scale applied to the accumulator
   // SwiGLU mode (template flag): B tile = 128 rows of B (gate) followed by 128 rows
   // of B2 (up); outputs h = silu(g)*u to C (width N) and, when set, g and u.
+  // With act == kActSwigluBwd (plain mode) the product is dh, the gradient of h = silu(g) * u: the epilogue reads
+  // g and u at the output coordinates from G and U (row stride ldc), overwrites them with dg and du, and writes
+  // nothing to C.
   void* G;
   void* U;
   // Optional readiness flags, one per group of `flag_rows` rows of the B operand
@@ -145,6 +148,87 @@ __device__ __forceinline__ float apply_act(float x, int act) {
   }
 }
 
+// Epilogue of the fused "input gradient of the down projection + SwiGLU backward" product: the accumulator tile is
+// dh; g and u are read at the output coordinates (thread = row, 32 columns = 64 bytes per step, the next step's
+// reads in flight under the current step's arithmetic) and overwritten with
+//   dg = dh u s(g) (1 + g (1 - s(g))),  du = dh g s(g),   s = logistic function.
+// dh is rounded to bf16 first, as the two-kernel path (GEMM, then the elementwise kernel) does.
+__device__ __forceinline__ void epilogue_swiglu_bwd(const Params& p, int m0, int n0, uint32_t t_row, int warp, int lane,
+                                                    bool vec_ok) {
+  const int row = m0 + (warp & 3) * 32 + lane;
+  const bool row_ok = row < p.M;
+  __nv_bfloat16* grow = reinterpret_cast<__nv_bfloat16*>(p.G) + (long long)(row_ok ? row : 0) * p.ldc + n0;
+  __nv_bfloat16* urow = reinterpret_cast<__nv_bfloat16*>(p.U) + (long long)(row_ok ? row : 0) * p.ldc + n0;
+  auto grads = [](float d, float g, float u, float& dg, float& du) {
+    d = __bfloat162float(__float2bfloat16(d));
+    const float sg = 1.0f / (1.0f + __expf(-g));
+    dg = d * u * sg * (1.0f + g * (1.0f - sg));
+    du = d * g * sg;
+  };
+  const bool fast = vec_ok && n0 + BN <= p.N;      // warp-uniform
+  if (fast) {
+    // full tile: the reads of g and u run DEPTH steps ahead of the arithmetic (L2 latency under the main loop's
+    // operand traffic is a few thousand cycles, one step of arithmetic a few hundred)
+    constexpr int DEPTH = 3, STEPS = BN / 32;
+    uint4 gq[DEPTH][4], uq[DEPTH][4];
+    auto fetch = [&](int step, int slot) {
+      if (row_ok) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          gq[slot][q] = *reinterpret_cast<const uint4*>(grow + step * 32 + 8 * q);
+          uq[slot][q] = *reinterpret_cast<const uint4*>(urow + step * 32 + 8 * q);
+        }
+      }
+    };
+#pragma unroll
+    for (int s0 = 0; s0 < DEPTH; ++s0) fetch(s0, s0);
+#pragma unroll
+    for (int st = 0; st < STEPS; ++st) {
+      const int slot = st % DEPTH, c = st * 32;
+      uint32_t r[32];
+      tmem_ld_32x32(t_row + c, r);
+      tmem_ld_wait();
+      if (row_ok) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t gw[4] = {gq[slot][q].x, gq[slot][q].y, gq[slot][q].z, gq[slot][q].w};
+          const uint32_t uw[4] = {uq[slot][q].x, uq[slot][q].y, uq[slot][q].z, uq[slot][q].w};
+          uint32_t og[4], ou[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 g2 = unpack_bf16x2(gw[j]), u2 = unpack_bf16x2(uw[j]);
+            float dg0, du0, dg1, du1;
+            grads(__uint_as_float(r[8 * q + 2 * j]), g2.x, u2.x, dg0, du0);
+            grads(__uint_as_float(r[8 * q + 2 * j + 1]), g2.y, u2.y, dg1, du1);
+            og[j] = pack_bf16x2(dg0, dg1);
+            ou[j] = pack_bf16x2(du0, du1);
+          }
+          *reinterpret_cast<uint4*>(grow + c + 8 * q) = make_uint4(og[0], og[1], og[2], og[3]);
+          *reinterpret_cast<uint4*>(urow + c + 8 * q) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+        }
+      }
+      if (st + DEPTH < STEPS) fetch(st + DEPTH, slot);
+    }
+    return;
+  }
+#pragma unroll 1
+  for (int c = 0; c < BN; c += 32) {
+    if (n0 + c >= p.N) break;   // warp-uniform
+    uint32_t r[32];
+    tmem_ld_32x32(t_row + c, r);
+    tmem_ld_wait();
+    if (!row_ok) continue;
+    for (int j = 0; j < 32; ++j) {
+      if (n0 + c + j < p.N) {
+        float dg, du;
+        grads(__uint_as_float(r[j]), __bfloat162float(grow[c + j]), __bfloat162float(urow[c + j]), dg, du);
+        grow[c + j] = __float2bfloat16(dg);
+        urow[c + j] = __float2bfloat16(du);
+      }
+    }
+  }
+}
+
 // Epilogue of one 128 x 256 accumulator tile, executed by one epilogue warp for its 32 TMEM lanes:
 // `t_row` is the TMEM address of the warp's first lane at the tile's first column, (m0, n0) the tile origin in C.
 template <int SWIGLU>
@@ -152,7 +236,7 @@ __device__ __forceinline__ void epilogue_tile(const Params& p, int m0, int n0, u
                                               bool vec_ok, __nv_bfloat16* rs_stage_base) {
   const int quarter = warp & 3;
   const int row = m0 + quarter * 32 + lane;
-  if (SWIGLU) {
+  if (SWIGLU == 1) {
     // columns [0,128) hold the gate product, [128,256) the up product
 #pragma unroll 1
     for (int c = 0; c < 128; c += 32) {
@@ -198,6 +282,7 @@ __device__ __forceinline__ void epilogue_tile(const Params& p, int m0, int n0, u
       }
     }
   } else {
+    if (SWIGLU == 2) { epilogue_swiglu_bwd(p, m0, n0, t_row, warp, lane, vec_ok); return; }
 #pragma unroll 1
     for (int c = 0; c < BN; c += 32) {
       const int col = n0 + c;

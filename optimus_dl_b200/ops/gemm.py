@@ -185,6 +185,38 @@ def swiglu_gemm(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, save_gu: bo
     return h, g, u
 
 
+def swiglu_bwd_gemm(dy: torch.Tensor, wc: torch.Tensor, g: torch.Tensor, u: torch.Tensor) -> bool:
+    """``dh = dy @ wc`` fused with the SwiGLU backward: ``g <- dg``, ``u <- du`` in place, ``dh`` never stored.
+
+    ``dy`` is ``[M, D]``, ``wc`` the down projection ``[D, F]``, ``g`` / ``u`` the saved ``[M, F]`` gate and up
+    products. Returns False (and touches nothing) when the fused two-SM kernel does not apply; the caller then runs
+    the GEMM and the elementwise kernel separately.
+
+    The feed-forward block does NOT use this by default: at 8192 x 14336 x 4096 it measures 0.76 ms against 0.62 ms
+    for the plain product plus 0.22 ms for the elementwise kernel, and the same step time in the 8B training step.
+    The product runs at the L2 bandwidth its 256 x 256 tiles need (about 11 TB/s of operand reads), so the 0.9 GB
+    that the epilogue reads and writes are not hidden under the main loop but add to it.
+    """
+    M, D = dy.shape
+    F = wc.shape[1]
+    ok = (
+        USE_2SM
+        and _use_kernel(dy, wc, g, u)
+        and dy.is_contiguous() and g.is_contiguous() and u.is_contiguous() and wc.stride(1) == 1
+        and g.shape == (M, F) and u.shape == (M, F) and wc.shape[0] == D
+        and F % 8 == 0 and D % 8 == 0 and wc.stride(0) % 8 == 0
+        and ((M + 255) // 256) * ((F + 255) // 256) >= PAIR_MIN_TILES
+    )
+    if not ok:
+        return False
+    rc = _lib.lib().ob_gemm2_swiglu_bwd_bf16(
+        _lib.ptr(dy), dy.stride(0), _lib.ptr(wc), wc.stride(0), _lib.ptr(g), _lib.ptr(u), g.stride(0), M, F, D,
+        _lib.ptr(_lib.status_word(dy.device)), _lib.stream(),
+    )
+    _lib.check(rc, "ob_gemm2_swiglu_bwd_bf16")
+    return True
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, bias):

@@ -84,6 +84,26 @@ def test_gemm_two_sm_epilogues_and_swiglu():
     _lib.check_status()
 
 
+def test_swiglu_backward_fused_into_the_down_projection_gradient():
+    """dh = dy Wc never reaches memory: the GEMM epilogue reads g / u and leaves dg / du in their place. Checked
+    against the fp32 formulas, with a ragged last tile in both directions."""
+    from optimus_dl_b200.ops import _lib, gemm
+
+    torch.manual_seed(11)
+    T, D, F = 2304 + 40, 328, 2312           # more than 74 tiles of 256 x 256; T, F not multiples of the tile
+    dy = (torch.randn(T, D, device=_dev()) * 0.5).bfloat16()
+    wc = (torch.randn(D, F, device=_dev()) * 0.05).bfloat16()
+    g = torch.randn(T, F, device=_dev()).bfloat16()
+    u = torch.randn(T, F, device=_dev()).bfloat16()
+    g0, u0 = g.float(), u.float()
+    assert gemm.swiglu_bwd_gemm(dy, wc, g, u)
+    dh = (dy.float() @ wc.float()).bfloat16().float()
+    sg = torch.sigmoid(g0)
+    _close(g, dh * u0 * sg * (1 + g0 * (1 - sg)), 2e-2, 2e-2, "dg")
+    _close(u, dh * g0 * sg, 2e-2, 2e-2, "du")
+    _lib.check_status()
+
+
 @pytest.mark.parametrize("layout", ["fwd", "dgrad", "wgrad"])
 def test_gemm_at_flagship_shapes(layout):
     """The MLP products of the 8B config at full size (8192 tokens, 4096 x 14336), in the three operand layouts of
