@@ -162,6 +162,29 @@ def bench_gemm_fp8(t: Timer, sizes) -> None:
               quant_with_transpose_ms=round(ms_t, 4), quant_with_transpose_gbs=round(M * K * 4 / ms_t / 1e6, 1))
 
 
+def bench_gemm_swiglu_bwd(t: Timer, T: int, D: int, F: int) -> None:
+    """dh = dy Wc followed by the SwiGLU backward: the plain product, product + elementwise kernel, and the fused form."""
+    from . import _lib, gemm
+
+    dy = (torch.randn(T, D, device="cuda") * 0.5).bfloat16()
+    wc = (torch.randn(D, F, device="cuda") * 0.05).bfloat16()
+    g = torch.randn(T, F, device="cuda").bfloat16()
+    u = torch.randn(T, F, device="cuda").bfloat16()
+    h = torch.empty_like(g)
+
+    def two_kernels():
+        dh = gemm.gemm(dy, wc, b_mn=True)
+        _lib.check(_lib.lib().ob_swiglu_bwd(_lib.ptr(dh), _lib.ptr(g), _lib.ptr(u), _lib.ptr(g), _lib.ptr(u), _lib.ptr(h),
+                                            g.numel(), _lib.stream()), "swiglu_bwd")
+
+    ms_plain = t(lambda: gemm.gemm(dy, wc, b_mn=True))
+    ms_two = t(two_kernels)
+    ms_fused = t(lambda: gemm.swiglu_bwd_gemm(dy, wc, g, u))
+    _emit("gemm_swiglu_bwd", dict(M=T, N=F, K=D), ms_fused, flops=2.0 * T * F * D, plain_product_ms=round(ms_plain, 4),
+          product_plus_elementwise_ms=round(ms_two, 4))
+    _lib.check_status()
+
+
 def bench_attention(t: Timer, cases, library_rows: bool = True) -> None:
     from . import attention as A
 
@@ -512,7 +535,7 @@ def _lib_check(dev) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", required=True, choices=["gemm_bf16", "gemm_skinny", "gemm_fp8", "attention", "decode", "sampler", "elementwise",
+    ap.add_argument("--op", required=True, choices=["gemm_bf16", "gemm_skinny", "gemm_swiglu_bwd", "gemm_fp8", "attention", "decode", "sampler", "elementwise",
                                                     "tp_ag_gemm", "tp_gemm_rs", "tp_ag_gemm_fp8", "tp_gemm_rs_fp8",
                                                     "fsdp_ag_gemm", "fsdp_rs_adamw"])
     ap.add_argument("--iters", type=int, default=20)
@@ -528,6 +551,8 @@ def main() -> None:
     if args.op == "gemm_bf16":
         bench_gemm_bf16(t, [(4096, 4096, 4096)] if args.small else [(8192, 8192, 8192), (8192, 6144, 4096), (8192, 4096, 14336),
                                                                     (8192, 28672, 4096)])
+    elif args.op == "gemm_swiglu_bwd":
+        bench_gemm_swiglu_bwd(t, 8192, 4096, 14336)
     elif args.op == "gemm_skinny":   # decode-step shapes of a 1.7B model at batch 64: weight-streaming bound
         bench_gemm_skinny(t, [(64, 4096, 2048), (64, 12288, 2048), (64, 2048, 6144), (64, 151936, 2048), (8, 4096, 4096)])
     elif args.op == "gemm_fp8":
