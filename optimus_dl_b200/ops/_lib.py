@@ -70,7 +70,8 @@ class _CountingLib:
         return counted
 
 
-_NO_LAUNCH = {"ob_norm_bwd_grid", "ob_rope_grid", "ob_bind_thread", "ob_set_flag_wait_iters", "ob_gemm_skinny_splits"}
+_NO_LAUNCH = {"ob_norm_bwd_grid", "ob_rope_grid", "ob_bind_thread", "ob_set_flag_wait_iters", "ob_gemm_skinny_splits",
+              "ob_gemm2_ce_tiles"}
 _tls = threading.local()
 
 
@@ -197,6 +198,9 @@ def _declare(l: ctypes.CDLL) -> None:
     sig("ob_gemm2_bf16", [P, L, I, P, L, I, P, L, I, I, I, I, I, P, I, F, I, P, P])
     sig("ob_gemm2_swiglu_bf16", [P, L, P, P, L, P, P, P, L, I, I, I, P, P])
     sig("ob_gemm2_swiglu_bwd_bf16", [P, L, P, L, P, P, L, I, I, I, P, P])
+    sig("ob_gemm2_ce_tiles", [I])
+    sig("ob_gemm2_ce_stats_bf16", [P, L, P, L, I, I, I, P, P, P, P, I, I, F, P, P])
+    sig("ob_ce_stats_merge", [P, P, I, I, P, P, P, P, P, I, P])
     sig("ob_rmsnorm_fwd", [P, P, P, P, P, P, I, I, F, P])
     sig("ob_rmsnorm_fwd_fp8", [P, P, P, P, P, P, P, P, L, I, I, F, P])
     sig("ob_rmsnorm_bwd", [P, P, P, P, P, P, P, P, P, I, I, I, P])

@@ -185,6 +185,35 @@ def bench_gemm_swiglu_bwd(t: Timer, T: int, D: int, F: int) -> None:
     _lib.check_status()
 
 
+def bench_linear_ce_stats(t: Timer, cases) -> None:
+    """Cross-entropy statistics of one row chunk of the head without gradients: logits written by the GEMM and read by
+    the statistics kernel, against the GEMM whose epilogue reduces its tiles to the statistics."""
+    from . import _lib, gemm
+
+    gemm.CE_STATS_MIN_K = 0          # measure the fused form at every K (the dispatch keeps small K on two kernels)
+    for rows, d, V in cases:
+        x = (torch.randn(rows, d, device="cuda") * 0.5).bfloat16()
+        w = (torch.randn(V, d, device="cuda") * 0.05).bfloat16()
+        tg = torch.randint(0, V, (rows,), device="cuda", dtype=torch.int64)
+        st = torch.empty(5, rows, device="cuda", dtype=torch.float32)
+        bi = torch.empty(rows, device="cuda", dtype=torch.int32)
+        ld = (V + 7) // 8 * 8
+        buf = torch.empty(rows, ld, device="cuda", dtype=torch.bfloat16)
+        out_view = buf.as_strided((rows, V), (ld, 1))
+        l = _lib.lib()
+
+        def two_kernels():
+            gemm.gemm(x, w, out=out_view)
+            _lib.check(l.ob_ce_stats(_lib.ptr(out_view), ld, _lib.ptr(tg), _lib.ptr(st[0]), _lib.ptr(st[1]), _lib.ptr(st[2]),
+                                     _lib.ptr(st[3]), _lib.ptr(st[4]), _lib.ptr(bi), rows, V, 0, 0, 1.0, _lib.stream()), "ce_stats")
+
+        ms_two = t(two_kernels)
+        ms_fused = t(lambda: gemm.ce_stats_gemm(x, w, tg, st, bi))
+        _emit("linear_ce_stats", dict(rows=rows, d=d, V=V), ms_fused, flops=2.0 * rows * d * V,
+              gemm_plus_stats_kernel_ms=round(ms_two, 4))
+        _lib.check_status()
+
+
 def bench_attention(t: Timer, cases, library_rows: bool = True) -> None:
     from . import attention as A
 
@@ -535,7 +564,7 @@ def _lib_check(dev) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", required=True, choices=["gemm_bf16", "gemm_skinny", "gemm_swiglu_bwd", "gemm_fp8", "attention", "decode", "sampler", "elementwise",
+    ap.add_argument("--op", required=True, choices=["gemm_bf16", "gemm_skinny", "gemm_swiglu_bwd", "linear_ce_stats", "gemm_fp8", "attention", "decode", "sampler", "elementwise",
                                                     "tp_ag_gemm", "tp_gemm_rs", "tp_ag_gemm_fp8", "tp_gemm_rs_fp8",
                                                     "fsdp_ag_gemm", "fsdp_rs_adamw"])
     ap.add_argument("--iters", type=int, default=20)
@@ -553,6 +582,8 @@ def main() -> None:
                                                                     (8192, 28672, 4096)])
     elif args.op == "gemm_swiglu_bwd":
         bench_gemm_swiglu_bwd(t, 8192, 4096, 14336)
+    elif args.op == "linear_ce_stats":      # one 4096-row chunk of the output head: Llama-3-8B and Qwen3-1.7B
+        bench_linear_ce_stats(t, [(4096, 4096, 128256), (4096, 2048, 151936)])
     elif args.op == "gemm_skinny":   # decode-step shapes of a 1.7B model at batch 64: weight-streaming bound
         bench_gemm_skinny(t, [(64, 4096, 2048), (64, 12288, 2048), (64, 2048, 6144), (64, 151936, 2048), (8, 4096, 4096)])
     elif args.op == "gemm_fp8":

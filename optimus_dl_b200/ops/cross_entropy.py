@@ -4,7 +4,9 @@
 holding the ``[tokens, vocab]`` logits: rows are processed in chunks; each chunk's logits come
 from the tcgen05 GEMM, two kernels (``csrc/ce.cu``) turn them into per-row statistics and then,
 in place, into ``d loss / d logits``; two more GEMMs give ``dX`` and accumulate ``dW``. The
-backward pass therefore only rescales the stored gradients.
+backward pass therefore only rescales the stored gradients. When no gradient is asked for
+(evaluation, metrics, the log-probability pass of the GRPO recipe) not even a chunk is written:
+the GEMM's epilogue reduces its accumulator tiles to the statistics (``gemm.ce_stats_gemm``).
 
 With a tensor-parallel group the weight is a vocabulary shard ``[V/tp, d]``; ranks exchange
 ``(max, sum-exp, target logit, sum of logits, arg max)`` per row (5 floats) instead of logits.
@@ -88,7 +90,7 @@ class _LinearCE(torch.autograd.Function):
             first_acc = False
         ld = (V + 7) // 8 * 8
         chunk_rows = min(chunk_rows, T)
-        logits_buf = torch.empty((chunk_rows, ld), dtype=torch.bfloat16, device=dev)
+        logits_buf = None                 # allocated when a chunk has to be materialised
         stats = torch.empty((5, T), dtype=torch.float32, device=dev)
         best_idx = torch.empty(T, dtype=torch.int32, device=dev)
         lse_all = torch.empty(T, dtype=torch.float32, device=dev)
@@ -96,14 +98,20 @@ class _LinearCE(torch.autograd.Function):
         for r0 in range(0, T, chunk_rows):
             r1 = min(T, r0 + chunk_rows)
             rows = r1 - r0
-            lg = logits_buf[:rows, :V] if ld == V else logits_buf[:rows]
-            out_view = logits_buf[:rows].as_strided((rows, V), (ld, 1))
-            gemm.gemm(x2[r0:r1], weight, out=out_view)
+            # Without gradients (evaluation, metrics) the statistics come out of the GEMM's epilogue and no logits
+            # are written; with gradients the bf16 chunk is needed anyway (it becomes d loss / d logits in place).
             st = stats[:, r0:r1]
-            rc = l.ob_ce_stats(_lib.ptr(out_view), ld, _lib.ptr(tg[r0:r1]), _lib.ptr(st[0]), _lib.ptr(st[1]),
-                               _lib.ptr(st[2]), _lib.ptr(st[3]), _lib.ptr(st[4]), _lib.ptr(best_idx[r0:r1]), rows, V,
-                               int(vocab_offset), mode, cap_c, _lib.stream())
-            _lib.check(rc, "ob_ce_stats")
+            fused = not (need_dx or need_dw) and gemm.ce_stats_gemm(
+                x2[r0:r1], weight, tg[r0:r1], st, best_idx[r0:r1], int(vocab_offset), mode, cap_c)
+            if not fused:
+                if logits_buf is None:
+                    logits_buf = torch.empty((chunk_rows, ld), dtype=torch.bfloat16, device=dev)
+                out_view = logits_buf[:rows].as_strided((rows, V), (ld, 1))
+                gemm.gemm(x2[r0:r1], weight, out=out_view)
+                rc = l.ob_ce_stats(_lib.ptr(out_view), ld, _lib.ptr(tg[r0:r1]), _lib.ptr(st[0]), _lib.ptr(st[1]),
+                                   _lib.ptr(st[2]), _lib.ptr(st[3]), _lib.ptr(st[4]), _lib.ptr(best_idx[r0:r1]), rows, V,
+                                   int(vocab_offset), mode, cap_c, _lib.stream())
+                _lib.check(rc, "ob_ce_stats")
             mx, se, sz, zt, bv = st[0], st[1], st[2], st[3], st[4]
             if tp_group is not None:
                 import torch.distributed as dist
@@ -191,7 +199,7 @@ class _LinearTokenLoss(torch.autograd.Function):
             dw, first_acc = (torch.empty_like(weight) if need_dw else None), False
         ld = (V + 7) // 8 * 8
         chunk_rows = min(chunk_rows, T)
-        logits_buf = torch.empty((chunk_rows, ld), dtype=torch.bfloat16, device=dev)
+        logits_buf = None                 # allocated when a chunk has to be materialised (gradients)
         st = torch.empty((5, chunk_rows), dtype=torch.float32, device=dev)
         best = torch.empty(chunk_rows, dtype=torch.int32, device=dev)
         nll_all = torch.empty(T, dtype=torch.float32, device=dev)
@@ -200,12 +208,17 @@ class _LinearTokenLoss(torch.autograd.Function):
         for r0 in range(0, T, chunk_rows):
             r1 = min(T, r0 + chunk_rows)
             rows = r1 - r0
-            out_view = logits_buf[:rows].as_strided((rows, V), (ld, 1))
-            gemm.gemm(x2[r0:r1], weight, out=out_view)
-            rc = l.ob_ce_stats(_lib.ptr(out_view), ld, _lib.ptr(tg[r0:r1]), _lib.ptr(st[0]), _lib.ptr(st[1]),
-                               _lib.ptr(st[2]), _lib.ptr(st[3]), _lib.ptr(st[4]), _lib.ptr(best), rows, V, 0, 0, 1.0,
-                               _lib.stream())
-            _lib.check(rc, "ob_ce_stats")
+            fused = not (need_dx or need_dw) and gemm.ce_stats_gemm(x2[r0:r1], weight, tg[r0:r1], st[:, :rows],
+                                                                     best[:rows], 0, 0, 1.0)
+            if not fused:
+                if logits_buf is None:
+                    logits_buf = torch.empty((chunk_rows, ld), dtype=torch.bfloat16, device=dev)
+                out_view = logits_buf[:rows].as_strided((rows, V), (ld, 1))
+                gemm.gemm(x2[r0:r1], weight, out=out_view)
+                rc = l.ob_ce_stats(_lib.ptr(out_view), ld, _lib.ptr(tg[r0:r1]), _lib.ptr(st[0]), _lib.ptr(st[1]),
+                                   _lib.ptr(st[2]), _lib.ptr(st[3]), _lib.ptr(st[4]), _lib.ptr(best), rows, V, 0, 0, 1.0,
+                                   _lib.stream())
+                _lib.check(rc, "ob_ce_stats")
             lse = st[0, :rows] + torch.log(st[1, :rows])
             nll = lse - st[3, :rows]
             nll_all[r0:r1] = nll

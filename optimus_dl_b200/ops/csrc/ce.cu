@@ -142,8 +142,54 @@ ce_grad_kernel(__nv_bfloat16* __restrict__ logits, long long ld, const long long
   }
 }
 
+// Folds the per-tile statistics of the fused "linear + statistics" product (gemm::Params::ce_part: one float4 and one
+// column index per row and 256-column tile, a row's tiles contiguous) into the same per-row outputs as
+// ce_stats_kernel.  One warp per row; equal maxima keep the lowest column.
+__global__ void __launch_bounds__(THREADS)
+ce_stats_merge_kernel(const float4* __restrict__ part, const int* __restrict__ part_idx, int rows, int tiles_n,
+                      float* __restrict__ row_max, float* __restrict__ row_sumexp, float* __restrict__ row_sum,
+                      float* __restrict__ row_best, int* __restrict__ row_best_idx, int vocab_offset) {
+  const int row = blockIdx.x * (THREADS / 32) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  Stat st{-INFINITY, 0.f, 0.f, -INFINITY, 0x7fffffff};
+  for (int t = lane; t < tiles_n; t += 32) {
+    const float4 v = part[(long long)row * tiles_n + t];
+    Stat o{v.x, v.y, v.z, v.w, part_idx[(long long)row * tiles_n + t]};
+    stat_merge(st, o);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Stat other;
+    other.m = __shfl_xor_sync(0xffffffffu, st.m, o);
+    other.s = __shfl_xor_sync(0xffffffffu, st.s, o);
+    other.sum = __shfl_xor_sync(0xffffffffu, st.sum, o);
+    other.best = __shfl_xor_sync(0xffffffffu, st.best, o);
+    other.best_idx = __shfl_xor_sync(0xffffffffu, st.best_idx, o);
+    stat_merge(st, other);
+  }
+  if (lane == 0) {
+    row_max[row] = st.m;
+    row_sumexp[row] = st.s;
+    row_sum[row] = st.sum;
+    row_best[row] = st.best;
+    row_best_idx[row] = st.best_idx + vocab_offset;
+  }
+}
+
 }  // namespace ce
 }  // namespace ob
+
+extern "C" int ob_ce_stats_merge(const void* part, const void* part_idx, int rows, int tiles_n, void* row_max,
+                                 void* row_sumexp, void* row_sum, void* row_best, void* row_best_idx, int vocab_offset,
+                                 cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  constexpr int rows_per_block = ob::ce::THREADS / 32;
+  ob::ce::ce_stats_merge_kernel<<<(rows + rows_per_block - 1) / rows_per_block, ob::ce::THREADS, 0, stream>>>(
+      (const float4*)part, (const int*)part_idx, rows, tiles_n, (float*)row_max, (float*)row_sumexp, (float*)row_sum,
+      (float*)row_best, (int*)row_best_idx, vocab_offset);
+  return (int)cudaGetLastError();
+}
+
 
 using namespace ob::ce;
 

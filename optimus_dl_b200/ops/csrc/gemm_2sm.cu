@@ -13,7 +13,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   gemm2_cta<A_MN, B_MN, SWIGLU>(&tmA, &tmB, &tmB2, p, blockIdx.x >> 1, gridDim.x >> 1, smem_raw);
 }
 
-static int g_max_pairs[4][3] = {};
+static int g_max_pairs[4][4] = {};
 
 template <int A_MN, int B_MN, int SWIGLU>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const Params& p, int max_ctas,
@@ -106,4 +106,26 @@ extern "C" int ob_gemm2_swiglu_bwd_bf16(const void* DY, long long lddy, const vo
   p.M = M; p.N = N; p.K = K; p.C = nullptr; p.ldc = ldg; p.G = G; p.U = U; p.act = gemm::kActSwigluBwd; p.alpha = 1.0f;
   p.status = status; p.flag_rows = 1; p.a_flag_rows = 1;
   return gemm2::launch<0, 1, 2>(ta, tb, tb, p, 0, stream);
+}
+
+// Logits = X[M, K] W[N, K]^T reduced on the fly to per-row cross-entropy statistics (Params::ce_part): nothing of
+// size M x N is written.  `part` holds M * tiles_n float4 (16-byte aligned), `part_idx` M * tiles_n ints (tiles_n =
+// ceil(N / 256), see ob_gemm2_ce_tiles), `tgt_out` M floats that the caller zeroes first.  ob_ce_stats_merge folds
+// the tiles.
+extern "C" int ob_gemm2_ce_tiles(int N) { return (N + gemm2::TN - 1) / gemm2::TN; }
+extern "C" int ob_gemm2_ce_stats_bf16(const void* X, long long ldx, const void* W, long long ldw, int M, int N, int K,
+                                      const void* targets, void* part, void* part_idx, void* tgt_out, int vocab_offset,
+                                      int softcap, float cap_c, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d(&ta, X, M, K, ldx, 128, gemm2::BK, 2);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tb, W, N, K, ldw, 128, gemm2::BK, 2);
+  if (rc) return rc;
+  gemm::Params p{};
+  p.M = M; p.N = N; p.K = K; p.C = nullptr; p.ldc = 0; p.alpha = 1.0f; p.status = status; p.flag_rows = 1; p.a_flag_rows = 1;
+  p.ce_targets = (const long long*)targets; p.ce_part = (float*)part; p.ce_part_idx = (int*)part_idx;
+  p.ce_tgt = (float*)tgt_out; p.ce_tiles = (N + gemm2::TN - 1) / gemm2::TN; p.ce_vocab_offset = vocab_offset;
+  p.ce_softcap = softcap; p.ce_cap = cap_c;
+  return gemm2::launch<0, 0, 3>(ta, tb, tb, p, 0, stream);
 }

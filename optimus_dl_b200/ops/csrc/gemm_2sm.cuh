@@ -109,7 +109,8 @@ __device__ __forceinline__ void gemm2_cta(const CUtensorMap* tmA_, const CUtenso
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
-  constexpr bool DUAL = SWIGLU == 1;                   // 1: dual-B SwiGLU forward, 2: SwiGLU-backward epilogue
+  constexpr bool DUAL = SWIGLU == 1;                   // 1: dual-B SwiGLU forward, 2: SwiGLU-backward epilogue,
+                                                       // 3: cross-entropy statistics epilogue (no output tensor)
   constexpr int bn = DUAL ? TN / 2 : TN;               // output columns per tile
   const int tiles_m = (p.M + TM - 1) / TM;
   const int tiles_n = (p.N + bn - 1) / bn;

@@ -77,6 +77,19 @@ struct Params {
   void* rs_dst[16];
   int rs_rows;
   int rs_me;
+  // Cross-entropy statistics epilogue (own kernel instantiation): the product is a block of logits that is never
+  // stored.  Per output row and 256-column tile the epilogue leaves max, sum exp(z - max), sum z and the largest
+  // value as one float4 in ce_part[row * ce_tiles + tile_n], its column in ce_part_idx[row * ce_tiles + tile_n], and
+  // the logit of the row's target (when the target lies in the tile) in ce_tgt[row].  z is the bf16-rounded logit after the optional
+  // soft cap (ce_softcap: 0 none, 1 c tanh(x / c), 2 23 sigmoid((x + 5) / 7.5)).
+  const long long* ce_targets;
+  float* ce_part;
+  int* ce_part_idx;
+  float* ce_tgt;
+  int ce_tiles;          // 256-column tiles per row = ceil(N / 256)
+  int ce_vocab_offset;
+  int ce_softcap;
+  float ce_cap;
 };
 
 struct TileCoord {
@@ -229,6 +242,67 @@ __device__ __forceinline__ void epilogue_swiglu_bwd(const Params& p, int m0, int
   }
 }
 
+// Epilogue of the "linear layer + cross-entropy statistics" product (see Params::ce_part).  Thread = row; the 256
+// columns of the tile go by in eight steps of 32 with a running (max, sum-exp) pair that is rescaled once per step.
+__device__ __forceinline__ void epilogue_ce_stats(const Params& p, int m0, int n0, uint32_t t_row, int warp, int lane) {
+  const int row = m0 + (warp & 3) * 32 + lane;
+  const bool row_ok = row < p.M;
+  long long y = -1;
+  if (row_ok) y = p.ce_targets[row] - p.ce_vocab_offset;        // outside [0, N): not in this slice (or ignored)
+  float m = -INFINITY, s = 0.f, sum = 0.f, best = -INFINITY, tgt = 0.f;
+  int best_idx = 0x7fffffff;
+  bool has_tgt = false;
+  auto capf = [&](float x) {
+    x = __bfloat162float(__float2bfloat16(x));
+    if (p.ce_softcap == 1) return p.ce_cap * tanhf(x / p.ce_cap);
+    if (p.ce_softcap == 2) return 23.0f / (1.0f + __expf(-(x + 5.0f) / 7.5f));
+    return x;
+  };
+  auto step = [&](const uint32_t* r, int c) {
+    const int col = n0 + c;
+    const int ncols = min(32, p.N - col);    // warp-uniform
+    float z[32];
+    float cm = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      z[j] = j < ncols ? capf(__uint_as_float(r[j])) : -INFINITY;
+      cm = fmaxf(cm, z[j]);
+    }
+    if (cm > m) { s *= __expf(m - cm); m = cm; }
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      s += __expf(z[j] - m);                 // -inf for the columns past N: adds 0
+      sum += j < ncols ? z[j] : 0.f;
+      if (z[j] > best) { best = z[j]; best_idx = col + j; }
+      if ((long long)(col + j) == y) { tgt = z[j]; has_tgt = true; }
+    }
+  };
+  // two register buffers: the TMEM read of the next 32 columns is in flight while the current ones are reduced (a
+  // read waits behind the accumulator traffic of the running MMAs for a few thousand cycles)
+  uint32_t ra[32], rb[32];
+  tmem_ld_32x32(t_row, ra);
+  tmem_ld_wait32(ra);
+#pragma unroll 1
+  for (int c = 0; c < BN; c += 64) {
+    const bool has_b = n0 + c + 32 < p.N;                 // all warp-uniform
+    const bool has_next = c + 64 < BN && n0 + c + 64 < p.N;
+    if (has_b) tmem_ld_32x32(t_row + c + 32, rb);
+    step(ra, c);
+    if (!has_b) break;
+    tmem_ld_wait32(rb);
+    if (has_next) tmem_ld_32x32(t_row + c + 64, ra);
+    step(rb, c + 32);
+    if (!has_next) break;
+    tmem_ld_wait32(ra);
+  }
+  if (row_ok) {
+    const long long slot = (long long)row * p.ce_tiles + n0 / BN;
+    reinterpret_cast<float4*>(p.ce_part)[slot] = make_float4(m, s, sum, best);
+    p.ce_part_idx[slot] = best_idx;
+    if (has_tgt) p.ce_tgt[row] = tgt;
+  }
+}
+
 // Epilogue of one 128 x 256 accumulator tile, executed by one epilogue warp for its 32 TMEM lanes:
 // `t_row` is the TMEM address of the warp's first lane at the tile's first column, (m0, n0) the tile origin in C.
 template <int SWIGLU>
@@ -283,6 +357,7 @@ __device__ __forceinline__ void epilogue_tile(const Params& p, int m0, int n0, u
     }
   } else {
     if (SWIGLU == 2) { epilogue_swiglu_bwd(p, m0, n0, t_row, warp, lane, vec_ok); return; }
+    if (SWIGLU == 3) { epilogue_ce_stats(p, m0, n0, t_row, warp, lane); return; }
 #pragma unroll 1
     for (int c = 0; c < BN; c += 32) {
       const int col = n0 + c;

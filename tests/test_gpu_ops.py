@@ -84,6 +84,51 @@ def test_gemm_two_sm_epilogues_and_swiglu():
     _lib.check_status()
 
 
+@pytest.mark.parametrize("softcap", [(0, 1.0), (1, 30.0), (2, 1.0)])
+def test_cross_entropy_statistics_from_the_gemm_epilogue(softcap, monkeypatch):
+    """Per-row (max, sum-exp, sum, target logit, arg-max) straight from the accumulator tiles against the statistics
+    kernel on materialised bf16 logits; vocabulary not a multiple of the tile, targets outside the slice, rows not
+    a multiple of the tile; then the whole loss without gradients against the same call with gradients."""
+    from optimus_dl_b200.ops import _lib, gemm
+    from optimus_dl_b200.ops.cross_entropy import linear_cross_entropy
+
+    monkeypatch.setattr(gemm, "CE_STATS_MIN_K", 0)     # the dispatch keeps small K on the two-kernel path
+    torch.manual_seed(13)
+    mode, cap = softcap
+    rows, d, V, off = 2304 + 24, 328, 2312 + 56, 1000
+    x = (torch.randn(rows, d, device=_dev()) * 0.7).bfloat16()
+    w = (torch.randn(V, d, device=_dev()) * 0.2).bfloat16()
+    tg = torch.randint(0, V + 2 * off, (rows,), device=_dev(), dtype=torch.int64)      # some fall outside [off, off + V)
+    tg[::7] = -100
+    st = torch.empty(5, rows, device=_dev(), dtype=torch.float32)
+    bi = torch.empty(rows, device=_dev(), dtype=torch.int32)
+    assert gemm.ce_stats_gemm(x, w, tg, st, bi, off, mode, cap)
+    logits = gemm.gemm(x, w)
+    st_r = torch.empty_like(st)
+    bi_r = torch.empty_like(bi)
+    l = _lib.lib()
+    _lib.check(l.ob_ce_stats(_lib.ptr(logits), logits.stride(0), _lib.ptr(tg), _lib.ptr(st_r[0]), _lib.ptr(st_r[1]),
+                             _lib.ptr(st_r[2]), _lib.ptr(st_r[3]), _lib.ptr(st_r[4]), _lib.ptr(bi_r), rows, V, off, mode, cap,
+                             _lib.stream()), "ob_ce_stats")
+    assert torch.equal(st[0], st_r[0]) and torch.equal(st[4], st_r[4]) and torch.equal(st[3], st_r[3])
+    assert torch.equal(bi, bi_r)
+    lse, lse_r = st[0] + st[1].log(), st_r[0] + st_r[1].log()
+    assert (lse - lse_r).abs().max().item() < 1e-4
+    assert ((st[2] - st_r[2]).abs() <= 1e-4 * st_r[2].abs() + 2e-2).all()
+    _lib.check_status()
+
+    tg2 = torch.randint(0, V, (rows,), device=_dev(), dtype=torch.int64)
+    tg2[::5] = -100
+    kw = dict(label_smoothing=0.1, softcap=cap if mode == 1 else None, softcap_type="sigmoid" if mode == 2 else "tanh")
+    with torch.no_grad():
+        a = linear_cross_entropy(x, w, tg2, **kw)
+    xg = x.clone().requires_grad_(True)
+    b = linear_cross_entropy(xg, w, tg2, **kw)
+    assert abs(a.loss.item() - b.loss.item()) < 1e-4 * max(1.0, abs(b.loss.item()))
+    assert a.n_correct.item() == b.n_correct.item() and a.n_valid.item() == b.n_valid.item()
+    _lib.check_status()
+
+
 def test_swiglu_backward_fused_into_the_down_projection_gradient():
     """dh = dy Wc never reaches memory: the GEMM epilogue reads g / u and leaves dg / du in their place. Checked
     against the fp32 formulas, with a ragged last tile in both directions."""
