@@ -35,6 +35,10 @@ def bootstrap() -> None:
 
 
 def _init() -> None:
+    from .core import aliases
+
+    aliases.install()      # the reference's module paths that differ from this tree resolve to the modules here
+    from .core import config_utils  # noqa: F401  (registers the eval / env / hash resolvers of the config system)
     threads = _os.environ.get("OPTIMUS_DL_NUM_THREADS", "1")
     try:
         import torch

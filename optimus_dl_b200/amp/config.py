@@ -1,3 +1,3 @@
 """Re-export of the AMP configs (optimus_dl/modules/amp/config.py)."""
 
-from ..optim.config import AmpConfig, Fp8Config  # noqa: F401
+from ..optim.config import AmpConfig, Fp8Config, OptimizationConfig  # noqa: F401

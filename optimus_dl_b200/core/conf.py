@@ -171,14 +171,16 @@ def _wrap(value: Any, parent: Node | None, key: Any) -> Any:
         object.__setattr__(value, "_parent", parent)
         object.__setattr__(value, "_key", key)
         return value
+    import dataclasses
+
+    # dataclass instances first: flexible registry configs are dataclasses AND dict subclasses (their fields would be
+    # lost if they were taken for plain mappings; _dataclass_to_dict adds the mapping's own items on top)
+    if dataclasses.is_dataclass(value) and not isinstance(value, type):
+        return DictNode(_dataclass_to_dict(value), parent=parent, key=key)
     if isinstance(value, Mapping):
         return DictNode(value, parent=parent, key=key)
     if isinstance(value, (list, tuple)):
         return ListNode(value, parent=parent, key=key)
-    import dataclasses
-
-    if dataclasses.is_dataclass(value) and not isinstance(value, type):
-        return DictNode(_dataclass_to_dict(value), parent=parent, key=key)
     return value
 
 

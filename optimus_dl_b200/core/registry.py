@@ -49,8 +49,9 @@ class RegistryConfig(dict):
         pass
 
 
-class ConfigValidationError(ValueError):
-    pass
+class ConfigValidationError(ValueError, TypeError):
+    """A config does not fit its dataclass: unknown key (the reference raises ValueError there) or a value that
+    cannot be cast (TypeError there); both ``except`` forms catch this class."""
 
 
 def _is_registry_cfg(cls: Any) -> bool:
@@ -101,7 +102,7 @@ def _hints(cls: type) -> dict[str, Any]:
         return {f.name: f.type for f in dataclasses.fields(cls)}
 
 
-def validate_and_cast(tp: Any, value: Any, path: str = "") -> Any:
+def _validate_and_cast(tp: Any, value: Any, path: str = "") -> Any:
     """Recursively check ``value`` against the type ``tp`` and cast where it is safe.
 
     Handles dataclasses, ``Optional``/``Union``, ``list``/``tuple``/``dict`` generics, enums and
@@ -118,17 +119,13 @@ def validate_and_cast(tp: Any, value: Any, path: str = "") -> Any:
         if value is None and type(None) in args:
             return None
         errors = []
-        # exact type match wins before any casting is tried
-        for a in args:
-            if a is type(None):
-                continue
-            if isinstance(a, type) and not dataclasses.is_dataclass(a) and type(value) is a:
-                return value
+        # the first member the value can be cast to wins ("123" for int | str is 123), as in
+        # optimus_dl/core/registry.py's union handling
         for a in args:
             if a is type(None):
                 continue
             try:
-                return validate_and_cast(a, value, path)
+                return _validate_and_cast(a, value, path)
             except ConfigValidationError as e:
                 errors.append(str(e))
         raise ConfigValidationError(f"{path or 'value'}: {value!r} matches none of {_type_name(tp)} ({'; '.join(errors)})")
@@ -144,17 +141,17 @@ def validate_and_cast(tp: Any, value: Any, path: str = "") -> Any:
             flexible = issubclass(tp, dict)
             for k, v in raw.items():
                 if k not in hints and k != "_name" and not flexible:
-                    raise ConfigValidationError(f"{path + '.' if path else ''}{k}: unknown key for {tp.__name__}")
+                    raise ConfigValidationError(f"Unknown keys for {tp.__name__}: {path + '.' if path else ''}{k}")
                 merged[k] = _deep_merge(merged.get(k), v)
             for k in list(merged):
                 if k in hints:
-                    merged[k] = validate_and_cast(hints[k], merged[k], f"{path + '.' if path else ''}{k}")
+                    merged[k] = _validate_and_cast(hints[k], merged[k], f"{path + '.' if path else ''}{k}")
             return merged
         raise ConfigValidationError(f"{path or 'value'}: expected mapping for {tp.__name__}, got {type(value).__name__}")
     if origin in (list, typing.List) or tp is list:
         if isinstance(value, (list, tuple, ListNode)):
             (et,) = get_args(tp) or (Any,)
-            return [validate_and_cast(et, v, f"{path}[{i}]") for i, v in enumerate(_raw_list(value))]
+            return [_validate_and_cast(et, v, f"{path}[{i}]") for i, v in enumerate(_raw_list(value))]
         raise ConfigValidationError(f"{path or 'value'}: expected list, got {type(value).__name__}")
     if origin in (tuple, typing.Tuple) or tp is tuple:
         if isinstance(value, (list, tuple, ListNode)):
@@ -163,16 +160,16 @@ def validate_and_cast(tp: Any, value: Any, path: str = "") -> Any:
             if args and args[-1] is not Ellipsis:
                 if len(args) != len(vals):
                     raise ConfigValidationError(f"{path or 'value'}: expected {len(args)} items, got {len(vals)}")
-                return [validate_and_cast(a, v, f"{path}[{i}]") for i, (a, v) in enumerate(zip(args, vals))]
+                return [_validate_and_cast(a, v, f"{path}[{i}]") for i, (a, v) in enumerate(zip(args, vals))]
             et = args[0] if args else Any
-            return [validate_and_cast(et, v, f"{path}[{i}]") for i, v in enumerate(vals)]
+            return [_validate_and_cast(et, v, f"{path}[{i}]") for i, v in enumerate(vals)]
         raise ConfigValidationError(f"{path or 'value'}: expected tuple, got {type(value).__name__}")
     if origin in (dict, typing.Dict) or tp is dict:
         if isinstance(value, (dict, DictNode)):
             args = get_args(tp)
             vt = args[1] if len(args) == 2 else Any
             raw = conf.to_container(value, resolve=False) if isinstance(value, DictNode) else value
-            return {k: validate_and_cast(vt, v, f"{path}.{k}") for k, v in raw.items()}
+            return {k: _validate_and_cast(vt, v, f"{path}.{k}") for k, v in raw.items()}
         if dataclasses.is_dataclass(value) and not isinstance(value, type):
             return instance_to_dict(value)
         raise ConfigValidationError(f"{path or 'value'}: expected dict, got {type(value).__name__}")
@@ -227,6 +224,21 @@ def validate_and_cast(tp: Any, value: Any, path: str = "") -> Any:
         raise ConfigValidationError(f"{path or 'value'}: {value!r} not in {get_args(tp)}")
     return value
 
+
+
+def validate_and_cast(tp: Any, value: Any, path: str = "") -> Any:
+    """Check ``value`` against the type ``tp`` and cast where it is safe (see ``_validate_and_cast``).
+
+    For a dataclass type the result is a config node: attribute and item access, extra keys of flexible configs kept
+    (``casted.simple.param_int``, ``casted["extra"]``), as optimus_dl/core/registry.py:96-257 returns an OmegaConf
+    object. Interpolations in a config node are resolved first.
+    """
+    if isinstance(value, conf.Node):
+        value = conf.to_container(value, resolve=True)
+    out = _validate_and_cast(tp, value, path)
+    if dataclasses.is_dataclass(tp) and isinstance(tp, type) and isinstance(out, dict):
+        return conf.create(out)
+    return out
 
 def _raw_list(v: Any) -> list:
     if isinstance(v, ListNode):

@@ -120,7 +120,8 @@ class CrossEntropyCriterion(BaseCriterion):
         flat_targets = targets.reshape(-1)
         want_logits = bool(requested & LOGIT_PROTOCOLS)
         use_fused = self.cfg.fused_head if self.cfg.fused_head is not None else True
-        use_fused = use_fused and getattr(model_root(model), "supports_fused_head", False) and not want_logits
+        # ``is True``: a stand-in model (unittest.mock.Mock and the like) answers any attribute with a truthy object
+        use_fused = use_fused and getattr(model_root(model), "supports_fused_head", False) is True and not want_logits
         exposed: dict[str, Any] = {}
         if use_fused:
             hidden = model(**batch, skip_lm_head=True)["hidden"]
@@ -144,7 +145,7 @@ class CrossEntropyCriterion(BaseCriterion):
         log_summed("total_tokens", lambda: n_valid() / tp, reset=False)
         loss_val = cached_lambda(lambda: loss.detach().float().item())
         log_averaged("loss", loss_val, weight=n_valid, round=4, priority=0)
-        log_averaged_exponent("perplexity", loss_val, weight=n_valid, round=4, priority=1)
+        log_averaged_exponent("perplexity", value=loss_val, weight=n_valid, round=4, priority=1)
         if "loss" in requested:
             exposed["loss"] = loss.detach()
         if "input_tokens" in requested:
@@ -160,6 +161,30 @@ class CrossEntropyCriterion(BaseCriterion):
             if "classification" in requested:
                 exposed["classification"] = {"predictions": lg.argmax(-1), "targets": tg, "mask": mask}
         return loss, exposed
+
+    # ------------------------------------------------------------------ helpers of the reference's public surface
+    @torch.no_grad()
+    def gather_predictions(self, logits: torch.Tensor) -> torch.Tensor:
+        """Arg-max token per position (optimus_dl/modules/criterion/cross_entropy.py:410-442). With a
+        vocabulary-sharded head (``logits`` holds this rank's slice) the ranks exchange their best value and its
+        global index."""
+        tp = self._tp_size()
+        if tp <= 1 or self.collective is None:
+            return logits.argmax(-1)
+        tp_world = self.collective.tp_world
+        best = logits.max(-1)
+        idx = best.indices + self.collective.tp_rank * logits.shape[-1]
+        vals = tp_world.all_gather_to_list(best.values)
+        idxs = tp_world.all_gather_to_list(idx)
+        winner = torch.stack(vals, -1).argmax(-1, keepdim=True)
+        return torch.stack(idxs, -1).gather(-1, winner).squeeze(-1)
+
+    @torch.no_grad()
+    def accuracy_metric(self, predictions: torch.Tensor, targets: torch.Tensor) -> float:
+        """Top-1 accuracy over the valid targets (optimus_dl/modules/criterion/cross_entropy.py:444-454)."""
+        valid = (targets >= 0) & (targets != self.padding_token_id)
+        correct = ((predictions == targets) & valid).float()
+        return (correct.sum() / valid.sum()).item()
 
     @staticmethod
     def _unflatten(logits: torch.Tensor, targets: torch.Tensor, batch: dict[str, Any]):

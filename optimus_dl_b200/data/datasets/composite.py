@@ -116,26 +116,32 @@ class CompositeDataset(BaseDataset):
         return {"sampler": self.sampler.state(), "exhausted": sorted(self.exhausted), "epochs": dict(self.epochs),
                 "datasets": {n: ds.state_dict() for n, ds in self.datasets.items()}}
 
+    def _check_stop(self) -> None:
+        """Stop rules of optimus_dl/modules/data/datasets/composite.py:328-338: a dataset that cycles never counts as
+        exhausted; ``cycle_forever`` never stops; otherwise the stream ends when every dataset is exhausted, or, with
+        ``first_dataset_exhausted``, when any is."""
+        if self.stop == StopCriteria.CYCLE_FOREVER:
+            return
+        if self.exhausted == set(self.datasets):
+            raise StopIteration
+        if self.stop == StopCriteria.FIRST_DATASET_EXHAUSTED and self.exhausted:
+            raise StopIteration
+
     def next(self) -> Any:
         while True:
+            self._check_stop()
             if not self.sampler.any_active():
-                raise StopIteration
+                raise RuntimeError("every dataset is exhausted and none of them cycles")
             name = self.sampler.next()
             try:
                 return next(self.datasets[name])
             except StopIteration:
-                self.exhausted.add(name)
-                if self.stop == StopCriteria.FIRST_DATASET_EXHAUSTED:
-                    raise
-                if self.stop == StopCriteria.ALL_DATASETS_EXHAUSTED and self.exhausted == set(self.datasets):
-                    raise
                 if self.entries[name].cycle:
                     self.epochs[name] += 1
-                    self.datasets[name] = build_dataset(self.entries[name].dataset, **self.kwargs)
                     self.datasets[name].reset()
                     try:
                         return next(self.datasets[name])
-                    except StopIteration:
-                        self.sampler.disable(name)
-                else:
-                    self.sampler.disable(name)
+                    except StopIteration as err:
+                        raise RuntimeError(f"dataset '{name}' yields nothing after the reset that should cycle it") from err
+                self.exhausted.add(name)
+                self.sampler.disable(name)

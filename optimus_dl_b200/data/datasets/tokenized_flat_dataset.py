@@ -1,6 +1,8 @@
 """``tokenized_flat``: memory-maps raw token files as one stream, gives every rank an equal token
-span and yields ready ``(batch_size, seq_len + 1)`` blocks
-(optimus_dl/modules/data/datasets/tokenized_flat_dataset.py:17-173)."""
+span and yields ready ``(batch_size, seq_len)`` blocks in the files' dtype
+(optimus_dl/modules/data/datasets/tokenized_flat_dataset.py:17-173: same shapes, same stop rule -- a block that ends
+past the rank's span is dropped -- and the same state keys). ``add_one_for_shift: true`` is an addition: rows of
+``seq_len + 1`` tokens that overlap by one, so that shifting inputs against targets loses no token."""
 
 from __future__ import annotations
 
@@ -24,7 +26,7 @@ class TokenizedFlatDatasetConfig(RegistryConfigStrict):
     seq_len: int = 1024
     header_bytes: int = 0
     offset: int | None = None       # the reference's name for header_bytes (bytes skipped at the start of raw files)
-    add_one_for_shift: bool = True
+    add_one_for_shift: bool = False
 
 
 @register_dataset("tokenized_flat", TokenizedFlatDatasetConfig)
@@ -52,7 +54,7 @@ class TokenizedFlatDataset(BaseDataset):
         self.pos = self.start
 
     def _read(self, a: int, b: int) -> np.ndarray:
-        out = np.empty(b - a, dtype=np.int64)
+        out = np.empty(b - a, dtype=self.maps[0].dtype)
         o = 0
         f = int(np.searchsorted(self.cum, a, side="right") - 1)
         while a < b:
@@ -66,16 +68,28 @@ class TokenizedFlatDataset(BaseDataset):
 
     def reset(self, initial_state: dict | None = None):
         super().reset(initial_state)
-        self.pos = int(initial_state["pos"]) if initial_state else self.start
+        st = initial_state or {}
+        assert st.get("world_size", self.world_size) == self.world_size and st.get("rank", self.rank) == self.rank
+        self.pos = int(st.get("index", st.get("pos", self.start)))
+        self.end = int(st.get("limit", self.end))
 
     def get_state(self) -> dict[str, Any]:
-        return {"pos": self.pos}
+        return {"files": list(self.files), "index": self.pos, "limit": self.end, "seq_len": int(self.cfg.seq_len),
+                "batch_size": int(self.cfg.batch_size), "rank": self.rank, "world_size": self.world_size}
 
     def next(self) -> dict[str, Any]:
-        extra = 1 if self.cfg.add_one_for_shift else 0
         B, T = int(self.cfg.batch_size), int(self.cfg.seq_len)
-        if self.pos + self.block + extra > self.end:
+        total = int(self.cum[-1])
+        if self.cfg.add_one_for_shift:
+            if self.pos + self.block + 1 > self.end:
+                raise StopIteration
+            rows = [self._read(self.pos + i * T, self.pos + (i + 1) * T + 1) for i in range(B)]
+            self.pos += self.block
+            return {"input_ids": np.stack(rows)}
+        if self.pos + self.block > total:
             raise StopIteration
-        rows = [self._read(self.pos + i * T, self.pos + (i + 1) * T + extra) for i in range(B)]
+        data = self._read(self.pos, self.pos + self.block)
         self.pos += self.block
-        return {"input_ids": np.stack(rows)}
+        if self.pos > self.end:              # the block reached past this rank's span: dropped, the rank is done
+            raise StopIteration
+        return {"input_ids": data.reshape(B, T)}

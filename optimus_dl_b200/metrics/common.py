@@ -50,8 +50,10 @@ class MaxMeter(BaseMeter):
         self.value = value if self.value is None else max(self.value, value)
 
     def compute(self) -> float:
+        """The extreme seen so far; before anything was logged the identity element itself (-inf for the maximum, +inf
+        for the minimum), as optimus_dl/modules/metrics/common.py:121-130 returns it."""
         if self.value is None or self.value == self._EMPTY:
-            return 0.0
+            return self._EMPTY
         return safe_round(self.value, self.round)
 
     def merge(self, other_state: dict[str, Any]) -> None:

@@ -125,10 +125,7 @@ class MetricEngine:
                         logger.exception("metric '%s' in group '%s' failed: %s", mname, g.prefix, e)
                         continue
                     for sub, kwargs in results.items():
-                        base = f"{mname}/{sub}" if mname != sub and mname != f"{sub}_metric" else sub
-                        full = f"{g.prefix}/{base}" if g.prefix else base
-                        if sub.startswith("_"):
-                            full = f"_internal/{full}"
+                        full = self._full_name(g.prefix, mname, sub)
                         acc = metric.accumulators.get(sub)
                         if acc is None:
                             logger.warning("no accumulator for sub-metric '%s' of '%s'; skipped", sub, mname)
@@ -137,12 +134,37 @@ class MetricEngine:
                             raise ValueError(f"Unknown accumulator type: {acc}")
                         log_meter(full, ACCUMULATORS[acc], **kwargs)
 
+    @staticmethod
+    def _full_name(prefix: str, metric_name: str, sub: str) -> str:
+        """``[_internal/][prefix/]metric_name/sub`` (just ``metric_name`` when the two are equal), the naming of
+        optimus_dl/modules/metrics/engine.py:306-318: ``accuracy`` of the ``accuracy`` metric is logged as
+        ``accuracy_metric/accuracy``; sub-metrics whose name starts with ``_`` are internal."""
+        base = f"{metric_name}/{sub}" if metric_name != sub else metric_name
+        full = f"{prefix}/{base}" if prefix else base
+        return f"_internal/{full}" if sub.startswith("_") else full
+
     def compute(self, raw_results: dict[str, Any]) -> dict[str, Any]:
-        out = dict(raw_results)
+        """Finalisation as in optimus_dl/modules/metrics/engine.py:350-404: every metric gets the aggregated values
+        of ITS accumulators keyed by sub-metric name (taken out of ``raw_results``), and what its ``finalize`` returns
+        is reported under the metric's names again; keys starting with ``_`` are dropped. Consumed entries leave
+        ``raw_results`` (the caller's dict), as there."""
+        report: dict[str, Any] = {}
         for g in self.groups:
-            for metric in g.metrics:
+            for i, metric in enumerate(g.metrics):
+                mname = metric.nested_name or (str(metric.cfg.get("_name", i)) + "_metric")
+                acc_data: dict[str, Any] = {}
+                for sub in metric.accumulators:
+                    full = self._full_name(g.prefix, mname, sub)
+                    if full in raw_results:
+                        acc_data[sub] = raw_results.pop(full)
+                if not acc_data:
+                    continue
                 try:
-                    out = metric.finalize(out)
+                    finalized = metric.finalize(acc_data)
                 except Exception as e:
-                    logger.exception("finalize of %s failed: %s", type(metric).__name__, e)
-        return {k: v for k, v in out.items() if not str(k).startswith("_internal/")}
+                    logger.exception("finalize of metric '%s' in group '%s' failed: %s", mname, g.prefix, e)
+                    continue
+                for k, v in finalized.items():
+                    if not str(k).startswith("_"):
+                        report[self._full_name(g.prefix, mname, k)] = v
+        return raw_results | report

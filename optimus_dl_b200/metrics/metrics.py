@@ -38,7 +38,9 @@ class Metric:
         raise NotImplementedError
 
     def finalize(self, aggregated: dict[str, Any]) -> dict[str, Any]:
-        return aggregated
+        """Final values from this metric's aggregated accumulators (sub-metric name -> value); names starting with
+        ``_`` are internal and not reported (optimus_dl/modules/metrics/metrics.py:79-89)."""
+        return {k: v for k, v in aggregated.items() if not str(k).startswith("_")}
 
 
 metric_registry, register_metric, build_metric = make_registry("metric", Metric)

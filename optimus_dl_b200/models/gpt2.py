@@ -179,4 +179,13 @@ def gpt2_124m():
     return GPTConfig(n_layer=12, n_head=12, n_embd=768)
 
 
-MLP = GELUMLP   # the reference keeps GPT-2's feed-forward block under this name in this module
+class MLP(GELUMLP):
+    """GPT-2's feed-forward block under the name and with the constructor of the reference
+    (optimus_dl/modules/model/gpt2.py:81-96): built from a config with ``n_embd``, ``bias`` and ``dropout``; the
+    ``gelu`` and ``dropout`` sub-modules always exist."""
+
+    def __init__(self, config):
+        super().__init__(config.n_embd, 4 * config.n_embd, bias=config.bias, dropout=config.dropout)
+        self.gelu = nn.GELU()
+        if self.dropout is None:
+            self.dropout = nn.Dropout(config.dropout)

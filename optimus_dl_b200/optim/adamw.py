@@ -104,6 +104,8 @@ def make_adamw(cfg, params, **_):
         return ShardedAdamW(groups, engine, lr=cfg.lr, betas=tuple(cfg.betas), eps=cfg.eps, weight_decay=cfg.weight_decay)
     if flat and all(p.is_cuda for p in flat):
         return FusedAdamW(groups, lr=cfg.lr, betas=tuple(cfg.betas), eps=cfg.eps, weight_decay=cfg.weight_decay)
+    # parameters that are not all on the GPU: the library optimizer with the config's own flags
+    # (optimus_dl/modules/optim/adamw.py:42-57)
     return torch.optim.AdamW(groups, lr=cfg.lr, betas=tuple(cfg.betas), eps=cfg.eps, weight_decay=cfg.weight_decay,
                              amsgrad=cfg.amsgrad, maximize=cfg.maximize, foreach=cfg.foreach,
-                             capturable=cfg.capturable, differentiable=cfg.differentiable, fused=False)
+                             capturable=cfg.capturable, differentiable=cfg.differentiable, fused=cfg.fused)

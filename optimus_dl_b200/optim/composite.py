@@ -155,10 +155,10 @@ def make_composite_optimizer(cfg: Any, params: Any, **kwargs: Any) -> CompositeO
             raise ValueError(f"Optimizer '{name}' with regex '{rx}' did not match any parameters.")
         for n, t in _iter_named(sub):
             if id(t) in claimed:
-                raise ValueError(f"Parameter '{n}' is matched by more than one optimizer (second match: '{name}').")
+                raise ValueError(f"Parameter '{n}' matched by multiple optimizers (currently matched by '{name}').")
             claimed.add(id(t))
         built[name] = build_optimizer(optimizer_config_of(entry), params=sub, **kwargs)
     missing = [n for i, n in names.items() if i not in claimed]
     if missing:
-        raise ValueError(f"Parameters not matched by any optimizer: {missing[:8]}{' ...' if len(missing) > 8 else ''}")
+        raise ValueError(f"The following parameters were not matched by any optimizer regex: {missing}")
     return CompositeOptimizer(built)

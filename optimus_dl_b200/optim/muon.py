@@ -125,7 +125,7 @@ def make_muon(cfg: Any, params: Any, **kwargs: Any):
         raise ValueError("Muon optimizer requires at least one 2D parameter (matrix).")
     muon = Muon(matrices, lr=float(cfg.lr), weight_decay=float(cfg.weight_decay), momentum=float(cfg.momentum),
                 nesterov=bool(cfg.nesterov), ns_coefficients=tuple(cfg.ns_coefficients), eps=float(cfg.eps),
-                ns_steps=int(cfg.ns_steps), adjust_lr_fn=cfg.get("adjust_lr_fn"))
+                ns_steps=int(cfg.ns_steps), adjust_lr_fn=getattr(cfg, "adjust_lr_fn", None))
     if not others:
         return muon
     support = build_optimizer(cfg.support_optimizer, params=others, **kwargs)

@@ -84,7 +84,7 @@ def test_registry_strict_flexible_and_casting():
             self.cfg, self.extra = cfg, extra
 
     t = build({"_name": "thing", "lr": "3e-4", "inner": {"n": "4"}, "opt": None, "mode": 3}, extra=5)
-    assert t.cfg.lr == pytest.approx(3e-4) and t.cfg.inner.n == 4 and t.cfg.betas == [0.9, 0.999] and t.cfg.mode == 3
+    assert t.cfg.lr == pytest.approx(3e-4) and t.cfg.inner.n == 4 and t.cfg.betas == [0.9, 0.999] and t.cfg.mode == "3"   # first castable member of str | int
     assert t.extra == 5 and build("thing").cfg.lr == 1e-3
     with pytest.raises(ConfigValidationError):
         build({"_name": "thing", "unknown": 1})

@@ -145,14 +145,19 @@ def test_composite_weights_stop_criteria_and_strict_load():
     ds.reset()
     lens = [len(next(ds)["input_ids"]) for _ in range(400)]
     assert 0.15 < lens.count(4) / 400 < 0.35
-    ds = build_dataset(cfg("FIRST_DATASET_EXHAUSTED"), rank=0, world_size=1, seed=4)
+    # a dataset that cycles never counts as exhausted (optimus_dl/modules/data/datasets/composite.py:365-372), so
+    # "first exhausted" needs a dataset that does not cycle
+    ds = build_dataset(cfg("FIRST_DATASET_EXHAUSTED", cycle=False), rank=0, world_size=1, seed=4)
     ds.reset()
     n = 0
     with pytest.raises(StopIteration):
-        while True:
+        while n < 1000:
             next(ds)
             n += 1
     assert n < 100
+    ds = build_dataset(cfg("FIRST_DATASET_EXHAUSTED"), rank=0, world_size=1, seed=4)
+    ds.reset()
+    assert sum(1 for _ in range(500) if next(ds) is not None) == 500        # both cycle: the stream does not end
     ds = build_dataset(cfg("ALL_DATASETS_EXHAUSTED", cycle=False), rank=0, world_size=1, seed=4)
     ds.reset()
     n = sum(1 for _ in iter(lambda: _next_or_none(ds), None))

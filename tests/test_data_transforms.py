@@ -276,7 +276,8 @@ def test_tokenized_flat_streams_files_as_one_sequence_with_equal_spans_per_rank(
     a, b = tmp_path / "a.bin", tmp_path / "b.npy"
     np.arange(0, 50, dtype=np.uint16).tofile(a)
     np.save(b, np.arange(50, 120, dtype=np.uint16))
-    cfg = {"_name": "tokenized_flat", "files": [str(a), str(b)], "dtype": "uint16", "batch_size": 2, "seq_len": 8}
+    cfg = {"_name": "tokenized_flat", "files": [str(a), str(b)], "dtype": "uint16", "batch_size": 2, "seq_len": 8,
+           "add_one_for_shift": True}
     whole = build_dataset(cfg)
     whole.reset()
     batches = _drain(whole)
@@ -294,9 +295,24 @@ def test_tokenized_flat_streams_files_as_one_sequence_with_equal_spans_per_rank(
     assert starts == [0, 60] and len(halves[0]) == len(halves[1])   # ranks read disjoint, equally long spans
     straight, resumed = _resume_equals_straight(lambda: build_dataset(cfg), 2, 5)
     assert _same(straight, resumed)
-    no_shift = build_dataset({**cfg, "add_one_for_shift": False})
+    # the reference's form (the default): (batch, seq_len) blocks in the files' dtype; 5 ranks over 104 tokens read
+    # 20 tokens each, and together exactly the first 100 (optimus_dl tests/data/test_tokenized_flat_dataset.py)
+    ref_cfg = {k: v for k, v in cfg.items() if k != "add_one_for_shift"}
+    no_shift = build_dataset(ref_cfg)
     no_shift.reset()
-    assert np.asarray(next(no_shift)["input_ids"]).shape == (2, 8)
+    blk = np.asarray(next(no_shift)["input_ids"])
+    assert blk.shape == (2, 8) and blk.dtype == np.uint16
+    assert set(no_shift.state_dict()) >= {"files", "index", "limit", "seq_len", "batch_size", "rank", "world_size"}
+    c, d2 = tmp_path / "c.u8", tmp_path / "d.u8"
+    np.arange(0, 77, dtype=np.uint8).tofile(c)
+    np.arange(77, 104, dtype=np.uint8).tofile(d2)
+    got = []
+    for rank in range(5):
+        ds5 = build_dataset({"_name": "tokenized_flat", "files": [str(c), str(d2)], "dtype": "np.uint8", "batch_size": 1,
+                             "seq_len": 5}, rank=rank, world_size=5)
+        ds5.reset()
+        got += [np.asarray(x["input_ids"]).reshape(-1) for x in _drain(ds5)]
+    assert np.concatenate(got).tolist() == list(range(100))
     glob_cfg = {**cfg, "files": str(tmp_path / "*.bin")}
     g = build_dataset(glob_cfg)
     g.reset()

@@ -31,7 +31,7 @@ def test_summed_max_min_meters():
         s.log(v)
     assert s.compute() == 6.5
     hi, lo = mc.MaxMeter(), mc.MinMeter()
-    assert hi.compute() == 0.0 and lo.compute() == 0.0
+    assert hi.compute() == -float("inf") and lo.compute() == float("inf")     # nothing logged: the identity elements
     for v in (3, -1, 7):
         hi.log(v)
         lo.log(v)
@@ -84,7 +84,7 @@ def test_stopwatch_and_frequency_meters_measure_milliseconds():
     a.merge(b.state_dict())
     assert (a.elapsed, a.counter, a.compute()) == (3_000_000, 3, 1.0)
     assert mc.MaxMeter(round=2).value == -float("inf") and mc.MinMeter().value == float("inf")
-    assert mc.MaxMeter().compute() == 0.0         # nothing logged yet
+    assert mc.MaxMeter().compute() == -float("inf")         # nothing logged yet
 
 
 def test_gather_meter_collects_and_merges():

@@ -50,12 +50,8 @@ class _Ratio(Metric):
     def __call__(self, data):
         return {"_num": {"value": float(data["loss"])}, "_den": {"value": 2.0}}
 
-    def finalize(self, agg):
-        num = [k for k in agg if k.endswith("_num")]
-        out = dict(agg)
-        for k in num:
-            out[k.replace("_internal/", "").replace("/_num", "/ratio").replace("_num", "ratio")] = agg[k] / agg[k.replace("_num", "_den")]
-        return out
+    def finalize(self, agg):           # this metric's own accumulators, keyed by sub-metric name
+        return {"ratio": agg["_num"] / agg["_den"]}
 
 
 def _register():
@@ -91,7 +87,7 @@ def test_equal_configs_share_one_evaluation_and_different_configs_do_not():
     e.update({})
     assert CALLS["loss"] == 2                       # value 2.0 once (shared by a and b), value 5.0 once
     out = e.compute(mb.compute_meters("g"))
-    assert out["a/loss"] == 2.0 and out["b/loss"] == 2.0 and out["c/loss"] == 5.0
+    assert out["a/loss_metric/loss"] == 2.0 and out["b/loss_metric/loss"] == 2.0 and out["c/loss_metric/loss"] == 5.0
     e.update({})                                    # the cache lives for one batch only
     assert CALLS["loss"] == 4
     hashes = {g.sources[r].config_hash for g in e.groups for r in g.sources}
@@ -104,7 +100,7 @@ def test_sources_may_depend_on_other_sources_of_their_group():
         "top": _src(value=1.0, provide="loss", need=["hidden"]),
     }, "metrics": [{"_name": "loss"}]}])
     e.update({})
-    assert e.compute(mb.compute_meters("g"))["loss"] == 4.0 and CALLS == {"hidden": 1, "loss": 1}
+    assert e.compute(mb.compute_meters("g"))["loss_metric/loss"] == 4.0 and CALLS == {"hidden": 1, "loss": 1}
 
 
 def test_cycles_and_missing_protocols_are_reported_without_stopping_other_metrics(caplog):
@@ -121,7 +117,7 @@ def test_cycles_and_missing_protocols_are_reported_without_stopping_other_metric
     with caplog.at_level("ERROR"):
         e.update({})
     out = e.compute(mb.compute_meters("g"))
-    assert out == {k: v for k, v in out.items() if k.startswith("ok/") or k == "ms_spent_logging"} and out["ok/loss"] == 7.0
+    assert out == {k: v for k, v in out.items() if k.startswith("ok/") or k == "ms_spent_logging"} and out["ok/loss_metric/loss"] == 7.0
     text = caplog.text
     assert "Cyclic dependency" in text and "nowhere" in text and "source failed" in text
     assert CALLS.get("loss", 0) == 2                # the failing source ran once; its error was cached for the second metric
@@ -138,9 +134,9 @@ def test_external_protocols_are_taken_from_the_criterion_and_override_sources():
     e.update({}, given)
     out = e.compute(mb.compute_meters("g"))
     nll = torch.nn.functional.cross_entropy(logits[0], targets[0])
-    assert out["perplexity"] == pytest.approx(math.exp(nll.item()), rel=1e-5)
-    assert out["accuracy"] == 0.5
-    assert out["s/loss"] == 42.0 and "loss" not in CALLS      # a value the caller already has is not recomputed
+    assert out["perplexity_metric/perplexity"] == pytest.approx(math.exp(nll.item()), rel=1e-5)
+    assert out["accuracy_metric/accuracy"] == 0.5        # named as optimus_dl/modules/metrics/engine.py:306-318 names it
+    assert out["s/loss_metric/loss"] == 42.0 and "loss" not in CALLS      # a value the caller already has is not recomputed
 
 
 def test_nested_names_internal_submetrics_and_finalisers():
@@ -151,7 +147,7 @@ def test_nested_names_internal_submetrics_and_finalisers():
     raw = mb.compute_meters("g")
     assert raw["_internal/p/r/_num"] == 12.0 and raw["_internal/p/r/_den"] == 4.0
     out = e.compute(raw)
-    assert out["p/r/ratio"] == 3.0 and out["p/loss"] == 6.0
+    assert out["p/r/ratio"] == 3.0 and out["p/loss_metric/loss"] == 6.0
     assert not [k for k in out if k.startswith("_internal/")]
 
 

@@ -45,7 +45,7 @@ class Flexible(RegistryConfig):
 @pytest.mark.parametrize("tp,value,want", [
     (int, "7", 7), (int, 7.0, 7), (float, 3, 3.0), (float, "1e-3", 1e-3), (str, 5, "5"), (str, True, "True"),
     (bool, "yes", True), (bool, "off", False), (bool, 1, True), (bool, 0, False),
-    (int | None, None, None), (int | None, "4", 4), (float | str, "fast", "fast"), (int | str, 3, 3), (int | str, "3", "3"),
+    (int | None, None, None), (int | None, "4", 4), (float | str, "fast", "fast"), (int | str, 3, 3), (int | str, "3", 3), (str | int, 3, "3"),
     (list[int], ("1", 2.0), [1, 2]), (list, [1, "a"], [1, "a"]), (tuple[float, float], [1, "2"], [1.0, 2.0]),
     (tuple[int, ...], ["1", 2, 3.0], [1, 2, 3]), (dict[str, float], {"a": "1.5"}, {"a": 1.5}),
     (Color, "blue", Color.BLUE), (Color, "RED", Color.RED), (Color, Color.BLUE, Color.BLUE),

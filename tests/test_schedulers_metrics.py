@@ -103,4 +103,5 @@ def test_metric_engine_protocols_sources_and_caching():
     e.update({}, {"classification": {"predictions": pred, "targets": torch.tensor([[1, 0, 3]]), "mask": torch.ones(1, 3, dtype=torch.bool)}})
     assert counter["n"] == 1        # identical sources are evaluated once per batch across groups
     out = e.compute(compute_meters("eng"))
-    assert out["a/loss"] == 2.0 and out["b/loss"] == 2.0 and out["accuracy"] == pytest.approx(2 / 3)
+    assert out["a/loss_metric/loss"] == 2.0 and out["b/loss_metric/loss"] == 2.0
+    assert out["accuracy_metric/accuracy"] == pytest.approx(2 / 3)
