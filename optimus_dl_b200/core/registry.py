@@ -38,6 +38,11 @@ class RegistryConfigStrict:
 
     _name: str | None = None
 
+    def get(self, key: str, default: Any = None) -> Any:
+        """Mapping-style read of a declared field, so that a component built directly from a config INSTANCE (not
+        through its registry, which hands over a config node) can use the same ``cfg.get(...)`` calls."""
+        return getattr(self, key) if key in getattr(self, "__dataclass_fields__", {}) else default
+
 
 @dataclass
 class RegistryConfig(dict):
@@ -47,6 +52,12 @@ class RegistryConfig(dict):
 
     def __post_init__(self) -> None:
         pass
+
+    def get(self, key: str, default: Any = None) -> Any:
+        """Extra keys first (mapping items), then declared fields, then ``default``."""
+        if dict.__contains__(self, key):
+            return dict.__getitem__(self, key)
+        return getattr(self, key) if key in getattr(self, "__dataclass_fields__", {}) else default
 
 
 class ConfigValidationError(ValueError, TypeError):

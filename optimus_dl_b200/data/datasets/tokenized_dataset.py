@@ -46,9 +46,16 @@ class TokenizedDataset(BaseDataset):
             lens.append(np.asarray(l, dtype=np.int64))
             self.shard_doc_start.append(self.shard_doc_start[-1] + len(l))
         self.doc_lens = np.concatenate(lens) if lens else np.zeros(0, dtype=np.int64)
-        limit = cfg.get("limit") if cfg.get("limit") is not None else cfg.limit_documents
+        self.shard_num_docs = [len(l) for l in lens]
+        limit = cfg.get("limit") if cfg.get("limit") is not None else cfg.get("limit_documents")
         if limit is not None:
             self.doc_lens = self.doc_lens[: int(limit)]
+        self.total_docs = len(self.doc_lens)
+        # tokens come back in the dtype the shards were written with (index.json: config.dtype; "np.uint16" and
+        # "uint16" both name the type), batchers widen to int64
+        name = str((self.index.get("config") or {}).get("dtype", "")) if isinstance(self.index, dict) else ""
+        name = name[3:] if name.startswith("np.") else name
+        self.dtype = np.dtype(name) if name else None
         self.shard_tok_start = [np.concatenate([[0], np.cumsum(l)]) for l in lens]
         self.strategy = build_strategy(cfg.strategy, rank=rank, world_size=world_size, seed=seed)
         self.strategy.global_seed = seed
@@ -65,7 +72,14 @@ class TokenizedDataset(BaseDataset):
         s = int(np.searchsorted(self.shard_doc_start, doc, side="right") - 1)
         local = doc - self.shard_doc_start[s]
         base = int(self.shard_tok_start[s][local])
-        return np.asarray(self._shard_tokens(s)[base + start: base + end], dtype=np.int64)
+        toks = self._shard_tokens(s)
+        if base + end > len(toks):
+            raise RuntimeError(f"Data corruption: lens file does not match token file (shard {s}: document {local} ends "
+                               f"at token {base + end}, the shard has {len(toks)}).")
+        out = np.asarray(toks[base + start: base + end])
+        if self.dtype is None:
+            self.dtype = out.dtype
+        return out if out.dtype == self.dtype else out.astype(self.dtype)
 
     def reset(self, initial_state: dict | None = None):
         super().reset(initial_state)

@@ -31,6 +31,9 @@ def _to_tensor(batch: Any) -> Any:
     if isinstance(batch, dict):
         return {k: _to_tensor(v) for k, v in batch.items()}
     if isinstance(batch, np.ndarray):
+        if batch.dtype in (np.uint16, np.uint32, np.uint64):
+            # token files are stored unsigned; index-taking ops (embedding, gather) want signed 64-bit
+            batch = batch.astype(np.int64)
         return torch.from_numpy(np.ascontiguousarray(batch))
     return batch
 

@@ -39,13 +39,25 @@ class GPTConfig(ModelConfig):
     padding_token_id: int | None = None
 
 
+class MLP(GELUMLP):
+    """GPT-2's feed-forward block under the name and with the constructor of the reference
+    (optimus_dl/modules/model/gpt2.py:81-96): built from a config with ``n_embd``, ``bias`` and ``dropout``; the
+    ``gelu`` and ``dropout`` sub-modules always exist."""
+
+    def __init__(self, config):
+        super().__init__(config.n_embd, 4 * config.n_embd, bias=config.bias, dropout=config.dropout)
+        self.gelu = nn.GELU()
+        if self.dropout is None:
+            self.dropout = nn.Dropout(config.dropout)
+
+
 class Block(nn.Module):
     def __init__(self, config):
         super().__init__()
         self.ln_1 = LayerNorm(config.n_embd, bias=config.bias)
         self.attn = CausalSelfAttention(config)
         self.ln_2 = LayerNorm(config.n_embd, bias=config.bias)
-        self.mlp = GELUMLP(config.n_embd, 4 * config.n_embd, bias=config.bias, dropout=config.dropout)
+        self.mlp = MLP(config)
 
     def forward(self, x, **kw):
         x = x + self.attn(self.ln_1(x), **kw)
@@ -177,15 +189,3 @@ class GPT(BaseModel):
 @GPT.register_arch("124m")
 def gpt2_124m():
     return GPTConfig(n_layer=12, n_head=12, n_embd=768)
-
-
-class MLP(GELUMLP):
-    """GPT-2's feed-forward block under the name and with the constructor of the reference
-    (optimus_dl/modules/model/gpt2.py:81-96): built from a config with ``n_embd``, ``bias`` and ``dropout``; the
-    ``gelu`` and ``dropout`` sub-modules always exist."""
-
-    def __init__(self, config):
-        super().__init__(config.n_embd, 4 * config.n_embd, bias=config.bias, dropout=config.dropout)
-        self.gelu = nn.GELU()
-        if self.dropout is None:
-            self.dropout = nn.Dropout(config.dropout)

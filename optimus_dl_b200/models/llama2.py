@@ -59,6 +59,7 @@ class Llama(GPT):
             for name, p in self.named_parameters():
                 if name.endswith("c_proj.weight") or name.endswith("wo.weight"):
                     nn.init.zeros_(p)
+        self.head_dim = self._head_dim(config)
         self.freqs_cis = self._make_freqs(config)
 
     def _head_dim(self, config) -> int:

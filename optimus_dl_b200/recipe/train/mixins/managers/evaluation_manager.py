@@ -21,7 +21,7 @@ from .....core.profile import measured_next
 from .....core.registry import RegistryConfig, make_registry
 from .....metrics import MetricEngine
 from .....metrics.base import compute_meters, meters_group, step_meters
-from .....metrics.common import log_averaged, log_event_end, log_event_start
+from .....metrics.common import log_averaged, log_event_end, log_event_start, log_summed
 
 logger = logging.getLogger(__name__)
 
@@ -34,12 +34,27 @@ class EvaluatorConfig(RegistryConfig):
 class Evaluator:
     def __init__(self, cfg: Any = None, eval_freq: int = 0, eval_iterations: int | None = None,
                  eval_guaranteed_same_batches: bool = False, eval_checkpointing: int | None = None,
-                 metrics_config: Any = None, eval_checkpoint_manager: Any = None, **kwargs: Any):
+                 metrics_config: Any = None, eval_checkpoint_manager: Any = None, output_path: Any = None,
+                 **kwargs: Any):
         self.cfg = cfg
         self.eval_freq, self.eval_iterations = eval_freq, eval_iterations
         self.same_batches, self.eval_checkpointing = eval_guaranteed_same_batches, eval_checkpointing
         self.metrics_config = metrics_config or {}
+        self.output_path = output_path
+        if eval_checkpoint_manager is None and output_path is not None:
+            from .....checkpoint.eval_checkpoint_manager import EvaluationCheckpointManager
+            eval_checkpoint_manager = EvaluationCheckpointManager(output_path)
         self.eval_ckpt = eval_checkpoint_manager
+
+    @property
+    def eval_checkpoint_manager(self) -> Any:
+        """The manager of mid-evaluation state (attribute name of
+        optimus_dl/recipe/train/mixins/managers/evaluation_manager.py:96-99); settable."""
+        return self.eval_ckpt
+
+    @eval_checkpoint_manager.setter
+    def eval_checkpoint_manager(self, manager: Any) -> None:
+        self.eval_ckpt = manager
 
     def should_evaluate(self, iteration: int, pipeline: Any = None) -> bool:
         freq = (pipeline.eval_freq if pipeline is not None and pipeline.eval_freq is not None else self.eval_freq)
@@ -74,25 +89,52 @@ class Evaluator:
         return training_context["amp_ctx"]()
 
     @torch.no_grad()
-    def run_evaluation(self, model: torch.nn.Module, criterion: Any, eval_data: dict[str, Any], iteration: int,
-                       collective: Any = None, training_context: dict[str, Any] | None = None, prefix: str = "eval",
-                       force: bool = False) -> dict[str, dict[str, Any]]:
+    def run_evaluation(self, model: torch.nn.Module, criterion: Any, eval_data_dict: dict[str, Any] | None = None,
+                       device: Any = None, max_iterations: int | None = None, collective: Any = None,
+                       all_metrics_configs: Any = None, metrics_prefix: str = "eval", show_progress: bool = False,
+                       iteration: int | None = None, *, training_context: dict[str, Any] | None = None,
+                       force: bool = False, prefix: str | None = None, eval_data: dict[str, Any] | None = None,
+                       ) -> dict[str, dict[str, Any]]:
+        """Evaluate the given datasets; ``{"<prefix>/<name>": metrics}``.
+
+        Arguments up to ``iteration`` are those of optimus_dl/recipe/train/mixins/managers/evaluation_manager.py:
+        246-258, in that order (``max_iterations`` caps datasets that set no ``eval_iterations`` of their own;
+        ``all_metrics_configs`` replaces the evaluator's metric configs for this call). With ``iteration`` given and
+        ``force`` false, datasets whose frequency does not divide it are skipped; without ``iteration`` everything
+        given is evaluated, as there. The keyword-only arguments are this package's (``prefix`` / ``eval_data`` are
+        earlier spellings of ``metrics_prefix`` / ``eval_data_dict``).
+        """
+        data = eval_data_dict if eval_data_dict is not None else (eval_data or {})
+        if isinstance(device, int) and not isinstance(device, bool) and iteration is None:
+            iteration, device = device, None      # earlier positional form: (model, criterion, data, iteration)
+        if prefix is not None:
+            metrics_prefix = prefix
+        ckpt_iteration = iteration            # None: no mid-evaluation state is read or written
+        if iteration is None:
+            iteration, force = 0, True
+        saved_cfg, saved_iters = self.metrics_config, self.eval_iterations
+        if all_metrics_configs is not None:
+            self.metrics_config = all_metrics_configs
+        if max_iterations is not None:
+            self.eval_iterations = max_iterations if max_iterations >= 0 else None
         was_training = model.training
         model.eval()
         results: dict[str, dict[str, Any]] = {}
-        device = training_context["device"] if training_context else next(model.parameters()).device
+        if device is None:
+            device = training_context["device"] if training_context else next(model.parameters()).device
         try:
-            for name in sorted(eval_data):
-                pipe = eval_data[name]
-                if not force and not self.should_evaluate(iteration, pipe):
+            for name in sorted(data):
+                pipe = data[name]
+                if pipe is None or (not force and not self.should_evaluate(iteration, pipe)):
                     continue
-                results[f"{prefix}/{name}"] = self._evaluate_one(model, criterion, name, pipe, iteration, collective,
-                                                                 training_context, device, prefix)
+                results[f"{metrics_prefix}/{name}"] = self._evaluate_one(model, criterion, name, pipe, ckpt_iteration, collective,
+                                                                         training_context, device, metrics_prefix)
         finally:
             model.train(was_training)
+            self.metrics_config, self.eval_iterations = saved_cfg, saved_iters
         return results
 
-    def _evaluate_one(self, model, criterion, name, pipe, iteration, collective, ctx, device, prefix) -> dict[str, Any]:
+    def _evaluate_one(self, model, criterion, name, pipe, ckpt_iteration, collective, ctx, device, prefix) -> dict[str, Any]:
         group = f"{prefix}/{name}"
         cfgs = self.metrics_config.get(name) if hasattr(self.metrics_config, "get") else None
         engine = MetricEngine(group, cfgs) if cfgs else None
@@ -103,15 +145,17 @@ class Evaluator:
         with meters_group(group, log_freq=1, force_recreate=True):
             t_start = time.perf_counter()
             log_event_start("perf/total_run")
-            data_iter = iter(pipe.dataloader)
+            loader = getattr(pipe, "dataloader", pipe)
+            restorable = loader if hasattr(loader, "load_state_dict") else None
+            data_iter = iter(loader)
             processed = 0
-            if self.eval_ckpt is not None and ckpt_every:
-                st = self.eval_ckpt.load_iteration_state(iteration, name, group)
-                if st is not None:
-                    processed = int(st.get("eval_iterations_processed", 0))
-                    if st.get("dataloader") is not None and hasattr(pipe.dataloader, "load_state_dict"):
-                        pipe.dataloader.load_state_dict(st["dataloader"])
-                        data_iter = iter(pipe.dataloader)
+            if self.eval_ckpt is not None and ckpt_iteration is not None:
+                processed = self.eval_ckpt.load_iteration_state(
+                    ckpt_iteration, name, group, eval_iter=restorable if restorable is not None else data_iter,
+                    collective=collective)
+                if processed:
+                    if restorable is not None:
+                        data_iter = iter(loader)
                     logger.info("resuming evaluation %s at batch %d", name, processed)
             requested = engine.required_external_protocols if engine is not None else None
             while max_iters is None or processed < max_iters:
@@ -132,11 +176,14 @@ class Evaluator:
                 if engine is not None:
                     engine.update(dict(model=model, batch=batch), exposed)
                 log_event_end("perf/full_iteration")
+                log_summed("num_batches", lambda: 1)
                 step_meters(group)
                 processed += 1
                 if self.eval_ckpt is not None and ckpt_every and processed % int(ckpt_every) == 0:
-                    dl_state = pipe.dataloader.state_dict() if hasattr(pipe.dataloader, "state_dict") else None
-                    self.eval_ckpt.save_iteration_state(iteration, name, group, dl_state, processed)
+                    assert ckpt_iteration is not None, "Iteration must be provided for checkpointing"
+                    src = loader if hasattr(loader, "state_dict") else data_iter
+                    self.eval_ckpt.save_iteration_state(ckpt_iteration, name, src.state_dict(), group, collective=collective,
+                                                        eval_iterations_processed=processed)
             log_event_end("perf/total_run")
             total_ms = (time.perf_counter() - t_start) * 1e3
             log_averaged("perf/total_run_ms", total_ms, round=1)

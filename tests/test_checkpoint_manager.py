@@ -185,10 +185,15 @@ def test_checkpoint_path_helpers_and_eval_state_cleanup(tmp_path):
     assert cp.is_dcp_checkpoint() and cp.per_rank_metadata(0) == str(tmp_path / "per_rank_metadata_0_000000004.pt")
     assert os.path.exists(cp.per_rank_metadata(0)) and cp.per_rank_metadata(3).endswith("per_rank_metadata_3_000000004.pt")
     ev = EvaluationCheckpointManager(str(tmp_path), rank=0)
+    from optimus_dl_b200.metrics.base import meters_group
+    from optimus_dl_b200.metrics.common import log_summed
+    with meters_group("eval/tiny", log_freq=1, force_recreate=True):
+        log_summed("num_batches", lambda: 2)
     for it in (10, 20, 30):
-        ev.save_iteration_state(it, "tiny", "eval/tiny", {"pos": it}, processed=2)
+        ev.save_iteration_state(it, "tiny", {"pos": it}, "eval/tiny", eval_iterations_processed=2)
     assert ev.get_eval_checkpoints_dir(20).name == "eval_checkpoints_iter_20" and ev.get_eval_checkpoints_dir(20).is_dir()
-    assert ev.load_iteration_state(20, "tiny", "eval/tiny")["dataloader"] == {"pos": 20}
+    assert ev.read_iteration_state(20, "tiny")["dataloader_state"] == {"pos": 20}
+    assert ev.load_iteration_state(20, "tiny", "eval/tiny") == 2
     ev.cleanup(iteration=10)
     assert not ev.get_eval_checkpoints_dir(10).exists() and ev.get_eval_checkpoints_dir(20).exists()
     ev.cleanup(exclude_iteration=30)

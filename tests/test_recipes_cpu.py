@@ -27,7 +27,8 @@ def test_metrics_recipe(tmp_path):
     results = recipe.run()
     assert list(results) == ["metrics/synth"]
     vals = results["metrics/synth"]
-    assert 4.0 < vals["loss"] < 7.0 and "lm/accuracy" in vals and "lm/perplexity" in vals
+    # metric names as the reference forms them: <prefix>/<name>_metric/<sub-metric>
+    assert 4.0 < vals["loss"] < 7.0 and "lm/accuracy_metric/accuracy" in vals and "lm/perplexity_metric/perplexity" in vals
     assert any((tmp_path / "logs").rglob("*.jsonl"))
 
 
