@@ -43,6 +43,10 @@ class InterpolationError(ConfigError):
     pass
 
 
+class CircularDependencyError(InterpolationError, ValueError):
+    """Two lazily instantiated ``_target_`` blocks need each other."""
+
+
 _RESOLVERS: dict[str, tuple[Callable[..., Any], bool, bool]] = {}
 
 
@@ -90,7 +94,7 @@ class LazyTarget:
 
     def get(self) -> Any:
         if self._busy:
-            raise InterpolationError(f"circular dependency while instantiating '{self.definition._full_key()}'")
+            raise CircularDependencyError(f"Circular dependency detected while instantiating '{self.definition._full_key()}'")
         self._busy = True
         try:
             plain = to_container(self.definition, resolve=True)
@@ -501,7 +505,12 @@ def select_relative(container: Node, path: str, *, origin_key: Any = None, throw
                     if throw:
                         raise InterpolationError(f"key {tok!r} not found while resolving {path!r} (at '{container._full_key()}')")
                     return default
-            node = _resolve_value(node._data[key], node, key, _stack) if (resolve or i < len(tokens) - 1) else node._data[key]
+            raw = node._data[key]
+            if isinstance(raw, LazyTarget) and raw._busy and i < len(tokens) - 1:
+                # a ``_target_`` block naming one of its own parameters by absolute path: read the definition
+                node = raw.definition
+            else:
+                node = _resolve_value(raw, node, key, _stack) if (resolve or i < len(tokens) - 1) else raw
         elif isinstance(node, ListNode):
             try:
                 idx = int(tok)

@@ -60,9 +60,10 @@ class RegistryConfig(dict):
         return getattr(self, key) if key in getattr(self, "__dataclass_fields__", {}) else default
 
 
-class ConfigValidationError(ValueError, TypeError):
-    """A config does not fit its dataclass: unknown key (the reference raises ValueError there) or a value that
-    cannot be cast (TypeError there); both ``except`` forms catch this class."""
+class ConfigValidationError(ValueError, TypeError, AssertionError):
+    """A config does not fit its dataclass: unknown key (the reference raises ValueError there, AssertionError
+    when the key is met inside ``build``) or a value that cannot be cast (TypeError there); each of these
+    ``except`` forms catches this class."""
 
 
 def _is_registry_cfg(cls: Any) -> bool:

@@ -17,6 +17,16 @@ class HuggingFaceDatasetConfig(RegistryConfigStrict):
     dataset_load_kwargs: dict = "???"  # type: ignore[assignment]
 
 
+def __getattr__(name: str) -> Any:
+    """``load_dataset`` is a module-level name (callers can substitute it) that imports the optional and
+    slow-to-import ``datasets`` package on first use only."""
+    if name == "load_dataset":
+        from datasets import load_dataset
+
+        return load_dataset
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+
+
 @register_dataset("huggingface_dataset", HuggingFaceDatasetConfig)
 class HuggingFaceDataset(BaseDataset):
     def __init__(self, cfg, rank: int = 0, world_size: int = 1, **kwargs: Any):
@@ -26,13 +36,13 @@ class HuggingFaceDataset(BaseDataset):
         self._ds = None
 
     def _open(self):
-        import datasets
-        from datasets.distributed import split_dataset_by_node
-
+        load_dataset = globals().get("load_dataset") or __getattr__("load_dataset")
         kw = dict(self.cfg.dataset_load_kwargs)
         kw.setdefault("streaming", True)
-        ds = datasets.load_dataset(**kw)
+        ds = load_dataset(**kw)
         if self.world_size > 1:
+            from datasets.distributed import split_dataset_by_node
+
             ds = split_dataset_by_node(ds, rank=self.rank, world_size=self.world_size)
         return ds
 

@@ -10,6 +10,7 @@ from typing import Any
 from torchdata.nodes import BaseNode, Mapper, ParallelMapper
 
 from ...core.registry import RegistryConfig
+from ...tokenizer import build_tokenizer       # module-level so that callers can substitute the factory
 from . import register_transform
 from .base import BaseTransform, MapperConfig
 
@@ -36,8 +37,6 @@ class _Tokenize:
 
     def __call__(self, item: dict) -> dict:
         if self._tok is None:
-            from ...tokenizer import build_tokenizer
-
             self._tok = build_tokenizer(self.tok_cfg)
         out = dict(item) if self.keep else {k: v for k, v in item.items() if k != self.in_f}
         out[self.out_f] = self._tok.encode(item[self.in_f])

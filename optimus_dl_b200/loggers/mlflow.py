@@ -5,6 +5,7 @@ deferred; a missing package disables the logger with a warning."""
 
 from __future__ import annotations
 
+import importlib.util
 import json
 import logging
 import os
@@ -19,6 +20,9 @@ from .base import BaseMetricsLogger, RunStatus, flatten_metrics
 from .config import MetricsLoggerConfig
 
 logger = logging.getLogger(__name__)
+# whether the package can be imported at all (name of optimus_dl/modules/loggers/mlflow.py:28-34); the import
+# itself still waits for ``setup``
+MLFLOW_AVAILABLE = importlib.util.find_spec("mlflow") is not None
 MAX_PARAM_LEN = 500
 MAX_PARAMS_PER_CALL = 100
 
@@ -79,6 +83,9 @@ class MlflowLogger(BaseMetricsLogger):
         self.run_id = (state_dict or {}).get("run_id")
         self._mlflow = None
         self._active = False
+        if self.enabled and not MLFLOW_AVAILABLE:
+            logger.warning("mlflow is not installed; the mlflow logger is disabled")
+            self.enabled = False
 
     def setup(self, experiment_name: str, config: dict[str, Any], logs_parent_path: str | None = None,
               start_iteration: int | None = None) -> None:

@@ -177,6 +177,14 @@ def compute_meters(name: str, aggregate: bool = False, collective: Any = None) -
     merged: "OrderedDict[str, MeterEntry]" = OrderedDict()
     for rank_states in all_states:
         for k, sd in rank_states.items():
+            if "meter_class" not in sd:
+                # a bare meter state (what optimus_dl/modules/metrics/base.py:519-523 gathers): the class and
+                # the priority are those of this rank's meter of the same name
+                local = g.meters.get(k) if g is not None else None
+                if local is None:
+                    continue
+                sd = {"meter": sd, "meter_class": type(local.meter).__name__, "reset": local.reset,
+                      "priority": local.priority}
             if k not in merged:
                 merged[k] = MeterEntry.from_state_dict(sd)
             else:

@@ -32,7 +32,10 @@ class Metric:
 
     @property
     def accumulators(self) -> dict[str, str]:
-        return {}
+        """Accumulator per sub-metric; by default one averaged sub-metric named like the metric
+        (optimus_dl/modules/metrics/metrics.py:54-61)."""
+        name = self.cfg.get("_name") if self.cfg is not None and hasattr(self.cfg, "get") else None
+        return {str(name): "average"} if name else {}
 
     def __call__(self, sources_data: dict[str, Any]) -> dict[str, dict[str, Any]]:
         raise NotImplementedError
@@ -46,32 +49,50 @@ class Metric:
 metric_registry, register_metric, build_metric = make_registry("metric", Metric)
 
 
+def _mask_weight(sources_data: dict[str, Any]) -> float:
+    """Number of valid tokens when the classification view comes along, else 1."""
+    c = sources_data.get(P.CLASSIFICATION)
+    if c and "mask" in c:
+        return c["mask"].sum().item()
+    return 1.0
+
+
 @register_metric("accuracy", MetricConfig)
 class AccuracyMetric(Metric):
+    """Token accuracy over the valid positions, and their count (``total``, summed)."""
+
     requires = {P.CLASSIFICATION}
-    accumulators = {"accuracy": "average"}
+    accumulators = {"accuracy": "average", "total": "sum"}
 
     def __call__(self, sources_data):
-        c = sources_data[P.CLASSIFICATION]
+        c = sources_data.get(P.CLASSIFICATION)
+        if not c:
+            return {}
         mask = c.get("mask")
         hit = (c["predictions"] == c["targets"])
         if mask is not None:
-            n = mask.sum().item()
-            return {"accuracy": {"value": (hit & mask).sum().item() / max(n, 1), "weight": n}}
-        return {"accuracy": {"value": hit.float().mean().item(), "weight": hit.numel()}}
+            hit, total = hit & mask, mask.sum().item()
+        else:
+            total = c["targets"].numel()
+        if total == 0:
+            return {}
+        return {"accuracy": {"value": hit.sum().item() / total, "weight": total}, "total": {"value": total}}
 
 
 @register_metric("perplexity", MetricConfig)
 class PerplexityMetric(Metric):
-    requires = {P.LOGITS, P.LOGITS_TARGETS}
+    """``exp`` of the mean loss. Needs only the LOSS protocol, which the criterion exposes with or without a fused
+    head (optimus_dl/modules/metrics/metrics.py:139-168): no logits are materialised for it."""
+
+    requires = {P.LOSS}
     accumulators = {"perplexity": "perplexity"}
 
     def __call__(self, sources_data):
-        logits, targets = sources_data[P.LOGITS], sources_data[P.LOGITS_TARGETS]
-        nll = F.cross_entropy(logits.reshape(-1, logits.shape[-1]).float(), targets.reshape(-1), ignore_index=-100,
-                              reduction="sum")
-        n = (targets != -100).sum().item()
-        return {"perplexity": {"value": nll.item() / max(n, 1), "weight": n}}
+        loss = sources_data.get(P.LOSS)
+        if loss is None:
+            return {}
+        return {"perplexity": {"value": loss.item() if hasattr(loss, "item") else loss,
+                               "weight": _mask_weight(sources_data)}}
 
 
 @register_metric("loss", MetricConfig)
@@ -80,8 +101,10 @@ class LossMetric(Metric):
     accumulators = {"loss": "average"}
 
     def __call__(self, sources_data):
-        loss = sources_data[P.LOSS]
-        return {"loss": {"value": loss.item() if isinstance(loss, torch.Tensor) else float(loss), "weight": 1.0}}
+        loss = sources_data.get(P.LOSS)
+        if loss is None:
+            return {}
+        return {"loss": {"value": loss.item() if hasattr(loss, "item") else loss, "weight": _mask_weight(sources_data)}}
 
 
 # per-metric config names of the reference (all carry the same fields here)

@@ -42,18 +42,42 @@ def _policy(ops: list[Any]):
     return policy
 
 
-def checkpoint_module(m: nn.Module, ctx_fn: Any = None, use_reentrant: bool = False) -> None:
-    """Make ``m`` recompute its forward during backward (its ``forward`` is wrapped in place, so hooks registered on
-    the module keep firing once per outer call and not during the recomputation)."""
-    orig = m.forward
+class CheckpointWrapper(nn.Module):
+    """Marker base of checkpointed modules (class name of optimus_dl/modules/model_transforms/checkpoint.py:24-60).
 
-    def wrapped(*a, _orig=orig, **k):
+    A module is checkpointed by giving it a subclass of its own class that also derives from this one, under the same
+    class name: ``isinstance(m, CheckpointWrapper)`` holds, ``m.module`` is the module itself, and neither parameter
+    names nor class-name matching by later transforms change."""
+
+    _ckpt_ctx_fn: Any = None
+    use_reentrant: bool = False
+
+    @property
+    def module(self) -> nn.Module:
+        return self
+
+    def forward(self, *args: Any, **kwargs: Any):
+        inner = self.__dict__.get("_ckpt_inner_forward") or super().forward
         if not torch.is_grad_enabled():
-            return _orig(*a, **k)
-        extra = {"context_fn": ctx_fn} if ctx_fn is not None else {}
-        return checkpoint(_orig, *a, use_reentrant=use_reentrant, **extra, **k)
+            return inner(*args, **kwargs)
+        extra = {"context_fn": self._ckpt_ctx_fn} if self._ckpt_ctx_fn is not None else {}
+        return checkpoint(inner, *args, use_reentrant=self.use_reentrant, **extra, **kwargs)
 
-    m.forward = wrapped
+
+@functools.lru_cache(maxsize=None)
+def _checkpointed_class(cls: type) -> type:
+    return type(cls.__name__, (CheckpointWrapper, cls), {"__module__": cls.__module__, "__qualname__": cls.__qualname__})
+
+
+def checkpoint_module(m: nn.Module, ctx_fn: Any = None, use_reentrant: bool = False) -> None:
+    """Make ``m`` recompute its forward during backward, in place: hooks registered on the module keep firing once
+    per outer call and not during the recomputation."""
+    if not isinstance(m, CheckpointWrapper):
+        m.__class__ = _checkpointed_class(type(m))
+    if "forward" in m.__dict__:          # a forward set on the instance would hide the class's: it becomes the inner one
+        m._ckpt_inner_forward = m.__dict__.pop("forward")
+    m._ckpt_ctx_fn = ctx_fn
+    m.use_reentrant = bool(use_reentrant)
     m._activation_checkpointed = True
 
 

@@ -15,6 +15,13 @@ from ...ops import attention as attn_ops
 from ...ops import linear as lin_ops
 from .layer_norms import RMSNorm
 
+# Which attention back ends exist, under the names of optimus_dl/modules/model/blocks/attention.py:24-40. The
+# reference picks flash-attn / flex attention / SDPA by these flags; here every masked form (causal, sliding
+# window, packed documents, per-row lengths) runs in the same kernels, so both are true wherever those kernels
+# are, and code that switches them off only loses nothing.
+FLASH_ATTENTION_AVAILABLE = True
+FLEX_ATTENTION_AVAILABLE = True
+
 
 def attention_mask_fn(b, _, q_idx, kv_idx, window_size=None, seq_lens=None, document_ids=None):
     """The visibility rule of every attention path, as a predicate over index tensors (same arguments as
@@ -60,7 +67,8 @@ class BaseSelfAttention(nn.Module):
             kd = self.head_dim if qk_norm_per_head else self.n_kv_head * self.head_dim
             self.q_norm = RMSNorm(qd, eps=rmsnorm_eps)
             self.k_norm = RMSNorm(kd, eps=rmsnorm_eps)
-        self.resid_dropout = nn.Dropout(dropout) if dropout > 0 else None
+        self.attn_dropout = nn.Dropout(dropout)      # holds the rate; applied inside the attention product
+        self.resid_dropout = nn.Dropout(dropout)
         # tensor-parallel state (parallel.tp.TPState), set by apply_tensor_parallel together with local head counts
         self.tp = None
         # decoding state (recipe.generation.LayerKV) while a generation session is active
@@ -99,9 +107,10 @@ class BaseSelfAttention(nn.Module):
         y = attn_ops.qkv_attention(qkv, n_head=Hq, n_kv_head=Hk, head_dim=hd, doc_start=doc_start,
                                    freqs_cis=freqs_cis if self.use_rope else None,
                                    position_ids=position_ids if self.use_rope else None, q_norm_weight=qw,
-                                   k_norm_weight=kw, norm_eps=self.rmsnorm_eps, window=self.sliding_window)
+                                   k_norm_weight=kw, norm_eps=self.rmsnorm_eps, window=self.sliding_window,
+                                   dropout_p=self.attn_dropout.p if self.training else 0.0)
         y = lin_ops.linear(y, self.wo.weight, self.wo.bias)
-        return self.resid_dropout(y) if self.resid_dropout is not None else y
+        return self.resid_dropout(y) if self.training and self.resid_dropout.p > 0 else y
 
 
     @torch.no_grad()

@@ -14,6 +14,10 @@ from . import utils
 logger = logging.getLogger(__name__)
 
 
+def __getattr__(name: str) -> Any:
+    return utils.lazy_hub_class(__name__, name)
+
+
 @dataclass
 class HFLlamaConfig(LlamaConfig):
     hf_model_name: str = "meta-llama/Llama-2-7b-hf"
@@ -35,6 +39,6 @@ def llama_from_hf(cfg: Any, hf_config: Any, hf_state_dict: dict | None) -> Llama
 @register_model("preset_hfllama2", HFLlamaConfig)
 def make_hf_llama_model(cfg: Any, **_: Any) -> Llama:
     logger.info("loading HF model %s", cfg.hf_model_name)
-    hf_config = utils.load_hf_config(cfg.hf_model_name)
-    sd = utils.load_hf_state_dict(cfg.hf_model_name) if cfg.load_weights else None
+    hf_config = utils.load_hf_config(cfg.hf_model_name, globals().get("AutoConfig"))
+    sd = utils.load_hf_state_dict(cfg.hf_model_name, globals().get("AutoModelForCausalLM")) if cfg.load_weights else None
     return llama_from_hf(cfg, hf_config, sd)

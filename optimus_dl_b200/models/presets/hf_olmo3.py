@@ -14,6 +14,10 @@ from . import utils
 logger = logging.getLogger(__name__)
 
 
+def __getattr__(name: str) -> Any:
+    return utils.lazy_hub_class(__name__, name)
+
+
 @dataclass
 class HFOlmo3Config(Olmo3Config):
     hf_model_name: str = "allenai/Olmo-3-1025-7B"
@@ -39,6 +43,6 @@ def olmo3_from_hf(cfg: Any, hf_config: Any, hf_state_dict: dict | None) -> Olmo3
 @register_model("preset_hfolmo3", HFOlmo3Config)
 def make_hf_olmo3_model(cfg: Any, **_: Any) -> Olmo3:
     logger.info("loading HF model %s", cfg.hf_model_name)
-    hf_config = utils.load_hf_config(cfg.hf_model_name)
-    sd = utils.load_hf_state_dict(cfg.hf_model_name) if cfg.load_weights else None
+    hf_config = utils.load_hf_config(cfg.hf_model_name, globals().get("AutoConfig"))
+    sd = utils.load_hf_state_dict(cfg.hf_model_name, globals().get("AutoModelForCausalLM")) if cfg.load_weights else None
     return olmo3_from_hf(cfg, hf_config, sd)

@@ -14,6 +14,10 @@ from . import utils
 logger = logging.getLogger(__name__)
 
 
+def __getattr__(name: str) -> Any:
+    return utils.lazy_hub_class(__name__, name)
+
+
 @dataclass
 class HFQwen3Config(Qwen3Config):
     hf_model_name: str = "Qwen/Qwen3-4B-Thinking-2507"
@@ -38,6 +42,6 @@ def qwen3_from_hf(cfg: Any, hf_config: Any, hf_state_dict: dict | None) -> Qwen3
 @register_model("preset_hfqwen3", HFQwen3Config)
 def make_hf_qwen3_model(cfg: Any, **_: Any) -> Qwen3:
     logger.info("loading HF model %s", cfg.hf_model_name)
-    hf_config = utils.load_hf_config(cfg.hf_model_name)
-    sd = utils.load_hf_state_dict(cfg.hf_model_name) if cfg.load_weights else None
+    hf_config = utils.load_hf_config(cfg.hf_model_name, globals().get("AutoConfig"))
+    sd = utils.load_hf_state_dict(cfg.hf_model_name, globals().get("AutoModelForCausalLM")) if cfg.load_weights else None
     return qwen3_from_hf(cfg, hf_config, sd)

@@ -130,16 +130,29 @@ def update_config_from_hf(cfg: Any, hf: Any, head_dim_fallback: int | None = Non
     cfg.head_dim = hd if isinstance(hd, int) else (head_dim_fallback or cfg.n_embd // cfg.n_head)
 
 
-def load_hf_config(name_or_path: str) -> Any:
-    from transformers import AutoConfig
+def lazy_hub_class(module_name: str, name: str) -> Any:
+    """Module ``__getattr__`` of the preset modules: ``AutoConfig`` and ``AutoModelForCausalLM`` are module-level
+    names there (callers can substitute them) that import ``transformers`` on first use only."""
+    if name in ("AutoConfig", "AutoModelForCausalLM"):
+        import transformers
 
-    return AutoConfig.from_pretrained(name_or_path)
+        return getattr(transformers, name)
+    raise AttributeError(f"module {module_name!r} has no attribute {name!r}")
 
 
-def load_hf_state_dict(name_or_path: str) -> dict[str, torch.Tensor]:
-    from transformers import AutoModelForCausalLM
+def load_hf_config(name_or_path: str, auto_config: Any = None) -> Any:
+    """``auto_config``: the class to ask (a preset module's ``AutoConfig`` when something replaced it)."""
+    if auto_config is None:
+        from transformers import AutoConfig as auto_config
 
-    model = AutoModelForCausalLM.from_pretrained(name_or_path, dtype=torch.float32, low_cpu_mem_usage=True)
+    return auto_config.from_pretrained(name_or_path)
+
+
+def load_hf_state_dict(name_or_path: str, auto_model: Any = None) -> dict[str, torch.Tensor]:
+    if auto_model is None:
+        from transformers import AutoModelForCausalLM as auto_model
+
+    model = auto_model.from_pretrained(name_or_path, dtype=torch.float32, low_cpu_mem_usage=True)
     return model.state_dict()
 
 

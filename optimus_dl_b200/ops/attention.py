@@ -26,6 +26,10 @@ from . import _lib, rope as rope_ops
 from .norm import rms_norm_ref
 
 
+class BoundaryError(ValueError, AssertionError):
+    """Document boundaries that do not cover the batch exactly."""
+
+
 def build_doc_start(B: int, T: int, device: torch.device, document_ids: torch.Tensor | None = None,
                     cu_seqlens: torch.Tensor | None = None) -> torch.Tensor:
     """Flat ``int32 [B*T]`` index of the first token of each token's document."""
@@ -33,9 +37,11 @@ def build_doc_start(B: int, T: int, device: torch.device, document_ids: torch.Te
     if cu_seqlens is not None:
         if not cu_seqlens.is_cuda and cu_seqlens.numel() > 0:
             # host-side boundaries can be checked without a device synchronisation: they must cover the batch exactly
-            if int(cu_seqlens[0]) != 0 or int(cu_seqlens[-1]) != B * T:
-                raise ValueError(f"cu_seqlens must start at 0 and end at the number of tokens ({B * T}); "
-                                 f"got {int(cu_seqlens[0])} .. {int(cu_seqlens[-1])}")
+            # (same two conditions and wording as optimus_dl/modules/model/blocks/attention.py:282-287)
+            if int(cu_seqlens[0]) != 0:
+                raise BoundaryError(f"cu_seqlens must start with 0, got {int(cu_seqlens[0])}")
+            if int(cu_seqlens[-1]) != B * T:
+                raise BoundaryError(f"cu_seqlens[-1] ({int(cu_seqlens[-1])}) must match sequence length T ({B * T})")
         cu = cu_seqlens.to(device=device, dtype=torch.int64)
         flat = idx.view(-1)
         seg = torch.searchsorted(cu, flat, right=True) - 1
@@ -174,17 +180,20 @@ def qkv_attention(qkv: torch.Tensor, *, n_head: int, n_kv_head: int, head_dim: i
                   freqs_cis: torch.Tensor | None = None, position_ids: torch.Tensor | None = None,
                   q_norm_weight: torch.Tensor | None = None, k_norm_weight: torch.Tensor | None = None,
                   norm_eps: float = 1e-6, window: int | None = None, seq_len: int | None = None,
-                  scale: float | None = None) -> torch.Tensor:
+                  scale: float | None = None, dropout_p: float = 0.0) -> torch.Tensor:
     """Attention on a fused projection ``qkv [B, T, (Hq + 2 Hk) * hd]``; returns ``[B, T, Hq * hd]``.
 
     Order of operations matches the reference: per-head QK-norm (when weights are given), then
-    interleaved RoPE (when ``freqs_cis`` is given), then masked softmax attention.
+    interleaved RoPE (when ``freqs_cis`` is given), then masked softmax attention. ``dropout_p > 0``
+    (dropout on the attention probabilities, optimus_dl/modules/model/blocks/attention.py:133, used by
+    GPT-2 configurations that train with dropout) has no kernel of its own and takes the row-wise
+    PyTorch path with its ``[B, T, T]`` mask.
     """
     B, T, W = qkv.shape
     Hq, Hk, hd = n_head, n_kv_head, head_dim
     scale = scale if scale is not None else 1.0 / math.sqrt(hd)
     seq_len = seq_len or T
-    if _kernel_ok(qkv, hd):
+    if _kernel_ok(qkv, hd) and dropout_p == 0.0:
         pos = position_ids.reshape(-1).to(torch.int32).contiguous() if position_ids is not None else None
         fr = freqs_cis.to(device=qkv.device, dtype=torch.float32).contiguous() if freqs_cis is not None else None
         flat = qkv.reshape(B * T, W)
@@ -200,9 +209,31 @@ def qkv_attention(qkv: torch.Tensor, *, n_head: int, n_kv_head: int, head_dim: i
         k = rms_norm_ref(k, k_norm_weight, norm_eps)
     if freqs_cis is not None:
         q, k = rope_ops.apply_rotary_emb(q, k, freqs_cis, position_ids)
+    if dropout_p > 0.0:
+        return attention_sdpa_rows(q, k, v, doc_start, window, scale, dropout_p).reshape(B, T, Hq * hd)
     out = attention_sdpa(q.reshape(B * T, Hq, hd), k.reshape(B * T, Hk, hd), v.reshape(B * T, Hk, hd), doc_start, window,
                          scale)
     return out.reshape(B, T, Hq * hd)
+
+
+def attention_sdpa_rows(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, doc_start: torch.Tensor, window: int | None,
+                        scale: float, dropout_p: float = 0.0) -> torch.Tensor:
+    """Differentiable PyTorch path per batch row: ``q [B, T, Hq, hd]``, ``k, v [B, T, Hk, hd]``, mask ``[B, 1, T, T]``
+    built from the flat ``doc_start`` (a document never crosses a row), dropout on the probabilities."""
+    B, T, Hq, hd = q.shape
+    Hk = k.shape[2]
+    i = torch.arange(T, device=q.device)
+    lo = doc_start.to(torch.int64).view(B, T) - (torch.arange(B, device=q.device) * T).view(B, 1)
+    if window is not None and window > 0:
+        lo = torch.maximum(lo, (i - window + 1).view(1, T))
+    j = i.view(1, 1, T)
+    mask = ((j <= i.view(1, T, 1)) & (j >= lo.view(B, T, 1))).unsqueeze(1)
+    qh, kh, vh = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+    if Hk != Hq:
+        kh = kh.repeat_interleave(Hq // Hk, dim=1)
+        vh = vh.repeat_interleave(Hq // Hk, dim=1)
+    o = F.scaled_dot_product_attention(qh, kh, vh, attn_mask=mask, dropout_p=dropout_p, scale=scale)
+    return o.transpose(1, 2)
 
 
 def attention_sdpa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, doc_start: torch.Tensor,

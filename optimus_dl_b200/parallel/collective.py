@@ -185,10 +185,26 @@ class Meshes(NamedTuple):
 class MeshCollective(Collective):
     """``torch.distributed`` backed collective with (dp_replicate, dp_shard, tp) topology."""
 
-    def __init__(self, rank: int, world_size: int, local_rank: int, local_world_size: int,
-                 device_type: str = "cuda", config: DistributedConfig | None = None, timeout_s: float | None = None,
-                 _group: Any = None, _parent: "MeshCollective | None" = None):
-        cfg = config or DistributedConfig()
+    def __init__(self, rank: int, world_size: int, local_world_size: int, local_rank: int,
+                 device_type: str = "cuda", mesh: Any = None, process_group: Any = None, tp_size: int | None = None,
+                 sharding_world_size: int | None = None, *, config: DistributedConfig | None = None,
+                 timeout_s: float | None = None, _group: Any = None, _parent: "MeshCollective | None" = None):
+        """Positional order and the ``tp_size`` / ``sharding_world_size`` / ``process_group`` keywords are those of
+        optimus_dl/modules/distributed/mesh.py:66-77; ``config`` carries the same two sizes (explicit keywords win).
+        A prebuilt ``mesh`` is not taken: the meshes are derived from the sizes."""
+        if mesh is not None:
+            raise NotImplementedError("MeshCollective builds its own device meshes; pass tp_size / sharding_world_size")
+        if config is None:      # the keyword form: an absent sharding size means the node's ranks divided by tp_size
+            cfg = DistributedConfig(tp_size=int(tp_size or 1), sharding_world_size=sharding_world_size) \
+                if (tp_size is not None or sharding_world_size is not None) else DistributedConfig()
+        else:
+            cfg = config
+            if tp_size is not None or sharding_world_size is not None:
+                cfg = DistributedConfig(tp_size=int(tp_size if tp_size is not None else cfg.tp_size),
+                                        sharding_world_size=sharding_world_size if sharding_world_size is not None
+                                        else cfg.sharding_world_size)
+        if process_group is not None and _group is None:
+            _group = process_group
         self._rank, self._world, self._local_rank, self._local_world = rank, world_size, local_rank, local_world_size
         self._device_type = device_type
         self.config = cfg
@@ -306,8 +322,9 @@ class MeshCollective(Collective):
         root = self._parent or self
         if root._local_sub is None:
             g = root._physical_mesh.get_group("local_ranks")
-            root._local_sub = MeshCollective(dist.get_rank(g), dist.get_world_size(g), root._local_rank,
-                                             root._local_world, root._device_type, root.config, _group=g, _parent=root)
+            root._local_sub = MeshCollective(dist.get_rank(g), dist.get_world_size(g), root._local_world,
+                                             root._local_rank, root._device_type, config=root.config, _group=g,
+                                             _parent=root)
         return root._local_sub
 
     @property
@@ -315,8 +332,9 @@ class MeshCollective(Collective):
         root = self._parent or self
         if root._tp_sub is None:
             g = root._parallel_mesh.get_group("tp")
-            root._tp_sub = MeshCollective(dist.get_rank(g), dist.get_world_size(g), root._local_rank,
-                                          root._local_world, root._device_type, root.config, _group=g, _parent=root)
+            root._tp_sub = MeshCollective(dist.get_rank(g), dist.get_world_size(g), root._local_world,
+                                          root._local_rank, root._device_type, config=root.config, _group=g,
+                                          _parent=root)
         return root._tp_sub
 
     # collectives --------------------------------------------------------------
@@ -379,8 +397,8 @@ def build_best_collective(config: DistributedConfig | Any = None, device: torch.
     needed = ("LOCAL_RANK", "LOCAL_WORLD_SIZE", "RANK", "WORLD_SIZE")
     if all(k in os.environ for k in needed) and env.get_world_size() > 1:
         dtype = (device.type if device is not None else ("cuda" if torch.cuda.is_available() else "cpu"))
-        _collective = MeshCollective(env.get_rank(), env.get_world_size(), env.get_local_rank(),
-                                     env.get_local_world_size(), dtype, config)
+        _collective = MeshCollective(env.get_rank(), env.get_world_size(), env.get_local_world_size(),
+                                     env.get_local_rank(), dtype, config=config)
     else:
         _collective = FakeCollective(0, 1, device)
     return _collective

@@ -821,10 +821,11 @@ def attention_forward(mod: nn.Module, x: torch.Tensor, *, freqs_cis=None, positi
     y = attn_ops.qkv_attention(qkv, n_head=Hq, n_kv_head=Hk, head_dim=hd, doc_start=doc_start,
                                freqs_cis=freqs_cis if mod.use_rope else None,
                                position_ids=position_ids if mod.use_rope else None, q_norm_weight=qw,
-                               k_norm_weight=kw, norm_eps=mod.rmsnorm_eps, window=mod.sliding_window)
+                               k_norm_weight=kw, norm_eps=mod.rmsnorm_eps, window=mod.sliding_window,
+                               dropout_p=mod.attn_dropout.p if mod.training else 0.0)
     out = row_parallel_linear(tp, y.reshape(B * T, Hq * hd), mod.wo.weight, mod.wo.bias)
     out = out.view(1, -1, D) if tp.sequence_parallel else out.view(B, T, D)
-    return mod.resid_dropout(out) if mod.resid_dropout is not None else out
+    return mod.resid_dropout(out) if mod.training and mod.resid_dropout.p > 0 else out
 
 
 def swiglu_mlp_forward(mod: nn.Module, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:

@@ -23,10 +23,10 @@ class Sharder:
     def __init__(self, output_config: Any, proc_config: Any):
         self.output_dir = Path(str(output_config.dir))
         self.output_name = str(output_config.name)
-        self.max_shard_bytes = int(proc_config.shard_size_mb) * 1024 * 1024
-        self.dtype = np.uint16 if str(proc_config.dtype) == "uint16" else np.uint32
-        self._cap = max(self.max_shard_bytes // np.dtype(self.dtype).itemsize, 1)
-        self._buf = np.empty(min(self._cap, 1 << 20), dtype=self.dtype)
+        self.max_shard_bytes = int(float(proc_config.shard_size_mb) * 1024 * 1024)    # fractions of a MB are allowed
+        self._dtype = np.dtype(np.uint16 if str(proc_config.dtype) == "uint16" else np.uint32)
+        self._cap = max(self.max_shard_bytes // self._dtype.itemsize, 1)
+        self._buf = np.empty(min(self._cap, 1 << 20), dtype=self._dtype)
         self._n = 0
         self._lens: list[int] = []
         self.shard_idx = 0
@@ -48,6 +48,27 @@ class Sharder:
         self._buf[: len(cur)] = cur
         self._n = len(cur)
         self._lens = [int(x) for x in state.get("current_shard_doc_lens", [])]
+
+    @property
+    def dtype(self) -> np.dtype:
+        return self._dtype
+
+    @dtype.setter
+    def dtype(self, value: Any) -> None:
+        """Changing the token type converts what is already staged."""
+        value = np.dtype(value)
+        if value != self._dtype:
+            self._buf, self._dtype = self._buf.astype(value), value
+            self._cap = max(self.max_shard_bytes // value.itemsize, 1)
+
+    @property
+    def current_shard_tokens(self) -> list[int]:
+        """The staged tokens of the open shard as a list (a copy: for inspection and state, not for appending)."""
+        return self._buf[: self._n].tolist()
+
+    @property
+    def current_shard_doc_lens(self) -> list[int]:
+        return list(self._lens)
 
     @property
     def current_shard_size_bytes(self) -> int:

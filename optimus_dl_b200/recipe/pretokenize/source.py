@@ -23,6 +23,11 @@ from typing import Any, Iterator
 
 import yaml
 
+try:  # module-level names so that callers (and tests) can substitute the two hub calls
+    from huggingface_hub import hf_hub_download, list_repo_files
+except ImportError:  # pragma: no cover - local directories need no hub client
+    hf_hub_download = list_repo_files = None
+
 logger = logging.getLogger(__name__)
 
 DATA_SUFFIXES = (".parquet", ".jsonl", ".json", ".jsonl.gz", ".txt")
@@ -38,15 +43,15 @@ class _Repo:
     def list_files(self) -> list[str]:
         if self.local is not None:
             return sorted(str(p.relative_to(self.local)).replace(os.sep, "/") for p in self.local.rglob("*") if p.is_file())
-        from huggingface_hub import list_repo_files
-
+        if list_repo_files is None:
+            raise ImportError(f"{self.repo_id!r} is not a local directory and huggingface_hub is not installed")
         return list(list_repo_files(repo_id=self.repo_id, repo_type="dataset"))
 
     def fetch(self, name: str) -> Path:
         if self.local is not None:
             return self.local / name
-        from huggingface_hub import hf_hub_download
-
+        if hf_hub_download is None:
+            raise ImportError(f"{self.repo_id!r} is not a local directory and huggingface_hub is not installed")
         return Path(hf_hub_download(repo_id=self.repo_id, filename=name, repo_type="dataset", cache_dir=self.cache_dir))
 
 

@@ -179,3 +179,40 @@ def test_doc_start_masks_equal_the_visibility_predicate():
     lens = torch.tensor([10, 6])
     pred = torch.stack([attention_mask_fn(b, None, q, k, seq_lens=lens) for b in range(B)])
     assert pred[1, 5, :6].all() and not pred[1, 7].any() and not pred[1, :, 6:].any() and pred[0].equal(k <= q)
+
+
+def test_attention_dropout_acts_on_the_probabilities_in_training_only():
+    """GPT-2 with ``dropout > 0``: the attention block drops probabilities (and residual outputs) while training,
+    and is exactly the dropout-free block in evaluation mode
+    (optimus_dl/modules/model/blocks/attention.py:133-134, 528)."""
+    from optimus_dl_b200.ops.attention import attention_sdpa_rows
+
+    B, T, Hq, Hk, hd = 2, 12, 4, 2, 16
+    torch.manual_seed(1)
+    q, k, v = torch.randn(B, T, Hq, hd), torch.randn(B, T, Hk, hd), torch.randn(B, T, Hk, hd)
+    docs = torch.tensor([[0] * 5 + [1] * 7, [2] * 12])
+    ds = build_doc_start(B, T, q.device, document_ids=docs)
+    for window in (None, 3):
+        rows = attention_sdpa_rows(q, k, v, ds, window, 1.0 / math.sqrt(hd))
+        flat = attention_ref(q.reshape(B * T, Hq, hd), k.reshape(B * T, Hk, hd), v.reshape(B * T, Hk, hd), ds, window)
+        assert torch.allclose(rows.reshape(B * T, Hq, hd), flat, atol=1e-5)
+    m = _model("gpt2", dropout=0.3)
+    plain = _model("gpt2")
+    plain.load_state_dict(m.state_dict())
+    x = torch.randint(0, V, (2, 16))
+    assert torch.allclose(m(x)["logits"], plain(x)["logits"], atol=1e-6)
+    att = m.transformer.h[0].attn
+    assert att.attn_dropout.p == 0.3 and att.resid_dropout.p == 0.3
+    att.train()
+    h = torch.randn(2, 16, 64)
+    torch.manual_seed(5)
+    a = att(h)
+    torch.manual_seed(6)
+    b = att(h)
+    assert not torch.allclose(a, b) and torch.isfinite(a).all()
+    att.resid_dropout.p = 0.0                      # what is left is the dropout inside the attention product
+    torch.manual_seed(5)
+    c = att(h)
+    torch.manual_seed(6)
+    d = att(h)
+    assert not torch.allclose(c, d)

@@ -184,6 +184,10 @@ def test_aggregation_merges_every_rank_including_keys_only_a_peer_has():
     assert abs(out["loss"] - 3.5) < 1e-9 and out["tokens"] == 40.0 and out["peak"] == 9.0
     assert list(out)[0] == "loss"
     assert mb.compute_meters("eval")["tokens"] == 10.0       # local values are untouched by aggregation
+    # a peer may also send bare meter states; class and priority are then those of the local meter of that name
+    bare = {"loss": peer_loss.state_dict(), "tokens": peer_tok.state_dict(), "peak": peer_only.state_dict()}
+    out = mb.compute_meters("eval", aggregate=True, collective=_TwoRanks(bare))
+    assert abs(out["loss"] - 3.5) < 1e-9 and out["tokens"] == 40.0 and "peak" not in out
 
 
 def test_entry_and_group_structure():

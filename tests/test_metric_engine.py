@@ -126,17 +126,18 @@ def test_cycles_and_missing_protocols_are_reported_without_stopping_other_metric
 def test_external_protocols_are_taken_from_the_criterion_and_override_sources():
     e = MetricEngine("g", [{"_name": "perplexity"}, {"_name": "accuracy"},
                            {"_name": "source_group", "prefix": "s", "sources": {"x": _src(value=1.0)}, "metrics": [{"_name": "loss"}]}])
-    assert e.required_external_protocols == {"logits", "logits_targets", "classification"}
+    assert e.required_external_protocols == {"loss", "classification"}
     logits = torch.tensor([[[2.0, 0.0, 0.0], [0.0, 3.0, 0.0]]])
     targets = torch.tensor([[0, 2]])
-    given = {"logits": logits, "logits_targets": targets, "loss": torch.tensor(42.0),
+    nll = torch.nn.functional.cross_entropy(logits[0], targets[0])
+    given = {"logits": logits, "logits_targets": targets, "loss": nll,
              "classification": {"predictions": logits.argmax(-1), "targets": targets, "mask": targets != -100}}
     e.update({}, given)
     out = e.compute(mb.compute_meters("g"))
-    nll = torch.nn.functional.cross_entropy(logits[0], targets[0])
     assert out["perplexity_metric/perplexity"] == pytest.approx(math.exp(nll.item()), rel=1e-5)
     assert out["accuracy_metric/accuracy"] == 0.5        # named as optimus_dl/modules/metrics/engine.py:306-318 names it
-    assert out["s/loss_metric/loss"] == 42.0 and "loss" not in CALLS      # a value the caller already has is not recomputed
+    assert out["accuracy_metric/total"] == 2            # the count of valid positions, summed over batches
+    assert out["s/loss_metric/loss"] == pytest.approx(nll.item()) and "loss" not in CALLS      # a value the caller already has is not recomputed
 
 
 def test_nested_names_internal_submetrics_and_finalisers():

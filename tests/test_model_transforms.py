@@ -35,6 +35,10 @@ def test_activation_checkpoint_recomputes_and_changes_nothing_numerically():
         blk.forward = counted
     out = build_model_transform({"_name": "activation_checkpoint", "layer_classes": ["LlamaBlock", "RotaryTransformerBlock"]}).apply(ckpt)
     assert out is ckpt and set(ckpt.state_dict()) == set(plain.state_dict())      # parameter names are untouched
+    from optimus_dl_b200.model_transforms.checkpoint import CheckpointWrapper
+    blk0 = ckpt.transformer.h[0]
+    assert isinstance(blk0, CheckpointWrapper) and blk0.module is blk0 and blk0.use_reentrant is False
+    assert type(blk0).__name__ == type(plain.transformer.h[0]).__name__ and isinstance(blk0, type(plain.transformer.h[0]))
     _loss(plain, x).backward()
     _loss(ckpt, x).backward()
     assert calls["n"] == 2 * len(ckpt.transformer.h)                               # every block ran again in backward
