@@ -42,11 +42,14 @@ class Fp8RecipeType(str, enum.Enum):
 def parse_fp8_format(s: Any) -> Fp8Format:
     if isinstance(s, Fp8Format):
         return s
-    key = str(s).strip().lower().replace("fp8_", "").replace("float8_", "")
+    key = str(s).strip().lower().replace("torch.", "")
+    for affix in ("fp8_", "float8_"):
+        key = key.removeprefix(affix)
+    key = key.removesuffix("_fp8").removesuffix("fn")
     for f in Fp8Format:
         if key in (f.value, f.name.lower()):
             return f
-    raise ValueError(f"unknown fp8 format {s!r}; expected one of {[f.value for f in Fp8Format]}")
+    raise ValueError(f"Unknown FP8 format {s!r}; expected one of {[f.value for f in Fp8Format]}")
 
 
 def parse_fp8_recipe(s: Any) -> Fp8RecipeType:

@@ -57,6 +57,8 @@ class TrainingIterationMixin:
                                metric_engine: Any = None, collective: Any = None) -> bool:
         device = training_context["device"]
         scaler = training_context["scaler"]
+        if scaler is not None and not scaler.is_enabled():
+            scaler = None                      # a disabled scaler scales nothing: take the plain path
         with meters_group("train", log_freq=log_freq) as should_log:
             optimizer.zero_grad()
             model.train()

@@ -45,9 +45,9 @@ def test_dtype_names_and_fp8_helpers():
         D.str_to_dtype("float7")
     assert D.is_fp8_dtype("fp8") and D.is_fp8_dtype(torch.float8_e5m2) and not D.is_fp8_dtype("bfloat16")
     assert not D.is_fp8_dtype("nonsense")
-    assert D.get_fp8_format_from_dtype("float8_e4m3fn") == "e4m3" and D.get_fp8_format_from_dtype("e5m2") == "e5m2"
-    with pytest.raises(ValueError):
-        D.get_fp8_format_from_dtype("float32")
+    assert D.get_fp8_format_from_dtype("float8_e4m3fn") == "e4m3fn" and D.get_fp8_format_from_dtype("e5m2") == "e5m2"
+    assert D.get_fp8_format_from_dtype("float32") is None
+    assert D.str_to_dtype("fp8_e4m3fn") is torch.float8_e4m3fn and D.str_to_dtype("Float8_E5M2fn") is torch.float8_e5m2
 
 
 def test_env_readers_fall_through_launchers_and_reject_garbage(monkeypatch):

@@ -94,3 +94,38 @@ def test_recorded_maxima_are_reduced_over_ranks(tmp_path, unique_port):
            "--master-port", str(unique_port), str(script), root]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
     assert res.returncode == 0 and res.stdout.count("REDUCE_OK") == 2, res.stdout[-2000:] + res.stderr[-3000:]
+
+
+def test_training_context_entries_follow_the_reference_contract():
+    """``TrainingContextMixin(optimization_config).setup_training_context(device)``: the scaler is always a
+    ``GradScaler`` (disabled on CPU and with FP8), the two context entries can be entered directly or called, and
+    an fp8 dtype without ``fp8.enabled`` runs bf16 autocast
+    (optimus_dl/recipe/train/mixins/execution/context_mixin.py:42-150)."""
+    import contextlib
+
+    import torch
+
+    from optimus_dl_b200.amp.config import AmpConfig, Fp8Config, OptimizationConfig
+    from optimus_dl_b200.recipe.train.mixins.execution.context_mixin import FreshContext, TrainingContextMixin
+
+    mixin = TrainingContextMixin(OptimizationConfig(amp=AmpConfig(enabled=True, dtype="torch.bfloat16", enable_scaler=True)))
+    ctx = mixin.setup_training_context(torch.device("cpu"))
+    assert isinstance(ctx["scaler"], torch.GradScaler) and not ctx["scaler"].is_enabled()
+    assert ctx["fp8_recipe"] is None and ctx["fp8_enabled"] is False and ctx["is_fp8_dtype"] is False
+    assert isinstance(ctx["amp_ctx"], FreshContext) and isinstance(mixin.get_fp8_backward_ctx(), contextlib.nullcontext)
+    a = torch.randn(4, 4)
+    with ctx["amp_ctx"]:
+        assert (a @ a).dtype == torch.bfloat16
+        with ctx["amp_ctx"]():                      # nested, through the call form
+            assert (a @ a).dtype == torch.bfloat16
+    assert (a @ a).dtype == torch.float32
+    with ctx["fp8_backward_ctx"], ctx["fp8_backward_ctx"]():
+        pass
+    off = TrainingContextMixin(OptimizationConfig(amp=AmpConfig(
+        enabled=True, dtype="torch.float8_e4m3fn", fp8=Fp8Config(enabled=False)))).setup_training_context(torch.device("cpu"))
+    assert off["is_fp8_dtype"] is True and off["fp8_enabled"] is False and off["fp8_recipe"] is None
+    with off["amp_ctx"]:
+        assert (a @ a).dtype == torch.bfloat16
+    plain = TrainingContextMixin(OptimizationConfig(amp=AmpConfig(enabled=False))).setup_training_context(torch.device("cpu"))
+    with plain["amp_ctx"]:
+        assert (a @ a).dtype == torch.float32
