@@ -41,5 +41,10 @@ class RMSNorm(nn.Module):
             emit = fp8_enabled() and fp8_ops.scaling_mode() == "block"
         return norm_ops.rms_norm(x, self.weight, self.eps, residual, emit_fp8=emit)
 
+    def _norm(self, x: torch.Tensor) -> torch.Tensor:
+        """``x / rms(x)`` without the weight (the helper of optimus_dl/modules/model/blocks/layer_norms.py:86-96);
+        ``forward`` does not go through it."""
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + self.eps)
+
     def extra_repr(self) -> str:
         return f"{self.weight.numel()}, eps={self.eps}"
