@@ -58,7 +58,9 @@ class TokenizedDataset(BaseDataset):
         self.dtype = np.dtype(name) if name else None
         self.shard_tok_start = [np.concatenate([[0], np.cumsum(l)]) for l in lens]
         self.strategy = build_strategy(cfg.strategy, rank=rank, world_size=world_size, seed=seed)
-        self.strategy.global_seed = seed
+        # what all ranks must draw alike (shuffles, offsets) comes from the corpus-wide seed when the builder passes
+        # one; ``seed`` itself may differ per rank
+        self.strategy.global_seed = kwargs.get("global_seed")
         self.strategy.initialize(self.doc_lens)
 
     def _shard_tokens(self, s: int) -> np.ndarray:
@@ -87,12 +89,16 @@ class TokenizedDataset(BaseDataset):
             assert initial_state.get("rank", self.rank) == self.rank and \
                 initial_state.get("world_size", self.world_size) == self.world_size, \
                 "tokenized_dataset must be resumed with the same rank and world size"
-            self.strategy.reset(initial_state["strategy"])
+            self.strategy.reset(initial_state["strategy_state"] if "strategy_state" in initial_state
+                                else initial_state.get("strategy"))          # "strategy": this package's earlier key
         else:
             self.strategy.reset(None)
 
     def get_state(self) -> dict[str, Any]:
-        return {"strategy": self.strategy.get_state(), "rank": self.rank, "world_size": self.world_size}
+        """Keys of optimus_dl/modules/data/datasets/tokenized_dataset.py:299-311."""
+        limit = self.cfg.get("limit") if self.cfg.get("limit") is not None else self.cfg.get("limit_documents")
+        return {"rank": self.rank, "world_size": self.world_size, "strategy_state": self.strategy.get_state(),
+                "data_dir": str(self.cfg.data_dir), "index_file": self.cfg.index_file, "limit": limit, "seed": self.seed}
 
     def next(self) -> dict[str, Any]:
         segs = self.strategy.next_segments()

@@ -56,7 +56,11 @@ class DataBuilder:
     def _kwargs(self, collective: Any, device: Any) -> dict[str, Any]:
         rank = collective.dp_rank if collective is not None else 0
         world = collective.dp_world_size if collective is not None else 1
-        return dict(rank=rank, world_size=world, seed=per_rank_seed(self.data_seed, rank, world), device=device)
+        # ``seed`` differs per rank (shuffle buffers, sampling); ``global_seed`` is the same everywhere, for what the
+        # ranks must agree on (a sharded dataset's permutation and offset: with per-rank seeds the ranks' shares of a
+        # shuffled corpus would overlap)
+        return dict(rank=rank, world_size=world, seed=per_rank_seed(self.data_seed, rank, world), device=device,
+                    global_seed=int(self.data_seed))
 
     def build_train_data(self, collective: Any = None, device: Any = None, **kwargs: Any):
         cfg = self.data_config.get("train_datasets") if self.data_config is not None else None

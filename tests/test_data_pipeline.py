@@ -192,3 +192,55 @@ def test_txt_lines_and_tokenizers(tmp_path):
     assert il.encode("ABxC") == [il.bos_token_id, 1, 2]
     with pytest.raises(ValueError):
         build_tokenizer({"_name": "inline_tokens_tokenizer", "tokens": ["A"]}).encode("B")
+
+
+def test_strategy_state_names_partition_rule_and_disjoint_shuffles_under_the_data_builder(tmp_path):
+    """State and attributes carry the reference's names (optimus_dl/modules/data/datasets/strategies/document.py:
+    30-85, concat_random.py:36-171); the unshuffled split gives the remainder to the last rank; the train recipe's
+    builder hands every rank its own ``seed`` but one ``global_seed``, so shuffled shares stay disjoint."""
+    from types import SimpleNamespace
+
+    from optimus_dl_b200.core import conf
+    from optimus_dl_b200.recipe.train.builders.data_builder import DataBuilder
+
+    total = _write_shards(tmp_path, [[3, 4, 5], [6, 7], [8, 9, 2, 1, 3]])          # ten documents
+    ds = [build_dataset({"_name": "tokenized_dataset", "data_dir": str(tmp_path)}, rank=r, world_size=3, seed=7) for r in range(3)]
+    assert [d.strategy.indices.tolist() for d in ds] == [[0, 1, 2], [3, 4, 5], [6, 7, 8, 9]]
+    ds[2].reset()
+    next(ds[2]), next(ds[2])
+    st = ds[2].state_dict()
+    assert st["strategy_state"] == {"ptr": 2, "rank": 2} and st["seed"] == 7 and st["world_size"] == 3 and st["limit"] is None
+    assert st["data_dir"] == str(tmp_path) and st["index_file"] == "index.json"
+    again = build_dataset({"_name": "tokenized_dataset", "data_dir": str(tmp_path)}, rank=2, world_size=3, seed=7)
+    again.reset(st)
+    assert again.strategy.ptr == 2 and next(again)["input_ids"].tolist() == next(ds[2])["input_ids"].tolist()
+    again.reset({"strategy": {"pos": 1}, "rank": 2, "world_size": 3})               # the earlier spelling still loads
+    assert again.strategy.ptr == 1
+    cr = build_dataset({"_name": "tokenized_dataset", "data_dir": str(tmp_path),
+                        "strategy": {"_name": "concat_random", "chunk_size": 5}}, rank=0, world_size=2, seed=11)
+    cr.reset()
+    next(cr)
+    s = cr.strategy
+    assert 0 <= s.global_offset < 5 and s.chunk_ptr == 1 and s.get_state() == {"chunk_ptr": 1, "seed": 11, "rank": 0}
+    assert s.next_sample()[0][1][1] > s.next_sample()[0][1][0] >= 0                  # [(doc, (start, end)), ...]
+    rng = np.random.default_rng(11)                                                 # the reference's draw order
+    assert s.global_offset == int(rng.integers(0, 5))
+    assert s.my_chunk_indices.tolist() == rng.permutation((total - s.global_offset) // 5)[0::2].tolist()
+    # through the builder: per-rank seeds differ, the shuffled document shares still partition the corpus
+    cfg = conf.create({"train_datasets": {"source": {"_name": "tokenized_dataset", "data_dir": str(tmp_path),
+                                                     "strategy": {"_name": "document", "shuffle": True}}}})
+    seen, seeds = [], set()
+    for r in range(3):
+        pipe = DataBuilder(data_config=cfg, data_seed=5).build_train_data(SimpleNamespace(dp_rank=r, dp_world_size=3))
+        inner = pipe.datasets.source if hasattr(pipe.datasets, "source") else pipe.datasets
+        node = inner
+        while not hasattr(node, "strategy"):
+            node = node.source
+        seeds.add(node.seed)
+        node.reset()
+        while True:
+            try:
+                seen.extend(next(node)["input_ids"].tolist())
+            except StopIteration:
+                break
+    assert len(seeds) == 3 and sorted(seen) == list(range(total))
