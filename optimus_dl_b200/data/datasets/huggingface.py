@@ -51,8 +51,11 @@ class HuggingFaceDataset(BaseDataset):
         self._ds = self._open()
         self.position = 0
         if initial_state:
+            assert initial_state.get("rank", self.rank) == self.rank and \
+                initial_state.get("world_size", self.world_size) == self.world_size, \
+                "huggingface_dataset must be resumed with the same rank and world size"
             self.position = int(initial_state.get("position", 0))
-            hf_state = initial_state.get("hf_state")
+            hf_state = initial_state.get("dataset_state", initial_state.get("hf_state"))    # "hf_state": earlier key
             if hf_state is not None and hasattr(self._ds, "load_state_dict"):
                 self._ds.load_state_dict(hf_state)
             elif self.position:
@@ -61,10 +64,12 @@ class HuggingFaceDataset(BaseDataset):
         self._iter = iter(self._ds)
 
     def get_state(self) -> dict[str, Any]:
-        st: dict[str, Any] = {"position": self.position}
+        """Keys of optimus_dl/modules/data/datasets/huggingface.py:58-72."""
+        st: dict[str, Any] = {"cfg": copy.deepcopy(self.cfg), "dataset_state": None, "world_size": self.world_size,
+                              "rank": self.rank, "position": self.position}
         if self._ds is not None and hasattr(self._ds, "state_dict"):
             try:
-                st["hf_state"] = copy.deepcopy(self._ds.state_dict())
+                st["dataset_state"] = copy.deepcopy(self._ds.state_dict())
             except Exception:
                 pass
         return st

@@ -27,6 +27,9 @@ class LoopDataset(BaseDataset):
     def reset(self, initial_state: dict | None = None):
         super().reset(initial_state)
         if initial_state:
+            assert initial_state.get("rank", self.rank) == self.rank and \
+                initial_state.get("world_size", self.world_size) == self.world_size, \
+                "loop must be resumed with the same rank and world size"
             self.epoch = initial_state.get("epoch", 0)
             self.inner.reset(initial_state.get("inner_state"))
         else:
@@ -34,7 +37,7 @@ class LoopDataset(BaseDataset):
             self.inner.reset()
 
     def get_state(self) -> dict[str, Any]:
-        return {"epoch": self.epoch, "inner_state": self.inner.state_dict()}
+        return {"rank": self.rank, "world_size": self.world_size, "epoch": self.epoch, "inner_state": self.inner.state_dict()}
 
     def next(self) -> Any:
         try:

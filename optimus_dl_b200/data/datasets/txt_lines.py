@@ -30,7 +30,7 @@ class TxtLinesDataset(BaseDataset):
         super().__init__(cfg, rank, world_size, seed)
         self.path = self._resolve(cfg.file_link, os.path.expanduser(cfg.cache_dir))
         self._lines: list[str] | None = None
-        self.index = 0
+        self.index = self.limit = 0
 
     @staticmethod
     def _resolve(link: str, cache_dir: str) -> str:
@@ -45,6 +45,9 @@ class TxtLinesDataset(BaseDataset):
         return os.path.expanduser(link)
 
     def _load(self) -> list[str]:
+        """All items of the file; this rank's share is ``[start, limit)`` with ``total // world_size`` items per rank
+        (the remainder is left out, so every rank has equally many: optimus_dl/modules/data/datasets/txt_lines.py:
+        115-127)."""
         if self._lines is None:
             with open(self.path, encoding="utf-8") as f:
                 lines = [l.rstrip("\n") for l in f]
@@ -53,20 +56,26 @@ class TxtLinesDataset(BaseDataset):
             n = int(self.cfg.lines_per_item)
             if n > 1:
                 lines = ["\n".join(lines[i:i + n]) for i in range(0, len(lines), n)]
-            per = (len(lines) + self.world_size - 1) // self.world_size
-            self._lines = lines[self.rank * per:(self.rank + 1) * per]
+            self._lines = lines
+            per = len(lines) // self.world_size
+            self.start, self.limit = per * self.rank, per * (self.rank + 1)
         return self._lines
 
     def reset(self, initial_state: dict | None = None):
         super().reset(initial_state)
-        self.index = int(initial_state["index"]) if initial_state else 0
+        st = initial_state or {}
+        assert st.get("rank", self.rank) == self.rank and st.get("world_size", self.world_size) == self.world_size, \
+            "txt_lines must be resumed with the same rank and world size"
+        self._load()
+        self.index = int(st["index"]) if "index" in st else self.start      # a position in the whole file
 
     def get_state(self) -> dict[str, Any]:
-        return {"index": self.index}
+        return {"index": self.index, "file_link": self.cfg.file_link, "skip_empty_lines": bool(self.cfg.skip_empty_lines),
+                "rank": self.rank, "world_size": self.world_size}
 
     def next(self) -> dict[str, Any]:
         lines = self._load()
-        if self.index >= len(lines):
+        if self.index >= self.limit:
             raise StopIteration
         item = {self.cfg.field: lines[self.index]}
         self.index += 1

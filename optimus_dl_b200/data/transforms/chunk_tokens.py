@@ -23,34 +23,41 @@ class ChunkTransformConfig(RegistryConfigStrict):
 
 
 class ChunkTokensNode(BaseNode):
+    """State under the reference's keys: ``buffer`` holds what is left of the current document, ``cfg`` the
+    configuration, ``source_state`` the upstream state (``rest``, the document's other fields, is this package's
+    addition: the reference drops them)."""
+
     def __init__(self, node: BaseNode, cfg: Any):
         super().__init__()
         self.node, self.cfg = node, cfg
-        self.pending: list = []
+        self.buffer: Any = []
+        self.rest: dict[str, Any] = {}
 
     def reset(self, initial_state: dict | None = None):
         super().reset(initial_state)
+        self.buffer, self.rest = [], {}
         if initial_state:
-            self.pending = copy.deepcopy(initial_state.get("pending", []))
+            self.buffer = copy.deepcopy(initial_state.get("buffer", []))
+            self.rest = copy.deepcopy(initial_state.get("rest", {}))
+            self.cfg = initial_state.get("cfg", self.cfg)
             self.node.reset(initial_state["source_state"])
         else:
-            self.pending = []
             self.node.reset()
 
     def get_state(self) -> dict[str, Any]:
-        return {"pending": copy.deepcopy(self.pending), "source_state": self.node.state_dict()}
+        return copy.deepcopy({"buffer": self.buffer, "cfg": self.cfg, "source_state": self.node.state_dict(),
+                              "rest": self.rest})
 
     def next(self) -> dict[str, Any]:
-        while not self.pending:
+        size = int(self.cfg.max_seq_len) + (1 if self.cfg.add_one_for_shift else 0)
+        while len(self.buffer) == 0:                       # empty documents give no chunk
             item = next(self.node)
-            toks = item[self.cfg.field]
-            size = int(self.cfg.max_seq_len) + (1 if self.cfg.add_one_for_shift else 0)
-            chunks = [toks[i:i + size] for i in range(0, len(toks), size)]
+            self.buffer = item[self.cfg.field]
             if self.cfg.max_chunks is not None:
-                chunks = chunks[: int(self.cfg.max_chunks)]
-            rest = {k: v for k, v in item.items() if k != self.cfg.field}
-            self.pending = [{**rest, self.cfg.field: c} for c in chunks if len(c) > 0]
-        return self.pending.pop(0)
+                self.buffer = self.buffer[: int(self.cfg.max_chunks) * size]
+            self.rest = {k: v for k, v in item.items() if k != self.cfg.field}
+        chunk, self.buffer = self.buffer[:size], self.buffer[size:]
+        return {**self.rest, self.cfg.field: chunk}
 
 
 @register_transform("chunk_tokens", ChunkTransformConfig)

@@ -34,7 +34,10 @@ class FlatTokensBatcherConfig(RegistryConfigStrict):
 
 
 class FlatTokensBatcherNode(BaseNode):
-    _BUFS = ("inputs", "labels", "positions", "docs")
+    # attribute -> key in the checkpointed state (the keys of
+    # optimus_dl/modules/data/transforms/flat_tokens_batcher.py:109-121, so states are interchangeable)
+    _BUFS = {"inputs": "input_buffer", "labels": "label_buffer", "positions": "position_ids_buffer",
+             "docs": "document_ids_buffer"}
 
     def __init__(self, node: BaseNode, cfg: Any):
         super().__init__()
@@ -67,16 +70,17 @@ class FlatTokensBatcherNode(BaseNode):
         super().reset(initial_state)
         self._clear()
         if initial_state:
-            for k in self._BUFS:
-                setattr(self, k, list(initial_state.get(k, [])))
-            self.next_doc = initial_state.get("next_doc", 0)
+            for attr, key in self._BUFS.items():
+                setattr(self, attr, list(initial_state.get(key, initial_state.get(attr, []))))
+            self.next_doc = initial_state.get("_current_doc_id", initial_state.get("next_doc", 0))
+            self.cfg = initial_state.get("cfg", self.cfg)
             self.node.reset(initial_state["source_state"])
         else:
             self.node.reset()
 
     def get_state(self) -> dict[str, Any]:
-        st = {k: list(getattr(self, k)) for k in self._BUFS}
-        st.update(next_doc=self.next_doc, cfg=self.cfg, source_state=self.node.state_dict())
+        st = {key: list(getattr(self, attr)) for attr, key in self._BUFS.items()}
+        st.update(_current_doc_id=self.next_doc, cfg=self.cfg, source_state=self.node.state_dict())
         return copy.deepcopy(st)
 
     def next(self) -> dict[str, Any]:

@@ -99,14 +99,16 @@ class SkipRandomNode(BaseNode):
     def reset(self, initial_state: dict | None = None):
         super().reset(initial_state)
         if initial_state:
-            self.rng.setstate(initial_state["rng"])
+            st = initial_state.get("rng_state", initial_state.get("rng"))      # "rng": this package's earlier key
+            if st is not None:
+                self.rng.setstate(tuple(tuple(x) if isinstance(x, list) else x for x in st))
             self.node.reset(initial_state["source_state"])
         else:
             self.rng = random.Random(self.seed)
             self.node.reset()
 
     def get_state(self) -> dict[str, Any]:
-        return {"rng": self.rng.getstate(), "source_state": self.node.state_dict()}
+        return {"rng_state": self.rng.getstate(), "source_state": self.node.state_dict()}
 
     def next(self) -> Any:
         while True:

@@ -163,7 +163,7 @@ def test_composite_weights_stop_criteria_and_strict_load():
     n = sum(1 for _ in iter(lambda: _next_or_none(ds), None))
     assert n == 405
     st = ds.state_dict()
-    st["datasets"].pop("a")
+    st["dataset_node_states"].pop("a")
     with pytest.raises(ValueError):
         build_dataset(cfg("CYCLE_FOREVER"), rank=0, world_size=1, seed=4).reset(st)
 
@@ -244,3 +244,31 @@ def test_strategy_state_names_partition_rule_and_disjoint_shuffles_under_the_dat
             except StopIteration:
                 break
     assert len(seeds) == 3 and sorted(seen) == list(range(total))
+
+
+def test_composite_draws_the_reference_sequence_and_resumes_inside_a_block():
+    """Which dataset serves item ``i`` is ``multinomial(weights, 1000)`` from a generator seeded through
+    ``seed -> manual_seed(seed + 10000 * epoch) -> randint(2**32)`` (optimus_dl/modules/data/datasets/composite.py:
+    67-75, 155-168); the state holds the generator state from before the current block and the offset into it."""
+    spec = {"_name": "composite", "stop_criteria": "ALL_DATASETS_EXHAUSTED", "datasets": {
+        "a": {"dataset": {"_name": "synthetic_tokens", "length": 3, "num_documents": 40}, "weight": 1.0, "cycle": False},
+        "b": {"dataset": {"_name": "synthetic_tokens", "length": 5, "num_documents": 2000}, "weight": 2.0, "cycle": True}}}
+    ds = build_dataset(spec, rank=0, world_size=1, seed=21)
+    ds.reset()
+    g = torch.Generator()
+    g.manual_seed(21)
+    g2 = torch.Generator()
+    g2.manual_seed(int(torch.randint(0, 2**32, (1,), generator=g).item()))
+    picks = torch.multinomial(torch.tensor([1.0, 2.0], dtype=torch.float64), 1000, replacement=True, generator=g2).tolist()
+    first_a_exhaustion = [i for i, p in enumerate(picks) if p == 0][40]      # the 41st request for "a" finds it empty
+    got = [len(next(ds)["input_ids"]) for _ in range(first_a_exhaustion)]
+    assert got == [3 if p == 0 else 5 for p in picks[:first_a_exhaustion]]
+    st = ds.state_dict()
+    assert set(st) == {"datasets_exhausted", "dataset_node_states", "epoch", "num_yielded", "weighted_sampler_state", "cycles"}
+    assert st["num_yielded"] == first_a_exhaustion and st["weighted_sampler_state"]["offset"] == first_a_exhaustion
+    assert st["datasets_exhausted"] == {"a": False, "b": False}
+    tail = [next(ds)["input_ids"].tolist() for _ in range(30)]           # crosses the exhaustion of "a": a new block
+    assert ds.state_dict()["datasets_exhausted"] == {"a": True, "b": False} and all(len(t) == 5 for t in tail)
+    other = build_dataset(spec, rank=0, world_size=1, seed=21)
+    other.reset(st)
+    assert [next(other)["input_ids"].tolist() for _ in range(30)] == tail

@@ -499,3 +499,67 @@ def test_profiler_tracer_scope_summaries_tree_and_periodic_report():
             assert word in text, word
     finally:
         log.removeHandler(handler), log.setLevel(old_level)
+
+
+def test_node_states_use_the_reference_keys_and_the_shuffle_stream_is_the_reference_stream(tmp_path):
+    """Checkpointed state of the data nodes is interchangeable with the reference's: same keys, same meaning
+    (optimus_dl/modules/data/transforms/shuffle.py:74-98, chunk_tokens.py:56-84, flat_tokens_batcher.py:109-121,
+    skip.py:118-123, datasets/txt_lines.py:115-168, loop_dataset.py:87-95). The shuffle buffer draws with numpy's
+    ``default_rng(seed + 41 * rank).integers(0, len(buffer))`` and pops that element."""
+    sh = build_transform({"_name": "shuffle", "buffer_size": 4}, rank=2, seed=9).build(_Range(10))
+    sh.reset()
+    got = [x["input_ids"][0] for x in _drain(sh)]
+    rng, buf, src, want = np.random.default_rng(9 + 2 * 41), [], list(range(10)), []
+    while True:
+        while src and len(buf) < 4:
+            buf.append(src.pop(0))
+        if not buf:
+            break
+        want.append(buf.pop(int(rng.integers(0, len(buf)))))
+    assert got == want and sorted(got) == list(range(10))
+    sh.reset()
+    next(sh)
+    st = sh.state_dict()
+    assert set(st) >= {"buffer", "cfg", "source_state", "rng_state", "terminated", "rank"} and st["rank"] == 2
+    assert st["rng_state"]["bit_generator"] == "PCG64" and st["terminated"] is False and len(st["buffer"]) == 3
+
+    ch = build_transform({"_name": "chunk_tokens", "max_seq_len": 3, "add_one_for_shift": False}).build(
+        _Range(2, lambda i: {"input_ids": list(range(10 * i, 10 * i + 8)), "tag": i}))
+    ch.reset()
+    assert next(ch) == {"input_ids": [0, 1, 2], "tag": 0}
+    st = ch.state_dict()
+    assert st["buffer"] == [3, 4, 5, 6, 7] and st["rest"] == {"tag": 0} and "cfg" in st and "source_state" in st
+
+    fb = build_transform({"_name": "flat_batcher", "batch_size": 1, "seq_len": 4, "mask_documents": True}).build(
+        _Range(3, lambda i: {"input_ids": list(range(10 * i, 10 * i + 4))}))
+    fb.reset()
+    next(fb)
+    st = fb.state_dict()
+    assert st["input_buffer"] == [11, 12] and st["label_buffer"] == [12, 13] and st["position_ids_buffer"] == [1, 2]
+    assert st["document_ids_buffer"] == [1, 1] and st["_current_doc_id"] == 2 and "cfg" in st
+    fb2 = build_transform({"_name": "flat_batcher", "batch_size": 1, "seq_len": 4, "mask_documents": True}).build(
+        _Range(3, lambda i: {"input_ids": list(range(10 * i, 10 * i + 4))}))
+    fb2.reset(st)
+    assert next(fb2)["input_ids"].tolist() == next(fb)["input_ids"].tolist() == [[11, 12, 20, 21]]
+
+    sr = build_transform({"_name": "skip_random", "probability": 0.5}, seed=3).build(_Range(20))
+    sr.reset()
+    next(sr)
+    assert set(sr.state_dict()) == {"rng_state", "source_state"}
+
+    f = tmp_path / "t.txt"
+    f.write_text("".join(f"line {i}\n" for i in range(11)))
+    parts = [build_dataset({"_name": "txt_lines", "file_link": str(f)}, rank=r, world_size=3) for r in range(3)]
+    for p in parts:
+        p.reset()
+    assert [[x["text"] for x in _drain(p)] for p in parts] == [[f"line {i}" for i in range(a, a + 3)] for a in (0, 3, 6)]
+    parts[1].reset()
+    next(parts[1])
+    st = parts[1].state_dict()
+    assert st == {"index": 4, "file_link": str(f), "skip_empty_lines": st["skip_empty_lines"], "rank": 1, "world_size": 3}
+    parts[1].reset(st)
+    assert next(parts[1])["text"] == "line 4"                       # ``index`` is a position in the whole file
+    lp = build_dataset({"_name": "loop", "inner": {"_name": "txt_lines", "file_link": str(f)}}, rank=0, world_size=3)
+    lp.reset()
+    assert [next(lp)["text"] for _ in range(4)] == ["line 0", "line 1", "line 2", "line 0"]
+    assert set(lp.state_dict()) == {"rank", "world_size", "epoch", "inner_state"}
