@@ -301,6 +301,10 @@ class DictNode(Node, MutableMapping):
             new._data[k] = _wrap(copy.deepcopy(v, memo), new, k)
         return new
 
+    def copy(self) -> "DictNode":
+        """A detached copy of this subtree (what ``DictConfig.copy()`` gives); interpolations stay unresolved."""
+        return copy.deepcopy(self)
+
     def __getstate__(self):
         return {"data": to_container(self, resolve=False)}
 
@@ -364,6 +368,9 @@ class ListNode(Node, MutableSequence):
         for i, v in enumerate(self._items):
             new._items.append(_wrap(copy.deepcopy(v, memo), new, i))
         return new
+
+    def copy(self) -> "ListNode":
+        return copy.deepcopy(self)
 
     def __getstate__(self):
         return {"data": to_container(self, resolve=False)}

@@ -26,7 +26,7 @@ import torch.nn.functional as F
 
 from ..core.log import warn_once
 from ..core.registry import RegistryConfigStrict
-from ..metrics.common import cached_lambda, log_averaged, log_averaged_exponent, log_summed
+from ..metrics.common import cached_lambda, log_averaged, log_averaged_exponent, log_max, log_summed
 from ..ops import cross_entropy as ce_ops
 from . import register_criterion
 from .base import BaseCriterion
@@ -104,8 +104,9 @@ class CrossEntropyCriterion(BaseCriterion):
         else:
             lens = lambda: torch.full((ids.shape[0],), float(ids.shape[1]))  # noqa: E731
             n_samples = lambda: float(ids.shape[0])  # noqa: E731
-        log_averaged("input_max_seq_len", lambda: lens().max().item(), round=2)
-        log_averaged("input_mean_seq_len", lambda: lens().mean().item(), round=2)
+        # kinds, weights and rounding as optimus_dl/modules/criterion/cross_entropy.py:133-186 logs them
+        log_max("input_max_seq_len", lambda: lens().max().item(), round=2)
+        log_averaged("input_mean_seq_len", lambda: lens().mean().item(), weight=lambda: n_samples() / tp, round=2)
         log_summed("batch_samples", lambda: n_samples() / tp)
         log_summed("total_samples", lambda: n_samples() / tp, reset=False)
 
@@ -140,12 +141,12 @@ class CrossEntropyCriterion(BaseCriterion):
         loss = res.loss
         tp = self._tp_size()
         n_valid = cached_lambda(lambda: res.n_valid.item())
-        log_averaged("accuracy", lambda: res.n_correct.item() / max(n_valid(), 1), weight=n_valid, round=4)
+        log_averaged("accuracy", lambda: res.n_correct.item() / max(n_valid(), 1), weight=n_valid, round=2)
         log_summed("batch_tokens", lambda: n_valid() / tp)
         log_summed("total_tokens", lambda: n_valid() / tp, reset=False)
         loss_val = cached_lambda(lambda: loss.detach().float().item())
-        log_averaged("loss", loss_val, weight=n_valid, round=4, priority=0)
-        log_averaged_exponent("perplexity", value=loss_val, weight=n_valid, round=4, priority=1)
+        log_averaged("loss", loss_val, weight=n_valid, priority=0)
+        log_averaged_exponent("perplexity", value=loss_val, weight=n_valid, priority=1)
         if "loss" in requested:
             exposed["loss"] = loss.detach()
         if "input_tokens" in requested:

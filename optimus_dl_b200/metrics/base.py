@@ -36,7 +36,10 @@ class BaseMeter(ABC):
 
     @classmethod
     def from_state_dict(cls, state_dict: dict[str, Any]) -> "BaseMeter":
-        m = cls.__new__(cls)
+        try:
+            m = cls()
+        except TypeError:                   # a meter whose constructor needs arguments: the state supplies everything
+            m = cls.__new__(cls)
         m.load_state_dict(state_dict)
         return m
 

@@ -41,31 +41,34 @@ class SummedMeter(BaseMeter):
 
 
 class MaxMeter(BaseMeter):
-    _EMPTY = -float("inf")
-
     def __init__(self, round: int | None = None):
-        self.round, self.value = round, self._EMPTY
+        self.round, self.value = round, -float("inf")
 
     def log(self, value: float) -> None:
-        self.value = value if self.value is None else max(self.value, value)
+        self.value = max(self.value, value)
 
     def compute(self) -> float:
-        """The extreme seen so far; before anything was logged the identity element itself (-inf for the maximum, +inf
-        for the minimum), as optimus_dl/modules/metrics/common.py:121-130 returns it."""
-        if self.value is None or self.value == self._EMPTY:
-            return self._EMPTY
+        """The largest value seen; before anything was logged the identity element itself (``-inf``), as
+        optimus_dl/modules/metrics/common.py:121-130 returns it."""
+        if not math.isfinite(self.value):
+            return self.value
         return safe_round(self.value, self.round)
 
     def merge(self, other_state: dict[str, Any]) -> None:
         if other_state["value"] is not None:
-            self.log(other_state["value"])
+            self.value = max(self.value, other_state["value"])
 
 
 class MinMeter(MaxMeter):
-    _EMPTY = float("inf")
+    """The smallest value seen (``+inf`` before anything was logged). Kept as the maximum of the negated values, so
+    ``value`` in the state is the NEGATED minimum, as in optimus_dl/modules/metrics/common.py:146-180: states and
+    cross-rank merges are interchangeable with it."""
 
     def log(self, value: float) -> None:
-        self.value = value if self.value is None else min(self.value, value)
+        super().log(-value)
+
+    def compute(self) -> float:
+        return -super().compute()
 
 
 class _IntervalMeter(BaseMeter):
@@ -133,26 +136,45 @@ class StopwatchMeter(_IntervalMeter):
 
 
 class AveragedExponentMeter(BaseMeter):
-    """``exp(weighted mean(value))`` — perplexity from mean loss."""
+    """``exp(weighted mean(value))`` -- perplexity from mean loss. The mean lives in an inner :class:`AverageMeter`;
+    the state is ``{"internal": <its state>, "round": ...}`` (optimus_dl/modules/metrics/common.py:398-452)."""
 
     def __init__(self, round: int | None = None):
-        self.round, self.sum, self.count = round, 0.0, 0.0
+        self._internal = AverageMeter()
+        self.round = round
+
+    @property
+    def sum(self) -> float:
+        return self._internal.sum
+
+    @property
+    def count(self) -> float:
+        return self._internal.count
 
     def log(self, value: float, weight: float = 1.0) -> None:
-        self.sum += value * weight
-        self.count += weight
+        self._internal.log(value, weight)
 
     def compute(self) -> float:
-        if not self.count:
+        if not self._internal.count:
             return 0.0
         try:
-            return safe_round(math.exp(self.sum / self.count), self.round)
+            return safe_round(math.exp(self._internal.sum / self._internal.count), self.round)
         except OverflowError:
             return float("inf")
 
+    @staticmethod
+    def _inner(state: dict[str, Any]) -> dict[str, Any]:
+        return state["internal"] if "internal" in state else {"sum": state["sum"], "count": state["count"], "round": None}
+
     def merge(self, other_state: dict[str, Any]) -> None:
-        self.sum += other_state["sum"]
-        self.count += other_state["count"]
+        self._internal.merge(self._inner(other_state))
+
+    def state_dict(self) -> dict[str, Any]:
+        return {"internal": self._internal.state_dict(), "round": self.round}
+
+    def load_state_dict(self, state_dict: dict[str, Any]) -> None:
+        self._internal.load_state_dict(self._inner(state_dict))
+        self.round = state_dict.get("round")
 
 
 class GatherMeter(BaseMeter):

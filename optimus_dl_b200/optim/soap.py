@@ -60,11 +60,11 @@ def merged_shape(shape: tuple[int, ...], limit: int) -> list[int]:
 
 def _mode_product(t: torch.Tensor, q: torch.Tensor | None, transpose: bool) -> torch.Tensor:
     """Contract the leading axis of ``t`` with ``q`` (or just rotate the axes) and move it last: applying this
-    once per axis returns to the original axis order."""
+    once per axis returns to the original axis order. The columns of ``q`` are eigenvectors, so coordinates in the
+    eigenbasis are ``q^T t`` (``transpose=False``: into the basis) and ``q t`` leads back (``transpose=True``)."""
     if q is None:
         return t.movedim(0, -1)
-    m = q.t() if transpose else q
-    return torch.tensordot(t, m, dims=([0], [1]))
+    return torch.tensordot(t, q, dims=([0], [1] if transpose else [0]))
 
 
 class SOAP(Optimizer):

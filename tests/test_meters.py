@@ -83,7 +83,16 @@ def test_stopwatch_and_frequency_meters_measure_milliseconds():
     a.elapsed, a.counter, b.elapsed, b.counter = 1_000_000, 1, 2_000_000, 2
     a.merge(b.state_dict())
     assert (a.elapsed, a.counter, a.compute()) == (3_000_000, 3, 1.0)
-    assert mc.MaxMeter(round=2).value == -float("inf") and mc.MinMeter().value == float("inf")
+    # the minimum is kept as the maximum of the negated values (optimus_dl/modules/metrics/common.py:146-180)
+    assert mc.MaxMeter(round=2).value == -float("inf") and mc.MinMeter().value == -float("inf")
+    lo = mc.MinMeter()
+    lo.log(4.0), lo.log(2.5)
+    assert lo.state_dict()["value"] == -2.5 and lo.compute() == 2.5
+    ex = mc.AveragedExponentMeter(round=3)
+    ex.log(1.0, 2.0)
+    assert ex.state_dict() == {"internal": {"round": None, "sum": 2.0, "count": 2.0}, "round": 3}
+    older = mc.AveragedExponentMeter.from_state_dict({"sum": 2.0, "count": 2.0, "round": 3})   # the flat form still loads
+    assert older.compute() == ex.compute() == 2.718
     assert mc.MaxMeter().compute() == -float("inf")         # nothing logged yet
 
 

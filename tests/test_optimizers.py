@@ -118,7 +118,7 @@ def test_soap_descends_and_merges_dims():
     target = x @ torch.randn(12, 20)
     opt = SOAP([w, b], lr=0.05, weight_decay=0.0, precondition_frequency=5)
     losses = []
-    for _ in range(80):
+    for _ in range(200):
         opt.zero_grad()
         loss = ((x @ w.t() + b) - target).pow(2).mean()
         loss.backward()
@@ -128,6 +128,55 @@ def test_soap_descends_and_merges_dims():
     q = opt.state[w]["Q"]
     assert torch.allclose(q[0].t() @ q[0], torch.eye(20), atol=1e-4)
     assert opt.state[b]["GG"] == [None]
+
+
+def test_soap_is_adam_in_the_eigenbasis_of_the_gradient_statistics():
+    """The update written out for a matrix (optimus_dl/modules/optim/soap.py:157-279): statistics ``L = EMA(G G^T)``,
+    ``R = EMA(G^T G)`` with eigenvectors in the COLUMNS of ``Q_L``, ``Q_R``; Adam runs on ``Q_L^T G Q_R`` and its
+    direction returns as ``Q_L (.) Q_R^T``; the first call only seeds the statistics; they are updated after each
+    step and their bases refreshed by one QR power iteration every ``precondition_frequency`` steps."""
+    torch.manual_seed(3)
+    lr, b1, b2, eps, wd, freq = 0.02, 0.9, 0.95, 1e-8, 0.1, 3
+    # square, so that both statistics have full rank from the first gradient on (in a null space the eigenvectors
+    # are arbitrary and Adam's m / sqrt(v) turns rounding noise into visible steps)
+    w = nn.Parameter(torch.randn(6, 6))
+    opt = SOAP([w], lr=lr, betas=(b1, b2), eps=eps, weight_decay=wd, precondition_frequency=freq)
+    p = w.detach().clone()
+    grads = [torch.randn(6, 6) for _ in range(6)]
+
+    def eig(m):
+        return torch.linalg.eigh(m + 1e-30 * torch.eye(m.shape[0]))[1].flip(1)
+
+    L = (1 - b2) * grads[0] @ grads[0].t()
+    Rm = (1 - b2) * grads[0].t() @ grads[0]
+    QL, QR = eig(L), eig(Rm)
+    m, v = torch.zeros(6, 6), torch.zeros(6, 6)
+    w.grad = grads[0]
+    opt.step()
+    assert torch.equal(w.detach(), p)                            # the first call moves nothing
+    for t, g in enumerate(grads[1:], start=1):
+        g_rot = QL.t() @ g @ QR
+        m = b1 * m + (1 - b1) * g
+        v = b2 * v + (1 - b2) * g_rot * g_rot
+        direction = QL @ ((QL.t() @ m @ QR) / (v.sqrt() + eps)) @ QR.t()
+        p = p - lr * ((1 - b2 ** t) ** 0.5) / (1 - b1 ** t) * direction
+        p = p - lr * wd * p
+        L = b2 * L + (1 - b2) * g @ g.t()
+        Rm = b2 * Rm + (1 - b2) * g.t() @ g
+        if t % freq == 0:
+            for axis, (stat, q) in enumerate(((L, QL), (Rm, QR))):
+                order = torch.argsort(torch.diag(q.t() @ stat @ q), descending=True)
+                v = v.index_select(axis, order)
+                qn = torch.linalg.qr(stat @ q[:, order])[0]
+                if axis == 0:
+                    QL = qn
+                else:
+                    QR = qn
+        w.grad = g
+        opt.step()
+        assert torch.allclose(w.detach(), p, atol=1e-4), (t, (w.detach() - p).abs().max().item())
+    # a rotation by Q instead of Q^T is also orthogonal and also descends, but it is a different optimizer
+    assert not torch.allclose(QL, QL.t(), atol=1e-2)
 
 
 # ---------------------------------------------------------------------- adamw factory and the optimizer builder
