@@ -85,7 +85,7 @@ def test_padding_token_is_ignored_and_tokens_are_counted():
     assert abs(m["perplexity"] - math.exp(ref.item())) / math.exp(ref.item()) < 1e-3
     pred = model.table[ids[:, :-1]].argmax(-1)
     acc = ((pred == tg) & (tg != -100)).sum().item() / n_valid
-    assert abs(m["accuracy"] - acc) < 1e-3
+    assert abs(m["accuracy"] - acc) <= 5e-3                          # logged with two decimals, as the reference does
 
 
 @pytest.mark.parametrize("smoothing", [0.0, 0.1])
