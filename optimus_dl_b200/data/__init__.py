@@ -88,7 +88,7 @@ def build_data_pipeline(cfg: Any, profile_name: str | None = None, eval_pipeline
     pipeline: Any = dataset
     profiler = None
     if _get(cfg, "profile", False):
-        profiler = PipelineProfiler(name=profile_name or repr(dataset), report_freq=_get(cfg, "report_freq", 500))
+        profiler = PipelineProfiler(name=profile_name or repr(dataset), report_freq=_get(cfg, "report_freq", 100))
         pipeline = ProfilingProxyNode(pipeline, name=dataset_class, profiler=profiler)
     with scope_profiler(profiler):
         tcfg = _get(cfg, "transform")

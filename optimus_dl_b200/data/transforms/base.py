@@ -16,6 +16,43 @@ from torchdata.nodes import BaseNode
 from ..profiling import maybe_profile
 
 
+def adopt_saved_cfg(own: Any, saved: Any) -> Any:
+    """Configuration of a node restored from a checkpoint: the saved values win (a run continues with the settings
+    it was started with, as in the reference), for the fields this node knows; fields the saved object does not have
+    (it may come from another version, or from the reference) keep their current value."""
+    if saved is None or saved is own:
+        return own
+    import copy
+    import dataclasses
+
+    def has(obj: Any, k: str) -> bool:
+        try:
+            return k in obj
+        except TypeError:
+            return hasattr(obj, k)
+
+    def get(obj: Any, k: str) -> Any:
+        try:
+            return obj[k]
+        except (TypeError, KeyError, AttributeError):
+            return getattr(obj, k)
+
+    out = copy.copy(own)
+    names = [f.name for f in dataclasses.fields(own)] if dataclasses.is_dataclass(own) else list(own.keys())
+    for k in names:
+        if k.startswith("_") or not has(saved, k):
+            continue
+        try:
+            v = get(saved, k)
+        except Exception:  # noqa: BLE001 - a missing mandatory value in the saved object
+            continue
+        if dataclasses.is_dataclass(own):
+            setattr(out, k, v)
+        else:
+            out[k] = v
+    return out
+
+
 class BaseTransform:
     def __init__(self, cfg: Any = None, **kwargs: Any):
         self.cfg = cfg

@@ -11,7 +11,7 @@ from torchdata.nodes import BaseNode
 
 from ...core.registry import RegistryConfigStrict
 from . import register_transform
-from .base import BaseTransform
+from .base import BaseTransform, adopt_saved_cfg
 
 
 @dataclass
@@ -39,7 +39,7 @@ class ChunkTokensNode(BaseNode):
         if initial_state:
             self.buffer = copy.deepcopy(initial_state.get("buffer", []))
             self.rest = copy.deepcopy(initial_state.get("rest", {}))
-            self.cfg = initial_state.get("cfg", self.cfg)
+            self.cfg = adopt_saved_cfg(self.cfg, initial_state.get("cfg"))
             self.node.reset(initial_state["source_state"])
         else:
             self.node.reset()

@@ -19,7 +19,7 @@ from torchdata.nodes import BaseNode
 
 from ...core.registry import RegistryConfigStrict
 from . import register_transform
-from .base import BaseTransform, MapperConfig, ProcessMapperConfig
+from .base import BaseTransform, adopt_saved_cfg, MapperConfig, ProcessMapperConfig
 
 
 @dataclass
@@ -73,7 +73,7 @@ class FlatTokensBatcherNode(BaseNode):
             for attr, key in self._BUFS.items():
                 setattr(self, attr, list(initial_state.get(key, initial_state.get(attr, []))))
             self.next_doc = initial_state.get("_current_doc_id", initial_state.get("next_doc", 0))
-            self.cfg = initial_state.get("cfg", self.cfg)
+            self.cfg = adopt_saved_cfg(self.cfg, initial_state.get("cfg"))
             self.node.reset(initial_state["source_state"])
         else:
             self.node.reset()

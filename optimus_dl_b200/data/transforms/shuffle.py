@@ -13,7 +13,7 @@ from torchdata.nodes import BaseNode
 
 from ...core.registry import RegistryConfigStrict
 from . import register_transform
-from .base import BaseTransform
+from .base import BaseTransform, adopt_saved_cfg
 
 
 @dataclass
@@ -44,7 +44,7 @@ class ShuffleNode(BaseNode):
         self.rng = np.random.default_rng(self._default_seed)
         if initial_state:
             self.buffer = copy.deepcopy(initial_state["buffer"])
-            self.cfg = initial_state.get("cfg", self.cfg)
+            self.cfg = adopt_saved_cfg(self.cfg, initial_state.get("cfg"))
             self.rng.bit_generator.state = initial_state["rng_state"]
             self.terminated = bool(initial_state["terminated"])
             assert initial_state.get("rank", self.rank) == self.rank, "shuffle state belongs to another rank"

@@ -38,6 +38,24 @@ def _to_tensor(batch: Any) -> Any:
     return batch
 
 
+class _StatelessMap(BaseNode):
+    """``fn`` applied to every item; the state IS the source's state (no ``source`` level of its own)."""
+
+    def __init__(self, source: BaseNode, fn: Any):
+        super().__init__()
+        self.source, self.fn = source, fn
+
+    def reset(self, initial_state: dict | None = None):
+        super().reset(initial_state)
+        self.source.reset(initial_state)
+
+    def get_state(self) -> dict[str, Any]:
+        return self.source.state_dict()
+
+    def next(self) -> Any:
+        return self.fn(next(self.source))
+
+
 class _Mover:
     def __init__(self, device: torch.device, non_blocking: bool):
         self.device, self.non_blocking = device, non_blocking
@@ -73,19 +91,27 @@ class ToDeviceTransform(BaseTransform):
         return _Mover(self.device, bool(self.cfg.non_blocking))(_to_tensor(sample))
 
     def build(self, source: BaseNode) -> BaseNode:
+        """CPU: one ``Mapper``. CUDA: ``PinMemory`` -> ``Mapper`` (asynchronous copy) -> ``Prefetcher``, the chain of
+        optimus_dl/modules/data/transforms/to_device.py:92-119; the conversion of numpy arrays to tensors that has to
+        precede pinning (``PinMemory`` leaves arrays as they are) is a node that adds no level to the checkpointed
+        state, so states nest alike in both code bases."""
         props = list(self.properties) if self.properties is not None else None
         if props is None:
-            node: BaseNode = Mapper(source, _to_tensor)
+            convert = _to_tensor
         else:
-            node = Mapper(source, lambda b, _p=frozenset(props): {k: (_to_tensor(v) if k in _p else v) for k, v in b.items()}
-                          if isinstance(b, dict) else _to_tensor(b))
+            convert = lambda b, _p=frozenset(props): ({k: (_to_tensor(v) if k in _p else v) for k, v in b.items()}  # noqa: E731
+                                                      if isinstance(b, dict) else _to_tensor(b))
         depth = self.cfg.pin_prefetch_factor if self.cfg.pin_prefetch_factor is not None else self.cfg.prefetch_factor
-        if self.device.type == "cuda":
+        if self.device.type == "cpu":
+            node: BaseNode = Mapper(source, convert)
+        elif self.device.type != "cuda":
+            mover = _Mover(self.device, False)
+            node = Mapper(source, lambda b: mover(convert(b)))
+        else:
+            node = _StatelessMap(source, convert)
             if self.cfg.pin_memory:
-                node = PinMemory(node, pin_memory_device="cuda")
+                node = PinMemory(node, pin_memory_device="cuda", snapshot_frequency=int(self.cfg.pin_snapshot_frequency))
             node = Mapper(node, _Mover(self.device, bool(self.cfg.non_blocking)))
             if depth and depth > 0:
                 node = Prefetcher(node, prefetch_factor=int(depth), snapshot_frequency=int(self.cfg.pin_snapshot_frequency))
-        elif self.device.type != "cpu":
-            node = Mapper(node, _Mover(self.device, False))
         return node

@@ -7,7 +7,7 @@ import logging
 from dataclasses import dataclass, field
 from typing import Any
 
-from torchdata.nodes import BaseNode, Mapper, ParallelMapper
+from torchdata.nodes import BaseNode, ParallelMapper
 
 from ...core.registry import RegistryConfig
 from ...tokenizer import build_tokenizer       # module-level so that callers can substitute the factory
@@ -70,9 +70,10 @@ class TokenizeTransform(BaseTransform):
         return self._fn(item)
 
     def build(self, source: BaseNode) -> BaseNode:
-        fn = self._callable()
+        """Always a ``ParallelMapper`` with the configured worker settings (it maps inline when ``num_workers`` is 0), as
+        optimus_dl/modules/data/transforms/tokenize.py:97-103 builds it: the node's checkpointed state then nests
+        the same way in both code bases."""
         w = self.cfg.worker_cfg
-        if not w.num_workers:
-            return Mapper(source, fn)
-        return ParallelMapper(source, fn, num_workers=int(w.num_workers), in_order=bool(w.in_order), method=w.method,
-                              snapshot_frequency=int(w.snapshot_frequency), prebatch=w.prebatch)
+        return ParallelMapper(source=source, map_fn=self._callable(), num_workers=int(w.num_workers),
+                              in_order=bool(w.in_order), method=w.method, snapshot_frequency=int(w.snapshot_frequency),
+                              prebatch=w.prebatch)
