@@ -563,3 +563,52 @@ def test_node_states_use_the_reference_keys_and_the_shuffle_stream_is_the_refere
     lp.reset()
     assert [next(lp)["text"] for _ in range(4)] == ["line 0", "line 1", "line 2", "line 0"]
     assert set(lp.state_dict()) == {"rank", "world_size", "epoch", "inner_state"}
+
+
+def test_to_device_cuda_chain_order_and_state_nesting(monkeypatch):
+    """On a CUDA device the chain is conversion (no state level of its own) -> ``PinMemory`` -> ``Mapper`` (copy) ->
+    ``Prefetcher``, with the configured snapshot frequency and prefetch depth
+    (optimus_dl/modules/data/transforms/to_device.py:92-119). Built here with stand-ins for the two nodes that need a
+    GPU; the copy itself is replaced by an identity."""
+    import optimus_dl_b200.data.transforms.to_device as td
+
+    calls = []
+
+    class Pass(tn.BaseNode):
+        def __init__(self, source, **kw):
+            super().__init__()
+            self.source, self.kw = source, kw
+            calls.append((type(self).__name__, kw))
+
+        def reset(self, initial_state=None):
+            super().reset(initial_state)
+            self.source.reset(initial_state["source"] if initial_state else None)
+
+        def get_state(self):
+            return {"source": self.source.state_dict()}
+
+        def next(self):
+            return next(self.source)
+
+    class FakePin(Pass):
+        pass
+
+    class FakePrefetch(Pass):
+        pass
+
+    monkeypatch.setattr(td, "PinMemory", FakePin)
+    monkeypatch.setattr(td, "Prefetcher", FakePrefetch)
+    monkeypatch.setattr(td._Mover, "__call__", lambda self, b: b)
+    t = build_transform({"_name": "to_device", "pin_prefetch_factor": 3, "pin_snapshot_frequency": 77}, device=torch.device("cuda", 0))
+    node = t.build(_Range(5, lambda i: {"input_ids": np.array([i, i + 1], dtype=np.uint16), "n": i}))
+    assert [c[0] for c in calls] == ["FakePin", "FakePrefetch"]
+    assert calls[0][1] == {"pin_memory_device": "cuda", "snapshot_frequency": 77}
+    assert calls[1][1] == {"prefetch_factor": 3, "snapshot_frequency": 77}
+    node.reset()
+    first = next(node)
+    assert first["input_ids"].dtype == torch.int64 and first["input_ids"].tolist() == [0, 1] and first["n"] == 0
+    st = node.state_dict()
+    # prefetch -> mapper -> pin -> (conversion: transparent) -> source
+    assert st == {"source": {"it_state": {"source": {"source": {"i": 1}}}}}
+    node.reset(st)
+    assert next(node)["input_ids"].tolist() == [1, 2]
