@@ -143,7 +143,7 @@ def optimizer_state_dict(model: nn.Module, optimizer: Any, mesh: Any = None) -> 
         # fresh optimizer can be filled in place by a checkpoint load
         from torch.distributed.checkpoint.state_dict import get_optimizer_state_dict
 
-        return get_optimizer_state_dict(model, optimizer)
+        return _with_reference_group_keys(get_optimizer_state_dict(model, optimizer), adamw=False)
     use_mesh = mesh if eng.world > 1 else None
     state: dict[str, Any] = {}
     for name, g, inf in eng.named_sharded_state():
@@ -159,7 +159,26 @@ def optimizer_state_dict(model: nn.Module, optimizer: Any, mesh: Any = None) -> 
         d = {k: v for k, v in pg.items() if k != "params"}
         d["params"] = [names[id(p)] for p in pg["params"]]
         groups.append(d)
-    return {"state": state, "param_groups": groups}
+    return _with_reference_group_keys({"state": state, "param_groups": groups}, adamw=True)
+
+
+# what ``torch.optim.AdamW`` keeps in every parameter group; the reference's optimizer is that class, and a
+# distributed-checkpoint load into it asks the checkpoint for each of these keys
+_TORCH_ADAMW_GROUP_DEFAULTS = {"amsgrad": False, "maximize": False, "foreach": None, "capturable": False,
+                               "differentiable": False, "fused": True, "decoupled_weight_decay": True}
+
+
+def _with_reference_group_keys(sd: dict[str, Any], adamw: bool) -> dict[str, Any]:
+    """Parameter groups as the reference writes them: ``param_names`` beside ``params`` (torch records the names of
+    parameters that were handed over as ``(name, parameter)`` pairs, which the reference does), and for this
+    package's own AdamW the remaining keys of ``torch.optim.AdamW`` groups, so that either code base can load the
+    other's optimizer state."""
+    for g in sd.get("param_groups", []):
+        g.setdefault("param_names", list(g.get("params", [])))
+        if adamw:
+            for k, v in _TORCH_ADAMW_GROUP_DEFAULTS.items():
+                g.setdefault(k, v)
+    return sd
 
 
 def load_optimizer_state_dict(model: nn.Module, optimizer: Any, sd: dict[str, Any]) -> None:

@@ -118,6 +118,13 @@ def test_full_round_trip_restores_model_optimizer_schedule_loaders_and_meters(tm
     torch.manual_seed(5)
     _train(m2, o2, s2, 1)
     assert all(torch.equal(a, b) for a, b in zip(model.state_dict().values(), m2.state_dict().values()))
+    # what the reference's loader asks a checkpoint for: every parameter group carries ``param_names`` beside
+    # ``params`` (torch records them for optimizers built from named parameters, which the reference's are)
+    from optimus_dl_b200.parallel import state as pstate
+
+    exported = pstate.optimizer_state_dict(model, opt, None)
+    assert all(g["param_names"] == g["params"] and g["params"] for g in exported["param_groups"])
+    assert set(exported["state"]) == {n for n, _ in model.named_parameters()}
 
 
 def test_load_strategy_switches_each_part_off(tmp_path):
