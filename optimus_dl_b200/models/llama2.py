@@ -56,8 +56,10 @@ class Llama(GPT):
         self._freqs_cache: dict = {}
         super().__init__(config)
         if getattr(config, "zero_init_projections", False):
+            # the feed-forward output projections start at zero; the attention output projection keeps its scaled
+            # normal initialisation (optimus_dl/modules/model/llama2.py:196-213)
             for name, p in self.named_parameters():
-                if name.endswith("c_proj.weight") or name.endswith("wo.weight"):
+                if name.endswith("c_proj.weight"):
                     nn.init.zeros_(p)
         self.head_dim = self._head_dim(config)
         self.freqs_cis = self._make_freqs(config)
