@@ -168,15 +168,18 @@ def get_group(name: str) -> MeterGroup | None:
 
 
 def compute_meters(name: str, aggregate: bool = False, collective: Any = None) -> dict[str, Any]:
-    """Values of group ``name``; with ``aggregate`` every rank's meter states are merged first."""
+    """Values of group ``name``; with ``aggregate`` (and a collective) every rank's meter states are merged first.
+    Aggregated values come from freshly built meters and therefore carry no rounding, whatever ``round`` the logging
+    call named: that is what optimus_dl/modules/metrics/base.py:531-556 reports (a one-rank collective included), and
+    so what ends up in the logs of a training run."""
     g = _meter_groups.get(name)
     if g is None:
         local_states: dict[str, Any] = {}
     else:
         local_states = {k: e.state_dict() for k, e in g.meters.items()}
-    if not aggregate or collective is None or collective.world_size == 1:
+    if not aggregate or collective is None:
         return g.compute() if g is not None else {}
-    all_states = collective.all_gather_objects(local_states)
+    all_states = [local_states] if collective.world_size == 1 else collective.all_gather_objects(local_states)
     merged: "OrderedDict[str, MeterEntry]" = OrderedDict()
     for rank_states in all_states:
         for k, sd in rank_states.items():
@@ -190,6 +193,8 @@ def compute_meters(name: str, aggregate: bool = False, collective: Any = None) -
                       "priority": local.priority}
             if k not in merged:
                 merged[k] = MeterEntry.from_state_dict(sd)
+                if getattr(merged[k].meter, "round", None) is not None:
+                    merged[k].meter.round = None
             else:
                 merged[k].meter.merge(sd["meter"])
     ordered = sorted(merged.items(), key=lambda kv: (kv[1].priority, kv[0]))

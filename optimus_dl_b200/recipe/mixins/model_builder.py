@@ -16,7 +16,7 @@ import torch
 
 from ...core.model_utils import get_num_parameters
 from ...core.registry import RegistryConfig, make_registry
-from ...metrics.common import log_summed
+from ...metrics.common import log_averaged, log_summed
 from ...model_transforms import build_model_transform
 from ...models import build_model
 
@@ -51,8 +51,12 @@ class ModelBuilder:
         logger.info("model has %.2fM parameters (%.2fM trainable)", n_all / 1e6, n_train / 1e6)
         log_summed("model/num_params_total", n_all, reset=False)
         log_summed("model/num_params_trainable", n_train, reset=False)
-        return self.apply_transforms(model, collective=collective, device=device, is_restart=is_restart,
-                                     checkpoint_manager=checkpoint_manager)
+        # the two meters of optimus_dl/recipe/mixins/model_builder.py:74-86 (averaged over ranks)
+        log_averaged("model/num_params_before_transforms", n_all)
+        model = self.apply_transforms(model, collective=collective, device=device, is_restart=is_restart,
+                                      checkpoint_manager=checkpoint_manager)
+        log_averaged("model/num_params_after_transforms", lambda: get_num_parameters(model))
+        return model
 
     def apply_transforms(self, model: torch.nn.Module, **kwargs: Any) -> torch.nn.Module:
         for tcfg in self.model_transforms:

@@ -194,7 +194,7 @@ class TrainRecipe(TrainingContextMixin, TrainingIterationMixin, TrainingInterrup
             log_event_end("perf/init")
         init_metrics = compute_meters("init", aggregate=True, collective=collective)
         if collective.is_master and init_metrics:
-            self.logger_manager.log_metrics_to_loggers(init_metrics, start_iteration - 1, "init")
+            self.logger_manager.log_metrics_to_loggers(init_metrics, start_iteration, "init")
         train_iter = iter(train_loader) if train_loader is not None else None
         engine_cfg = cfg.metrics.get("train") if cfg.metrics else None
         metric_engine = MetricEngine("train", engine_cfg) if engine_cfg else None

@@ -27,7 +27,9 @@ class DataBuilderConfig(RegistryConfig):
 def per_rank_seed(seed: int, rank: int, world_size: int) -> int:
     g = torch.Generator()
     g.manual_seed(int(seed) + world_size * 10000 + rank)
-    return int(torch.randint(0, 2**31 - 1, (1,), generator=g).item())
+    # the same draw as optimus_dl/recipe/train/builders/data_builder.py:51-57, so that one ``data_seed`` gives one
+    # data order in both code bases
+    return int(torch.randint(0, 2**32, (1,), generator=g).item())
 
 
 class LoaderIterResettable:

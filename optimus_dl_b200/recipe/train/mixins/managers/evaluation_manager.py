@@ -160,8 +160,9 @@ class Evaluator:
             requested = engine.required_external_protocols if engine is not None else None
             while max_iters is None or processed < max_iters:
                 exhausted, batch = 0, None
+                elapsed_batch_get = 0.0
                 try:
-                    _, batch = measured_next(data_iter)
+                    elapsed_batch_get, batch = measured_next(data_iter)
                 except StopIteration:
                     exhausted = 1
                 if world > 1 and not same:
@@ -176,6 +177,7 @@ class Evaluator:
                 if engine is not None:
                     engine.update(dict(model=model, batch=batch), exposed)
                 log_event_end("perf/full_iteration")
+                log_averaged("perf/batch_get", elapsed_batch_get)
                 log_summed("num_batches", lambda: 1)
                 step_meters(group)
                 processed += 1
