@@ -1,0 +1,343 @@
+"""Worker of tests/test_reference_differential.py: imports the UNMODIFIED reference (baseline/_ref, with the stand-in
+third-party modules of baseline/ref_deps) next to this package in one CPU process and compares the two on the same
+inputs. ``python tests/_ref_diff_worker.py <check>`` prints ``DIFF_OK <check>`` or raises."""
+
+import importlib
+import json
+import os
+import sys
+import tempfile
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path[:0] = [os.path.join(ROOT, "baseline", "ref_deps"), os.path.join(ROOT, "baseline", "_ref"), ROOT]
+
+import logging  # noqa: E402
+
+logging.disable(logging.INFO)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+import optimus_dl  # noqa: E402,F401
+from omegaconf import OmegaConf  # noqa: E402
+
+
+def R(mod: str):
+    return importlib.import_module("optimus_dl.modules." + mod)
+
+
+MODELS = {
+    "gpt2": dict(_name="gpt2", n_layer=2, n_head=4, n_embd=64, vocab_size=97, block_size=64, bias=True),
+    "llama2": dict(_name="llama2", n_layer=2, n_head=4, n_kv_head=2, n_embd=64, vocab_size=97, sequence_length=64, multiple_of=8),
+    "llama2_qknorm": dict(_name="llama2", n_layer=2, n_head=4, n_kv_head=2, n_embd=64, vocab_size=97, sequence_length=64,
+                          multiple_of=8, use_qk_norm=True),
+    "qwen3": dict(_name="qwen3", n_layer=2, n_head=4, n_kv_head=2, n_embd=64, head_dim=32, vocab_size=97, sequence_length=64,
+                  intermediate_size=96),
+    "olmo3": dict(_name="olmo3", n_layer=2, n_head=4, n_kv_head=2, n_embd=64, vocab_size=97, sequence_length=64,
+                  intermediate_size=96, layer_types=["sliding_attention", "full_attention"], sliding_window=8),
+}
+
+
+def _pair(cfg):
+    import optimus_dl_b200.models as om
+
+    torch.manual_seed(0)
+    ref = R("model").build_model(OmegaConf.create(cfg))
+    ours = om.build_model(dict(cfg))
+    assert set(ref.state_dict()) == set(ours.state_dict()), sorted(set(ref.state_dict()) ^ set(ours.state_dict()))[:5]
+    ours.load_state_dict(ref.state_dict())
+    return ref, ours
+
+
+def check_models() -> None:
+    """Same weights -> same logits (plain and packed batches), same parameter groups, for every model family."""
+    for name, cfg in MODELS.items():
+        ref, ours = _pair(cfg)
+        ref.eval(), ours.eval()
+        x = torch.randint(0, 97, (2, 24))
+        docs = torch.tensor([[0] * 10 + [1] * 14, [0] * 24])
+        pos = torch.stack([torch.cat([torch.arange(10), torch.arange(14)]), torch.arange(24)])
+        with torch.no_grad():
+            assert torch.allclose(ref(x)["logits"], ours(x)["logits"], atol=2e-6), name
+            if name != "gpt2":       # the reference's GPT-2 ignores document and position ids
+                a = ref(x, document_ids=docs, position_ids=pos)["logits"]
+                b = ours(x, document_ids=docs, position_ids=pos)["logits"]
+                assert torch.allclose(a, b, atol=2e-6), name
+
+        def sig(groups):
+            return [(tuple(sorted(k for k in g if k != "params")), len(g["params"]), g.get("weight_decay")) for g in groups]
+
+        assert sig(ref.make_parameter_groups()) == sig(ours.make_parameter_groups()), name
+
+
+def check_train_parts() -> None:
+    """Criterion loss and meters; AdamW / SOAP with every schedule, step by step, from the same gradients."""
+    import optimus_dl_b200.criterion as oc
+    import optimus_dl_b200.lr_scheduler as ol
+    import optimus_dl_b200.optim as oo
+    from optimus_dl_b200.metrics import base as omb
+    from optimus_dl_b200.parallel.collective import FakeCollective
+
+    rmb = importlib.import_module("optimus_dl.modules.metrics")
+    ref, ours = _pair(MODELS["llama2"])
+    rfake = importlib.import_module("optimus_dl.modules.distributed.fake").FakeCollective(0, 1)
+    for ccfg in (dict(_name="cross_entropy"), dict(_name="cross_entropy", label_smoothing=0.1),
+                 dict(_name="cross_entropy", padding_token_id=5)):
+        rc = R("criterion").build_criterion(OmegaConf.create(ccfg), collective=rfake)
+        c = oc.build_criterion(dict(ccfg), collective=FakeCollective(0, 1, torch.device("cpu")))
+        x = torch.randint(0, 97, (3, 20))
+        with rmb.meters_group("g", log_freq=1):
+            rl, _ = rc(ref, {"input_ids": x.clone()})
+        with omb.meters_group("g", log_freq=1):
+            l, _ = c(ours, {"input_ids": x.clone()})
+        assert abs(rl.item() - l.item()) < 1e-6, ccfg
+        a, b = rmb.compute_meters("g"), omb.compute_meters("g")
+        a.pop("ms_spent_logging", None), b.pop("ms_spent_logging", None)
+        assert set(a) == set(b), (sorted(a), sorted(b))
+        assert all(abs(float(a[k]) - float(b[k])) <= 1e-6 * max(1.0, abs(float(a[k]))) for k in a), (ccfg, a, b)
+        rmb.reset_meters("g"), omb.reset_meters("g")
+    for ocfg in (dict(_name="adamw", lr=1e-2, weight_decay=0.1), dict(_name="soap", lr=1e-2, weight_decay=0.01, precondition_frequency=2)):
+        for scfg in (None, dict(_name="wsd", warmup_steps=2, fract_decay=0.5), dict(_name="cosine_annealing"),
+                     dict(_name="linear_warmup", warmup_steps=3)):
+            ref, ours = _pair(MODELS["llama2"])
+            ro = R("optim").build_optimizer(OmegaConf.create(ocfg), params=ref.make_parameter_groups())
+            o = oo.build_optimizer(dict(ocfg), params=ours.make_parameter_groups())
+            rs = R("lr_scheduler").build_lr_scheduler(OmegaConf.create(scfg), optimizer=ro, iterations=4) if scfg else None
+            s = ol.build_lr_scheduler(dict(scfg), optimizer=o, iterations=4) if scfg else None
+            g = torch.Generator().manual_seed(1)
+            for _ in range(4):
+                x = torch.randint(0, 97, (8, 32), generator=g)
+                ref(x)["logits"].float().logsumexp(-1).mean().backward()
+                for p, q in zip(ref.parameters(), ours.parameters()):     # the same gradients for both optimizers
+                    q.grad = p.grad.clone()
+                ro.step(), o.step(), ro.zero_grad(), o.zero_grad()
+                if rs is not None:
+                    rs.step(), s.step()
+                assert [gr["lr"] for gr in ro.param_groups] == [gr["lr"] for gr in o.param_groups]
+            worst = max((p - q).abs().max().item() for p, q in zip(ref.parameters(), ours.parameters()))
+            assert worst < (1e-7 if ocfg["_name"] == "adamw" else 1e-4), (ocfg["_name"], scfg, worst)
+
+
+def _corpus(tmp: str) -> tuple[str, str]:
+    txt = os.path.join(tmp, "t.txt")
+    with open(txt, "w") as f:
+        for i in range(400):
+            f.write(("line %d " % i) + "abcdefghij" * (i % 7 + 1) + "\n")
+    tok = os.path.join(tmp, "tok")
+    os.makedirs(tok)
+    rng, c, files = np.random.default_rng(0), 0, []
+    for s in range(3):
+        lens = rng.integers(5, 60, size=20)
+        np.save(os.path.join(tok, f"s_{s:010d}.npy"), np.arange(c, c + lens.sum(), dtype=np.uint16))
+        np.save(os.path.join(tok, f"s_{s:010d}_lens.npy"), lens.astype(np.uint32))
+        files.append({"file": f"s_{s:010d}.npy", "lens_file": f"s_{s:010d}_lens.npy", "num_tokens": int(lens.sum()),
+                      "num_docs": len(lens), "shard_idx": s})
+        c += int(lens.sum())
+    json.dump({"files": files, "total_tokens": c, "config": {"dtype": "np.uint16"}}, open(os.path.join(tok, "index.json"), "w"))
+    return txt, tok
+
+
+def _same(a, b) -> bool:
+    if isinstance(a, dict):
+        return isinstance(b, dict) and a.keys() == b.keys() and all(_same(a[k], b[k]) for k in a)
+    if isinstance(a, (np.ndarray, torch.Tensor)) or isinstance(b, (np.ndarray, torch.Tensor)):
+        return np.array_equal(np.asarray(a), np.asarray(b))
+    return a == b
+
+
+def check_data() -> None:
+    """Pipelines built from one config hand out identical batches, and each resumes from the other's state."""
+    import optimus_dl_b200.data as od
+
+    rd = R("data")
+    txt, tok = _corpus(tempfile.mkdtemp())
+
+    def chain(bs):
+        return {"_name": "compose", "transforms": [
+            {"_name": "tokenize", "tokenizer_config": {"_name": "char_tokenize"}, "worker_cfg": {"num_workers": 0}},
+            {"_name": "chunk_tokens", "max_seq_len": 32}, {"_name": "shuffle", "buffer_size": 16},
+            {"_name": "flat_batcher", "batch_size": bs, "seq_len": 32, "mask_documents": True}]}
+
+    pipes = {
+        "txt+loop": {"source": {"_name": "loop", "inner": {"_name": "txt_lines", "file_link": txt}}, "transform": chain(2)},
+        "documents shuffled, flat": {
+            "source": {"_name": "tokenized_dataset", "data_dir": tok, "strategy": {"_name": "document", "shuffle": True}},
+            "transform": {"_name": "compose", "transforms": [
+                {"_name": "shuffle", "buffer_size": 8},
+                {"_name": "flat_batcher", "batch_size": 2, "seq_len": 16, "mask_documents": True, "flatten": True}]}},
+        "skips + padded batches": {
+            "source": {"_name": "tokenized_dataset", "data_dir": tok, "strategy": {"_name": "document"}},
+            "transform": {"_name": "compose", "transforms": [
+                {"_name": "skip_random", "probability": 0.3}, {"_name": "skip_interleaved", "skip_count": 1},
+                {"_name": "basic_batcher", "batch_size": 3, "pad_token_id": 0}]}},
+        "composite": {"source": {"_name": "composite", "stop_criteria": "CYCLE_FOREVER", "datasets": {
+            "a": {"dataset": {"_name": "txt_lines", "file_link": txt}, "weight": 1.0, "cycle": True},
+            "b": {"dataset": {"_name": "loop", "inner": {"_name": "txt_lines", "file_link": txt}}, "weight": 3.0, "cycle": True}}},
+            "transform": chain(1)},
+    }
+    for name, cfg in pipes.items():
+        for rank, world in ((0, 1), (1, 3)):
+            def build(ref: bool):
+                if ref:
+                    return rd.build_data_pipeline(OmegaConf.create({**cfg, "profile": False, "report_freq": 100}), rank=rank,
+                                                  world_size=world, seed=13).dataloader
+                return od.build_data_pipeline(dict(cfg), rank=rank, world_size=world, seed=13).dataloader
+
+            r, o = build(True), build(False)
+            r.reset(), o.reset()
+            n = 0
+            for _ in range(12):
+                try:
+                    a = next(r)
+                except StopIteration:
+                    a = None
+                try:
+                    b = next(o)
+                except StopIteration:
+                    b = None
+                assert (a is None) == (b is None) and (a is None or _same(a, b)), (name, rank, world, n)
+                if a is None:
+                    break
+                n += 1
+            if a is None:
+                continue
+            r2, o2 = build(True), build(False)
+            r2.reset(o.state_dict()), o2.reset(r.state_dict())
+            want = next(r)
+            assert _same(next(r2), want) and _same(next(o2), want), (name, rank, world, "resume from the other's state")
+
+
+def check_checkpoints() -> None:
+    """A checkpoint written by either manager loads in the other; both then continue bit-identically."""
+    import optimus_dl_b200.lr_scheduler as ol
+    import optimus_dl_b200.models as om
+    import optimus_dl_b200.optim as oo
+    from optimus_dl_b200.checkpoint import CheckpointManager as OurCM
+    from optimus_dl_b200.parallel.collective import FakeCollective as OurFake
+
+    ck = R("checkpoint")
+    rfake = importlib.import_module("optimus_dl.modules.distributed.fake").FakeCollective
+    cfg, ocfg, scfg = MODELS["llama2"], dict(_name="adamw", lr=1e-2, weight_decay=0.1), dict(_name="wsd", warmup_steps=2, fract_decay=0.5)
+
+    def make(ref: bool):
+        torch.manual_seed(0)
+        if ref:
+            m = R("model").build_model(OmegaConf.create(cfg))
+            o = R("optim").build_optimizer(OmegaConf.create(ocfg), params=m.make_parameter_groups())
+            return m, o, R("lr_scheduler").build_lr_scheduler(OmegaConf.create(scfg), optimizer=o, iterations=10)
+        m = om.build_model(dict(cfg))
+        m.load_state_dict(make(True)[0].state_dict())
+        o = oo.build_optimizer(dict(ocfg), params=m.make_parameter_groups())
+        return m, o, ol.build_lr_scheduler(dict(scfg), optimizer=o, iterations=10)
+
+    def train(m, o, s, n, seed):
+        g = torch.Generator().manual_seed(seed)
+        for _ in range(n):
+            x = torch.randint(0, 97, (4, 16), generator=g)
+            loss = m(x)["logits"].float().logsumexp(-1).mean()
+            o.zero_grad(), loss.backward(), o.step(), s.step()
+
+    for from_ref in (True, False):
+        d = tempfile.mkdtemp()
+        m, o, s = make(from_ref)
+        train(m, o, s, 3, seed=1)
+        if from_ref:
+            ck.CheckpointManager(ck.CheckpointManagerConfig(_name="base")).save_checkpoint(
+                checkpoint_path=d, model=m, optimizer=o, lr_scheduler=s, collective=rfake(0, 1), full_config={"model": cfg},
+                iteration=3, is_save_persistent=True, is_save_last=True)
+            m2, o2, s2 = make(False)
+            OurCM(output_path=d).load_checkpoint(d, model=m2, optimizer=o2, lr_scheduler=s2,
+                                                 collective=OurFake(0, 1, torch.device("cpu")))
+        else:
+            OurCM(output_path=d).save_checkpoint(iteration=3, model=m, optimizer=o, lr_scheduler=s,
+                                                 collective=OurFake(0, 1, torch.device("cpu")), full_config={"model": cfg})
+            m2, o2, s2 = make(True)
+            ck.CheckpointManager(ck.CheckpointManagerConfig(_name="base")).load_checkpoint(
+                checkpoint_path=d, model=m2, optimizer=o2, lr_scheduler=s2, collective=rfake(0, 1))
+        train(m, o, s, 2, seed=5), train(m2, o2, s2, 2, seed=5)
+        assert all(torch.equal(p, q) for p, q in zip(m.parameters(), m2.parameters())), from_ref
+        assert o.param_groups[0]["lr"] == o2.param_groups[0]["lr"]
+
+
+def check_recipe() -> None:
+    """The whole training recipe (8 iterations, evaluation every 4, checkpoints) from one composed config and the
+    same initial weights: every number either side logs (loss, perplexity, accuracy, gradient norm, learning rate,
+    token counts, metric-engine values; train and eval groups) agrees."""
+    import glob
+
+    from optimus_dl_b200.core import compose, conf
+
+    tmp = tempfile.mkdtemp()
+    data = os.path.join(tmp, "data.txt")
+    with open(data, "w") as f:
+        for i in range(600):
+            f.write(f"Line {i}: This is some dummy text for training Llama, number {i * i}.\n")
+
+    def overrides(which):
+        return [f"common.output_path={tmp}/{which}", "optimization.iterations=8", "common.save_freq=4", "common.log_freq=1",
+                "common.eval_freq=4", "++common.eval_iterations=2", "++common.use_gpu=false", "~model_transforms",
+                "optimization.amp.enabled=false", "data.train_datasets.source.inner._name=txt_lines",
+                f"+data.train_datasets.source.inner.file_link={data}", "data.eval_datasets.tinyshakespeare.source._name=txt_lines",
+                f"+data.eval_datasets.tinyshakespeare.source.file_link={data}", "++common.seed=42", "++common.data_seed=42",
+                "++common.deterministic=true", "++model.n_layer=1", "++model.n_head=2", "++model.n_embd=32",
+                "++model.intermediate_size=64", "lr_scheduler.warmup_steps=0", "args.batch_size=4", "args.seq_len=64",
+                "loggers.1.enabled=false", f"loggers.0.output_dir={tmp}/{which}/logs"]
+
+    cfg_dir = os.path.join(ROOT, "configs", "train")
+    init_file = os.path.join(tmp, "init.pt")
+    # the reference's recipe, on the fully resolved config (its own instantiate step needs OmegaConf internals)
+    import optimus_dl.recipe.train.base  # noqa: F401
+    from optimus_dl.core.registry import build as ref_build
+    import optimus_dl_b200.core.config_utils  # noqa: F401  (registers the resolvers the config uses)
+
+    plain = conf.to_container(compose.compose(cfg_dir, "train_llama_shakespeare", overrides("ref")), resolve=True)
+    for k in ("model_builder", "optimizer_builder", "criterion_builder", "data_builder", "scheduler_builder", "logger_manager",
+              "checkpoint_manager", "evaluator"):
+        plain[k] = {**(plain.get(k) or {})}
+        if plain[k].get("_name") is None:
+            plain[k]["_name"] = "base"
+    plain.setdefault("model_transforms", [])
+    recipe = ref_build("train_recipe", OmegaConf.create(plain))
+    orig = recipe.build_model
+
+    def keep_initial_weights(*a, **k):
+        m = orig(*a, **k)
+        torch.save({n: v.detach().clone() for n, v in m.state_dict().items()}, init_file)
+        return m
+
+    recipe.build_model = keep_initial_weights
+    recipe.run()
+    # this package's recipe, started from the same weights
+    from optimus_dl_b200.core.config_utils import non_resolving_instantiate
+    from optimus_dl_b200.core.registry import build
+    import optimus_dl_b200.recipe.train  # noqa: F401
+
+    cfg = compose.compose(cfg_dir, "train_llama_shakespeare", overrides("ours"))
+    cfg.model_transforms = [{"_name": "load_weights", "checkpoint_path": init_file}]
+    build("train_recipe", non_resolving_instantiate(cfg)).run()
+
+    def logs(which):
+        out = {}
+        for f in sorted(glob.glob(f"{tmp}/{which}/logs/**/*.jsonl", recursive=True)):
+            for line in open(f):
+                r = json.loads(line)
+                out.setdefault((r["group"], r["step"]), {}).update({k: v for k, v in r.items() if k != "timestamp"})
+        return out
+
+    r, o = logs("ref"), logs("ours")
+    assert set(r) == set(o), (sorted(r, key=str), sorted(o, key=str))
+    assert ("train", 8) in r and ("eval/tinyshakespeare", 8) in r and ("init", 1) in r
+    ours_only = {"optimizer_step_skipped", "model/num_params_total", "model/num_params_trainable"}
+    for key in r:
+        a, b = r[key], o[key]
+        assert set(a) <= set(b) and set(b) - set(a) <= ours_only, (key, sorted(set(a) ^ set(b)))
+        for k, v in a.items():
+            if k.startswith("perf/") or k == "ms_spent_logging" or not isinstance(v, (int, float)):
+                continue
+            assert abs(v - b[k]) <= 1e-5 * max(1.0, abs(v)), (key, k, v, b[k])
+
+
+if __name__ == "__main__":
+    name = sys.argv[1]
+    globals()["check_" + name]()
+    print("DIFF_OK", name, flush=True)
