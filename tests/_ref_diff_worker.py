@@ -259,7 +259,18 @@ def check_checkpoints() -> None:
         assert o.param_groups[0]["lr"] == o2.param_groups[0]["lr"]
 
 
-def check_recipe() -> None:
+def check_recipe_accumulation() -> None:
+    """The recipe with two accumulation steps, gradient clipping and bf16 autocast."""
+    check_recipe(extra=["optimization.acc_steps=2", "optimization.clip_grad_norm=0.5", "optimization.amp.enabled=true"], tol=1e-3)
+
+
+def check_recipe_resume() -> None:
+    """Four iterations, then a second run on the same output directory that resumes from the checkpoint (model,
+    optimizer, schedule, data position, meters) and continues to eight."""
+    check_recipe(phases=[["optimization.iterations=4"], ["optimization.iterations=8"]])
+
+
+def check_recipe(extra: list[str] | None = None, tol: float = 1e-5, phases: list[list[str]] | None = None) -> None:
     """The whole training recipe (8 iterations, evaluation every 4, checkpoints) from one composed config and the
     same initial weights: every number either side logs (loss, perplexity, accuracy, gradient norm, learning rate,
     token counts, metric-engine values; train and eval groups) agrees."""
@@ -281,7 +292,7 @@ def check_recipe() -> None:
                 f"+data.eval_datasets.tinyshakespeare.source.file_link={data}", "++common.seed=42", "++common.data_seed=42",
                 "++common.deterministic=true", "++model.n_layer=1", "++model.n_head=2", "++model.n_embd=32",
                 "++model.intermediate_size=64", "lr_scheduler.warmup_steps=0", "args.batch_size=4", "args.seq_len=64",
-                "loggers.1.enabled=false", f"loggers.0.output_dir={tmp}/{which}/logs"]
+                "loggers.1.enabled=false", f"loggers.0.output_dir={tmp}/{which}/logs"] + list(extra or [])
 
     cfg_dir = os.path.join(ROOT, "configs", "train")
     init_file = os.path.join(tmp, "init.pt")
@@ -290,31 +301,34 @@ def check_recipe() -> None:
     from optimus_dl.core.registry import build as ref_build
     import optimus_dl_b200.core.config_utils  # noqa: F401  (registers the resolvers the config uses)
 
-    plain = conf.to_container(compose.compose(cfg_dir, "train_llama_shakespeare", overrides("ref")), resolve=True)
-    for k in ("model_builder", "optimizer_builder", "criterion_builder", "data_builder", "scheduler_builder", "logger_manager",
-              "checkpoint_manager", "evaluator"):
-        plain[k] = {**(plain.get(k) or {})}
-        if plain[k].get("_name") is None:
-            plain[k]["_name"] = "base"
-    plain.setdefault("model_transforms", [])
-    recipe = ref_build("train_recipe", OmegaConf.create(plain))
-    orig = recipe.build_model
+    for i, phase in enumerate(phases or [[]]):
+        plain = conf.to_container(compose.compose(cfg_dir, "train_llama_shakespeare", overrides("ref") + phase), resolve=True)
+        for k in ("model_builder", "optimizer_builder", "criterion_builder", "data_builder", "scheduler_builder",
+                  "logger_manager", "checkpoint_manager", "evaluator"):
+            plain[k] = {**(plain.get(k) or {})}
+            if plain[k].get("_name") is None:
+                plain[k]["_name"] = "base"
+        plain.setdefault("model_transforms", [])
+        recipe = ref_build("train_recipe", OmegaConf.create(plain))
+        if i == 0:
+            orig = recipe.build_model
 
-    def keep_initial_weights(*a, **k):
-        m = orig(*a, **k)
-        torch.save({n: v.detach().clone() for n, v in m.state_dict().items()}, init_file)
-        return m
+            def keep_initial_weights(*a, _orig=orig, **k):
+                m = _orig(*a, **k)
+                torch.save({n: v.detach().clone() for n, v in m.state_dict().items()}, init_file)
+                return m
 
-    recipe.build_model = keep_initial_weights
-    recipe.run()
+            recipe.build_model = keep_initial_weights
+        recipe.run()
     # this package's recipe, started from the same weights
     from optimus_dl_b200.core.config_utils import non_resolving_instantiate
     from optimus_dl_b200.core.registry import build
     import optimus_dl_b200.recipe.train  # noqa: F401
 
-    cfg = compose.compose(cfg_dir, "train_llama_shakespeare", overrides("ours"))
-    cfg.model_transforms = [{"_name": "load_weights", "checkpoint_path": init_file}]
-    build("train_recipe", non_resolving_instantiate(cfg)).run()
+    for phase in (phases or [[]]):
+        cfg = compose.compose(cfg_dir, "train_llama_shakespeare", overrides("ours") + phase)
+        cfg.model_transforms = [{"_name": "load_weights", "checkpoint_path": init_file}]
+        build("train_recipe", non_resolving_instantiate(cfg)).run()
 
     def logs(which):
         out = {}
@@ -334,7 +348,7 @@ def check_recipe() -> None:
         for k, v in a.items():
             if k.startswith("perf/") or k == "ms_spent_logging" or not isinstance(v, (int, float)):
                 continue
-            assert abs(v - b[k]) <= 1e-5 * max(1.0, abs(v)), (key, k, v, b[k])
+            assert abs(v - b[k]) <= tol * max(1.0, abs(v)), (key, k, v, b[k])
 
 
 if __name__ == "__main__":
