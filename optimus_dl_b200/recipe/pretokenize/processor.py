@@ -40,21 +40,23 @@ def _worker_encode(texts: list[str]) -> list[list[int]]:
     return [list(_WORKER_TOKENIZER.encode(t)) for t in texts]
 
 
-def shuffled(texts: Iterator[str], buffer_size: int, rng: random.Random) -> Iterator[str]:
-    """Streaming shuffle: keep ``buffer_size`` items, emit a random one for each new arrival."""
-    if buffer_size <= 1:
+def shuffled(texts: Iterator[str], buffer_size: int | None, init_seed: int) -> Iterator[str]:
+    """Block shuffle: collect ``buffer_size`` texts, shuffle them with a generator seeded ``init_seed + block index``,
+    hand them out, start the next block (the order optimus_dl/recipe/pretokenize/processor.py:70-90 produces, so
+    one seed gives the same shards in both code bases). ``None`` keeps the file's order."""
+    if buffer_size is None:
         yield from texts
         return
-    buf: list[str] = []
+    block, buf = 0, []
     for t in texts:
-        if len(buf) < buffer_size:
-            buf.append(t)
-            continue
-        i = rng.randrange(buffer_size)
-        yield buf[i]
-        buf[i] = t
-    rng.shuffle(buf)
-    yield from buf
+        buf.append(t)
+        if len(buf) >= buffer_size:
+            random.Random(init_seed + block).shuffle(buf)
+            yield from buf
+            block, buf = block + 1, []
+    if buf:
+        random.Random(init_seed + block).shuffle(buf)
+        yield from buf
 
 
 class TokenProcessor:
@@ -82,8 +84,9 @@ class TokenProcessor:
 
     # ------------------------------------------------------------------ iteration
     def _texts_of(self, idx: int) -> Iterator[str]:
-        rng = random.Random((int(self.config.processing.seed) * 1_000_003 + idx) & 0xFFFFFFFF)
-        return shuffled(self.reader.read_texts(self.files[idx]), int(self.config.processing.shuffle_buffer_size), rng)
+        size = self.config.processing.shuffle_buffer_size
+        return shuffled(self.reader.read_texts(self.files[idx]), int(size) if size is not None else None,
+                        idx * 100 + int(self.config.processing.seed))
 
     def _tokenizer_cfg(self) -> Any:
         t = self.config.tokenizer

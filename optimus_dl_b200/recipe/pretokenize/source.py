@@ -116,7 +116,9 @@ class FileFinder:
         if not files:
             logger.warning("no files found for split %r", self.config.split)
             return []
-        files = sorted(set(files))
+        # order before the shuffle as optimus_dl/recipe/pretokenize/source.py:60-97 leaves it: every pattern's matches
+        # sorted, the patterns one after the other
+        files = list(dict.fromkeys(files))
         random.Random(self.seed).shuffle(files)
         logger.info("%d files to process", len(files))
         return files

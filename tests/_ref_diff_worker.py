@@ -351,6 +351,69 @@ def check_recipe(extra: list[str] | None = None, tol: float = 1e-5, phases: list
             assert abs(v - b[k]) <= tol * max(1.0, abs(v)), (key, k, v, b[k])
 
 
+def check_pretokenize() -> None:
+    """Both data-preparation recipes on one local corpus (parquet and JSON-lines files, several output shards, two
+    tokenizer processes): the same shard files, byte for byte, and the same index. The reference lists and fetches
+    files through the hub client; here those two calls are pointed at the local directory, and its worker processes
+    are forked instead of spawned so that they see the same substitution."""
+    import hashlib
+    import multiprocessing as mp
+    from unittest.mock import patch
+
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+
+    from optimus_dl_b200.core import conf
+    from optimus_dl_b200.recipe.pretokenize import DataPrepConfig, DataPrepRecipe
+
+    tmp = tempfile.mkdtemp()
+    src = os.path.join(tmp, "repo")
+    os.makedirs(os.path.join(src, "data"))
+    rng = np.random.default_rng(0)
+    for f in range(3):
+        texts = ["doc %d-%d " % (f, i) + "lorem ipsum " * int(rng.integers(1, 40)) for i in range(1500)]
+        pq.write_table(pa.table({"text": texts}), os.path.join(src, "data", f"train-{f:05d}-of-00003.parquet"))
+    with open(os.path.join(src, "data", "train_extra.jsonl"), "w") as fh:
+        for i in range(50):
+            fh.write(json.dumps({"text": f"json line {i} " + "x y z " * (i % 9)}) + "\n")
+
+    def cfg(out):
+        return {"dataset": {"repo_id": src, "split": "train", "config_name": None, "cache_dir": None, "file_pattern": None},
+                "processing": {"shard_size_mb": 1, "shuffle_buffer_size": 500, "text_column": "text", "seed": 42,
+                               "dtype": "uint16", "num_proc": 2},
+                "output": {"dir": out, "name": "shard"}, "tokenizer": {"_name": "char_tokenize"}}
+
+    def digest(d):
+        out = {}
+        for f in sorted(os.listdir(d)):
+            if f.endswith(".npy"):
+                a = np.load(os.path.join(d, f))
+                out[f] = (a.dtype.str, a.shape, hashlib.sha1(a.tobytes()).hexdigest())
+            elif f == "index.json":
+                j = json.load(open(os.path.join(d, f)))
+                out[f] = (j["files"], j["total_tokens"])
+        return out
+
+    DataPrepRecipe(conf.merge(conf.create(DataPrepConfig()), conf.create(cfg(os.path.join(tmp, "ours"))))).run()
+    rr = importlib.import_module("optimus_dl.recipe.pretokenize.recipe")
+    rs = importlib.import_module("optimus_dl.recipe.pretokenize.source")
+    rp = importlib.import_module("optimus_dl.recipe.pretokenize.processor")
+    rc = importlib.import_module("optimus_dl.recipe.pretokenize.config")
+
+    def list_files(repo_id, repo_type=None, **_):
+        return sorted(os.path.relpath(os.path.join(r, f), repo_id) for r, _d, fs in os.walk(repo_id) for f in fs)
+
+    def download(repo_id, filename, repo_type=None, cache_dir=None, **_):
+        return os.path.join(repo_id, filename)
+
+    get_context = mp.get_context
+    with patch.object(rs, "list_repo_files", list_files), patch.object(rs, "hf_hub_download", download), \
+            patch.object(rp, "hf_hub_download", download), patch.object(mp, "get_context", lambda method=None: get_context("fork")):
+        rr.DataPrepRecipe(OmegaConf.merge(OmegaConf.structured(rc.DataPrepConfig), OmegaConf.create(cfg(os.path.join(tmp, "ref"))))).run()
+    a, b = digest(os.path.join(tmp, "ref")), digest(os.path.join(tmp, "ours"))
+    assert len(a) >= 5 and a == b, [k for k in set(a) | set(b) if a.get(k) != b.get(k)]
+
+
 if __name__ == "__main__":
     name = sys.argv[1]
     globals()["check_" + name]()
