@@ -351,6 +351,95 @@ def check_recipe(extra: list[str] | None = None, tol: float = 1e-5, phases: list
             assert abs(v - b[k]) <= tol * max(1.0, abs(v)), (key, k, v, b[k])
 
 
+def check_generation() -> None:
+    """The ``generation`` metric source: greedy, with an end-of-sequence token, and sampled (temperature, top-k,
+    top-p) under the same torch seed give the same tokens, for a rotary, a learned-position and a sliding-window
+    model (this package decodes with a key/value cache, the reference re-runs the prefix)."""
+    from optimus_dl_b200.metrics.source import build_metric_source
+
+    ref_build = importlib.import_module("optimus_dl.modules.metrics.source").build_metric_source
+    for name in ("llama2", "gpt2", "olmo3"):
+        ref, ours = _pair(MODELS[name])
+        ref.eval(), ours.eval()
+        for scfg in (dict(_name="generation", max_new_tokens=12), dict(_name="generation", max_new_tokens=12, eos_token_id=3),
+                     dict(_name="generation", max_new_tokens=8, do_sample=True, temperature=0.8, top_k=5),
+                     dict(_name="generation", max_new_tokens=8, do_sample=True, temperature=1.3, top_p=0.7)):
+            x = torch.randint(0, 97, (3, 9))
+            torch.manual_seed(1)
+            a = ref_build(OmegaConf.create(scfg))({}, model=ref, batch={"input_ids": x.clone()})
+            torch.manual_seed(1)
+            b = build_metric_source(dict(scfg))({}, model=ours, batch={"input_ids": x.clone()})
+            assert sorted(a) == sorted(b) and all(torch.equal(a[k], b[k]) for k in a), (name, scfg)
+
+
+def check_metrics_recipe() -> None:
+    """The metrics recipe (model from a config, criterion, one evaluation dataset, a source group and a bare metric)
+    from the same weights: the same result keys and values, and the same logger group / file / step."""
+    import glob
+
+    import optimus_dl.recipe.metrics.base  # noqa: F401
+    from optimus_dl.core.registry import build as ref_build
+    from optimus_dl_b200.core import conf
+    from optimus_dl_b200.core.config_utils import non_resolving_instantiate
+    from optimus_dl_b200.core.registry import build
+    import optimus_dl_b200.recipe.metrics  # noqa: F401
+
+    tmp = tempfile.mkdtemp()
+    data, init_file = os.path.join(tmp, "d.txt"), os.path.join(tmp, "init.pt")
+    with open(data, "w") as f:
+        f.write("".join(f"Line {i}: some text to score, number {i * i}.\n" for i in range(300)))
+
+    def cfg(which):
+        return {"_name": "base", "args": {},
+                "common": {"name": "m", "seed": 42, "data_seed": 42, "output_path": f"{tmp}/{which}", "checkpoint_path": None,
+                           "use_gpu": False, "max_iterations": 3, "distributed": {"tp_size": 1, "sharding_world_size": 1}},
+                "model": {"_name": "llama2", "n_layer": 1, "n_head": 2, "n_embd": 32, "vocab_size": 264, "sequence_length": 64,
+                          "multiple_of": 8},
+                "criterion": {"_name": "cross_entropy"},
+                "data": {"eval_datasets": {"txt": {"source": {"_name": "txt_lines", "file_link": data},
+                                                   "transform": {"_name": "compose", "transforms": [
+                                                       {"_name": "tokenize", "tokenizer_config": {"_name": "char_tokenize"},
+                                                        "worker_cfg": {"num_workers": 0}},
+                                                       {"_name": "chunk_tokens", "max_seq_len": 32},
+                                                       {"_name": "flat_batcher", "batch_size": 4, "seq_len": 32},
+                                                       {"_name": "to_device"}]}}}},
+                "metrics": {"txt": [{"_name": "source_group", "prefix": "lm", "sources": {"lm": {"_name": "causal_lm"}},
+                                     "metrics": [{"_name": "accuracy"}, {"_name": "perplexity"}, {"_name": "loss"}]},
+                                    {"_name": "accuracy"}]},
+                "model_transforms": [], "loggers": [{"_name": "jsonl", "output_dir": f"{tmp}/{which}/logs"}]}
+
+    c = cfg("ref")
+    for k in ("model_builder", "criterion_builder", "data_builder", "logger_manager", "checkpoint_manager", "evaluator"):
+        c[k] = {"_name": "base"}
+    rec = ref_build("metrics_recipe", OmegaConf.create(c))
+    orig = rec.model_builder.build_model
+
+    def keep(*a, **k):
+        m = orig(*a, **k)
+        torch.save(m.state_dict(), init_file)
+        return m
+
+    rec.model_builder.build_model = keep
+    r = rec.run()
+    c = cfg("ours")
+    c["model_transforms"] = [{"_name": "load_weights", "checkpoint_path": init_file}]
+    o = build("metrics_recipe", non_resolving_instantiate(conf.create(c))).run()
+    assert sorted(r) == sorted(o) == ["metrics/txt"]
+    a, b = r["metrics/txt"], o["metrics/txt"]
+    assert set(a) == set(b) and "lm/perplexity_metric/perplexity" in a and "accuracy_metric/total" in a, sorted(set(a) ^ set(b))
+    for k, v in a.items():
+        if not k.startswith("perf/") and k != "ms_spent_logging" and isinstance(v, (int, float)):
+            assert abs(v - b[k]) <= 1e-6 * max(1.0, abs(v)), (k, v, b[k])
+
+    def logged(which):
+        out = set()
+        for f in glob.glob(f"{tmp}/{which}/logs/**/*.jsonl", recursive=True):
+            out |= {(os.path.basename(f), json.loads(line)["group"], json.loads(line)["step"]) for line in open(f)}
+        return out
+
+    assert logged("ref") == logged("ours") == {("metrics_eval_metrics_txt.jsonl", "eval/metrics/txt", 0)}
+
+
 def check_pretokenize() -> None:
     """Both data-preparation recipes on one local corpus (parquet and JSON-lines files, several output shards, two
     tokenizer processes): the same shard files, byte for byte, and the same index. The reference lists and fetches
