@@ -33,6 +33,15 @@ MODELS = {
                           multiple_of=8, use_qk_norm=True),
     "qwen3": dict(_name="qwen3", n_layer=2, n_head=4, n_kv_head=2, n_embd=64, head_dim=32, vocab_size=97, sequence_length=64,
                   intermediate_size=96),
+    "llama2_rope_llama3": dict(_name="llama2", n_layer=2, n_head=4, n_kv_head=2, n_embd=64, vocab_size=97, sequence_length=64,
+                               multiple_of=8, tie_word_embeddings=True,
+                               rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                                             "high_freq_factor": 4.0, "original_max_position_embeddings": 16}),
+    "llama2_rope_yarn": dict(_name="llama2", n_layer=2, n_head=4, n_kv_head=2, n_embd=64, vocab_size=97, sequence_length=64,
+                             multiple_of=8, bias=True, rope_theta=500000.0,
+                             rope_scaling={"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 16}),
+    "qwen3_bias": dict(_name="qwen3", n_layer=2, n_head=4, n_kv_head=2, n_embd=64, head_dim=32, vocab_size=97,
+                       sequence_length=64, intermediate_size=96, attention_bias=True),
     "olmo3": dict(_name="olmo3", n_layer=2, n_head=4, n_kv_head=2, n_embd=64, vocab_size=97, sequence_length=64,
                   intermediate_size=96, layer_types=["sliding_attention", "full_attention"], sliding_window=8),
 }
@@ -63,6 +72,16 @@ def check_models() -> None:
                 a = ref(x, document_ids=docs, position_ids=pos)["logits"]
                 b = ours(x, document_ids=docs, position_ids=pos)["logits"]
                 assert torch.allclose(a, b, atol=2e-6), name
+                # a flat (packed) batch described by cumulative lengths, and per-row valid lengths (positions past
+                # them are padding and not compared)
+                cu = torch.tensor([0, 7, 15, 24], dtype=torch.int32)
+                fpos = torch.cat([torch.arange(7), torch.arange(8), torch.arange(9)])[None]
+                a = ref(x[:1], cu_seqlens=cu, max_seqlen=9, position_ids=fpos)["logits"]
+                b = ours(x[:1], cu_seqlens=cu, max_seqlen=9, position_ids=fpos)["logits"]
+                assert torch.allclose(a, b, atol=2e-6), name
+            lens = torch.tensor([24, 13])
+            a, b = ref(x, seq_lens=lens)["logits"], ours(x, seq_lens=lens)["logits"]
+            assert torch.allclose(a[0], b[0], atol=2e-6) and torch.allclose(a[1, :13], b[1, :13], atol=2e-6), name
 
         def sig(groups):
             return [(tuple(sorted(k for k in g if k != "params")), len(g["params"]), g.get("weight_decay")) for g in groups]
@@ -82,7 +101,9 @@ def check_train_parts() -> None:
     ref, ours = _pair(MODELS["llama2"])
     rfake = importlib.import_module("optimus_dl.modules.distributed.fake").FakeCollective(0, 1)
     for ccfg in (dict(_name="cross_entropy"), dict(_name="cross_entropy", label_smoothing=0.1),
-                 dict(_name="cross_entropy", padding_token_id=5)):
+                 dict(_name="cross_entropy", padding_token_id=5),
+                 dict(_name="cross_entropy", logit_softcap=5.0, softcap_type="tanh"),
+                 dict(_name="cross_entropy", label_smoothing=0.2, logit_softcap=1.0, softcap_type="sigmoid")):
         rc = R("criterion").build_criterion(OmegaConf.create(ccfg), collective=rfake)
         c = oc.build_criterion(dict(ccfg), collective=FakeCollective(0, 1, torch.device("cpu")))
         x = torch.randint(0, 97, (3, 20))
@@ -91,6 +112,8 @@ def check_train_parts() -> None:
         with omb.meters_group("g", log_freq=1):
             l, _ = c(ours, {"input_ids": x.clone()})
         assert abs(rl.item() - l.item()) < 1e-6, ccfg
+        gr, g = torch.autograd.grad(rl, ref.lm_head.weight)[0], torch.autograd.grad(l, ours.lm_head.weight)[0]
+        assert torch.allclose(gr, g, atol=1e-7), ccfg
         a, b = rmb.compute_meters("g"), omb.compute_meters("g")
         a.pop("ms_spent_logging", None), b.pop("ms_spent_logging", None)
         assert set(a) == set(b), (sorted(a), sorted(b))
