@@ -194,4 +194,5 @@ def load_optimizer_state_dict(model: nn.Module, optimizer: Any, sd: dict[str, An
     if steps:
         optimizer.step_count = int(max(steps))
     for pg, saved in zip(optimizer.param_groups, sd.get("param_groups", [])):
-        pg.update({k: v for k, v in saved.items() if k != "params"})
+        # only what this optimizer keeps per group (a checkpoint also carries torch AdamW's other group keys)
+        pg.update({k: v for k, v in saved.items() if k != "params" and k in pg})
