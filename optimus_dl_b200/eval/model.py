@@ -33,8 +33,16 @@ def _args(request: Any) -> tuple:
 
 class LLMBaselinesModel(_LMBase):
     def __init__(self, model: torch.nn.Module, tokenizer: Any, tokenizer_config: Any = None,
-                 device: torch.device | str = "cpu", batch_size: int = 8, max_gen_toks: int = 256):
+                 device: torch.device | str = "cpu", batch_size: int = 8, max_gen_toks: int = 256,
+                 reference_scoring: bool = False):
+        """``reference_scoring``: score exactly as optimus_dl/modules/eval/model.py:69-165 does, for numbers that have
+        to be compared with runs of the reference: context and continuation are encoded separately WITH the
+        tokenizer's special tokens (so a BOS token sits between them), an empty context is left empty, and the
+        rolling log-likelihood does not score the first token. The default follows the harness's own conventions
+        (special tokens stripped from the pieces, an end-of-text token as the empty context, every token scored,
+        windows for texts longer than the model's context)."""
         super().__init__()
+        self.reference_scoring = bool(reference_scoring)
         self.model = model.eval()
         self.tokenizer = tokenizer
         self.tokenizer_config = tokenizer_config
@@ -112,6 +120,9 @@ class LLMBaselinesModel(_LMBase):
         pairs = []
         for r in requests:
             context, continuation = _args(r)[:2]
+            if self.reference_scoring:
+                pairs.append((list(self.tokenizer.encode(context)), list(self.tokenizer.encode(continuation))))
+                continue
             ctx = self.tok_encode(context) if context else []
             if not ctx:
                 ctx = [self.eot_token_id]
@@ -122,6 +133,10 @@ class LLMBaselinesModel(_LMBase):
         res = []
         for r in requests:
             (text,) = _args(r)[:1]
+            if self.reference_scoring:
+                raw = list(self.tokenizer.encode(text))
+                res.append(self._score([(raw[:1], raw[1:])])[0][0] if len(raw) > 1 else 0.0)
+                continue
             ids = self.tok_encode(text)
             total, prev = 0.0, [self.eot_token_id]
             # disjoint windows of at most max_length targets, each conditioned on the previous window's tail

@@ -50,7 +50,8 @@ class EvalRecipe:
             base = base.to(torch.bfloat16)
         self.tokenizer = build_tokenizer(c.tokenizer)
         self.model = LLMBaselinesModel(base.eval(), self.tokenizer, c.tokenizer, device=device,
-                                       batch_size=int(self.cfg.lm_eval.batch_size))
+                                       batch_size=int(self.cfg.lm_eval.batch_size),
+                                       reference_scoring=bool(self.cfg.lm_eval.get("reference_scoring", False)))
         return self.model
 
     def run_lm_eval(self) -> dict:

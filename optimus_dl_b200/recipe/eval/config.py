@@ -24,6 +24,7 @@ class LMEvalConfig:
     batch_size: int = 1
     limit: int | None = None
     output_path: str | None = None
+    reference_scoring: bool = False     # score as the reference's adapter does (see eval/model.py); not a reference field
 
 
 @dataclass

@@ -463,6 +463,30 @@ def check_metrics_recipe() -> None:
     assert logged("ref") == logged("ours") == {("metrics_eval_metrics_txt.jsonl", "eval/metrics/txt", 0)}
 
 
+def check_eval_adapter() -> None:
+    """The lm_eval adapter in ``reference_scoring`` mode returns the reference adapter's numbers (log-likelihood of a
+    continuation, greedy flag, rolling log-likelihood); the default mode follows the harness's conventions instead."""
+    from types import SimpleNamespace
+
+    import optimus_dl_b200.tokenizer as ot
+    from optimus_dl_b200.eval.model import LLMBaselinesModel
+
+    cfg = dict(MODELS["llama2"], vocab_size=264, sequence_length=128)
+    ref_model, our_model = _pair(cfg)
+    tcfg = {"_name": "char_tokenize"}
+    r = R("eval.model").LLMBaselinesModel(ref_model.eval(), R("tokenizer").build_tokenizer(OmegaConf.create(tcfg)),
+                                          OmegaConf.create(tcfg), device="cpu")
+    o = LLMBaselinesModel(our_model.eval(), ot.build_tokenizer(dict(tcfg)), dict(tcfg), device="cpu", reference_scoring=True)
+    reqs = [SimpleNamespace(args=("The quick brown", " fox jumps")), SimpleNamespace(args=("", "hello")),
+            SimpleNamespace(args=("abc" * 30, "def" * 10))]
+    for (a, ga), (b, gb) in zip(r.loglikelihood(reqs), o.loglikelihood(reqs)):
+        assert abs(a - b) < 1e-3 and ga == gb, (a, b)
+    rolling = [SimpleNamespace(args=("some longer text to roll over " * 3,)), SimpleNamespace(args=("x",))]
+    assert all(abs(a - b) < 1e-3 for a, b in zip(r.loglikelihood_rolling(rolling), o.loglikelihood_rolling(rolling)))
+    plain = LLMBaselinesModel(our_model.eval(), ot.build_tokenizer(dict(tcfg)), dict(tcfg), device="cpu")
+    assert abs(plain.loglikelihood(reqs[:1])[0][0] - o.loglikelihood(reqs[:1])[0][0]) > 1e-3      # a different convention
+
+
 def check_pretokenize() -> None:
     """Both data-preparation recipes on one local corpus (parquet and JSON-lines files, several output shards, two
     tokenizer processes): the same shard files, byte for byte, and the same index. The reference lists and fetches
