@@ -293,65 +293,77 @@ def check_recipe_resume() -> None:
     check_recipe(phases=[["optimization.iterations=4"], ["optimization.iterations=8"]])
 
 
-def check_recipe(extra: list[str] | None = None, tol: float = 1e-5, phases: list[list[str]] | None = None) -> None:
-    """The whole training recipe (8 iterations, evaluation every 4, checkpoints) from one composed config and the
-    same initial weights: every number either side logs (loss, perplexity, accuracy, gradient norm, learning rate,
-    token counts, metric-engine values; train and eval groups) agrees."""
-    import glob
+def _recipe_overrides(tmp: str, which: str, data: str, extra: list[str] | None) -> list[str]:
+    return [f"common.output_path={tmp}/{which}", "optimization.iterations=8", "common.save_freq=4", "common.log_freq=1",
+            "common.eval_freq=4", "++common.eval_iterations=2", "++common.use_gpu=false", "~model_transforms",
+            "optimization.amp.enabled=false", "data.train_datasets.source.inner._name=txt_lines",
+            f"+data.train_datasets.source.inner.file_link={data}", "data.eval_datasets.tinyshakespeare.source._name=txt_lines",
+            f"+data.eval_datasets.tinyshakespeare.source.file_link={data}", "++common.seed=42", "++common.data_seed=42",
+            "++common.deterministic=true", "++model.n_layer=1", "++model.n_head=2", "++model.n_embd=32",
+            "++model.intermediate_size=64", "lr_scheduler.warmup_steps=0", "args.batch_size=4", "args.seq_len=64",
+            "loggers.1.enabled=false", f"loggers.0.output_dir={tmp}/{which}/logs"] + list(extra or [])
 
-    from optimus_dl_b200.core import compose, conf
 
-    tmp = tempfile.mkdtemp()
+def _recipe_corpus(tmp: str) -> str:
     data = os.path.join(tmp, "data.txt")
-    with open(data, "w") as f:
-        for i in range(600):
-            f.write(f"Line {i}: This is some dummy text for training Llama, number {i * i}.\n")
+    if not os.path.exists(data):
+        with open(data + f".{os.getpid()}", "w") as f:
+            for i in range(600):
+                f.write(f"Line {i}: This is some dummy text for training Llama, number {i * i}.\n")
+        os.replace(data + f".{os.getpid()}", data)
+    return data
 
-    def overrides(which):
-        return [f"common.output_path={tmp}/{which}", "optimization.iterations=8", "common.save_freq=4", "common.log_freq=1",
-                "common.eval_freq=4", "++common.eval_iterations=2", "++common.use_gpu=false", "~model_transforms",
-                "optimization.amp.enabled=false", "data.train_datasets.source.inner._name=txt_lines",
-                f"+data.train_datasets.source.inner.file_link={data}", "data.eval_datasets.tinyshakespeare.source._name=txt_lines",
-                f"+data.eval_datasets.tinyshakespeare.source.file_link={data}", "++common.seed=42", "++common.data_seed=42",
-                "++common.deterministic=true", "++model.n_layer=1", "++model.n_head=2", "++model.n_embd=32",
-                "++model.intermediate_size=64", "lr_scheduler.warmup_steps=0", "args.batch_size=4", "args.seq_len=64",
-                "loggers.1.enabled=false", f"loggers.0.output_dir={tmp}/{which}/logs"] + list(extra or [])
 
-    cfg_dir = os.path.join(ROOT, "configs", "train")
-    init_file = os.path.join(tmp, "init.pt")
-    # the reference's recipe, on the fully resolved config (its own instantiate step needs OmegaConf internals)
+def _run_reference_recipe(tmp: str, extra: list[str] | None, phases: list[list[str]], transforms: list[dict]) -> None:
+    """The reference's recipe on the fully resolved config (its own instantiate step needs OmegaConf internals); the
+    weights it starts from are kept in ``init.pt`` for the other side."""
     import optimus_dl.recipe.train.base  # noqa: F401
     from optimus_dl.core.registry import build as ref_build
+    from optimus_dl_b200.core import compose, conf
     import optimus_dl_b200.core.config_utils  # noqa: F401  (registers the resolvers the config uses)
 
-    for i, phase in enumerate(phases or [[]]):
-        plain = conf.to_container(compose.compose(cfg_dir, "train_llama_shakespeare", overrides("ref") + phase), resolve=True)
+    data, init_file = _recipe_corpus(tmp), os.path.join(tmp, "init.pt")
+    for i, phase in enumerate(phases):
+        cfg = compose.compose(os.path.join(ROOT, "configs", "train"), "train_llama_shakespeare",
+                              _recipe_overrides(tmp, "ref", data, extra) + phase)
+        plain = conf.to_container(cfg, resolve=True)
         for k in ("model_builder", "optimizer_builder", "criterion_builder", "data_builder", "scheduler_builder",
                   "logger_manager", "checkpoint_manager", "evaluator"):
             plain[k] = {**(plain.get(k) or {})}
             if plain[k].get("_name") is None:
                 plain[k]["_name"] = "base"
-        plain.setdefault("model_transforms", [])
+        plain["model_transforms"] = list(transforms)
         recipe = ref_build("train_recipe", OmegaConf.create(plain))
         if i == 0:
             orig = recipe.build_model
 
             def keep_initial_weights(*a, _orig=orig, **k):
                 m = _orig(*a, **k)
-                torch.save({n: v.detach().clone() for n, v in m.state_dict().items()}, init_file)
+                if int(os.environ.get("RANK", 0)) == 0:
+                    inner = getattr(m, "module", m)
+                    torch.save({n: v.detach().clone() for n, v in inner.state_dict().items()}, init_file)
                 return m
 
             recipe.build_model = keep_initial_weights
         recipe.run()
-    # this package's recipe, started from the same weights
+
+
+def _run_our_recipe(tmp: str, extra: list[str] | None, phases: list[list[str]], transforms: list[dict]) -> None:
+    from optimus_dl_b200.core import compose
     from optimus_dl_b200.core.config_utils import non_resolving_instantiate
     from optimus_dl_b200.core.registry import build
     import optimus_dl_b200.recipe.train  # noqa: F401
 
-    for phase in (phases or [[]]):
-        cfg = compose.compose(cfg_dir, "train_llama_shakespeare", overrides("ours") + phase)
-        cfg.model_transforms = [{"_name": "load_weights", "checkpoint_path": init_file}]
+    data, init_file = _recipe_corpus(tmp), os.path.join(tmp, "init.pt")
+    for phase in phases:
+        cfg = compose.compose(os.path.join(ROOT, "configs", "train"), "train_llama_shakespeare",
+                              _recipe_overrides(tmp, "ours", data, extra) + phase)
+        cfg.model_transforms = [{"_name": "load_weights", "checkpoint_path": init_file}] + list(transforms)
         build("train_recipe", non_resolving_instantiate(cfg)).run()
+
+
+def _compare_recipe_logs(tmp: str, tol: float) -> None:
+    import glob
 
     def logs(which):
         out = {}
@@ -372,6 +384,28 @@ def check_recipe(extra: list[str] | None = None, tol: float = 1e-5, phases: list
             if k.startswith("perf/") or k == "ms_spent_logging" or not isinstance(v, (int, float)):
                 continue
             assert abs(v - b[k]) <= tol * max(1.0, abs(v)), (key, k, v, b[k])
+
+
+def check_recipe(extra: list[str] | None = None, tol: float = 1e-5, phases: list[list[str]] | None = None) -> None:
+    """The whole training recipe (8 iterations, evaluation every 4, checkpoints) from one composed config and the
+    same initial weights: every number either side logs (loss, perplexity, accuracy, gradient norm, learning rate,
+    token counts, metric-engine values; train and eval groups) agrees."""
+    tmp = tempfile.mkdtemp()
+    _run_reference_recipe(tmp, extra, phases or [[]], [])
+    _run_our_recipe(tmp, extra, phases or [[]], [])
+    _compare_recipe_logs(tmp, tol)
+
+
+def check_recipe_ddp_side() -> None:
+    """One side (``ref`` / ``ours`` / ``compare``) of the two-rank variant: each recipe runs under its own ``torchrun``
+    with the ``ddp`` transform, in the directory named on the command line."""
+    side, tmp = sys.argv[2], sys.argv[3]
+    if side == "ref":
+        _run_reference_recipe(tmp, None, [[]], [{"_name": "ddp"}])
+    elif side == "ours":
+        _run_our_recipe(tmp, None, [[]], [{"_name": "ddp"}])
+    else:
+        _compare_recipe_logs(tmp, 1e-5)
 
 
 def check_generation() -> None:

@@ -33,3 +33,19 @@ def test_same_inputs_give_the_same_results_as_the_reference(check):
     res = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "_ref_diff_worker.py"), check], capture_output=True,
                          text=True, timeout=900, env=dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=ROOT))
     assert res.returncode == 0 and f"DIFF_OK {check}" in res.stdout, res.stdout[-1500:] + res.stderr[-3000:]
+
+
+@pytest.mark.skipif(not _have_tree(), reason="reference tree not present")
+def test_two_rank_ddp_recipe_logs_the_same_numbers_as_the_reference(tmp_path, unique_port):
+    """The training recipe on two Gloo ranks with the ``ddp`` transform, each code base under its own ``torchrun``:
+    per-rank data shares, gradient averaging and the cross-rank aggregation of meters give the same log records."""
+    worker = os.path.join(ROOT, "tests", "_ref_diff_worker.py")
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=ROOT)
+    for i, side in enumerate(("ref", "ours")):
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+               "--master-port", str(unique_port + i), worker, "recipe_ddp_side", side, str(tmp_path)]
+        res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+        assert res.returncode == 0 and res.stdout.count("DIFF_OK") == 2, res.stdout[-1500:] + res.stderr[-3000:]
+    res = subprocess.run([sys.executable, worker, "recipe_ddp_side", "compare", str(tmp_path)], capture_output=True, text=True,
+                         timeout=300, env=env)
+    assert res.returncode == 0 and "DIFF_OK" in res.stdout, res.stdout[-1500:] + res.stderr[-3000:]
