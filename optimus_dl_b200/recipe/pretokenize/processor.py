@@ -67,16 +67,29 @@ class TokenProcessor:
         self.num_proc = max(int(config.processing.num_proc), 1)
         self.file_idx = 0
         self.docs_in_file = 0
+        self.total_docs_yielded = 0
         self._pool = None
         self._tokenizer = None
 
     # ------------------------------------------------------------------ state
     def get_state(self) -> dict[str, Any]:
-        return {"file_idx": self.file_idx, "docs_in_file": self.docs_in_file}
+        """Position under the reference's keys (optimus_dl/recipe/pretokenize/processor.py:237-247): the file being
+        read, the index of the last document taken from it (``None`` before the first) and the running total; an
+        interrupted run can be continued by either code base. ``file_idx`` / ``docs_in_file`` say the same in this
+        package's earlier spelling."""
+        return {"yielded_doc_idx": self.docs_in_file - 1 if self.docs_in_file > 0 else None,
+                "yielded_file_idx": self.file_idx, "total_docs_yielded": self.total_docs_yielded,
+                "file_idx": self.file_idx, "docs_in_file": self.docs_in_file}
 
     def load_state(self, state: dict[str, Any]) -> None:
-        self.file_idx = int(state.get("file_idx", 0))
-        self.docs_in_file = int(state.get("docs_in_file", 0))
+        if "yielded_file_idx" in state:
+            self.file_idx = int(state.get("yielded_file_idx") or 0)
+            last = state.get("yielded_doc_idx")
+            self.docs_in_file = int(last) + 1 if last is not None else 0
+        else:
+            self.file_idx = int(state.get("file_idx", 0))
+            self.docs_in_file = int(state.get("docs_in_file", 0))
+        self.total_docs_yielded = int(state.get("total_docs_yielded", 0))
 
     @property
     def progress(self) -> int:
@@ -127,6 +140,7 @@ class TokenProcessor:
                         continue
                     self.docs_in_file = n + 1
                     if toks:
+                        self.total_docs_yielded += 1
                         yield toks
                 self.file_idx += 1
                 self.docs_in_file = 0
