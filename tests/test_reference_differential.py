@@ -41,9 +41,16 @@ def test_two_rank_ddp_recipe_logs_the_same_numbers_as_the_reference(tmp_path, un
     per-rank data shares, gradient averaging and the cross-rank aggregation of meters give the same log records."""
     worker = os.path.join(ROOT, "tests", "_ref_diff_worker.py")
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=ROOT)
-    for i, side in enumerate(("ref", "ours")):
+    import socket
+
+    for side in ("ref", "ours"):
+        port = unique_port
+        if side == "ours":                         # a second free port for the second launch
+            with socket.socket() as s:
+                s.bind(("127.0.0.1", 0))
+                port = s.getsockname()[1]
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-               "--master-port", str(unique_port + i), worker, "recipe_ddp_side", side, str(tmp_path)]
+               "--master-port", str(port), worker, "recipe_ddp_side", side, str(tmp_path)]
         res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
         assert res.returncode == 0 and res.stdout.count("DIFF_OK") == 2, res.stdout[-1500:] + res.stderr[-3000:]
     res = subprocess.run([sys.executable, worker, "recipe_ddp_side", "compare", str(tmp_path)], capture_output=True, text=True,
