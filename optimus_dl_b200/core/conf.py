@@ -372,6 +372,19 @@ class ListNode(Node, MutableSequence):
     def copy(self) -> "ListNode":
         return copy.deepcopy(self)
 
+    # concatenation with lists and other list nodes, as ``ListConfig`` allows (``[0.0] + cfg.points``); the result
+    # is a detached list node of the resolved items
+    def __add__(self, other: Any) -> "ListNode":
+        if not isinstance(other, (list, tuple, ListNode)):
+            return NotImplemented
+        return ListNode(list(to_container(self, resolve=True)) + list(to_container(other, resolve=True)
+                                                                     if isinstance(other, ListNode) else other))
+
+    def __radd__(self, other: Any) -> "ListNode":
+        if not isinstance(other, (list, tuple)):
+            return NotImplemented
+        return ListNode(list(other) + list(to_container(self, resolve=True)))
+
     def __getstate__(self):
         return {"data": to_container(self, resolve=False)}
 
