@@ -521,6 +521,38 @@ def check_eval_adapter() -> None:
     assert abs(plain.loglikelihood(reqs[:1])[0][0] - o.loglikelihood(reqs[:1])[0][0]) > 1e-3      # a different convention
 
 
+def check_schedules() -> None:
+    """Every learning-rate schedule over its whole length, two parameter groups, two run lengths: the same rate at
+    every step (about 200 configurations: all WSD decay shapes, warm-up lengths, final factors, piecewise-linear
+    waypoints, a lowered cool-down start, cosine annealing, linear warm-up)."""
+    import itertools
+
+    import optimus_dl_b200.lr_scheduler as ol
+
+    def opt():
+        return torch.optim.SGD([{"params": [torch.nn.Parameter(torch.zeros(1))], "lr": 0.3},
+                                {"params": [torch.nn.Parameter(torch.zeros(1))], "lr": 0.01}], lr=0.1)
+
+    cfgs = [dict(_name="wsd", warmup_steps=w, fract_decay=fd, decay_type=dt, final_lr_factor=f, init_div_factor=idv, **extra)
+            for w, fd, dt, f, idv in itertools.product((0, 7), (0.1, 0.5), ("linear", "cosine", "exp", "miror_cosine", "square", "sqrt"),
+                                                       (0.0, 0.1), (25, 100))
+            for extra in ({}, {"sqrt_power": 0.3} if dt == "sqrt" else {})]
+    cfgs += [dict(_name="wsd", warmup_steps=5, fract_decay=0.4, decay_type="linear_pw", linear_pw_subdivisions=[0.5, 0.2], final_lr_factor=0.05),
+             dict(_name="wsd", warmup_steps=None, warmup_steps_fraction=0.1, fract_decay=0.3, cooldown_start_lr_factor=0.7),
+             dict(_name="cosine_annealing", eta_min=0.01), dict(_name="cosine_annealing", T_max=13),
+             dict(_name="linear_warmup", warmup_steps=9, start_lr=0.001), dict(_name="linear_warmup", warmup_steps=0)]
+    for c in cfgs:
+        for iters in (40, 101):
+            a, b = opt(), opt()
+            ra = R("lr_scheduler").build_lr_scheduler(OmegaConf.create(c), optimizer=a, iterations=iters)
+            rb = ol.build_lr_scheduler(dict(c), optimizer=b, iterations=iters)
+            for step in range(iters + 5):
+                la, lb = [g["lr"] for g in a.param_groups], [g["lr"] for g in b.param_groups]
+                assert all(abs(x - y) <= 1e-12 * max(1.0, abs(x)) for x, y in zip(la, lb)), (c, iters, step, la, lb)
+                a.step(), b.step(), ra.step(), rb.step()
+            assert ra.state_dict().keys() == rb.state_dict().keys(), c
+
+
 def check_pretokenize() -> None:
     """Both data-preparation recipes on one local corpus (parquet and JSON-lines files, several output shards, two
     tokenizer processes): the same shard files, byte for byte, and the same index. The reference lists and fetches
