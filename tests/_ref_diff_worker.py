@@ -521,6 +521,39 @@ def check_eval_adapter() -> None:
     assert abs(plain.loglikelihood(reqs[:1])[0][0] - o.loglikelihood(reqs[:1])[0][0]) > 1e-3      # a different convention
 
 
+def check_optimizer_routing() -> None:
+    """Which parameters each sub-optimizer of ``muon`` and of a ``composite`` configuration receives, with which
+    group settings; the composite then takes the same steps from the same gradients and exports the same state keys."""
+    import optimus_dl_b200.optim as oo
+
+    def routing(opt, model):
+        names = {id(p): n for n, p in model.named_parameters()}
+        return {f"{k}:{type(o).__name__}": [(sorted(names[id(p)] for p in g["params"]),
+                                             {a: b for a, b in g.items() if a in ("lr", "weight_decay")}) for g in o.param_groups]
+                for k, o in opt.optimizers.items()}
+
+    composite = dict(_name="composite", optimizers={
+        "a_attn": {"params_regexp": ".*attn.*", "optimizer_config": {"_name": "adamw", "lr": 1e-3}},
+        "b_mlp": {"params_regexp": ".*mlp\\.w.*", "optimizer_config": {"_name": "soap", "lr": 3e-3}},
+        "z_rest": {"params_regexp": None, "optimizer_config": {"_name": "adamw", "lr": 2e-3, "weight_decay": 0.0}}})
+    for ocfg in (dict(_name="muon", lr=1e-2, weight_decay=0.1), composite):
+        ref, ours = _pair(MODELS["llama2"])
+        ro = R("optim").build_optimizer(OmegaConf.create(ocfg), params=ref.make_parameter_groups())
+        o = oo.build_optimizer(dict(ocfg), params=ours.make_parameter_groups())
+        assert routing(ro, ref) == routing(o, ours), ocfg["_name"]
+        if ocfg["_name"] != "composite":
+            continue
+        g = torch.Generator().manual_seed(1)
+        for _ in range(3):
+            x = torch.randint(0, 97, (8, 32), generator=g)
+            ref(x)["logits"].float().logsumexp(-1).mean().backward()
+            for p, q in zip(ref.parameters(), ours.parameters()):
+                q.grad = p.grad.clone()
+            ro.step(), o.step(), ro.zero_grad(), o.zero_grad()
+        assert max((p - q).abs().max().item() for p, q in zip(ref.parameters(), ours.parameters())) < 1e-4
+        assert sorted(ro.state_dict()) == sorted(o.state_dict())
+
+
 def check_schedules() -> None:
     """Every learning-rate schedule over its whole length, two parameter groups, two run lengths: the same rate at
     every step (about 200 configurations: all WSD decay shapes, warm-up lengths, final factors, piecewise-linear

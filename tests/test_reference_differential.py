@@ -18,7 +18,7 @@ def _have_tree() -> bool:
 
 
 @pytest.mark.skipif(not _have_tree(), reason="reference tree not present")
-@pytest.mark.parametrize("check", ["models", "train_parts", "data", "checkpoints", "recipe", "recipe_accumulation", "recipe_resume", "pretokenize", "generation", "metrics_recipe", "eval_adapter", "schedules"])
+@pytest.mark.parametrize("check", ["models", "train_parts", "data", "checkpoints", "recipe", "recipe_accumulation", "recipe_resume", "pretokenize", "generation", "metrics_recipe", "eval_adapter", "schedules", "optimizer_routing"])
 def test_same_inputs_give_the_same_results_as_the_reference(check):
     """``models``: logits and parameter groups of every model family from shared weights, plain and packed batches;
     ``train_parts``: criterion loss and meters, AdamW and SOAP under every schedule; ``data``: identical batches and
@@ -29,7 +29,8 @@ def test_same_inputs_give_the_same_results_as_the_reference(check):
     then a second run that resumes from the checkpoint and continues to eight; ``pretokenize``: the data-preparation
     recipe writes byte-identical shards and the same index; ``generation``: greedy and seeded sampled decoding give
     the same tokens; ``metrics_recipe``: the metrics recipe's results and log records; ``eval_adapter``:
-    the lm_eval adapter's scores in its reference-scoring mode; ``schedules``: every learning-rate schedule, step by step."""
+    the lm_eval adapter's scores in its reference-scoring mode; ``schedules``: every learning-rate schedule, step by step;
+    ``optimizer_routing``: which parameters Muon's and a composite's sub-optimizers get."""
     res = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "_ref_diff_worker.py"), check], capture_output=True,
                          text=True, timeout=900, env=dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=ROOT))
     assert res.returncode == 0 and f"DIFF_OK {check}" in res.stdout, res.stdout[-1500:] + res.stderr[-3000:]
